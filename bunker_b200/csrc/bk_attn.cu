@@ -1,0 +1,415 @@
+// bk_attn.cu -- split-KV flash-decode GQA attention over a bf16 KV cache.
+//
+// Replaces bunker's single-tile decode attention (emitFA2Attn, src/emitters.ts:188-226;
+// buildFA2Attn, prototypes/decode.ts:427-468), whose cache is capped at 128 rows and
+// replicated per query head.  Here the cache is per KV head, [B][Hkv][max_len][256],
+// and a (batch, KV head) pair is cut into splits of split_len rows, one CTA each, so
+// every SM streams K/V.  The same kernel applies the q/k head RMSNorm and the partial
+// rotary (emitQNorm/emitKNorm/emitRoPE/emitRoPEK, src/emitters.ts:123-183) and appends
+// the new K/V row, so one launch replaces five of the reference's.
+//
+// Per split: scores for all rows (each K row is read once for the G query heads of
+// the group), exact max, p = exp(s-m), then o = sum p*V with each V row read once.
+// A second kernel merges the splits and applies the sigmoid output gate.
+// Orders are fixed (see the CPU checker): lane l owns dims [8l,8l+8); row jj of a
+// split belongs to warp jj mod 8; warps and splits are added in ascending order.
+#include "bk_common.cuh"
+#include "bk_internal.h"
+
+namespace {
+
+constexpr int kW = 8;        // warps per split CTA
+constexpr int kHD = 256;     // head dim (8 per lane)
+constexpr int kMaxSplits = 1024;
+
+struct AttnParams {
+  const uint16_t* qg;
+  const uint16_t* k;
+  const uint16_t* v;
+  const uint16_t* q_norm_w;
+  const uint16_t* k_norm_w;
+  const float* cos_t;
+  const float* sin_t;
+  uint16_t* k_cache;
+  uint16_t* v_cache;
+  const int32_t* pos;
+  uint16_t* out;
+  float* scratch;
+  const uint16_t* gate;
+  int B, Hq, Hkv, rot_half, max_len, split_len, max_splits, fused;
+  float scale;
+};
+
+__device__ __forceinline__ void bf16x8_to_f32(uint4 v, float (&y)[8]) {
+  y[0] = __uint_as_float(v.x << 16);
+  y[1] = __uint_as_float(v.x & 0xffff0000u);
+  y[2] = __uint_as_float(v.y << 16);
+  y[3] = __uint_as_float(v.y & 0xffff0000u);
+  y[4] = __uint_as_float(v.z << 16);
+  y[5] = __uint_as_float(v.z & 0xffff0000u);
+  y[6] = __uint_as_float(v.w << 16);
+  y[7] = __uint_as_float(v.w & 0xffff0000u);
+}
+
+// head RMSNorm*(1+w) -> bf16 -> rotary on the first 2*rot_half dims, result in `stage`
+__device__ __forceinline__ void norm_rope_256(const uint16_t* src, const uint16_t* w, const float* cos_row,
+                                              const float* sin_row, int rot_half, uint16_t* stage) {
+  const int lane = threadIdx.x & 31;
+  float x[8], wv[8];
+  bf16x8_to_f32(*reinterpret_cast<const uint4*>(src + lane * 8), x);
+  bf16x8_to_f32(*reinterpret_cast<const uint4*>(w + lane * 8), wv);
+  float acc = 0.0f;
+#pragma unroll
+  for (int e = 0; e < 8; e++) acc = fmaf(x[e], x[e], acc);
+  acc = bk_warp_sum(acc);
+  float rstd = bk_rcp_sqrt(__fadd_rn(__fdiv_rn(acc, (float)kHD), 1e-6f));
+#pragma unroll
+  for (int e = 0; e < 8; e++)
+    stage[lane * 8 + e] = bk_f32_to_bf16(__fmul_rn(__fmul_rn(x[e], rstd), __fadd_rn(1.0f, wv[e])));
+  __syncwarp();
+  for (int i = lane; i < rot_half; i += 32) {
+    float x1 = bk_bf16_to_f32(stage[i]), x2 = bk_bf16_to_f32(stage[i + rot_half]);
+    float c = cos_row[i], s = sin_row[i];
+    uint16_t r1 = bk_f32_to_bf16(__fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s)));
+    uint16_t r2 = bk_f32_to_bf16(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s)));
+    stage[i] = r1;
+    stage[i + rot_half] = r2;
+  }
+  __syncwarp();
+}
+
+// Sum 8 per-lane values over the warp with 9 shuffles instead of 40: at each of the
+// first three levels a lane keeps half of its values and trades the other half with
+// its xor partner.  The additions are the butterfly's, so the bits are too.
+// On return lane l holds the total of value index 4*bit4(l) + 2*bit3(l) + bit2(l).
+__device__ __forceinline__ float warp_sum8(const float (&v)[8]) {
+  const int lane = threadIdx.x & 31;
+  const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
+  float w[4], x[2];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    float send = b4 ? v[i] : v[i + 4];
+    float keep = b4 ? v[i + 4] : v[i];
+    w[i] = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, 16));
+  }
+#pragma unroll
+  for (int i = 0; i < 2; i++) {
+    float send = b3 ? w[i] : w[i + 2];
+    float keep = b3 ? w[i + 2] : w[i];
+    x[i] = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, 8));
+  }
+  float send = b2 ? x[0] : x[1];
+  float keep = b2 ? x[1] : x[0];
+  float y = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, 4));
+  y = __fadd_rn(y, __shfl_xor_sync(0xffffffffu, y, 2));
+  y = __fadd_rn(y, __shfl_xor_sync(0xffffffffu, y, 1));
+  return y;
+}
+
+// dynamic shared memory layout (bytes):
+//   q_st  : 8*256 bf16                 4096
+//   k_st  : 256 bf16                    512
+//   m_s   : 8 f32 (+8 spare)             64
+//   l_s   : kW*8 f32                    256
+//   s_s   : split_len*8 f32
+//   o_s   : kW*8*256 f32              65536
+template <int G>
+__global__ void __launch_bounds__(kW * 32) attn_split_kernel(const AttnParams p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  uint16_t* q_st = reinterpret_cast<uint16_t*>(smem);
+  uint16_t* k_st = q_st + 8 * kHD;
+  float* m_s = reinterpret_cast<float*>(k_st + kHD);
+  float* l_s = m_s + 16;
+  float* s_s = l_s + kW * 8;
+  float* o_s = s_s + (size_t)p.split_len * 8;
+
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int pos = p.pos[b];
+  const int n = pos + 1;
+  const int j0 = split * p.split_len;
+  if (j0 >= n) return;
+  const int ns = min(n, j0 + p.split_len) - j0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+  uint16_t* Kb = p.k_cache + ((size_t)b * p.Hkv + kvh) * (size_t)p.max_len * kHD;
+  uint16_t* Vb = p.v_cache + ((size_t)b * p.Hkv + kvh) * (size_t)p.max_len * kHD;
+
+  // ---- phase 0: q (and, in the split that owns row pos, k/v append) ----
+  if (p.fused) {
+    const float* cr = p.cos_t + (size_t)pos * p.rot_half;
+    const float* sr = p.sin_t + (size_t)pos * p.rot_half;
+    if (warp < G) {
+      const uint16_t* src = p.qg + ((size_t)b * p.Hq + kvh * G + warp) * 2 * kHD;
+      norm_rope_256(src, p.q_norm_w, cr, sr, p.rot_half, q_st + warp * kHD);
+    }
+    if (warp == kW - 1 && pos >= j0 && pos < j0 + ns) {
+      norm_rope_256(p.k + ((size_t)b * p.Hkv + kvh) * kHD, p.k_norm_w, cr, sr, p.rot_half, k_st);
+      *reinterpret_cast<uint4*>(Kb + (size_t)pos * kHD + lane * 8) = *reinterpret_cast<const uint4*>(k_st + lane * 8);
+      *reinterpret_cast<uint4*>(Vb + (size_t)pos * kHD + lane * 8) =
+          *reinterpret_cast<const uint4*>(p.v + ((size_t)b * p.Hkv + kvh) * kHD + lane * 8);
+    }
+  } else {
+    if (warp < G)
+      *reinterpret_cast<uint4*>(q_st + warp * kHD + lane * 8) =
+          *reinterpret_cast<const uint4*>(p.qg + ((size_t)b * p.Hq + kvh * G + warp) * kHD + lane * 8);
+  }
+  __syncthreads();  // the appended K/V row is visible to this CTA from here on
+
+  // ---- phase 1: scores ----
+  {
+    float qf[G][8];
+#pragma unroll
+    for (int g = 0; g < G; g++) bf16x8_to_f32(*reinterpret_cast<const uint4*>(q_st + g * kHD + lane * 8), qf[g]);
+    const int hsel = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+    for (int jj = warp; jj < ns; jj += 2 * kW) {
+      const int jj2 = jj + kW;
+      const bool has2 = jj2 < ns;
+      uint4 ka = *reinterpret_cast<const uint4*>(Kb + (size_t)(j0 + jj) * kHD + lane * 8);
+      uint4 kb = has2 ? *reinterpret_cast<const uint4*>(Kb + (size_t)(j0 + jj2) * kHD + lane * 8) : make_uint4(0, 0, 0, 0);
+      float k1[8], k2[8], pa[8], pb[8];
+      bf16x8_to_f32(ka, k1);
+      bf16x8_to_f32(kb, k2);
+#pragma unroll
+      for (int g = 0; g < 8; g++) {
+        float a1 = 0.0f, a2 = 0.0f;
+        if (g < G) {
+#pragma unroll
+          for (int e = 0; e < 8; e++) {
+            a1 = fmaf(qf[g < G ? g : 0][e], k1[e], a1);
+            a2 = fmaf(qf[g < G ? g : 0][e], k2[e], a2);
+          }
+        }
+        pa[g] = a1;
+        pb[g] = a2;
+      }
+      float s1 = warp_sum8(pa);
+      float s2 = warp_sum8(pb);
+      if ((lane & 3) == 0) {
+        s_s[(size_t)jj * 8 + hsel] = __fmul_rn(s1, p.scale);
+        if (has2) s_s[(size_t)jj2 * 8 + hsel] = __fmul_rn(s2, p.scale);
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- phase 2: exact max per head, p = exp(s - m) in place ----
+  {
+    const int g = tid & 7;
+    float m = -INFINITY;
+    for (int jj = tid >> 3; jj < ns; jj += (kW * 32) >> 3) m = fmaxf(m, s_s[(size_t)jj * 8 + g]);
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+    if (lane < 8) l_s[warp * 8 + lane] = m;  // l_s doubles as the cross-warp max buffer
+    __syncthreads();
+    if (tid < 8) {
+      float mm = l_s[tid];
+#pragma unroll
+      for (int w = 1; w < kW; w++) mm = fmaxf(mm, l_s[w * 8 + tid]);
+      m_s[tid] = mm;
+    }
+    __syncthreads();
+    const float mg = m_s[g];
+    for (int jj = tid >> 3; jj < ns; jj += (kW * 32) >> 3) {
+      float s = s_s[(size_t)jj * 8 + g];
+      s_s[(size_t)jj * 8 + g] = (g < G) ? bk_expf(__fsub_rn(s, mg)) : 0.0f;
+    }
+  }
+  __syncthreads();
+
+  // ---- phase 3: o = sum p * V ----
+  {
+    float acc[G][8], lw[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+      lw[g] = 0.0f;
+#pragma unroll
+      for (int e = 0; e < 8; e++) acc[g][e] = 0.0f;
+    }
+    for (int jj = warp; jj < ns; jj += kW) {
+      uint4 vr = *reinterpret_cast<const uint4*>(Vb + (size_t)(j0 + jj) * kHD + lane * 8);
+      float vf[8];
+      bf16x8_to_f32(vr, vf);
+      const float4 p0 = *reinterpret_cast<const float4*>(s_s + (size_t)jj * 8);
+      const float4 p1 = *reinterpret_cast<const float4*>(s_s + (size_t)jj * 8 + 4);
+      const float pp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+      for (int g = 0; g < G; g++) {
+        lw[g] = __fadd_rn(lw[g], pp[g]);
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[g][e] = fmaf(pp[g], vf[e], acc[g][e]);
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+      float4* d = reinterpret_cast<float4*>(o_s + ((size_t)(warp * 8 + g)) * kHD + lane * 8);
+      d[0] = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+      d[1] = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
+      if (lane == 0) l_s[warp * 8 + g] = lw[g];
+    }
+  }
+  __syncthreads();
+
+  // ---- cross-warp sums in warp order, partial out ----
+  float* sc_ml = p.scratch;
+  float* sc_o = p.scratch + (size_t)p.B * p.Hq * p.max_splits * 2;
+  for (int idx = tid; idx < G * kHD; idx += kW * 32) {
+    const int g = idx >> 8, d = idx & 255;
+    float o = o_s[(size_t)g * kHD + d];
+#pragma unroll
+    for (int w = 1; w < kW; w++) o = __fadd_rn(o, o_s[((size_t)(w * 8 + g)) * kHD + d]);
+    sc_o[(((size_t)b * p.Hq + kvh * G + g) * p.max_splits + split) * kHD + d] = o;
+  }
+  if (tid < G) {
+    float l = l_s[tid];
+#pragma unroll
+    for (int w = 1; w < kW; w++) l = __fadd_rn(l, l_s[w * 8 + tid]);
+    size_t o = (((size_t)b * p.Hq + kvh * G + tid) * p.max_splits + split) * 2;
+    sc_ml[o] = m_s[tid];
+    sc_ml[o + 1] = l;
+  }
+}
+
+// merge the splits of one (batch, q head); thread d owns output dim d
+__global__ void __launch_bounds__(kHD) attn_combine_kernel(const AttnParams p) {
+  __shared__ float w_s[kMaxSplits];
+  __shared__ float l_sh[kMaxSplits];
+  __shared__ float red[8];
+  const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+  const int n = p.pos[b] + 1;
+  const int ns = (n + p.split_len - 1) / p.split_len;
+  const float* sc_ml = p.scratch + ((size_t)b * p.Hq + h) * p.max_splits * 2;
+  const float* sc_o = p.scratch + (size_t)p.B * p.Hq * p.max_splits * 2 + ((size_t)b * p.Hq + h) * p.max_splits * kHD;
+  float m = -INFINITY;
+  for (int s = tid; s < ns; s += kHD) {
+    float ms = sc_ml[2 * s];
+    w_s[s] = ms;
+    l_sh[s] = sc_ml[2 * s + 1];
+    m = fmaxf(m, ms);
+  }
+  m = bk_warp_max(m);
+  if ((tid & 31) == 0) red[tid >> 5] = m;
+  __syncthreads();
+  float M = red[0];
+#pragma unroll
+  for (int w = 1; w < 8; w++) M = fmaxf(M, red[w]);
+  for (int s = tid; s < ns; s += kHD) w_s[s] = bk_expf(__fsub_rn(w_s[s], M));
+  __syncthreads();
+  float L = 0.0f, O = 0.0f;
+  for (int s = 0; s < ns; s++) {
+    const float w = w_s[s];
+    L = fmaf(w, l_sh[s], L);
+    O = fmaf(w, sc_o[(size_t)s * kHD + tid], O);
+  }
+  const uint16_t gbits = p.fused ? p.qg[((size_t)b * p.Hq + h) * 2 * kHD + kHD + tid]
+                                 : p.gate[((size_t)b * p.Hq + h) * kHD + tid];
+  float o = __fmul_rn(__fdiv_rn(O, L), bk_sigmoidf(bk_bf16_to_f32(gbits)));
+  p.out[((size_t)b * p.Hq + h) * kHD + tid] = bk_f32_to_bf16(o);
+}
+
+size_t attn_smem_bytes(int split_len) { return 4096 + 512 + 64 + 256 + (size_t)split_len * 32 + (size_t)kW * 8 * kHD * 4; }
+
+template <int G>
+int32_t launch_split(const AttnParams& p, dim3 grid, size_t smem) {
+  static size_t configured = 0;
+  if (smem > configured) {
+    BK_CUDA(cudaFuncSetAttribute(attn_split_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
+  attn_split_kernel<G><<<grid, kW * 32, smem, bk_ctx().stream>>>(p);
+  BK_CHECK_LAUNCH();
+  return BK_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t bkAttnPlan(int32_t n_rows, int32_t B, int32_t Hkv, int32_t* split_len, int32_t* warps) {
+  BK_REQUIRE_INIT();
+  BK_ARG(n_rows > 0 && B > 0 && Hkv > 0 && split_len, "bkAttnPlan: bad arguments");
+  // enough splits for about two CTAs per SM, rows per split a multiple of 64 in [64, 512]
+  int target = (2 * bk_ctx().sm_count + B * Hkv - 1) / (B * Hkv);
+  int len = (n_rows + target - 1) / target;
+  len = ((len + 63) / 64) * 64;
+  if (len < 64) len = 64;
+  if (len > 512) len = 512;
+  *split_len = len;
+  if (warps) *warps = kW;
+  return BK_OK;
+}
+
+uint64_t bkAttnScratchBytes(int32_t B, int32_t Hq, int32_t HD, int32_t max_len, int32_t split_len) {
+  if (split_len <= 0) return 0;
+  uint64_t ms = (uint64_t)(max_len + split_len - 1) / split_len;
+  return (uint64_t)B * Hq * ms * (uint64_t)(HD + 2) * 4;
+}
+
+int32_t bkAttnDecode(const bkAttnArgs* args) {
+  BK_REQUIRE_INIT();
+  BK_ARG(args != nullptr, "bkAttnDecode: args is null");
+  bkAttnArgs a = *args;
+  BK_ARG(a.HD == kHD, "bkAttnDecode: head_dim %d unsupported (256 only)", a.HD);
+  BK_ARG(a.B > 0 && a.Hq > 0 && a.Hkv > 0 && a.Hq % a.Hkv == 0 && a.Hq / a.Hkv <= 8,
+         "bkAttnDecode: bad head counts B=%d Hq=%d Hkv=%d (group size 1..8)", a.B, a.Hq, a.Hkv);
+  BK_ARG(a.max_len > 0 && a.max_pos >= 0 && a.max_pos < a.max_len, "bkAttnDecode: max_pos=%d outside cache of %d rows",
+         a.max_pos, a.max_len);
+  BK_ARG(a.qg && a.k_cache && a.v_cache && a.pos && a.out && a.scratch, "bkAttnDecode: null pointer");
+  BK_ARG(((a.qg | a.k_cache | a.v_cache | a.out) & 15) == 0, "bkAttnDecode: pointers must be 16-byte aligned");
+  if (a.fused_norm_rope) {
+    BK_ARG(a.k && a.v && a.q_norm_w && a.k_norm_w && a.cos_t && a.sin_t, "bkAttnDecode: fused mode needs k, v, norm weights and tables");
+    BK_ARG(((a.k | a.v | a.q_norm_w | a.k_norm_w) & 15) == 0, "bkAttnDecode: pointers must be 16-byte aligned");
+    BK_ARG(a.rot_half > 0 && 2 * a.rot_half <= kHD, "bkAttnDecode: rot_half=%d", a.rot_half);
+  } else {
+    BK_ARG(a.gate != 0, "bkAttnDecode: gate is null");
+  }
+  int split_len = a.split_len;
+  if (split_len <= 0) {
+    int32_t rc = bkAttnPlan(a.max_pos + 1, a.B, a.Hkv, &split_len, nullptr);
+    if (rc) return rc;
+  }
+  BK_ARG(split_len % 8 == 0 && split_len <= 2048, "bkAttnDecode: split_len=%d must be a multiple of 8, at most 2048", split_len);
+  int max_splits = (a.max_len + split_len - 1) / split_len;
+  BK_ARG(max_splits <= kMaxSplits, "bkAttnDecode: %d splits exceed the limit of %d", max_splits, kMaxSplits);
+  int nsplit = (a.max_pos + split_len) / split_len;
+  AttnParams p;
+  p.qg = bk_ptr<uint16_t>(a.qg);
+  p.k = bk_ptr<uint16_t>(a.k);
+  p.v = bk_ptr<uint16_t>(a.v);
+  p.q_norm_w = bk_ptr<uint16_t>(a.q_norm_w);
+  p.k_norm_w = bk_ptr<uint16_t>(a.k_norm_w);
+  p.cos_t = bk_ptr<float>(a.cos_t);
+  p.sin_t = bk_ptr<float>(a.sin_t);
+  p.k_cache = bk_ptr<uint16_t>(a.k_cache);
+  p.v_cache = bk_ptr<uint16_t>(a.v_cache);
+  p.pos = bk_ptr<int32_t>(a.pos);
+  p.out = bk_ptr<uint16_t>(a.out);
+  p.scratch = bk_ptr<float>(a.scratch);
+  p.gate = bk_ptr<uint16_t>(a.gate);
+  p.B = a.B;
+  p.Hq = a.Hq;
+  p.Hkv = a.Hkv;
+  p.rot_half = a.rot_half;
+  p.max_len = a.max_len;
+  p.split_len = split_len;
+  p.max_splits = max_splits;
+  p.fused = a.fused_norm_rope;
+  p.scale = a.scale;
+  size_t smem = attn_smem_bytes(split_len);
+  dim3 grid(nsplit, a.Hkv, a.B);
+  int32_t rc;
+  switch (a.Hq / a.Hkv) {
+    case 1: rc = launch_split<1>(p, grid, smem); break;
+    case 2: rc = launch_split<2>(p, grid, smem); break;
+    case 3: rc = launch_split<3>(p, grid, smem); break;
+    case 4: rc = launch_split<4>(p, grid, smem); break;
+    case 5: rc = launch_split<5>(p, grid, smem); break;
+    case 6: rc = launch_split<6>(p, grid, smem); break;
+    case 7: rc = launch_split<7>(p, grid, smem); break;
+    default: rc = launch_split<8>(p, grid, smem); break;
+  }
+  if (rc) return rc;
+  attn_combine_kernel<<<dim3(a.Hq, a.B), kHD, 0, bk_ctx().stream>>>(p);
+  BK_CHECK_LAUNCH();
+  return BK_OK;
+}
+
+}  // extern "C"

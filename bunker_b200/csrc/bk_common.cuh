@@ -1,0 +1,149 @@
+// bk_common.cuh -- device-side numerics shared by every kernel of libbunker_cuda.
+//
+// Every f32 rounding point is spelled out (explicit __fmul_rn/__fadd_rn/fmaf)
+// and the file is compiled with -fmad=false, so a*b+c never fuses by accident.
+// The CPU checker mirrors the same operation sequences; that is what makes the
+// kernels bit-reproducible on a host.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define BK_DEVINL __device__ __forceinline__
+
+// ---- bf16 / f16 -----------------------------------------------------------
+
+BK_DEVINL float bk_bf16_to_f32(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
+
+// round-to-nearest-even, NaN kept quiet (MLIR arith.truncf semantics of the
+// reference's device casts, src/ttir.ts:846)
+BK_DEVINL uint16_t bk_f32_to_bf16(float f) {
+  uint32_t u = __float_as_uint(f);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40u);
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+
+// IEEE half -> float, subnormals kept (Q4_K superblock d / dmin)
+BK_DEVINL float bk_f16_to_f32(uint16_t h) {
+  float f;
+  asm("{ .reg .b16 t; mov.b16 t, %1; cvt.f32.f16 %0, t; }" : "=f"(f) : "h"(h));
+  return f;
+}
+
+// Q8_1 scale encode: truncate the mantissa, flush below-normal to signed zero
+// (the reference's encodeHalf, bench/bench.ts:41-51)
+BK_DEVINL uint16_t bk_f32_to_f16_trunc(float v) {
+  if (v == 0.0f) return 0;
+  uint32_t bits = __float_as_uint(v);
+  uint32_t s = (bits >> 16) & 0x8000u, e = (bits >> 23) & 0xffu, m = bits & 0x7fffffu;
+  int ne = (int)e - 127 + 15;
+  if (ne >= 31) return (uint16_t)(s | 0x7c00u);
+  if (ne <= 0) return (uint16_t)s;
+  return (uint16_t)(s | ((uint32_t)ne << 10) | (m >> 13));
+}
+
+// Q8_1 scale decode: zero exponent field reads as 0 (the reference's
+// half_to_float, src/dsl.ts:955-975)
+BK_DEVINL float bk_q8half_to_f32(uint16_t h) {
+  if (((h >> 10) & 0x1fu) == 0) return 0.0f;
+  return bk_f16_to_f32(h);
+}
+
+// ---- deterministic transcendentals ----------------------------------------
+
+BK_DEVINL float bk_expf(float x) {
+  if (x > 88.0f) x = 88.0f;
+  if (x < -87.0f) x = -87.0f;
+  float t = __fmul_rn(x, 1.44269504088896341f);
+  float n = rintf(t);
+  float r = fmaf(n, -0.693359375f, x);
+  r = fmaf(n, 2.12194440e-4f, r);
+  float p = 1.9875691500e-4f;
+  p = fmaf(p, r, 1.3981999507e-3f);
+  p = fmaf(p, r, 8.3334519073e-3f);
+  p = fmaf(p, r, 4.1665795894e-2f);
+  p = fmaf(p, r, 1.6666665459e-1f);
+  p = fmaf(p, r, 5.0000001201e-1f);
+  float r2 = __fmul_rn(r, r);
+  float y = fmaf(p, r2, r);
+  y = __fadd_rn(y, 1.0f);
+  int ni = (int)n;
+  float scale = __uint_as_float((uint32_t)(ni + 127) << 23);
+  return __fmul_rn(y, scale);
+}
+
+// log(x), x positive and normal
+BK_DEVINL float bk_logf(float x) {
+  uint32_t u = __float_as_uint(x);
+  int e = (int)((u >> 23) & 0xffu) - 126;
+  float m = __uint_as_float((u & 0x007fffffu) | 0x3f000000u);
+  if (m < 0.707106781186547524f) {
+    e -= 1;
+    m = __fadd_rn(m, m);
+  }
+  m = __fadd_rn(m, -1.0f);
+  float z = __fmul_rn(m, m);
+  float p = 7.0376836292e-2f;
+  p = fmaf(p, m, -1.1514610310e-1f);
+  p = fmaf(p, m, 1.1676998740e-1f);
+  p = fmaf(p, m, -1.2420140846e-1f);
+  p = fmaf(p, m, 1.4249322787e-1f);
+  p = fmaf(p, m, -1.6668057665e-1f);
+  p = fmaf(p, m, 2.0000714765e-1f);
+  p = fmaf(p, m, -2.4999993993e-1f);
+  p = fmaf(p, m, 3.3333331174e-1f);
+  float y = __fmul_rn(__fmul_rn(m, z), p);
+  float fe = (float)e;
+  y = fmaf(fe, -2.12194440e-4f, y);
+  y = fmaf(-0.5f, z, y);
+  float r = __fadd_rn(m, y);
+  r = fmaf(fe, 0.693359375f, r);
+  return r;
+}
+
+BK_DEVINL float bk_rcp_sqrt(float x) { return __fdiv_rn(1.0f, __fsqrt_rn(x)); }
+BK_DEVINL float bk_sigmoidf(float x) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, bk_expf(-x))); }
+BK_DEVINL float bk_softplusf(float x) { return bk_logf(__fadd_rn(1.0f, bk_expf(x))); }
+
+// ---- warp reductions --------------------------------------------------------
+
+// xor butterfly 16,8,4,2,1: every lane ends with the same bits
+BK_DEVINL float bk_warp_sum(float v) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, off));
+  return v;
+}
+BK_DEVINL float bk_warp_max(float v) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+  return v;
+}
+
+// ---- Q4_K superblock header -------------------------------------------------
+// bytes [4,16) of a superblock as three words w0,w1,w2; sub-block j in 0..7
+BK_DEVINL void bk_q4k_scale_min(uint32_t w0, uint32_t w1, uint32_t w2, int j, int& sc, int& mn) {
+  // b[i] = byte i of the 12
+  uint32_t lo = (j & 1) * 8 + ((j & 2) ? 16 : 0);  // shift of byte (j&3) in a word
+  if (j < 4) {
+    sc = (w0 >> lo) & 63;
+    mn = (w1 >> lo) & 63;
+  } else {
+    uint32_t b8 = (w2 >> lo) & 0xffu;   // b[j+4]
+    uint32_t b0 = (w0 >> lo) & 0xffu;   // b[j-4]
+    uint32_t b4 = (w1 >> lo) & 0xffu;   // b[j]
+    sc = (int)((b8 & 0x0fu) | ((b0 >> 6) << 4));
+    mn = (int)((b8 >> 4) | ((b4 >> 6) << 4));
+  }
+}
+
+BK_DEVINL int bk_dp4a(uint32_t a, uint32_t b, int c) {
+  // a: four unsigned bytes (nibble values), b: four signed bytes
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+BK_DEVINL int bk_dp4a_ss(uint32_t a, uint32_t b, int c) {
+  int d;
+  asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}

@@ -1,0 +1,591 @@
+// bk_gemv.cu -- Q4_K x Q8_1 dequant-GEMV for batch 1..8 (HBM-bound path).
+//
+// Replaces the bf16 tt.dot GEMMs of bunker's decode loop (buildMM / buildGateSwiglu,
+// prototypes/decode.ts:101-186; emitGemm, src/fusion.ts:276-293) with integer block
+// dots on 4-bit weights.
+//
+// Work split.  A weight row of K columns is K/64 "units": one 32-byte quant group
+// (sub-blocks 2p, 2p+1 of superblock s; u = 4s+p).  A warp owns whole rows; lane l
+// owns the units u = l (mod 32).  All loads are 128-bit: per unit two for the quants
+// and one for the 16-byte superblock header (shared by the 4 lanes of a superblock,
+// one transaction).  A warp therefore reads a row as one contiguous, fully used span.
+//
+// Arithmetic per unit and batch column: 16 dp4a (nibbles x int8) -> two exact int32
+// sub-block sums; then the fixed f32 form
+//     accd = fma(d8_b, f32(sc_b*isum_b), accd), accm = fma(s8_b, f32(m_b), accm)
+//     val  = fma(d, accd, -(dmin*accm));  lane_sum += val   (ascending u)
+// and the xor-butterfly over the 32 lanes.  The order is fixed so a host can
+// reproduce the result bit for bit.
+//
+// The activation lives in shared memory for the whole CTA: int8 quants padded to
+// 80 bytes per 64 (conflict-free 128-bit reads at lane stride), plus per-block
+// d8 and s8 = d8*sum(q8) (exact in f32).  Three prologues fill it: ready-made
+// Q8_1 blocks, bf16 rows quantised in place, or bf16 rows through RMSNorm first.
+#include "bk_common.cuh"
+#include "bk_internal.h"
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kUnitWords = 20;  // 16 data words + 4 pad
+
+struct SegDev {
+  const uint8_t* W;
+  const uint8_t* W2;
+  void* out;
+  const uint16_t* res;
+  int n_rows;
+  int epi;
+  int ld_out;
+  int col_off;
+  int task_begin;  // first task index of this segment
+};
+
+struct GemvParams {
+  int K;
+  int n_segs;
+  int prologue;
+  int total_tasks;
+  const void* x;
+  const uint16_t* norm_w;
+  float eps;
+  SegDev segs[4];
+};
+
+// ---- prologues ---------------------------------------------------------------
+
+// Q8_1 blocks [B][nblk][36] -> shared layout
+template <int B>
+__device__ void prologue_q8(const GemvParams& p, uint32_t* xs, float* d8s, float* s8s) {
+  const int nblk = p.K / 32, nunits = p.K / 64;
+  const uint32_t* src = reinterpret_cast<const uint32_t*>(p.x);
+  for (int i = threadIdx.x; i < B * nblk; i += kThreads) {
+    int b = i / nblk, blk = i - b * nblk;
+    const uint32_t* s = src + (size_t)i * 9;
+    uint32_t* dst = xs + ((size_t)b * nunits + (blk >> 1)) * kUnitWords + (blk & 1) * 8;
+    int qsum = 0;
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+      uint32_t w = s[k];
+      dst[k] = w;
+      qsum = bk_dp4a_ss(w, 0x01010101u, qsum);
+    }
+    float d8 = bk_q8half_to_f32((uint16_t)(s[8] & 0xffffu));
+    d8s[i] = d8;
+    s8s[i] = __fmul_rn(d8, (float)qsum);
+  }
+}
+
+// quantise 8 consecutive values held by this thread; the 4 threads of an aligned
+// lane group hold one 32-element block (packQ8_1, bench/bench.ts:53-72, in f32)
+__device__ __forceinline__ void quant_chunk(const float (&y)[8], int q, int b, int nunits, int nblk, uint32_t* xs,
+                                            float* d8s, float* s8s) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(y[e]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  float d = __fdiv_rn(amax, 127.0f);
+  float dd = (d == 0.0f) ? 1.0f : d;
+  int qs[8];
+  int qsum = 0;
+#pragma unroll
+  for (int e = 0; e < 8; e++) {
+    int v = (int)floorf(__fadd_rn(__fdiv_rn(y[e], dd), 0.5f));
+    v = max(-128, min(127, v));
+    qs[e] = v;
+    qsum += v;
+  }
+  qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
+  qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
+  uint32_t w0 = (uint32_t)(qs[0] & 0xff) | ((uint32_t)(qs[1] & 0xff) << 8) | ((uint32_t)(qs[2] & 0xff) << 16) |
+                ((uint32_t)(qs[3] & 0xff) << 24);
+  uint32_t w1 = (uint32_t)(qs[4] & 0xff) | ((uint32_t)(qs[5] & 0xff) << 8) | ((uint32_t)(qs[6] & 0xff) << 16) |
+                ((uint32_t)(qs[7] & 0xff) << 24);
+  int blk = q >> 2;
+  uint32_t* dst = xs + ((size_t)b * nunits + (blk >> 1)) * kUnitWords + (blk & 1) * 8 + (q & 3) * 2;
+  dst[0] = w0;
+  dst[1] = w1;
+  if ((q & 3) == 0) {
+    float d8 = bk_q8half_to_f32(bk_f32_to_f16_trunc(d));
+    d8s[b * nblk + blk] = d8;
+    s8s[b * nblk + blk] = __fmul_rn(d8, (float)qsum);
+  }
+}
+
+__device__ __forceinline__ void load_chunk_bf16(const uint16_t* row, int q, float (&y)[8]) {
+  uint4 v = *reinterpret_cast<const uint4*>(row + (size_t)q * 8);
+  y[0] = __uint_as_float(v.x << 16);
+  y[1] = __uint_as_float(v.x & 0xffff0000u);
+  y[2] = __uint_as_float(v.y << 16);
+  y[3] = __uint_as_float(v.y & 0xffff0000u);
+  y[4] = __uint_as_float(v.z << 16);
+  y[5] = __uint_as_float(v.z & 0xffff0000u);
+  y[6] = __uint_as_float(v.w << 16);
+  y[7] = __uint_as_float(v.w & 0xffff0000u);
+}
+
+// bf16 rows -> (optional RMSNorm -> bf16) -> Q8_1 in shared memory.
+// Sum of squares in the 256-thread block order: chunk q (8 elements) belongs to
+// thread q mod 256, fmaf chain inside; warp butterflies; the 8 warp sums in order.
+template <int B, bool NORM>
+__device__ void prologue_bf16(const GemvParams& p, uint32_t* xs, float* d8s, float* s8s, float* red) {
+  const int K = p.K, nblk = K / 32, nunits = K / 64, nchunk = K / 8;
+  const uint16_t* x = reinterpret_cast<const uint16_t*>(p.x);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int b = 0; b < B; b++) {
+    const uint16_t* row = x + (size_t)b * K;
+    float rstd = 1.0f;
+    if (NORM) {
+      float acc = 0.0f;
+      for (int q = threadIdx.x; q < nchunk; q += kThreads) {
+        float y[8];
+        load_chunk_bf16(row, q, y);
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc = fmaf(y[e], y[e], acc);
+      }
+      acc = bk_warp_sum(acc);
+      __syncthreads();  // red[] reuse across batch rows
+      if (lane == 0) red[warp] = acc;
+      __syncthreads();
+      float total = red[0];
+#pragma unroll
+      for (int w = 1; w < kWarps; w++) total = __fadd_rn(total, red[w]);
+      float ms = __fdiv_rn(total, (float)K);
+      rstd = bk_rcp_sqrt(__fadd_rn(ms, p.eps));
+    }
+    for (int q = threadIdx.x; q < nchunk; q += kThreads) {
+      float y[8];
+      load_chunk_bf16(row, q, y);
+      if (NORM) {
+        float wv[8];
+        load_chunk_bf16(p.norm_w, q, wv);
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+          float v = __fmul_rn(__fmul_rn(y[e], rstd), __fadd_rn(1.0f, wv[e]));
+          y[e] = bk_bf16_to_f32(bk_f32_to_bf16(v));
+        }
+      }
+      quant_chunk(y, q, b, nunits, nblk, xs, d8s, s8s);
+    }
+  }
+}
+
+// ---- main kernel -------------------------------------------------------------
+
+struct RowRegs {
+  uint4 hdr, qa, qb;
+};
+
+__device__ __forceinline__ RowRegs load_unit(const uint8_t* row, int u) {
+  const uint8_t* sb = row + (size_t)(u >> 2) * 144;
+  RowRegs r;
+  r.hdr = __ldg(reinterpret_cast<const uint4*>(sb));
+  const uint4* q = reinterpret_cast<const uint4*>(sb + 16 + (u & 3) * 32);
+  r.qa = __ldg(q);
+  r.qb = __ldg(q + 1);
+  return r;
+}
+
+template <int B>
+__device__ __forceinline__ void unit_dot(const RowRegs& r, int u, const uint32_t* xs, const float* d8s,
+                                         const float* s8s, int nunits, int nblk, float (&acc)[B]) {
+  const int p = u & 3;
+  float d = bk_f16_to_f32((uint16_t)(r.hdr.x & 0xffffu));
+  float dmin = bk_f16_to_f32((uint16_t)(r.hdr.x >> 16));
+  int sc0, mn0, sc1, mn1;
+  bk_q4k_scale_min(r.hdr.y, r.hdr.z, r.hdr.w, 2 * p, sc0, mn0);
+  bk_q4k_scale_min(r.hdr.y, r.hdr.z, r.hdr.w, 2 * p + 1, sc1, mn1);
+  const uint32_t qw[8] = {r.qa.x, r.qa.y, r.qa.z, r.qa.w, r.qb.x, r.qb.y, r.qb.z, r.qb.w};
+  uint32_t lo[8], hi[8];
+#pragma unroll
+  for (int k = 0; k < 8; k++) {
+    lo[k] = qw[k] & 0x0f0f0f0fu;
+    hi[k] = (qw[k] >> 4) & 0x0f0f0f0fu;
+  }
+  const float fm0 = (float)mn0, fm1 = (float)mn1;
+#pragma unroll
+  for (int b = 0; b < B; b++) {
+    const uint4* xv = reinterpret_cast<const uint4*>(xs + ((size_t)b * nunits + u) * kUnitWords);
+    uint4 x0 = xv[0], x1 = xv[1], x2 = xv[2], x3 = xv[3];
+    int i0 = 0, i1 = 0;
+    i0 = bk_dp4a(lo[0], x0.x, i0);
+    i0 = bk_dp4a(lo[1], x0.y, i0);
+    i0 = bk_dp4a(lo[2], x0.z, i0);
+    i0 = bk_dp4a(lo[3], x0.w, i0);
+    i0 = bk_dp4a(lo[4], x1.x, i0);
+    i0 = bk_dp4a(lo[5], x1.y, i0);
+    i0 = bk_dp4a(lo[6], x1.z, i0);
+    i0 = bk_dp4a(lo[7], x1.w, i0);
+    i1 = bk_dp4a(hi[0], x2.x, i1);
+    i1 = bk_dp4a(hi[1], x2.y, i1);
+    i1 = bk_dp4a(hi[2], x2.z, i1);
+    i1 = bk_dp4a(hi[3], x2.w, i1);
+    i1 = bk_dp4a(hi[4], x3.x, i1);
+    i1 = bk_dp4a(hi[5], x3.y, i1);
+    i1 = bk_dp4a(hi[6], x3.z, i1);
+    i1 = bk_dp4a(hi[7], x3.w, i1);
+    const float2 d8 = *reinterpret_cast<const float2*>(d8s + b * nblk + 2 * u);
+    const float2 s8 = *reinterpret_cast<const float2*>(s8s + b * nblk + 2 * u);
+    float accd = __fmul_rn(d8.x, (float)(sc0 * i0));
+    accd = fmaf(d8.y, (float)(sc1 * i1), accd);
+    float accm = __fmul_rn(s8.x, fm0);
+    accm = fmaf(s8.y, fm1, accm);
+    float t = __fmul_rn(dmin, accm);
+    float val = fmaf(d, accd, -t);
+    acc[b] = __fadd_rn(acc[b], val);
+  }
+}
+
+template <int B>
+__global__ void __launch_bounds__(kThreads) gemv_q4k_kernel(const GemvParams p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  const int K = p.K, nunits = K / 64, nblk = K / 32;
+  uint32_t* xs = reinterpret_cast<uint32_t*>(smem_raw);
+  float* d8s = reinterpret_cast<float*>(xs + (size_t)B * nunits * kUnitWords);
+  float* s8s = d8s + (size_t)B * nblk;
+  float* red = s8s + (size_t)B * nblk;
+
+  if (p.prologue == BK_PRO_Q8)
+    prologue_q8<B>(p, xs, d8s, s8s);
+  else if (p.prologue == BK_PRO_BF16)
+    prologue_bf16<B, false>(p, xs, d8s, s8s, red);
+  else
+    prologue_bf16<B, true>(p, xs, d8s, s8s, red);
+  __syncthreads();
+
+  const int lane = threadIdx.x & 31;
+  const int gwarp = blockIdx.x * kWarps + (threadIdx.x >> 5);
+  const int nwarps = gridDim.x * kWarps;
+
+  for (int task = gwarp; task < p.total_tasks; task += nwarps) {
+    // segment lookup
+    int si = 0;
+#pragma unroll
+    for (int s = 1; s < 4; s++)
+      if (s < p.n_segs && task >= p.segs[s].task_begin) si = s;
+    const SegDev& sg = p.segs[si];
+    const int t = task - sg.task_begin;
+    const size_t rowb = (size_t)(K / 256) * 144;
+    const uint8_t *row0, *row1;
+    int n0, n1;  // output columns (relative to segment) of the two rows; n1 < 0 if absent
+    if (sg.epi == BK_EPI_SWIGLU) {
+      n0 = t;
+      n1 = t;
+      row0 = sg.W + rowb * t;
+      row1 = sg.W2 + rowb * t;
+    } else {
+      n0 = 2 * t;
+      n1 = (2 * t + 1 < sg.n_rows) ? 2 * t + 1 : -1;
+      row0 = sg.W + rowb * n0;
+      row1 = sg.W + rowb * (n1 >= 0 ? n1 : n0);
+    }
+    float acc0[B], acc1[B];
+#pragma unroll
+    for (int b = 0; b < B; b++) {
+      acc0[b] = 0.0f;
+      acc1[b] = 0.0f;
+    }
+    for (int u = lane; u < nunits; u += 32) {
+      RowRegs r0 = load_unit(row0, u);
+      RowRegs r1 = load_unit(row1, u);
+      unit_dot<B>(r0, u, xs, d8s, s8s, nunits, nblk, acc0);
+      unit_dot<B>(r1, u, xs, d8s, s8s, nunits, nblk, acc1);
+    }
+#pragma unroll
+    for (int b = 0; b < B; b++) {
+      acc0[b] = bk_warp_sum(acc0[b]);
+      acc1[b] = bk_warp_sum(acc1[b]);
+    }
+    // epilogue: lane b handles batch column b of row0 (and row1)
+    float v0 = 0.0f, v1 = 0.0f;
+#pragma unroll
+    for (int b = 0; b < B; b++)
+      if (lane == b) {
+        v0 = acc0[b];
+        v1 = acc1[b];
+      }
+    if (lane < B) {
+      const size_t ob = (size_t)lane * sg.ld_out + sg.col_off;
+      if (sg.epi == BK_EPI_SWIGLU) {
+        float sig = bk_sigmoidf(v0);
+        float o = __fmul_rn(__fmul_rn(v0, sig), v1);
+        reinterpret_cast<uint16_t*>(sg.out)[ob + n0] = bk_f32_to_bf16(o);
+      } else if (sg.epi == BK_EPI_F32) {
+        float* o = reinterpret_cast<float*>(sg.out);
+        o[ob + n0] = v0;
+        if (n1 >= 0) o[ob + n1] = v1;
+      } else if (sg.epi == BK_EPI_BF16) {
+        uint16_t* o = reinterpret_cast<uint16_t*>(sg.out);
+        o[ob + n0] = bk_f32_to_bf16(v0);
+        if (n1 >= 0) o[ob + n1] = bk_f32_to_bf16(v1);
+      } else {  // BK_EPI_ADD_BF16
+        uint16_t* o = reinterpret_cast<uint16_t*>(sg.out);
+        o[ob + n0] = bk_f32_to_bf16(__fadd_rn(v0, bk_bf16_to_f32(sg.res[ob + n0])));
+        if (n1 >= 0) o[ob + n1] = bk_f32_to_bf16(__fadd_rn(v1, bk_bf16_to_f32(sg.res[ob + n1])));
+      }
+    }
+  }
+}
+
+size_t gemv_smem_bytes(int K, int B) {
+  size_t nunits = K / 64, nblk = K / 32;
+  return (size_t)B * nunits * kUnitWords * 4 + (size_t)B * nblk * 8 + kWarps * 4 + 16;
+}
+
+template <int B>
+int32_t launch_gemv(const GemvParams& p, int grid, size_t smem) {
+  static size_t configured = 0;
+  if (smem > configured) {
+    BK_CUDA(cudaFuncSetAttribute(gemv_q4k_kernel<B>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
+  gemv_q4k_kernel<B><<<grid, kThreads, smem, bk_ctx().stream>>>(p);
+  BK_CHECK_LAUNCH();
+  return BK_OK;
+}
+
+// ---- dequant / block-dot check kernels ---------------------------------------
+
+// One thread per (row, unit): writes 64 f32 weights, dl = d*sc, ml = dmin*m, w = dl*q - ml
+__global__ void dequant_q4k_kernel(const uint8_t* W, int N, int K, float* out) {
+  const int nunits = K / 64;
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)N * nunits) return;
+  int n = (int)(idx / nunits), u = (int)(idx - (size_t)n * nunits);
+  const uint8_t* row = W + (size_t)n * (K / 256) * 144;
+  RowRegs r = load_unit(row, u);
+  int p = u & 3;
+  float d = bk_f16_to_f32((uint16_t)(r.hdr.x & 0xffffu));
+  float dmin = bk_f16_to_f32((uint16_t)(r.hdr.x >> 16));
+  int sc0, mn0, sc1, mn1;
+  bk_q4k_scale_min(r.hdr.y, r.hdr.z, r.hdr.w, 2 * p, sc0, mn0);
+  bk_q4k_scale_min(r.hdr.y, r.hdr.z, r.hdr.w, 2 * p + 1, sc1, mn1);
+  float dl0 = __fmul_rn(d, (float)sc0), ml0 = __fmul_rn(dmin, (float)mn0);
+  float dl1 = __fmul_rn(d, (float)sc1), ml1 = __fmul_rn(dmin, (float)mn1);
+  const uint32_t qw[8] = {r.qa.x, r.qa.y, r.qa.z, r.qa.w, r.qb.x, r.qb.y, r.qb.z, r.qb.w};
+  float* o = out + (size_t)n * K + (size_t)u * 64;
+#pragma unroll
+  for (int k = 0; k < 8; k++)
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      uint32_t byte = (qw[k] >> (8 * e)) & 0xffu;
+      o[k * 4 + e] = __fsub_rn(__fmul_rn(dl0, (float)(byte & 15u)), ml0);
+      o[32 + k * 4 + e] = __fsub_rn(__fmul_rn(dl1, (float)(byte >> 4)), ml1);
+    }
+}
+
+// One thread per (row, unit): the two int32 sub-block sums and the q8 sums
+__global__ void block_dots_kernel(const uint8_t* W, int N, int K, const uint32_t* xq, int32_t* isum, int32_t* qsum) {
+  const int nunits = K / 64, nblk = K / 32;
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)N * nunits) return;
+  int n = (int)(idx / nunits), u = (int)(idx - (size_t)n * nunits);
+  const uint8_t* row = W + (size_t)n * (K / 256) * 144;
+  RowRegs r = load_unit(row, u);
+  const uint32_t qw[8] = {r.qa.x, r.qa.y, r.qa.z, r.qa.w, r.qb.x, r.qb.y, r.qb.z, r.qb.w};
+  const uint32_t* x0 = xq + (size_t)(2 * u) * 9;
+  const uint32_t* x1 = xq + (size_t)(2 * u + 1) * 9;
+  int i0 = 0, i1 = 0, s0 = 0, s1 = 0;
+#pragma unroll
+  for (int k = 0; k < 8; k++) {
+    i0 = bk_dp4a(qw[k] & 0x0f0f0f0fu, x0[k], i0);
+    i1 = bk_dp4a((qw[k] >> 4) & 0x0f0f0f0fu, x1[k], i1);
+    s0 = bk_dp4a_ss(x0[k], 0x01010101u, s0);
+    s1 = bk_dp4a_ss(x1[k], 0x01010101u, s1);
+  }
+  isum[(size_t)n * nblk + 2 * u] = i0;
+  isum[(size_t)n * nblk + 2 * u + 1] = i1;
+  qsum[(size_t)n * nblk + 2 * u] = s0;
+  qsum[(size_t)n * nblk + 2 * u + 1] = s1;
+}
+
+// packQ8_1 on the device: one aligned group of 4 lanes per 32-element block
+template <bool BF16>
+__global__ void quant_q8_1_kernel(const void* x, int K, int B, uint8_t* out) {
+  const int nchunk = K / 8;
+  size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  bool active = gid < (size_t)B * nchunk;
+  size_t g = active ? gid : 0;
+  int b = (int)(g / nchunk), q = (int)(g - (size_t)b * nchunk);
+  float y[8];
+  if (BF16) {
+    load_chunk_bf16(reinterpret_cast<const uint16_t*>(x) + (size_t)b * K, q, y);
+  } else {
+    const float4* s = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + (size_t)b * K + (size_t)q * 8);
+    float4 a = s[0], c = s[1];
+    y[0] = a.x; y[1] = a.y; y[2] = a.z; y[3] = a.w;
+    y[4] = c.x; y[5] = c.y; y[6] = c.z; y[7] = c.w;
+  }
+  float amax = 0.0f;
+#pragma unroll
+  for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(y[e]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  float d = __fdiv_rn(amax, 127.0f);
+  float dd = (d == 0.0f) ? 1.0f : d;
+  int sum = 0;
+  uint32_t w[2] = {0, 0};
+#pragma unroll
+  for (int e = 0; e < 8; e++) {
+    int v = (int)floorf(__fadd_rn(__fdiv_rn(y[e], dd), 0.5f));
+    sum += v;  // the reference sums before clamping (bench/bench.ts:66-67)
+    v = max(-128, min(127, v));
+    w[e >> 2] |= (uint32_t)(v & 0xff) << (8 * (e & 3));
+  }
+  sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+  sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+  if (!active) return;
+  int blk = q >> 2;
+  uint32_t* ob = reinterpret_cast<uint32_t*>(out + ((size_t)b * (K / 32) + blk) * 36);
+  ob[(q & 3) * 2] = w[0];
+  ob[(q & 3) * 2 + 1] = w[1];
+  if ((q & 3) == 0) {
+    uint32_t hd = bk_f32_to_f16_trunc(d);
+    uint32_t hs = bk_f32_to_f16_trunc(__fmul_rn((float)sum, d));
+    ob[8] = hd | (hs << 16);
+  }
+}
+
+}  // namespace
+
+// ---- host entry points ---------------------------------------------------------
+
+int32_t bk_gemv_launch(const bkGemvArgs& a) {
+  BkContext& c = bk_ctx();
+  BK_ARG(a.K > 0 && a.K % 256 == 0, "bkGemvQ4K: K=%d is not a positive multiple of 256", a.K);
+  BK_ARG(a.B >= 1 && a.B <= 8, "bkGemvQ4K: B=%d outside 1..8", a.B);
+  BK_ARG(a.n_segs >= 1 && a.n_segs <= 4, "bkGemvQ4K: n_segs=%d outside 1..4", a.n_segs);
+  BK_ARG(a.prologue >= BK_PRO_Q8 && a.prologue <= BK_PRO_RMSNORM, "bkGemvQ4K: unknown prologue %d", a.prologue);
+  BK_ARG(a.x != 0 && (a.x & 15) == 0, "bkGemvQ4K: x must be a non-null 16-byte aligned device pointer");
+  if (a.prologue == BK_PRO_RMSNORM)
+    BK_ARG(a.norm_w != 0 && (a.norm_w & 15) == 0, "bkGemvQ4K: norm_w must be non-null and 16-byte aligned");
+  GemvParams p;
+  p.K = a.K;
+  p.n_segs = a.n_segs;
+  p.prologue = a.prologue;
+  p.x = bk_ptr<void>(a.x);
+  p.norm_w = bk_ptr<uint16_t>(a.norm_w);
+  p.eps = a.eps;
+  int tasks = 0;
+  for (int s = 0; s < 4; s++) {
+    SegDev& d = p.segs[s];
+    if (s >= a.n_segs) {
+      d = SegDev{nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0x7fffffff};
+      continue;
+    }
+    const bkGemvSeg& g = a.segs[s];
+    BK_ARG(g.n_rows > 0, "bkGemvQ4K: segment %d has n_rows=%d", s, g.n_rows);
+    BK_ARG(g.W != 0 && (g.W & 15) == 0, "bkGemvQ4K: segment %d W must be non-null and 16-byte aligned", s);
+    BK_ARG(g.out != 0, "bkGemvQ4K: segment %d out is null", s);
+    BK_ARG(g.epilogue >= BK_EPI_F32 && g.epilogue <= BK_EPI_SWIGLU, "bkGemvQ4K: segment %d unknown epilogue %d", s,
+           g.epilogue);
+    BK_ARG(g.ld_out >= g.col_off + g.n_rows, "bkGemvQ4K: segment %d ld_out=%d < col_off+n_rows", s, g.ld_out);
+    if (g.epilogue == BK_EPI_SWIGLU)
+      BK_ARG(g.W2 != 0 && (g.W2 & 15) == 0, "bkGemvQ4K: segment %d needs a 16-byte aligned W2 for SwiGLU", s);
+    if (g.epilogue == BK_EPI_ADD_BF16) BK_ARG(g.residual != 0, "bkGemvQ4K: segment %d needs a residual", s);
+    d.W = bk_ptr<uint8_t>(g.W);
+    d.W2 = bk_ptr<uint8_t>(g.W2);
+    d.out = bk_ptr<void>(g.out);
+    d.res = bk_ptr<uint16_t>(g.residual);
+    d.n_rows = g.n_rows;
+    d.epi = g.epilogue;
+    d.ld_out = g.ld_out;
+    d.col_off = g.col_off;
+    d.task_begin = tasks;
+    tasks += (g.epilogue == BK_EPI_SWIGLU) ? g.n_rows : (g.n_rows + 1) / 2;
+  }
+  p.total_tasks = tasks;
+  size_t smem = gemv_smem_bytes(a.K, a.B);
+  BK_ARG(smem <= c.smem_optin, "bkGemvQ4K: K=%d B=%d needs %zu bytes of shared memory (limit %zu)", a.K, a.B, smem,
+         c.smem_optin);
+  int ctas_per_sm = (int)((c.smem_optin) / (smem + 1024));
+  if (ctas_per_sm > 4) ctas_per_sm = 4;
+  if (ctas_per_sm < 1) ctas_per_sm = 1;
+  int grid = (tasks + kWarps - 1) / kWarps;
+  int cap = c.sm_count * ctas_per_sm;
+  if (grid > cap) grid = cap;
+  switch (a.B) {
+    case 1: return launch_gemv<1>(p, grid, smem);
+    case 2: return launch_gemv<2>(p, grid, smem);
+    case 3: return launch_gemv<3>(p, grid, smem);
+    case 4: return launch_gemv<4>(p, grid, smem);
+    case 5: return launch_gemv<5>(p, grid, smem);
+    case 6: return launch_gemv<6>(p, grid, smem);
+    case 7: return launch_gemv<7>(p, grid, smem);
+    default: return launch_gemv<8>(p, grid, smem);
+  }
+}
+
+extern "C" {
+
+int32_t bkGemvQ4K(const bkGemvArgs* args) {
+  BK_REQUIRE_INIT();
+  BK_ARG(args != nullptr, "bkGemvQ4K: args is null");
+  bkGemvArgs a = *args;  // copied before any asynchronous use
+  return bk_gemv_launch(a);
+}
+
+int32_t bkGemvQ4KSimple(uint64_t W, int32_t N, int32_t K, uint64_t xq, int32_t B, uint64_t y) {
+  BK_REQUIRE_INIT();
+  bkGemvArgs a = {};
+  a.K = K;
+  a.B = B;
+  a.n_segs = 1;
+  a.prologue = BK_PRO_Q8;
+  a.x = xq;
+  a.segs[0].W = W;
+  a.segs[0].out = y;
+  a.segs[0].n_rows = N;
+  a.segs[0].epilogue = BK_EPI_F32;
+  a.segs[0].ld_out = N;
+  return bk_gemv_launch(a);
+}
+
+int32_t bkDequantQ4K(uint64_t W, int32_t N, int32_t K, uint64_t out_f32) {
+  BK_REQUIRE_INIT();
+  BK_ARG(K > 0 && K % 256 == 0 && N > 0, "bkDequantQ4K: bad shape N=%d K=%d", N, K);
+  BK_ARG(W && out_f32 && (W & 15) == 0, "bkDequantQ4K: null or misaligned pointer");
+  size_t total = (size_t)N * (K / 64);
+  dequant_q4k_kernel<<<(unsigned)((total + 255) / 256), 256, 0, bk_ctx().stream>>>(bk_ptr<uint8_t>(W), N, K,
+                                                                                  bk_ptr<float>(out_f32));
+  BK_CHECK_LAUNCH();
+  return BK_OK;
+}
+
+int32_t bkBlockDotsQ4K(uint64_t W, int32_t N, int32_t K, uint64_t xq, uint64_t isum, uint64_t qsum) {
+  BK_REQUIRE_INIT();
+  BK_ARG(K > 0 && K % 256 == 0 && N > 0, "bkBlockDotsQ4K: bad shape N=%d K=%d", N, K);
+  BK_ARG(W && xq && isum && qsum && (W & 15) == 0 && (xq & 3) == 0, "bkBlockDotsQ4K: null or misaligned pointer");
+  size_t total = (size_t)N * (K / 64);
+  block_dots_kernel<<<(unsigned)((total + 255) / 256), 256, 0, bk_ctx().stream>>>(
+      bk_ptr<uint8_t>(W), N, K, bk_ptr<uint32_t>(xq), bk_ptr<int32_t>(isum), bk_ptr<int32_t>(qsum));
+  BK_CHECK_LAUNCH();
+  return BK_OK;
+}
+
+static int32_t quant_common(uint64_t x, int32_t K, int32_t B, uint64_t out, bool bf16) {
+  BK_ARG(K > 0 && K % 32 == 0 && B > 0, "bkQuantQ8_1: bad shape K=%d B=%d", K, B);
+  BK_ARG(x && out && (x & 15) == 0 && (out & 3) == 0, "bkQuantQ8_1: null or misaligned pointer");
+  size_t total = (size_t)B * (K / 8);
+  unsigned grid = (unsigned)((total + 255) / 256);
+  if (bf16)
+    quant_q8_1_kernel<true><<<grid, 256, 0, bk_ctx().stream>>>(bk_ptr<void>(x), K, B, bk_ptr<uint8_t>(out));
+  else
+    quant_q8_1_kernel<false><<<grid, 256, 0, bk_ctx().stream>>>(bk_ptr<void>(x), K, B, bk_ptr<uint8_t>(out));
+  BK_CHECK_LAUNCH();
+  return BK_OK;
+}
+
+int32_t bkQuantQ8_1(uint64_t x_f32, int32_t K, int32_t B, uint64_t out_blocks) {
+  BK_REQUIRE_INIT();
+  return quant_common(x_f32, K, B, out_blocks, false);
+}
+
+int32_t bkQuantQ8_1Bf16(uint64_t x_bf16, int32_t K, int32_t B, uint64_t out_blocks) {
+  BK_REQUIRE_INIT();
+  return quant_common(x_bf16, K, B, out_blocks, true);
+}
+
+}  // extern "C"

@@ -1,0 +1,58 @@
+// bk_internal.h -- host-side state shared by the translation units of libbunker_cuda.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/bunker_cuda.h"
+
+struct BkContext {
+  bool ready = false;
+  int device = -1;
+  int sm_count = 0;
+  int cc_major = 0, cc_minor = 0;
+  size_t total_mem = 0;
+  size_t smem_optin = 0;
+  cudaStream_t stream = nullptr;
+  unsigned long long launches = 0;   // kernels enqueued outside graphs + graph kernels replayed
+  bool capturing = false;            // true while a graph capture is open on `stream`
+  unsigned long long captured = 0;   // kernels recorded into the open capture
+  char err[512] = {0};
+};
+
+BkContext& bk_ctx();
+int32_t bk_fail(int32_t code, const char* fmt, ...);
+
+// count one kernel launch (directly executed or recorded into a capture)
+inline void bk_count_launch() {
+  BkContext& c = bk_ctx();
+  if (c.capturing) c.captured++; else c.launches++;
+}
+
+#define BK_REQUIRE_INIT()                                                            \
+  do {                                                                               \
+    if (!bk_ctx().ready) return bk_fail(BK_ERR_STATE, "%s: bkInit has not been called", __func__); \
+  } while (0)
+
+#define BK_CUDA(expr)                                                                \
+  do {                                                                               \
+    cudaError_t _e = (expr);                                                         \
+    if (_e != cudaSuccess)                                                           \
+      return bk_fail((int32_t)_e, "%s: %s -> %s", __func__, #expr, cudaGetErrorString(_e)); \
+  } while (0)
+
+#define BK_CHECK_LAUNCH()                                                            \
+  do {                                                                               \
+    cudaError_t _e = cudaGetLastError();                                             \
+    if (_e != cudaSuccess)                                                           \
+      return bk_fail((int32_t)_e, "%s: kernel launch -> %s", __func__, cudaGetErrorString(_e)); \
+    bk_count_launch();                                                               \
+  } while (0)
+
+#define BK_ARG(cond, ...)                                                            \
+  do {                                                                               \
+    if (!(cond)) return bk_fail(BK_ERR_ARG, __VA_ARGS__);                             \
+  } while (0)
+
+template <typename T>
+static inline T* bk_ptr(uint64_t p) { return reinterpret_cast<T*>(static_cast<uintptr_t>(p)); }

@@ -1,0 +1,497 @@
+// bk_ops.cu -- the non-GEMV decode ops: embed, RMSNorm, SwiGLU, conv1d, the fused
+// conv1d + gated-DeltaNet step, q/k head norm + partial rotary, argmax.
+// Math follows bunker's emitters (src/emitters.ts) and tuned decode kernels
+// (prototypes/decode.ts); reduction orders are fixed so a host can reproduce the bits.
+#include <math.h>
+
+#include "bk_common.cuh"
+#include "bk_internal.h"
+
+namespace {
+
+// ---- embed: x[b] = bf16(dequant(E[ids[b]])) (src/emitters.ts:31-45) ------------
+__global__ void embed_q4k_kernel(const uint8_t* table, int H, const int32_t* ids, uint16_t* x) {
+  const int b = blockIdx.x;
+  const int nunits = H / 64;
+  const uint8_t* row = table + (size_t)ids[b] * (H / 256) * 144;
+  for (int u = threadIdx.x; u < nunits; u += blockDim.x) {
+    const uint8_t* sb = row + (size_t)(u >> 2) * 144;
+    uint4 hdr = __ldg(reinterpret_cast<const uint4*>(sb));
+    const uint4* q = reinterpret_cast<const uint4*>(sb + 16 + (u & 3) * 32);
+    uint4 qa = __ldg(q), qb = __ldg(q + 1);
+    int p = u & 3;
+    float d = bk_f16_to_f32((uint16_t)(hdr.x & 0xffffu)), dmin = bk_f16_to_f32((uint16_t)(hdr.x >> 16));
+    int sc0, mn0, sc1, mn1;
+    bk_q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * p, sc0, mn0);
+    bk_q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * p + 1, sc1, mn1);
+    float dl0 = __fmul_rn(d, (float)sc0), ml0 = __fmul_rn(dmin, (float)mn0);
+    float dl1 = __fmul_rn(d, (float)sc1), ml1 = __fmul_rn(dmin, (float)mn1);
+    const uint32_t qw[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+    uint16_t* o = x + (size_t)b * H + (size_t)u * 64;
+#pragma unroll
+    for (int k = 0; k < 8; k++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        uint32_t byte = (qw[k] >> (8 * e)) & 0xffu;
+        o[k * 4 + e] = bk_f32_to_bf16(__fsub_rn(__fmul_rn(dl0, (float)(byte & 15u)), ml0));
+        o[32 + k * 4 + e] = bk_f32_to_bf16(__fsub_rn(__fmul_rn(dl1, (float)(byte >> 4)), ml1));
+      }
+  }
+}
+
+__device__ __forceinline__ void load8_bf16(const uint16_t* p, float (&y)[8]) {
+  uint4 v = *reinterpret_cast<const uint4*>(p);
+  y[0] = __uint_as_float(v.x << 16);
+  y[1] = __uint_as_float(v.x & 0xffff0000u);
+  y[2] = __uint_as_float(v.y << 16);
+  y[3] = __uint_as_float(v.y & 0xffff0000u);
+  y[4] = __uint_as_float(v.z << 16);
+  y[5] = __uint_as_float(v.z & 0xffff0000u);
+  y[6] = __uint_as_float(v.w << 16);
+  y[7] = __uint_as_float(v.w & 0xffff0000u);
+}
+
+// ---- RMSNorm (buildRMS, prototypes/decode.ts:201-216), one CTA of 256 per row ----
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t* x, const uint16_t* w, int H, float eps,
+                                                      uint16_t* y) {
+  __shared__ float red[8];
+  const uint16_t* row = x + (size_t)blockIdx.x * H;
+  uint16_t* out = y + (size_t)blockIdx.x * H;
+  const int nchunk = H / 8;
+  float acc = 0.0f;
+  for (int q = threadIdx.x; q < nchunk; q += 256) {
+    float v[8];
+    load8_bf16(row + (size_t)q * 8, v);
+#pragma unroll
+    for (int e = 0; e < 8; e++) acc = fmaf(v[e], v[e], acc);
+  }
+  acc = bk_warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  float total = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; i++) total = __fadd_rn(total, red[i]);
+  float rstd = bk_rcp_sqrt(__fadd_rn(__fdiv_rn(total, (float)H), eps));
+  for (int q = threadIdx.x; q < nchunk; q += 256) {
+    float v[8], wv[8];
+    load8_bf16(row + (size_t)q * 8, v);
+    load8_bf16(w + (size_t)q * 8, wv);
+    uint32_t o[4];
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) {
+      uint32_t lo = bk_f32_to_bf16(__fmul_rn(__fmul_rn(v[e], rstd), __fadd_rn(1.0f, wv[e])));
+      uint32_t hi = bk_f32_to_bf16(__fmul_rn(__fmul_rn(v[e + 1], rstd), __fadd_rn(1.0f, wv[e + 1])));
+      o[e >> 1] = lo | (hi << 16);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)q * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// ---- SwiGLU (src/fusion.ts:324-330) ---------------------------------------------
+__global__ void swiglu_kernel(const float* g, const float* u, int n, uint16_t* out) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float gv = g[i];
+  out[i] = bk_f32_to_bf16(__fmul_rn(__fmul_rn(gv, bk_sigmoidf(gv)), u[i]));
+}
+
+// ---- conv1d decode step (src/emitters.ts:48-72) ----------------------------------
+__device__ __forceinline__ float conv_tap4(float s0, float s1, float s2, float xv, const uint16_t* w4) {
+  uint2 wv = *reinterpret_cast<const uint2*>(w4);
+  float w0 = __uint_as_float(wv.x << 16), w1 = __uint_as_float(wv.x & 0xffff0000u);
+  float w2 = __uint_as_float(wv.y << 16), w3 = __uint_as_float(wv.y & 0xffff0000u);
+  float raw = __fadd_rn(__fadd_rn(__fmul_rn(w0, s0), __fmul_rn(w1, s1)), __fadd_rn(__fmul_rn(w2, s2), __fmul_rn(w3, xv)));
+  return __fmul_rn(raw, bk_sigmoidf(raw));
+}
+
+__global__ void conv1d_step_kernel(const uint16_t* x, const uint16_t* st, const uint16_t* w, int C, int B,
+                                   uint16_t* out, uint16_t* sn) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= B * C) return;
+  int b = i / C, c = i - b * C;
+  const uint16_t* s = st + (size_t)b * 3 * C;
+  uint16_t h0 = s[c], h1 = s[C + c], h2 = s[2 * C + c], hx = x[i];
+  float o = conv_tap4(bk_bf16_to_f32(h0), bk_bf16_to_f32(h1), bk_bf16_to_f32(h2), bk_bf16_to_f32(hx), w + 4 * (size_t)c);
+  out[i] = bk_f32_to_bf16(o);
+  uint16_t* d = sn + (size_t)b * 3 * C;
+  d[c] = h1;
+  d[C + c] = h2;
+  d[2 * C + c] = hx;
+}
+
+// ---- fused conv1d + gated DeltaNet step ------------------------------------------
+// One CTA of 512 threads per (batch, value head).  Thread (r = t>>7, j = t&127)
+// keeps rows 32r..32r+31 of column j of the 128x128 state in registers: one read
+// and one write of the state per step.  Column sums over the 128 rows use the four
+// row groups in order ((g0+g1)+g2)+g3.
+struct GdnParams {
+  const uint16_t* qkv;
+  const uint16_t* z;
+  const float* a;
+  const float* b;
+  const uint16_t* conv_w;
+  const uint16_t* cs_in;
+  uint16_t* cs_new;
+  const float* A_log;
+  const uint16_t* dt_bias;
+  const float* norm_w;
+  const float* S_in;
+  float* S_new;
+  uint16_t* out;
+  float* o_raw;
+  uint16_t* conv_out;
+  int B, Hk, Hv, apply_conv;
+};
+
+__global__ void __launch_bounds__(512) gdn_step_kernel(const GdnParams p) {
+  constexpr int D = 128;
+  __shared__ float s_q[D], s_k[D], s_v[D], s_o[D];
+  __shared__ float s_part[4][D];
+  __shared__ float s_scal[4];  // q scale, k rstd, decay, beta
+  const int hv = blockIdx.x, b = blockIdx.y, t = threadIdx.x;
+  const int ratio = p.Hv / p.Hk, hk = hv / ratio;
+  const int keydim = p.Hk * D, C = 2 * keydim + p.Hv * D;
+
+  if (t < 3 * D) {
+    int ch, which = t >> 7, i = t & 127;
+    if (which == 0) ch = hk * D + i;
+    else if (which == 1) ch = keydim + hk * D + i;
+    else ch = 2 * keydim + hv * D + i;
+    uint16_t hx = p.qkv[(size_t)b * C + ch];
+    float val;
+    if (p.apply_conv) {
+      const uint16_t* s = p.cs_in + (size_t)b * 3 * C;
+      uint16_t h0 = s[ch], h1 = s[C + ch], h2 = s[2 * C + ch];
+      float o = conv_tap4(bk_bf16_to_f32(h0), bk_bf16_to_f32(h1), bk_bf16_to_f32(h2), bk_bf16_to_f32(hx),
+                          p.conv_w + 4 * (size_t)ch);
+      uint16_t ob = bk_f32_to_bf16(o);
+      val = bk_bf16_to_f32(ob);
+      // q/k channels are shared by `ratio` value heads: the first of them writes
+      if (which == 2 || hv % ratio == 0) {
+        uint16_t* d = p.cs_new + (size_t)b * 3 * C;
+        d[ch] = h1;
+        d[C + ch] = h2;
+        d[2 * C + ch] = hx;
+        if (p.conv_out) p.conv_out[(size_t)b * C + ch] = ob;
+      }
+    } else {
+      val = bk_bf16_to_f32(hx);
+    }
+    if (which == 0) s_q[i] = val;
+    else if (which == 1) s_k[i] = val;
+    else s_v[i] = val;
+  }
+  __syncthreads();
+  const int warp = t >> 5, lane = t & 31;
+  if (warp < 2) {
+    const float* src = warp == 0 ? s_q : s_k;
+    float acc = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 4; e++) acc = fmaf(src[lane * 4 + e], src[lane * 4 + e], acc);
+    acc = bk_warp_sum(acc);
+    float r = bk_rcp_sqrt(__fadd_rn(acc, 1e-6f));
+    if (lane == 0) s_scal[warp] = (warp == 0) ? __fmul_rn(r, 0.088388347648318441f) : r;
+  } else if (warp == 2 && lane == 0) {
+    float sp = bk_softplusf(__fadd_rn(p.a[(size_t)b * p.Hv + hv], bk_bf16_to_f32(p.dt_bias[hv])));
+    s_scal[2] = bk_expf(-__fmul_rn(bk_expf(p.A_log[hv]), sp));
+    s_scal[3] = bk_sigmoidf(p.b[(size_t)b * p.Hv + hv]);
+  }
+  __syncthreads();
+  if (t < D) s_q[t] = __fmul_rn(s_q[t], s_scal[0]);
+  else if (t < 2 * D) s_k[t - D] = __fmul_rn(s_k[t - D], s_scal[1]);
+  __syncthreads();
+
+  const int r = t >> 7, j = t & 127;
+  const float decay = s_scal[2], beta = s_scal[3];
+  const float* S = p.S_in + (((size_t)b * p.Hv + hv) * D + 32 * r) * D + j;
+  float* Sn = p.S_new + (((size_t)b * p.Hv + hv) * D + 32 * r) * D + j;
+  float sd[32];
+#pragma unroll
+  for (int i = 0; i < 32; i++) sd[i] = S[(size_t)i * D];
+  float acc = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 32; i++) {
+    sd[i] = __fmul_rn(sd[i], decay);
+    acc = fmaf(s_k[32 * r + i], sd[i], acc);
+  }
+  s_part[r][j] = acc;
+  __syncthreads();
+  float kS = __fadd_rn(__fadd_rn(__fadd_rn(s_part[0][j], s_part[1][j]), s_part[2][j]), s_part[3][j]);
+  float delta = __fmul_rn(__fsub_rn(s_v[j], kS), beta);
+  __syncthreads();
+  acc = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 32; i++) {
+    float sn = fmaf(s_k[32 * r + i], delta, sd[i]);
+    Sn[(size_t)i * D] = sn;
+    acc = fmaf(s_q[32 * r + i], sn, acc);
+  }
+  s_part[r][j] = acc;
+  __syncthreads();
+  if (t < D) {
+    float o = __fadd_rn(__fadd_rn(__fadd_rn(s_part[0][t], s_part[1][t]), s_part[2][t]), s_part[3][t]);
+    s_o[t] = o;
+    if (p.o_raw) p.o_raw[((size_t)b * p.Hv + hv) * D + t] = o;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    float a2 = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 4; e++) a2 = fmaf(s_o[lane * 4 + e], s_o[lane * 4 + e], a2);
+    a2 = bk_warp_sum(a2);
+    if (lane == 0) s_scal[0] = bk_rcp_sqrt(__fadd_rn(__fdiv_rn(a2, (float)D), 1e-6f));
+  }
+  __syncthreads();
+  if (t < D) {
+    float zv = bk_bf16_to_f32(p.z[((size_t)b * p.Hv + hv) * D + t]);
+    float zs = __fmul_rn(zv, bk_sigmoidf(zv));
+    float ow = __fmul_rn(__fmul_rn(s_o[t], s_scal[0]), p.norm_w[t]);
+    p.out[((size_t)b * p.Hv + hv) * D + t] = bk_f32_to_bf16(__fmul_rn(ow, zs));
+  }
+}
+
+// ---- q/k head RMSNorm + partial rotary, one warp per (batch, head) ----------------
+// (src/emitters.ts:123-183).  Lane l owns the HD/32 contiguous dims of the head.
+template <int C>
+__device__ __forceinline__ void headnorm_rope_warp(const uint16_t* src, const uint16_t* w, const float* cos_row,
+                                                   const float* sin_row, int rot_half, uint16_t* stage,
+                                                   uint16_t* dst) {
+  const int lane = threadIdx.x & 31;
+  float x[C];
+#pragma unroll
+  for (int e = 0; e < C; e++) x[e] = bk_bf16_to_f32(src[lane * C + e]);
+  float acc = 0.0f;
+#pragma unroll
+  for (int e = 0; e < C; e++) acc = fmaf(x[e], x[e], acc);
+  acc = bk_warp_sum(acc);
+  float rstd = bk_rcp_sqrt(__fadd_rn(__fdiv_rn(acc, (float)(32 * C)), 1e-6f));
+#pragma unroll
+  for (int e = 0; e < C; e++) {
+    float wv = bk_bf16_to_f32(w[lane * C + e]);
+    stage[lane * C + e] = bk_f32_to_bf16(__fmul_rn(__fmul_rn(x[e], rstd), __fadd_rn(1.0f, wv)));
+  }
+  __syncwarp();
+  for (int i = lane; i < rot_half; i += 32) {
+    float x1 = bk_bf16_to_f32(stage[i]), x2 = bk_bf16_to_f32(stage[i + rot_half]);
+    float c = cos_row[i], s = sin_row[i];
+    uint16_t r1 = bk_f32_to_bf16(__fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s)));
+    uint16_t r2 = bk_f32_to_bf16(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s)));
+    stage[i] = r1;  // each pair (i, i+rot_half) is read and written by this lane only
+    stage[i + rot_half] = r2;
+  }
+  __syncwarp();
+  if (dst != stage) {
+#pragma unroll
+    for (int e = 0; e < C; e++) dst[lane * C + e] = stage[lane * C + e];
+  }
+}
+
+__global__ void __launch_bounds__(128) headnorm_rope_kernel(const uint16_t* in, int in_stride, const uint16_t* w,
+                                                            const float* cos_t, const float* sin_t, int rot_half,
+                                                            const int32_t* pos, int B, int nheads, int HD,
+                                                            uint16_t* out) {
+  __shared__ uint16_t stage[4][512];
+  const int warp = threadIdx.x >> 5;
+  const int idx = blockIdx.x * 4 + warp;
+  if (idx >= B * nheads) return;
+  const int b = idx / nheads;
+  const uint16_t* src = in + (size_t)idx * in_stride;
+  uint16_t* dst = out + (size_t)idx * HD;
+  const float* c = cos_t + (size_t)pos[b] * rot_half;
+  const float* s = sin_t + (size_t)pos[b] * rot_half;
+  if (HD == 256) headnorm_rope_warp<8>(src, w, c, s, rot_half, stage[warp], dst);
+  else headnorm_rope_warp<4>(src, w, c, s, rot_half, stage[warp], dst);
+}
+
+// ---- argmax: exact max, lowest index on ties (prototypes/decode.ts:776-784) -------
+__device__ __forceinline__ void argmax_merge(float& v, int& i, float ov, int oi) {
+  if (ov > v || (ov == v && oi < i)) {
+    v = ov;
+    i = oi;
+  }
+}
+
+constexpr int kArgmaxBlocks = 64;
+
+__global__ void __launch_bounds__(256) argmax_kernel(const float* logits, int V, int32_t* idx, float* val,
+                                                     float* part_v, int32_t* part_i, unsigned int* counter) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  __shared__ bool last;
+  const int b = blockIdx.y;
+  const float* l = logits + (size_t)b * V;
+  const int per = (V + gridDim.x - 1) / gridDim.x;
+  const int lo = blockIdx.x * per, hi = min(V, lo + per);
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = lo + threadIdx.x; i < hi; i += 256) {
+    float v = l[i];
+    if (v > bv) {
+      bv = v;
+      bi = i;
+    }
+  }
+  for (int off = 16; off >= 1; off >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+    int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+    argmax_merge(bv, bi, ov, oi);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    sv[threadIdx.x >> 5] = bv;
+    si[threadIdx.x >> 5] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; w++) argmax_merge(bv, bi, sv[w], si[w]);
+    part_v[b * kArgmaxBlocks + blockIdx.x] = bv;
+    part_i[b * kArgmaxBlocks + blockIdx.x] = bi;
+    __threadfence();
+    unsigned int done = atomicAdd(&counter[b], 1u);
+    last = (done == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (last && threadIdx.x == 0) {
+    __threadfence();
+    volatile float* pv = part_v;
+    volatile int32_t* pi = part_i;
+    float v = -INFINITY;
+    int i = 0x7fffffff;
+    for (unsigned k = 0; k < gridDim.x; k++) argmax_merge(v, i, pv[b * kArgmaxBlocks + k], pi[b * kArgmaxBlocks + k]);
+    if (i == 0x7fffffff) i = 0;
+    idx[b] = i;
+    val[b] = v;
+    counter[b] = 0;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t bkEmbedQ4K(uint64_t table, int32_t H, uint64_t ids, int32_t B, uint64_t x_out) {
+  BK_REQUIRE_INIT();
+  BK_ARG(H > 0 && H % 256 == 0 && B > 0, "bkEmbedQ4K: bad shape H=%d B=%d", H, B);
+  BK_ARG(table && ids && x_out && (table & 15) == 0, "bkEmbedQ4K: null or misaligned pointer");
+  embed_q4k_kernel<<<B, 64, 0, bk_ctx().stream>>>(bk_ptr<uint8_t>(table), H, bk_ptr<int32_t>(ids),
+                                                 bk_ptr<uint16_t>(x_out));
+  BK_CHECK_LAUNCH();
+  return BK_OK;
+}
+
+int32_t bkRmsNorm(uint64_t x, uint64_t w, int32_t H, int32_t B, float eps, uint64_t y) {
+  BK_REQUIRE_INIT();
+  BK_ARG(H > 0 && H % 8 == 0 && B > 0, "bkRmsNorm: bad shape H=%d B=%d", H, B);
+  BK_ARG(x && w && y && ((x | w | y) & 15) == 0, "bkRmsNorm: null or misaligned pointer");
+  rmsnorm_kernel<<<B, 256, 0, bk_ctx().stream>>>(bk_ptr<uint16_t>(x), bk_ptr<uint16_t>(w), H, eps,
+                                                bk_ptr<uint16_t>(y));
+  BK_CHECK_LAUNCH();
+  return BK_OK;
+}
+
+int32_t bkSwiglu(uint64_t g_f32, uint64_t u_f32, int32_t n, uint64_t out_bf16) {
+  BK_REQUIRE_INIT();
+  BK_ARG(n > 0 && g_f32 && u_f32 && out_bf16, "bkSwiglu: bad arguments");
+  swiglu_kernel<<<(n + 255) / 256, 256, 0, bk_ctx().stream>>>(bk_ptr<float>(g_f32), bk_ptr<float>(u_f32), n,
+                                                             bk_ptr<uint16_t>(out_bf16));
+  BK_CHECK_LAUNCH();
+  return BK_OK;
+}
+
+int32_t bkConv1dStep(uint64_t x, uint64_t state_in, uint64_t w, int32_t C, int32_t B, uint64_t out,
+                     uint64_t state_new) {
+  BK_REQUIRE_INIT();
+  BK_ARG(C > 0 && B > 0, "bkConv1dStep: bad shape C=%d B=%d", C, B);
+  BK_ARG(x && state_in && w && out && state_new && (w & 7) == 0, "bkConv1dStep: null or misaligned pointer");
+  BK_ARG(state_in != state_new, "bkConv1dStep: state_in and state_new must be distinct buffers");
+  int n = B * C;
+  conv1d_step_kernel<<<(n + 255) / 256, 256, 0, bk_ctx().stream>>>(bk_ptr<uint16_t>(x), bk_ptr<uint16_t>(state_in),
+                                                                  bk_ptr<uint16_t>(w), C, B, bk_ptr<uint16_t>(out),
+                                                                  bk_ptr<uint16_t>(state_new));
+  BK_CHECK_LAUNCH();
+  return BK_OK;
+}
+
+int32_t bkGdnStep(const bkGdnArgs* args) {
+  BK_REQUIRE_INIT();
+  BK_ARG(args != nullptr, "bkGdnStep: args is null");
+  bkGdnArgs a = *args;
+  BK_ARG(a.B > 0 && a.Hk > 0 && a.Hv > 0 && a.Hv % a.Hk == 0, "bkGdnStep: bad head counts B=%d Hk=%d Hv=%d", a.B, a.Hk,
+         a.Hv);
+  BK_ARG(a.qkv && a.z && a.a && a.b && a.A_log && a.dt_bias && a.norm_w && a.S_in && a.S_new && a.out,
+         "bkGdnStep: null pointer among required arguments");
+  if (a.apply_conv) {
+    BK_ARG(a.conv_w && a.conv_state_in && a.conv_state_new && (a.conv_w & 7) == 0,
+           "bkGdnStep: conv weights/state missing or misaligned");
+    BK_ARG(a.conv_state_in != a.conv_state_new, "bkGdnStep: conv state buffers must be distinct");
+  }
+  GdnParams p;
+  p.qkv = bk_ptr<uint16_t>(a.qkv);
+  p.z = bk_ptr<uint16_t>(a.z);
+  p.a = bk_ptr<float>(a.a);
+  p.b = bk_ptr<float>(a.b);
+  p.conv_w = bk_ptr<uint16_t>(a.conv_w);
+  p.cs_in = bk_ptr<uint16_t>(a.conv_state_in);
+  p.cs_new = bk_ptr<uint16_t>(a.conv_state_new);
+  p.A_log = bk_ptr<float>(a.A_log);
+  p.dt_bias = bk_ptr<uint16_t>(a.dt_bias);
+  p.norm_w = bk_ptr<float>(a.norm_w);
+  p.S_in = bk_ptr<float>(a.S_in);
+  p.S_new = bk_ptr<float>(a.S_new);
+  p.out = bk_ptr<uint16_t>(a.out);
+  p.o_raw = bk_ptr<float>(a.o_raw);
+  p.conv_out = bk_ptr<uint16_t>(a.conv_out);
+  p.B = a.B;
+  p.Hk = a.Hk;
+  p.Hv = a.Hv;
+  p.apply_conv = a.apply_conv;
+  gdn_step_kernel<<<dim3(a.Hv, a.B), 512, 0, bk_ctx().stream>>>(p);
+  BK_CHECK_LAUNCH();
+  return BK_OK;
+}
+
+int32_t bkRopeTables(int32_t max_len, int32_t rot_dim, double theta, float* cos_out, float* sin_out) {
+  if (max_len <= 0 || rot_dim <= 0 || (rot_dim & 1) || !cos_out || !sin_out)
+    return bk_fail(BK_ERR_ARG, "bkRopeTables: bad arguments");
+  int half = rot_dim / 2;
+  for (int p = 0; p < max_len; p++)
+    for (int i = 0; i < half; i++) {
+      double freq = 1.0 / pow(theta, 2.0 * i / rot_dim);
+      cos_out[(size_t)p * half + i] = (float)cos(p * freq);
+      sin_out[(size_t)p * half + i] = (float)sin(p * freq);
+    }
+  return BK_OK;
+}
+
+int32_t bkHeadNormRope(uint64_t in, int32_t in_stride, uint64_t w, uint64_t cos_t, uint64_t sin_t, int32_t rot_half,
+                       uint64_t pos, int32_t B, int32_t nheads, int32_t HD, uint64_t out) {
+  BK_REQUIRE_INIT();
+  BK_ARG(HD == 256 || HD == 128, "bkHeadNormRope: HD=%d unsupported (128 or 256)", HD);
+  BK_ARG(B > 0 && nheads > 0 && in_stride >= HD && rot_half > 0 && 2 * rot_half <= HD, "bkHeadNormRope: bad shape");
+  BK_ARG(rot_half <= 256, "bkHeadNormRope: rot_half=%d too large", rot_half);
+  BK_ARG(in && w && cos_t && sin_t && pos && out, "bkHeadNormRope: null pointer");
+  int n = B * nheads;
+  headnorm_rope_kernel<<<(n + 3) / 4, 128, 0, bk_ctx().stream>>>(
+      bk_ptr<uint16_t>(in), in_stride, bk_ptr<uint16_t>(w), bk_ptr<float>(cos_t), bk_ptr<float>(sin_t), rot_half,
+      bk_ptr<int32_t>(pos), B, nheads, HD, bk_ptr<uint16_t>(out));
+  BK_CHECK_LAUNCH();
+  return BK_OK;
+}
+
+uint64_t bkArgmaxScratchBytes(int32_t B) { return (uint64_t)(B > 0 ? B : 1) * (kArgmaxBlocks * 8 + 4); }
+
+int32_t bkArgmax(uint64_t logits, int32_t V, int32_t B, uint64_t idx, uint64_t val, uint64_t scratch) {
+  BK_REQUIRE_INIT();
+  BK_ARG(V > 0 && B > 0 && logits && idx && val && scratch, "bkArgmax: bad arguments");
+  // scratch: [B][64] f32, [B][64] i32, [B] counters (zero before first use; the kernel re-zeroes them)
+  float* pv = bk_ptr<float>(scratch);
+  int32_t* pi = reinterpret_cast<int32_t*>(pv + (size_t)B * kArgmaxBlocks);
+  unsigned int* cnt = reinterpret_cast<unsigned int*>(pi + (size_t)B * kArgmaxBlocks);
+  int blocks = (V + 2047) / 2048;
+  if (blocks > kArgmaxBlocks) blocks = kArgmaxBlocks;
+  argmax_kernel<<<dim3(blocks, B), 256, 0, bk_ctx().stream>>>(bk_ptr<float>(logits), V, bk_ptr<int32_t>(idx),
+                                                             bk_ptr<float>(val), pv, pi, cnt);
+  BK_CHECK_LAUNCH();
+  return BK_OK;
+}
+
+}  // extern "C"

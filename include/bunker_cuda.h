@@ -1,0 +1,206 @@
+/*
+ * bunker_cuda.h -- C ABI of libbunker_cuda.so, the sm_100a replacement for
+ * bunker's Triton lowering (shim/triton_shim.c) and raw-driver runtime
+ * (src/ttir.ts:223-348) on the hybrid decode hot path.
+ *
+ * Conventions (chosen for bun:ffi, see bunker's LOG.md:725-733):
+ *   - every entry point returns int32: 0 = success, otherwise a CUDA runtime
+ *     error number or one of the BK_ERR_* codes below; bkLastError() gives text
+ *   - device pointers, events and handles travel as uint64_t, never as `ptr`
+ *   - host buffers are borrowed for the duration of the call only
+ *   - argument structs are copied before the call returns
+ *   - nothing is read from the environment (bun's process.env never reaches
+ *     getenv, LOG.md:605-607)
+ *   - one context per process, one library-owned stream; every op enqueues on
+ *     that stream and returns without waiting (src/ttir.ts:342 uses stream 0)
+ *
+ * Citations name files of skyne98/bunker.
+ */
+#ifndef BUNKER_CUDA_H
+#define BUNKER_CUDA_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define BK_API __attribute__((visibility("default")))
+#else
+#define BK_API
+#endif
+
+#define BK_OK 0
+#define BK_ERR_ARG 10001       /* bad argument (size, alignment, null, range) */
+#define BK_ERR_STATE 10002     /* call made in the wrong state (not initialised, ...) */
+#define BK_ERR_TIMEOUT 10003   /* a bounded device-side wait gave up */
+#define BK_ERR_UNSUPPORTED 10004
+#define BK_ERR_COMM 10005      /* communicator / peer-mapping failure */
+
+/* ---- runtime: replaces cu()/cuAlloc/cuHtoD/cuDtoH/cuFree/cuSync ---------- */
+
+/* src/ttir.ts:223-261 cu(): open the driver, create the context on `device`. */
+BK_API int32_t bkInit(int32_t device);
+BK_API int32_t bkShutdown(void);
+/* Text of the most recent failure on this thread's library context. */
+BK_API const char* bkLastError(void);
+BK_API int32_t bkDeviceInfo(int32_t* sm_count, int32_t* cc_major, int32_t* cc_minor, uint64_t* total_mem);
+
+/* src/ttir.ts:266 cuAlloc */
+BK_API int32_t bkAlloc(uint64_t bytes, uint64_t* out_ptr);
+/* src/ttir.ts:283 cuFree */
+BK_API int32_t bkFree(uint64_t ptr);
+/* src/ttir.ts:273 cuHtoD (ordered after queued ops; returns when the host buffer may be reused) */
+BK_API int32_t bkHtoD(uint64_t dst, const void* src, uint64_t bytes);
+/* src/ttir.ts:278 cuDtoH (synchronous: doubles as the per-token barrier, prototypes/decode.ts:1042-1049) */
+BK_API int32_t bkDtoH(void* dst, uint64_t src, uint64_t bytes);
+/* src/ttir.ts:305-317 async copies; host memory must stay valid until bkSync */
+BK_API int32_t bkHtoDAsync(uint64_t dst, const void* src, uint64_t bytes);
+BK_API int32_t bkDtoHAsync(void* dst, uint64_t src, uint64_t bytes);
+BK_API int32_t bkDtoD(uint64_t dst, uint64_t src, uint64_t bytes);
+BK_API int32_t bkMemset(uint64_t dst, int32_t byte_value, uint64_t bytes);
+/* pinned host staging for bkHtoDAsync/bkDtoHAsync */
+BK_API int32_t bkHostAlloc(uint64_t bytes, void** out);
+BK_API int32_t bkHostFree(void* p);
+/* src/ttir.ts:285 cuSync */
+BK_API int32_t bkSync(void);
+
+/* src/ttir.ts:352-417 CUDA-event profiler: events on the library stream. */
+BK_API int32_t bkEventCreate(uint64_t* out_event);
+BK_API int32_t bkEventRecord(uint64_t event);
+BK_API int32_t bkEventSync(uint64_t event);
+BK_API int32_t bkEventElapsedMs(uint64_t start, uint64_t stop, float* out_ms);
+BK_API int32_t bkEventDestroy(uint64_t event);
+/* Number of kernels this library has launched since bkInit (graph replays count their kernels). */
+BK_API int32_t bkLaunchCount(uint64_t* out_count);
+
+/* ---- Q4_K x Q8_1 GEMV: replaces buildMM/buildGateSwiglu (prototypes/decode.ts:101-186),
+ *      emitGemm (src/fusion.ts:276-293) ------------------------------------- */
+
+/* prologues: how the activation reaches the kernel */
+#define BK_PRO_Q8 0       /* x = Q8_1 blocks [B][K/32][36] (bench/bench.ts:7 layout) */
+#define BK_PRO_BF16 1     /* x = bf16 [B][K]; quantised to Q8_1 inside the kernel */
+#define BK_PRO_RMSNORM 2  /* x = bf16 [B][K]; RMSNorm(x, norm_w, eps) -> bf16 -> Q8_1 inside the kernel
+                             (buildRMS, prototypes/decode.ts:201-216, fused) */
+/* epilogues */
+#define BK_EPI_F32 0      /* out f32 */
+#define BK_EPI_BF16 1     /* out bf16(acc)                      (decode.ts cast) */
+#define BK_EPI_ADD_BF16 2 /* out bf16(acc + f32(residual))      (decode.ts:152-154 add) */
+#define BK_EPI_SWIGLU 3   /* out bf16((g*sigmoid(g))*u), g from W, u from W2 (decode.ts:117-119) */
+
+typedef struct bkGemvSeg {
+  uint64_t W;        /* Q4_K rows [n_rows][K/256][144] */
+  uint64_t W2;       /* BK_EPI_SWIGLU: the up_proj rows, else 0 */
+  uint64_t out;      /* [B][ld_out] of the epilogue's element type */
+  uint64_t residual; /* BK_EPI_ADD_BF16: bf16 [B][ld_out] */
+  int32_t n_rows;
+  int32_t epilogue;
+  int32_t ld_out;    /* elements between consecutive batch rows of out / residual */
+  int32_t col_off;   /* column of out that receives this segment's row 0 */
+} bkGemvSeg;
+
+typedef struct bkGemvArgs {
+  int32_t K;         /* multiple of 256 */
+  int32_t B;         /* 1..8 */
+  int32_t n_segs;    /* 1..4 row segments that share the activation (qkv|z|a|b, gate|up, ...) */
+  int32_t prologue;
+  uint64_t x;
+  uint64_t norm_w;   /* bf16 [K], BK_PRO_RMSNORM only */
+  float eps;
+  int32_t reserved;
+  bkGemvSeg segs[4];
+} bkGemvArgs;
+
+BK_API int32_t bkGemvQ4K(const bkGemvArgs* args);
+/* config-0 convenience: y f32 [B][N] = W[N][K] (Q4_K) x xq (Q8_1 blocks) */
+BK_API int32_t bkGemvQ4KSimple(uint64_t W, int32_t N, int32_t K, uint64_t xq, int32_t B, uint64_t y);
+
+/* dequant (kernel.ts:422 / tests/test_dequant.ts:13-21 analogue for the 144-byte layout): f32 [N][K] */
+BK_API int32_t bkDequantQ4K(uint64_t W, int32_t N, int32_t K, uint64_t out_f32);
+/* integer stage alone (bench/bench.ts:24-33 s1/s2): int32 [N][K/32] each, for one Q8_1 row */
+BK_API int32_t bkBlockDotsQ4K(uint64_t W, int32_t N, int32_t K, uint64_t xq, uint64_t isum, uint64_t qsum);
+
+/* packQ8_1 (bench/bench.ts:53-72) on the device: f32 or bf16 [B][K] -> blocks [B][K/32][36] */
+BK_API int32_t bkQuantQ8_1(uint64_t x_f32, int32_t K, int32_t B, uint64_t out_blocks);
+BK_API int32_t bkQuantQ8_1Bf16(uint64_t x_bf16, int32_t K, int32_t B, uint64_t out_blocks);
+
+/* ---- small decode ops ------------------------------------------------------- */
+
+/* emitEmbed (src/emitters.ts:31-45): x bf16 [B][H] = dequant(table[ids[b]]); ids int32 on the device */
+BK_API int32_t bkEmbedQ4K(uint64_t table, int32_t H, uint64_t ids, int32_t B, uint64_t x_out);
+/* buildRMS (prototypes/decode.ts:201-216): y = bf16((x*rstd)*(1+w)) */
+BK_API int32_t bkRmsNorm(uint64_t x, uint64_t w, int32_t H, int32_t B, float eps, uint64_t y);
+/* emitSwiGLU (src/fusion.ts:324-330): out bf16 [n] from f32 g,u */
+BK_API int32_t bkSwiglu(uint64_t g_f32, uint64_t u_f32, int32_t n, uint64_t out_bf16);
+/* emitConv1d (src/emitters.ts:48-72): state [B][3][C] bf16 oldest first, w [C][4] bf16 */
+BK_API int32_t bkConv1dStep(uint64_t x, uint64_t state_in, uint64_t w, int32_t C, int32_t B, uint64_t out,
+                     uint64_t state_new);
+
+/* emitConv1d + emitGDN fused (src/emitters.ts:48-120, prototypes/decode.ts:272-388).
+ * qkv: bf16 [B][2*Hk*128+Hv*128] (pre-conv projection); z bf16 [B][Hv*128]; a,b f32 [B][Hv];
+ * conv state [B][3][C]; S f32 [B][Hv][128][128]; out bf16 [B][Hv*128] (normed and gated);
+ * o_raw (optional, 0 to skip) f32 [B][Hv*128] un-normalised head output.
+ * conv_out (optional) bf16 [B][C] receives the post-conv activations. */
+typedef struct bkGdnArgs {
+  uint64_t qkv, z, a, b;
+  uint64_t conv_w, conv_state_in, conv_state_new;
+  uint64_t A_log, dt_bias, norm_w;
+  uint64_t S_in, S_new;
+  uint64_t out, o_raw, conv_out;
+  int32_t B, Hk, Hv, apply_conv; /* apply_conv=0: qkv already holds conv output */
+} bkGdnArgs;
+BK_API int32_t bkGdnStep(const bkGdnArgs* args);
+
+/* f32 tables [max_len][rot_dim/2], filled on the host in double as prototypes/decode.ts:865-871 */
+BK_API int32_t bkRopeTables(int32_t max_len, int32_t rot_dim, double theta, float* cos_out, float* sin_out);
+
+/* emitQNorm/emitKNorm + emitRoPE/emitRoPEK (src/emitters.ts:123-183):
+ * in bf16 [B][nheads][in_stride] (first HD of each slot), out bf16 [B][nheads*HD]; pos int32 [B] on device */
+BK_API int32_t bkHeadNormRope(uint64_t in, int32_t in_stride, uint64_t w, uint64_t cos_t, uint64_t sin_t,
+                       int32_t rot_half, uint64_t pos, int32_t B, int32_t nheads, int32_t HD, uint64_t out);
+
+/* emitFA2Attn (src/emitters.ts:188-226) as split-KV flash-decode over a per-KV-head cache.
+ * qg: bf16 [B][Hq][2*HD] = per head q | gate (q_proj output); k, v: bf16 [B][Hkv*HD] projections.
+ * The kernel norms+rotates q and k, appends k,v at row pos[b], attends over rows 0..pos[b],
+ * and writes out bf16 [B][Hq*HD] = attention * sigmoid(gate).
+ * caches: bf16 [B][Hkv][max_len][HD].  scratch: bkAttnScratchBytes() bytes. */
+typedef struct bkAttnArgs {
+  uint64_t qg, k, v;
+  uint64_t q_norm_w, k_norm_w, cos_t, sin_t;
+  uint64_t k_cache, v_cache;
+  uint64_t pos;      /* int32 [B] on the device */
+  uint64_t out;
+  uint64_t scratch;
+  int32_t B, Hq, Hkv, HD, rot_half, max_len;
+  int32_t split_len; /* rows per split; 0 = library default from bkAttnPlan */
+  int32_t max_pos;   /* upper bound of pos[] this call may see (sizes the grid) */
+  float scale;
+  int32_t fused_norm_rope; /* 1: as above. 0: qg holds ready q in [B][Hq*HD], gate in `gate`, cache already appended */
+  uint64_t gate;     /* only for fused_norm_rope=0: bf16 [B][Hq*HD] */
+} bkAttnArgs;
+BK_API int32_t bkAttnDecode(const bkAttnArgs* args);
+/* split length and warps per split the library uses for n rows */
+BK_API int32_t bkAttnPlan(int32_t n_rows, int32_t B, int32_t Hkv, int32_t* split_len, int32_t* warps);
+BK_API uint64_t bkAttnScratchBytes(int32_t B, int32_t Hq, int32_t HD, int32_t max_len, int32_t split_len);
+
+/* buildArgmax+buildArgmaxComb (prototypes/decode.ts:749-791): exact max, lowest index on ties.
+ * logits f32 [B][V]; idx int32 [B]; val f32 [B]; scratch >= bkArgmaxScratchBytes(B) bytes */
+BK_API int32_t bkArgmax(uint64_t logits, int32_t V, int32_t B, uint64_t idx, uint64_t val, uint64_t scratch);
+BK_API uint64_t bkArgmaxScratchBytes(int32_t B);
+
+/* cuLaunch-shaped entry (src/ttir.ts:321-348): op id + 8-byte argument slots.
+ * Slot lists per op are documented in INTEGRATION.md. */
+BK_API int32_t bkLaunch(int32_t op, const uint64_t* slots, int32_t nslots);
+#define BK_OP_EMBED 1
+#define BK_OP_RMSNORM 2
+#define BK_OP_GEMV 3
+#define BK_OP_SWIGLU 4
+#define BK_OP_CONV1D 5
+#define BK_OP_ARGMAX 6
+#define BK_OP_QUANT_Q8_1 7
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BUNKER_CUDA_H */

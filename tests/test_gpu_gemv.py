@@ -1,0 +1,159 @@
+"""GPU parity of the Q4_K x Q8_1 path against the CPU oracle: dequant and integer block dots bit-exact,
+GEMV bit-exact against the canonical-order oracle and within 1e-3 of the plain restatement."""
+import numpy as np
+import pytest
+
+from bunker_b200 import ops, synth
+from bunker_b200 import runtime as R
+from oracle import oracle as O
+from tests.util import assert_same_bits, dev, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def test_dequant_bit_exact(bk):
+    N, K = 96, 1024
+    W = synth.q4k_weights(np.random.default_rng(1), N, K)
+    dW, out = dev(W), R.DeviceBuffer(N * K * 4)
+    ops.dequant_q4k(dW.ptr, N, K, out.ptr)
+    assert_same_bits(out.download(np.float32, (N, K)), O.q4k_dequant(W, N, K), "dequant")
+
+
+def test_dequant_denormal_and_extreme_headers(bk):
+    # d/dmin below the smallest normal half, scale bytes of all ones / all zeros
+    N, K = 4, 512
+    W = synth.q4k_weights(np.random.default_rng(2), N, K).reshape(N, K // 256, 144)
+    W[0, :, 0:4] = np.array([1e-6, 3e-7], np.float16).view(np.uint8)
+    W[1, :, 4:16] = 0xFF
+    W[2, :, 4:16] = 0
+    W[3, :, 16:] = 0xFF
+    W = W.reshape(N, -1)
+    dW, out = dev(W), R.DeviceBuffer(N * K * 4)
+    ops.dequant_q4k(dW.ptr, N, K, out.ptr)
+    assert_same_bits(out.download(np.float32, (N, K)), O.q4k_dequant(W, N, K), "dequant edge")
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_quant_q8_1_bit_exact(bk, bf16):
+    B, K = 3, 2048
+    x = np.random.default_rng(3).normal(0, 1, (B, K)).astype(np.float32)
+    x[0, :32] = 0.0          # all-zero block
+    x[1, 32:64] = 1e-30      # scale below half range
+    x[2, 64] = 3e4           # large magnitude
+    if bf16:
+        xb = synth.f32_to_bf16(x)
+        want = O.q8_1_quantize_bf16(xb)
+        dx = dev(xb)
+    else:
+        want = O.q8_1_quantize(x)
+        dx = dev(x)
+    out = R.DeviceBuffer(B * K // 32 * 36)
+    ops.quant_q8_1(dx.ptr, K, B, out.ptr, bf16=bf16)
+    assert_same_bits(out.download(np.uint8, (B, K // 32, 36)), want, "q8_1 blocks")
+
+
+def test_block_dots_bit_exact(bk):
+    N, K = 64, 2048
+    W, x = synth.gemv_case(N, K, 1)
+    xq = O.q8_1_quantize(x)
+    dW, dx = dev(W), dev(xq)
+    di, dq = R.DeviceBuffer(N * K // 32 * 4), R.DeviceBuffer(N * K // 32 * 4)
+    ops.block_dots(dW.ptr, N, K, dx.ptr, di.ptr, dq.ptr)
+    gi, gq = di.download(np.int32, (N, K // 32)), dq.download(np.int32, (N, K // 32))
+    for n in range(N):
+        wi, wq = O.block_dots(W[n], xq[0], K)
+        assert np.array_equal(gi[n], wi) and np.array_equal(gq[n], wq), f"row {n}"
+
+
+def test_gemv_config0(bk):
+    """configs[0]: 4096x4096 Q4_K, x f32 N(0,1) -> Q8_1, y f32."""
+    N, K = 4096, 4096
+    W, x = synth.gemv_case(N, K, 1)
+    dW, dx = dev(W), dev(x)
+    dxq, dy = R.DeviceBuffer(K // 32 * 36), R.DeviceBuffer(N * 4)
+    ops.quant_q8_1(dx.ptr, K, 1, dxq.ptr)
+    ops.gemv_simple(dW.ptr, N, K, dxq.ptr, 1, dy.ptr)
+    y = dy.download(np.float32, (1, N))
+    xq = O.q8_1_quantize(x)
+    assert_same_bits(dxq.download(np.uint8, (1, K // 32, 36)), xq, "xq")
+    assert_same_bits(y, O.gemv_q4k_q8(W, N, K, xq), "gemv canonical")
+    assert rel_err(y, O.gemv_q4k_q8_plain(W, N, K, xq)) < 1e-3
+
+
+@pytest.mark.parametrize("B", [1, 2, 3, 4, 5, 6, 7, 8])
+@pytest.mark.parametrize("K", [256, 2048, 6144])
+def test_gemv_batches_and_tails(bk, B, K):
+    N = 131  # odd: exercises the unpaired last row
+    W, x = synth.gemv_case(N, K, B, config_id=10 + B)
+    xq = O.q8_1_quantize(x)
+    dW, dxq, dy = dev(W), dev(xq), R.DeviceBuffer(B * N * 4)
+    ops.gemv_simple(dW.ptr, N, K, dxq.ptr, B, dy.ptr)
+    assert_same_bits(dy.download(np.float32, (B, N)), O.gemv_q4k_q8(W, N, K, xq), f"gemv B={B} K={K}")
+
+
+@pytest.mark.parametrize("B", [1, 8])
+def test_gemv_fused_prologues_epilogues(bk, B):
+    """One launch: RMSNorm prologue, three segments with f32 / bf16 / residual-add epilogues."""
+    K, N0, N1, N2 = 2048, 96, 64, 32
+    rng = np.random.default_rng(40 + B)
+    Ws = [synth.q4k_weights(rng, n, K) for n in (N0, N1, N2)]
+    x = synth.normal_bf16(rng, (B, K))
+    nw = synth.normal_bf16(rng, (K,), 0.02)
+    res = synth.normal_bf16(rng, (B, N2))
+    xn = O.rmsnorm(x, nw)
+    xq = O.q8_1_quantize_bf16(xn)
+    want0 = O.gemv_q4k_q8(Ws[0], N0, K, xq)
+    want1 = O.epilogue_cast(O.gemv_q4k_q8(Ws[1], N1, K, xq))
+    want2 = O.epilogue_add(O.gemv_q4k_q8(Ws[2], N2, K, xq), res)
+    dWs = [dev(w) for w in Ws]
+    dx, dnw, dres = dev(x), dev(nw), dev(res)
+    o0, o1, o2 = R.DeviceBuffer(B * N0 * 4), R.DeviceBuffer(B * N1 * 2), R.DeviceBuffer(B * N2 * 2)
+    ops.gemv(dx.ptr, K, B, [
+        ops.gemv_seg(dWs[0].ptr, N0, o0.ptr, R.BK_EPI_F32),
+        ops.gemv_seg(dWs[1].ptr, N1, o1.ptr, R.BK_EPI_BF16),
+        ops.gemv_seg(dWs[2].ptr, N2, o2.ptr, R.BK_EPI_ADD_BF16, residual=dres.ptr),
+    ], prologue=R.BK_PRO_RMSNORM, norm_w=dnw.ptr)
+    assert_same_bits(o0.download(np.float32, (B, N0)), want0, "f32 segment")
+    assert_same_bits(o1.download(np.uint16, (B, N1)), want1, "bf16 segment")
+    assert_same_bits(o2.download(np.uint16, (B, N2)), want2, "add segment")
+
+
+@pytest.mark.parametrize("B", [1, 4])
+def test_gemv_swiglu_bf16_prologue(bk, B):
+    K, N = 1024, 200
+    rng = np.random.default_rng(50 + B)
+    Wg, Wu = synth.q4k_weights(rng, N, K), synth.q4k_weights(rng, N, K)
+    x = synth.normal_bf16(rng, (B, K))
+    xq = O.q8_1_quantize_bf16(x)
+    want = O.swiglu(O.gemv_q4k_q8(Wg, N, K, xq), O.gemv_q4k_q8(Wu, N, K, xq))
+    dWg, dWu, dx, out = dev(Wg), dev(Wu), dev(x), R.DeviceBuffer(B * N * 2)
+    ops.gemv(dx.ptr, K, B, [ops.gemv_seg(dWg.ptr, N, out.ptr, R.BK_EPI_SWIGLU, W2=dWu.ptr)], prologue=R.BK_PRO_BF16)
+    assert_same_bits(out.download(np.uint16, (B, N)), want, "swiglu")
+
+
+def test_gemv_rejects_bad_arguments(bk):
+    with pytest.raises(R.BunkerCudaError) as e:
+        ops.gemv_simple(16, 4, 100, 16, 1, 16)  # K not a multiple of 256
+    assert e.value.code == R.BK_ERR_ARG
+    with pytest.raises(R.BunkerCudaError):
+        ops.gemv_simple(16, 4, 256, 16, 9, 16)  # batch beyond 8
+
+
+def test_gemv_linearity_full_size(bk):
+    """Size-independent property at lm_head scale: doubling every Q8_1 scale doubles y exactly."""
+    N, K = 151936, 2048
+    W, x = synth.gemv_case(N, K, 1, config_id=77)
+    xq = O.q8_1_quantize(x)
+    xq2 = xq.copy()
+    d = xq2[:, :, 32:34].copy().view(np.float16)
+    xq2[:, :, 32:34] = (d * np.float16(2)).view(np.uint8)
+    dW, a, b = dev(W), dev(xq), dev(xq2)
+    ya, yb = R.DeviceBuffer(N * 4), R.DeviceBuffer(N * 4)
+    ops.gemv_simple(dW.ptr, N, K, a.ptr, 1, ya.ptr)
+    ops.gemv_simple(dW.ptr, N, K, b.ptr, 1, yb.ptr)
+    y1, y2 = ya.download(np.float32, (N,)), yb.download(np.float32, (N,))
+    assert np.isfinite(y1).all()
+    assert_same_bits(y2, y1 * np.float32(2), "linearity")
+    rows = np.random.default_rng(0).choice(N, 64, replace=False)
+    want = O.gemv_q4k_q8(W[rows], 64, K, xq)
+    assert_same_bits(y1[rows].reshape(1, -1), want, "sampled rows")

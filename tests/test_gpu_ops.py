@@ -1,0 +1,233 @@
+"""GPU parity of the non-GEMV decode ops (embed, rmsnorm, swiglu, conv1d, GDN step, head norm + rope,
+attention, argmax) against the CPU oracle: bit-exact against the canonical-order functions, 1e-3
+relative against the plain restatements of the reference's host loops."""
+import numpy as np
+import pytest
+
+from bunker_b200 import ops, synth
+from bunker_b200 import runtime as R
+from oracle import oracle as O
+from tests.util import assert_same_bits, dev, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def test_embed(bk):
+    V, H, B = 300, 2048, 5
+    table = synth.q4k_weights(np.random.default_rng(5), V, H)
+    ids = np.array([0, 299, 17, 17, 123], np.int32)
+    dt, di, out = dev(table), dev(ids), R.DeviceBuffer(B * H * 2)
+    ops.embed(dt.ptr, H, di.ptr, B, out.ptr)
+    assert_same_bits(out.download(np.uint16, (B, H)), O.embed_q4k(table, H, ids), "embed")
+
+
+@pytest.mark.parametrize("H", [2048, 5120, 256])
+def test_rmsnorm(bk, H):
+    B = 3
+    rng = np.random.default_rng(6)
+    x, w = synth.normal_bf16(rng, (B, H), 3.0), synth.normal_bf16(rng, (H,), 0.02)
+    dx, dw, dy = dev(x), dev(w), R.DeviceBuffer(B * H * 2)
+    ops.rmsnorm(dx.ptr, dw.ptr, H, B, dy.ptr)
+    y = dy.download(np.uint16, (B, H))
+    assert_same_bits(y, O.rmsnorm(x, w), "rmsnorm")
+    assert rel_err(synth.bf16_to_f32(y), O.rmsnorm_plain(x, w)) < 5e-3  # bf16 output rounding
+
+
+def test_swiglu(bk):
+    n = 6144
+    rng = np.random.default_rng(7)
+    g, u = rng.normal(0, 4, n).astype(np.float32), rng.normal(0, 4, n).astype(np.float32)
+    g[:4] = [0.0, -100.0, 100.0, -1e-8]
+    dg, du, out = dev(g), dev(u), R.DeviceBuffer(n * 2)
+    ops.swiglu(dg.ptr, du.ptr, n, out.ptr)
+    assert_same_bits(out.download(np.uint16, (n,)), O.swiglu(g, u), "swiglu")
+
+
+def test_conv1d_step(bk):
+    B, Cw = 2, 8192
+    rng = np.random.default_rng(8)
+    x, st, w = synth.normal_bf16(rng, (B, Cw)), synth.normal_bf16(rng, (B, 3, Cw)), synth.normal_bf16(rng, (Cw, 4), 0.3)
+    dx, ds, dw = dev(x), dev(st), dev(w)
+    out, sn = R.DeviceBuffer(B * Cw * 2), R.DeviceBuffer(B * 3 * Cw * 2)
+    ops.conv1d_step(dx.ptr, ds.ptr, dw.ptr, Cw, B, out.ptr, sn.ptr)
+    wo, ws = O.conv1d_step(x, st, w)
+    assert_same_bits(out.download(np.uint16, (B, Cw)), wo, "conv out")
+    assert_same_bits(sn.download(np.uint16, (B, 3, Cw)), ws, "conv state")
+
+
+def _gdn_oracle(c):
+    conv_out, cs_new = O.conv1d_step(c["qkv"], c["conv_state"], c["conv_w"])
+    S_new, o_raw = O.gdn_step(conv_out, c["a"], c["b"], c["A_log"], c["dt_bias"], c["S"], c["Hk"], c["Hv"])
+    out = O.gdn_gate_norm(o_raw, c["z"], c["norm_w"], c["Hv"])
+    return conv_out, cs_new, S_new, o_raw, out
+
+
+@pytest.mark.parametrize("B", [1, 8])
+def test_gdn_step_config1(bk, B):
+    """configs[1]: 16 key heads, 32 value heads, d=128, fused causal conv over width 8192."""
+    c = synth.gdn_case(B)
+    Hk, Hv = c["Hk"], c["Hv"]
+    Cw = 2 * Hk * 128 + Hv * 128
+    d = {k: dev(v) for k, v in c.items() if isinstance(v, np.ndarray)}
+    cs_new, S_new = R.DeviceBuffer(B * 3 * Cw * 2), R.DeviceBuffer(B * Hv * 128 * 128 * 4)
+    out, o_raw, conv_out = R.DeviceBuffer(B * Hv * 128 * 2), R.DeviceBuffer(B * Hv * 128 * 4), R.DeviceBuffer(B * Cw * 2)
+    ops.gdn_step(qkv=d["qkv"].ptr, z=d["z"].ptr, a=d["a"].ptr, b=d["b"].ptr, conv_w=d["conv_w"].ptr,
+                 conv_state_in=d["conv_state"].ptr, conv_state_new=cs_new.ptr, A_log=d["A_log"].ptr,
+                 dt_bias=d["dt_bias"].ptr, norm_w=d["norm_w"].ptr, S_in=d["S"].ptr, S_new=S_new.ptr, out=out.ptr,
+                 o_raw=o_raw.ptr, conv_out=conv_out.ptr, B=B, Hk=Hk, Hv=Hv, apply_conv=1)
+    w_conv, w_cs, w_S, w_o, w_out = _gdn_oracle(c)
+    assert_same_bits(conv_out.download(np.uint16, (B, Cw)), w_conv, "conv_out")
+    assert_same_bits(cs_new.download(np.uint16, (B, 3, Cw)), w_cs, "conv state")
+    assert_same_bits(o_raw.download(np.float32, (B, Hv, 128)), w_o, "o_raw")
+    assert_same_bits(S_new.download(np.float32, (B, Hv, 128, 128)), w_S, "S_new")
+    assert_same_bits(out.download(np.uint16, (B, Hv * 128)), w_out, "gated out")
+    # plain recurrence (prototypes/gdn_gated.ts:67-88) on head (0, 5), double math
+    import math
+    hv, hk = 5, 5 // (Hv // Hk)
+    co = synth.bf16_to_f32(w_conv[0])
+    q, k = co[hk * 128:(hk + 1) * 128], co[Hk * 128 + hk * 128: Hk * 128 + (hk + 1) * 128]
+    v = co[2 * Hk * 128 + hv * 128: 2 * Hk * 128 + (hv + 1) * 128]
+    sp = math.log1p(math.exp(float(c["a"][0, hv]) + float(synth.bf16_to_f32(c["dt_bias"][hv:hv + 1])[0])))
+    decay = math.exp(-math.exp(float(c["A_log"][hv])) * sp)
+    beta = 1.0 / (1.0 + math.exp(-float(c["b"][0, hv])))
+    Sp, op = O.gdn_step_plain(q, k, v, decay, beta, c["S"][0, hv])
+    assert rel_err(w_S[0, hv], Sp) < 1e-3 and rel_err(w_o[0, hv], op) < 1e-3
+
+
+def test_gdn_step_without_conv(bk):
+    c = synth.gdn_case(2, Hk=2, Hv=4, config_id=21)
+    Hk, Hv, B = 2, 4, 2
+    d = {k: dev(v) for k, v in c.items() if isinstance(v, np.ndarray)}
+    S_new, out = R.DeviceBuffer(B * Hv * 128 * 128 * 4), R.DeviceBuffer(B * Hv * 128 * 2)
+    ops.gdn_step(qkv=d["qkv"].ptr, z=d["z"].ptr, a=d["a"].ptr, b=d["b"].ptr, A_log=d["A_log"].ptr,
+                 dt_bias=d["dt_bias"].ptr, norm_w=d["norm_w"].ptr, S_in=d["S"].ptr, S_new=S_new.ptr, out=out.ptr,
+                 B=B, Hk=Hk, Hv=Hv, apply_conv=0)
+    w_S, w_o = O.gdn_step(c["qkv"], c["a"], c["b"], c["A_log"], c["dt_bias"], c["S"], Hk, Hv)
+    assert_same_bits(S_new.download(np.float32, (B, Hv, 128, 128)), w_S, "S_new")
+    assert_same_bits(out.download(np.uint16, (B, Hv * 128)), O.gdn_gate_norm(w_o, c["z"], c["norm_w"], Hv), "out")
+
+
+def test_headnorm_rope(bk):
+    B, nh, HD = 3, 16, 256
+    rng = np.random.default_rng(9)
+    x, w = synth.normal_bf16(rng, (B, nh * 2 * HD)), synth.normal_bf16(rng, (HD,), 0.02)
+    cos_t, sin_t = ops.rope_tables(4096)
+    oc, os_ = O.rope_tables(4096)
+    assert_same_bits(cos_t, oc, "cos table")
+    assert_same_bits(sin_t, os_, "sin table")
+    pos = np.array([0, 77, 4095], np.int32)
+    dx, dw, dc, ds, dp = dev(x), dev(w), dev(cos_t), dev(sin_t), dev(pos)
+    out = R.DeviceBuffer(B * nh * HD * 2)
+    ops.headnorm_rope(dx.ptr, 2 * HD, dw.ptr, dc.ptr, ds.ptr, 32, dp.ptr, B, nh, HD, out.ptr)
+    assert_same_bits(out.download(np.uint16, (B, nh * HD)), O.headnorm_rope(x, 2 * HD, w, cos_t, sin_t, pos, nh, HD),
+                     "headnorm_rope")
+
+
+def _attn_oracle(c, cos_t, sin_t, split_len, W):
+    B, Hq, Hkv, HD = c["B"], c["Hq"], c["Hkv"], c["HD"]
+    q = O.headnorm_rope(c["qg"], 2 * HD, c["q_norm_w"], cos_t, sin_t, c["pos"], Hq, HD)
+    k = O.headnorm_rope(c["k"], HD, c["k_norm_w"], cos_t, sin_t, c["pos"], Hkv, HD)
+    Kc, Vc = c["k_cache"].copy(), c["v_cache"].copy()
+    for b in range(B):
+        Kc[b, :, c["pos"][b]] = k[b].reshape(Hkv, HD)
+        Vc[b, :, c["pos"][b]] = c["v"][b].reshape(Hkv, HD)
+    gate = np.ascontiguousarray(c["qg"].reshape(B, Hq, 2, HD)[:, :, 1])
+    out = O.attn_decode(q, gate, HD, Kc, Vc, c["pos"], Hq, Hkv, HD, split_len, W, 1.0 / 16.0)
+    return q, Kc, Vc, out
+
+
+def _run_attn(c, cos_t, sin_t, split_len=0):
+    B, Hq, Hkv, HD, ml = c["B"], c["Hq"], c["Hkv"], c["HD"], c["max_len"]
+    max_pos = int(c["pos"].max())
+    if split_len == 0:
+        split_len, W = ops.attn_plan(max_pos + 1, B, Hkv)
+    else:
+        W = 8
+    d = {k: dev(v) for k, v in c.items() if isinstance(v, np.ndarray)}
+    dc, ds = dev(cos_t), dev(sin_t)
+    scratch = R.DeviceBuffer(ops.attn_scratch_bytes(B, Hq, HD, ml, split_len))
+    out = R.DeviceBuffer(B * Hq * HD * 2)
+    ops.attn_decode(qg=d["qg"].ptr, k=d["k"].ptr, v=d["v"].ptr, q_norm_w=d["q_norm_w"].ptr, k_norm_w=d["k_norm_w"].ptr,
+                    cos_t=dc.ptr, sin_t=ds.ptr, k_cache=d["k_cache"].ptr, v_cache=d["v_cache"].ptr, pos=d["pos"].ptr,
+                    out=out.ptr, scratch=scratch.ptr, B=B, Hq=Hq, Hkv=Hkv, HD=HD, rot_half=32, max_len=ml,
+                    split_len=split_len, max_pos=max_pos, scale=1.0 / 16.0, fused_norm_rope=1)
+    got = out.download(np.uint16, (B, Hq * HD))
+    Kg = d["k_cache"].download(np.uint16, c["k_cache"].shape)
+    Vg = d["v_cache"].download(np.uint16, c["v_cache"].shape)
+    for b in d.values():
+        b.free()
+    scratch.free(), out.free(), dc.free(), ds.free()
+    return got, Kg, Vg, split_len, W
+
+
+@pytest.mark.parametrize("B,L", [(1, 1), (1, 7), (2, 64), (1, 65), (2, 300), (1, 1024), (8, 1024), (1, 4096)])
+def test_attn_decode(bk, B, L):
+    """configs[2] shapes: 16 q heads, 2 kv heads, head_dim 256, rotary 64 of 256, theta 1e7, sigmoid gate."""
+    cos_t, sin_t = ops.rope_tables(max(L, 64))
+    c = synth.attn_case(B, L)
+    got, Kg, Vg, split_len, W = _run_attn(c, cos_t, sin_t)
+    q, Kc, Vc, want = _attn_oracle(c, cos_t, sin_t, split_len, W)
+    assert_same_bits(Kg, Kc, "k cache after append")
+    assert_same_bits(Vg, Vc, "v cache after append")
+    assert_same_bits(got, want, f"attention B={B} L={L} split_len={split_len}")
+
+
+def test_attn_decode_ragged_positions_and_plain(bk):
+    """Sequences of different lengths in one batch; one head also checked against the plain softmax."""
+    B, L = 4, 700
+    cos_t, sin_t = ops.rope_tables(1024)
+    c = synth.attn_case(B, L, max_len=1024, config_id=31)
+    c["pos"] = np.array([0, 63, 64, 699], np.int32)
+    got, Kg, Vg, split_len, W = _run_attn(c, cos_t, sin_t, split_len=64)
+    q, Kc, Vc, want = _attn_oracle(c, cos_t, sin_t, split_len, W)
+    assert_same_bits(got, want, "ragged attention")
+    b, h, HD = 3, 9, 256
+    kvh = h // 8
+    plain = O.attn_decode_plain(q[b, h * HD:(h + 1) * HD], Kc[b, kvh], Vc[b, kvh], 700, HD, 1.0 / 16.0)
+    gate = synth.bf16_to_f32(c["qg"].reshape(B, 16, 2, HD)[b, h, 1]).astype(np.float64)
+    plain = plain / (1.0 + np.exp(-gate))
+    assert rel_err(synth.bf16_to_f32(got[b, h * HD:(h + 1) * HD]), plain) < 5e-3  # bf16 output rounding
+
+
+def test_attn_decode_long_context(bk):
+    """configs[2] longest cache (32768 rows), batch 1, default plan; bit-exact against the oracle."""
+    L = 32768
+    cos_t, sin_t = ops.rope_tables(L)
+    c = synth.attn_case(1, L)
+    got, Kg, Vg, split_len, W = _run_attn(c, cos_t, sin_t)
+    q, Kc, Vc, want = _attn_oracle(c, cos_t, sin_t, split_len, W)
+    assert_same_bits(got, want, f"attention L={L} split_len={split_len}")
+
+
+def test_argmax(bk):
+    B, V = 3, 151936
+    rng = np.random.default_rng(11)
+    logits = rng.normal(0, 3, (B, V)).astype(np.float32)
+    logits[0, 5] = logits[0, 150000] = 50.0       # tie: lowest index wins
+    logits[1, V - 1] = 60.0                       # maximum in the last, short chunk
+    logits[2, :] = -7.0                           # all equal -> index 0
+    dl, idx, val = dev(logits), R.DeviceBuffer(B * 4), R.DeviceBuffer(B * 4)
+    scratch = R.DeviceBuffer.zeros(ops.argmax_scratch_bytes(B))
+    for _ in range(2):  # second call checks that the kernel re-armed its counters
+        ops.argmax(dl.ptr, V, B, idx.ptr, val.ptr, scratch.ptr)
+    wi, wv = O.argmax(logits)
+    assert np.array_equal(idx.download(np.int32, (B,)), wi) and list(wi) == [5, V - 1, 0]
+    assert_same_bits(val.download(np.float32, (B,)), wv, "argmax value")
+
+
+def test_culaunch_surface(bk):
+    """The cuLaunch-shaped path (src/ttir.ts:321-348): op handle + 8-byte slots; rc returned, not raised."""
+    H, B = 2048, 2
+    rng = np.random.default_rng(12)
+    x, w = synth.normal_bf16(rng, (B, H)), synth.normal_bf16(rng, (H,), 0.02)
+    dx, dw, dy = R.cuAlloc(x.nbytes), R.cuAlloc(w.nbytes), R.cuAlloc(x.nbytes)
+    R.cuHtoD(dx, x), R.cuHtoD(dw, w)
+    k = R.loadOp("rmsnorm")
+    assert R.cuLaunch(k, [1, 1, 1], [128, 1, 1], [dx, dw, dy, H, B, 1e-6]) == 0
+    assert R.cuSync() == 0
+    y = np.empty_like(x)
+    R.cuDtoH(y, dy)
+    assert_same_bits(y, O.rmsnorm(x, w), "rmsnorm via cuLaunch")
+    assert R.cuLaunch(k, [1, 1, 1], [128, 1, 1], [dx, dw]) == R.BK_ERR_ARG  # wrong slot count -> rc, no raise
+    for p in (dx, dw, dy):
+        R.cuFree(p)
