@@ -1,0 +1,437 @@
+// bk_model.cu -- the whole hybrid decode step behind one call per token.
+//
+// Stands where bunker's graph executor stands: buildModelGraph (src/model.ts:46-204) declares the
+// per-token DAG and runGraphDecode (src/runner.ts:116-162) launches ~287 kernels per token from
+// TypeScript.  bunker found that replaying a CUDA graph through bun:ffi crashes (LOG.md:710-738), so
+// here the graph is captured and replayed inside the library and the host makes one call per token.
+//
+// Step (tp_size = 1), per layer:
+//   GDN layer      : [RMSNorm+Q8_1 | qkv,z,a,b GEMV] -> [conv1d+GDN] -> [Q8_1 | out_proj GEMV + residual]
+//   attention layer: [RMSNorm+Q8_1 | q,k,v GEMV] -> [norm+rope+append+split attention] -> [combine+gate]
+//                    -> [Q8_1 | o_proj GEMV + residual]
+//   MLP            : [RMSNorm+Q8_1 | gate,up GEMV + SwiGLU] -> [Q8_1 | down GEMV + residual]
+// then [RMSNorm+Q8_1 | lm_head GEMV] -> [argmax, token feedback, pos++].
+// Layer kind: layer % interval == interval-1 is full attention (src/model.ts:61).
+#include <string.h>
+
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "bk_internal.h"
+
+namespace {
+
+struct Tensor {
+  uint64_t ptr = 0;
+  uint64_t bytes = 0;
+};
+
+struct LayerW {
+  bool full = false;
+  uint64_t in_ln = 0, post_ln = 0;
+  // GDN
+  uint64_t qkv = 0, z = 0, a = 0, b = 0, conv_w = 0, A_log = 0, dt_bias = 0, gnorm = 0, out_proj = 0;
+  // attention
+  uint64_t q = 0, k = 0, v = 0, q_norm = 0, k_norm = 0, o = 0;
+  // MLP
+  uint64_t gate = 0, up = 0, down = 0;
+  // state (owned by the model)
+  uint64_t conv_state[2] = {0, 0}, S = 0, kc = 0, vc = 0;
+};
+
+struct Model {
+  bkModelConfig cfg;
+  std::unordered_map<std::string, Tensor> tensors;
+  std::vector<LayerW> layers;
+  uint64_t embed = 0, final_norm = 0;
+  bool finalized = false;
+  int B = 0;
+  // derived, per rank
+  int Hk = 0, Hv = 0, Hq = 0, Hkv = 0, Cw = 0, ZD = 0, QG = 0, KVD = 0, inter = 0, vocab_local = 0;
+  int split_len = 0;
+  // device buffers
+  std::vector<uint64_t> owned;
+  uint64_t x[2] = {0, 0}, h1 = 0, qkv = 0, z = 0, a = 0, b = 0, attn_out = 0, qg = 0, kbuf = 0, vbuf = 0, act = 0;
+  uint64_t logits = 0, ids = 0, val = 0, pos = 0, hist = 0, argmax_scratch = 0, attn_scratch = 0, cos_t = 0, sin_t = 0;
+  int32_t* pin_ids = nullptr;  // pinned staging: B ids in, B ids out, B vals
+  cudaGraphExec_t graph[2] = {nullptr, nullptr};
+  unsigned long long graph_kernels = 0;
+  long long steps = 0;  // steps taken since the last reset (host mirror of pos)
+};
+
+int32_t dev_alloc(Model& m, size_t bytes, uint64_t* out, bool zero = true) {
+  void* p = nullptr;
+  BK_CUDA(cudaMalloc(&p, bytes ? bytes : 16));
+  if (zero) BK_CUDA(cudaMemsetAsync(p, 0, bytes ? bytes : 16, bk_ctx().stream));
+  *out = (uint64_t)(uintptr_t)p;
+  m.owned.push_back(*out);
+  return BK_OK;
+}
+
+int32_t need(Model& m, const std::string& name, uint64_t bytes, uint64_t* out) {
+  auto it = m.tensors.find(name);
+  if (it == m.tensors.end()) return bk_fail(BK_ERR_STATE, "bkModelFinalize: tensor '%s' was never set", name.c_str());
+  if (it->second.bytes != bytes)
+    return bk_fail(BK_ERR_ARG, "bkModelFinalize: tensor '%s' has %llu bytes, expected %llu", name.c_str(),
+                   (unsigned long long)it->second.bytes, (unsigned long long)bytes);
+  if (it->second.ptr & 15) return bk_fail(BK_ERR_ARG, "bkModelFinalize: tensor '%s' is not 16-byte aligned", name.c_str());
+  *out = it->second.ptr;
+  return BK_OK;
+}
+
+inline uint64_t q4k_bytes(uint64_t n, uint64_t k) { return n * (k / 256) * 144; }
+
+#define TRY(expr)            \
+  do {                       \
+    int32_t _rc = (expr);    \
+    if (_rc) return _rc;     \
+  } while (0)
+
+// enqueue one decode step on the library stream; parity selects the conv-state buffer pair
+int32_t enqueue_step(Model& m, int parity) {
+  const bkModelConfig& c = m.cfg;
+  const int B = m.B, H = c.hidden;
+  int cur = 0;
+  TRY(bkEmbedQ4K(m.embed, H, m.ids, B, m.x[0]));
+  for (int li = 0; li < c.n_layers; li++) {
+    LayerW& L = m.layers[li];
+    bkGemvArgs g;
+    if (!L.full) {
+      memset(&g, 0, sizeof(g));
+      g.K = H; g.B = B; g.prologue = BK_PRO_RMSNORM; g.x = m.x[cur]; g.norm_w = L.in_ln; g.eps = c.eps;
+      g.n_segs = 4;
+      g.segs[0] = bkGemvSeg{L.qkv, 0, m.qkv, 0, m.Cw, BK_EPI_BF16, m.Cw, 0};
+      g.segs[1] = bkGemvSeg{L.z, 0, m.z, 0, m.ZD, BK_EPI_BF16, m.ZD, 0};
+      g.segs[2] = bkGemvSeg{L.a, 0, m.a, 0, m.Hv, BK_EPI_F32, m.Hv, 0};
+      g.segs[3] = bkGemvSeg{L.b, 0, m.b, 0, m.Hv, BK_EPI_F32, m.Hv, 0};
+      TRY(bk_gemv_launch(g));
+      bkGdnArgs ga;
+      memset(&ga, 0, sizeof(ga));
+      ga.qkv = m.qkv; ga.z = m.z; ga.a = m.a; ga.b = m.b;
+      ga.conv_w = L.conv_w; ga.conv_state_in = L.conv_state[parity]; ga.conv_state_new = L.conv_state[parity ^ 1];
+      ga.A_log = L.A_log; ga.dt_bias = L.dt_bias; ga.norm_w = L.gnorm;
+      ga.S_in = L.S; ga.S_new = L.S;  // in place: each thread rewrites exactly the rows it read
+      ga.out = m.attn_out; ga.B = B; ga.Hk = m.Hk; ga.Hv = m.Hv; ga.apply_conv = 1;
+      TRY(bkGdnStep(&ga));
+      memset(&g, 0, sizeof(g));
+      g.K = m.ZD; g.B = B; g.prologue = BK_PRO_BF16; g.x = m.attn_out; g.n_segs = 1;
+      g.segs[0] = bkGemvSeg{L.out_proj, 0, m.h1, m.x[cur], H, BK_EPI_ADD_BF16, H, 0};
+      TRY(bk_gemv_launch(g));
+    } else {
+      memset(&g, 0, sizeof(g));
+      g.K = H; g.B = B; g.prologue = BK_PRO_RMSNORM; g.x = m.x[cur]; g.norm_w = L.in_ln; g.eps = c.eps;
+      g.n_segs = 3;
+      g.segs[0] = bkGemvSeg{L.q, 0, m.qg, 0, m.QG, BK_EPI_BF16, m.QG, 0};
+      g.segs[1] = bkGemvSeg{L.k, 0, m.kbuf, 0, m.KVD, BK_EPI_BF16, m.KVD, 0};
+      g.segs[2] = bkGemvSeg{L.v, 0, m.vbuf, 0, m.KVD, BK_EPI_BF16, m.KVD, 0};
+      TRY(bk_gemv_launch(g));
+      bkAttnArgs aa;
+      memset(&aa, 0, sizeof(aa));
+      aa.qg = m.qg; aa.k = m.kbuf; aa.v = m.vbuf; aa.q_norm_w = L.q_norm; aa.k_norm_w = L.k_norm;
+      aa.cos_t = m.cos_t; aa.sin_t = m.sin_t; aa.k_cache = L.kc; aa.v_cache = L.vc; aa.pos = m.pos;
+      aa.out = m.attn_out; aa.scratch = m.attn_scratch;
+      aa.B = B; aa.Hq = m.Hq; aa.Hkv = m.Hkv; aa.HD = c.head_dim; aa.rot_half = c.rot_dim / 2; aa.max_len = c.max_len;
+      aa.split_len = m.split_len; aa.max_pos = c.max_len - 1; aa.scale = 1.0f / sqrtf((float)c.head_dim);
+      aa.fused_norm_rope = 1;
+      TRY(bkAttnDecode(&aa));
+      memset(&g, 0, sizeof(g));
+      g.K = m.Hq * c.head_dim; g.B = B; g.prologue = BK_PRO_BF16; g.x = m.attn_out; g.n_segs = 1;
+      g.segs[0] = bkGemvSeg{L.o, 0, m.h1, m.x[cur], H, BK_EPI_ADD_BF16, H, 0};
+      TRY(bk_gemv_launch(g));
+    }
+    memset(&g, 0, sizeof(g));
+    g.K = H; g.B = B; g.prologue = BK_PRO_RMSNORM; g.x = m.h1; g.norm_w = L.post_ln; g.eps = c.eps; g.n_segs = 1;
+    g.segs[0] = bkGemvSeg{L.gate, L.up, m.act, 0, m.inter, BK_EPI_SWIGLU, m.inter, 0};
+    TRY(bk_gemv_launch(g));
+    memset(&g, 0, sizeof(g));
+    g.K = m.inter; g.B = B; g.prologue = BK_PRO_BF16; g.x = m.act; g.n_segs = 1;
+    g.segs[0] = bkGemvSeg{L.down, 0, m.x[cur ^ 1], m.h1, H, BK_EPI_ADD_BF16, H, 0};
+    TRY(bk_gemv_launch(g));
+    cur ^= 1;
+  }
+  bkGemvArgs g;
+  memset(&g, 0, sizeof(g));
+  g.K = H; g.B = B; g.prologue = BK_PRO_RMSNORM; g.x = m.x[cur]; g.norm_w = m.final_norm; g.eps = c.eps; g.n_segs = 1;
+  g.segs[0] = bkGemvSeg{m.embed, 0, m.logits, 0, m.vocab_local, BK_EPI_F32, m.vocab_local, 0};
+  TRY(bk_gemv_launch(g));
+  TRY(bk_argmax_launch(m.logits, m.vocab_local, B, m.ids, m.val, m.argmax_scratch, m.pos, m.hist, B, c.max_len));
+  return BK_OK;
+}
+
+int32_t capture(Model& m, int parity) {
+  BkContext& c = bk_ctx();
+  cudaGraph_t g = nullptr;
+  BK_CUDA(cudaStreamBeginCapture(c.stream, cudaStreamCaptureModeThreadLocal));
+  c.capturing = true;
+  c.captured = 0;
+  int32_t rc = enqueue_step(m, parity);
+  c.capturing = false;
+  cudaError_t e = cudaStreamEndCapture(c.stream, &g);
+  if (rc) {
+    if (g) cudaGraphDestroy(g);
+    return rc;
+  }
+  if (e != cudaSuccess) return bk_fail((int32_t)e, "bkModelFinalize: graph capture -> %s", cudaGetErrorString(e));
+  m.graph_kernels = c.captured;
+  e = cudaGraphInstantiate(&m.graph[parity], g, 0);
+  cudaGraphDestroy(g);
+  if (e != cudaSuccess) return bk_fail((int32_t)e, "bkModelFinalize: graph instantiate -> %s", cudaGetErrorString(e));
+  return BK_OK;
+}
+
+int32_t reset_state(Model& m) {
+  cudaStream_t st = bk_ctx().stream;
+  const bkModelConfig& c = m.cfg;
+  for (auto& L : m.layers) {
+    if (!L.full) {
+      BK_CUDA(cudaMemsetAsync(bk_ptr<void>(L.conv_state[0]), 0, (size_t)m.B * 3 * m.Cw * 2, st));
+      BK_CUDA(cudaMemsetAsync(bk_ptr<void>(L.conv_state[1]), 0, (size_t)m.B * 3 * m.Cw * 2, st));
+      BK_CUDA(cudaMemsetAsync(bk_ptr<void>(L.S), 0, (size_t)m.B * m.Hv * 128 * 128 * 4, st));
+    } else {
+      size_t kv = (size_t)m.B * m.Hkv * c.max_len * c.head_dim * 2;
+      BK_CUDA(cudaMemsetAsync(bk_ptr<void>(L.kc), 0, kv, st));
+      BK_CUDA(cudaMemsetAsync(bk_ptr<void>(L.vc), 0, kv, st));
+    }
+  }
+  BK_CUDA(cudaMemsetAsync(bk_ptr<void>(m.pos), 0, (size_t)m.B * 4, st));
+  BK_CUDA(cudaMemsetAsync(bk_ptr<void>(m.ids), 0, (size_t)m.B * 4, st));
+  BK_CUDA(cudaMemsetAsync(bk_ptr<void>(m.hist), 0, (size_t)c.max_len * m.B * 4, st));
+  m.steps = 0;
+  return BK_OK;
+}
+
+Model* as_model(uint64_t h) { return reinterpret_cast<Model*>(static_cast<uintptr_t>(h)); }
+
+}  // namespace
+
+extern "C" {
+
+int32_t bkModelCreate(const bkModelConfig* cfg, uint64_t* out_model) {
+  BK_REQUIRE_INIT();
+  BK_ARG(cfg && out_model, "bkModelCreate: null argument");
+  bkModelConfig c = *cfg;
+  BK_ARG(c.hidden > 0 && c.hidden % 256 == 0, "bkModelCreate: hidden=%d must be a positive multiple of 256", c.hidden);
+  BK_ARG(c.n_layers > 0 && c.full_attn_interval > 0, "bkModelCreate: bad layer counts");
+  BK_ARG(c.intermediate > 0 && c.intermediate % 256 == 0, "bkModelCreate: intermediate=%d must be a multiple of 256", c.intermediate);
+  BK_ARG(c.gdn_k_heads > 0 && c.gdn_v_heads % c.gdn_k_heads == 0, "bkModelCreate: bad GDN head counts");
+  BK_ARG(c.attn_q_heads > 0 && c.attn_kv_heads > 0 && c.attn_q_heads % c.attn_kv_heads == 0 &&
+             c.attn_q_heads / c.attn_kv_heads <= 8, "bkModelCreate: bad attention head counts");
+  BK_ARG(c.head_dim == 256, "bkModelCreate: head_dim=%d unsupported (256)", c.head_dim);
+  BK_ARG(c.rot_dim > 0 && c.rot_dim % 2 == 0 && c.rot_dim <= c.head_dim, "bkModelCreate: rot_dim=%d", c.rot_dim);
+  BK_ARG(c.batch >= 1 && c.batch <= 8, "bkModelCreate: batch=%d outside 1..8", c.batch);
+  BK_ARG(c.max_len >= 1, "bkModelCreate: max_len=%d", c.max_len);
+  BK_ARG(c.vocab > 0, "bkModelCreate: vocab=%d", c.vocab);
+  BK_ARG(c.tp_size == 1 && c.tp_rank == 0, "bkModelCreate: tensor parallelism is configured through bkCommInit (tp_size must be 1 here)");
+  Model* m = new Model();
+  m->cfg = c;
+  m->B = c.batch;
+  *out_model = (uint64_t)(uintptr_t)m;
+  return BK_OK;
+}
+
+int32_t bkModelSetTensor(uint64_t model, const char* name, uint64_t dev_ptr, uint64_t bytes) {
+  BK_REQUIRE_INIT();
+  BK_ARG(model && name && dev_ptr, "bkModelSetTensor: null argument");
+  Model* m = as_model(model);
+  BK_ARG(!m->finalized, "bkModelSetTensor: model is already finalized");
+  m->tensors[std::string(name)] = Tensor{dev_ptr, bytes};
+  return BK_OK;
+}
+
+int32_t bkModelFinalize(uint64_t model) {
+  BK_REQUIRE_INIT();
+  BK_ARG(model, "bkModelFinalize: null model");
+  Model& m = *as_model(model);
+  if (m.finalized) return BK_OK;
+  const bkModelConfig& c = m.cfg;
+  const int H = c.hidden, B = m.B;
+  m.Hk = c.gdn_k_heads; m.Hv = c.gdn_v_heads; m.Hq = c.attn_q_heads; m.Hkv = c.attn_kv_heads;
+  m.Cw = 2 * m.Hk * 128 + m.Hv * 128; m.ZD = m.Hv * 128; m.QG = m.Hq * 2 * c.head_dim; m.KVD = m.Hkv * c.head_dim;
+  m.inter = c.intermediate; m.vocab_local = c.vocab;
+  TRY(need(m, "embed.weight", q4k_bytes(c.vocab, H), &m.embed));
+  TRY(need(m, "final.norm.weight", (uint64_t)H * 2, &m.final_norm));
+  m.layers.resize(c.n_layers);
+  for (int li = 0; li < c.n_layers; li++) {
+    LayerW& L = m.layers[li];
+    L.full = (li % c.full_attn_interval) == c.full_attn_interval - 1;
+    std::string p = "model.layers." + std::to_string(li) + ".";
+    TRY(need(m, p + "input_layernorm.weight", (uint64_t)H * 2, &L.in_ln));
+    TRY(need(m, p + "post_attention_layernorm.weight", (uint64_t)H * 2, &L.post_ln));
+    TRY(need(m, p + "mlp.gate_proj.weight", q4k_bytes(m.inter, H), &L.gate));
+    TRY(need(m, p + "mlp.up_proj.weight", q4k_bytes(m.inter, H), &L.up));
+    TRY(need(m, p + "mlp.down_proj.weight", q4k_bytes(H, m.inter), &L.down));
+    if (!L.full) {
+      std::string q = p + "linear_attn.";
+      TRY(need(m, q + "in_proj_qkv.weight", q4k_bytes(m.Cw, H), &L.qkv));
+      TRY(need(m, q + "in_proj_z.weight", q4k_bytes(m.ZD, H), &L.z));
+      TRY(need(m, q + "in_proj_a.weight", q4k_bytes(m.Hv, H), &L.a));
+      TRY(need(m, q + "in_proj_b.weight", q4k_bytes(m.Hv, H), &L.b));
+      TRY(need(m, q + "conv1d.weight", (uint64_t)m.Cw * 4 * 2, &L.conv_w));
+      TRY(need(m, q + "A_log", (uint64_t)m.Hv * 4, &L.A_log));
+      TRY(need(m, q + "dt_bias", (uint64_t)m.Hv * 2, &L.dt_bias));
+      TRY(need(m, q + "norm.weight", 128 * 4, &L.gnorm));
+      TRY(need(m, q + "out_proj.weight", q4k_bytes(H, m.ZD), &L.out_proj));
+      TRY(dev_alloc(m, (size_t)B * 3 * m.Cw * 2, &L.conv_state[0]));
+      TRY(dev_alloc(m, (size_t)B * 3 * m.Cw * 2, &L.conv_state[1]));
+      TRY(dev_alloc(m, (size_t)B * m.Hv * 128 * 128 * 4, &L.S));
+    } else {
+      std::string q = p + "self_attn.";
+      TRY(need(m, q + "q_proj.weight", q4k_bytes(m.QG, H), &L.q));
+      TRY(need(m, q + "k_proj.weight", q4k_bytes(m.KVD, H), &L.k));
+      TRY(need(m, q + "v_proj.weight", q4k_bytes(m.KVD, H), &L.v));
+      TRY(need(m, q + "q_norm.weight", (uint64_t)c.head_dim * 2, &L.q_norm));
+      TRY(need(m, q + "k_norm.weight", (uint64_t)c.head_dim * 2, &L.k_norm));
+      TRY(need(m, q + "o_proj.weight", q4k_bytes(H, (uint64_t)m.Hq * c.head_dim), &L.o));
+      size_t kv = (size_t)B * m.Hkv * c.max_len * c.head_dim * 2;
+      TRY(dev_alloc(m, kv, &L.kc));
+      TRY(dev_alloc(m, kv, &L.vc));
+    }
+  }
+  int attn_w = m.Hq * c.head_dim;
+  TRY(dev_alloc(m, (size_t)B * H * 2, &m.x[0]));
+  TRY(dev_alloc(m, (size_t)B * H * 2, &m.x[1]));
+  TRY(dev_alloc(m, (size_t)B * H * 2, &m.h1));
+  TRY(dev_alloc(m, (size_t)B * m.Cw * 2, &m.qkv));
+  TRY(dev_alloc(m, (size_t)B * m.ZD * 2, &m.z));
+  TRY(dev_alloc(m, (size_t)B * m.Hv * 4, &m.a));
+  TRY(dev_alloc(m, (size_t)B * m.Hv * 4, &m.b));
+  TRY(dev_alloc(m, (size_t)B * (m.ZD > attn_w ? m.ZD : attn_w) * 2, &m.attn_out));
+  TRY(dev_alloc(m, (size_t)B * m.QG * 2, &m.qg));
+  TRY(dev_alloc(m, (size_t)B * m.KVD * 2, &m.kbuf));
+  TRY(dev_alloc(m, (size_t)B * m.KVD * 2, &m.vbuf));
+  TRY(dev_alloc(m, (size_t)B * m.inter * 2, &m.act));
+  TRY(dev_alloc(m, (size_t)B * m.vocab_local * 4, &m.logits));
+  TRY(dev_alloc(m, (size_t)B * 4, &m.ids));
+  TRY(dev_alloc(m, (size_t)B * 4, &m.val));
+  TRY(dev_alloc(m, (size_t)B * 4, &m.pos));
+  TRY(dev_alloc(m, (size_t)c.max_len * B * 4, &m.hist));
+  TRY(dev_alloc(m, bkArgmaxScratchBytes(B), &m.argmax_scratch));
+  int32_t sl = 0;
+  TRY(bkAttnPlan(c.max_len, B, m.Hkv, &sl, nullptr));
+  m.split_len = sl;
+  TRY(dev_alloc(m, bkAttnScratchBytes(B, m.Hq, c.head_dim, c.max_len, sl), &m.attn_scratch, false));
+  {
+    int half = c.rot_dim / 2;
+    std::vector<float> ct((size_t)c.max_len * half), st((size_t)c.max_len * half);
+    TRY(bkRopeTables(c.max_len, c.rot_dim, c.rope_theta, ct.data(), st.data()));
+    TRY(dev_alloc(m, ct.size() * 4, &m.cos_t, false));
+    TRY(dev_alloc(m, st.size() * 4, &m.sin_t, false));
+    BK_CUDA(cudaMemcpyAsync(bk_ptr<void>(m.cos_t), ct.data(), ct.size() * 4, cudaMemcpyHostToDevice, bk_ctx().stream));
+    BK_CUDA(cudaMemcpyAsync(bk_ptr<void>(m.sin_t), st.data(), st.size() * 4, cudaMemcpyHostToDevice, bk_ctx().stream));
+    BK_CUDA(cudaStreamSynchronize(bk_ctx().stream));
+  }
+  BK_CUDA(cudaHostAlloc((void**)&m.pin_ids, (size_t)B * 4 * 3, cudaHostAllocDefault));
+  // one eager step sets the kernels' shared-memory attributes and validates every pointer, then the
+  // state is cleared and the two parity graphs are captured
+  TRY(enqueue_step(m, 0));
+  BK_CUDA(cudaStreamSynchronize(bk_ctx().stream));
+  TRY(reset_state(m));
+  TRY(capture(m, 0));
+  TRY(capture(m, 1));
+  BK_CUDA(cudaStreamSynchronize(bk_ctx().stream));
+  m.finalized = true;
+  return BK_OK;
+}
+
+int32_t bkModelReset(uint64_t model) {
+  BK_REQUIRE_INIT();
+  BK_ARG(model, "bkModelReset: null model");
+  Model& m = *as_model(model);
+  BK_ARG(m.finalized, "bkModelReset: model is not finalized");
+  return reset_state(m);
+}
+
+int32_t bkModelInfo(uint64_t model, int32_t* split_len, int32_t* attn_warps, int32_t* kernels_per_step, int64_t* steps) {
+  BK_REQUIRE_INIT();
+  BK_ARG(model, "bkModelInfo: null model");
+  Model& m = *as_model(model);
+  if (split_len) *split_len = m.split_len;
+  if (attn_warps) *attn_warps = 8;
+  if (kernels_per_step) *kernels_per_step = (int32_t)m.graph_kernels;
+  if (steps) *steps = m.steps;
+  return BK_OK;
+}
+
+static int32_t launch_step(Model& m) {
+  BkContext& c = bk_ctx();
+  BK_ARG(m.steps < m.cfg.max_len, "bkDecodeStep: position %lld reached max_len=%d", m.steps, m.cfg.max_len);
+  BK_CUDA(cudaGraphLaunch(m.graph[m.steps & 1], c.stream));
+  c.launches += m.graph_kernels;
+  m.steps++;
+  return BK_OK;
+}
+
+int32_t bkDecodeStep(uint64_t model, const int32_t* tokens, int32_t* out_ids, float* out_vals) {
+  BK_REQUIRE_INIT();
+  BK_ARG(model, "bkDecodeStep: null model");
+  Model& m = *as_model(model);
+  BK_ARG(m.finalized, "bkDecodeStep: model is not finalized");
+  cudaStream_t st = bk_ctx().stream;
+  const int B = m.B;
+  if (tokens) {
+    for (int b = 0; b < B; b++) {
+      BK_ARG(tokens[b] >= 0 && tokens[b] < m.cfg.vocab, "bkDecodeStep: token %d outside the vocabulary", tokens[b]);
+      m.pin_ids[b] = tokens[b];
+    }
+    BK_CUDA(cudaMemcpyAsync(bk_ptr<void>(m.ids), m.pin_ids, (size_t)B * 4, cudaMemcpyHostToDevice, st));
+  }
+  TRY(launch_step(m));
+  if (out_ids || out_vals) {
+    BK_CUDA(cudaMemcpyAsync(m.pin_ids + B, bk_ptr<void>(m.ids), (size_t)B * 4, cudaMemcpyDeviceToHost, st));
+    if (out_vals) BK_CUDA(cudaMemcpyAsync(m.pin_ids + 2 * B, bk_ptr<void>(m.val), (size_t)B * 4, cudaMemcpyDeviceToHost, st));
+    BK_CUDA(cudaStreamSynchronize(st));
+    if (out_ids) memcpy(out_ids, m.pin_ids + B, (size_t)B * 4);
+    if (out_vals) memcpy(out_vals, m.pin_ids + 2 * B, (size_t)B * 4);
+  }
+  return BK_OK;
+}
+
+int32_t bkDecodeRun(uint64_t model, int32_t n_steps) {
+  BK_REQUIRE_INIT();
+  BK_ARG(model && n_steps >= 0, "bkDecodeRun: bad arguments");
+  Model& m = *as_model(model);
+  BK_ARG(m.finalized, "bkDecodeRun: model is not finalized");
+  for (int i = 0; i < n_steps; i++) TRY(launch_step(m));
+  return BK_OK;
+}
+
+int32_t bkModelTokens(uint64_t model, int32_t first_step, int32_t n_steps, int32_t* out) {
+  BK_REQUIRE_INIT();
+  BK_ARG(model && out, "bkModelTokens: null argument");
+  Model& m = *as_model(model);
+  BK_ARG(first_step >= 0 && n_steps >= 0 && first_step + n_steps <= m.cfg.max_len, "bkModelTokens: range outside max_len");
+  BK_CUDA(cudaMemcpyAsync(out, bk_ptr<int32_t>(m.hist) + (size_t)first_step * m.B, (size_t)n_steps * m.B * 4,
+                          cudaMemcpyDeviceToHost, bk_ctx().stream));
+  BK_CUDA(cudaStreamSynchronize(bk_ctx().stream));
+  return BK_OK;
+}
+
+int32_t bkModelBuffer(uint64_t model, const char* name, uint64_t* out_ptr) {
+  BK_REQUIRE_INIT();
+  BK_ARG(model && name && out_ptr, "bkModelBuffer: null argument");
+  Model& m = *as_model(model);
+  std::string n(name);
+  if (n == "logits") *out_ptr = m.logits;
+  else if (n == "ids") *out_ptr = m.ids;
+  else if (n == "pos") *out_ptr = m.pos;
+  else if (n == "x0") *out_ptr = m.x[0];
+  else if (n == "x1") *out_ptr = m.x[1];
+  else return bk_fail(BK_ERR_ARG, "bkModelBuffer: unknown buffer '%s'", name);
+  return BK_OK;
+}
+
+int32_t bkModelDestroy(uint64_t model) {
+  BK_REQUIRE_INIT();
+  if (!model) return BK_OK;
+  Model* m = as_model(model);
+  cudaStreamSynchronize(bk_ctx().stream);
+  for (int i = 0; i < 2; i++)
+    if (m->graph[i]) cudaGraphExecDestroy(m->graph[i]);
+  for (uint64_t p : m->owned) cudaFree(bk_ptr<void>(p));
+  if (m->pin_ids) cudaFreeHost(m->pin_ids);
+  delete m;
+  return BK_OK;
+}
+
+}  // extern "C"

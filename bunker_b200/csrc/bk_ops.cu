@@ -313,8 +313,11 @@ __device__ __forceinline__ void argmax_merge(float& v, int& i, float ov, int oi)
 
 constexpr int kArgmaxBlocks = 64;
 
+// pos/hist (optional): the finishing block also records the token at hist[pos[b]*hist_ld + b] and advances
+// pos[b], which is how the model-level decode step feeds the next token without a host round trip.
 __global__ void __launch_bounds__(256) argmax_kernel(const float* logits, int V, int32_t* idx, float* val,
-                                                     float* part_v, int32_t* part_i, unsigned int* counter) {
+                                                     float* part_v, int32_t* part_i, unsigned int* counter,
+                                                     int32_t* pos, int32_t* hist, int hist_ld, int hist_rows) {
   __shared__ float sv[8];
   __shared__ int si[8];
   __shared__ bool last;
@@ -361,6 +364,11 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float* logits, int V,
     idx[b] = i;
     val[b] = v;
     counter[b] = 0;
+    if (pos) {
+      int pcur = pos[b];
+      if (hist && pcur < hist_rows) hist[(size_t)pcur * hist_ld + b] = i;
+      pos[b] = pcur + 1;
+    }
   }
 }
 
@@ -480,6 +488,13 @@ int32_t bkHeadNormRope(uint64_t in, int32_t in_stride, uint64_t w, uint64_t cos_
 uint64_t bkArgmaxScratchBytes(int32_t B) { return (uint64_t)(B > 0 ? B : 1) * (kArgmaxBlocks * 8 + 4); }
 
 int32_t bkArgmax(uint64_t logits, int32_t V, int32_t B, uint64_t idx, uint64_t val, uint64_t scratch) {
+  return bk_argmax_launch(logits, V, B, idx, val, scratch, 0, 0, 0, 0);
+}
+
+}  // extern "C"
+
+int32_t bk_argmax_launch(uint64_t logits, int32_t V, int32_t B, uint64_t idx, uint64_t val, uint64_t scratch,
+                         uint64_t pos, uint64_t hist, int32_t hist_ld, int32_t hist_rows) {
   BK_REQUIRE_INIT();
   BK_ARG(V > 0 && B > 0 && logits && idx && val && scratch, "bkArgmax: bad arguments");
   // scratch: [B][64] f32, [B][64] i32, [B] counters (zero before first use; the kernel re-zeroes them)
@@ -489,9 +504,8 @@ int32_t bkArgmax(uint64_t logits, int32_t V, int32_t B, uint64_t idx, uint64_t v
   int blocks = (V + 2047) / 2048;
   if (blocks > kArgmaxBlocks) blocks = kArgmaxBlocks;
   argmax_kernel<<<dim3(blocks, B), 256, 0, bk_ctx().stream>>>(bk_ptr<float>(logits), V, bk_ptr<int32_t>(idx),
-                                                             bk_ptr<float>(val), pv, pi, cnt);
+                                                             bk_ptr<float>(val), pv, pi, cnt, bk_ptr<int32_t>(pos),
+                                                             bk_ptr<int32_t>(hist), hist_ld, hist_rows);
   BK_CHECK_LAUNCH();
   return BK_OK;
 }
-
-}  // extern "C"

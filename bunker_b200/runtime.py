@@ -63,6 +63,14 @@ class bkAttnArgs(C.Structure):
                [("scale", C.c_float), ("fused_norm_rope", C.c_int32), ("gate", C.c_uint64)]
 
 
+class bkModelConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("hidden", "n_layers", "full_attn_interval", "vocab", "gdn_k_heads",
+                                          "gdn_v_heads", "attn_q_heads", "attn_kv_heads", "head_dim", "rot_dim",
+                                          "intermediate", "max_len", "batch", "tp_rank", "tp_size")] + \
+               [("eps", C.c_float), ("rope_theta", C.c_double)]
+
+
+
 # name -> (restype, argtypes); the list doubles as the export check used by the CPU tests
 _U64, _I32, _F32, _VP = C.c_uint64, C.c_int32, C.c_float, C.c_void_p
 _PU64 = C.POINTER(C.c_uint64)
@@ -108,6 +116,21 @@ SIGNATURES = {
     "bkArgmaxScratchBytes": (_U64, [_I32]),
     "bkLaunch": (_I32, [_I32, _PU64, _I32]),
 }
+
+_MODEL_SIGS = {
+    "bkModelCreate": (C.c_int32, [C.POINTER(bkModelConfig), C.POINTER(C.c_uint64)]),
+    "bkModelSetTensor": (C.c_int32, [C.c_uint64, C.c_char_p, C.c_uint64, C.c_uint64]),
+    "bkModelFinalize": (C.c_int32, [C.c_uint64]),
+    "bkModelReset": (C.c_int32, [C.c_uint64]),
+    "bkDecodeStep": (C.c_int32, [C.c_uint64, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
+    "bkDecodeRun": (C.c_int32, [C.c_uint64, C.c_int32]),
+    "bkModelTokens": (C.c_int32, [C.c_uint64, C.c_int32, C.c_int32, C.POINTER(C.c_int32)]),
+    "bkModelInfo": (C.c_int32, [C.c_uint64, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32),
+                                C.POINTER(C.c_int64)]),
+    "bkModelBuffer": (C.c_int32, [C.c_uint64, C.c_char_p, C.POINTER(C.c_uint64)]),
+    "bkModelDestroy": (C.c_int32, [C.c_uint64]),
+}
+SIGNATURES.update(_MODEL_SIGS)
 
 _lib = None
 

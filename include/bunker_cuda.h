@@ -189,6 +189,53 @@ BK_API uint64_t bkAttnScratchBytes(int32_t B, int32_t Hq, int32_t HD, int32_t ma
 BK_API int32_t bkArgmax(uint64_t logits, int32_t V, int32_t B, uint64_t idx, uint64_t val, uint64_t scratch);
 BK_API uint64_t bkArgmaxScratchBytes(int32_t B);
 
+/* ---- whole decode step: replaces buildModelGraph + compileStep + runGraphDecode
+ *      (src/model.ts:46-204, src/runner.ts:94-162) --------------------------------
+ * One call per token; the CUDA graph lives inside the library because replaying a graph
+ * through bun:ffi crashed the reference (LOG.md:710-738).  Dims follow src/model.ts:14-18. */
+typedef struct bkModelConfig {
+  int32_t hidden;             /* H */
+  int32_t n_layers;           /* NL */
+  int32_t full_attn_interval; /* FAI: layer % FAI == FAI-1 is gated attention (src/model.ts:61) */
+  int32_t vocab;              /* VOCAB; embedding and lm_head are tied (src/model.ts:196) */
+  int32_t gdn_k_heads;        /* LKH, head dim 128 */
+  int32_t gdn_v_heads;        /* LVH, head dim 128 */
+  int32_t attn_q_heads;       /* NH */
+  int32_t attn_kv_heads;      /* NKV */
+  int32_t head_dim;           /* HD = 256 */
+  int32_t rot_dim;            /* ROT_DIM = 64 */
+  int32_t intermediate;       /* INTER */
+  int32_t max_len;            /* KV cache rows per sequence (the reference fixes 128) */
+  int32_t batch;              /* sequences decoded in lockstep, 1..8 */
+  int32_t tp_rank, tp_size;   /* tensor-parallel rank / world (1 = single GPU) */
+  float eps;                  /* EPS = 1e-6 */
+  double rope_theta;          /* 1e7 (prototypes/decode.ts:868) */
+} bkModelConfig;
+
+BK_API int32_t bkModelCreate(const bkModelConfig* cfg, uint64_t* out_model);
+/* Register a weight that already sits in device memory (the caller uploads one slab and addresses
+ * it by offset, prototypes/decode.ts:64-75).  Names are the reference's graph names
+ * (src/model.ts:72-196): "embed.weight", "final.norm.weight", "model.layers.N.input_layernorm.weight",
+ * "...linear_attn.in_proj_qkv.weight" and so on.  Linear weights are Q4_K rows. */
+BK_API int32_t bkModelSetTensor(uint64_t model, const char* name, uint64_t dev_ptr, uint64_t bytes);
+/* Checks the tensor set, allocates state and activations, captures the step graphs. */
+BK_API int32_t bkModelFinalize(uint64_t model);
+/* Zero the recurrent state, conv state, KV cache and position. */
+BK_API int32_t bkModelReset(uint64_t model);
+/* One decode step (runGraphDecode's loop body, src/runner.ts:133-160).  tokens: B host ints, or NULL to
+ * feed back the previous step's argmax on the device.  out_ids / out_vals: B host values each, or NULL to
+ * skip the read-back (and its synchronisation). */
+BK_API int32_t bkDecodeStep(uint64_t model, const int32_t* tokens, int32_t* out_ids, float* out_vals);
+/* n_steps greedy steps with device-side token feedback and no host traffic. */
+BK_API int32_t bkDecodeRun(uint64_t model, int32_t n_steps);
+/* Tokens produced by steps [first_step, first_step+n_steps): out[n_steps][B] host ints. */
+BK_API int32_t bkModelTokens(uint64_t model, int32_t first_step, int32_t n_steps, int32_t* out);
+BK_API int32_t bkModelInfo(uint64_t model, int32_t* split_len, int32_t* attn_warps, int32_t* kernels_per_step,
+                           int64_t* steps);
+/* Device address of an internal buffer: "logits" f32 [B][vocab], "ids", "pos", "x0", "x1". */
+BK_API int32_t bkModelBuffer(uint64_t model, const char* name, uint64_t* out_ptr);
+BK_API int32_t bkModelDestroy(uint64_t model);
+
 /* cuLaunch-shaped entry (src/ttir.ts:321-348): op id + 8-byte argument slots.
  * Slot lists per op are documented in INTEGRATION.md. */
 BK_API int32_t bkLaunch(int32_t op, const uint64_t* slots, int32_t nslots);
