@@ -1,0 +1,279 @@
+#!/usr/bin/env python
+"""Decode throughput of the hybrid Q4_K model (BASELINE configs[3]) on N B200s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl ours|reference]
+
+One "step" is one decode step: one token for each of the B sequences through all 24 layers and the
+lm_head.  Weights are random-init Q4_K (synthetic), the prompt is 32 random token ids.  The step's
+inputs (1.1 GB of weights) exceed L2, so no flush is needed between timed steps.
+
+`value`  : tokens/s over K graph-replayed steps with the token fed back on the device (inputs resident).
+`e2e`    : tokens/s over K calls of the per-token API with HOST buffers: token ids copied host->device,
+           (id, logit) copied device->host and synchronised every step (the reference's loop, src/runner.ts:133-160).
+`roofline`: the dominant kernel (gemv_q4k_kernel) timed with CUDA-event pairs around each launch of
+           one eagerly launched step; algorithmic bytes = Q4_K weight bytes + activations of those launches.
+`cpu_baseline` / `--impl reference`: the CPU oracle (C restatement of the reference's op math, OpenMP) on the
+           host cores.  The reference is TypeScript for bun with Triton-generated GPU kernels; neither bun
+           nor its shim exist here, so kind = "port".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PROMPT_LEN = 32
+METRIC = "q4k_hybrid_decode_tok_s"
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Polls NVML for SM clock and throttle reasons while the timed region runs (read-only queries)."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:  # noqa: BLE001
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:  # noqa: BLE001
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self.nv:
+            self._thr = threading.Thread(target=self._loop, daemon=True)
+            self._thr.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thr:
+            self._thr.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def make_config(steps: int, warmup: int):
+    from bunker_b200 import model as M
+    need = PROMPT_LEN + warmup + steps + 8
+    return M.CONFIG_HYBRID_24L.with_(max_len=(max(need, 320) + 63) // 64 * 64)
+
+
+def cpu_tokens_per_s(cfg, weights, batch: int, steps: int, warmup: int, budget_s: float = 150.0):
+    """Oracle decode on the host cores.  Runs the full model when K steps fit the budget, else a 1/6 sample
+    (4 of 24 layers in the same 3:1 layer mix and 1/6 of the lm_head rows) with the rate scaled by 1/6."""
+    from oracle.model_oracle import OracleModel
+    om = OracleModel(cfg, weights, batch=batch, split_len=64)
+    tok = np.zeros((batch,), np.int32)
+    t0 = time.perf_counter()
+    om.step(tok)
+    t_full = time.perf_counter() - t0
+    scale, sample = 1.0, "full model, every step one whole token"
+    if t_full * (steps + warmup) > budget_s:
+        from bunker_b200 import model as M
+        small = cfg.with_(n_layers=4, vocab=(cfg.vocab // 6 + 255) // 256 * 256)
+        names = {n for n, _, _ in M.tensor_specs(small)}
+        w2 = {n: (weights[n][: small.vocab] if n == "embed.weight" else weights[n]) for n in names}
+        om = OracleModel(small, w2, batch=batch, split_len=64)
+        scale = M.weight_bytes(small) / M.weight_bytes(cfg)
+        sample = (f"per step 4 of {cfg.n_layers} layers (3 GDN + 1 attention) and {small.vocab} of {cfg.vocab} lm_head rows "
+                  f"= {scale:.4f} of the weight bytes; rate scaled by that factor")
+    for _ in range(warmup):
+        om.step(tok)
+        if om.pos >= om.cfg.max_len - 1:
+            om.reset()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        om.step(tok)
+        if om.pos >= om.cfg.max_len - 1:
+            om.reset()
+    dt = time.perf_counter() - t0
+    return steps * batch / dt * scale, dt / steps * 1e3, sample
+
+
+def run_reference(args):
+    """CPU arm: the oracle port on all host cores, same config, metric and unit."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from bunker_b200 import model as M
+    cfg = make_config(args.steps, args.warmup)
+    weights = M.synth_weights(cfg)
+    val, ms, sample = cpu_tokens_per_s(cfg, weights, args.batch, args.steps, args.warmup)
+    cores = os.cpu_count() or 1
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int8xint4->int32, f32 accumulate", "data": "synthetic",
+        "config": {"workload": f"configs[3] hybrid 24-layer Q4_K decode, batch {args.batch}, CPU oracle",
+                   "batch": args.batch, "inputs": "weights larger than L2"},
+        "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "reference is TypeScript for bun + Triton-generated kernels; bun is absent, so its op math runs as the C port",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    from bunker_b200 import model as M
+    from bunker_b200 import runtime as R
+
+    if args.gpus != 1:
+        raise SystemExit("tensor-parallel bench path not built yet")
+    K, W, B = args.steps, args.warmup, args.batch
+    cfg = make_config(K, W)
+    weights = M.synth_weights(cfg)
+    R.cu(0)
+    gm = M.DecodeModel(cfg, weights, batch=B)
+    info = gm.info()
+    prompt = np.random.default_rng(0xB0B0 + 3000).integers(0, cfg.vocab, (PROMPT_LEN, B)).astype(np.int32)
+    wbytes = M.weight_bytes(cfg)
+    hbm_peak, peak_src = load_peaks()
+
+    # ---- resident leg: prompt, W warm-up steps, K timed graph replays with device-side token feedback ----
+    for t in range(PROMPT_LEN):
+        gm.step(prompt[t], read=False)
+    gm.run(W)
+    assert R.cuSync() == 0
+    sampler = ClockSampler(0)
+    e0, e1 = R.Event(), R.Event()
+    l0 = R.launch_count()
+    with sampler:
+        e0.record()
+        gm.run(K)
+        e1.record()
+        e1.synchronize()
+    ms = e0.elapsed_ms(e1)
+    launches = R.launch_count() - l0
+    value = K * B / (ms * 1e-3)
+    tokens_resident = gm.tokens(PROMPT_LEN + W, K)
+
+    # ---- per-op profile of one eager step (events around every launch) ----
+    prof = gm.step_profiled()
+    gemv_ms = sum(v[0] for k, v in prof.items() if k.startswith("gemv"))
+    gemv_calls = sum(v[1] for k, v in prof.items() if k.startswith("gemv"))
+    H = cfg.hidden
+    act_bytes = 0
+    for li in range(cfg.n_layers):  # bf16 activations read by the prologues and written by the epilogues, per launch
+        if cfg.is_full(li):
+            act_bytes += B * (2 * H + 2 * (cfg.qgate_dim + 2 * cfg.kv_dim)) + B * (2 * cfg.attn_q_heads * cfg.head_dim + 4 * H)
+        else:
+            act_bytes += B * (2 * H + 2 * (cfg.conv_width + cfg.z_dim) + 8 * cfg.gdn_v_heads) + B * (2 * cfg.z_dim + 4 * H)
+        act_bytes += B * (2 * H + 2 * cfg.intermediate) + B * (2 * cfg.intermediate + 4 * H)
+    act_bytes += B * (2 * H + 4 * cfg.vocab)
+    gemv_bytes = wbytes + act_bytes
+    achieved = gemv_bytes / (gemv_ms * 1e-3) / 1e9
+
+    # ---- end-to-end leg: host token in, host (id, logit) out, every step ----
+    gm.reset()
+    ids = None
+    for t in range(PROMPT_LEN):
+        ids, _ = gm.step(prompt[t])
+    for _ in range(W):
+        ids, _ = gm.step(ids)
+    e2, e3 = R.Event(), R.Event()
+    e2.record()
+    t0 = time.perf_counter()
+    toks = []
+    for _ in range(K):
+        ids, _ = gm.step(ids)
+        toks.append(ids)
+    e3.record()
+    e3.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    e2e_ms = max(e2.elapsed_ms(e3), wall_ms)
+    same_stream = bool(np.array_equal(np.stack(toks), tokens_resident))
+
+    cpu_val, cpu_ms, cpu_sample = cpu_tokens_per_s(cfg, weights, B, steps=6, warmup=1, budget_s=30.0)
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int8xint4->int32, f32 accumulate", "data": "synthetic",
+        "config": {"workload": f"configs[3] hybrid 24-layer Q4_K decode (hidden 2048, vocab 151936), batch {B}, "
+                               f"{PROMPT_LEN}-token random prompt then greedy", "batch": B, "parallelism": "tp1",
+                   "inputs": "weights (1.12 GB/step) larger than L2, no flush", "max_len": cfg.max_len,
+                   "attn_split_len": info["split_len"], "kernels_per_step": info["kernels_per_step"]},
+        "clocks": sampler.summary(),
+        "e2e": {"value": K * B / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 4 * B,
+                "d2h_bytes_per_step": 8 * B, "ms_per_step": e2e_ms / K, "same_tokens_as_resident_leg": same_stream},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "kernel": f"gemv_q4k_kernel<{B}>", "achieved": achieved, "peak": hbm_peak,
+                     "unit": "GB/s", "frac": achieved / hbm_peak, "traffic": None, "peak_source": peak_src,
+                     "launches_per_step": gemv_calls, "avg_launch_us": gemv_ms * 1e3 / gemv_calls,
+                     "algorithmic_bytes_per_step": gemv_bytes},
+        "model_roofline": {"weight_bytes_per_step": wbytes, "achieved_gbs": wbytes / (ms / K * 1e-3) / 1e9,
+                           "frac_of_hbm": wbytes / (ms / K * 1e-3) / 1e9 / hbm_peak,
+                           "roofline_tok_s": hbm_peak * 1e9 / wbytes * B},
+        "per_op_ms": {k: round(v[0], 5) for k, v in prof.items()},
+        "per_op_calls": {k: v[1] for k, v in prof.items()},
+        "cpu_baseline": {"value": cpu_val, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port",
+                         "sample": cpu_sample + f"; {6} timed steps", "ms_per_step": cpu_ms},
+    }
+    print(json.dumps(line), flush=True)
+    gm.destroy()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -88,12 +88,47 @@ inline uint64_t q4k_bytes(uint64_t n, uint64_t k) { return n * (k / 256) * 144; 
     if (_rc) return _rc;     \
   } while (0)
 
+// Per-op CUDA-event pairs for one eagerly launched step, the analogue of the reference's
+// BUNKER_GPU_PROF=1 profiler (src/ttir.ts:352-417).  Classes index the ms/count arrays of
+// bkDecodeStepProfiled.
+enum ProfClass { PC_EMBED = 0, PC_GEMV_PROJ, PC_GDN, PC_ATTN, PC_GEMV_OUT, PC_GEMV_GATEUP, PC_GEMV_DOWN, PC_GEMV_LMHEAD,
+                 PC_ARGMAX, PC_COUNT };
+
+struct Prof {
+  bool on = false;
+  std::vector<cudaEvent_t> ev;
+  std::vector<int> cls;
+};
+Prof g_prof;
+
+struct ProfScope {
+  bool on;
+  explicit ProfScope(int cls) : on(g_prof.on) {
+    if (!on) return;
+    cudaEvent_t a, b;
+    cudaEventCreate(&a);
+    cudaEventCreate(&b);
+    cudaEventRecord(a, bk_ctx().stream);
+    g_prof.ev.push_back(a);
+    g_prof.ev.push_back(b);
+    g_prof.cls.push_back(cls);
+  }
+  ~ProfScope() {
+    if (on) cudaEventRecord(g_prof.ev.back(), bk_ctx().stream);
+  }
+};
+#define PROF(cls, expr)    \
+  do {                     \
+    ProfScope _ps(cls);    \
+    TRY(expr);             \
+  } while (0)
+
 // enqueue one decode step on the library stream; parity selects the conv-state buffer pair
 int32_t enqueue_step(Model& m, int parity) {
   const bkModelConfig& c = m.cfg;
   const int B = m.B, H = c.hidden;
   int cur = 0;
-  TRY(bkEmbedQ4K(m.embed, H, m.ids, B, m.x[0]));
+  PROF(PC_EMBED, bkEmbedQ4K(m.embed, H, m.ids, B, m.x[0]));
   for (int li = 0; li < c.n_layers; li++) {
     LayerW& L = m.layers[li];
     bkGemvArgs g;
@@ -105,7 +140,7 @@ int32_t enqueue_step(Model& m, int parity) {
       g.segs[1] = bkGemvSeg{L.z, 0, m.z, 0, m.ZD, BK_EPI_BF16, m.ZD, 0};
       g.segs[2] = bkGemvSeg{L.a, 0, m.a, 0, m.Hv, BK_EPI_F32, m.Hv, 0};
       g.segs[3] = bkGemvSeg{L.b, 0, m.b, 0, m.Hv, BK_EPI_F32, m.Hv, 0};
-      TRY(bk_gemv_launch(g));
+      PROF(PC_GEMV_PROJ, bk_gemv_launch(g));
       bkGdnArgs ga;
       memset(&ga, 0, sizeof(ga));
       ga.qkv = m.qkv; ga.z = m.z; ga.a = m.a; ga.b = m.b;
@@ -113,11 +148,11 @@ int32_t enqueue_step(Model& m, int parity) {
       ga.A_log = L.A_log; ga.dt_bias = L.dt_bias; ga.norm_w = L.gnorm;
       ga.S_in = L.S; ga.S_new = L.S;  // in place: each thread rewrites exactly the rows it read
       ga.out = m.attn_out; ga.B = B; ga.Hk = m.Hk; ga.Hv = m.Hv; ga.apply_conv = 1;
-      TRY(bkGdnStep(&ga));
+      PROF(PC_GDN, bkGdnStep(&ga));
       memset(&g, 0, sizeof(g));
       g.K = m.ZD; g.B = B; g.prologue = BK_PRO_BF16; g.x = m.attn_out; g.n_segs = 1;
       g.segs[0] = bkGemvSeg{L.out_proj, 0, m.h1, m.x[cur], H, BK_EPI_ADD_BF16, H, 0};
-      TRY(bk_gemv_launch(g));
+      PROF(PC_GEMV_OUT, bk_gemv_launch(g));
     } else {
       memset(&g, 0, sizeof(g));
       g.K = H; g.B = B; g.prologue = BK_PRO_RMSNORM; g.x = m.x[cur]; g.norm_w = L.in_ln; g.eps = c.eps;
@@ -125,7 +160,7 @@ int32_t enqueue_step(Model& m, int parity) {
       g.segs[0] = bkGemvSeg{L.q, 0, m.qg, 0, m.QG, BK_EPI_BF16, m.QG, 0};
       g.segs[1] = bkGemvSeg{L.k, 0, m.kbuf, 0, m.KVD, BK_EPI_BF16, m.KVD, 0};
       g.segs[2] = bkGemvSeg{L.v, 0, m.vbuf, 0, m.KVD, BK_EPI_BF16, m.KVD, 0};
-      TRY(bk_gemv_launch(g));
+      PROF(PC_GEMV_PROJ, bk_gemv_launch(g));
       bkAttnArgs aa;
       memset(&aa, 0, sizeof(aa));
       aa.qg = m.qg; aa.k = m.kbuf; aa.v = m.vbuf; aa.q_norm_w = L.q_norm; aa.k_norm_w = L.k_norm;
@@ -134,28 +169,28 @@ int32_t enqueue_step(Model& m, int parity) {
       aa.B = B; aa.Hq = m.Hq; aa.Hkv = m.Hkv; aa.HD = c.head_dim; aa.rot_half = c.rot_dim / 2; aa.max_len = c.max_len;
       aa.split_len = m.split_len; aa.max_pos = c.max_len - 1; aa.scale = 1.0f / sqrtf((float)c.head_dim);
       aa.fused_norm_rope = 1;
-      TRY(bkAttnDecode(&aa));
+      PROF(PC_ATTN, bkAttnDecode(&aa));
       memset(&g, 0, sizeof(g));
       g.K = m.Hq * c.head_dim; g.B = B; g.prologue = BK_PRO_BF16; g.x = m.attn_out; g.n_segs = 1;
       g.segs[0] = bkGemvSeg{L.o, 0, m.h1, m.x[cur], H, BK_EPI_ADD_BF16, H, 0};
-      TRY(bk_gemv_launch(g));
+      PROF(PC_GEMV_OUT, bk_gemv_launch(g));
     }
     memset(&g, 0, sizeof(g));
     g.K = H; g.B = B; g.prologue = BK_PRO_RMSNORM; g.x = m.h1; g.norm_w = L.post_ln; g.eps = c.eps; g.n_segs = 1;
     g.segs[0] = bkGemvSeg{L.gate, L.up, m.act, 0, m.inter, BK_EPI_SWIGLU, m.inter, 0};
-    TRY(bk_gemv_launch(g));
+    PROF(PC_GEMV_GATEUP, bk_gemv_launch(g));
     memset(&g, 0, sizeof(g));
     g.K = m.inter; g.B = B; g.prologue = BK_PRO_BF16; g.x = m.act; g.n_segs = 1;
     g.segs[0] = bkGemvSeg{L.down, 0, m.x[cur ^ 1], m.h1, H, BK_EPI_ADD_BF16, H, 0};
-    TRY(bk_gemv_launch(g));
+    PROF(PC_GEMV_DOWN, bk_gemv_launch(g));
     cur ^= 1;
   }
   bkGemvArgs g;
   memset(&g, 0, sizeof(g));
   g.K = H; g.B = B; g.prologue = BK_PRO_RMSNORM; g.x = m.x[cur]; g.norm_w = m.final_norm; g.eps = c.eps; g.n_segs = 1;
   g.segs[0] = bkGemvSeg{m.embed, 0, m.logits, 0, m.vocab_local, BK_EPI_F32, m.vocab_local, 0};
-  TRY(bk_gemv_launch(g));
-  TRY(bk_argmax_launch(m.logits, m.vocab_local, B, m.ids, m.val, m.argmax_scratch, m.pos, m.hist, B, c.max_len));
+  PROF(PC_GEMV_LMHEAD, bk_gemv_launch(g));
+  PROF(PC_ARGMAX, bk_argmax_launch(m.logits, m.vocab_local, B, m.ids, m.val, m.argmax_scratch, m.pos, m.hist, B, c.max_len));
   return BK_OK;
 }
 
@@ -384,6 +419,38 @@ int32_t bkDecodeStep(uint64_t model, const int32_t* tokens, int32_t* out_ids, fl
     if (out_ids) memcpy(out_ids, m.pin_ids + B, (size_t)B * 4);
     if (out_vals) memcpy(out_vals, m.pin_ids + 2 * B, (size_t)B * 4);
   }
+  return BK_OK;
+}
+
+int32_t bkDecodeStepProfiled(uint64_t model, float* ms_out, int32_t* count_out, int32_t n_classes) {
+  BK_REQUIRE_INIT();
+  BK_ARG(model && ms_out && count_out && n_classes >= PC_COUNT, "bkDecodeStepProfiled: need %d classes", (int)PC_COUNT);
+  Model& m = *as_model(model);
+  BK_ARG(m.finalized, "bkDecodeStepProfiled: model is not finalized");
+  BK_ARG(m.steps < m.cfg.max_len, "bkDecodeStepProfiled: position reached max_len");
+  g_prof.on = true;
+  g_prof.ev.clear();
+  g_prof.cls.clear();
+  int32_t rc = enqueue_step(m, (int)(m.steps & 1));
+  g_prof.on = false;
+  cudaError_t e = cudaStreamSynchronize(bk_ctx().stream);
+  for (int i = 0; i < n_classes; i++) {
+    ms_out[i] = 0.0f;
+    count_out[i] = 0;
+  }
+  for (size_t i = 0; i < g_prof.cls.size(); i++) {
+    float ms = 0.0f;
+    if (!rc && e == cudaSuccess) cudaEventElapsedTime(&ms, g_prof.ev[2 * i], g_prof.ev[2 * i + 1]);
+    ms_out[g_prof.cls[i]] += ms;
+    count_out[g_prof.cls[i]] += 1;
+    cudaEventDestroy(g_prof.ev[2 * i]);
+    cudaEventDestroy(g_prof.ev[2 * i + 1]);
+  }
+  g_prof.ev.clear();
+  g_prof.cls.clear();
+  if (rc) return rc;
+  if (e != cudaSuccess) return bk_fail((int32_t)e, "bkDecodeStepProfiled: %s", cudaGetErrorString(e));
+  m.steps++;
   return BK_OK;
 }
 

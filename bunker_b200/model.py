@@ -198,6 +198,16 @@ class DecodeModel:
     def run(self, n_steps: int) -> None:
         R._check(R.cu().bkDecodeRun(self.handle, n_steps))
 
+    PROFILE_CLASSES = ("embed", "gemv_proj", "gdn", "attn", "gemv_out", "gemv_gateup", "gemv_down", "gemv_lmhead",
+                       "argmax")
+
+    def step_profiled(self) -> dict[str, tuple[float, int]]:
+        """One eager step (device token feedback) with an event pair around every op: {class: (ms, calls)}."""
+        n = len(self.PROFILE_CLASSES)
+        ms, cnt = (C.c_float * n)(), (C.c_int32 * n)()
+        R._check(R.cu().bkDecodeStepProfiled(self.handle, ms, cnt, n))
+        return {k: (ms[i], cnt[i]) for i, k in enumerate(self.PROFILE_CLASSES)}
+
     def tokens(self, first_step: int, n_steps: int) -> np.ndarray:
         out = np.empty((n_steps, self.batch), np.int32)
         R._check(R.cu().bkModelTokens(self.handle, first_step, n_steps, out.ctypes.data_as(C.POINTER(C.c_int32))))

@@ -228,6 +228,10 @@ BK_API int32_t bkModelReset(uint64_t model);
 BK_API int32_t bkDecodeStep(uint64_t model, const int32_t* tokens, int32_t* out_ids, float* out_vals);
 /* n_steps greedy steps with device-side token feedback and no host traffic. */
 BK_API int32_t bkDecodeRun(uint64_t model, int32_t n_steps);
+/* One eagerly launched step with a CUDA-event pair around every op (the BUNKER_GPU_PROF=1 profiler of
+ * src/ttir.ts:352-417).  ms_out/count_out[n_classes >= 9]: 0 embed, 1 projection GEMV (qkv|z|a|b, q|k|v),
+ * 2 conv1d+GDN, 3 attention (2 kernels per call), 4 out/o_proj GEMV, 5 gate|up GEMV, 6 down GEMV, 7 lm_head GEMV, 8 argmax. */
+BK_API int32_t bkDecodeStepProfiled(uint64_t model, float* ms_out, int32_t* count_out, int32_t n_classes);
 /* Tokens produced by steps [first_step, first_step+n_steps): out[n_steps][B] host ints. */
 BK_API int32_t bkModelTokens(uint64_t model, int32_t first_step, int32_t n_steps, int32_t* out);
 BK_API int32_t bkModelInfo(uint64_t model, int32_t* split_len, int32_t* attn_warps, int32_t* kernels_per_step,
