@@ -38,6 +38,8 @@ struct AttnParams {
   const uint16_t* gate;
   int B, Hq, Hkv, rot_half, max_len, split_len, max_splits, fused;
   float scale;
+  unsigned long long* trace;
+  unsigned long long* trace2;
 };
 
 __device__ __forceinline__ void bf16x8_to_f32(uint4 v, float (&y)[8]) {
@@ -115,6 +117,10 @@ __device__ __forceinline__ float warp_sum8(const float (&v)[8]) {
 //   o_s   : kW*8*256 f32              65536
 template <int G>
 __global__ void __launch_bounds__(kW * 32) attn_split_kernel(const AttnParams p) {
+  bk_pdl_trigger();
+  bk_stamp(p.trace, 0);
+  bk_pdl_wait();
+  bk_stamp(p.trace, 2);
   extern __shared__ __align__(16) uint8_t smem[];
   uint16_t* q_st = reinterpret_cast<uint16_t*>(smem);
   uint16_t* k_st = q_st + 8 * kHD;
@@ -266,6 +272,7 @@ __global__ void __launch_bounds__(kW * 32) attn_split_kernel(const AttnParams p)
     sc_ml[o] = m_s[tid];
     sc_ml[o + 1] = l;
   }
+  bk_stamp(p.trace, 5);
 }
 
 // merge the splits of one (batch, q head); thread d owns output dim d
@@ -273,6 +280,10 @@ __global__ void __launch_bounds__(kHD) attn_combine_kernel(const AttnParams p) {
   __shared__ float w_s[kMaxSplits];
   __shared__ float l_sh[kMaxSplits];
   __shared__ float red[8];
+  bk_pdl_trigger();
+  bk_stamp(p.trace2, 0);
+  bk_pdl_wait();
+  bk_stamp(p.trace2, 2);
   const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
   const int n = p.pos[b] + 1;
   const int ns = (n + p.split_len - 1) / p.split_len;
@@ -303,6 +314,7 @@ __global__ void __launch_bounds__(kHD) attn_combine_kernel(const AttnParams p) {
                                  : p.gate[((size_t)b * p.Hq + h) * kHD + tid];
   float o = __fmul_rn(__fdiv_rn(O, L), bk_sigmoidf(bk_bf16_to_f32(gbits)));
   p.out[((size_t)b * p.Hq + h) * kHD + tid] = bk_f32_to_bf16(o);
+  bk_stamp(p.trace2, 5);
 }
 
 size_t attn_smem_bytes(int split_len) { return 4096 + 512 + 64 + 256 + (size_t)split_len * 32 + (size_t)kW * 8 * kHD * 4; }
@@ -314,7 +326,7 @@ int32_t launch_split(const AttnParams& p, dim3 grid, size_t smem) {
     BK_CUDA(cudaFuncSetAttribute(attn_split_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = smem;
   }
-  attn_split_kernel<G><<<grid, kW * 32, smem, bk_ctx().stream>>>(p);
+  BK_CUDA(bk_launch_pdl(attn_split_kernel<G>, grid, dim3(kW * 32), smem, p));
   BK_CHECK_LAUNCH();
   return BK_OK;
 }
@@ -393,6 +405,8 @@ int32_t bkAttnDecode(const bkAttnArgs* args) {
   p.max_splits = max_splits;
   p.fused = a.fused_norm_rope;
   p.scale = a.scale;
+  p.trace = bk_trace_slot();
+  p.trace2 = bk_trace_slot();
   size_t smem = attn_smem_bytes(split_len);
   dim3 grid(nsplit, a.Hkv, a.B);
   int32_t rc;
@@ -407,7 +421,7 @@ int32_t bkAttnDecode(const bkAttnArgs* args) {
     default: rc = launch_split<8>(p, grid, smem); break;
   }
   if (rc) return rc;
-  attn_combine_kernel<<<dim3(a.Hq, a.B), kHD, 0, bk_ctx().stream>>>(p);
+  BK_CUDA(bk_launch_pdl(attn_combine_kernel, dim3(a.Hq, a.B), dim3(kHD), 0, p));
   BK_CHECK_LAUNCH();
   return BK_OK;
 }

@@ -10,6 +10,21 @@
 
 #define BK_DEVINL __device__ __forceinline__
 
+// ---- programmatic dependent launch -------------------------------------------
+// trigger: lets the next kernel on the stream start its own pre-wait part now.
+// wait   : returns once every earlier kernel has completed and its writes are visible.
+BK_DEVINL void bk_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;"); }
+BK_DEVINL void bk_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// ---- device-side timeline (bkTraceEnable): thread 0 of CTA 0 stamps the global timer ----
+BK_DEVINL void bk_stamp(unsigned long long* rec, int slot) {
+  if (rec && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    rec[slot] = t;
+  }
+}
+
 // ---- bf16 / f16 -----------------------------------------------------------
 
 BK_DEVINL float bk_bf16_to_f32(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }

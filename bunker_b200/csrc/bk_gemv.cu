@@ -17,6 +17,12 @@
 // and the xor-butterfly over the 32 lanes.  The order is fixed so a host can
 // reproduce the result bit for bit.
 //
+// Weight staging.  One CTA per SM.  Each warp owns a ring of shared-memory stages; lane 0 fills a
+// stage with two bulk async copies (cp.async.bulk, completion on an mbarrier), one per row of the task.
+// The copies of a warp's first tasks are issued before the programmatic-dependency wait, so the weight
+// stream of this launch is in flight while the previous kernel drains and while the activation
+// prologue runs; the dot products then read weights from shared memory.
+//
 // The activation lives in shared memory for the whole CTA: int8 quants padded to
 // 80 bytes per 64 (conflict-free 128-bit reads at lane stride), plus per-block
 // d8 and s8 = d8*sum(q8) (exact in f32).  Three prologues fill it: ready-made
@@ -26,7 +32,7 @@
 
 namespace {
 
-constexpr int kThreads = 256;
+constexpr int kThreads = 256;   // threads of the canonical sum-of-squares order (and of the small kernels below)
 constexpr int kWarps = kThreads / 32;
 constexpr int kUnitWords = 20;  // 16 data words + 4 pad
 
@@ -39,17 +45,22 @@ struct SegDev {
   int epi;
   int ld_out;
   int col_off;
-  int task_begin;  // first task index of this segment
+  int vrow_begin;  // first virtual row of this segment
 };
 
 struct GemvParams {
   int K;
   int n_segs;
   int prologue;
-  int total_tasks;
+  int total_vrows;
+  int rows_per_cta;
+  int n_slots;       // weight slots (and mbarriers) per CTA
+  int depth;         // 0: one slot per group, all requested up front; >0: per-warp ring of this depth
   const void* x;
   const uint16_t* norm_w;
   float eps;
+  int* status;       // device status word: set when a bounded wait gives up
+  unsigned long long* trace;  // timeline record of this launch, or null
   SegDev segs[4];
 };
 
@@ -60,7 +71,7 @@ template <int B>
 __device__ void prologue_q8(const GemvParams& p, uint32_t* xs, float* d8s, float* s8s) {
   const int nblk = p.K / 32, nunits = p.K / 64;
   const uint32_t* src = reinterpret_cast<const uint32_t*>(p.x);
-  for (int i = threadIdx.x; i < B * nblk; i += kThreads) {
+  for (int i = threadIdx.x; i < B * nblk; i += blockDim.x) {
     int b = i / nblk, blk = i - b * nblk;
     const uint32_t* s = src + (size_t)i * 9;
     uint32_t* dst = xs + ((size_t)b * nunits + (blk >> 1)) * kUnitWords + (blk & 1) * 8;
@@ -139,23 +150,26 @@ __device__ void prologue_bf16(const GemvParams& p, uint32_t* xs, float* d8s, flo
     float rstd = 1.0f;
     if (NORM) {
       float acc = 0.0f;
-      for (int q = threadIdx.x; q < nchunk; q += kThreads) {
-        float y[8];
-        load_chunk_bf16(row, q, y);
+      if (threadIdx.x < kThreads) {  // the fixed 256-thread order, whatever the CTA size
+        for (int q = threadIdx.x; q < nchunk; q += kThreads) {
+          float y[8];
+          load_chunk_bf16(row, q, y);
 #pragma unroll
-        for (int e = 0; e < 8; e++) acc = fmaf(y[e], y[e], acc);
+          for (int e = 0; e < 8; e++) acc = fmaf(y[e], y[e], acc);
+        }
+        acc = bk_warp_sum(acc);
       }
-      acc = bk_warp_sum(acc);
       __syncthreads();  // red[] reuse across batch rows
-      if (lane == 0) red[warp] = acc;
+      if (lane == 0 && warp < kWarps) red[warp] = acc;
       __syncthreads();
       float total = red[0];
 #pragma unroll
       for (int w = 1; w < kWarps; w++) total = __fadd_rn(total, red[w]);
       float ms = __fdiv_rn(total, (float)K);
       rstd = bk_rcp_sqrt(__fadd_rn(ms, p.eps));
+      bk_stamp(p.trace, 6);
     }
-    for (int q = threadIdx.x; q < nchunk; q += kThreads) {
+    for (int q = threadIdx.x; q < nchunk; q += blockDim.x) {
       float y[8];
       load_chunk_bf16(row, q, y);
       if (NORM) {
@@ -169,6 +183,7 @@ __device__ void prologue_bf16(const GemvParams& p, uint32_t* xs, float* d8s, flo
       }
       quant_chunk(y, q, b, nunits, nblk, xs, d8s, s8s);
     }
+    bk_stamp(p.trace, 7);
   }
 }
 
@@ -238,14 +253,170 @@ __device__ __forceinline__ void unit_dot(const RowRegs& r, int u, const uint32_t
   }
 }
 
-template <int B>
-__global__ void __launch_bounds__(kThreads) gemv_q4k_kernel(const GemvParams p) {
-  extern __shared__ __align__(16) uint8_t smem_raw[];
+// ---- virtual rows --------------------------------------------------------------
+// The rows of all segments of a launch are numbered consecutively.  A SwiGLU segment contributes
+// 2*n_rows virtual rows: even = gate row, odd = the up row of the same output column.
+struct VRow {
+  const uint8_t* row;
+  int si;  // segment
+  int n;   // output column within the segment
+};
+
+__device__ __forceinline__ VRow decode_vrow(const GemvParams& p, int v) {
+  int si = 0;
+#pragma unroll
+  for (int s = 1; s < 4; s++)
+    if (s < p.n_segs && v >= p.segs[s].vrow_begin) si = s;
+  const SegDev& sg = p.segs[si];
+  const int t = v - sg.vrow_begin;
+  const size_t rowb = (size_t)(p.K / 256) * 144;
+  VRow r;
+  r.si = si;
+  if (sg.epi == BK_EPI_SWIGLU) {
+    r.n = t >> 1;
+    r.row = ((t & 1) ? sg.W2 : sg.W) + rowb * (size_t)r.n;
+  } else {
+    r.n = t;
+    r.row = sg.W + rowb * (size_t)t;
+  }
+  return r;
+}
+
+__device__ __forceinline__ RowRegs load_unit_smem(const uint8_t* row, int u) {
+  const uint8_t* sb = row + (size_t)(u >> 2) * 144;
+  RowRegs r;
+  r.hdr = *reinterpret_cast<const uint4*>(sb);
+  const uint4* q = reinterpret_cast<const uint4*>(sb + 16 + (u & 3) * 32);
+  r.qa = q[0];
+  r.qb = q[1];
+  return r;
+}
+
+// ---- mbarrier + bulk async copy (global -> this CTA's shared memory, no multicast) ----
+BK_DEVINL uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+BK_DEVINL void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+BK_DEVINL void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+BK_DEVINL void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+BK_DEVINL bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// bounded: a copy that never lands sets the status word instead of hanging the GPU
+BK_DEVINL void mbar_wait_bounded(uint32_t bar, uint32_t parity, int* status) {
+  for (int it = 0; it < (1 << 22); it++)
+    if (mbar_try_wait(bar, parity)) return;
+  if (status) atomicExch(status, BK_ERR_TIMEOUT);
+}
+
+// Sum 8 per-lane values over the warp with 9 shuffles instead of 40: at each of the first three
+// levels a lane keeps half of its values and trades the other half with its xor partner.  Every
+// addition is one the 16,8,4,2,1 butterfly would make, so the bits are the butterfly's.
+// On return lane l holds the total of value index 4*bit4(l) + 2*bit3(l) + bit2(l).
+__device__ __forceinline__ float warp_sum8(const float (&v)[8]) {
+  const int lane = threadIdx.x & 31;
+  const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
+  float w[4], x[2];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    float send = b4 ? v[i] : v[i + 4];
+    float keep = b4 ? v[i + 4] : v[i];
+    w[i] = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, 16));
+  }
+#pragma unroll
+  for (int i = 0; i < 2; i++) {
+    float send = b3 ? w[i] : w[i + 2];
+    float keep = b3 ? w[i + 2] : w[i];
+    x[i] = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, 8));
+  }
+  float send = b2 ? x[0] : x[1];
+  float keep = b2 ? x[1] : x[0];
+  float y = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, 4));
+  y = __fadd_rn(y, __shfl_xor_sync(0xffffffffu, y, 2));
+  y = __fadd_rn(y, __shfl_xor_sync(0xffffffffu, y, 1));
+  return y;
+}
+
+__device__ __forceinline__ void store_epilogue(const SegDev& sg, size_t o, float y, float yup) {
+  if (sg.epi == BK_EPI_SWIGLU) {
+    float sig = bk_sigmoidf(y);
+    reinterpret_cast<uint16_t*>(sg.out)[o] = bk_f32_to_bf16(__fmul_rn(__fmul_rn(y, sig), yup));
+  } else if (sg.epi == BK_EPI_F32) {
+    reinterpret_cast<float*>(sg.out)[o] = y;
+  } else if (sg.epi == BK_EPI_BF16) {
+    reinterpret_cast<uint16_t*>(sg.out)[o] = bk_f32_to_bf16(y);
+  } else {  // BK_EPI_ADD_BF16
+    reinterpret_cast<uint16_t*>(sg.out)[o] = bk_f32_to_bf16(__fadd_rn(y, bk_bf16_to_f32(sg.res[o])));
+  }
+}
+
+// One CTA per SM owns the contiguous virtual rows [c*rows_per_cta, ...).  Rows are processed in
+// groups of G by one warp (group g of the CTA belongs to warp g mod nw).  Each group has a slot of
+// G rows in shared memory and an mbarrier.  depth == 0 ("pool"): every group has its own slot and all
+// copies are issued before the dependency wait.  depth > 0 ("ring"): a warp owns `depth` slots and
+// refills a slot with its next group as soon as the slot is consumed.
+template <int B, int G>
+__global__ void __launch_bounds__(512, ((B * G <= 16) ? 2 : 1)) gemv_q4k_kernel(const GemvParams p) {
+  bk_pdl_trigger();
+  bk_stamp(p.trace, 0);
+  extern __shared__ __align__(128) uint8_t smem_raw[];
   const int K = p.K, nunits = K / 64, nblk = K / 32;
+  const int nw = blockDim.x >> 5;
   uint32_t* xs = reinterpret_cast<uint32_t*>(smem_raw);
   float* d8s = reinterpret_cast<float*>(xs + (size_t)B * nunits * kUnitWords);
   float* s8s = d8s + (size_t)B * nblk;
   float* red = s8s + (size_t)B * nblk;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(red + 8);
+  uint8_t* slots = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(bars + p.n_slots) + 127) & ~(uintptr_t)127);
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c0 = blockIdx.x * p.rows_per_cta;
+  const int n_rows_cta = min(p.total_vrows, c0 + p.rows_per_cta) - c0;
+  const int n_groups = (n_rows_cta + G - 1) / G;
+  const uint32_t rowb = (uint32_t)(K / 256) * 144;
+  const uint32_t slot_bytes = G * rowb;
+  const int depth = p.depth;
+  const uint32_t bar_base = smem_u32(bars);
+  const uint32_t slot_base = smem_u32(slots);
+
+  // ---- before the dependency wait: weights only ----
+  if (lane == 0) {
+    int first = depth == 0 ? (n_groups - warp + nw - 1) / nw : depth;  // groups to request now
+    for (int gi = 0; gi < first; gi++) {
+      const int g = warp + gi * nw;
+      const int slot = depth == 0 ? g : gi * nw + warp;
+      mbar_init(bar_base + 8 * slot, 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    for (int gi = 0; gi < first; gi++) {
+      const int g = warp + gi * nw;
+      if (g >= n_groups) break;
+      const int slot = depth == 0 ? g : gi * nw + warp;
+      const int nr = min(G, n_rows_cta - g * G);
+      mbar_expect_tx(bar_base + 8 * slot, nr * rowb);
+      for (int r = 0; r < nr; r++) {
+        VRow vr = decode_vrow(p, c0 + g * G + r);
+        bulk_g2s(slot_base + slot * slot_bytes + r * rowb, vr.row, rowb, bar_base + 8 * slot);
+      }
+    }
+  }
+  __syncwarp();
+  bk_stamp(p.trace, 1);
+  bk_pdl_wait();
+  bk_stamp(p.trace, 2);
 
   if (p.prologue == BK_PRO_Q8)
     prologue_q8<B>(p, xs, d8s, s8s);
@@ -254,96 +425,86 @@ __global__ void __launch_bounds__(kThreads) gemv_q4k_kernel(const GemvParams p) 
   else
     prologue_bf16<B, true>(p, xs, d8s, s8s, red);
   __syncthreads();
+  bk_stamp(p.trace, 3);
 
-  const int lane = threadIdx.x & 31;
-  const int gwarp = blockIdx.x * kWarps + (threadIdx.x >> 5);
-  const int nwarps = gridDim.x * kWarps;
-
-  for (int task = gwarp; task < p.total_tasks; task += nwarps) {
-    // segment lookup
-    int si = 0;
+  const int ri = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);  // row this lane reports
+  for (int gi = 0, g = warp; g < n_groups; gi++, g += nw) {
+    const int slot = depth == 0 ? g : (gi % depth) * nw + warp;
+    const uint32_t parity = depth == 0 ? 0u : (uint32_t)((gi / depth) & 1);
+    const int nr = min(G, n_rows_cta - g * G);
+    mbar_wait_bounded(bar_base + 8 * slot, parity, p.status);
+    if (gi == 0) bk_stamp(p.trace, 4);
+    const uint8_t* wbase = slots + (size_t)slot * slot_bytes;
+    float acc[G][B];
 #pragma unroll
-    for (int s = 1; s < 4; s++)
-      if (s < p.n_segs && task >= p.segs[s].task_begin) si = s;
-    const SegDev& sg = p.segs[si];
-    const int t = task - sg.task_begin;
-    const size_t rowb = (size_t)(K / 256) * 144;
-    const uint8_t *row0, *row1;
-    int n0, n1;  // output columns (relative to segment) of the two rows; n1 < 0 if absent
-    if (sg.epi == BK_EPI_SWIGLU) {
-      n0 = t;
-      n1 = t;
-      row0 = sg.W + rowb * t;
-      row1 = sg.W2 + rowb * t;
-    } else {
-      n0 = 2 * t;
-      n1 = (2 * t + 1 < sg.n_rows) ? 2 * t + 1 : -1;
-      row0 = sg.W + rowb * n0;
-      row1 = sg.W + rowb * (n1 >= 0 ? n1 : n0);
-    }
-    float acc0[B], acc1[B];
+    for (int r = 0; r < G; r++)
 #pragma unroll
-    for (int b = 0; b < B; b++) {
-      acc0[b] = 0.0f;
-      acc1[b] = 0.0f;
-    }
+      for (int b = 0; b < B; b++) acc[r][b] = 0.0f;
     for (int u = lane; u < nunits; u += 32) {
-      RowRegs r0 = load_unit(row0, u);
-      RowRegs r1 = load_unit(row1, u);
-      unit_dot<B>(r0, u, xs, d8s, s8s, nunits, nblk, acc0);
-      unit_dot<B>(r1, u, xs, d8s, s8s, nunits, nblk, acc1);
+#pragma unroll
+      for (int r = 0; r < G; r++) {
+        if (r < nr) {
+          RowRegs rr = load_unit_smem(wbase + (size_t)r * rowb, u);
+          unit_dot<B>(rr, u, xs, d8s, s8s, nunits, nblk, acc[r]);
+        }
+      }
     }
+    __syncwarp();  // every lane has consumed the slot
+    if (depth > 0 && lane == 0) {
+      const int g2 = g + depth * nw;
+      if (g2 < n_groups) {
+        const int nr2 = min(G, n_rows_cta - g2 * G);
+        mbar_expect_tx(bar_base + 8 * slot, nr2 * rowb);
+        for (int r = 0; r < nr2; r++) {
+          VRow vr = decode_vrow(p, c0 + g2 * G + r);
+          bulk_g2s(slot_base + slot * slot_bytes + r * rowb, vr.row, rowb, bar_base + 8 * slot);
+        }
+      }
+    }
+    // reduce over lanes; lane (lane&3)==0 ends up with the sum of row ri of the group
+    const int v = c0 + g * G + ri;
+    const bool mine = (lane & 3) == 0 && ri < nr;
+    VRow vr = {nullptr, 0, 0};
+    if (mine) vr = decode_vrow(p, v);
+    const SegDev& sg = p.segs[vr.si];
 #pragma unroll
     for (int b = 0; b < B; b++) {
-      acc0[b] = bk_warp_sum(acc0[b]);
-      acc1[b] = bk_warp_sum(acc1[b]);
-    }
-    // epilogue: lane b handles batch column b of row0 (and row1)
-    float v0 = 0.0f, v1 = 0.0f;
+      float pa[8];
 #pragma unroll
-    for (int b = 0; b < B; b++)
-      if (lane == b) {
-        v0 = acc0[b];
-        v1 = acc1[b];
-      }
-    if (lane < B) {
-      const size_t ob = (size_t)lane * sg.ld_out + sg.col_off;
-      if (sg.epi == BK_EPI_SWIGLU) {
-        float sig = bk_sigmoidf(v0);
-        float o = __fmul_rn(__fmul_rn(v0, sig), v1);
-        reinterpret_cast<uint16_t*>(sg.out)[ob + n0] = bk_f32_to_bf16(o);
-      } else if (sg.epi == BK_EPI_F32) {
-        float* o = reinterpret_cast<float*>(sg.out);
-        o[ob + n0] = v0;
-        if (n1 >= 0) o[ob + n1] = v1;
-      } else if (sg.epi == BK_EPI_BF16) {
-        uint16_t* o = reinterpret_cast<uint16_t*>(sg.out);
-        o[ob + n0] = bk_f32_to_bf16(v0);
-        if (n1 >= 0) o[ob + n1] = bk_f32_to_bf16(v1);
-      } else {  // BK_EPI_ADD_BF16
-        uint16_t* o = reinterpret_cast<uint16_t*>(sg.out);
-        o[ob + n0] = bk_f32_to_bf16(__fadd_rn(v0, bk_bf16_to_f32(sg.res[ob + n0])));
-        if (n1 >= 0) o[ob + n1] = bk_f32_to_bf16(__fadd_rn(v1, bk_bf16_to_f32(sg.res[ob + n1])));
-      }
+      for (int r = 0; r < 8; r++) pa[r] = r < G ? acc[r < G ? r : 0][b] : 0.0f;
+      const float y = warp_sum8(pa);
+      const float yup = __shfl_xor_sync(0xffffffffu, y, 4);  // the odd neighbour row (the "up" row of a SwiGLU pair)
+      if (mine && !(sg.epi == BK_EPI_SWIGLU && (ri & 1))) store_epilogue(sg, (size_t)b * sg.ld_out + sg.col_off + vr.n, y, yup);
     }
   }
+  bk_stamp(p.trace, 5);
 }
 
-size_t gemv_smem_bytes(int K, int B) {
+// bytes of shared memory before the weight slots: activation, scales, reduction scratch, barriers (+ alignment slack)
+size_t gemv_fixed_smem(int K, int B, int n_slots) {
   size_t nunits = K / 64, nblk = K / 32;
-  return (size_t)B * nunits * kUnitWords * 4 + (size_t)B * nblk * 8 + kWarps * 4 + 16;
+  return (size_t)B * nunits * kUnitWords * 4 + (size_t)B * nblk * 8 + 8 * 4 + (size_t)n_slots * 8 + 128;
+}
+
+template <int B, int G>
+int32_t launch_gemv(const GemvParams& p, int grid, int threads, size_t smem) {
+  static size_t configured = 0;
+  if (smem > configured) {
+    BK_CUDA((cudaFuncSetAttribute(gemv_q4k_kernel<B, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)));
+    configured = smem;
+  }
+  BK_CUDA((bk_launch_pdl(gemv_q4k_kernel<B, G>, dim3(grid), dim3(threads), smem, p)));
+  BK_CHECK_LAUNCH();
+  return BK_OK;
 }
 
 template <int B>
-int32_t launch_gemv(const GemvParams& p, int grid, size_t smem) {
-  static size_t configured = 0;
-  if (smem > configured) {
-    BK_CUDA(cudaFuncSetAttribute(gemv_q4k_kernel<B>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = smem;
+int32_t launch_gemv_g(const GemvParams& p, int G, int grid, int threads, size_t smem) {
+  if (G == 8) {
+    if constexpr (B <= 2) return launch_gemv<B, 8>(p, grid, threads, smem);
   }
-  gemv_q4k_kernel<B><<<grid, kThreads, smem, bk_ctx().stream>>>(p);
-  BK_CHECK_LAUNCH();
-  return BK_OK;
+  if (G >= 4) return launch_gemv<B, 4>(p, grid, threads, smem);
+  return launch_gemv<B, 2>(p, grid, threads, smem);
 }
 
 // ---- dequant / block-dot check kernels ---------------------------------------
@@ -468,7 +629,8 @@ int32_t bk_gemv_launch(const bkGemvArgs& a) {
   p.x = bk_ptr<void>(a.x);
   p.norm_w = bk_ptr<uint16_t>(a.norm_w);
   p.eps = a.eps;
-  int tasks = 0;
+  int vrows = 0;
+  bool has_swiglu = false;
   for (int s = 0; s < 4; s++) {
     SegDev& d = p.segs[s];
     if (s >= a.n_segs) {
@@ -482,8 +644,10 @@ int32_t bk_gemv_launch(const bkGemvArgs& a) {
     BK_ARG(g.epilogue >= BK_EPI_F32 && g.epilogue <= BK_EPI_SWIGLU, "bkGemvQ4K: segment %d unknown epilogue %d", s,
            g.epilogue);
     BK_ARG(g.ld_out >= g.col_off + g.n_rows, "bkGemvQ4K: segment %d ld_out=%d < col_off+n_rows", s, g.ld_out);
-    if (g.epilogue == BK_EPI_SWIGLU)
+    if (g.epilogue == BK_EPI_SWIGLU) {
       BK_ARG(g.W2 != 0 && (g.W2 & 15) == 0, "bkGemvQ4K: segment %d needs a 16-byte aligned W2 for SwiGLU", s);
+      has_swiglu = true;
+    }
     if (g.epilogue == BK_EPI_ADD_BF16) BK_ARG(g.residual != 0, "bkGemvQ4K: segment %d needs a residual", s);
     d.W = bk_ptr<uint8_t>(g.W);
     d.W2 = bk_ptr<uint8_t>(g.W2);
@@ -493,28 +657,65 @@ int32_t bk_gemv_launch(const bkGemvArgs& a) {
     d.epi = g.epilogue;
     d.ld_out = g.ld_out;
     d.col_off = g.col_off;
-    d.task_begin = tasks;
-    tasks += (g.epilogue == BK_EPI_SWIGLU) ? g.n_rows : (g.n_rows + 1) / 2;
+    d.vrow_begin = vrows;
+    vrows += (g.epilogue == BK_EPI_SWIGLU) ? 2 * g.n_rows : g.n_rows;
   }
-  p.total_tasks = tasks;
-  size_t smem = gemv_smem_bytes(a.K, a.B);
-  BK_ARG(smem <= c.smem_optin, "bkGemvQ4K: K=%d B=%d needs %zu bytes of shared memory (limit %zu)", a.K, a.B, smem,
-         c.smem_optin);
-  int ctas_per_sm = (int)((c.smem_optin) / (smem + 1024));
-  if (ctas_per_sm > 4) ctas_per_sm = 4;
-  if (ctas_per_sm < 1) ctas_per_sm = 1;
-  int grid = (tasks + kWarps - 1) / kWarps;
-  int cap = c.sm_count * ctas_per_sm;
-  if (grid > cap) grid = cap;
+  // gate/up pairs must sit at even virtual rows so that a pair never straddles a group
+  BK_ARG(!has_swiglu || a.n_segs == 1, "bkGemvQ4K: a SwiGLU segment must be the only segment of its launch");
+  p.total_vrows = vrows;
+  p.status = c.d_status;
+  p.trace = bk_trace_slot();
+
+  // ---- launch shape ----
+  const size_t rowb = (size_t)(a.K / 256) * 144;
+  const size_t limit = c.smem_optin - 1024;
+  int grid = (vrows + 7) / 8;
+  if (grid > c.sm_count) grid = c.sm_count;
+  int rpc = (vrows + grid - 1) / grid;
+  rpc = (rpc + 1) & ~1;
+  grid = (vrows + rpc - 1) / rpc;
+  // rows per group: enough groups to keep a dozen warps busy; register budget caps G for wide batches
+  int G = rpc >= 128 ? 8 : (rpc >= 48 ? 4 : 2);
+  if (a.B > 2 && G > 4) G = 4;
+  const int n_groups = (rpc + G - 1) / G;
+  int nw = n_groups < 8 ? 8 : (n_groups > 16 ? 16 : n_groups);
+  // pool if the CTA's whole slice fits in about half of the SM's shared memory (so the next kernel's CTA can
+  // become resident and start its own copies while this one computes), else a per-warp ring
+  int depth = 0, n_slots = n_groups;
+  const size_t half = limit / 2;
+  if (gemv_fixed_smem(a.K, a.B, n_groups) + (size_t)n_groups * G * rowb > half) {
+    size_t per_level = (size_t)nw * G * rowb;
+    while (nw > 8 && gemv_fixed_smem(a.K, a.B, nw) + per_level > limit) {
+      nw = 8;
+      per_level = (size_t)nw * G * rowb;
+    }
+    while (G > 2 && gemv_fixed_smem(a.K, a.B, nw) + per_level > limit) {
+      G >>= 1;
+      per_level = (size_t)nw * G * rowb;
+    }
+    const size_t fixed = gemv_fixed_smem(a.K, a.B, nw * 8);
+    BK_ARG(fixed + per_level <= limit, "bkGemvQ4K: K=%d B=%d does not fit in shared memory", a.K, a.B);
+    const int groups = (rpc + G - 1) / G;
+    depth = (int)((limit - fixed) / per_level);
+    const int max_depth = (groups + nw - 1) / nw;
+    if (depth > max_depth) depth = max_depth;
+    if (depth > 8) depth = 8;
+    n_slots = depth * nw;
+  }
+  p.rows_per_cta = rpc;
+  p.n_slots = n_slots;
+  p.depth = depth;
+  const size_t smem = gemv_fixed_smem(a.K, a.B, n_slots) + (size_t)n_slots * G * rowb;
+  const int threads = nw * 32;
   switch (a.B) {
-    case 1: return launch_gemv<1>(p, grid, smem);
-    case 2: return launch_gemv<2>(p, grid, smem);
-    case 3: return launch_gemv<3>(p, grid, smem);
-    case 4: return launch_gemv<4>(p, grid, smem);
-    case 5: return launch_gemv<5>(p, grid, smem);
-    case 6: return launch_gemv<6>(p, grid, smem);
-    case 7: return launch_gemv<7>(p, grid, smem);
-    default: return launch_gemv<8>(p, grid, smem);
+    case 1: return launch_gemv_g<1>(p, G, grid, threads, smem);
+    case 2: return launch_gemv_g<2>(p, G, grid, threads, smem);
+    case 3: return launch_gemv_g<3>(p, G, grid, threads, smem);
+    case 4: return launch_gemv_g<4>(p, G, grid, threads, smem);
+    case 5: return launch_gemv_g<5>(p, G, grid, threads, smem);
+    case 6: return launch_gemv_g<6>(p, G, grid, threads, smem);
+    case 7: return launch_gemv_g<7>(p, G, grid, threads, smem);
+    default: return launch_gemv_g<8>(p, G, grid, threads, smem);
   }
 }
 

@@ -17,6 +17,10 @@ struct BkContext {
   unsigned long long launches = 0;   // kernels enqueued outside graphs + graph kernels replayed
   bool capturing = false;            // true while a graph capture is open on `stream`
   unsigned long long captured = 0;   // kernels recorded into the open capture
+  unsigned long long* trace = nullptr;  // device trace buffer (bkTraceEnable), 8 slots per launch
+  int trace_cap = 0;                  // launches the buffer can hold
+  int trace_seq = 0;                  // next launch index
+  int* d_status = nullptr;           // device word set by kernels whose bounded waits gave up
   char err[512] = {0};
 };
 
@@ -61,3 +65,28 @@ static inline T* bk_ptr(uint64_t p) { return reinterpret_cast<T*>(static_cast<ui
 int32_t bk_gemv_launch(const bkGemvArgs& a);
 int32_t bk_argmax_launch(uint64_t logits, int32_t V, int32_t B, uint64_t idx, uint64_t val, uint64_t scratch,
                          uint64_t pos, uint64_t hist, int32_t hist_ld, int32_t hist_rows);
+
+// Launch with programmatic dependent launch: the kernel may start while its predecessor on the
+// stream is still running; it must execute bk_pdl_wait() (bk_common.cuh) before it touches anything
+// an earlier kernel wrote or may still read.  Works eagerly and under stream capture.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t bk_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = bk_ctx().stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// next trace record for a launch (nullptr when tracing is off or the buffer is full)
+inline unsigned long long* bk_trace_slot() {
+  BkContext& c = bk_ctx();
+  if (!c.trace || c.trace_seq >= c.trace_cap) return nullptr;
+  return c.trace + (size_t)(c.trace_seq++) * 8;
+}

@@ -11,6 +11,8 @@ namespace {
 
 // ---- embed: x[b] = bf16(dequant(E[ids[b]])) (src/emitters.ts:31-45) ------------
 __global__ void embed_q4k_kernel(const uint8_t* table, int H, const int32_t* ids, uint16_t* x) {
+  bk_pdl_trigger();
+  bk_pdl_wait();
   const int b = blockIdx.x;
   const int nunits = H / 64;
   const uint8_t* row = table + (size_t)ids[b] * (H / 256) * 144;
@@ -141,6 +143,7 @@ struct GdnParams {
   float* o_raw;
   uint16_t* conv_out;
   int B, Hk, Hv, apply_conv;
+  unsigned long long* trace;
 };
 
 __global__ void __launch_bounds__(512) gdn_step_kernel(const GdnParams p) {
@@ -148,6 +151,10 @@ __global__ void __launch_bounds__(512) gdn_step_kernel(const GdnParams p) {
   __shared__ float s_q[D], s_k[D], s_v[D], s_o[D];
   __shared__ float s_part[4][D];
   __shared__ float s_scal[4];  // q scale, k rstd, decay, beta
+  bk_pdl_trigger();
+  bk_stamp(p.trace, 0);
+  bk_pdl_wait();
+  bk_stamp(p.trace, 2);
   const int hv = blockIdx.x, b = blockIdx.y, t = threadIdx.x;
   const int ratio = p.Hv / p.Hk, hk = hv / ratio;
   const int keydim = p.Hk * D, C = 2 * keydim + p.Hv * D;
@@ -248,6 +255,7 @@ __global__ void __launch_bounds__(512) gdn_step_kernel(const GdnParams p) {
     float ow = __fmul_rn(__fmul_rn(s_o[t], s_scal[0]), p.norm_w[t]);
     p.out[((size_t)b * p.Hv + hv) * D + t] = bk_f32_to_bf16(__fmul_rn(ow, zs));
   }
+  bk_stamp(p.trace, 5);
 }
 
 // ---- q/k head RMSNorm + partial rotary, one warp per (batch, head) ----------------
@@ -321,6 +329,8 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float* logits, int V,
   __shared__ float sv[8];
   __shared__ int si[8];
   __shared__ bool last;
+  bk_pdl_trigger();
+  bk_pdl_wait();
   const int b = blockIdx.y;
   const float* l = logits + (size_t)b * V;
   const int per = (V + gridDim.x - 1) / gridDim.x;
@@ -380,8 +390,8 @@ int32_t bkEmbedQ4K(uint64_t table, int32_t H, uint64_t ids, int32_t B, uint64_t 
   BK_REQUIRE_INIT();
   BK_ARG(H > 0 && H % 256 == 0 && B > 0, "bkEmbedQ4K: bad shape H=%d B=%d", H, B);
   BK_ARG(table && ids && x_out && (table & 15) == 0, "bkEmbedQ4K: null or misaligned pointer");
-  embed_q4k_kernel<<<B, 64, 0, bk_ctx().stream>>>(bk_ptr<uint8_t>(table), H, bk_ptr<int32_t>(ids),
-                                                 bk_ptr<uint16_t>(x_out));
+  BK_CUDA(bk_launch_pdl(embed_q4k_kernel, dim3(B), dim3(64), 0, bk_ptr<uint8_t>(table), H, bk_ptr<int32_t>(ids),
+                        bk_ptr<uint16_t>(x_out)));
   BK_CHECK_LAUNCH();
   return BK_OK;
 }
@@ -452,7 +462,8 @@ int32_t bkGdnStep(const bkGdnArgs* args) {
   p.Hk = a.Hk;
   p.Hv = a.Hv;
   p.apply_conv = a.apply_conv;
-  gdn_step_kernel<<<dim3(a.Hv, a.B), 512, 0, bk_ctx().stream>>>(p);
+  p.trace = bk_trace_slot();
+  BK_CUDA(bk_launch_pdl(gdn_step_kernel, dim3(a.Hv, a.B), dim3(512), 0, p));
   BK_CHECK_LAUNCH();
   return BK_OK;
 }
@@ -503,9 +514,9 @@ int32_t bk_argmax_launch(uint64_t logits, int32_t V, int32_t B, uint64_t idx, ui
   unsigned int* cnt = reinterpret_cast<unsigned int*>(pi + (size_t)B * kArgmaxBlocks);
   int blocks = (V + 2047) / 2048;
   if (blocks > kArgmaxBlocks) blocks = kArgmaxBlocks;
-  argmax_kernel<<<dim3(blocks, B), 256, 0, bk_ctx().stream>>>(bk_ptr<float>(logits), V, bk_ptr<int32_t>(idx),
-                                                             bk_ptr<float>(val), pv, pi, cnt, bk_ptr<int32_t>(pos),
-                                                             bk_ptr<int32_t>(hist), hist_ld, hist_rows);
+  BK_CUDA(bk_launch_pdl(argmax_kernel, dim3(blocks, B), dim3(256), 0, bk_ptr<float>(logits), V, bk_ptr<int32_t>(idx),
+                        bk_ptr<float>(val), pv, pi, cnt, bk_ptr<int32_t>(pos), bk_ptr<int32_t>(hist), hist_ld,
+                        hist_rows));
   BK_CHECK_LAUNCH();
   return BK_OK;
 }

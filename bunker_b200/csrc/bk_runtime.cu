@@ -39,6 +39,8 @@ int32_t bkInit(int32_t device) {
   g_ctx.total_mem = prop.totalGlobalMem;
   g_ctx.smem_optin = prop.sharedMemPerBlockOptin;
   BK_CUDA(cudaStreamCreateWithFlags(&g_ctx.stream, cudaStreamNonBlocking));
+  BK_CUDA(cudaMalloc((void**)&g_ctx.d_status, sizeof(int)));
+  BK_CUDA(cudaMemset(g_ctx.d_status, 0, sizeof(int)));
   g_ctx.launches = 0;
   g_ctx.ready = true;
   return BK_OK;
@@ -140,6 +142,12 @@ int32_t bkHostFree(void* p) {
 int32_t bkSync(void) {
   BK_REQUIRE_INIT();
   BK_CUDA(cudaStreamSynchronize(g_ctx.stream));
+  int st = 0;
+  BK_CUDA(cudaMemcpy(&st, g_ctx.d_status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (st != 0) {
+    cudaMemset(g_ctx.d_status, 0, sizeof(int));
+    return bk_fail(st, "bkSync: a kernel reported status %d (a bounded device-side wait gave up)", st);
+  }
   return BK_OK;
 }
 
@@ -174,6 +182,22 @@ int32_t bkEventElapsedMs(uint64_t start, uint64_t stop, float* out_ms) {
 int32_t bkEventDestroy(uint64_t event) {
   BK_REQUIRE_INIT();
   BK_CUDA(cudaEventDestroy((cudaEvent_t)(uintptr_t)event));
+  return BK_OK;
+}
+
+int32_t bkTraceEnable(uint64_t dev_buf, int32_t max_launches) {
+  BK_REQUIRE_INIT();
+  BK_ARG(dev_buf && max_launches > 0, "bkTraceEnable: bad arguments");
+  g_ctx.trace = bk_ptr<unsigned long long>(dev_buf);
+  g_ctx.trace_cap = max_launches;
+  g_ctx.trace_seq = 0;
+  return BK_OK;
+}
+
+int32_t bkTraceDisable(void) {
+  BK_REQUIRE_INIT();
+  g_ctx.trace = nullptr;
+  g_ctx.trace_cap = 0;
   return BK_OK;
 }
 

@@ -96,6 +96,8 @@ SIGNATURES = {
     "bkEventElapsedMs": (_I32, [_U64, _U64, C.POINTER(_F32)]),
     "bkEventDestroy": (_I32, [_U64]),
     "bkLaunchCount": (_I32, [_PU64]),
+    "bkTraceEnable": (_I32, [_U64, _I32]),
+    "bkTraceDisable": (_I32, []),
     "bkGemvQ4K": (_I32, [C.POINTER(bkGemvArgs)]),
     "bkGemvQ4KSimple": (_I32, [_U64, _I32, _I32, _U64, _I32, _U64]),
     "bkDequantQ4K": (_I32, [_U64, _I32, _I32, _U64]),

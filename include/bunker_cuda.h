@@ -72,6 +72,12 @@ BK_API int32_t bkEventRecord(uint64_t event);
 BK_API int32_t bkEventSync(uint64_t event);
 BK_API int32_t bkEventElapsedMs(uint64_t start, uint64_t stop, float* out_ms);
 BK_API int32_t bkEventDestroy(uint64_t event);
+/* Device-side timeline.  While enabled, every kernel launched (or captured into a graph) gets the next
+ * 64-byte record of dev_buf and thread 0 of its CTA 0 stamps %globaltimer (ns) into slots:
+ * 0 entry, 1 own weight copies issued, 2 dependency wait returned, 3 prologue done, 4 first weights landed, 5 exit.
+ * A graph replays the records it was captured with.  Off by default. */
+BK_API int32_t bkTraceEnable(uint64_t dev_buf, int32_t max_launches);
+BK_API int32_t bkTraceDisable(void);
 /* Number of kernels this library has launched since bkInit (graph replays count their kernels). */
 BK_API int32_t bkLaunchCount(uint64_t* out_count);
 
