@@ -32,10 +32,15 @@ BK_DEVINL float bk_bf16_to_f32(uint16_t h) { return __uint_as_float((uint32_t)h 
 // round-to-nearest-even, NaN kept quiet (MLIR arith.truncf semantics of the
 // reference's device casts, src/ttir.ts:846)
 BK_DEVINL uint16_t bk_f32_to_bf16(float f) {
-  uint32_t u = __float_as_uint(f);
-  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40u);
-  u += 0x7fffu + ((u >> 16) & 1u);
-  return (uint16_t)(u >> 16);
+  uint16_t h;
+  asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(h) : "f"(f));
+  return h;
+}
+// two values -> packed pair (lo in the low half), one instruction
+BK_DEVINL uint32_t bk_f32x2_to_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
 }
 
 // IEEE half -> float, subnormals kept (Q4_K superblock d / dmin)
@@ -149,6 +154,18 @@ BK_DEVINL void bk_q4k_scale_min(uint32_t w0, uint32_t w1, uint32_t w2, int j, in
     sc = (int)((b8 & 0x0fu) | ((b0 >> 6) << 4));
     mn = (int)((b8 >> 4) | ((b4 >> 6) << 4));
   }
+}
+
+// scales and mins of the two sub-blocks 2p, 2p+1 (p = 0..3) in one go, branch-free:
+// byte 0 of the results belongs to sub-block 2p, byte 1 to 2p+1
+BK_DEVINL void bk_q4k_scale_min_pair(uint32_t w0, uint32_t w1, uint32_t w2, int p, uint32_t& sc2, uint32_t& mn2) {
+  const int sh = (p & 1) * 16;
+  const uint32_t h0 = (w0 >> sh) & 0xffffu, h1 = (w1 >> sh) & 0xffffu, h2 = (w2 >> sh) & 0xffffu;
+  const uint32_t sc_lo = h0 & 0x3f3fu, mn_lo = h1 & 0x3f3fu;
+  const uint32_t sc_hi = (h2 & 0x0f0fu) | ((h0 >> 2) & 0x3030u);
+  const uint32_t mn_hi = ((h2 >> 4) & 0x0f0fu) | ((h1 >> 2) & 0x3030u);
+  sc2 = p >= 2 ? sc_hi : sc_lo;
+  mn2 = p >= 2 ? mn_hi : mn_lo;
 }
 
 BK_DEVINL int bk_dp4a(uint32_t a, uint32_t b, int c) {

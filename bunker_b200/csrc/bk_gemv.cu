@@ -98,12 +98,12 @@ __device__ __forceinline__ void quant_chunk(const float (&y)[8], int q, int b, i
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
   float d = __fdiv_rn(amax, 127.0f);
-  float dd = (d == 0.0f) ? 1.0f : d;
+  float id = (d == 0.0f) ? 1.0f : __fdiv_rn(1.0f, d);
   int qs[8];
   int qsum = 0;
 #pragma unroll
   for (int e = 0; e < 8; e++) {
-    int v = (int)floorf(__fadd_rn(__fdiv_rn(y[e], dd), 0.5f));
+    int v = __float2int_rd(fmaf(y[e], id, 0.5f));
     v = max(-128, min(127, v));
     qs[e] = v;
     qsum += v;
@@ -176,9 +176,12 @@ __device__ void prologue_bf16(const GemvParams& p, uint32_t* xs, float* d8s, flo
         float wv[8];
         load_chunk_bf16(p.norm_w, q, wv);
 #pragma unroll
-        for (int e = 0; e < 8; e++) {
-          float v = __fmul_rn(__fmul_rn(y[e], rstd), __fadd_rn(1.0f, wv[e]));
-          y[e] = bk_bf16_to_f32(bk_f32_to_bf16(v));
+        for (int e = 0; e < 8; e += 2) {
+          float v0 = __fmul_rn(__fmul_rn(y[e], rstd), __fadd_rn(1.0f, wv[e]));
+          float v1 = __fmul_rn(__fmul_rn(y[e + 1], rstd), __fadd_rn(1.0f, wv[e + 1]));
+          uint32_t pk = bk_f32x2_to_bf16x2(v0, v1);
+          y[e] = __uint_as_float(pk << 16);
+          y[e + 1] = __uint_as_float(pk & 0xffff0000u);
         }
       }
       quant_chunk(y, q, b, nunits, nblk, xs, d8s, s8s);
@@ -203,54 +206,75 @@ __device__ __forceinline__ RowRegs load_unit(const uint8_t* row, int u) {
   return r;
 }
 
-template <int B>
-__device__ __forceinline__ void unit_dot(const RowRegs& r, int u, const uint32_t* xs, const float* d8s,
-                                         const float* s8s, int nunits, int nblk, float (&acc)[B]) {
-  const int p = u & 3;
-  float d = bk_f16_to_f32((uint16_t)(r.hdr.x & 0xffffu));
-  float dmin = bk_f16_to_f32((uint16_t)(r.hdr.x >> 16));
-  int sc0, mn0, sc1, mn1;
-  bk_q4k_scale_min(r.hdr.y, r.hdr.z, r.hdr.w, 2 * p, sc0, mn0);
-  bk_q4k_scale_min(r.hdr.y, r.hdr.z, r.hdr.w, 2 * p + 1, sc1, mn1);
-  const uint32_t qw[8] = {r.qa.x, r.qa.y, r.qa.z, r.qa.w, r.qb.x, r.qb.y, r.qb.z, r.qb.w};
+// activation of one unit (two Q8_1 blocks) for one batch column
+struct XRegs {
+  uint4 x0, x1, x2, x3;
+  float2 d8, s8;
+};
+
+__device__ __forceinline__ XRegs load_x(const uint32_t* xs, const float* d8s, const float* s8s, int b, int u, int nunits,
+                                        int nblk) {
+  XRegs r;
+  const uint4* xv = reinterpret_cast<const uint4*>(xs + (b * nunits + u) * kUnitWords);
+  r.x0 = xv[0];
+  r.x1 = xv[1];
+  r.x2 = xv[2];
+  r.x3 = xv[3];
+  r.d8 = *reinterpret_cast<const float2*>(d8s + b * nblk + 2 * u);
+  r.s8 = *reinterpret_cast<const float2*>(s8s + b * nblk + 2 * u);
+  return r;
+}
+
+// weights of one unit, decoded once and shared by all batch columns
+struct WRegs {
   uint32_t lo[8], hi[8];
+  float d, dmin, fm0, fm1;
+  int sc0, sc1;
+};
+
+__device__ __forceinline__ WRegs decode_unit(const RowRegs& r, int p) {
+  WRegs w;
+  w.d = bk_f16_to_f32((uint16_t)(r.hdr.x & 0xffffu));
+  w.dmin = bk_f16_to_f32((uint16_t)(r.hdr.x >> 16));
+  uint32_t sc2, mn2;
+  bk_q4k_scale_min_pair(r.hdr.y, r.hdr.z, r.hdr.w, p, sc2, mn2);
+  w.sc0 = (int)(sc2 & 0xffu);
+  w.sc1 = (int)(sc2 >> 8);
+  w.fm0 = (float)(int)(mn2 & 0xffu);
+  w.fm1 = (float)(int)(mn2 >> 8);
+  const uint32_t qw[8] = {r.qa.x, r.qa.y, r.qa.z, r.qa.w, r.qb.x, r.qb.y, r.qb.z, r.qb.w};
 #pragma unroll
   for (int k = 0; k < 8; k++) {
-    lo[k] = qw[k] & 0x0f0f0f0fu;
-    hi[k] = (qw[k] >> 4) & 0x0f0f0f0fu;
+    w.lo[k] = qw[k] & 0x0f0f0f0fu;
+    w.hi[k] = (qw[k] >> 4) & 0x0f0f0f0fu;
   }
-  const float fm0 = (float)mn0, fm1 = (float)mn1;
-#pragma unroll
-  for (int b = 0; b < B; b++) {
-    const uint4* xv = reinterpret_cast<const uint4*>(xs + ((size_t)b * nunits + u) * kUnitWords);
-    uint4 x0 = xv[0], x1 = xv[1], x2 = xv[2], x3 = xv[3];
-    int i0 = 0, i1 = 0;
-    i0 = bk_dp4a(lo[0], x0.x, i0);
-    i0 = bk_dp4a(lo[1], x0.y, i0);
-    i0 = bk_dp4a(lo[2], x0.z, i0);
-    i0 = bk_dp4a(lo[3], x0.w, i0);
-    i0 = bk_dp4a(lo[4], x1.x, i0);
-    i0 = bk_dp4a(lo[5], x1.y, i0);
-    i0 = bk_dp4a(lo[6], x1.z, i0);
-    i0 = bk_dp4a(lo[7], x1.w, i0);
-    i1 = bk_dp4a(hi[0], x2.x, i1);
-    i1 = bk_dp4a(hi[1], x2.y, i1);
-    i1 = bk_dp4a(hi[2], x2.z, i1);
-    i1 = bk_dp4a(hi[3], x2.w, i1);
-    i1 = bk_dp4a(hi[4], x3.x, i1);
-    i1 = bk_dp4a(hi[5], x3.y, i1);
-    i1 = bk_dp4a(hi[6], x3.z, i1);
-    i1 = bk_dp4a(hi[7], x3.w, i1);
-    const float2 d8 = *reinterpret_cast<const float2*>(d8s + b * nblk + 2 * u);
-    const float2 s8 = *reinterpret_cast<const float2*>(s8s + b * nblk + 2 * u);
-    float accd = __fmul_rn(d8.x, (float)(sc0 * i0));
-    accd = fmaf(d8.y, (float)(sc1 * i1), accd);
-    float accm = __fmul_rn(s8.x, fm0);
-    accm = fmaf(s8.y, fm1, accm);
-    float t = __fmul_rn(dmin, accm);
-    float val = fmaf(d, accd, -t);
-    acc[b] = __fadd_rn(acc[b], val);
-  }
+  return w;
+}
+
+__device__ __forceinline__ float unit_val(const WRegs& w, const XRegs& x) {
+  int i0 = 0, i1 = 0;
+  i0 = bk_dp4a(w.lo[0], x.x0.x, i0);
+  i0 = bk_dp4a(w.lo[1], x.x0.y, i0);
+  i0 = bk_dp4a(w.lo[2], x.x0.z, i0);
+  i0 = bk_dp4a(w.lo[3], x.x0.w, i0);
+  i0 = bk_dp4a(w.lo[4], x.x1.x, i0);
+  i0 = bk_dp4a(w.lo[5], x.x1.y, i0);
+  i0 = bk_dp4a(w.lo[6], x.x1.z, i0);
+  i0 = bk_dp4a(w.lo[7], x.x1.w, i0);
+  i1 = bk_dp4a(w.hi[0], x.x2.x, i1);
+  i1 = bk_dp4a(w.hi[1], x.x2.y, i1);
+  i1 = bk_dp4a(w.hi[2], x.x2.z, i1);
+  i1 = bk_dp4a(w.hi[3], x.x2.w, i1);
+  i1 = bk_dp4a(w.hi[4], x.x3.x, i1);
+  i1 = bk_dp4a(w.hi[5], x.x3.y, i1);
+  i1 = bk_dp4a(w.hi[6], x.x3.z, i1);
+  i1 = bk_dp4a(w.hi[7], x.x3.w, i1);
+  float accd = __fmul_rn(x.d8.x, (float)(w.sc0 * i0));
+  accd = fmaf(x.d8.y, (float)(w.sc1 * i1), accd);
+  float accm = __fmul_rn(x.s8.x, w.fm0);
+  accm = fmaf(x.s8.y, w.fm1, accm);
+  const float t = __fmul_rn(w.dmin, accm);
+  return fmaf(w.d, accd, -t);
 }
 
 // ---- virtual rows --------------------------------------------------------------
@@ -434,18 +458,35 @@ __global__ void __launch_bounds__(512, ((B * G <= 16) ? 2 : 1)) gemv_q4k_kernel(
     const int nr = min(G, n_rows_cta - g * G);
     mbar_wait_bounded(bar_base + 8 * slot, parity, p.status);
     if (gi == 0) bk_stamp(p.trace, 4);
-    const uint8_t* wbase = slots + (size_t)slot * slot_bytes;
+    const uint8_t* wbase = slots + slot * slot_bytes;
     float acc[G][B];
 #pragma unroll
     for (int r = 0; r < G; r++)
 #pragma unroll
       for (int b = 0; b < B; b++) acc[r][b] = 0.0f;
     for (int u = lane; u < nunits; u += 32) {
+      const int pp = u & 3;
+      if constexpr (B <= 2) {
+        // few columns: the activation of this unit stays in registers across the G rows
+        XRegs xr[B];
 #pragma unroll
-      for (int r = 0; r < G; r++) {
-        if (r < nr) {
-          RowRegs rr = load_unit_smem(wbase + (size_t)r * rowb, u);
-          unit_dot<B>(rr, u, xs, d8s, s8s, nunits, nblk, acc[r]);
+        for (int b = 0; b < B; b++) xr[b] = load_x(xs, d8s, s8s, b, u, nunits, nblk);
+#pragma unroll
+        for (int r = 0; r < G; r++) {
+          if (r < nr) {
+            const WRegs w = decode_unit(load_unit_smem(wbase + r * rowb, u), pp);
+#pragma unroll
+            for (int b = 0; b < B; b++) acc[r][b] = __fadd_rn(acc[r][b], unit_val(w, xr[b]));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < G; r++) {
+          if (r < nr) {
+            const WRegs w = decode_unit(load_unit_smem(wbase + r * rowb, u), pp);
+#pragma unroll
+            for (int b = 0; b < B; b++) acc[r][b] = __fadd_rn(acc[r][b], unit_val(w, load_x(xs, d8s, s8s, b, u, nunits, nblk)));
+          }
         }
       }
     }
@@ -585,12 +626,12 @@ __global__ void quant_q8_1_kernel(const void* x, int K, int B, uint8_t* out) {
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
   float d = __fdiv_rn(amax, 127.0f);
-  float dd = (d == 0.0f) ? 1.0f : d;
+  float id = (d == 0.0f) ? 1.0f : __fdiv_rn(1.0f, d);
   int sum = 0;
   uint32_t w[2] = {0, 0};
 #pragma unroll
   for (int e = 0; e < 8; e++) {
-    int v = (int)floorf(__fadd_rn(__fdiv_rn(y[e], dd), 0.5f));
+    int v = __float2int_rd(fmaf(y[e], id, 0.5f));
     sum += v;  // the reference sums before clamping (bench/bench.ts:66-67)
     v = max(-128, min(127, v));
     w[e >> 2] |= (uint32_t)(v & 0xff) << (8 * (e & 3));

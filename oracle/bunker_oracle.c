@@ -82,7 +82,7 @@ ORC_API float orc_q8half_to_f32(uint16_t h) {
  * round-to-nearest-even (src/ttir.ts:846). */
 ORC_API uint16_t orc_f32_to_bf16(float f) {
   uint32_t u = f2u(f);
-  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40u);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return 0x7fffu; /* canonical NaN, as cvt.rn.bf16.f32 gives */
   u += 0x7fffu + ((u >> 16) & 1u);
   return (uint16_t)(u >> 16);
 }
@@ -269,8 +269,10 @@ ORC_API void orc_embed_q4k(const uint8_t* table, int H, const int32_t* ids, int 
 /* ------------------------------------------------------------------------ */
 /* packQ8_1, bench/bench.ts:53-72: d = amax/127, q = round-half-up(x/d)
  * clamped to [-128,127], s = (sum q)*d; both halves by truncation.  The JS
- * arithmetic is double; here it is f32 with IEEE division so the GPU can
- * reproduce it bit for bit. */
+ * arithmetic is double; here it is f32, and the quotient is taken as
+ * x * (1/d) with one fused multiply-add, q = floor(fma(x, 1/d, 0.5)), which is
+ * what the GPU computes (one IEEE division per block instead of 32).  The two
+ * forms differ only when x/d lies within an ulp of a half-integer. */
 ORC_API void orc_q8_1_quantize(const float* x, int K, uint8_t* out) {
   int nb = K / 32;
   for (int b = 0; b < nb; b++) {
@@ -281,11 +283,11 @@ ORC_API void orc_q8_1_quantize(const float* x, int K, uint8_t* out) {
       if (a > amax) amax = a;
     }
     float d = amax / 127.0f;
-    float dd = (d == 0.0f) ? 1.0f : d;
+    float id = (d == 0.0f) ? 1.0f : 1.0f / d;
     int32_t sum = 0;
     uint8_t* ob = out + (size_t)b * 36;
     for (int i = 0; i < 32; i++) {
-      float v = floorf(xb[i] / dd + 0.5f);
+      float v = floorf(fmaf(xb[i], id, 0.5f));
       int32_t q = (int32_t)v;
       sum += q; /* the reference sums before clamping (bench.ts:66-67) */
       if (q > 127) q = 127;

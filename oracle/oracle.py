@@ -63,8 +63,9 @@ def _c(a, dtype) -> np.ndarray:
 def f32_to_bf16(x: np.ndarray) -> np.ndarray:
     """Round-to-nearest-even f32 -> bf16 bit patterns (vectorised twin of orc_f32_to_bf16)."""
     u = _c(x, np.float32).view(np.uint32)
-    r = (u + (0x7FFF + ((u >> 16) & 1))) >> 16
-    return r.astype(np.uint16)
+    r = ((u + (0x7FFF + ((u >> 16) & 1))) >> 16).astype(np.uint16)
+    r[(u & 0x7FFFFFFF) > 0x7F800000] = 0x7FFF
+    return r
 
 
 def bf16_to_f32(h: np.ndarray) -> np.ndarray:
