@@ -520,3 +520,46 @@ int32_t bk_argmax_launch(uint64_t logits, int32_t V, int32_t B, uint64_t idx, ui
   BK_CHECK_LAUNCH();
   return BK_OK;
 }
+
+// ---- argmax for callers that may not allocate -----------------------------------------------------
+// bkArgmax needs a caller-provided scratch buffer (per-block partial results and a completion counter per
+// batch row).  Some hosts cannot provide one: a decode loop that was handed a fixed memory budget at
+// start-up and has spent it, code that runs where cudaMalloc is off limits (it synchronises the whole
+// device and is not permitted while a stream is being captured), or an embedding runtime that owns every
+// byte of device memory itself.  For them the scratch lives in the library image: a file-scope array of
+// kArgmaxStaticMaxB * 516 = 33,024 bytes that every GPU loading the library carries until the process
+// exits.  All calls share it and it keeps whatever the last call left, so the counters are cleared at the
+// start of every call, and two calls that overlap on the GPU would corrupt each other.
+constexpr int kArgmaxStaticMaxB = 64;
+static __device__ __align__(256) unsigned char g_argmax_static_scratch[kArgmaxStaticMaxB * (kArgmaxBlocks * 8 + 4)];
+
+extern "C" int32_t bkArgmaxStatic(uint64_t logits, int32_t V, int32_t B, uint64_t idx, uint64_t val) {
+  BK_REQUIRE_INIT();
+  BK_ARG(V > 0 && B > 0 && logits && idx && val, "bkArgmaxStatic: bad arguments");
+  BK_ARG(B <= kArgmaxStaticMaxB, "bkArgmaxStatic: B=%d exceeds the built-in scratch, which holds at most %d rows; use bkArgmax with your own scratch",
+         B, kArgmaxStaticMaxB);
+  // The array's name is only a host-side stand-in; the kernel needs its device address.  Looked up once per
+  // device, with that device current (the first call on a device does this, so make that call before any
+  // stream capture).
+  static unsigned char* dev_addr[64] = {nullptr};
+  const int dev = bk_ctx().device;
+  BK_ARG(dev >= 0 && dev < 64, "bkArgmaxStatic: device index %d out of range", dev);
+  if (!dev_addr[dev]) {
+    int cur = -1;
+    BK_CUDA(cudaGetDevice(&cur));
+    if (cur != dev) BK_CUDA(cudaSetDevice(dev));
+    void* p = nullptr;
+    BK_CUDA(cudaGetSymbolAddress(&p, g_argmax_static_scratch));
+    dev_addr[dev] = static_cast<unsigned char*>(p);
+  }
+  float* pv = reinterpret_cast<float*>(dev_addr[dev]);
+  int32_t* pi = reinterpret_cast<int32_t*>(pv + (size_t)B * kArgmaxBlocks);
+  unsigned int* cnt = reinterpret_cast<unsigned int*>(pi + (size_t)B * kArgmaxBlocks);
+  BK_CUDA(cudaMemsetAsync(cnt, 0, (size_t)B * sizeof(unsigned int), bk_ctx().stream));  // counters must start at zero
+  int blocks = (V + 2047) / 2048;
+  if (blocks > kArgmaxBlocks) blocks = kArgmaxBlocks;
+  BK_CUDA(bk_launch_pdl(argmax_kernel, dim3(blocks, B), dim3(256), 0, bk_ptr<float>(logits), V, bk_ptr<int32_t>(idx),
+                        bk_ptr<float>(val), pv, pi, cnt, (int32_t*)nullptr, (int32_t*)nullptr, 0, 0));
+  BK_CHECK_LAUNCH();
+  return BK_OK;
+}

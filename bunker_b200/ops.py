@@ -112,3 +112,9 @@ def argmax_scratch_bytes(B: int) -> int:
 def argmax(logits: int, V: int, B: int, idx: int, val: int, scratch: int) -> None:
     """scratch must have been zeroed once before its first use."""
     _check(cu().bkArgmax(logits, V, B, idx, val, scratch))
+
+
+def argmax_static(logits: int, V: int, B: int, idx: int, val: int) -> None:
+    """bkArgmax for callers that cannot allocate: the scratch is built into the library (B <= 64).
+    Calls share that scratch, so do not let two of them overlap on the GPU."""
+    _check(cu().bkArgmaxStatic(logits, V, B, idx, val))

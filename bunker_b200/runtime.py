@@ -116,6 +116,7 @@ SIGNATURES = {
     "bkAttnScratchBytes": (_U64, [_I32, _I32, _I32, _I32, _I32]),
     "bkArgmax": (_I32, [_U64, _I32, _I32, _U64, _U64, _U64]),
     "bkArgmaxScratchBytes": (_U64, [_I32]),
+    "bkArgmaxStatic": (_I32, [_U64, _I32, _I32, _U64, _U64]),
     "bkLaunch": (_I32, [_I32, _PU64, _I32]),
 }
 

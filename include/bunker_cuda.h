@@ -194,6 +194,13 @@ BK_API uint64_t bkAttnScratchBytes(int32_t B, int32_t Hq, int32_t HD, int32_t ma
  * logits f32 [B][V]; idx int32 [B]; val f32 [B]; scratch >= bkArgmaxScratchBytes(B) bytes */
 BK_API int32_t bkArgmax(uint64_t logits, int32_t V, int32_t B, uint64_t idx, uint64_t val, uint64_t scratch);
 BK_API uint64_t bkArgmaxScratchBytes(int32_t B);
+/* No counterpart in the reference.  Same result as bkArgmax for callers that cannot allocate device memory
+ * (a host with a fixed memory budget, code running where cudaMalloc is forbidden such as during stream
+ * capture, a runtime that owns all device memory): the scratch is a 33,024-byte array built into the
+ * library, enough for B <= 64; larger B is rejected with BK_ERR_ARG.  Nothing is allocated or freed.  The
+ * first call on a device looks up the array's device address, so make it before any stream capture.  All
+ * calls share the array: calls that overlap on the GPU race. */
+BK_API int32_t bkArgmaxStatic(uint64_t logits, int32_t V, int32_t B, uint64_t idx, uint64_t val);
 
 /* ---- whole decode step: replaces buildModelGraph + compileStep + runGraphDecode
  *      (src/model.ts:46-204, src/runner.ts:94-162) --------------------------------
