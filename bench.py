@@ -163,24 +163,29 @@ def run_ours(args):
     from bunker_b200 import model as M
     from bunker_b200 import runtime as R
 
-    if args.gpus != 1:
-        raise SystemExit("tensor-parallel bench path not built yet")
+    from bunker_b200 import dist
     K, W, B = args.steps, args.warmup, args.batch
+    rank, world = dist.init("nccl") if args.gpus > 1 else (0, 1)
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (launch with torch.distributed.run), found {world}")
+    local = dist.env_rank()[2] if world > 1 else 0
     cfg = make_config(K, W)
     weights = M.synth_weights(cfg)
-    R.cu(0)
-    gm = M.DecodeModel(cfg, weights, batch=B)
+    R.cu(local)
+    gm = M.DecodeModel(cfg, weights, batch=B, device=local, tp_rank=rank, tp_size=world)
     info = gm.info()
     prompt = np.random.default_rng(0xB0B0 + 3000).integers(0, cfg.vocab, (PROMPT_LEN, B)).astype(np.int32)
-    wbytes = M.weight_bytes(cfg)
+    wbytes = M.weight_bytes(cfg)          # whole model; every rank streams 1/world of it (plus the lm_head shard)
     hbm_peak, peak_src = load_peaks()
+    hbm_peak *= world
 
     # ---- resident leg: prompt, W warm-up steps, K timed graph replays with device-side token feedback ----
     for t in range(PROMPT_LEN):
         gm.step(prompt[t], read=False)
     gm.run(W)
-    assert R.cuSync() == 0
-    sampler = ClockSampler(0)
+    assert R.cuSync() == 0, R.last_error()
+    dist.barrier()
+    sampler = ClockSampler(local)
     e0, e1 = R.Event(), R.Event()
     l0 = R.launch_count()
     with sampler:
@@ -188,7 +193,9 @@ def run_ours(args):
         gm.run(K)
         e1.record()
         e1.synchronize()
-    ms = e0.elapsed_ms(e1)
+    assert R.cuSync() == 0, R.last_error()
+    dist.barrier()
+    ms = dist.max_over_ranks(e0.elapsed_ms(e1))
     launches = R.launch_count() - l0
     value = K * B / (ms * 1e-3)
     tokens_resident = gm.tokens(PROMPT_LEN + W, K)
@@ -226,17 +233,26 @@ def run_ours(args):
     e3.record()
     e3.synchronize()
     wall_ms = (time.perf_counter() - t0) * 1e3
-    e2e_ms = max(e2.elapsed_ms(e3), wall_ms)
+    e2e_ms = dist.max_over_ranks(max(e2.elapsed_ms(e3), wall_ms))
     same_stream = bool(np.array_equal(np.stack(toks), tokens_resident))
 
-    cpu_val, cpu_ms, cpu_sample = cpu_tokens_per_s(cfg, weights, B, steps=6, warmup=1, budget_s=30.0)
+    if rank != 0:
+        gm.destroy()
+        dist.shutdown()
+        return
+    if world == 1:
+        cpu_val, cpu_ms, cpu_sample = cpu_tokens_per_s(cfg, weights, B, steps=6, warmup=1, budget_s=30.0)
+        cpu = {"value": cpu_val, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port",
+               "sample": cpu_sample + "; 6 timed steps", "ms_per_step": cpu_ms}
+    else:
+        cpu = None   # reported at N=1 only
 
     line = {
-        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8xint4->int32, f32 accumulate", "data": "synthetic",
         "config": {"workload": f"configs[3] hybrid 24-layer Q4_K decode (hidden 2048, vocab 151936), batch {B}, "
-                               f"{PROMPT_LEN}-token random prompt then greedy", "batch": B, "parallelism": "tp1",
+                               f"{PROMPT_LEN}-token random prompt then greedy", "batch": B, "parallelism": f"tp{world}",
                    "inputs": "weights (1.12 GB/step) larger than L2, no flush", "max_len": cfg.max_len,
                    "attn_split_len": info["split_len"], "kernels_per_step": info["kernels_per_step"]},
         "clocks": sampler.summary(),
@@ -252,11 +268,11 @@ def run_ours(args):
                            "roofline_tok_s": hbm_peak * 1e9 / wbytes * B},
         "per_op_ms": {k: round(v[0], 5) for k, v in prof.items()},
         "per_op_calls": {k: v[1] for k, v in prof.items()},
-        "cpu_baseline": {"value": cpu_val, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port",
-                         "sample": cpu_sample + f"; {6} timed steps", "ms_per_step": cpu_ms},
+        "cpu_baseline": cpu,
     }
     print(json.dumps(line), flush=True)
     gm.destroy()
+    dist.shutdown()
 
 
 def main():

@@ -90,3 +90,10 @@ inline unsigned long long* bk_trace_slot() {
   if (!c.trace || c.trace_seq >= c.trace_cap) return nullptr;
   return c.trace + (size_t)(c.trace_seq++) * 8;
 }
+
+// tensor-parallel exchange (bk_comm.cu)
+uint64_t bk_comm_slot_ptr(uint64_t comm, int slot);
+int32_t bk_comm_allreduce_residual(uint64_t comm, int slot, int n, uint64_t residual, uint64_t out);
+int32_t bk_comm_argmax_merge(uint64_t comm, int slot, int B, uint64_t local_val, uint64_t local_idx, int offset, uint64_t idx,
+                             uint64_t val, uint64_t pos, uint64_t hist, int hist_ld, int hist_rows);
+int32_t bk_comm_info(uint64_t comm, int* rank, int* nranks);

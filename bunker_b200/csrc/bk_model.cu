@@ -50,6 +50,10 @@ struct Model {
   // derived, per rank
   int Hk = 0, Hv = 0, Hq = 0, Hkv = 0, Cw = 0, ZD = 0, QG = 0, KVD = 0, inter = 0, vocab_local = 0;
   int split_len = 0;
+  int vocab_offset = 0;   // first vocabulary row of this rank's lm_head shard
+  uint64_t comm = 0;      // tensor-parallel exchange (bk_comm.cu), 0 for a single GPU
+  int tp = 1, rank = 0;
+  uint64_t lval = 0, lidx = 0;  // per-rank argmax before the merge
   // device buffers
   std::vector<uint64_t> owned;
   uint64_t x[2] = {0, 0}, h1 = 0, qkv = 0, z = 0, a = 0, b = 0, attn_out = 0, qg = 0, kbuf = 0, vbuf = 0, act = 0;
@@ -92,7 +96,7 @@ inline uint64_t q4k_bytes(uint64_t n, uint64_t k) { return n * (k / 256) * 144; 
 // BUNKER_GPU_PROF=1 profiler (src/ttir.ts:352-417).  Classes index the ms/count arrays of
 // bkDecodeStepProfiled.
 enum ProfClass { PC_EMBED = 0, PC_GEMV_PROJ, PC_GDN, PC_ATTN, PC_GEMV_OUT, PC_GEMV_GATEUP, PC_GEMV_DOWN, PC_GEMV_LMHEAD,
-                 PC_ARGMAX, PC_COUNT };
+                 PC_ARGMAX, PC_EXCHANGE, PC_COUNT };
 
 struct Prof {
   bool on = false;
@@ -151,8 +155,14 @@ int32_t enqueue_step(Model& m, int parity) {
       PROF(PC_GDN, bkGdnStep(&ga));
       memset(&g, 0, sizeof(g));
       g.K = m.ZD; g.B = B; g.prologue = BK_PRO_BF16; g.x = m.attn_out; g.n_segs = 1;
-      g.segs[0] = bkGemvSeg{L.out_proj, 0, m.h1, m.x[cur], H, BK_EPI_ADD_BF16, H, 0};
-      PROF(PC_GEMV_OUT, bk_gemv_launch(g));
+      if (m.tp == 1) {
+        g.segs[0] = bkGemvSeg{L.out_proj, 0, m.h1, m.x[cur], H, BK_EPI_ADD_BF16, H, 0};
+        PROF(PC_GEMV_OUT, bk_gemv_launch(g));
+      } else {
+        g.segs[0] = bkGemvSeg{L.out_proj, 0, bk_comm_slot_ptr(m.comm, 0), 0, H, BK_EPI_F32, H, 0};
+        PROF(PC_GEMV_OUT, bk_gemv_launch(g));
+        PROF(PC_EXCHANGE, bk_comm_allreduce_residual(m.comm, 0, B * H, m.x[cur], m.h1));
+      }
     } else {
       memset(&g, 0, sizeof(g));
       g.K = H; g.B = B; g.prologue = BK_PRO_RMSNORM; g.x = m.x[cur]; g.norm_w = L.in_ln; g.eps = c.eps;
@@ -172,8 +182,14 @@ int32_t enqueue_step(Model& m, int parity) {
       PROF(PC_ATTN, bkAttnDecode(&aa));
       memset(&g, 0, sizeof(g));
       g.K = m.Hq * c.head_dim; g.B = B; g.prologue = BK_PRO_BF16; g.x = m.attn_out; g.n_segs = 1;
-      g.segs[0] = bkGemvSeg{L.o, 0, m.h1, m.x[cur], H, BK_EPI_ADD_BF16, H, 0};
-      PROF(PC_GEMV_OUT, bk_gemv_launch(g));
+      if (m.tp == 1) {
+        g.segs[0] = bkGemvSeg{L.o, 0, m.h1, m.x[cur], H, BK_EPI_ADD_BF16, H, 0};
+        PROF(PC_GEMV_OUT, bk_gemv_launch(g));
+      } else {
+        g.segs[0] = bkGemvSeg{L.o, 0, bk_comm_slot_ptr(m.comm, 0), 0, H, BK_EPI_F32, H, 0};
+        PROF(PC_GEMV_OUT, bk_gemv_launch(g));
+        PROF(PC_EXCHANGE, bk_comm_allreduce_residual(m.comm, 0, B * H, m.x[cur], m.h1));
+      }
     }
     memset(&g, 0, sizeof(g));
     g.K = H; g.B = B; g.prologue = BK_PRO_RMSNORM; g.x = m.h1; g.norm_w = L.post_ln; g.eps = c.eps; g.n_segs = 1;
@@ -181,16 +197,28 @@ int32_t enqueue_step(Model& m, int parity) {
     PROF(PC_GEMV_GATEUP, bk_gemv_launch(g));
     memset(&g, 0, sizeof(g));
     g.K = m.inter; g.B = B; g.prologue = BK_PRO_BF16; g.x = m.act; g.n_segs = 1;
-    g.segs[0] = bkGemvSeg{L.down, 0, m.x[cur ^ 1], m.h1, H, BK_EPI_ADD_BF16, H, 0};
-    PROF(PC_GEMV_DOWN, bk_gemv_launch(g));
+    if (m.tp == 1) {
+      g.segs[0] = bkGemvSeg{L.down, 0, m.x[cur ^ 1], m.h1, H, BK_EPI_ADD_BF16, H, 0};
+      PROF(PC_GEMV_DOWN, bk_gemv_launch(g));
+    } else {
+      g.segs[0] = bkGemvSeg{L.down, 0, bk_comm_slot_ptr(m.comm, 1), 0, H, BK_EPI_F32, H, 0};
+      PROF(PC_GEMV_DOWN, bk_gemv_launch(g));
+      PROF(PC_EXCHANGE, bk_comm_allreduce_residual(m.comm, 1, B * H, m.h1, m.x[cur ^ 1]));
+    }
     cur ^= 1;
   }
   bkGemvArgs g;
   memset(&g, 0, sizeof(g));
   g.K = H; g.B = B; g.prologue = BK_PRO_RMSNORM; g.x = m.x[cur]; g.norm_w = m.final_norm; g.eps = c.eps; g.n_segs = 1;
-  g.segs[0] = bkGemvSeg{m.embed, 0, m.logits, 0, m.vocab_local, BK_EPI_F32, m.vocab_local, 0};
+  g.segs[0] = bkGemvSeg{m.embed + (uint64_t)m.vocab_offset * (H / 256) * 144, 0, m.logits, 0, m.vocab_local, BK_EPI_F32,
+                        m.vocab_local, 0};
   PROF(PC_GEMV_LMHEAD, bk_gemv_launch(g));
-  PROF(PC_ARGMAX, bk_argmax_launch(m.logits, m.vocab_local, B, m.ids, m.val, m.argmax_scratch, m.pos, m.hist, B, c.max_len));
+  if (m.tp == 1) {
+    PROF(PC_ARGMAX, bk_argmax_launch(m.logits, m.vocab_local, B, m.ids, m.val, m.argmax_scratch, m.pos, m.hist, B, c.max_len));
+  } else {
+    PROF(PC_ARGMAX, bk_argmax_launch(m.logits, m.vocab_local, B, m.lidx, m.lval, m.argmax_scratch, 0, 0, 0, 0));
+    PROF(PC_EXCHANGE, bk_comm_argmax_merge(m.comm, 2, B, m.lval, m.lidx, m.vocab_offset, m.ids, m.val, m.pos, m.hist, B, c.max_len));
+  }
   return BK_OK;
 }
 
@@ -257,10 +285,20 @@ int32_t bkModelCreate(const bkModelConfig* cfg, uint64_t* out_model) {
   BK_ARG(c.batch >= 1 && c.batch <= 8, "bkModelCreate: batch=%d outside 1..8", c.batch);
   BK_ARG(c.max_len >= 1, "bkModelCreate: max_len=%d", c.max_len);
   BK_ARG(c.vocab > 0, "bkModelCreate: vocab=%d", c.vocab);
-  BK_ARG(c.tp_size == 1 && c.tp_rank == 0, "bkModelCreate: tensor parallelism is configured through bkCommInit (tp_size must be 1 here)");
+  BK_ARG(c.tp_size >= 1 && c.tp_size <= 8 && c.tp_rank >= 0 && c.tp_rank < c.tp_size, "bkModelCreate: tp rank %d of %d", c.tp_rank, c.tp_size);
+  if (c.tp_size > 1) {
+    const int n = c.tp_size;
+    BK_ARG(c.gdn_k_heads % n == 0 && c.gdn_v_heads % n == 0 && c.attn_q_heads % n == 0,
+           "bkModelCreate: head counts (%d,%d,%d) are not divisible by tp_size=%d", c.gdn_k_heads, c.gdn_v_heads, c.attn_q_heads, n);
+    BK_ARG(c.attn_kv_heads % n == 0 || n % c.attn_kv_heads == 0, "bkModelCreate: %d KV heads cannot be split or replicated over %d ranks",
+           c.attn_kv_heads, n);
+    BK_ARG(c.intermediate / 256 >= n, "bkModelCreate: intermediate=%d has fewer superblocks than ranks", c.intermediate);
+  }
   Model* m = new Model();
   m->cfg = c;
   m->B = c.batch;
+  m->tp = c.tp_size;
+  m->rank = c.tp_rank;
   *out_model = (uint64_t)(uintptr_t)m;
   return BK_OK;
 }
@@ -274,6 +312,15 @@ int32_t bkModelSetTensor(uint64_t model, const char* name, uint64_t dev_ptr, uin
   return BK_OK;
 }
 
+int32_t bkModelSetComm(uint64_t model, uint64_t comm) {
+  BK_REQUIRE_INIT();
+  BK_ARG(model && comm, "bkModelSetComm: null argument");
+  Model* m = as_model(model);
+  BK_ARG(!m->finalized, "bkModelSetComm: model is already finalized");
+  m->comm = comm;
+  return BK_OK;
+}
+
 int32_t bkModelFinalize(uint64_t model) {
   BK_REQUIRE_INIT();
   BK_ARG(model, "bkModelFinalize: null model");
@@ -281,9 +328,25 @@ int32_t bkModelFinalize(uint64_t model) {
   if (m.finalized) return BK_OK;
   const bkModelConfig& c = m.cfg;
   const int H = c.hidden, B = m.B;
-  m.Hk = c.gdn_k_heads; m.Hv = c.gdn_v_heads; m.Hq = c.attn_q_heads; m.Hkv = c.attn_kv_heads;
+  // per-rank shard shapes: heads split evenly, KV heads split or replicated, FFN and vocabulary rows split with the
+  // remainder going to the lowest ranks (FFN in whole 256-column superblocks)
+  const int n = m.tp, r = m.rank;
+  if (n > 1) {
+    BK_ARG(m.comm != 0, "bkModelFinalize: tp_size=%d needs a communicator (bkModelSetComm)", n);
+    int cr = -1, cn = -1;
+    TRY(bk_comm_info(m.comm, &cr, &cn));
+    BK_ARG(cr == r && cn == n, "bkModelFinalize: communicator is rank %d of %d, model is rank %d of %d", cr, cn, r, n);
+  }
+  m.Hk = c.gdn_k_heads / n; m.Hv = c.gdn_v_heads / n; m.Hq = c.attn_q_heads / n;
+  m.Hkv = c.attn_kv_heads >= n ? c.attn_kv_heads / n : 1;
   m.Cw = 2 * m.Hk * 128 + m.Hv * 128; m.ZD = m.Hv * 128; m.QG = m.Hq * 2 * c.head_dim; m.KVD = m.Hkv * c.head_dim;
-  m.inter = c.intermediate; m.vocab_local = c.vocab;
+  {
+    const int nsb = c.intermediate / 256;
+    m.inter = (nsb / n + (r < nsb % n ? 1 : 0)) * 256;
+    const int vb = c.vocab / n, ve = c.vocab % n;
+    m.vocab_local = vb + (r < ve ? 1 : 0);
+    m.vocab_offset = r * vb + (r < ve ? r : ve);
+  }
   TRY(need(m, "embed.weight", q4k_bytes(c.vocab, H), &m.embed));
   TRY(need(m, "final.norm.weight", (uint64_t)H * 2, &m.final_norm));
   m.layers.resize(c.n_layers);
@@ -339,6 +402,8 @@ int32_t bkModelFinalize(uint64_t model) {
   TRY(dev_alloc(m, (size_t)B * m.vocab_local * 4, &m.logits));
   TRY(dev_alloc(m, (size_t)B * 4, &m.ids));
   TRY(dev_alloc(m, (size_t)B * 4, &m.val));
+  TRY(dev_alloc(m, (size_t)B * 4, &m.lval));
+  TRY(dev_alloc(m, (size_t)B * 4, &m.lidx));
   TRY(dev_alloc(m, (size_t)B * 4, &m.pos));
   TRY(dev_alloc(m, (size_t)c.max_len * B * 4, &m.hist));
   TRY(dev_alloc(m, bkArgmaxScratchBytes(B), &m.argmax_scratch));

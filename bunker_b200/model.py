@@ -143,13 +143,100 @@ def synth_weights(cfg: ModelConfig, seed: int = 3) -> dict[str, np.ndarray]:
 bkModelConfig = R.bkModelConfig
 
 
+def split_counts(total: int, n: int) -> list[int]:
+    """total items over n ranks, the remainder to the lowest ranks (the rule the library applies to FFN
+    superblocks and vocabulary rows)."""
+    base, extra = divmod(total, n)
+    return [base + (1 if r < extra else 0) for r in range(n)]
+
+
+def local_dims(cfg: ModelConfig, rank: int, n: int) -> dict:
+    """Shard shapes of one tensor-parallel rank (heads per rank, KV heads split or replicated,
+    row-parallel K slices in whole superblocks)."""
+    assert cfg.gdn_k_heads % n == 0 and cfg.gdn_v_heads % n == 0 and cfg.attn_q_heads % n == 0
+    hkv = cfg.attn_kv_heads
+    assert hkv % n == 0 or n % hkv == 0
+    hq_l = cfg.attn_q_heads // n
+    if hkv >= n:
+        kv_l, kv0 = hkv // n, rank * (hkv // n)
+    else:
+        kv_l, kv0 = 1, (rank * hq_l) // (cfg.attn_q_heads // hkv)
+    sb = split_counts(cfg.intermediate // 256, n)
+    vr = split_counts(cfg.vocab, n)
+    return {"Hk": cfg.gdn_k_heads // n, "Hv": cfg.gdn_v_heads // n, "Hq": hq_l, "Hkv": kv_l, "kv0": kv0,
+            "inter": sb[rank] * 256, "inter_off": sum(sb[:rank]) * 256, "vocab": vr[rank], "vocab_off": sum(vr[:rank])}
+
+
+def _q4k_rows(W: np.ndarray, rows) -> np.ndarray:
+    return np.ascontiguousarray(W[rows])
+
+
+def _q4k_kslice(W: np.ndarray, K: int, k0: int, k1: int) -> np.ndarray:
+    N = W.shape[0]
+    W3 = W.reshape(N, K // 256, 144)
+    return np.ascontiguousarray(W3[:, k0 // 256:k1 // 256]).reshape(N, -1)
+
+
+def shard_weights(cfg: ModelConfig, weights: dict[str, np.ndarray], rank: int, n: int) -> dict[str, np.ndarray]:
+    """The tensors rank `rank` of `n` registers.  Column-parallel: qkv/z/a/b (rows of the rank's key and value heads),
+    q/k/v (rows of its query heads and their KV head), gate/up (its FFN rows).  Row-parallel: out_proj, o_proj, down
+    (all rows, the rank's K slice).  Norm weights and the embedding table are replicated."""
+    if n == 1:
+        return weights
+    d = local_dims(cfg, rank, n)
+    H, D, HD = cfg.hidden, 128, cfg.head_dim
+    keydim = cfg.gdn_k_heads * D
+    hk = np.arange(rank * d["Hk"] * D, (rank + 1) * d["Hk"] * D)
+    hv = np.arange(rank * d["Hv"] * D, (rank + 1) * d["Hv"] * D)
+    chan = np.concatenate([hk, keydim + hk, 2 * keydim + hv])
+    vh = np.arange(rank * d["Hv"], (rank + 1) * d["Hv"])
+    out: dict[str, np.ndarray] = {}
+    for name, kind, shape in tensor_specs(cfg):
+        w = weights[name]
+        if name.endswith("in_proj_qkv.weight") or name.endswith("conv1d.weight"):
+            out[name] = _q4k_rows(w, chan)
+        elif name.endswith("in_proj_z.weight"):
+            out[name] = _q4k_rows(w, hv)
+        elif name.endswith(("in_proj_a.weight", "in_proj_b.weight", "A_log", "dt_bias")):
+            out[name] = _q4k_rows(w, vh)
+        elif name.endswith("linear_attn.out_proj.weight"):
+            out[name] = _q4k_kslice(w, cfg.z_dim, rank * d["Hv"] * D, (rank + 1) * d["Hv"] * D)
+        elif name.endswith("q_proj.weight"):
+            out[name] = _q4k_rows(w, np.arange(rank * d["Hq"] * 2 * HD, (rank + 1) * d["Hq"] * 2 * HD))
+        elif name.endswith(("k_proj.weight", "v_proj.weight")):
+            out[name] = _q4k_rows(w, np.arange(d["kv0"] * HD, (d["kv0"] + d["Hkv"]) * HD))
+        elif name.endswith("o_proj.weight"):
+            out[name] = _q4k_kslice(w, cfg.attn_q_heads * HD, rank * d["Hq"] * HD, (rank + 1) * d["Hq"] * HD)
+        elif name.endswith(("gate_proj.weight", "up_proj.weight")):
+            out[name] = _q4k_rows(w, np.arange(d["inter_off"], d["inter_off"] + d["inter"]))
+        elif name.endswith("down_proj.weight"):
+            out[name] = _q4k_kslice(w, cfg.intermediate, d["inter_off"], d["inter_off"] + d["inter"])
+        else:
+            out[name] = w
+    return out
+
+
 class DecodeModel:
     """Weights on the device + the library's step graph.  `weights` maps tensor names to numpy arrays."""
 
-    def __init__(self, cfg: ModelConfig, weights: dict[str, np.ndarray], batch: int = 1, device: int = 0):
-        self.cfg, self.batch = cfg, batch
+    def __init__(self, cfg: ModelConfig, weights: dict[str, np.ndarray], batch: int = 1, device: int = 0,
+                 tp_rank: int = 0, tp_size: int = 1):
+        """`weights` holds the FULL tensors; with tp_size > 1 this rank's shard is cut here and the ranks rendezvous
+        through bunker_b200.dist (torch.distributed must already be initialised)."""
+        self.cfg, self.batch, self.tp_rank, self.tp_size = cfg, batch, tp_rank, tp_size
         lib = R.cu(device)
         specs = tensor_specs(cfg)
+        weights = shard_weights(cfg, weights, tp_rank, tp_size)
+        self.comm = 0
+        if tp_size > 1:
+            from . import dist
+            h = C.c_uint64(0)
+            R._check(lib.bkCommCreate(tp_rank, tp_size, batch * cfg.hidden * 4, C.byref(h)))
+            self.comm = h.value
+            mine = (C.c_uint8 * 64)()
+            R._check(lib.bkCommExportHandle(self.comm, mine))
+            allh = b"".join(dist.all_gather_bytes(bytes(mine)))
+            R._check(lib.bkCommImportPeers(self.comm, (C.c_uint8 * len(allh)).from_buffer_copy(allh)))
         # one slab, addressed by offset (prototypes/decode.ts:64-75), 256-byte aligned tensors
         offs, total = {}, 0
         for name, _, _ in specs:
@@ -163,13 +250,20 @@ class DecodeModel:
                           vocab=cfg.vocab, gdn_k_heads=cfg.gdn_k_heads, gdn_v_heads=cfg.gdn_v_heads,
                           attn_q_heads=cfg.attn_q_heads, attn_kv_heads=cfg.attn_kv_heads, head_dim=cfg.head_dim,
                           rot_dim=cfg.rot_dim, intermediate=cfg.intermediate, max_len=cfg.max_len, batch=batch,
-                          tp_rank=0, tp_size=1, eps=cfg.eps, rope_theta=cfg.rope_theta)
+                          tp_rank=tp_rank, tp_size=tp_size, eps=cfg.eps, rope_theta=cfg.rope_theta)
         h = C.c_uint64(0)
         R._check(lib.bkModelCreate(C.byref(c), C.byref(h)))
         self.handle = h.value
         for name, _, _ in specs:
             R._check(lib.bkModelSetTensor(self.handle, name.encode(), self.slab.ptr + offs[name], weights[name].nbytes))
+        if tp_size > 1:
+            from . import dist
+            R._check(lib.bkModelSetComm(self.handle, self.comm))
+            assert R.cuSync() == 0
+            dist.barrier()       # finalize runs one step that exchanges with the peers: enter it together
         R._check(lib.bkModelFinalize(self.handle))
+        if tp_size > 1:
+            dist.barrier()
         self._ids = (C.c_int32 * batch)()
         self._out = (C.c_int32 * batch)()
         self._val = (C.c_float * batch)()
@@ -180,7 +274,14 @@ class DecodeModel:
         return {"split_len": sl.value, "attn_warps": w.value, "kernels_per_step": k.value, "steps": st.value}
 
     def reset(self) -> None:
+        if self.tp_size > 1:
+            from . import dist
+            assert R.cuSync() == 0
+            dist.barrier()
         R._check(R.cu().bkModelReset(self.handle))
+        if self.tp_size > 1:
+            assert R.cuSync() == 0
+            dist.barrier()
 
     def step(self, tokens: Iterable[int] | None = None, read: bool = True):
         """One token per sequence.  tokens=None feeds back the previous argmax on the device."""
@@ -199,7 +300,7 @@ class DecodeModel:
         R._check(R.cu().bkDecodeRun(self.handle, n_steps))
 
     PROFILE_CLASSES = ("embed", "gemv_proj", "gdn", "attn", "gemv_out", "gemv_gateup", "gemv_down", "gemv_lmhead",
-                       "argmax")
+                       "argmax", "exchange")
 
     def step_profiled(self) -> dict[str, tuple[float, int]]:
         """One eager step (device token feedback) with an event pair around every op: {class: (ms, calls)}."""
@@ -219,7 +320,8 @@ class DecodeModel:
         return p.value
 
     def logits(self) -> np.ndarray:
-        out = np.empty((self.batch, self.cfg.vocab), np.float32)
+        """f32 [B, rows of this rank's lm_head shard] (the whole vocabulary on a single GPU)."""
+        out = np.empty((self.batch, local_dims(self.cfg, self.tp_rank, self.tp_size)["vocab"]), np.float32)
         R.cuDtoH(out, self.buffer("logits"))
         return out
 
@@ -228,6 +330,12 @@ class DecodeModel:
             R._check(R.cu().bkModelDestroy(self.handle))
             self.handle = 0
             self.slab.free()
+            if self.comm:
+                from . import dist
+                assert R.cuSync() == 0
+                dist.barrier()   # nobody unmaps a buffer a peer may still read
+                R._check(R.cu().bkCommDestroy(self.comm))
+                self.comm = 0
 
 
 def runGraphDecode(model: DecodeModel, prompt: np.ndarray, gen_len: int,

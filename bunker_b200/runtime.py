@@ -118,11 +118,17 @@ SIGNATURES = {
     "bkArgmaxScratchBytes": (_U64, [_I32]),
     "bkArgmaxStatic": (_I32, [_U64, _I32, _I32, _U64, _U64]),
     "bkLaunch": (_I32, [_I32, _PU64, _I32]),
+    "bkCommCreate": (_I32, [_I32, _I32, _U64, _PU64]),
+    "bkCommExportHandle": (_I32, [_U64, C.POINTER(C.c_uint8)]),
+    "bkCommImportPeers": (_I32, [_U64, C.POINTER(C.c_uint8)]),
+    "bkCommDestroy": (_I32, [_U64]),
+    "bkCommAllReduceResidual": (_I32, [_U64, _I32, _U64, _I32, _U64, _U64]),
 }
 
 _MODEL_SIGS = {
     "bkModelCreate": (C.c_int32, [C.POINTER(bkModelConfig), C.POINTER(C.c_uint64)]),
     "bkModelSetTensor": (C.c_int32, [C.c_uint64, C.c_char_p, C.c_uint64, C.c_uint64]),
+    "bkModelSetComm": (C.c_int32, [C.c_uint64, C.c_uint64]),
     "bkModelFinalize": (C.c_int32, [C.c_uint64]),
     "bkModelReset": (C.c_int32, [C.c_uint64]),
     "bkDecodeStep": (C.c_int32, [C.c_uint64, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_float)]),

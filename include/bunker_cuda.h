@@ -231,7 +231,14 @@ BK_API int32_t bkModelCreate(const bkModelConfig* cfg, uint64_t* out_model);
  * (src/model.ts:72-196): "embed.weight", "final.norm.weight", "model.layers.N.input_layernorm.weight",
  * "...linear_attn.in_proj_qkv.weight" and so on.  Linear weights are Q4_K rows. */
 BK_API int32_t bkModelSetTensor(uint64_t model, const char* name, uint64_t dev_ptr, uint64_t bytes);
-/* Checks the tensor set, allocates state and activations, captures the step graphs. */
+/* Tensor parallelism (tp_size > 1): give the model its exchange object before bkModelFinalize.  Each rank registers
+ * only its shard of every weight: column-parallel matrices keep the rows of the rank's heads / FFN columns /
+ * vocabulary rows, row-parallel matrices (out_proj, o_proj, down_proj) keep all rows and the rank's K slice; the
+ * embedding table is registered whole (replicated).  Shard shapes are derived from the config by the rule in
+ * bunker_b200/model.py `shard_weights`. */
+BK_API int32_t bkModelSetComm(uint64_t model, uint64_t comm);
+/* Checks the tensor set, allocates state and activations, captures the step graphs.  With tp_size > 1 every rank
+ * must call it at about the same time: it runs one step, which exchanges with the peers. */
 BK_API int32_t bkModelFinalize(uint64_t model);
 /* Zero the recurrent state, conv state, KV cache and position. */
 BK_API int32_t bkModelReset(uint64_t model);
@@ -242,8 +249,9 @@ BK_API int32_t bkDecodeStep(uint64_t model, const int32_t* tokens, int32_t* out_
 /* n_steps greedy steps with device-side token feedback and no host traffic. */
 BK_API int32_t bkDecodeRun(uint64_t model, int32_t n_steps);
 /* One eagerly launched step with a CUDA-event pair around every op (the BUNKER_GPU_PROF=1 profiler of
- * src/ttir.ts:352-417).  ms_out/count_out[n_classes >= 9]: 0 embed, 1 projection GEMV (qkv|z|a|b, q|k|v),
- * 2 conv1d+GDN, 3 attention (2 kernels per call), 4 out/o_proj GEMV, 5 gate|up GEMV, 6 down GEMV, 7 lm_head GEMV, 8 argmax. */
+ * src/ttir.ts:352-417).  ms_out/count_out[n_classes >= 10]: 0 embed, 1 projection GEMV (qkv|z|a|b, q|k|v),
+ * 2 conv1d+GDN, 3 attention (2 kernels per call), 4 out/o_proj GEMV, 5 gate|up GEMV, 6 down GEMV, 7 lm_head GEMV, 8 argmax,
+ * 9 tensor-parallel exchanges. */
 BK_API int32_t bkDecodeStepProfiled(uint64_t model, float* ms_out, int32_t* count_out, int32_t n_classes);
 /* Tokens produced by steps [first_step, first_step+n_steps): out[n_steps][B] host ints. */
 BK_API int32_t bkModelTokens(uint64_t model, int32_t first_step, int32_t n_steps, int32_t* out);
@@ -252,6 +260,19 @@ BK_API int32_t bkModelInfo(uint64_t model, int32_t* split_len, int32_t* attn_war
 /* Device address of an internal buffer: "logits" f32 [B][vocab], "ids", "pos", "x0", "x1". */
 BK_API int32_t bkModelBuffer(uint64_t model, const char* name, uint64_t* out_ptr);
 BK_API int32_t bkModelDestroy(uint64_t model);
+
+/* ---- tensor-parallel exchange over NVLink peer memory (no counterpart in the reference, which is single-GPU) ----
+ * One process per GPU.  Each rank creates a communicator, exports its 64-byte IPC handle, the host gathers the handles
+ * of all ranks in rank order (nranks x 64 bytes) and hands them to bkCommImportPeers.  payload_bytes must hold the largest
+ * exchanged vector: batch x hidden x 4. */
+BK_API int32_t bkCommCreate(int32_t rank, int32_t nranks, uint64_t payload_bytes, uint64_t* out_comm);
+BK_API int32_t bkCommExportHandle(uint64_t comm, uint8_t* out_handle64);
+BK_API int32_t bkCommImportPeers(uint64_t comm, const uint8_t* handles);
+BK_API int32_t bkCommDestroy(uint64_t comm);
+/* out bf16[n] = (partials of all ranks summed in rank order) + residual; every rank calls it with the same slot (0..2)
+ * and n; consecutive calls must use different slots. */
+BK_API int32_t bkCommAllReduceResidual(uint64_t comm, int32_t slot, uint64_t partial_f32, int32_t n, uint64_t residual_bf16,
+                                       uint64_t out_bf16);
 
 /* cuLaunch-shaped entry (src/ttir.ts:321-348): op id + 8-byte argument slots.
  * Slot lists per op are documented in INTEGRATION.md. */
