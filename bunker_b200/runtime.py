@@ -171,14 +171,16 @@ def _check(rc: int) -> None:
 _initialised_device = None
 
 
-def cu(device: int = 0) -> C.CDLL:
-    """Open the library and create the context (src/ttir.ts:223-261 ``cu()``)."""
+def cu(device: int | None = None) -> C.CDLL:
+    """Open the library and create the context (src/ttir.ts:223-261 ``cu()``).  The first call picks the device
+    (0 unless given); later calls return the same context and reject a different device."""
     global _initialised_device
     lib = load_library()
     if _initialised_device is None:
-        _check(lib.bkInit(device))
-        _initialised_device = device
-    elif _initialised_device != device:
+        dev = 0 if device is None else int(device)
+        _check(lib.bkInit(dev))
+        _initialised_device = dev
+    elif device is not None and _initialised_device != device:
         raise BunkerCudaError(BK_ERR_STATE, f"context already on device {_initialised_device}")
     return lib
 
