@@ -56,6 +56,7 @@ struct GemvParams {
   int rows_per_cta;
   int n_slots;       // weight slots (and mbarriers) per CTA
   int depth;         // 0: one slot per group, all requested up front; >0: per-warp ring of this depth
+  int group_rows;    // rows one warp processes together (even when a SwiGLU segment is present)
   const void* x;
   const uint16_t* norm_w;
   float eps;
@@ -140,18 +141,27 @@ __device__ __forceinline__ void load_chunk_bf16(const uint16_t* row, int q, floa
 // bf16 rows -> (optional RMSNorm -> bf16) -> Q8_1 in shared memory.
 // Sum of squares in the 256-thread block order: chunk q (8 elements) belongs to
 // thread q mod 256, fmaf chain inside; warp butterflies; the 8 warp sums in order.
+// wpre: the norm weights of chunk threadIdx.x, loaded by the caller before the dependency wait.
 template <int B, bool NORM>
-__device__ void prologue_bf16(const GemvParams& p, uint32_t* xs, float* d8s, float* s8s, float* red) {
+__device__ void prologue_bf16(const GemvParams& p, uint32_t* xs, float* d8s, float* s8s, float* red, const uint4 wpre) {
   const int K = p.K, nblk = K / 32, nunits = K / 64, nchunk = K / 8;
   const uint16_t* x = reinterpret_cast<const uint16_t*>(p.x);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const bool one_pass = nchunk <= kThreads;   // every chunk has its own thread among the first 256: keep it in registers
   for (int b = 0; b < B; b++) {
     const uint16_t* row = x + (size_t)b * K;
     float rstd = 1.0f;
+    float y0[8];
+    const bool have0 = (int)threadIdx.x < nchunk;
+    if (have0) load_chunk_bf16(row, threadIdx.x, y0);
     if (NORM) {
       float acc = 0.0f;
       if (threadIdx.x < kThreads) {  // the fixed 256-thread order, whatever the CTA size
-        for (int q = threadIdx.x; q < nchunk; q += kThreads) {
+        if (have0) {
+#pragma unroll
+          for (int e = 0; e < 8; e++) acc = fmaf(y0[e], y0[e], acc);
+        }
+        for (int q = threadIdx.x + kThreads; q < nchunk; q += kThreads) {
           float y[8];
           load_chunk_bf16(row, q, y);
 #pragma unroll
@@ -167,14 +177,25 @@ __device__ void prologue_bf16(const GemvParams& p, uint32_t* xs, float* d8s, flo
       for (int w = 1; w < kWarps; w++) total = __fadd_rn(total, red[w]);
       float ms = __fdiv_rn(total, (float)K);
       rstd = bk_rcp_sqrt(__fadd_rn(ms, p.eps));
-      bk_stamp(p.trace, 6);
     }
     for (int q = threadIdx.x; q < nchunk; q += blockDim.x) {
       float y[8];
-      load_chunk_bf16(row, q, y);
+      if (q == (int)threadIdx.x) {
+#pragma unroll
+        for (int e = 0; e < 8; e++) y[e] = y0[e];
+      } else {
+        load_chunk_bf16(row, q, y);
+      }
       if (NORM) {
         float wv[8];
-        load_chunk_bf16(p.norm_w, q, wv);
+        if (q == (int)threadIdx.x) {
+          wv[0] = __uint_as_float(wpre.x << 16); wv[1] = __uint_as_float(wpre.x & 0xffff0000u);
+          wv[2] = __uint_as_float(wpre.y << 16); wv[3] = __uint_as_float(wpre.y & 0xffff0000u);
+          wv[4] = __uint_as_float(wpre.z << 16); wv[5] = __uint_as_float(wpre.z & 0xffff0000u);
+          wv[6] = __uint_as_float(wpre.w << 16); wv[7] = __uint_as_float(wpre.w & 0xffff0000u);
+        } else {
+          load_chunk_bf16(p.norm_w, q, wv);
+        }
 #pragma unroll
         for (int e = 0; e < 8; e += 2) {
           float v0 = __fmul_rn(__fmul_rn(y[e], rstd), __fadd_rn(1.0f, wv[e]));
@@ -186,7 +207,7 @@ __device__ void prologue_bf16(const GemvParams& p, uint32_t* xs, float* d8s, flo
       }
       quant_chunk(y, q, b, nunits, nblk, xs, d8s, s8s);
     }
-    bk_stamp(p.trace, 7);
+    (void)one_pass;
   }
 }
 
@@ -391,8 +412,8 @@ __device__ __forceinline__ void store_epilogue(const SegDev& sg, size_t o, float
 // G rows in shared memory and an mbarrier.  depth == 0 ("pool"): every group has its own slot and all
 // copies are issued before the dependency wait.  depth > 0 ("ring"): a warp owns `depth` slots and
 // refills a slot with its next group as soon as the slot is consumed.
-template <int B, int G>
-__global__ void __launch_bounds__(512, ((B * G <= 16) ? 2 : 1)) gemv_q4k_kernel(const GemvParams p) {
+template <int B, int GMAX>
+__global__ void __launch_bounds__(512, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kernel(const GemvParams p) {
   bk_pdl_trigger();
   bk_stamp(p.trace, 0);
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -408,6 +429,7 @@ __global__ void __launch_bounds__(512, ((B * G <= 16) ? 2 : 1)) gemv_q4k_kernel(
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int c0 = blockIdx.x * p.rows_per_cta;
   const int n_rows_cta = min(p.total_vrows, c0 + p.rows_per_cta) - c0;
+  const int G = p.group_rows;  // rows per group, 1..GMAX
   const int n_groups = (n_rows_cta + G - 1) / G;
   const uint32_t rowb = (uint32_t)(K / 256) * 144;
   const uint32_t slot_bytes = G * rowb;
@@ -437,6 +459,9 @@ __global__ void __launch_bounds__(512, ((B * G <= 16) ? 2 : 1)) gemv_q4k_kernel(
       }
     }
   }
+  uint4 wpre = make_uint4(0, 0, 0, 0);  // norm weights are weights: fetched before the wait as well
+  if (p.prologue == BK_PRO_RMSNORM && (int)threadIdx.x < K / 8)
+    wpre = __ldg(reinterpret_cast<const uint4*>(p.norm_w) + threadIdx.x);
   __syncwarp();
   bk_stamp(p.trace, 1);
   bk_pdl_wait();
@@ -445,9 +470,9 @@ __global__ void __launch_bounds__(512, ((B * G <= 16) ? 2 : 1)) gemv_q4k_kernel(
   if (p.prologue == BK_PRO_Q8)
     prologue_q8<B>(p, xs, d8s, s8s);
   else if (p.prologue == BK_PRO_BF16)
-    prologue_bf16<B, false>(p, xs, d8s, s8s, red);
+    prologue_bf16<B, false>(p, xs, d8s, s8s, red, wpre);
   else
-    prologue_bf16<B, true>(p, xs, d8s, s8s, red);
+    prologue_bf16<B, true>(p, xs, d8s, s8s, red, wpre);
   __syncthreads();
   bk_stamp(p.trace, 3);
 
@@ -459,9 +484,9 @@ __global__ void __launch_bounds__(512, ((B * G <= 16) ? 2 : 1)) gemv_q4k_kernel(
     mbar_wait_bounded(bar_base + 8 * slot, parity, p.status);
     if (gi == 0) bk_stamp(p.trace, 4);
     const uint8_t* wbase = slots + slot * slot_bytes;
-    float acc[G][B];
+    float acc[GMAX][B];
 #pragma unroll
-    for (int r = 0; r < G; r++)
+    for (int r = 0; r < GMAX; r++)
 #pragma unroll
       for (int b = 0; b < B; b++) acc[r][b] = 0.0f;
     for (int u = lane; u < nunits; u += 32) {
@@ -472,7 +497,7 @@ __global__ void __launch_bounds__(512, ((B * G <= 16) ? 2 : 1)) gemv_q4k_kernel(
 #pragma unroll
         for (int b = 0; b < B; b++) xr[b] = load_x(xs, d8s, s8s, b, u, nunits, nblk);
 #pragma unroll
-        for (int r = 0; r < G; r++) {
+        for (int r = 0; r < GMAX; r++) {
           if (r < nr) {
             const WRegs w = decode_unit(load_unit_smem(wbase + r * rowb, u), pp);
 #pragma unroll
@@ -481,7 +506,7 @@ __global__ void __launch_bounds__(512, ((B * G <= 16) ? 2 : 1)) gemv_q4k_kernel(
         }
       } else {
 #pragma unroll
-        for (int r = 0; r < G; r++) {
+        for (int r = 0; r < GMAX; r++) {
           if (r < nr) {
             const WRegs w = decode_unit(load_unit_smem(wbase + r * rowb, u), pp);
 #pragma unroll
@@ -490,6 +515,7 @@ __global__ void __launch_bounds__(512, ((B * G <= 16) ? 2 : 1)) gemv_q4k_kernel(
         }
       }
     }
+    if (gi == 0) bk_stamp(p.trace, 6);
     __syncwarp();  // every lane has consumed the slot
     if (depth > 0 && lane == 0) {
       const int g2 = g + depth * nw;
@@ -512,11 +538,12 @@ __global__ void __launch_bounds__(512, ((B * G <= 16) ? 2 : 1)) gemv_q4k_kernel(
     for (int b = 0; b < B; b++) {
       float pa[8];
 #pragma unroll
-      for (int r = 0; r < 8; r++) pa[r] = r < G ? acc[r < G ? r : 0][b] : 0.0f;
+      for (int r = 0; r < 8; r++) pa[r] = r < GMAX ? acc[r < GMAX ? r : 0][b] : 0.0f;
       const float y = warp_sum8(pa);
       const float yup = __shfl_xor_sync(0xffffffffu, y, 4);  // the odd neighbour row (the "up" row of a SwiGLU pair)
       if (mine && !(sg.epi == BK_EPI_SWIGLU && (ri & 1))) store_epilogue(sg, (size_t)b * sg.ld_out + sg.col_off + vr.n, y, yup);
     }
+    if (gi == 0) bk_stamp(p.trace, 7);
   }
   bk_stamp(p.trace, 5);
 }
@@ -527,26 +554,20 @@ size_t gemv_fixed_smem(int K, int B, int n_slots) {
   return (size_t)B * nunits * kUnitWords * 4 + (size_t)B * nblk * 8 + 8 * 4 + (size_t)n_slots * 8 + 128;
 }
 
-template <int B, int G>
+template <int B, int GMAX>
 int32_t launch_gemv(const GemvParams& p, int grid, int threads, size_t smem) {
   static size_t configured = 0;
   if (smem > configured) {
-    BK_CUDA((cudaFuncSetAttribute(gemv_q4k_kernel<B, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)));
+    BK_CUDA((cudaFuncSetAttribute(gemv_q4k_kernel<B, GMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)));
     configured = smem;
   }
-  BK_CUDA((bk_launch_pdl(gemv_q4k_kernel<B, G>, dim3(grid), dim3(threads), smem, p)));
+  BK_CUDA((bk_launch_pdl(gemv_q4k_kernel<B, GMAX>, dim3(grid), dim3(threads), smem, p)));
   BK_CHECK_LAUNCH();
   return BK_OK;
 }
 
-template <int B>
-int32_t launch_gemv_g(const GemvParams& p, int G, int grid, int threads, size_t smem) {
-  if (G == 8) {
-    if constexpr (B <= 2) return launch_gemv<B, 8>(p, grid, threads, smem);
-  }
-  if (G >= 4) return launch_gemv<B, 4>(p, grid, threads, smem);
-  return launch_gemv<B, 2>(p, grid, threads, smem);
-}
+// widest row group the register budget of batch B allows
+constexpr int gemv_gmax(int B) { return B <= 2 ? 8 : 4; }
 
 // ---- dequant / block-dot check kernels ---------------------------------------
 
@@ -715,10 +736,14 @@ int32_t bk_gemv_launch(const bkGemvArgs& a) {
   int rpc = (vrows + grid - 1) / grid;
   rpc = (rpc + 1) & ~1;
   grid = (vrows + rpc - 1) / rpc;
-  // rows per group: enough groups to keep a dozen warps busy; register budget caps G for wide batches
-  int G = rpc >= 128 ? 8 : (rpc >= 48 ? 4 : 2);
-  if (a.B > 2 && G > 4) G = 4;
-  const int n_groups = (rpc + G - 1) / G;
+  // rows per group: one group per warp when the CTA's rows allow it (a single round, evenly loaded), capped by the
+  // register budget; a SwiGLU launch keeps gate/up pairs together (even group size)
+  const int gmax = gemv_gmax(a.B);
+  int G = (rpc + 15) / 16;
+  if (G < 1) G = 1;
+  if (has_swiglu) G = (G + 1) & ~1;
+  if (G > gmax) G = gmax;
+  int n_groups = (rpc + G - 1) / G;
   int nw = n_groups < 8 ? 8 : (n_groups > 16 ? 16 : n_groups);
   // pool if the CTA's whole slice fits in about half of the SM's shared memory (so the next kernel's CTA can
   // become resident and start its own copies while this one computes), else a per-warp ring
@@ -726,37 +751,39 @@ int32_t bk_gemv_launch(const bkGemvArgs& a) {
   const size_t half = limit / 2;
   if (gemv_fixed_smem(a.K, a.B, n_groups) + (size_t)n_groups * G * rowb > half) {
     size_t per_level = (size_t)nw * G * rowb;
-    while (nw > 8 && gemv_fixed_smem(a.K, a.B, nw) + per_level > limit) {
+    while (nw > 8 && gemv_fixed_smem(a.K, a.B, nw * 8) + per_level > limit) {
       nw = 8;
       per_level = (size_t)nw * G * rowb;
     }
-    while (G > 2 && gemv_fixed_smem(a.K, a.B, nw) + per_level > limit) {
-      G >>= 1;
+    while (G > (has_swiglu ? 2 : 1) && gemv_fixed_smem(a.K, a.B, nw * 8) + per_level > limit) {
+      G = has_swiglu ? ((G / 2 + 1) & ~1) : (G + 1) / 2;
+      if (has_swiglu && G < 2) G = 2;
       per_level = (size_t)nw * G * rowb;
     }
     const size_t fixed = gemv_fixed_smem(a.K, a.B, nw * 8);
     BK_ARG(fixed + per_level <= limit, "bkGemvQ4K: K=%d B=%d does not fit in shared memory", a.K, a.B);
-    const int groups = (rpc + G - 1) / G;
+    n_groups = (rpc + G - 1) / G;
     depth = (int)((limit - fixed) / per_level);
-    const int max_depth = (groups + nw - 1) / nw;
+    const int max_depth = (n_groups + nw - 1) / nw;
     if (depth > max_depth) depth = max_depth;
     if (depth > 8) depth = 8;
     n_slots = depth * nw;
   }
+  p.group_rows = G;
   p.rows_per_cta = rpc;
   p.n_slots = n_slots;
   p.depth = depth;
   const size_t smem = gemv_fixed_smem(a.K, a.B, n_slots) + (size_t)n_slots * G * rowb;
   const int threads = nw * 32;
   switch (a.B) {
-    case 1: return launch_gemv_g<1>(p, G, grid, threads, smem);
-    case 2: return launch_gemv_g<2>(p, G, grid, threads, smem);
-    case 3: return launch_gemv_g<3>(p, G, grid, threads, smem);
-    case 4: return launch_gemv_g<4>(p, G, grid, threads, smem);
-    case 5: return launch_gemv_g<5>(p, G, grid, threads, smem);
-    case 6: return launch_gemv_g<6>(p, G, grid, threads, smem);
-    case 7: return launch_gemv_g<7>(p, G, grid, threads, smem);
-    default: return launch_gemv_g<8>(p, G, grid, threads, smem);
+    case 1: return launch_gemv<1, gemv_gmax(1)>(p, grid, threads, smem);
+    case 2: return launch_gemv<2, gemv_gmax(2)>(p, grid, threads, smem);
+    case 3: return launch_gemv<3, gemv_gmax(3)>(p, grid, threads, smem);
+    case 4: return launch_gemv<4, gemv_gmax(4)>(p, grid, threads, smem);
+    case 5: return launch_gemv<5, gemv_gmax(5)>(p, grid, threads, smem);
+    case 6: return launch_gemv<6, gemv_gmax(6)>(p, grid, threads, smem);
+    case 7: return launch_gemv<7, gemv_gmax(7)>(p, grid, threads, smem);
+    default: return launch_gemv<8, gemv_gmax(8)>(p, grid, threads, smem);
   }
 }
 

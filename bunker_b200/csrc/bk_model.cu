@@ -152,6 +152,7 @@ int32_t enqueue_step(Model& m, int parity) {
       ga.A_log = L.A_log; ga.dt_bias = L.dt_bias; ga.norm_w = L.gnorm;
       ga.S_in = L.S; ga.S_new = L.S;  // in place: each thread rewrites exactly the rows it read
       ga.out = m.attn_out; ga.B = B; ga.Hk = m.Hk; ga.Hv = m.Hv; ga.apply_conv = 1;
+      ga.state_is_settled = 1;  // this layer's state was last written one whole step ago
       PROF(PC_GDN, bkGdnStep(&ga));
       memset(&g, 0, sizeof(g));
       g.K = m.ZD; g.B = B; g.prologue = BK_PRO_BF16; g.x = m.attn_out; g.n_segs = 1;

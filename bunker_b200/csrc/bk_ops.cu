@@ -143,6 +143,7 @@ struct GdnParams {
   float* o_raw;
   uint16_t* conv_out;
   int B, Hk, Hv, apply_conv;
+  int early;  // state / conv state / weights are not outputs of the immediately preceding launch
   unsigned long long* trace;
 };
 
@@ -153,25 +154,58 @@ __global__ void __launch_bounds__(512) gdn_step_kernel(const GdnParams p) {
   __shared__ float s_scal[4];  // q scale, k rstd, decay, beta
   bk_pdl_trigger();
   bk_stamp(p.trace, 0);
-  bk_pdl_wait();
-  bk_stamp(p.trace, 2);
   const int hv = blockIdx.x, b = blockIdx.y, t = threadIdx.x;
   const int ratio = p.Hv / p.Hk, hk = hv / ratio;
   const int keydim = p.Hk * D, C = 2 * keydim + p.Hv * D;
+  const int warp = t >> 5, lane = t & 31;
+  const int r = t >> 7, j = t & 127;
+  const int which = t >> 7, ci = t & 127;
+  int ch = 0;
+  if (which == 0) ch = hk * D + ci;
+  else if (which == 1) ch = keydim + hk * D + ci;
+  else ch = 2 * keydim + hv * D + ci;
+  const float* S = p.S_in + (((size_t)b * p.Hv + hv) * D + 32 * r) * D + j;
+  float* Sn = p.S_new + (((size_t)b * p.Hv + hv) * D + 32 * r) * D + j;
 
+  // State, conv taps and per-head constants do not come from the kernel that runs just before this one
+  // (p.early != 0 asserts that), so they are requested before the dependency wait and arrive while the
+  // projection GEMV is still finishing.
+  float sd[32];
+  uint16_t h0 = 0, h1 = 0, h2 = 0;
+  uint2 cw = make_uint2(0, 0);
+  float alog = 0.0f, dtb = 0.0f, nw = 0.0f;
+  auto load_static = [&]() {
+#pragma unroll
+    for (int i = 0; i < 32; i++) sd[i] = S[(size_t)i * D];
+    if (t < 3 * D && p.apply_conv) {
+      const uint16_t* st = p.cs_in + (size_t)b * 3 * C;
+      h0 = st[ch];
+      h1 = st[C + ch];
+      h2 = st[2 * C + ch];
+      cw = *reinterpret_cast<const uint2*>(p.conv_w + 4 * (size_t)ch);
+    }
+    if (t == 3 * D) {
+      alog = p.A_log[hv];
+      dtb = bk_bf16_to_f32(p.dt_bias[hv]);
+    }
+    if (t < D) nw = p.norm_w[t];
+  };
+  if (p.early) load_static();
+  bk_pdl_wait();
+  bk_stamp(p.trace, 2);
+  if (!p.early) load_static();
+
+  float zv = 0.0f;
+  if (t < D) zv = bk_bf16_to_f32(p.z[((size_t)b * p.Hv + hv) * D + t]);
   if (t < 3 * D) {
-    int ch, which = t >> 7, i = t & 127;
-    if (which == 0) ch = hk * D + i;
-    else if (which == 1) ch = keydim + hk * D + i;
-    else ch = 2 * keydim + hv * D + i;
     uint16_t hx = p.qkv[(size_t)b * C + ch];
     float val;
     if (p.apply_conv) {
-      const uint16_t* s = p.cs_in + (size_t)b * 3 * C;
-      uint16_t h0 = s[ch], h1 = s[C + ch], h2 = s[2 * C + ch];
-      float o = conv_tap4(bk_bf16_to_f32(h0), bk_bf16_to_f32(h1), bk_bf16_to_f32(h2), bk_bf16_to_f32(hx),
-                          p.conv_w + 4 * (size_t)ch);
-      uint16_t ob = bk_f32_to_bf16(o);
+      float w0 = __uint_as_float(cw.x << 16), w1 = __uint_as_float(cw.x & 0xffff0000u);
+      float w2 = __uint_as_float(cw.y << 16), w3 = __uint_as_float(cw.y & 0xffff0000u);
+      float raw = __fadd_rn(__fadd_rn(__fmul_rn(w0, bk_bf16_to_f32(h0)), __fmul_rn(w1, bk_bf16_to_f32(h1))),
+                            __fadd_rn(__fmul_rn(w2, bk_bf16_to_f32(h2)), __fmul_rn(w3, bk_bf16_to_f32(hx))));
+      uint16_t ob = bk_f32_to_bf16(__fmul_rn(raw, bk_sigmoidf(raw)));
       val = bk_bf16_to_f32(ob);
       // q/k channels are shared by `ratio` value heads: the first of them writes
       if (which == 2 || hv % ratio == 0) {
@@ -184,37 +218,31 @@ __global__ void __launch_bounds__(512) gdn_step_kernel(const GdnParams p) {
     } else {
       val = bk_bf16_to_f32(hx);
     }
-    if (which == 0) s_q[i] = val;
-    else if (which == 1) s_k[i] = val;
-    else s_v[i] = val;
+    if (which == 0) s_q[ci] = val;
+    else if (which == 1) s_k[ci] = val;
+    else s_v[ci] = val;
+  } else if (t == 3 * D) {
+    // gates on an otherwise idle warp, overlapping the conv above
+    float sp = bk_softplusf(__fadd_rn(p.a[(size_t)b * p.Hv + hv], dtb));
+    s_scal[2] = bk_expf(-__fmul_rn(bk_expf(alog), sp));
+    s_scal[3] = bk_sigmoidf(p.b[(size_t)b * p.Hv + hv]);
   }
   __syncthreads();
-  const int warp = t >> 5, lane = t & 31;
   if (warp < 2) {
     const float* src = warp == 0 ? s_q : s_k;
     float acc = 0.0f;
 #pragma unroll
     for (int e = 0; e < 4; e++) acc = fmaf(src[lane * 4 + e], src[lane * 4 + e], acc);
     acc = bk_warp_sum(acc);
-    float r = bk_rcp_sqrt(__fadd_rn(acc, 1e-6f));
-    if (lane == 0) s_scal[warp] = (warp == 0) ? __fmul_rn(r, 0.088388347648318441f) : r;
-  } else if (warp == 2 && lane == 0) {
-    float sp = bk_softplusf(__fadd_rn(p.a[(size_t)b * p.Hv + hv], bk_bf16_to_f32(p.dt_bias[hv])));
-    s_scal[2] = bk_expf(-__fmul_rn(bk_expf(p.A_log[hv]), sp));
-    s_scal[3] = bk_sigmoidf(p.b[(size_t)b * p.Hv + hv]);
+    float rr = bk_rcp_sqrt(__fadd_rn(acc, 1e-6f));
+    if (lane == 0) s_scal[warp] = (warp == 0) ? __fmul_rn(rr, 0.088388347648318441f) : rr;
   }
   __syncthreads();
   if (t < D) s_q[t] = __fmul_rn(s_q[t], s_scal[0]);
   else if (t < 2 * D) s_k[t - D] = __fmul_rn(s_k[t - D], s_scal[1]);
   __syncthreads();
 
-  const int r = t >> 7, j = t & 127;
   const float decay = s_scal[2], beta = s_scal[3];
-  const float* S = p.S_in + (((size_t)b * p.Hv + hv) * D + 32 * r) * D + j;
-  float* Sn = p.S_new + (((size_t)b * p.Hv + hv) * D + 32 * r) * D + j;
-  float sd[32];
-#pragma unroll
-  for (int i = 0; i < 32; i++) sd[i] = S[(size_t)i * D];
   float acc = 0.0f;
 #pragma unroll
   for (int i = 0; i < 32; i++) {
@@ -250,9 +278,8 @@ __global__ void __launch_bounds__(512) gdn_step_kernel(const GdnParams p) {
   }
   __syncthreads();
   if (t < D) {
-    float zv = bk_bf16_to_f32(p.z[((size_t)b * p.Hv + hv) * D + t]);
     float zs = __fmul_rn(zv, bk_sigmoidf(zv));
-    float ow = __fmul_rn(__fmul_rn(s_o[t], s_scal[0]), p.norm_w[t]);
+    float ow = __fmul_rn(__fmul_rn(s_o[t], s_scal[0]), nw);
     p.out[((size_t)b * p.Hv + hv) * D + t] = bk_f32_to_bf16(__fmul_rn(ow, zs));
   }
   bk_stamp(p.trace, 5);
@@ -462,6 +489,7 @@ int32_t bkGdnStep(const bkGdnArgs* args) {
   p.Hk = a.Hk;
   p.Hv = a.Hv;
   p.apply_conv = a.apply_conv;
+  p.early = a.state_is_settled;
   p.trace = bk_trace_slot();
   BK_CUDA(bk_launch_pdl(gdn_step_kernel, dim3(a.Hv, a.B), dim3(512), 0, p));
   BK_CHECK_LAUNCH();

@@ -155,6 +155,10 @@ typedef struct bkGdnArgs {
   uint64_t S_in, S_new;
   uint64_t out, o_raw, conv_out;
   int32_t B, Hk, Hv, apply_conv; /* apply_conv=0: qkv already holds conv output */
+  int32_t state_is_settled;      /* 1: S_in, conv_state_in and the weights were NOT written by the launch that
+                                    immediately precedes this one on the stream, so the kernel may read them while that
+                                    launch is still running (programmatic dependent launch).  0: read everything after it. */
+  int32_t reserved;
 } bkGdnArgs;
 BK_API int32_t bkGdnStep(const bkGdnArgs* args);
 
