@@ -37,9 +37,9 @@ struct AttnParams {
   float* scratch;
   const uint16_t* gate;
   int B, Hq, Hkv, rot_half, max_len, split_len, max_splits, fused;
+  int settled;  // cache rows of earlier steps and pos[] are not outputs of the immediately preceding launch
   float scale;
   unsigned long long* trace;
-  unsigned long long* trace2;
 };
 
 __device__ __forceinline__ void bf16x8_to_f32(uint4 v, float (&y)[8]) {
@@ -108,19 +108,62 @@ __device__ __forceinline__ float warp_sum8(const float (&v)[8]) {
   return y;
 }
 
+// merge the splits of one (batch, q head) by one warp; lane l owns output dims [8l, 8l+8).
+// w_s: ns floats of shared memory private to the warp.  M = max m_s; w_s = exp(m_s - M);
+// L = fma(w_s, l_s, L) and O = fma(w_s, o_s, O) in ascending s; out = (O/L) * sigmoid(gate).
+__device__ void combine_head_warp(const AttnParams& p, int b, int h, int ns, float* w_s) {
+  const int lane = threadIdx.x & 31;
+  const float* sc_ml = p.scratch + ((size_t)b * p.Hq + h) * p.max_splits * 2;
+  const float* sc_o = p.scratch + (size_t)p.B * p.Hq * p.max_splits * 2 + ((size_t)b * p.Hq + h) * p.max_splits * kHD;
+  float m = -INFINITY;
+  for (int s = lane; s < ns; s += 32) {
+    float ms = __ldcg(sc_ml + 2 * s);
+    w_s[s] = ms;
+    m = fmaxf(m, ms);
+  }
+  const float M = bk_warp_max(m);
+  for (int s = lane; s < ns; s += 32) w_s[s] = bk_expf(__fsub_rn(w_s[s], M));
+  __syncwarp();
+  float L = 0.0f, O[8];
+#pragma unroll
+  for (int e = 0; e < 8; e++) O[e] = 0.0f;
+  for (int s = 0; s < ns; s++) {
+    const float w = w_s[s];
+    L = fmaf(w, __ldcg(sc_ml + 2 * s + 1), L);
+    const float4 a = __ldcg(reinterpret_cast<const float4*>(sc_o + (size_t)s * kHD + lane * 8));
+    const float4 c = __ldcg(reinterpret_cast<const float4*>(sc_o + (size_t)s * kHD + lane * 8) + 1);
+    O[0] = fmaf(w, a.x, O[0]); O[1] = fmaf(w, a.y, O[1]); O[2] = fmaf(w, a.z, O[2]); O[3] = fmaf(w, a.w, O[3]);
+    O[4] = fmaf(w, c.x, O[4]); O[5] = fmaf(w, c.y, O[5]); O[6] = fmaf(w, c.z, O[6]); O[7] = fmaf(w, c.w, O[7]);
+  }
+  const uint16_t* gp = p.fused ? p.qg + ((size_t)b * p.Hq + h) * 2 * kHD + kHD + lane * 8
+                               : p.gate + ((size_t)b * p.Hq + h) * kHD + lane * 8;
+  float gf[8];
+  bf16x8_to_f32(*reinterpret_cast<const uint4*>(gp), gf);
+  uint32_t o[4];
+#pragma unroll
+  for (int e = 0; e < 8; e += 2) {
+    float v0 = __fmul_rn(__fdiv_rn(O[e], L), bk_sigmoidf(gf[e]));
+    float v1 = __fmul_rn(__fdiv_rn(O[e + 1], L), bk_sigmoidf(gf[e + 1]));
+    o[e >> 1] = bk_f32x2_to_bf16x2(v0, v1);
+  }
+  *reinterpret_cast<uint4*>(p.out + ((size_t)b * p.Hq + h) * kHD + lane * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 // dynamic shared memory layout (bytes):
 //   q_st  : 8*256 bf16                 4096
 //   k_st  : 256 bf16                    512
 //   m_s   : 8 f32 (+8 spare)             64
 //   l_s   : kW*8 f32                    256
 //   s_s   : split_len*8 f32
-//   o_s   : kW*8*256 f32              65536
+//   o_s   : kW*8*256 f32              65536   (reused by the split merge)
+// One CTA per (split, KV head, batch).  Rows of the cache that were written in earlier steps do not depend on
+// the kernel running just before this one, so (p.settled) the first 8 K rows and 8 V rows of every warp are
+// requested before the dependency wait; longer splits stream further chunks of 8 rows per warp with the next
+// chunk in flight while the current one is reduced.  The CTA that finishes a (batch, KV head) last merges the splits.
 template <int G>
 __global__ void __launch_bounds__(kW * 32) attn_split_kernel(const AttnParams p) {
   bk_pdl_trigger();
   bk_stamp(p.trace, 0);
-  bk_pdl_wait();
-  bk_stamp(p.trace, 2);
   extern __shared__ __align__(16) uint8_t smem[];
   uint16_t* q_st = reinterpret_cast<uint16_t*>(smem);
   uint16_t* k_st = q_st + 8 * kHD;
@@ -128,16 +171,41 @@ __global__ void __launch_bounds__(kW * 32) attn_split_kernel(const AttnParams p)
   float* l_s = m_s + 16;
   float* s_s = l_s + kW * 8;
   float* o_s = s_s + (size_t)p.split_len * 8;
+  __shared__ int s_last;
 
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-  const int pos = p.pos[b];
-  const int n = pos + 1;
-  const int j0 = split * p.split_len;
-  if (j0 >= n) return;
-  const int ns = min(n, j0 + p.split_len) - j0;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
   uint16_t* Kb = p.k_cache + ((size_t)b * p.Hkv + kvh) * (size_t)p.max_len * kHD;
   uint16_t* Vb = p.v_cache + ((size_t)b * p.Hkv + kvh) * (size_t)p.max_len * kHD;
+  const int j0 = split * p.split_len;
+
+  // rows of this warp: jj = warp + 8*i; chunk c holds i in [8c, 8c+8)
+  uint4 kc[8], vc[8];
+  int pos = 0, ns = 0;
+  auto load_chunk = [&](const uint16_t* base, int c, uint4 (&dst)[8], bool skip_pos) {
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+      const int jj = warp + 8 * (8 * c + e);
+      const bool ok = jj < ns && !(skip_pos && j0 + jj == pos);
+      dst[e] = ok ? *reinterpret_cast<const uint4*>(base + (size_t)(j0 + jj) * kHD + lane * 8) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  if (p.settled) {
+    pos = p.pos[b];
+    ns = min(pos + 1, j0 + p.split_len) - j0;   // <= 0: nothing to do for this split
+    if (ns > 0) {
+      load_chunk(Kb, 0, kc, true);
+      load_chunk(Vb, 0, vc, true);
+    }
+  }
+  bk_pdl_wait();
+  bk_stamp(p.trace, 2);
+  if (!p.settled) {
+    pos = p.pos[b];
+    ns = min(pos + 1, j0 + p.split_len) - j0;
+  }
+  if (ns <= 0) return;
+  const int nsplits = (pos + p.split_len) / p.split_len;
 
   // ---- phase 0: q (and, in the split that owns row pos, k/v append) ----
   if (p.fused) {
@@ -159,6 +227,24 @@ __global__ void __launch_bounds__(kW * 32) attn_split_kernel(const AttnParams p)
           *reinterpret_cast<const uint4*>(p.qg + ((size_t)b * p.Hq + kvh * G + warp) * kHD + lane * 8);
   }
   __syncthreads();  // the appended K/V row is visible to this CTA from here on
+  bk_stamp(p.trace, 3);
+  if (!p.settled) {
+    load_chunk(Kb, 0, kc, false);
+    load_chunk(Vb, 0, vc, false);
+  } else {
+    // the row appended above was left out of the early loads
+    const int jp = pos - j0;
+    if (jp >= 0 && jp < ns && (jp & 7) == warp && (jp >> 3) < 8) {
+      const int e = jp >> 3;
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+        if (i == e) {
+          kc[i] = *reinterpret_cast<const uint4*>(Kb + (size_t)pos * kHD + lane * 8);
+          vc[i] = *reinterpret_cast<const uint4*>(Vb + (size_t)pos * kHD + lane * 8);
+        }
+    }
+  }
+  const int nchunks = (ns + 63) / 64;
 
   // ---- phase 1: scores ----
   {
@@ -166,36 +252,36 @@ __global__ void __launch_bounds__(kW * 32) attn_split_kernel(const AttnParams p)
 #pragma unroll
     for (int g = 0; g < G; g++) bf16x8_to_f32(*reinterpret_cast<const uint4*>(q_st + g * kHD + lane * 8), qf[g]);
     const int hsel = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-    for (int jj = warp; jj < ns; jj += 2 * kW) {
-      const int jj2 = jj + kW;
-      const bool has2 = jj2 < ns;
-      uint4 ka = *reinterpret_cast<const uint4*>(Kb + (size_t)(j0 + jj) * kHD + lane * 8);
-      uint4 kb = has2 ? *reinterpret_cast<const uint4*>(Kb + (size_t)(j0 + jj2) * kHD + lane * 8) : make_uint4(0, 0, 0, 0);
-      float k1[8], k2[8], pa[8], pb[8];
-      bf16x8_to_f32(ka, k1);
-      bf16x8_to_f32(kb, k2);
+    for (int c = 0; c < nchunks; c++) {
+      uint4 kn[8];
+      if (c + 1 < nchunks) load_chunk(Kb, c + 1, kn, false);
 #pragma unroll
-      for (int g = 0; g < 8; g++) {
-        float a1 = 0.0f, a2 = 0.0f;
-        if (g < G) {
+      for (int e = 0; e < 8; e++) {
+        const int jj = warp + 8 * (8 * c + e);
+        if (jj < ns) {   // warp-uniform
+          float kf[8], pa[8];
+          bf16x8_to_f32(kc[e], kf);
 #pragma unroll
-          for (int e = 0; e < 8; e++) {
-            a1 = fmaf(qf[g < G ? g : 0][e], k1[e], a1);
-            a2 = fmaf(qf[g < G ? g : 0][e], k2[e], a2);
+          for (int g = 0; g < 8; g++) {
+            float a1 = 0.0f;
+            if (g < G) {
+#pragma unroll
+              for (int d = 0; d < 8; d++) a1 = fmaf(qf[g < G ? g : 0][d], kf[d], a1);
+            }
+            pa[g] = a1;
           }
+          const float s1 = warp_sum8(pa);
+          if ((lane & 3) == 0) s_s[(size_t)jj * 8 + hsel] = __fmul_rn(s1, p.scale);
         }
-        pa[g] = a1;
-        pb[g] = a2;
       }
-      float s1 = warp_sum8(pa);
-      float s2 = warp_sum8(pb);
-      if ((lane & 3) == 0) {
-        s_s[(size_t)jj * 8 + hsel] = __fmul_rn(s1, p.scale);
-        if (has2) s_s[(size_t)jj2 * 8 + hsel] = __fmul_rn(s2, p.scale);
+      if (c + 1 < nchunks) {
+#pragma unroll
+        for (int e = 0; e < 8; e++) kc[e] = kn[e];
       }
     }
   }
   __syncthreads();
+  bk_stamp(p.trace, 4);
 
   // ---- phase 2: exact max per head, p = exp(s - m) in place ----
   {
@@ -215,8 +301,8 @@ __global__ void __launch_bounds__(kW * 32) attn_split_kernel(const AttnParams p)
     __syncthreads();
     const float mg = m_s[g];
     for (int jj = tid >> 3; jj < ns; jj += (kW * 32) >> 3) {
-      float s = s_s[(size_t)jj * 8 + g];
-      s_s[(size_t)jj * 8 + g] = (g < G) ? bk_expf(__fsub_rn(s, mg)) : 0.0f;
+      float sv = s_s[(size_t)jj * 8 + g];
+      s_s[(size_t)jj * 8 + g] = (g < G) ? bk_expf(__fsub_rn(sv, mg)) : 0.0f;
     }
   }
   __syncthreads();
@@ -230,18 +316,29 @@ __global__ void __launch_bounds__(kW * 32) attn_split_kernel(const AttnParams p)
 #pragma unroll
       for (int e = 0; e < 8; e++) acc[g][e] = 0.0f;
     }
-    for (int jj = warp; jj < ns; jj += kW) {
-      uint4 vr = *reinterpret_cast<const uint4*>(Vb + (size_t)(j0 + jj) * kHD + lane * 8);
-      float vf[8];
-      bf16x8_to_f32(vr, vf);
-      const float4 p0 = *reinterpret_cast<const float4*>(s_s + (size_t)jj * 8);
-      const float4 p1 = *reinterpret_cast<const float4*>(s_s + (size_t)jj * 8 + 4);
-      const float pp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+    for (int c = 0; c < nchunks; c++) {
+      uint4 vn[8];
+      if (c + 1 < nchunks) load_chunk(Vb, c + 1, vn, false);
 #pragma unroll
-      for (int g = 0; g < G; g++) {
-        lw[g] = __fadd_rn(lw[g], pp[g]);
+      for (int e = 0; e < 8; e++) {
+        const int jj = warp + 8 * (8 * c + e);
+        if (jj < ns) {
+          float vf[8];
+          bf16x8_to_f32(vc[e], vf);
+          const float4 p0 = *reinterpret_cast<const float4*>(s_s + (size_t)jj * 8);
+          const float4 p1 = *reinterpret_cast<const float4*>(s_s + (size_t)jj * 8 + 4);
+          const float pp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
 #pragma unroll
-        for (int e = 0; e < 8; e++) acc[g][e] = fmaf(pp[g], vf[e], acc[g][e]);
+          for (int g = 0; g < G; g++) {
+            lw[g] = __fadd_rn(lw[g], pp[g]);
+#pragma unroll
+            for (int d = 0; d < 8; d++) acc[g][d] = fmaf(pp[g], vf[d], acc[g][d]);
+          }
+        }
+      }
+      if (c + 1 < nchunks) {
+#pragma unroll
+        for (int e = 0; e < 8; e++) vc[e] = vn[e];
       }
     }
 #pragma unroll
@@ -253,6 +350,7 @@ __global__ void __launch_bounds__(kW * 32) attn_split_kernel(const AttnParams p)
     }
   }
   __syncthreads();
+  bk_stamp(p.trace, 6);
 
   // ---- cross-warp sums in warp order, partial out ----
   float* sc_ml = p.scratch;
@@ -272,49 +370,23 @@ __global__ void __launch_bounds__(kW * 32) attn_split_kernel(const AttnParams p)
     sc_ml[o] = m_s[tid];
     sc_ml[o + 1] = l;
   }
-  bk_stamp(p.trace, 5);
-}
 
-// merge the splits of one (batch, q head); thread d owns output dim d
-__global__ void __launch_bounds__(kHD) attn_combine_kernel(const AttnParams p) {
-  __shared__ float w_s[kMaxSplits];
-  __shared__ float l_sh[kMaxSplits];
-  __shared__ float red[8];
-  bk_pdl_trigger();
-  bk_stamp(p.trace2, 0);
-  bk_pdl_wait();
-  bk_stamp(p.trace2, 2);
-  const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
-  const int n = p.pos[b] + 1;
-  const int ns = (n + p.split_len - 1) / p.split_len;
-  const float* sc_ml = p.scratch + ((size_t)b * p.Hq + h) * p.max_splits * 2;
-  const float* sc_o = p.scratch + (size_t)p.B * p.Hq * p.max_splits * 2 + ((size_t)b * p.Hq + h) * p.max_splits * kHD;
-  float m = -INFINITY;
-  for (int s = tid; s < ns; s += kHD) {
-    float ms = sc_ml[2 * s];
-    w_s[s] = ms;
-    l_sh[s] = sc_ml[2 * s + 1];
-    m = fmaxf(m, ms);
-  }
-  m = bk_warp_max(m);
-  if ((tid & 31) == 0) red[tid >> 5] = m;
+  // ---- the CTA that completes this (batch, KV head) merges its splits ----
+  __threadfence();
   __syncthreads();
-  float M = red[0];
-#pragma unroll
-  for (int w = 1; w < 8; w++) M = fmaxf(M, red[w]);
-  for (int s = tid; s < ns; s += kHD) w_s[s] = bk_expf(__fsub_rn(w_s[s], M));
-  __syncthreads();
-  float L = 0.0f, O = 0.0f;
-  for (int s = 0; s < ns; s++) {
-    const float w = w_s[s];
-    L = fmaf(w, l_sh[s], L);
-    O = fmaf(w, sc_o[(size_t)s * kHD + tid], O);
+  bk_stamp(p.trace, 7);
+  unsigned int* cnt = reinterpret_cast<unsigned int*>(p.scratch + (size_t)p.B * p.Hq * p.max_splits * (kHD + 2)) + b * p.Hkv + kvh;
+  if (tid == 0) {
+    const unsigned int done = atomicAdd(cnt, 1u);
+    s_last = (done == (unsigned int)(nsplits - 1));
   }
-  const uint16_t gbits = p.fused ? p.qg[((size_t)b * p.Hq + h) * 2 * kHD + kHD + tid]
-                                 : p.gate[((size_t)b * p.Hq + h) * kHD + tid];
-  float o = __fmul_rn(__fdiv_rn(O, L), bk_sigmoidf(bk_bf16_to_f32(gbits)));
-  p.out[((size_t)b * p.Hq + h) * kHD + tid] = bk_f32_to_bf16(o);
-  bk_stamp(p.trace2, 5);
+  __syncthreads();
+  if (s_last) {
+    __threadfence();
+    if (warp < G) combine_head_warp(p, b, kvh * G + warp, nsplits, o_s + warp * kMaxSplits);  // one head per warp
+    if (tid == 0) *cnt = 0;
+  }
+  bk_stamp(p.trace, 5);
 }
 
 size_t attn_smem_bytes(int split_len) { return 4096 + 512 + 64 + 256 + (size_t)split_len * 32 + (size_t)kW * 8 * kHD * 4; }
@@ -352,7 +424,7 @@ int32_t bkAttnPlan(int32_t n_rows, int32_t B, int32_t Hkv, int32_t* split_len, i
 uint64_t bkAttnScratchBytes(int32_t B, int32_t Hq, int32_t HD, int32_t max_len, int32_t split_len) {
   if (split_len <= 0) return 0;
   uint64_t ms = (uint64_t)(max_len + split_len - 1) / split_len;
-  return (uint64_t)B * Hq * ms * (uint64_t)(HD + 2) * 4;
+  return (uint64_t)B * Hq * ms * (uint64_t)(HD + 2) * 4 + (uint64_t)B * Hq * 4;  // partials + completion counters
 }
 
 int32_t bkAttnDecode(const bkAttnArgs* args) {
@@ -406,7 +478,7 @@ int32_t bkAttnDecode(const bkAttnArgs* args) {
   p.fused = a.fused_norm_rope;
   p.scale = a.scale;
   p.trace = bk_trace_slot();
-  p.trace2 = bk_trace_slot();
+  p.settled = a.cache_is_settled;
   size_t smem = attn_smem_bytes(split_len);
   dim3 grid(nsplit, a.Hkv, a.B);
   int32_t rc;
@@ -421,8 +493,6 @@ int32_t bkAttnDecode(const bkAttnArgs* args) {
     default: rc = launch_split<8>(p, grid, smem); break;
   }
   if (rc) return rc;
-  BK_CUDA(bk_launch_pdl(attn_combine_kernel, dim3(a.Hq, a.B), dim3(kHD), 0, p));
-  BK_CHECK_LAUNCH();
   return BK_OK;
 }
 

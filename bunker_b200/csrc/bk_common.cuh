@@ -25,6 +25,15 @@ BK_DEVINL void bk_stamp(unsigned long long* rec, int slot) {
   }
 }
 
+// lane 0 of every warp folds its exit time into the record (slot = latest exit of the whole grid)
+BK_DEVINL void bk_stamp_max(unsigned long long* rec, int slot) {
+  if (rec && (threadIdx.x & 31) == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    atomicMax(rec + slot, t);
+  }
+}
+
 // ---- bf16 / f16 -----------------------------------------------------------
 
 BK_DEVINL float bk_bf16_to_f32(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }

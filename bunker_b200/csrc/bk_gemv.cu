@@ -62,6 +62,7 @@ struct GemvParams {
   float eps;
   int* status;       // device status word: set when a bounded wait gives up
   unsigned long long* trace;  // timeline record of this launch, or null
+  unsigned long long* cta_trace;  // per-CTA timeline of this launch, or null
   SegDev segs[4];
 };
 
@@ -416,6 +417,8 @@ template <int B, int GMAX>
 __global__ void __launch_bounds__(512, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kernel(const GemvParams p) {
   bk_pdl_trigger();
   bk_stamp(p.trace, 0);
+  unsigned long long* ctr = p.cta_trace ? p.cta_trace + 4 * blockIdx.x : nullptr;
+  if (ctr && threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); ctr[0] = t_; ctr[3] = 0; }
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int K = p.K, nunits = K / 64, nblk = K / 32;
   const int nw = blockDim.x >> 5;
@@ -466,6 +469,7 @@ __global__ void __launch_bounds__(512, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kern
   bk_stamp(p.trace, 1);
   bk_pdl_wait();
   bk_stamp(p.trace, 2);
+  if (ctr && threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); ctr[1] = t_; }
 
   if (p.prologue == BK_PRO_Q8)
     prologue_q8<B>(p, xs, d8s, s8s);
@@ -475,6 +479,7 @@ __global__ void __launch_bounds__(512, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kern
     prologue_bf16<B, true>(p, xs, d8s, s8s, red, wpre);
   __syncthreads();
   bk_stamp(p.trace, 3);
+  bk_stamp_max(p.trace, 1);  // (reuses slot 1) latest prologue end over all CTAs
 
   const int ri = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);  // row this lane reports
   for (int gi = 0, g = warp; g < n_groups; gi++, g += nw) {
@@ -482,7 +487,11 @@ __global__ void __launch_bounds__(512, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kern
     const uint32_t parity = depth == 0 ? 0u : (uint32_t)((gi / depth) & 1);
     const int nr = min(G, n_rows_cta - g * G);
     mbar_wait_bounded(bar_base + 8 * slot, parity, p.status);
-    if (gi == 0) bk_stamp(p.trace, 4);
+    if (gi == 0) {
+      bk_stamp(p.trace, 4);
+      bk_stamp_max(p.trace, 7);  // latest "first weights landed" over all warps
+      if (ctr && threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); ctr[2] = t_; }
+    }
     const uint8_t* wbase = slots + slot * slot_bytes;
     float acc[GMAX][B];
 #pragma unroll
@@ -515,7 +524,6 @@ __global__ void __launch_bounds__(512, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kern
         }
       }
     }
-    if (gi == 0) bk_stamp(p.trace, 6);
     __syncwarp();  // every lane has consumed the slot
     if (depth > 0 && lane == 0) {
       const int g2 = g + depth * nw;
@@ -543,9 +551,10 @@ __global__ void __launch_bounds__(512, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kern
       const float yup = __shfl_xor_sync(0xffffffffu, y, 4);  // the odd neighbour row (the "up" row of a SwiGLU pair)
       if (mine && !(sg.epi == BK_EPI_SWIGLU && (ri & 1))) store_epilogue(sg, (size_t)b * sg.ld_out + sg.col_off + vr.n, y, yup);
     }
-    if (gi == 0) bk_stamp(p.trace, 7);
   }
   bk_stamp(p.trace, 5);
+  bk_stamp_max(p.trace, 6);  // latest exit over all warps of all CTAs
+  if (ctr) bk_stamp_max(ctr, 3);
 }
 
 // bytes of shared memory before the weight slots: activation, scales, reduction scratch, barriers (+ alignment slack)
@@ -727,6 +736,8 @@ int32_t bk_gemv_launch(const bkGemvArgs& a) {
   p.total_vrows = vrows;
   p.status = c.d_status;
   p.trace = bk_trace_slot();
+  p.cta_trace = nullptr;
+  if (c.cta_trace && c.cta_trace_seen++ == c.cta_trace_launch) p.cta_trace = c.cta_trace;
 
   // ---- launch shape ----
   const size_t rowb = (size_t)(a.K / 256) * 144;

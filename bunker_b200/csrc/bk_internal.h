@@ -20,6 +20,9 @@ struct BkContext {
   unsigned long long* trace = nullptr;  // device trace buffer (bkTraceEnable), 8 slots per launch
   int trace_cap = 0;                  // launches the buffer can hold
   int trace_seq = 0;                  // next launch index
+  unsigned long long* cta_trace = nullptr;  // per-CTA timeline of one chosen GEMV launch (bkTraceCtas)
+  int cta_trace_launch = -1;          // index (among GEMV launches since bkTraceCtas) of the launch to record
+  int cta_trace_seen = 0;
   int* d_status = nullptr;           // device word set by kernels whose bounded waits gave up
   char err[512] = {0};
 };

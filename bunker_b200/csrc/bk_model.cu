@@ -180,6 +180,7 @@ int32_t enqueue_step(Model& m, int parity) {
       aa.B = B; aa.Hq = m.Hq; aa.Hkv = m.Hkv; aa.HD = c.head_dim; aa.rot_half = c.rot_dim / 2; aa.max_len = c.max_len;
       aa.split_len = m.split_len; aa.max_pos = c.max_len - 1; aa.scale = 1.0f / sqrtf((float)c.head_dim);
       aa.fused_norm_rope = 1;
+      aa.cache_is_settled = 1;  // pos and the older cache rows were written a whole step ago
       PROF(PC_ATTN, bkAttnDecode(&aa));
       memset(&g, 0, sizeof(g));
       g.K = m.Hq * c.head_dim; g.B = B; g.prologue = BK_PRO_BF16; g.x = m.attn_out; g.n_segs = 1;
@@ -411,7 +412,7 @@ int32_t bkModelFinalize(uint64_t model) {
   int32_t sl = 0;
   TRY(bkAttnPlan(c.max_len, B, m.Hkv, &sl, nullptr));
   m.split_len = sl;
-  TRY(dev_alloc(m, bkAttnScratchBytes(B, m.Hq, c.head_dim, c.max_len, sl), &m.attn_scratch, false));
+  TRY(dev_alloc(m, bkAttnScratchBytes(B, m.Hq, c.head_dim, c.max_len, sl), &m.attn_scratch));
   {
     int half = c.rot_dim / 2;
     std::vector<float> ct((size_t)c.max_len * half), st((size_t)c.max_len * half);

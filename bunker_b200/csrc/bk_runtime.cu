@@ -194,10 +194,19 @@ int32_t bkTraceEnable(uint64_t dev_buf, int32_t max_launches) {
   return BK_OK;
 }
 
+int32_t bkTraceCtas(uint64_t dev_buf, int32_t gemv_launch_index) {
+  BK_REQUIRE_INIT();
+  g_ctx.cta_trace = bk_ptr<unsigned long long>(dev_buf);
+  g_ctx.cta_trace_launch = gemv_launch_index;
+  g_ctx.cta_trace_seen = 0;
+  return BK_OK;
+}
+
 int32_t bkTraceDisable(void) {
   BK_REQUIRE_INIT();
   g_ctx.trace = nullptr;
   g_ctx.trace_cap = 0;
+  g_ctx.cta_trace = nullptr;
   return BK_OK;
 }
 

@@ -60,7 +60,8 @@ class bkAttnArgs(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in ("qg", "k", "v", "q_norm_w", "k_norm_w", "cos_t", "sin_t", "k_cache",
                                            "v_cache", "pos", "out", "scratch")] + \
                [(n, C.c_int32) for n in ("B", "Hq", "Hkv", "HD", "rot_half", "max_len", "split_len", "max_pos")] + \
-               [("scale", C.c_float), ("fused_norm_rope", C.c_int32), ("gate", C.c_uint64)]
+               [("scale", C.c_float), ("fused_norm_rope", C.c_int32), ("gate", C.c_uint64),
+                ("cache_is_settled", C.c_int32), ("reserved", C.c_int32)]
 
 
 class bkModelConfig(C.Structure):
@@ -97,6 +98,7 @@ SIGNATURES = {
     "bkEventDestroy": (_I32, [_U64]),
     "bkLaunchCount": (_I32, [_PU64]),
     "bkTraceEnable": (_I32, [_U64, _I32]),
+    "bkTraceCtas": (_I32, [_U64, _I32]),
     "bkTraceDisable": (_I32, []),
     "bkGemvQ4K": (_I32, [C.POINTER(bkGemvArgs)]),
     "bkGemvQ4KSimple": (_I32, [_U64, _I32, _I32, _U64, _I32, _U64]),

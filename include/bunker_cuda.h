@@ -77,6 +77,10 @@ BK_API int32_t bkEventDestroy(uint64_t event);
  * 0 entry, 1 own weight copies issued, 2 dependency wait returned, 3 prologue done, 4 first weights landed, 5 exit.
  * A graph replays the records it was captured with.  Off by default. */
 BK_API int32_t bkTraceEnable(uint64_t dev_buf, int32_t max_launches);
+/* Per-CTA timeline of ONE GEMV launch: the gemv_launch_index-th bkGemvQ4K-class launch issued (or captured) after
+ * this call records, for every CTA c, dev_buf[4c..4c+3] = {entry, dependency wait returned, first weights landed in
+ * warp 0, latest warp exit} in %globaltimer ns.  dev_buf must hold 4 x 8 bytes per SM. */
+BK_API int32_t bkTraceCtas(uint64_t dev_buf, int32_t gemv_launch_index);
 BK_API int32_t bkTraceDisable(void);
 /* Number of kernels this library has launched since bkInit (graph replays count their kernels). */
 BK_API int32_t bkLaunchCount(uint64_t* out_count);
@@ -174,7 +178,8 @@ BK_API int32_t bkHeadNormRope(uint64_t in, int32_t in_stride, uint64_t w, uint64
  * qg: bf16 [B][Hq][2*HD] = per head q | gate (q_proj output); k, v: bf16 [B][Hkv*HD] projections.
  * The kernel norms+rotates q and k, appends k,v at row pos[b], attends over rows 0..pos[b],
  * and writes out bf16 [B][Hq*HD] = attention * sigmoid(gate).
- * caches: bf16 [B][Hkv][max_len][HD].  scratch: bkAttnScratchBytes() bytes. */
+ * caches: bf16 [B][Hkv][max_len][HD].  scratch: bkAttnScratchBytes() bytes, zeroed once before its first use
+ * (it ends with completion counters that the kernel re-arms itself). */
 typedef struct bkAttnArgs {
   uint64_t qg, k, v;
   uint64_t q_norm_w, k_norm_w, cos_t, sin_t;
@@ -188,6 +193,9 @@ typedef struct bkAttnArgs {
   float scale;
   int32_t fused_norm_rope; /* 1: as above. 0: qg holds ready q in [B][Hq*HD], gate in `gate`, cache already appended */
   uint64_t gate;     /* only for fused_norm_rope=0: bf16 [B][Hq*HD] */
+  int32_t cache_is_settled; /* 1: pos[] and the cache rows below pos[b] were NOT written by the launch that immediately
+                               precedes this one on the stream, so they may be read while that launch is still running */
+  int32_t reserved;
 } bkAttnArgs;
 BK_API int32_t bkAttnDecode(const bkAttnArgs* args);
 /* split length and warps per split the library uses for n rows */

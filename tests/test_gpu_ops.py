@@ -145,7 +145,7 @@ def _run_attn(c, cos_t, sin_t, split_len=0):
         W = 8
     d = {k: dev(v) for k, v in c.items() if isinstance(v, np.ndarray)}
     dc, ds = dev(cos_t), dev(sin_t)
-    scratch = R.DeviceBuffer(ops.attn_scratch_bytes(B, Hq, HD, ml, split_len))
+    scratch = R.DeviceBuffer.zeros(ops.attn_scratch_bytes(B, Hq, HD, ml, split_len))
     out = R.DeviceBuffer(B * Hq * HD * 2)
     ops.attn_decode(qg=d["qg"].ptr, k=d["k"].ptr, v=d["v"].ptr, q_norm_w=d["q_norm_w"].ptr, k_norm_w=d["k_norm_w"].ptr,
                     cos_t=dc.ptr, sin_t=ds.ptr, k_cache=d["k_cache"].ptr, v_cache=d["v_cache"].ptr, pos=d["pos"].ptr,
