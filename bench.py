@@ -31,6 +31,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 PROMPT_LEN = 32
+# dram__bytes_read.sum + dram__bytes_write.sum of one lm_head GEMV launch at batch 1 (ncu capture summarised in
+# profiles/gemv_q4k_lmhead_b1.md)
+NCU_GEMV_LMHEAD_TRAFFIC = 180862720
 METRIC = "q4k_hybrid_decode_tok_s"
 
 
@@ -200,21 +203,33 @@ def run_ours(args):
     value = K * B / (ms * 1e-3)
     tokens_resident = gm.tokens(PROMPT_LEN + W, K)
 
-    # ---- per-op profile of one eager step (events around every launch) ----
+    # ---- per-op profile of one eager step (event pair around every launch; launch-bound, shares only) ----
     prof = gm.step_profiled()
-    gemv_ms = sum(v[0] for k, v in prof.items() if k.startswith("gemv"))
-    gemv_calls = sum(v[1] for k, v in prof.items() if k.startswith("gemv"))
-    H = cfg.hidden
-    act_bytes = 0
-    for li in range(cfg.n_layers):  # bf16 activations read by the prologues and written by the epilogues, per launch
-        if cfg.is_full(li):
-            act_bytes += B * (2 * H + 2 * (cfg.qgate_dim + 2 * cfg.kv_dim)) + B * (2 * cfg.attn_q_heads * cfg.head_dim + 4 * H)
-        else:
-            act_bytes += B * (2 * H + 2 * (cfg.conv_width + cfg.z_dim) + 8 * cfg.gdn_v_heads) + B * (2 * cfg.z_dim + 4 * H)
-        act_bytes += B * (2 * H + 2 * cfg.intermediate) + B * (2 * cfg.intermediate + 4 * H)
-    act_bytes += B * (2 * H + 4 * cfg.vocab)
-    gemv_bytes = wbytes + act_bytes
-    achieved = gemv_bytes / (gemv_ms * 1e-3) / 1e9
+
+    # ---- roofline of the dominant kernel: the GEMV on its largest launch (this rank's lm_head shard, 175 MB at N=1,
+    #      larger than L2), back to back on the library stream between two events ----
+    from bunker_b200 import ops
+    d = M.local_dims(cfg, rank, world)
+    H, Vl = cfg.hidden, d["vocab"]
+    rowb = H // 256 * 144
+    table = gm.slab.ptr + gm.offsets["embed.weight"] + d["vocab_off"] * rowb
+    xin = R.DeviceBuffer.from_numpy(np.random.default_rng(1).integers(0, 65535, (B, H)).astype(np.uint16) & 0x3FFF | 0x3C00)
+    nw_ptr = gm.slab.ptr + gm.offsets["final.norm.weight"]
+    lg = R.DeviceBuffer(B * Vl * 4)
+    seg = [ops.gemv_seg(table, Vl, lg.ptr, R.BK_EPI_F32)]
+    reps = 20
+    for _ in range(3):
+        ops.gemv(xin.ptr, H, B, seg, prologue=R.BK_PRO_RMSNORM, norm_w=nw_ptr)
+    g0, g1 = R.Event(), R.Event()
+    g0.record()
+    for _ in range(reps):
+        ops.gemv(xin.ptr, H, B, seg, prologue=R.BK_PRO_RMSNORM, norm_w=nw_ptr)
+    g1.record()
+    g1.synchronize()
+    gemv_us = g0.elapsed_ms(g1) * 1e3 / reps
+    gemv_bytes = Vl * rowb + B * H * 2 + H * 2 + B * Vl * 4      # Q4_K rows + bf16 x + norm weights + f32 logits
+    achieved = gemv_bytes / (gemv_us * 1e-6) / 1e9
+    xin.free(), lg.free()
 
     # ---- end-to-end leg: host token in, host (id, logit) out, every step ----
     gm.reset()
@@ -259,10 +274,11 @@ def run_ours(args):
         "e2e": {"value": K * B / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 4 * B,
                 "d2h_bytes_per_step": 8 * B, "ms_per_step": e2e_ms / K, "same_tokens_as_resident_leg": same_stream},
         "gpu_launches": int(launches),
-        "roofline": {"bound": "hbm", "kernel": f"gemv_q4k_kernel<{B}>", "achieved": achieved, "peak": hbm_peak,
-                     "unit": "GB/s", "frac": achieved / hbm_peak, "traffic": None, "peak_source": peak_src,
-                     "launches_per_step": gemv_calls, "avg_launch_us": gemv_ms * 1e3 / gemv_calls,
-                     "algorithmic_bytes_per_step": gemv_bytes},
+        "roofline": {"bound": "hbm", "kernel": f"gemv_q4k_kernel<{B},{8 if B <= 2 else 4}>", "achieved": achieved,
+                     "peak": hbm_peak / world, "unit": "GB/s", "frac": achieved / (hbm_peak / world),
+                     "traffic": NCU_GEMV_LMHEAD_TRAFFIC if (world == 1 and B == 1) else None, "peak_source": peak_src,
+                     "launch": f"lm_head shard [{Vl} x {H}] Q4_K, RMSNorm+Q8_1 prologue, batch {B}",
+                     "avg_launch_us": gemv_us, "algorithmic_bytes_per_launch": gemv_bytes, "launches_timed": reps},
         "model_roofline": {"weight_bytes_per_step": wbytes, "achieved_gbs": wbytes / (ms / K * 1e-3) / 1e9,
                            "frac_of_hbm": wbytes / (ms / K * 1e-3) / 1e9 / hbm_peak,
                            "roofline_tok_s": hbm_peak * 1e9 / wbytes * B},

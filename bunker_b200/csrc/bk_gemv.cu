@@ -408,6 +408,33 @@ __device__ __forceinline__ void store_epilogue(const SegDev& sg, size_t o, float
   }
 }
 
+// Request the nr rows of a group (first virtual row v0) into its slot.  Rows that follow each other inside one
+// matrix are contiguous in memory, so a run of them is ONE bulk copy; a SwiGLU group is two runs (its gate rows,
+// then its up rows), which is why its rows sit in the slot as [gate rows | up rows] (see slot_row()).
+__device__ __forceinline__ void request_group(const GemvParams& p, int v0, int nr, uint32_t rowb, uint32_t dst, uint32_t bar) {
+  mbar_expect_tx(bar, nr * rowb);
+  const VRow first = decode_vrow(p, v0);
+  const SegDev& sg = p.segs[first.si];
+  if (sg.epi == BK_EPI_SWIGLU) {
+    const int half = nr >> 1;
+    bulk_g2s(dst, sg.W + (size_t)rowb * first.n, half * rowb, bar);
+    bulk_g2s(dst + half * rowb, sg.W2 + (size_t)rowb * first.n, half * rowb, bar);
+    return;
+  }
+  int done = 0;
+  while (done < nr) {  // one iteration unless the group straddles a segment boundary
+    const VRow vr = decode_vrow(p, v0 + done);
+    const SegDev& s2 = p.segs[vr.si];
+    int run = s2.n_rows - vr.n;
+    if (run > nr - done) run = nr - done;
+    bulk_g2s(dst + done * rowb, vr.row, run * rowb, bar);
+    done += run;
+  }
+}
+
+// position of group row r inside its slot (SwiGLU groups are stored gate rows first, then up rows)
+__device__ __forceinline__ int slot_row(bool swiglu, int r, int nr) { return swiglu ? (r >> 1) + (r & 1) * (nr >> 1) : r; }
+
 // One CTA per SM owns the contiguous virtual rows [c*rows_per_cta, ...).  Rows are processed in
 // groups of G by one warp (group g of the CTA belongs to warp g mod nw).  Each group has a slot of
 // G rows in shared memory and an mbarrier.  depth == 0 ("pool"): every group has its own slot and all
@@ -455,11 +482,7 @@ __global__ void __launch_bounds__(512, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kern
       if (g >= n_groups) break;
       const int slot = depth == 0 ? g : gi * nw + warp;
       const int nr = min(G, n_rows_cta - g * G);
-      mbar_expect_tx(bar_base + 8 * slot, nr * rowb);
-      for (int r = 0; r < nr; r++) {
-        VRow vr = decode_vrow(p, c0 + g * G + r);
-        bulk_g2s(slot_base + slot * slot_bytes + r * rowb, vr.row, rowb, bar_base + 8 * slot);
-      }
+      request_group(p, c0 + g * G, nr, rowb, slot_base + slot * slot_bytes, bar_base + 8 * slot);
     }
   }
   uint4 wpre = make_uint4(0, 0, 0, 0);  // norm weights are weights: fetched before the wait as well
@@ -482,6 +505,7 @@ __global__ void __launch_bounds__(512, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kern
   bk_stamp_max(p.trace, 1);  // (reuses slot 1) latest prologue end over all CTAs
 
   const int ri = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);  // row this lane reports
+  const bool swiglu = p.segs[0].epi == BK_EPI_SWIGLU;  // such a segment is always alone in its launch
   for (int gi = 0, g = warp; g < n_groups; gi++, g += nw) {
     const int slot = depth == 0 ? g : (gi % depth) * nw + warp;
     const uint32_t parity = depth == 0 ? 0u : (uint32_t)((gi / depth) & 1);
@@ -508,7 +532,7 @@ __global__ void __launch_bounds__(512, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kern
 #pragma unroll
         for (int r = 0; r < GMAX; r++) {
           if (r < nr) {
-            const WRegs w = decode_unit(load_unit_smem(wbase + r * rowb, u), pp);
+            const WRegs w = decode_unit(load_unit_smem(wbase + slot_row(swiglu, r, nr) * rowb, u), pp);
 #pragma unroll
             for (int b = 0; b < B; b++) acc[r][b] = __fadd_rn(acc[r][b], unit_val(w, xr[b]));
           }
@@ -517,7 +541,7 @@ __global__ void __launch_bounds__(512, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kern
 #pragma unroll
         for (int r = 0; r < GMAX; r++) {
           if (r < nr) {
-            const WRegs w = decode_unit(load_unit_smem(wbase + r * rowb, u), pp);
+            const WRegs w = decode_unit(load_unit_smem(wbase + slot_row(swiglu, r, nr) * rowb, u), pp);
 #pragma unroll
             for (int b = 0; b < B; b++) acc[r][b] = __fadd_rn(acc[r][b], unit_val(w, load_x(xs, d8s, s8s, b, u, nunits, nblk)));
           }
@@ -529,11 +553,7 @@ __global__ void __launch_bounds__(512, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kern
       const int g2 = g + depth * nw;
       if (g2 < n_groups) {
         const int nr2 = min(G, n_rows_cta - g2 * G);
-        mbar_expect_tx(bar_base + 8 * slot, nr2 * rowb);
-        for (int r = 0; r < nr2; r++) {
-          VRow vr = decode_vrow(p, c0 + g2 * G + r);
-          bulk_g2s(slot_base + slot * slot_bytes + r * rowb, vr.row, rowb, bar_base + 8 * slot);
-        }
+        request_group(p, c0 + g2 * G, nr2, rowb, slot_base + slot * slot_bytes, bar_base + 8 * slot);
       }
     }
     // reduce over lanes; lane (lane&3)==0 ends up with the sum of row ri of the group

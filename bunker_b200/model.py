@@ -243,6 +243,7 @@ class DecodeModel:
             offs[name] = total
             total += (weights[name].nbytes + 255) // 256 * 256
         self.slab = R.DeviceBuffer(total)
+        self.offsets = offs
         for name, _, _ in specs:
             a = np.ascontiguousarray(weights[name])
             R.cuHtoD(self.slab.ptr + offs[name], a)
