@@ -27,190 +27,9 @@
 // 80 bytes per 64 (conflict-free 128-bit reads at lane stride), plus per-block
 // d8 and s8 = d8*sum(q8) (exact in f32).  Three prologues fill it: ready-made
 // Q8_1 blocks, bf16 rows quantised in place, or bf16 rows through RMSNorm first.
-#include "bk_common.cuh"
-#include "bk_internal.h"
+#include "bk_gemv_shared.cuh"
 
 namespace {
-
-constexpr int kThreads = 256;   // threads of the canonical sum-of-squares order (and of the small kernels below)
-constexpr int kWarps = kThreads / 32;
-constexpr int kUnitWords = 20;  // 16 data words + 4 pad
-
-struct SegDev {
-  const uint8_t* W;
-  const uint8_t* W2;
-  void* out;
-  const uint16_t* res;
-  int n_rows;
-  int epi;
-  int ld_out;
-  int col_off;
-  int vrow_begin;  // first virtual row of this segment
-};
-
-struct GemvParams {
-  int K;
-  int n_segs;
-  int prologue;
-  int total_vrows;
-  int rows_per_cta;
-  int n_slots;       // weight slots (and mbarriers) per CTA
-  int depth;         // 0: one slot per group, all requested up front; >0: per-warp ring of this depth
-  int group_rows;    // rows one warp processes together (even when a SwiGLU segment is present)
-  const void* x;
-  const uint16_t* norm_w;
-  float eps;
-  int* status;       // device status word: set when a bounded wait gives up
-  unsigned long long* trace;  // timeline record of this launch, or null
-  unsigned long long* cta_trace;  // per-CTA timeline of this launch, or null
-  SegDev segs[4];
-};
-
-// ---- prologues ---------------------------------------------------------------
-
-// Q8_1 blocks [B][nblk][36] -> shared layout
-template <int B>
-__device__ void prologue_q8(const GemvParams& p, uint32_t* xs, float* d8s, float* s8s) {
-  const int nblk = p.K / 32, nunits = p.K / 64;
-  const uint32_t* src = reinterpret_cast<const uint32_t*>(p.x);
-  for (int i = threadIdx.x; i < B * nblk; i += blockDim.x) {
-    int b = i / nblk, blk = i - b * nblk;
-    const uint32_t* s = src + (size_t)i * 9;
-    uint32_t* dst = xs + ((size_t)b * nunits + (blk >> 1)) * kUnitWords + (blk & 1) * 8;
-    int qsum = 0;
-#pragma unroll
-    for (int k = 0; k < 8; k++) {
-      uint32_t w = s[k];
-      dst[k] = w;
-      qsum = bk_dp4a_ss(w, 0x01010101u, qsum);
-    }
-    float d8 = bk_q8half_to_f32((uint16_t)(s[8] & 0xffffu));
-    d8s[i] = d8;
-    s8s[i] = __fmul_rn(d8, (float)qsum);
-  }
-}
-
-// quantise 8 consecutive values held by this thread; the 4 threads of an aligned
-// lane group hold one 32-element block (packQ8_1, bench/bench.ts:53-72, in f32)
-__device__ __forceinline__ void quant_chunk(const float (&y)[8], int q, int b, int nunits, int nblk, uint32_t* xs,
-                                            float* d8s, float* s8s) {
-  float amax = 0.0f;
-#pragma unroll
-  for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(y[e]));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-  float d = __fdiv_rn(amax, 127.0f);
-  float id = (d == 0.0f) ? 1.0f : __fdiv_rn(1.0f, d);
-  int qs[8];
-  int qsum = 0;
-#pragma unroll
-  for (int e = 0; e < 8; e++) {
-    int v = __float2int_rd(fmaf(y[e], id, 0.5f));
-    v = max(-128, min(127, v));
-    qs[e] = v;
-    qsum += v;
-  }
-  qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
-  qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
-  uint32_t w0 = (uint32_t)(qs[0] & 0xff) | ((uint32_t)(qs[1] & 0xff) << 8) | ((uint32_t)(qs[2] & 0xff) << 16) |
-                ((uint32_t)(qs[3] & 0xff) << 24);
-  uint32_t w1 = (uint32_t)(qs[4] & 0xff) | ((uint32_t)(qs[5] & 0xff) << 8) | ((uint32_t)(qs[6] & 0xff) << 16) |
-                ((uint32_t)(qs[7] & 0xff) << 24);
-  int blk = q >> 2;
-  uint32_t* dst = xs + ((size_t)b * nunits + (blk >> 1)) * kUnitWords + (blk & 1) * 8 + (q & 3) * 2;
-  dst[0] = w0;
-  dst[1] = w1;
-  if ((q & 3) == 0) {
-    float d8 = bk_q8half_to_f32(bk_f32_to_f16_trunc(d));
-    d8s[b * nblk + blk] = d8;
-    s8s[b * nblk + blk] = __fmul_rn(d8, (float)qsum);
-  }
-}
-
-__device__ __forceinline__ void load_chunk_bf16(const uint16_t* row, int q, float (&y)[8]) {
-  uint4 v = *reinterpret_cast<const uint4*>(row + (size_t)q * 8);
-  y[0] = __uint_as_float(v.x << 16);
-  y[1] = __uint_as_float(v.x & 0xffff0000u);
-  y[2] = __uint_as_float(v.y << 16);
-  y[3] = __uint_as_float(v.y & 0xffff0000u);
-  y[4] = __uint_as_float(v.z << 16);
-  y[5] = __uint_as_float(v.z & 0xffff0000u);
-  y[6] = __uint_as_float(v.w << 16);
-  y[7] = __uint_as_float(v.w & 0xffff0000u);
-}
-
-// bf16 rows -> (optional RMSNorm -> bf16) -> Q8_1 in shared memory.
-// Sum of squares in the 256-thread block order: chunk q (8 elements) belongs to
-// thread q mod 256, fmaf chain inside; warp butterflies; the 8 warp sums in order.
-// wpre: the norm weights of chunk threadIdx.x, loaded by the caller before the dependency wait.
-template <int B, bool NORM>
-__device__ void prologue_bf16(const GemvParams& p, uint32_t* xs, float* d8s, float* s8s, float* red, const uint4 wpre) {
-  const int K = p.K, nblk = K / 32, nunits = K / 64, nchunk = K / 8;
-  const uint16_t* x = reinterpret_cast<const uint16_t*>(p.x);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const bool one_pass = nchunk <= kThreads;   // every chunk has its own thread among the first 256: keep it in registers
-  for (int b = 0; b < B; b++) {
-    const uint16_t* row = x + (size_t)b * K;
-    float rstd = 1.0f;
-    float y0[8];
-    const bool have0 = (int)threadIdx.x < nchunk;
-    if (have0) load_chunk_bf16(row, threadIdx.x, y0);
-    if (NORM) {
-      float acc = 0.0f;
-      if (threadIdx.x < kThreads) {  // the fixed 256-thread order, whatever the CTA size
-        if (have0) {
-#pragma unroll
-          for (int e = 0; e < 8; e++) acc = fmaf(y0[e], y0[e], acc);
-        }
-        for (int q = threadIdx.x + kThreads; q < nchunk; q += kThreads) {
-          float y[8];
-          load_chunk_bf16(row, q, y);
-#pragma unroll
-          for (int e = 0; e < 8; e++) acc = fmaf(y[e], y[e], acc);
-        }
-        acc = bk_warp_sum(acc);
-      }
-      __syncthreads();  // red[] reuse across batch rows
-      if (lane == 0 && warp < kWarps) red[warp] = acc;
-      __syncthreads();
-      float total = red[0];
-#pragma unroll
-      for (int w = 1; w < kWarps; w++) total = __fadd_rn(total, red[w]);
-      float ms = __fdiv_rn(total, (float)K);
-      rstd = bk_rcp_sqrt(__fadd_rn(ms, p.eps));
-    }
-    for (int q = threadIdx.x; q < nchunk; q += blockDim.x) {
-      float y[8];
-      if (q == (int)threadIdx.x) {
-#pragma unroll
-        for (int e = 0; e < 8; e++) y[e] = y0[e];
-      } else {
-        load_chunk_bf16(row, q, y);
-      }
-      if (NORM) {
-        float wv[8];
-        if (q == (int)threadIdx.x) {
-          wv[0] = __uint_as_float(wpre.x << 16); wv[1] = __uint_as_float(wpre.x & 0xffff0000u);
-          wv[2] = __uint_as_float(wpre.y << 16); wv[3] = __uint_as_float(wpre.y & 0xffff0000u);
-          wv[4] = __uint_as_float(wpre.z << 16); wv[5] = __uint_as_float(wpre.z & 0xffff0000u);
-          wv[6] = __uint_as_float(wpre.w << 16); wv[7] = __uint_as_float(wpre.w & 0xffff0000u);
-        } else {
-          load_chunk_bf16(p.norm_w, q, wv);
-        }
-#pragma unroll
-        for (int e = 0; e < 8; e += 2) {
-          float v0 = __fmul_rn(__fmul_rn(y[e], rstd), __fadd_rn(1.0f, wv[e]));
-          float v1 = __fmul_rn(__fmul_rn(y[e + 1], rstd), __fadd_rn(1.0f, wv[e + 1]));
-          uint32_t pk = bk_f32x2_to_bf16x2(v0, v1);
-          y[e] = __uint_as_float(pk << 16);
-          y[e + 1] = __uint_as_float(pk & 0xffff0000u);
-        }
-      }
-      quant_chunk(y, q, b, nunits, nblk, xs, d8s, s8s);
-    }
-    (void)one_pass;
-  }
-}
 
 // ---- main kernel -------------------------------------------------------------
 
@@ -299,35 +118,6 @@ __device__ __forceinline__ float unit_val(const WRegs& w, const XRegs& x) {
   return fmaf(w.d, accd, -t);
 }
 
-// ---- virtual rows --------------------------------------------------------------
-// The rows of all segments of a launch are numbered consecutively.  A SwiGLU segment contributes
-// 2*n_rows virtual rows: even = gate row, odd = the up row of the same output column.
-struct VRow {
-  const uint8_t* row;
-  int si;  // segment
-  int n;   // output column within the segment
-};
-
-__device__ __forceinline__ VRow decode_vrow(const GemvParams& p, int v) {
-  int si = 0;
-#pragma unroll
-  for (int s = 1; s < 4; s++)
-    if (s < p.n_segs && v >= p.segs[s].vrow_begin) si = s;
-  const SegDev& sg = p.segs[si];
-  const int t = v - sg.vrow_begin;
-  const size_t rowb = (size_t)(p.K / 256) * 144;
-  VRow r;
-  r.si = si;
-  if (sg.epi == BK_EPI_SWIGLU) {
-    r.n = t >> 1;
-    r.row = ((t & 1) ? sg.W2 : sg.W) + rowb * (size_t)r.n;
-  } else {
-    r.n = t;
-    r.row = sg.W + rowb * (size_t)t;
-  }
-  return r;
-}
-
 __device__ __forceinline__ RowRegs load_unit_smem(const uint8_t* row, int u) {
   const uint8_t* sb = row + (size_t)(u >> 2) * 144;
   RowRegs r;
@@ -336,35 +126,6 @@ __device__ __forceinline__ RowRegs load_unit_smem(const uint8_t* row, int u) {
   r.qa = q[0];
   r.qb = q[1];
   return r;
-}
-
-// ---- mbarrier + bulk async copy (global -> this CTA's shared memory, no multicast) ----
-BK_DEVINL uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-BK_DEVINL void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-BK_DEVINL void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-BK_DEVINL void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
-BK_DEVINL bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// bounded: a copy that never lands sets the status word instead of hanging the GPU
-BK_DEVINL void mbar_wait_bounded(uint32_t bar, uint32_t parity, int* status) {
-  for (int it = 0; it < (1 << 22); it++)
-    if (mbar_try_wait(bar, parity)) return;
-  if (status) atomicExch(status, BK_ERR_TIMEOUT);
 }
 
 // Sum 8 per-lane values over the warp with 9 shuffles instead of 40: at each of the first three
@@ -393,19 +154,6 @@ __device__ __forceinline__ float warp_sum8(const float (&v)[8]) {
   y = __fadd_rn(y, __shfl_xor_sync(0xffffffffu, y, 2));
   y = __fadd_rn(y, __shfl_xor_sync(0xffffffffu, y, 1));
   return y;
-}
-
-__device__ __forceinline__ void store_epilogue(const SegDev& sg, size_t o, float y, float yup) {
-  if (sg.epi == BK_EPI_SWIGLU) {
-    float sig = bk_sigmoidf(y);
-    reinterpret_cast<uint16_t*>(sg.out)[o] = bk_f32_to_bf16(__fmul_rn(__fmul_rn(y, sig), yup));
-  } else if (sg.epi == BK_EPI_F32) {
-    reinterpret_cast<float*>(sg.out)[o] = y;
-  } else if (sg.epi == BK_EPI_BF16) {
-    reinterpret_cast<uint16_t*>(sg.out)[o] = bk_f32_to_bf16(y);
-  } else {  // BK_EPI_ADD_BF16
-    reinterpret_cast<uint16_t*>(sg.out)[o] = bk_f32_to_bf16(__fadd_rn(y, bk_bf16_to_f32(sg.res[o])));
-  }
 }
 
 // Request the nr rows of a group (first virtual row v0) into its slot.  Rows that follow each other inside one
@@ -495,11 +243,11 @@ __global__ void __launch_bounds__(512, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kern
   if (ctr && threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); ctr[1] = t_; }
 
   if (p.prologue == BK_PRO_Q8)
-    prologue_q8<B>(p, xs, d8s, s8s);
+    prologue_q8(p, B, xs, d8s, s8s);
   else if (p.prologue == BK_PRO_BF16)
-    prologue_bf16<B, false>(p, xs, d8s, s8s, red, wpre);
+    prologue_bf16<false>(p, B, xs, d8s, s8s, red, wpre);
   else
-    prologue_bf16<B, true>(p, xs, d8s, s8s, red, wpre);
+    prologue_bf16<true>(p, B, xs, d8s, s8s, red, wpre);
   __syncthreads();
   bk_stamp(p.trace, 3);
   bk_stamp_max(p.trace, 1);  // (reuses slot 1) latest prologue end over all CTAs
@@ -704,6 +452,8 @@ __global__ void quant_q8_1_kernel(const void* x, int K, int B, uint8_t* out) {
 
 // ---- host entry points ---------------------------------------------------------
 
+int32_t bk_gemv_mma_launch(void* params, int K, int B, int vrows, bool has_swiglu);  // bk_gemv_mma.cu
+
 int32_t bk_gemv_launch(const bkGemvArgs& a) {
   BkContext& c = bk_ctx();
   BK_ARG(a.K > 0 && a.K % 256 == 0, "bkGemvQ4K: K=%d is not a positive multiple of 256", a.K);
@@ -759,6 +509,8 @@ int32_t bk_gemv_launch(const bkGemvArgs& a) {
   p.cta_trace = nullptr;
   if (c.cta_trace && c.cta_trace_seen++ == c.cta_trace_launch) p.cta_trace = c.cta_trace;
 
+  if (a.B >= 3) return bk_gemv_mma_launch(&p, a.K, a.B, vrows, has_swiglu);
+
   // ---- launch shape ----
   const size_t rowb = (size_t)(a.K / 256) * 144;
   const size_t limit = c.smem_optin - 1024;
@@ -801,6 +553,8 @@ int32_t bk_gemv_launch(const bkGemvArgs& a) {
     n_slots = depth * nw;
   }
   p.group_rows = G;
+  p.x_unit_words = kUnitWords;
+  p.x_row_words = (a.K / 64) * kUnitWords;
   p.rows_per_cta = rpc;
   p.n_slots = n_slots;
   p.depth = depth;
