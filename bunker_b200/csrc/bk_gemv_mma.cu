@@ -23,8 +23,7 @@
 namespace {
 
 constexpr int kTileRows = 16;
-constexpr int kMmaWarps = 16;       // 4 tiles x 4 sub-block pairs per round
-constexpr int kTilesPerRound = 4;
+constexpr int kMaxTilesPerRound = 4;  // a round = tiles_per_round tiles x 4 sub-block pairs = up to 16 warps
 
 __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -63,7 +62,7 @@ __device__ __forceinline__ float unit_value(const RowHdr& h, int i0, int i1, flo
 
 // Shared memory: xs [B][K/4 + 4] words | d8s [B][K/32] | s8s [B][K/32] | red[8] | bars[n_slots] | part[2][4 tiles][4 p][16][8] f32 |
 // tile slots [n_slots][16 rows][rowb+16].
-__global__ void __launch_bounds__(kMmaWarps * 32, 1) gemv_q4k_mma_kernel(const GemvParams p, const int B) {
+__global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kernel(const GemvParams p, const int B) {
   bk_pdl_trigger();
   bk_stamp(p.trace, 0);
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -73,8 +72,10 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 1) gemv_q4k_mma_kernel(const G
   float* s8s = d8s + (size_t)B * nblk;
   float* red = s8s + (size_t)B * nblk;
   uint64_t* bars = reinterpret_cast<uint64_t*>(red + 8);
+  const int tpr = blockDim.x >> 7;   // tiles per round (4 or 2): four warps per tile
+  const int nwarps = blockDim.x >> 5;
   float* part = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(bars + p.n_slots) + 15) & ~(uintptr_t)15);
-  uint8_t* slots = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(part + 2 * kTilesPerRound * 4 * 128) + 127) & ~(uintptr_t)127);
+  uint8_t* slots = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(part + 2 * tpr * 4 * 128) + 127) & ~(uintptr_t)127);
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, tid = threadIdx.x;
   // tiles are dealt out evenly: the first tiles_extra CTAs own one tile more than the others
@@ -104,13 +105,13 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 1) gemv_q4k_mma_kernel(const G
   };
   // ---- before the dependency wait: weights only ----
   if (lane == 0) {
-    for (int s = warp; s < n_slots; s += kMmaWarps) mbar_init(bar_base + 8 * s, 1);
+    for (int s = warp; s < n_slots; s += nwarps) mbar_init(bar_base + 8 * s, 1);
   }
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncthreads();
   if (lane == 0) {
-    for (int t = warp; t < n_tiles && t < n_slots; t += kMmaWarps) request_tile(t, t);
+    for (int t = warp; t < n_tiles && t < n_slots; t += nwarps) request_tile(t, t);
   }
   uint4 wpre = make_uint4(0, 0, 0, 0);
   if (p.prologue == BK_PRO_RMSNORM && tid < K / 8) wpre = __ldg(reinterpret_cast<const uint4*>(p.norm_w) + tid);
@@ -129,10 +130,10 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 1) gemv_q4k_mma_kernel(const G
   const int tq = warp >> 2;                   // tile position inside a round
   const int col0 = 2 * j, col1 = 2 * j + 1;   // C columns of this lane
   const bool bcol = R < B;                    // B-fragment column = R: zero beyond the batch
-  const int n_rounds = (n_tiles + kTilesPerRound - 1) / kTilesPerRound;
+  const int n_rounds = (n_tiles + tpr - 1) / tpr;
 
   for (int rd = 0; rd < n_rounds; rd++) {
-    const int t = rd * kTilesPerRound + tq;
+    const int t = rd * tpr + tq;
     float T[4] = {0.0f, 0.0f, 0.0f, 0.0f};    // (R,col0) (R,col1) (R+8,col0) (R+8,col1)
     if (t < n_tiles) {
       const int slot = t % n_slots;
@@ -194,7 +195,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 1) gemv_q4k_mma_kernel(const G
     }
     __syncwarp();
     // ring refill: once the four p-warps of a tile are done with a slot the round barrier below releases it
-    float* pw = part + (size_t)(rd & 1) * (kTilesPerRound * 4 * 128) + (size_t)(tq * 4 + tp) * 128;
+    float* pw = part + (size_t)(rd & 1) * (tpr * 4 * 128) + (size_t)(tq * 4 + tp) * 128;
     pw[R * 8 + col0] = T[0];
     pw[R * 8 + col1] = T[1];
     pw[(R + 8) * 8 + col0] = T[2];
@@ -207,8 +208,8 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 1) gemv_q4k_mma_kernel(const G
     // epilogue: thread -> (tile position, row, column)
     {
       const int eq = tid >> 7, er = (tid >> 3) & 15, ec = tid & 7;
-      const int et = rd * kTilesPerRound + eq;
-      const float* pr = part + (size_t)(rd & 1) * (kTilesPerRound * 4 * 128) + (size_t)(eq * 4) * 128 + er * 8 + ec;
+      const int et = rd * tpr + eq;
+      const float* pr = part + (size_t)(rd & 1) * (tpr * 4 * 128) + (size_t)(eq * 4) * 128 + er * 8 + ec;
       if (et < n_tiles && ec < B) {
         const int nr = min(kTileRows, n_rows_cta - et * kTileRows);
         const float y = __fadd_rn(__fadd_rn(pr[0], pr[2 * 128]), __fadd_rn(pr[1 * 128], pr[3 * 128]));
@@ -232,9 +233,9 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 1) gemv_q4k_mma_kernel(const G
   bk_stamp_max(p.trace, 6);
 }
 
-size_t mma_fixed_smem(int K, int B, int n_slots) {
+size_t mma_fixed_smem(int K, int B, int n_slots, int tpr) {
   return (size_t)B * (K / 4 + 4) * 4 + (size_t)B * (K / 32) * 8 + 32 + (size_t)n_slots * 8 + 16 +
-         (size_t)2 * kTilesPerRound * 4 * 128 * 4 + 128;
+         (size_t)2 * tpr * 4 * 128 * 4 + 128;
 }
 
 }  // namespace
@@ -249,13 +250,17 @@ int32_t bk_gemv_mma_launch(void* params, int K, int B, int vrows, bool has_swigl
   const int grid = tiles < c.sm_count ? tiles : c.sm_count;
   const int base = tiles / grid, extra = tiles % grid;
   const int tpc = base + (extra ? 1 : 0);         // most tiles any CTA owns
-  int n_slots = tpc;                               // pool: every tile of the CTA has its slot
-  if (mma_fixed_smem(K, B, tpc) + (size_t)tpc * tile_bytes > limit) {
-    // ring of whole rounds (4 tiles)
-    int rounds = (int)((limit - mma_fixed_smem(K, B, 64)) / (kTilesPerRound * tile_bytes));
-    BK_ARG(rounds >= 1, "bkGemvQ4K: K=%d B=%d does not fit in shared memory on the tensor-core path", K, B);
+  // tiles per round: as many as fit (4, 2 or 1); slots: the CTA's whole share if it fits (every copy is then
+  // requested before the dependency wait), else a ring of whole rounds
+  int tpr = kMaxTilesPerRound;
+  while (tpr > 2 && mma_fixed_smem(K, B, 64, tpr) + (size_t)tpr * tile_bytes > limit) tpr >>= 1;  // >= 256 threads for the prologue
+  BK_ARG(mma_fixed_smem(K, B, 64, tpr) + (size_t)tpr * tile_bytes <= limit,
+         "bkGemvQ4K: K=%d with batch %d needs more shared memory than an SM has on the tensor-core path (batch <= 2 has no such limit)", K, B);
+  int n_slots = (tpc + tpr - 1) / tpr * tpr;
+  if (mma_fixed_smem(K, B, n_slots, tpr) + (size_t)n_slots * tile_bytes > limit) {
+    int rounds = (int)((limit - mma_fixed_smem(K, B, 64, tpr)) / ((size_t)tpr * tile_bytes));
     if (rounds > 8) rounds = 8;
-    n_slots = rounds * kTilesPerRound;
+    n_slots = rounds * tpr;
   }
   p.tiles_base = base;
   p.tiles_extra = extra;
@@ -266,13 +271,13 @@ int32_t bk_gemv_mma_launch(void* params, int K, int B, int vrows, bool has_swigl
   p.group_rows = kTileRows;
   p.x_unit_words = 16;
   p.x_row_words = K / 4 + 4;
-  const size_t smem = mma_fixed_smem(K, B, n_slots) + (size_t)n_slots * tile_bytes;
+  const size_t smem = mma_fixed_smem(K, B, n_slots, tpr) + (size_t)n_slots * tile_bytes;
   static size_t configured = 0;
   if (smem > configured) {
     BK_CUDA(cudaFuncSetAttribute(gemv_q4k_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = smem;
   }
-  BK_CUDA(bk_launch_pdl(gemv_q4k_mma_kernel, dim3(grid), dim3(kMmaWarps * 32), smem, p, B));
+  BK_CUDA(bk_launch_pdl(gemv_q4k_mma_kernel, dim3(grid), dim3(tpr * 128), smem, p, B));
   BK_CHECK_LAUNCH();
   return BK_OK;
 }

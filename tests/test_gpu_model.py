@@ -92,3 +92,39 @@ def test_full_size_model_first_steps_match_oracle(bk):
         assert_same_bits(gm.logits(), om.logits, f"logits at step {t}")
     assert np.isfinite(om.logits).all()
     gm.destroy()
+
+
+def test_scaled_model_shapes_first_steps_match_oracle(bk):
+    """configs[4] shapes (hidden 5120, 16/48 GDN heads, 24/4 attention heads of 256, FFN 17408 = 68 superblocks) on a
+    4-layer stack with a reduced vocabulary: exercises K = 5120, 6144 and 17408 and group size 6 in attention."""
+    cfg = M.CONFIG_HYBRID_64L.with_(n_layers=4, vocab=8192, max_len=64)
+    w = M.synth_weights(cfg, seed=11)
+    gm = M.DecodeModel(cfg, w, batch=1)
+    info = gm.info()
+    om = OracleModel(cfg, w, batch=1, split_len=info["split_len"], attn_warps=info["attn_warps"])
+    prompt = np.random.default_rng(4).integers(0, cfg.vocab, (3, 1)).astype(np.int32)
+    ids_g = ids_o = None
+    for t in range(5):
+        ids_o, val_o = om.step(prompt[t] if t < 3 else ids_o)
+        ids_g, val_g = gm.step(prompt[t] if t < 3 else ids_g)
+        assert np.array_equal(ids_g, ids_o), f"step {t}"
+        assert_same_bits(gm.logits(), om.logits, f"logits at step {t}")
+    gm.destroy()
+
+
+def test_scaled_model_shapes_batch8_tensor_core_path(bk):
+    """Same head shapes at batch 8 (int8 tensor-core GEMV path, K = 5120 and 6144).  The FFN is narrowed to 6144:
+    at batch >= 3 a K of 17408 does not fit an SM's shared memory on that path and is rejected."""
+    cfg = M.CONFIG_HYBRID_64L.with_(n_layers=4, vocab=4096, max_len=32, intermediate=6144)
+    w = M.synth_weights(cfg, seed=12)
+    gm = M.DecodeModel(cfg, w, batch=8)
+    info = gm.info()
+    om = OracleModel(cfg, w, batch=8, split_len=info["split_len"], attn_warps=info["attn_warps"])
+    prompt = np.random.default_rng(5).integers(0, cfg.vocab, (2, 8)).astype(np.int32)
+    ids_g = ids_o = None
+    for t in range(3):
+        ids_o, _ = om.step(prompt[t] if t < 2 else ids_o)
+        ids_g, _ = gm.step(prompt[t] if t < 2 else ids_g)
+        assert np.array_equal(ids_g, ids_o), f"step {t}"
+    assert_same_bits(gm.logits(), om.logits, "logits")
+    gm.destroy()
