@@ -555,6 +555,7 @@ int32_t bk_gemv_launch(const bkGemvArgs& a) {
   p.group_rows = G;
   p.x_unit_words = kUnitWords;
   p.x_row_words = (a.K / 64) * kUnitWords;
+  p.x_scale_ld = a.K / 32;
   p.rows_per_cta = rpc;
   p.n_slots = n_slots;
   p.depth = depth;

@@ -66,11 +66,11 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
   bk_pdl_trigger();
   bk_stamp(p.trace, 0);
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  const int K = p.K, nblk = K / 32, nsb = K / 256;
+  const int K = p.K, nsb = K / 256;
   uint32_t* xs = reinterpret_cast<uint32_t*>(smem_raw);
   float* d8s = reinterpret_cast<float*>(xs + (size_t)B * p.x_row_words);
-  float* s8s = d8s + (size_t)B * nblk;
-  float* red = s8s + (size_t)B * nblk;
+  float* s8s = d8s + (size_t)B * p.x_scale_ld;
+  float* red = s8s + (size_t)B * p.x_scale_ld;
   uint64_t* bars = reinterpret_cast<uint64_t*>(red + 8);
   const int tpr = blockDim.x >> 7;   // tiles per round (4 or 2): four warps per tile
   const int nwarps = blockDim.x >> 5;
@@ -129,7 +129,14 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
   const int tp = warp & 3;                    // sub-block pair of this warp
   const int tq = warp >> 2;                   // tile position inside a round
   const int col0 = 2 * j, col1 = 2 * j + 1;   // C columns of this lane
-  const bool bcol = R < B;                    // B-fragment column = R: zero beyond the batch
+  // columns beyond the batch read the last real column; their results are never stored
+  const int cR = min(R, B - 1), ca = min(col0, B - 1), cb = min(col1, B - 1);
+  const uint32_t* xbase = xs + (size_t)cR * p.x_row_words + tp * 16 + j;
+  const int ld8 = p.x_scale_ld;
+  const float* d8a = d8s + ca * ld8 + 2 * tp;
+  const float* s8a = s8s + ca * ld8 + 2 * tp;
+  const float* d8b = d8s + cb * ld8 + 2 * tp;
+  const float* s8b = s8s + cb * ld8 + 2 * tp;
   const int n_rounds = (n_tiles + tpr - 1) / tpr;
 
   for (int rd = 0; rd < n_rounds; rd++) {
@@ -142,40 +149,37 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
       if (rd == 0) bk_stamp(p.trace, 4);
       const uint8_t* rowA = slots + (size_t)slot * slot_bytes + R * rstride;
       const uint8_t* rowB = rowA + 8 * rstride;
+      const uint32_t qoff = 16 + tp * 32 + 4 * j;
       // classes in the order 0,4,2,6,1,5,3,7 so the tree closes with three live partial sums per value
       float stk0[4], stk1[4];
-#pragma unroll 1
+#pragma unroll
       for (int ci = 0; ci < 8; ci++) {
         const int c = ((ci & 1) << 2) | (ci & 2) | ((ci >> 2) & 1);
         float P[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         for (int s = c; s < nsb; s += 8) {
           const uint8_t* sa = rowA + s * 144;
           const uint8_t* sb = rowB + s * 144;
-          const RowHdr ha = decode_hdr(sa, tp), hb = decode_hdr(sb, tp);
-          const uint32_t qa0 = *reinterpret_cast<const uint32_t*>(sa + 16 + tp * 32 + 4 * j);
-          const uint32_t qa2 = *reinterpret_cast<const uint32_t*>(sa + 16 + tp * 32 + 16 + 4 * j);
-          const uint32_t qb0 = *reinterpret_cast<const uint32_t*>(sb + 16 + tp * 32 + 4 * j);
-          const uint32_t qb2 = *reinterpret_cast<const uint32_t*>(sb + 16 + tp * 32 + 16 + 4 * j);
-          const int u = 4 * s + tp;
-          const uint32_t* xr = xs + (size_t)(bcol ? R : 0) * p.x_row_words + u * 16;
-          const uint32_t x00 = bcol ? xr[j] : 0u, x01 = bcol ? xr[4 + j] : 0u;        // sub-block 2p
-          const uint32_t x10 = bcol ? xr[8 + j] : 0u, x11 = bcol ? xr[12 + j] : 0u;   // sub-block 2p+1
+          const uint32_t qa0 = *reinterpret_cast<const uint32_t*>(sa + qoff);
+          const uint32_t qa2 = *reinterpret_cast<const uint32_t*>(sa + qoff + 16);
+          const uint32_t qb0 = *reinterpret_cast<const uint32_t*>(sb + qoff);
+          const uint32_t qb2 = *reinterpret_cast<const uint32_t*>(sb + qoff + 16);
+          const uint32_t* xr = xbase + s * 64;
+          const uint32_t x00 = xr[0], x01 = xr[4], x10 = xr[8], x11 = xr[12];
           int ilo[4] = {0, 0, 0, 0}, ihi[4] = {0, 0, 0, 0};
           mma_s8(ilo, qa0 & 0x0f0f0f0fu, qb0 & 0x0f0f0f0fu, qa2 & 0x0f0f0f0fu, qb2 & 0x0f0f0f0fu, x00, x01);
           mma_s8(ihi, (qa0 >> 4) & 0x0f0f0f0fu, (qb0 >> 4) & 0x0f0f0f0fu, (qa2 >> 4) & 0x0f0f0f0fu, (qb2 >> 4) & 0x0f0f0f0fu,
                  x10, x11);
-          // scales of the two columns this lane holds (columns beyond the batch read column 0 and are discarded)
-          const int ca = col0 < B ? col0 : 0, cb = col1 < B ? col1 : 0;
-          const float2 d8a = *reinterpret_cast<const float2*>(d8s + ca * nblk + 2 * u);
-          const float2 s8a = *reinterpret_cast<const float2*>(s8s + ca * nblk + 2 * u);
-          const float2 d8b = *reinterpret_cast<const float2*>(d8s + cb * nblk + 2 * u);
-          const float2 s8b = *reinterpret_cast<const float2*>(s8s + cb * nblk + 2 * u);
-          P[0] = __fadd_rn(P[0], unit_value(ha, ilo[0], ihi[0], d8a, s8a));
-          P[1] = __fadd_rn(P[1], unit_value(ha, ilo[1], ihi[1], d8b, s8b));
-          P[2] = __fadd_rn(P[2], unit_value(hb, ilo[2], ihi[2], d8a, s8a));
-          P[3] = __fadd_rn(P[3], unit_value(hb, ilo[3], ihi[3], d8b, s8b));
+          const RowHdr ha = decode_hdr(sa, tp), hb = decode_hdr(sb, tp);
+          const float2 da = *reinterpret_cast<const float2*>(d8a + 8 * s);
+          const float2 sa8 = *reinterpret_cast<const float2*>(s8a + 8 * s);
+          const float2 db = *reinterpret_cast<const float2*>(d8b + 8 * s);
+          const float2 sb8 = *reinterpret_cast<const float2*>(s8b + 8 * s);
+          P[0] = __fadd_rn(P[0], unit_value(ha, ilo[0], ihi[0], da, sa8));
+          P[1] = __fadd_rn(P[1], unit_value(ha, ilo[1], ihi[1], db, sb8));
+          P[2] = __fadd_rn(P[2], unit_value(hb, ilo[2], ihi[2], da, sa8));
+          P[3] = __fadd_rn(P[3], unit_value(hb, ilo[3], ihi[3], db, sb8));
         }
-        // tree: ci 0,1 -> a = P0+P4; ci 2,3 -> b = P2+P6, ab = a+b; ci 4,5 -> a' ; ci 6,7 -> b', T = ab + (a'+b')
+        // tree: ci 0,1 -> a = P0+P4; ci 2,3 -> b = P2+P6, ab = a+b; ci 4,5 -> a'; ci 6,7 -> b', T = ab + (a'+b')
 #pragma unroll
         for (int v = 0; v < 4; v++) {
           if ((ci & 1) == 0) {
@@ -234,7 +238,7 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
 }
 
 size_t mma_fixed_smem(int K, int B, int n_slots, int tpr) {
-  return (size_t)B * (K / 4 + 4) * 4 + (size_t)B * (K / 32) * 8 + 32 + (size_t)n_slots * 8 + 16 +
+  return (size_t)B * (K / 4 + 4) * 4 + (size_t)B * (K / 32 + 2) * 8 + 32 + (size_t)n_slots * 8 + 16 +
          (size_t)2 * tpr * 4 * 128 * 4 + 128;
 }
 
@@ -271,6 +275,7 @@ int32_t bk_gemv_mma_launch(void* params, int K, int B, int vrows, bool has_swigl
   p.group_rows = kTileRows;
   p.x_unit_words = 16;
   p.x_row_words = K / 4 + 4;
+  p.x_scale_ld = K / 32 + 2;   // two floats of padding: the four column pairs of a quad land in different banks
   const size_t smem = mma_fixed_smem(K, B, n_slots, tpr) + (size_t)n_slots * tile_bytes;
   static size_t configured = 0;
   if (smem > configured) {

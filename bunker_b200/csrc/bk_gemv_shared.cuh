@@ -35,6 +35,7 @@ struct GemvParams {
   int group_rows;    // rows one warp processes together (even when a SwiGLU segment is present)
   int x_unit_words;  // words one 64-value unit of the staged activation occupies (16 data + padding)
   int x_row_words;   // words between batch rows of the staged activation
+  int x_scale_ld;    // floats between batch rows of the staged block scales d8 / s8
   int tiles_base;    // tensor-core path: every CTA owns tiles_base 16-row tiles, the first tiles_extra CTAs one more
   int tiles_extra;
   const void* x;
@@ -64,8 +65,8 @@ __device__ void prologue_q8(const GemvParams& p, const int B, uint32_t* xs, floa
       qsum = bk_dp4a_ss(w, 0x01010101u, qsum);
     }
     float d8 = bk_q8half_to_f32((uint16_t)(s[8] & 0xffffu));
-    d8s[i] = d8;
-    s8s[i] = __fmul_rn(d8, (float)qsum);
+    d8s[b * p.x_scale_ld + blk] = d8;
+    s8s[b * p.x_scale_ld + blk] = __fmul_rn(d8, (float)qsum);
   }
 }
 
@@ -101,8 +102,8 @@ __device__ __forceinline__ void quant_chunk(const GemvParams& p, const float (&y
   dst[1] = w1;
   if ((q & 3) == 0) {
     float d8 = bk_q8half_to_f32(bk_f32_to_f16_trunc(d));
-    d8s[b * nblk + blk] = d8;
-    s8s[b * nblk + blk] = __fmul_rn(d8, (float)qsum);
+    d8s[b * p.x_scale_ld + blk] = d8;
+    s8s[b * p.x_scale_ld + blk] = __fmul_rn(d8, (float)qsum);
   }
 }
 
