@@ -152,8 +152,9 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8xint4->int32, f32 accumulate", "data": "synthetic",
-        "config": {"workload": f"configs[3] hybrid 24-layer Q4_K decode, batch {args.batch}, CPU oracle",
-                   "batch": args.batch, "inputs": "weights larger than L2"},
+        "config": {"workload": f"configs[3] hybrid 24-layer Q4_K decode (hidden 2048, vocab 151936), batch {args.batch}, "
+                               f"{PROMPT_LEN}-token random prompt then greedy", "batch": args.batch, "parallelism": "cpu",
+                   "inputs": "weights (1.12 GB/step) larger than L2, no flush", "max_len": cfg.max_len},
         "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
