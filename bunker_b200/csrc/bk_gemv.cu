@@ -189,11 +189,11 @@ __device__ __forceinline__ int slot_row(bool swiglu, int r, int nr) { return swi
 // copies are issued before the dependency wait.  depth > 0 ("ring"): a warp owns `depth` slots and
 // refills a slot with its next group as soon as the slot is consumed.
 template <int B, int GMAX>
-__global__ void __launch_bounds__(512, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(576, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kernel(const GemvParams p) {
   bk_pdl_trigger();
   bk_stamp(p.trace, 0);
   unsigned long long* ctr = p.cta_trace ? p.cta_trace + 4 * blockIdx.x : nullptr;
-  if (ctr && threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); ctr[0] = t_; ctr[3] = 0; }
+  if (ctr && threadIdx.x == 0) { unsigned int sm_; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm_)); ctr[0] = sm_; ctr[3] = 0; }
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int K = p.K, nunits = K / 64, nblk = K / 32;
   const int nw = blockDim.x >> 5;
@@ -519,20 +519,28 @@ int32_t bk_gemv_launch(const bkGemvArgs& a) {
   int rpc = (vrows + grid - 1) / grid;
   rpc = (rpc + 1) & ~1;
   grid = (vrows + rpc - 1) / rpc;
+  // Occupancy classes.  The hardware may put two CTAs of one grid on the same SM when two slots are free, which
+  // makes that SM finish last.  Two classes keep every GEMV grid at one CTA per SM while still letting the NEXT
+  // kernel's CTA share the SM (so its weight copies run under this kernel):
+  //   class A (large weight slice): > half of the SM's shared memory, <= 14 warps  -> two A CTAs never share an SM
+  //   class B (small weight slice): 18 warps (> half of the register file at 64 registers) -> nor do two B CTAs
+  // and A + B fit together (65,536 registers, < 227 KB).  A decode layer alternates A and B launches.
+  const size_t slice_bytes = (size_t)rpc * rowb;
+  const bool class_a = slice_bytes > 56 * 1024;
+  const int max_warps = class_a ? 14 : 16;
   // rows per group: one group per warp when the CTA's rows allow it (a single round, evenly loaded), capped by the
   // register budget; a SwiGLU launch keeps gate/up pairs together (even group size)
   const int gmax = gemv_gmax(a.B);
-  int G = (rpc + 15) / 16;
+  int G = (rpc + max_warps - 1) / max_warps;
   if (G < 1) G = 1;
   if (has_swiglu) G = (G + 1) & ~1;
   if (G > gmax) G = gmax;
   int n_groups = (rpc + G - 1) / G;
-  int nw = n_groups < 8 ? 8 : (n_groups > 16 ? 16 : n_groups);
-  // pool if the CTA's whole slice fits in about half of the SM's shared memory (so the next kernel's CTA can
-  // become resident and start its own copies while this one computes), else a per-warp ring
+  int nw = n_groups < 8 ? 8 : (n_groups > max_warps ? max_warps : n_groups);
+  // pool if the CTA's whole slice fits in about half of the SM's shared memory, else a per-warp ring
   int depth = 0, n_slots = n_groups;
   const size_t half = limit / 2;
-  if (gemv_fixed_smem(a.K, a.B, n_groups) + (size_t)n_groups * G * rowb > half) {
+  if (gemv_fixed_smem(a.K, a.B, n_groups) + (size_t)n_groups * G * rowb > half + 8 * 1024) {
     size_t per_level = (size_t)nw * G * rowb;
     while (nw > 8 && gemv_fixed_smem(a.K, a.B, nw * 8) + per_level > limit) {
       nw = 8;
@@ -559,8 +567,15 @@ int32_t bk_gemv_launch(const bkGemvArgs& a) {
   p.rows_per_cta = rpc;
   p.n_slots = n_slots;
   p.depth = depth;
-  const size_t smem = gemv_fixed_smem(a.K, a.B, n_slots) + (size_t)n_slots * G * rowb;
-  const int threads = nw * 32;
+  size_t smem = gemv_fixed_smem(a.K, a.B, n_slots) + (size_t)n_slots * G * rowb;
+  int threads = nw * 32;
+  if (a.B <= 2) {  // the occupancy classes assume the 64-register build of the small-batch kernel
+    if (class_a) {
+      if (smem < limit / 2 + 2048) smem = limit / 2 + 2048;   // > half: one class-A CTA per SM
+    } else if (smem <= limit / 2 - 4096) {
+      threads = 18 * 32;                                        // > half of the registers: one class-B CTA per SM
+    }
+  }
   switch (a.B) {
     case 1: return launch_gemv<1, gemv_gmax(1)>(p, grid, threads, smem);
     case 2: return launch_gemv<2, gemv_gmax(2)>(p, grid, threads, smem);

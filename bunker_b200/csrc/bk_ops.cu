@@ -147,7 +147,8 @@ struct GdnParams {
   unsigned long long* trace;
 };
 
-__global__ void __launch_bounds__(512) gdn_step_kernel(const GdnParams p) {
+// Launched with 576 threads: the two extra warps only keep a second CTA of this grid off the SM (register file).
+__global__ void __launch_bounds__(576) gdn_step_kernel(const GdnParams p) {
   constexpr int D = 128;
   __shared__ float s_q[D], s_k[D], s_v[D], s_o[D];
   __shared__ float s_part[4][D];
@@ -158,7 +159,8 @@ __global__ void __launch_bounds__(512) gdn_step_kernel(const GdnParams p) {
   const int ratio = p.Hv / p.Hk, hk = hv / ratio;
   const int keydim = p.Hk * D, C = 2 * keydim + p.Hv * D;
   const int warp = t >> 5, lane = t & 31;
-  const int r = t >> 7, j = t & 127;
+  const bool active = t < 4 * D;            // threads beyond 512 only occupy registers (see the launch)
+  const int r = active ? t >> 7 : 0, j = t & 127;
   const int which = t >> 7, ci = t & 127;
   int ch = 0;
   if (which == 0) ch = hk * D + ci;
@@ -175,8 +177,10 @@ __global__ void __launch_bounds__(512) gdn_step_kernel(const GdnParams p) {
   uint2 cw = make_uint2(0, 0);
   float alog = 0.0f, dtb = 0.0f, nw = 0.0f;
   auto load_static = [&]() {
+    if (active) {
 #pragma unroll
-    for (int i = 0; i < 32; i++) sd[i] = S[(size_t)i * D];
+      for (int i = 0; i < 32; i++) sd[i] = S[(size_t)i * D];
+    }
     if (t < 3 * D && p.apply_conv) {
       const uint16_t* st = p.cs_in + (size_t)b * 3 * C;
       h0 = st[ch];
@@ -244,24 +248,28 @@ __global__ void __launch_bounds__(512) gdn_step_kernel(const GdnParams p) {
 
   const float decay = s_scal[2], beta = s_scal[3];
   float acc = 0.0f;
+  if (active) {
 #pragma unroll
-  for (int i = 0; i < 32; i++) {
-    sd[i] = __fmul_rn(sd[i], decay);
-    acc = fmaf(s_k[32 * r + i], sd[i], acc);
+    for (int i = 0; i < 32; i++) {
+      sd[i] = __fmul_rn(sd[i], decay);
+      acc = fmaf(s_k[32 * r + i], sd[i], acc);
+    }
+    s_part[r][j] = acc;
   }
-  s_part[r][j] = acc;
   __syncthreads();
   float kS = __fadd_rn(__fadd_rn(__fadd_rn(s_part[0][j], s_part[1][j]), s_part[2][j]), s_part[3][j]);
   float delta = __fmul_rn(__fsub_rn(s_v[j], kS), beta);
   __syncthreads();
   acc = 0.0f;
+  if (active) {
 #pragma unroll
-  for (int i = 0; i < 32; i++) {
-    float sn = fmaf(s_k[32 * r + i], delta, sd[i]);
-    Sn[(size_t)i * D] = sn;
-    acc = fmaf(s_q[32 * r + i], sn, acc);
+    for (int i = 0; i < 32; i++) {
+      float sn = fmaf(s_k[32 * r + i], delta, sd[i]);
+      Sn[(size_t)i * D] = sn;
+      acc = fmaf(s_q[32 * r + i], sn, acc);
+    }
+    s_part[r][j] = acc;
   }
-  s_part[r][j] = acc;
   __syncthreads();
   if (t < D) {
     float o = __fadd_rn(__fadd_rn(__fadd_rn(s_part[0][t], s_part[1][t]), s_part[2][t]), s_part[3][t]);
@@ -491,7 +499,7 @@ int32_t bkGdnStep(const bkGdnArgs* args) {
   p.apply_conv = a.apply_conv;
   p.early = a.state_is_settled;
   p.trace = bk_trace_slot();
-  BK_CUDA(bk_launch_pdl(gdn_step_kernel, dim3(a.Hv, a.B), dim3(512), 0, p));
+  BK_CUDA(bk_launch_pdl(gdn_step_kernel, dim3(a.Hv, a.B), dim3(576), 0, p));
   BK_CHECK_LAUNCH();
   return BK_OK;
 }
