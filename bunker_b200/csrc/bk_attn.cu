@@ -34,6 +34,7 @@ struct AttnParams {
   uint16_t* v_cache;
   const int32_t* pos;
   uint16_t* out;
+  uint8_t* out_q8;
   float* scratch;
   const uint16_t* gate;
   int B, Hq, Hkv, rot_half, max_len, split_len, max_splits, fused;
@@ -147,6 +148,15 @@ __device__ void combine_head_warp(const AttnParams& p, int b, int h, int ns, flo
     o[e >> 1] = bk_f32x2_to_bf16x2(v0, v1);
   }
   *reinterpret_cast<uint4*>(p.out + ((size_t)b * p.Hq + h) * kHD + lane * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+  if (p.out_q8) {  // four lanes hold one 32-value block
+    float y[8];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      y[2 * e] = __uint_as_float(o[e] << 16);
+      y[2 * e + 1] = __uint_as_float(o[e] & 0xffff0000u);
+    }
+    bk_q8_1_store<8>(p.out_q8 + ((((size_t)b * p.Hq + h) * kHD + lane * 8) >> 5) * 36, y, (lane & 3) * 8);
+  }
 }
 
 // dynamic shared memory layout (bytes):
@@ -466,6 +476,7 @@ int32_t bkAttnDecode(const bkAttnArgs* args) {
   p.v_cache = bk_ptr<uint16_t>(a.v_cache);
   p.pos = bk_ptr<int32_t>(a.pos);
   p.out = bk_ptr<uint16_t>(a.out);
+  p.out_q8 = bk_ptr<uint8_t>(a.out_q8);
   p.scratch = bk_ptr<float>(a.scratch);
   p.gate = bk_ptr<uint16_t>(a.gate);
   p.B = a.B;

@@ -148,6 +148,45 @@ BK_DEVINL float bk_warp_max(float v) {
   return v;
 }
 
+// ---- Q8_1 block stores from registers (packQ8_1, bench/bench.ts:53-72, in f32) ----
+// `group` consecutive lanes hold one 32-value block, 32/group consecutive values each (group = 32 or 4).
+// All lanes of the warp must call.  blk points at the 36-byte block of the calling lane.
+template <int PER>
+BK_DEVINL void bk_q8_1_store(uint8_t* blk, const float (&y)[PER], int idx_in_block) {
+  constexpr int GROUP = 32 / PER;
+  float amax = 0.0f;
+#pragma unroll
+  for (int e = 0; e < PER; e++) amax = fmaxf(amax, fabsf(y[e]));
+#pragma unroll
+  for (int off = GROUP / 2; off >= 1; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  const float d = __fdiv_rn(amax, 127.0f);
+  const float id = (d == 0.0f) ? 1.0f : __fdiv_rn(1.0f, d);
+  int sum = 0;
+  int qs[PER];
+#pragma unroll
+  for (int e = 0; e < PER; e++) {
+    int v = __float2int_rd(fmaf(y[e], id, 0.5f));
+    sum += v;  // the reference sums before clamping
+    qs[e] = max(-128, min(127, v));
+  }
+#pragma unroll
+  for (int off = GROUP / 2; off >= 1; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+  if (PER == 1) {
+    blk[idx_in_block] = (uint8_t)(int8_t)qs[0];
+  } else {
+    static_assert(PER == 1 || PER % 4 == 0, "values per lane");
+    uint32_t* w = reinterpret_cast<uint32_t*>(blk + idx_in_block);
+#pragma unroll
+    for (int e = 0; e < PER / 4 * 4; e += 4)
+      w[e >> 2] = (uint32_t)(qs[e] & 0xff) | ((uint32_t)(qs[e + 1] & 0xff) << 8) | ((uint32_t)(qs[e + 2] & 0xff) << 16) |
+                  ((uint32_t)(qs[e + 3] & 0xff) << 24);
+  }
+  if (idx_in_block == 0) {
+    const uint32_t hd = bk_f32_to_f16_trunc(d), hs = bk_f32_to_f16_trunc(__fmul_rn((float)sum, d));
+    *reinterpret_cast<uint32_t*>(blk + 32) = hd | (hs << 16);
+  }
+}
+
 // ---- Q4_K superblock header -------------------------------------------------
 // bytes [4,16) of a superblock as three words w0,w1,w2; sub-block j in 0..7
 BK_DEVINL void bk_q4k_scale_min(uint32_t w0, uint32_t w1, uint32_t w2, int j, int& sc, int& mn) {

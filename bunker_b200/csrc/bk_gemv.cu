@@ -453,6 +453,7 @@ __global__ void quant_q8_1_kernel(const void* x, int K, int B, uint8_t* out) {
 // ---- host entry points ---------------------------------------------------------
 
 int32_t bk_gemv_mma_launch(void* params, int K, int B, int vrows, bool has_swiglu);  // bk_gemv_mma.cu
+bool bk_gemv_mma_fits(int K, int B);
 
 int32_t bk_gemv_launch(const bkGemvArgs& a) {
   BkContext& c = bk_ctx();
@@ -463,6 +464,24 @@ int32_t bk_gemv_launch(const bkGemvArgs& a) {
   BK_ARG(a.x != 0 && (a.x & 15) == 0, "bkGemvQ4K: x must be a non-null 16-byte aligned device pointer");
   if (a.prologue == BK_PRO_RMSNORM)
     BK_ARG(a.norm_w != 0 && (a.norm_w & 15) == 0, "bkGemvQ4K: norm_w must be non-null and 16-byte aligned");
+  if (a.B >= 3 && !bk_gemv_mma_fits(a.K, a.B)) {
+    // A K this wide (FFN 17408 of the 64-layer configuration) leaves no room for a 16-row tile beside the staged
+    // activation of 3..8 columns.  The columns are independent, so the launch is cut into column pairs on the
+    // small-batch kernel (same arithmetic, same bits); the weights of the later pairs come mostly from L2.
+    for (int b0 = 0; b0 < a.B; b0 += 2) {
+      bkGemvArgs s = a;
+      s.B = a.B - b0 < 2 ? a.B - b0 : 2;
+      s.x = a.x + (uint64_t)b0 * (a.prologue == BK_PRO_Q8 ? (uint64_t)(a.K / 32) * 36 : (uint64_t)a.K * 2);
+      for (int i = 0; i < a.n_segs && i < 4; i++) {
+        const uint64_t esz = a.segs[i].epilogue == BK_EPI_F32 ? 4 : 2;
+        s.segs[i].out = a.segs[i].out + (uint64_t)b0 * a.segs[i].ld_out * esz;
+        if (a.segs[i].residual) s.segs[i].residual = a.segs[i].residual + (uint64_t)b0 * a.segs[i].ld_out * 2;
+      }
+      int32_t rc = bk_gemv_launch(s);
+      if (rc != BK_OK) return rc;
+    }
+    return BK_OK;
+  }
   GemvParams p;
   p.K = a.K;
   p.n_segs = a.n_segs;

@@ -60,7 +60,7 @@ __device__ __forceinline__ float unit_value(const RowHdr& h, int i0, int i1, flo
   return fmaf(h.d, accd, -t);
 }
 
-// Shared memory: xs [B][K/4 + 4] words | d8s [B][K/32] | s8s [B][K/32] | red[8] | bars[n_slots] | part[2][4 tiles][4 p][16][8] f32 |
+// Shared memory: xs [B][K/4 + 4] words | d8s [B][K/32+2] | s8s [B][K/32+2] | red[72] | bars[n_slots] | part[2][4 tiles][4 p][16][8] f32 |
 // tile slots [n_slots][16 rows][rowb+16].
 __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kernel(const GemvParams p, const int B) {
   bk_pdl_trigger();
@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
   float* d8s = reinterpret_cast<float*>(xs + (size_t)B * p.x_row_words);
   float* s8s = d8s + (size_t)B * p.x_scale_ld;
   float* red = s8s + (size_t)B * p.x_scale_ld;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(red + 8);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(red + 72);   // red: 8 warp sums per batch row + one rstd per row
   const int tpr = blockDim.x >> 7;   // tiles per round (4 or 2): four warps per tile
   const int nwarps = blockDim.x >> 5;
   float* part = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(bars + p.n_slots) + 15) & ~(uintptr_t)15);
@@ -113,15 +113,13 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
   if (lane == 0) {
     for (int t = warp; t < n_tiles && t < n_slots; t += nwarps) request_tile(t, t);
   }
-  uint4 wpre = make_uint4(0, 0, 0, 0);
-  if (p.prologue == BK_PRO_RMSNORM && tid < K / 8) wpre = __ldg(reinterpret_cast<const uint4*>(p.norm_w) + tid);
   bk_stamp(p.trace, 1);
   bk_pdl_wait();
   bk_stamp(p.trace, 2);
 
   if (p.prologue == BK_PRO_Q8) prologue_q8(p, B, xs, d8s, s8s);
-  else if (p.prologue == BK_PRO_BF16) prologue_bf16<false>(p, B, xs, d8s, s8s, red, wpre);
-  else prologue_bf16<true>(p, B, xs, d8s, s8s, red, wpre);
+  else if (p.prologue == BK_PRO_BF16) prologue_bf16_batched<false>(p, B, xs, d8s, s8s, red);
+  else prologue_bf16_batched<true>(p, B, xs, d8s, s8s, red);
   __syncthreads();
   bk_stamp(p.trace, 3);
 
@@ -238,11 +236,18 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
 }
 
 size_t mma_fixed_smem(int K, int B, int n_slots, int tpr) {
-  return (size_t)B * (K / 4 + 4) * 4 + (size_t)B * (K / 32 + 2) * 8 + 32 + (size_t)n_slots * 8 + 16 +
+  return (size_t)B * (K / 4 + 4) * 4 + (size_t)B * (K / 32 + 2) * 8 + 288 + (size_t)n_slots * 8 + 16 +
          (size_t)2 * tpr * 4 * 128 * 4 + 128;
 }
 
 }  // namespace
+
+// Whether one 16-row tile round plus the staged activation fits an SM's shared memory on this path.
+bool bk_gemv_mma_fits(int K, int B) {
+  const size_t rowb = (size_t)(K / 256) * 144, tile_bytes = (size_t)kTileRows * (rowb + 16);
+  const size_t limit = bk_ctx().smem_optin - 1024;
+  return mma_fixed_smem(K, B, 64, 2) + (size_t)2 * tile_bytes <= limit;
+}
 
 // Launch shape for the MMA path; `p` arrives with segments, prologue and trace already filled in.
 int32_t bk_gemv_mma_launch(void* params, int K, int B, int vrows, bool has_swiglu) {

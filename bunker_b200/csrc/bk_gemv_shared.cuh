@@ -192,6 +192,66 @@ __device__ void prologue_bf16(const GemvParams& p, const int B, uint32_t* xs, fl
   }
 }
 
+// The same prologue for several batch rows at once (batch 3..8 path).  Row b's sum of squares still uses the
+// canonical 256-thread order, but each aligned block of 256 threads takes a different row, the per-row warp sums
+// land in red[b*8 + w], and one barrier serves all rows; the quantisation then runs over the flattened
+// (row, chunk) items so that every thread has several independent items in flight.
+// red: 8*B + B floats.
+template <bool NORM>
+__device__ void prologue_bf16_batched(const GemvParams& p, const int B, uint32_t* xs, float* d8s, float* s8s, float* red) {
+  const int K = p.K, nblk = K / 32, nchunk = K / 8;
+  const uint16_t* x = reinterpret_cast<const uint16_t*>(p.x);
+  const int lane = threadIdx.x & 31;
+  float* rstd_s = red + 8 * B;
+  if (NORM) {
+    const int nsl = blockDim.x / kThreads;          // row slots of 256 threads
+    const int r = threadIdx.x / kThreads, t256 = threadIdx.x % kThreads;
+    if (r < nsl) {
+      for (int b = r; b < B; b += nsl) {
+        const uint16_t* row = x + (size_t)b * K;
+        float acc = 0.0f;
+        for (int q = t256; q < nchunk; q += kThreads) {
+          float y[8];
+          load_chunk_bf16(row, q, y);
+#pragma unroll
+          for (int e = 0; e < 8; e++) acc = fmaf(y[e], y[e], acc);
+        }
+        acc = bk_warp_sum(acc);
+        if (lane == 0) red[b * 8 + (t256 >> 5)] = acc;
+      }
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < B) {
+      const float* rb = red + threadIdx.x * 8;
+      float total = rb[0];
+#pragma unroll
+      for (int w = 1; w < kWarps; w++) total = __fadd_rn(total, rb[w]);
+      rstd_s[threadIdx.x] = bk_rcp_sqrt(__fadd_rn(__fdiv_rn(total, (float)K), p.eps));
+    }
+    __syncthreads();
+  }
+  const int items = B * nchunk;
+  for (int i = threadIdx.x; i < items; i += blockDim.x) {
+    const int b = i / nchunk, q = i - b * nchunk;
+    float y[8];
+    load_chunk_bf16(x + (size_t)b * K, q, y);
+    if (NORM) {
+      float wv[8];
+      load_chunk_bf16(p.norm_w, q, wv);
+      const float rstd = rstd_s[b];
+#pragma unroll
+      for (int e = 0; e < 8; e += 2) {
+        float v0 = __fmul_rn(__fmul_rn(y[e], rstd), __fadd_rn(1.0f, wv[e]));
+        float v1 = __fmul_rn(__fmul_rn(y[e + 1], rstd), __fadd_rn(1.0f, wv[e + 1]));
+        uint32_t pk = bk_f32x2_to_bf16x2(v0, v1);
+        y[e] = __uint_as_float(pk << 16);
+        y[e + 1] = __uint_as_float(pk & 0xffff0000u);
+      }
+    }
+    quant_chunk(p, y, q, b, nblk, xs, d8s, s8s);
+  }
+}
+
 // ---- virtual rows --------------------------------------------------------------
 // The rows of all segments of a launch are numbered consecutively.  A SwiGLU segment contributes
 // 2*n_rows virtual rows: even = gate row, odd = the up row of the same output column.

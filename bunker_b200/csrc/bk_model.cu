@@ -56,7 +56,7 @@ struct Model {
   uint64_t lval = 0, lidx = 0;  // per-rank argmax before the merge
   // device buffers
   std::vector<uint64_t> owned;
-  uint64_t x[2] = {0, 0}, h1 = 0, qkv = 0, z = 0, a = 0, b = 0, attn_out = 0, qg = 0, kbuf = 0, vbuf = 0, act = 0;
+  uint64_t x[2] = {0, 0}, h1 = 0, qkv = 0, z = 0, a = 0, b = 0, attn_out = 0, attn_q8 = 0, qg = 0, kbuf = 0, vbuf = 0, act = 0;
   uint64_t logits = 0, ids = 0, val = 0, pos = 0, hist = 0, argmax_scratch = 0, attn_scratch = 0, cos_t = 0, sin_t = 0;
   int32_t* pin_ids = nullptr;  // pinned staging: B ids in, B ids out, B vals
   cudaGraphExec_t graph[2] = {nullptr, nullptr};
@@ -132,6 +132,9 @@ int32_t enqueue_step(Model& m, int parity) {
   const bkModelConfig& c = m.cfg;
   const int B = m.B, H = c.hidden;
   int cur = 0;
+  // GDN / attention also emit their output as Q8_1 blocks.  Reading those spares the output projection its own
+  // quantisation, which pays once that prologue covers several batch rows; at batch 1-2 the bf16 row is as fast.
+  const bool q8_handoff = B >= 3;
   PROF(PC_EMBED, bkEmbedQ4K(m.embed, H, m.ids, B, m.x[0]));
   for (int li = 0; li < c.n_layers; li++) {
     LayerW& L = m.layers[li];
@@ -151,11 +154,12 @@ int32_t enqueue_step(Model& m, int parity) {
       ga.conv_w = L.conv_w; ga.conv_state_in = L.conv_state[parity]; ga.conv_state_new = L.conv_state[parity ^ 1];
       ga.A_log = L.A_log; ga.dt_bias = L.dt_bias; ga.norm_w = L.gnorm;
       ga.S_in = L.S; ga.S_new = L.S;  // in place: each thread rewrites exactly the rows it read
-      ga.out = m.attn_out; ga.B = B; ga.Hk = m.Hk; ga.Hv = m.Hv; ga.apply_conv = 1;
+      ga.out = m.attn_out; ga.out_q8 = q8_handoff ? m.attn_q8 : 0; ga.B = B; ga.Hk = m.Hk; ga.Hv = m.Hv; ga.apply_conv = 1;
       ga.state_is_settled = 1;  // this layer's state was last written one whole step ago
       PROF(PC_GDN, bkGdnStep(&ga));
       memset(&g, 0, sizeof(g));
-      g.K = m.ZD; g.B = B; g.prologue = BK_PRO_BF16; g.x = m.attn_out; g.n_segs = 1;
+      g.K = m.ZD; g.B = B; g.n_segs = 1;
+      g.prologue = q8_handoff ? BK_PRO_Q8 : BK_PRO_BF16; g.x = q8_handoff ? m.attn_q8 : m.attn_out;
       if (m.tp == 1) {
         g.segs[0] = bkGemvSeg{L.out_proj, 0, m.h1, m.x[cur], H, BK_EPI_ADD_BF16, H, 0};
         PROF(PC_GEMV_OUT, bk_gemv_launch(g));
@@ -176,14 +180,15 @@ int32_t enqueue_step(Model& m, int parity) {
       memset(&aa, 0, sizeof(aa));
       aa.qg = m.qg; aa.k = m.kbuf; aa.v = m.vbuf; aa.q_norm_w = L.q_norm; aa.k_norm_w = L.k_norm;
       aa.cos_t = m.cos_t; aa.sin_t = m.sin_t; aa.k_cache = L.kc; aa.v_cache = L.vc; aa.pos = m.pos;
-      aa.out = m.attn_out; aa.scratch = m.attn_scratch;
+      aa.out = m.attn_out; aa.out_q8 = q8_handoff ? m.attn_q8 : 0; aa.scratch = m.attn_scratch;
       aa.B = B; aa.Hq = m.Hq; aa.Hkv = m.Hkv; aa.HD = c.head_dim; aa.rot_half = c.rot_dim / 2; aa.max_len = c.max_len;
       aa.split_len = m.split_len; aa.max_pos = c.max_len - 1; aa.scale = 1.0f / sqrtf((float)c.head_dim);
       aa.fused_norm_rope = 1;
       aa.cache_is_settled = 1;  // pos and the older cache rows were written a whole step ago
       PROF(PC_ATTN, bkAttnDecode(&aa));
       memset(&g, 0, sizeof(g));
-      g.K = m.Hq * c.head_dim; g.B = B; g.prologue = BK_PRO_BF16; g.x = m.attn_out; g.n_segs = 1;
+      g.K = m.Hq * c.head_dim; g.B = B; g.n_segs = 1;
+      g.prologue = q8_handoff ? BK_PRO_Q8 : BK_PRO_BF16; g.x = q8_handoff ? m.attn_q8 : m.attn_out;
       if (m.tp == 1) {
         g.segs[0] = bkGemvSeg{L.o, 0, m.h1, m.x[cur], H, BK_EPI_ADD_BF16, H, 0};
         PROF(PC_GEMV_OUT, bk_gemv_launch(g));
@@ -397,6 +402,7 @@ int32_t bkModelFinalize(uint64_t model) {
   TRY(dev_alloc(m, (size_t)B * m.Hv * 4, &m.a));
   TRY(dev_alloc(m, (size_t)B * m.Hv * 4, &m.b));
   TRY(dev_alloc(m, (size_t)B * (m.ZD > attn_w ? m.ZD : attn_w) * 2, &m.attn_out));
+  TRY(dev_alloc(m, (size_t)B * (m.ZD > attn_w ? m.ZD : attn_w) / 32 * 36, &m.attn_q8));
   TRY(dev_alloc(m, (size_t)B * m.QG * 2, &m.qg));
   TRY(dev_alloc(m, (size_t)B * m.KVD * 2, &m.kbuf));
   TRY(dev_alloc(m, (size_t)B * m.KVD * 2, &m.vbuf));

@@ -142,6 +142,7 @@ struct GdnParams {
   uint16_t* out;
   float* o_raw;
   uint16_t* conv_out;
+  uint8_t* out_q8;
   int B, Hk, Hv, apply_conv;
   int early;  // state / conv state / weights are not outputs of the immediately preceding launch
   unsigned long long* trace;
@@ -288,7 +289,12 @@ __global__ void __launch_bounds__(576) gdn_step_kernel(const GdnParams p) {
   if (t < D) {
     float zs = __fmul_rn(zv, bk_sigmoidf(zv));
     float ow = __fmul_rn(__fmul_rn(s_o[t], s_scal[0]), nw);
-    p.out[((size_t)b * p.Hv + hv) * D + t] = bk_f32_to_bf16(__fmul_rn(ow, zs));
+    const uint16_t ob = bk_f32_to_bf16(__fmul_rn(ow, zs));
+    p.out[((size_t)b * p.Hv + hv) * D + t] = ob;
+    if (p.out_q8) {  // warp w of the first four holds block w of this head
+      const float y[1] = {bk_bf16_to_f32(ob)};
+      bk_q8_1_store<1>(p.out_q8 + (((size_t)b * p.Hv + hv) * 4 + warp) * 36, y, lane);
+    }
   }
   bk_stamp(p.trace, 5);
 }
@@ -493,6 +499,7 @@ int32_t bkGdnStep(const bkGdnArgs* args) {
   p.out = bk_ptr<uint16_t>(a.out);
   p.o_raw = bk_ptr<float>(a.o_raw);
   p.conv_out = bk_ptr<uint16_t>(a.conv_out);
+  p.out_q8 = bk_ptr<uint8_t>(a.out_q8);
   p.B = a.B;
   p.Hk = a.Hk;
   p.Hv = a.Hv;

@@ -53,7 +53,8 @@ class bkGemvArgs(C.Structure):
 class bkGdnArgs(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in ("qkv", "z", "a", "b", "conv_w", "conv_state_in", "conv_state_new", "A_log",
                                            "dt_bias", "norm_w", "S_in", "S_new", "out", "o_raw", "conv_out")] + \
-               [(n, C.c_int32) for n in ("B", "Hk", "Hv", "apply_conv", "state_is_settled", "reserved")]
+               [(n, C.c_int32) for n in ("B", "Hk", "Hv", "apply_conv", "state_is_settled", "reserved")] + \
+               [("out_q8", C.c_uint64)]
 
 
 class bkAttnArgs(C.Structure):
@@ -61,7 +62,7 @@ class bkAttnArgs(C.Structure):
                                            "v_cache", "pos", "out", "scratch")] + \
                [(n, C.c_int32) for n in ("B", "Hq", "Hkv", "HD", "rot_half", "max_len", "split_len", "max_pos")] + \
                [("scale", C.c_float), ("fused_norm_rope", C.c_int32), ("gate", C.c_uint64),
-                ("cache_is_settled", C.c_int32), ("reserved", C.c_int32)]
+                ("cache_is_settled", C.c_int32), ("reserved", C.c_int32), ("out_q8", C.c_uint64)]
 
 
 class bkModelConfig(C.Structure):

@@ -163,6 +163,8 @@ typedef struct bkGdnArgs {
                                     immediately precedes this one on the stream, so the kernel may read them while that
                                     launch is still running (programmatic dependent launch).  0: read everything after it. */
   int32_t reserved;
+  uint64_t out_q8;               /* optional (0 to skip): the same output as Q8_1 blocks [B][Hv*4][36], the form the
+                                    output projection reads with BK_PRO_Q8 */
 } bkGdnArgs;
 BK_API int32_t bkGdnStep(const bkGdnArgs* args);
 
@@ -196,6 +198,7 @@ typedef struct bkAttnArgs {
   int32_t cache_is_settled; /* 1: pos[] and the cache rows below pos[b] were NOT written by the launch that immediately
                                precedes this one on the stream, so they may be read while that launch is still running */
   int32_t reserved;
+  uint64_t out_q8;   /* optional (0 to skip): the same output as Q8_1 blocks [B][Hq*HD/32][36] */
 } bkAttnArgs;
 BK_API int32_t bkAttnDecode(const bkAttnArgs* args);
 /* split length and warps per split the library uses for n rows */

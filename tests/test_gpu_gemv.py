@@ -91,6 +91,29 @@ def test_gemv_batches_and_tails(bk, B, K):
     assert_same_bits(dy.download(np.float32, (B, N)), O.gemv_q4k_q8(W, N, K, xq), f"gemv B={B} K={K}")
 
 
+@pytest.mark.parametrize("B", [3, 8])
+def test_gemv_widest_k_batched(bk, B):
+    """K = 17408 (FFN width of the 64-layer configuration) at batch >= 3: too wide for the tensor-core path's
+    shared memory, served as column pairs; bf16 prologue, residual epilogue with a column offset."""
+    K, N, ld, off = 17408, 200, 256, 40
+    rng = np.random.default_rng(70 + B)
+    W = synth.q4k_weights(rng, N, K)
+    x = synth.normal_bf16(rng, (B, K))
+    res = synth.normal_bf16(rng, (B, ld))
+    xq = O.q8_1_quantize_bf16(x)
+    want = O.epilogue_add(O.gemv_q4k_q8(W, N, K, xq), np.ascontiguousarray(res[:, off:off + N]))
+    dW, dx, dres, out = dev(W), dev(x), dev(res), R.DeviceBuffer.zeros(B * ld * 2)
+    ops.gemv(dx.ptr, K, B, [ops.gemv_seg(dW.ptr, N, out.ptr, R.BK_EPI_ADD_BF16, ld_out=ld, col_off=off,
+                                         residual=dres.ptr)], prologue=R.BK_PRO_BF16)
+    got = out.download(np.uint16, (B, ld))
+    assert_same_bits(got[:, off:off + N], want, f"gemv K={K} B={B}")
+    assert not got[:, :off].any() and not got[:, off + N:].any()
+    xq8 = dev(xq)
+    y = R.DeviceBuffer(B * N * 4)
+    ops.gemv_simple(dW.ptr, N, K, xq8.ptr, B, y.ptr)
+    assert_same_bits(y.download(np.float32, (B, N)), O.gemv_q4k_q8(W, N, K, xq), "Q8_1 input, f32 output")
+
+
 @pytest.mark.parametrize("B", [1, 8])
 def test_gemv_fused_prologues_epilogues(bk, B):
     """One launch: RMSNorm prologue, three segments with f32 / bf16 / residual-add epilogues."""

@@ -113,9 +113,9 @@ def test_scaled_model_shapes_first_steps_match_oracle(bk):
 
 
 def test_scaled_model_shapes_batch8_tensor_core_path(bk):
-    """Same head shapes at batch 8 (int8 tensor-core GEMV path, K = 5120 and 6144).  The FFN is narrowed to 6144:
-    at batch >= 3 a K of 17408 does not fit an SM's shared memory on that path and is rejected."""
-    cfg = M.CONFIG_HYBRID_64L.with_(n_layers=4, vocab=4096, max_len=32, intermediate=6144)
+    """Same head shapes at batch 8: int8 tensor-core GEMV path for K = 5120 and 6144; the FFN down projection
+    (K = 17408) does not fit that path's shared memory and runs as column pairs on the small-batch kernel."""
+    cfg = M.CONFIG_HYBRID_64L.with_(n_layers=4, vocab=4096, max_len=32)
     w = M.synth_weights(cfg, seed=12)
     gm = M.DecodeModel(cfg, w, batch=8)
     info = gm.info()

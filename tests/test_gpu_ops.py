@@ -71,7 +71,8 @@ def test_gdn_step_config1(bk, B):
     d = {k: dev(v) for k, v in c.items() if isinstance(v, np.ndarray)}
     cs_new, S_new = R.DeviceBuffer(B * 3 * Cw * 2), R.DeviceBuffer(B * Hv * 128 * 128 * 4)
     out, o_raw, conv_out = R.DeviceBuffer(B * Hv * 128 * 2), R.DeviceBuffer(B * Hv * 128 * 4), R.DeviceBuffer(B * Cw * 2)
-    ops.gdn_step(qkv=d["qkv"].ptr, z=d["z"].ptr, a=d["a"].ptr, b=d["b"].ptr, conv_w=d["conv_w"].ptr,
+    out_q8 = R.DeviceBuffer(B * Hv * 4 * 36)
+    ops.gdn_step(out_q8=out_q8.ptr, qkv=d["qkv"].ptr, z=d["z"].ptr, a=d["a"].ptr, b=d["b"].ptr, conv_w=d["conv_w"].ptr,
                  conv_state_in=d["conv_state"].ptr, conv_state_new=cs_new.ptr, A_log=d["A_log"].ptr,
                  dt_bias=d["dt_bias"].ptr, norm_w=d["norm_w"].ptr, S_in=d["S"].ptr, S_new=S_new.ptr, out=out.ptr,
                  o_raw=o_raw.ptr, conv_out=conv_out.ptr, B=B, Hk=Hk, Hv=Hv, apply_conv=1)
@@ -81,6 +82,8 @@ def test_gdn_step_config1(bk, B):
     assert_same_bits(o_raw.download(np.float32, (B, Hv, 128)), w_o, "o_raw")
     assert_same_bits(S_new.download(np.float32, (B, Hv, 128, 128)), w_S, "S_new")
     assert_same_bits(out.download(np.uint16, (B, Hv * 128)), w_out, "gated out")
+    assert_same_bits(out_q8.download(np.uint8, (B, Hv * 4, 36)), O.q8_1_quantize_bf16(w_out).reshape(B, Hv * 4, 36),
+                     "gated out as Q8_1 blocks")
     # plain recurrence (prototypes/gdn_gated.ts:67-88) on head (0, 5), double math
     import math
     hv, hk = 5, 5 // (Hv // Hk)
@@ -146,12 +149,15 @@ def _run_attn(c, cos_t, sin_t, split_len=0):
     d = {k: dev(v) for k, v in c.items() if isinstance(v, np.ndarray)}
     dc, ds = dev(cos_t), dev(sin_t)
     scratch = R.DeviceBuffer.zeros(ops.attn_scratch_bytes(B, Hq, HD, ml, split_len))
-    out = R.DeviceBuffer(B * Hq * HD * 2)
-    ops.attn_decode(qg=d["qg"].ptr, k=d["k"].ptr, v=d["v"].ptr, q_norm_w=d["q_norm_w"].ptr, k_norm_w=d["k_norm_w"].ptr,
+    out, out_q8 = R.DeviceBuffer(B * Hq * HD * 2), R.DeviceBuffer(B * Hq * HD // 32 * 36)
+    ops.attn_decode(out_q8=out_q8.ptr, qg=d["qg"].ptr, k=d["k"].ptr, v=d["v"].ptr, q_norm_w=d["q_norm_w"].ptr, k_norm_w=d["k_norm_w"].ptr,
                     cos_t=dc.ptr, sin_t=ds.ptr, k_cache=d["k_cache"].ptr, v_cache=d["v_cache"].ptr, pos=d["pos"].ptr,
                     out=out.ptr, scratch=scratch.ptr, B=B, Hq=Hq, Hkv=Hkv, HD=HD, rot_half=32, max_len=ml,
                     split_len=split_len, max_pos=max_pos, scale=1.0 / 16.0, fused_norm_rope=1)
     got = out.download(np.uint16, (B, Hq * HD))
+    assert_same_bits(out_q8.download(np.uint8, (B, Hq * HD // 32, 36)),
+                     O.q8_1_quantize_bf16(got).reshape(B, Hq * HD // 32, 36), "attention output as Q8_1 blocks")
+    out_q8.free()
     Kg = d["k_cache"].download(np.uint16, c["k_cache"].shape)
     Vg = d["v_cache"].download(np.uint16, c["v_cache"].shape)
     for b in d.values():
