@@ -56,7 +56,7 @@ struct Model {
   uint64_t lval = 0, lidx = 0;  // per-rank argmax before the merge
   // device buffers
   std::vector<uint64_t> owned;
-  uint64_t x[2] = {0, 0}, h1 = 0, qkv = 0, z = 0, a = 0, b = 0, attn_out = 0, attn_q8 = 0, qg = 0, kbuf = 0, vbuf = 0, act = 0;
+  uint64_t x[2] = {0, 0}, h1 = 0, qkv = 0, z = 0, a = 0, b = 0, attn_out = 0, attn_q8 = 0, xq = 0, qg = 0, kbuf = 0, vbuf = 0, act = 0;
   uint64_t logits = 0, ids = 0, val = 0, pos = 0, hist = 0, argmax_scratch = 0, attn_scratch = 0, cos_t = 0, sin_t = 0;
   int32_t* pin_ids = nullptr;  // pinned staging: B ids in, B ids out, B vals
   cudaGraphExec_t graph[2] = {nullptr, nullptr};
@@ -96,7 +96,7 @@ inline uint64_t q4k_bytes(uint64_t n, uint64_t k) { return n * (k / 256) * 144; 
 // BUNKER_GPU_PROF=1 profiler (src/ttir.ts:352-417).  Classes index the ms/count arrays of
 // bkDecodeStepProfiled.
 enum ProfClass { PC_EMBED = 0, PC_GEMV_PROJ, PC_GDN, PC_ATTN, PC_GEMV_OUT, PC_GEMV_GATEUP, PC_GEMV_DOWN, PC_GEMV_LMHEAD,
-                 PC_ARGMAX, PC_EXCHANGE, PC_COUNT };
+                 PC_ARGMAX, PC_EXCHANGE, PC_QUANT, PC_COUNT };
 
 struct Prof {
   bool on = false;
@@ -135,13 +135,25 @@ int32_t enqueue_step(Model& m, int parity) {
   // GDN / attention also emit their output as Q8_1 blocks.  Reading those spares the output projection its own
   // quantisation, which pays once that prologue covers several batch rows; at batch 1-2 the bf16 row is as fast.
   const bool q8_handoff = B >= 3;
+  // Input of a projection: fused RMSNorm/quantise prologue at batch 1-2; at batch >= 3 one small launch
+  // normalises and quantises the rows once and every CTA of the projection just copies the blocks.
+  auto set_input = [&](bkGemvArgs& g, uint64_t x, int K, uint64_t norm_w) -> int32_t {
+    g.K = K; g.B = B; g.eps = c.eps;
+    if (q8_handoff) {
+      PROF(PC_QUANT, bkRmsNormQuantQ8_1(x, norm_w, K, B, c.eps, m.xq));
+      g.prologue = BK_PRO_Q8; g.x = m.xq;
+    } else {
+      g.prologue = norm_w ? BK_PRO_RMSNORM : BK_PRO_BF16; g.x = x; g.norm_w = norm_w;
+    }
+    return BK_OK;
+  };
   PROF(PC_EMBED, bkEmbedQ4K(m.embed, H, m.ids, B, m.x[0]));
   for (int li = 0; li < c.n_layers; li++) {
     LayerW& L = m.layers[li];
     bkGemvArgs g;
     if (!L.full) {
       memset(&g, 0, sizeof(g));
-      g.K = H; g.B = B; g.prologue = BK_PRO_RMSNORM; g.x = m.x[cur]; g.norm_w = L.in_ln; g.eps = c.eps;
+      TRY(set_input(g, m.x[cur], H, L.in_ln));
       g.n_segs = 4;
       g.segs[0] = bkGemvSeg{L.qkv, 0, m.qkv, 0, m.Cw, BK_EPI_BF16, m.Cw, 0};
       g.segs[1] = bkGemvSeg{L.z, 0, m.z, 0, m.ZD, BK_EPI_BF16, m.ZD, 0};
@@ -170,7 +182,7 @@ int32_t enqueue_step(Model& m, int parity) {
       }
     } else {
       memset(&g, 0, sizeof(g));
-      g.K = H; g.B = B; g.prologue = BK_PRO_RMSNORM; g.x = m.x[cur]; g.norm_w = L.in_ln; g.eps = c.eps;
+      TRY(set_input(g, m.x[cur], H, L.in_ln));
       g.n_segs = 3;
       g.segs[0] = bkGemvSeg{L.q, 0, m.qg, 0, m.QG, BK_EPI_BF16, m.QG, 0};
       g.segs[1] = bkGemvSeg{L.k, 0, m.kbuf, 0, m.KVD, BK_EPI_BF16, m.KVD, 0};
@@ -199,11 +211,13 @@ int32_t enqueue_step(Model& m, int parity) {
       }
     }
     memset(&g, 0, sizeof(g));
-    g.K = H; g.B = B; g.prologue = BK_PRO_RMSNORM; g.x = m.h1; g.norm_w = L.post_ln; g.eps = c.eps; g.n_segs = 1;
+    TRY(set_input(g, m.h1, H, L.post_ln));
+    g.n_segs = 1;
     g.segs[0] = bkGemvSeg{L.gate, L.up, m.act, 0, m.inter, BK_EPI_SWIGLU, m.inter, 0};
     PROF(PC_GEMV_GATEUP, bk_gemv_launch(g));
     memset(&g, 0, sizeof(g));
-    g.K = m.inter; g.B = B; g.prologue = BK_PRO_BF16; g.x = m.act; g.n_segs = 1;
+    TRY(set_input(g, m.act, m.inter, 0));
+    g.n_segs = 1;
     if (m.tp == 1) {
       g.segs[0] = bkGemvSeg{L.down, 0, m.x[cur ^ 1], m.h1, H, BK_EPI_ADD_BF16, H, 0};
       PROF(PC_GEMV_DOWN, bk_gemv_launch(g));
@@ -216,7 +230,8 @@ int32_t enqueue_step(Model& m, int parity) {
   }
   bkGemvArgs g;
   memset(&g, 0, sizeof(g));
-  g.K = H; g.B = B; g.prologue = BK_PRO_RMSNORM; g.x = m.x[cur]; g.norm_w = m.final_norm; g.eps = c.eps; g.n_segs = 1;
+  TRY(set_input(g, m.x[cur], H, m.final_norm));
+  g.n_segs = 1;
   g.segs[0] = bkGemvSeg{m.embed + (uint64_t)m.vocab_offset * (H / 256) * 144, 0, m.logits, 0, m.vocab_local, BK_EPI_F32,
                         m.vocab_local, 0};
   PROF(PC_GEMV_LMHEAD, bk_gemv_launch(g));
@@ -403,6 +418,7 @@ int32_t bkModelFinalize(uint64_t model) {
   TRY(dev_alloc(m, (size_t)B * m.Hv * 4, &m.b));
   TRY(dev_alloc(m, (size_t)B * (m.ZD > attn_w ? m.ZD : attn_w) * 2, &m.attn_out));
   TRY(dev_alloc(m, (size_t)B * (m.ZD > attn_w ? m.ZD : attn_w) / 32 * 36, &m.attn_q8));
+  TRY(dev_alloc(m, (size_t)B * (m.inter > H ? m.inter : H) / 32 * 36, &m.xq));
   TRY(dev_alloc(m, (size_t)B * m.QG * 2, &m.qg));
   TRY(dev_alloc(m, (size_t)B * m.KVD * 2, &m.kbuf));
   TRY(dev_alloc(m, (size_t)B * m.KVD * 2, &m.vbuf));

@@ -89,6 +89,69 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t* x, const u
   }
 }
 
+// ---- (RMSNorm ->) Q8_1 rows, computed once for all consumers ------------------------
+// At batch >= 3 the projection kernels read their activation as ready Q8_1 blocks instead of each of the
+// 148 CTAs normalising and quantising all batch rows again.  NORM: one CTA per batch row (the canonical
+// 256-thread sum of squares).  Plain: 256 chunks of 8 values per CTA.  Output blocks [B][K/32][36].
+template <bool NORM>
+__global__ void __launch_bounds__(256) quant_rows_kernel(const uint16_t* x, const uint16_t* w, int K, float eps,
+                                                         uint8_t* out) {
+  bk_pdl_trigger();
+  __shared__ float red[8];
+  const int b = blockIdx.y, nchunk = K / 8, tid = threadIdx.x;
+  const uint16_t* row = x + (size_t)b * K;
+  uint8_t* orow = out + (size_t)b * (K / 32) * 36;
+  if (NORM) {
+    float wv0[8];
+    const bool have0 = tid < nchunk;
+    if (have0) load8_bf16(w + (size_t)tid * 8, wv0);
+    bk_pdl_wait();
+    float y0[8];
+    float acc = 0.0f;
+    if (have0) {
+      load8_bf16(row + (size_t)tid * 8, y0);
+#pragma unroll
+      for (int e = 0; e < 8; e++) acc = fmaf(y0[e], y0[e], acc);
+    }
+    for (int q = tid + 256; q < nchunk; q += 256) {
+      float v[8];
+      load8_bf16(row + (size_t)q * 8, v);
+#pragma unroll
+      for (int e = 0; e < 8; e++) acc = fmaf(v[e], v[e], acc);
+    }
+    acc = bk_warp_sum(acc);
+    if ((tid & 31) == 0) red[tid >> 5] = acc;
+    __syncthreads();
+    float total = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) total = __fadd_rn(total, red[i]);
+    const float rstd = bk_rcp_sqrt(__fadd_rn(__fdiv_rn(total, (float)K), eps));
+    for (int q = tid; q < nchunk; q += 256) {  // nchunk is a multiple of 32: whole warps enter together
+      float v[8], wv[8];
+      if (q == tid) {
+#pragma unroll
+        for (int e = 0; e < 8; e++) { v[e] = y0[e]; wv[e] = wv0[e]; }
+      } else {
+        load8_bf16(row + (size_t)q * 8, v);
+        load8_bf16(w + (size_t)q * 8, wv);
+      }
+      float y[8];
+#pragma unroll
+      for (int e = 0; e < 8; e++)
+        y[e] = bk_bf16_to_f32(bk_f32_to_bf16(__fmul_rn(__fmul_rn(v[e], rstd), __fadd_rn(1.0f, wv[e]))));
+      bk_q8_1_store<8>(orow + (size_t)(q >> 2) * 36, y, (q & 3) * 8);
+    }
+  } else {
+    bk_pdl_wait();
+    const int q = blockIdx.x * 256 + tid;
+    if (q < nchunk) {
+      float y[8];
+      load8_bf16(row + (size_t)q * 8, y);
+      bk_q8_1_store<8>(orow + (size_t)(q >> 2) * 36, y, (q & 3) * 8);
+    }
+  }
+}
+
 // ---- SwiGLU (src/fusion.ts:324-330) ---------------------------------------------
 __global__ void swiglu_kernel(const float* g, const float* u, int n, uint16_t* out) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -443,6 +506,21 @@ int32_t bkRmsNorm(uint64_t x, uint64_t w, int32_t H, int32_t B, float eps, uint6
   BK_ARG(x && w && y && ((x | w | y) & 15) == 0, "bkRmsNorm: null or misaligned pointer");
   rmsnorm_kernel<<<B, 256, 0, bk_ctx().stream>>>(bk_ptr<uint16_t>(x), bk_ptr<uint16_t>(w), H, eps,
                                                 bk_ptr<uint16_t>(y));
+  BK_CHECK_LAUNCH();
+  return BK_OK;
+}
+
+int32_t bkRmsNormQuantQ8_1(uint64_t x, uint64_t w, int32_t K, int32_t B, float eps, uint64_t out_blocks) {
+  BK_REQUIRE_INIT();
+  BK_ARG(K > 0 && K % 256 == 0 && B > 0, "bkRmsNormQuantQ8_1: bad shape K=%d B=%d (K a multiple of 256)", K, B);
+  BK_ARG(x && out_blocks && ((x | w) & 15) == 0 && (out_blocks & 3) == 0, "bkRmsNormQuantQ8_1: null or misaligned pointer");
+  if (w) {
+    BK_CUDA(bk_launch_pdl(quant_rows_kernel<true>, dim3(1, B), dim3(256), 0, bk_ptr<uint16_t>(x), bk_ptr<uint16_t>(w), K,
+                          eps, bk_ptr<uint8_t>(out_blocks)));
+  } else {
+    BK_CUDA(bk_launch_pdl(quant_rows_kernel<false>, dim3((K / 8 + 255) / 256, B), dim3(256), 0, bk_ptr<uint16_t>(x),
+                          bk_ptr<uint16_t>(w), K, eps, bk_ptr<uint8_t>(out_blocks)));
+  }
   BK_CHECK_LAUNCH();
   return BK_OK;
 }

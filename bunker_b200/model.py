@@ -301,7 +301,7 @@ class DecodeModel:
         R._check(R.cu().bkDecodeRun(self.handle, n_steps))
 
     PROFILE_CLASSES = ("embed", "gemv_proj", "gdn", "attn", "gemv_out", "gemv_gateup", "gemv_down", "gemv_lmhead",
-                       "argmax", "exchange")
+                       "argmax", "exchange", "quant")
 
     def step_profiled(self) -> dict[str, tuple[float, int]]:
         """One eager step (device token feedback) with an event pair around every op: {class: (ms, calls)}."""

@@ -57,6 +57,11 @@ def rmsnorm(x: int, w: int, H: int, B: int, y: int, eps: float = 1e-6) -> None:
     _check(cu().bkRmsNorm(x, w, H, B, eps, y))
 
 
+def rmsnorm_quant_q8_1(x: int, w: int, K: int, B: int, out: int, eps: float = 1e-6) -> None:
+    """RMSNorm (w != 0) and Q8_1 quantisation of bf16 rows in one launch; w = 0 quantises the rows as they are."""
+    _check(cu().bkRmsNormQuantQ8_1(x, w, K, B, eps, out))
+
+
 def swiglu(g: int, u: int, n: int, out: int) -> None:
     _check(cu().bkSwiglu(g, u, n, out))
 

@@ -109,6 +109,7 @@ SIGNATURES = {
     "bkQuantQ8_1Bf16": (_I32, [_U64, _I32, _I32, _U64]),
     "bkEmbedQ4K": (_I32, [_U64, _I32, _U64, _I32, _U64]),
     "bkRmsNorm": (_I32, [_U64, _U64, _I32, _I32, _F32, _U64]),
+    "bkRmsNormQuantQ8_1": (_I32, [_U64, _U64, _I32, _I32, _F32, _U64]),
     "bkSwiglu": (_I32, [_U64, _U64, _I32, _U64]),
     "bkConv1dStep": (_I32, [_U64, _U64, _U64, _I32, _I32, _U64, _U64]),
     "bkGdnStep": (_I32, [C.POINTER(bkGdnArgs)]),

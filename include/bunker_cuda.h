@@ -141,6 +141,10 @@ BK_API int32_t bkQuantQ8_1Bf16(uint64_t x_bf16, int32_t K, int32_t B, uint64_t o
 BK_API int32_t bkEmbedQ4K(uint64_t table, int32_t H, uint64_t ids, int32_t B, uint64_t x_out);
 /* buildRMS (prototypes/decode.ts:201-216): y = bf16((x*rstd)*(1+w)) */
 BK_API int32_t bkRmsNorm(uint64_t x, uint64_t w, int32_t H, int32_t B, float eps, uint64_t y);
+/* buildRMS followed by packQ8_1 (prototypes/decode.ts:201-216, bench/bench.ts:53-72) in one launch: bf16 rows
+ * x [B][K] -> Q8_1 blocks [B][K/32][36] of bf16((x*rstd)*(1+w)); w = 0 skips the norm (plain bf16 -> Q8_1).
+ * The blocks are what bkGemvQ4K reads with BK_PRO_Q8; used between ops at batch >= 3. */
+BK_API int32_t bkRmsNormQuantQ8_1(uint64_t x, uint64_t w, int32_t K, int32_t B, float eps, uint64_t out_blocks);
 /* emitSwiGLU (src/fusion.ts:324-330): out bf16 [n] from f32 g,u */
 BK_API int32_t bkSwiglu(uint64_t g_f32, uint64_t u_f32, int32_t n, uint64_t out_bf16);
 /* emitConv1d (src/emitters.ts:48-72): state [B][3][C] bf16 oldest first, w [C][4] bf16 */
@@ -264,9 +268,9 @@ BK_API int32_t bkDecodeStep(uint64_t model, const int32_t* tokens, int32_t* out_
 /* n_steps greedy steps with device-side token feedback and no host traffic. */
 BK_API int32_t bkDecodeRun(uint64_t model, int32_t n_steps);
 /* One eagerly launched step with a CUDA-event pair around every op (the BUNKER_GPU_PROF=1 profiler of
- * src/ttir.ts:352-417).  ms_out/count_out[n_classes >= 10]: 0 embed, 1 projection GEMV (qkv|z|a|b, q|k|v),
+ * src/ttir.ts:352-417).  ms_out/count_out[n_classes >= 11]: 0 embed, 1 projection GEMV (qkv|z|a|b, q|k|v),
  * 2 conv1d+GDN, 3 attention (2 kernels per call), 4 out/o_proj GEMV, 5 gate|up GEMV, 6 down GEMV, 7 lm_head GEMV, 8 argmax,
- * 9 tensor-parallel exchanges. */
+ * 9 tensor-parallel exchanges, 10 stand-alone norm+quantise launches (batch >= 3 only). */
 BK_API int32_t bkDecodeStepProfiled(uint64_t model, float* ms_out, int32_t* count_out, int32_t n_classes);
 /* Tokens produced by steps [first_step, first_step+n_steps): out[n_steps][B] host ints. */
 BK_API int32_t bkModelTokens(uint64_t model, int32_t first_step, int32_t n_steps, int32_t* out);

@@ -33,6 +33,20 @@ def test_rmsnorm(bk, H):
     assert rel_err(synth.bf16_to_f32(y), O.rmsnorm_plain(x, w)) < 5e-3  # bf16 output rounding
 
 
+@pytest.mark.parametrize("K", [256, 2048, 5120, 17408])
+def test_rmsnorm_quant_q8_1(bk, K):
+    """The stand-alone (RMSNorm ->) Q8_1 launch used between ops at batch >= 3, with and without the norm."""
+    B = 5
+    rng = np.random.default_rng(60)
+    x, w = synth.normal_bf16(rng, (B, K), 2.0), synth.normal_bf16(rng, (K,), 0.02)
+    x[1, :32] = 0  # an all-zero block: d = 0
+    dx, dw, dq = dev(x), dev(w), R.DeviceBuffer(B * K // 32 * 36)
+    ops.rmsnorm_quant_q8_1(dx.ptr, dw.ptr, K, B, dq.ptr)
+    assert_same_bits(dq.download(np.uint8, (B, K // 32, 36)), O.q8_1_quantize_bf16(O.rmsnorm(x, w)), "norm + Q8_1")
+    ops.rmsnorm_quant_q8_1(dx.ptr, 0, K, B, dq.ptr)
+    assert_same_bits(dq.download(np.uint8, (B, K // 32, 36)), O.q8_1_quantize_bf16(x), "plain Q8_1")
+
+
 def test_swiglu(bk):
     n = 6144
     rng = np.random.default_rng(7)
