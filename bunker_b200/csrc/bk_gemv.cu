@@ -243,7 +243,7 @@ __global__ void __launch_bounds__(576, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kern
   if (ctr && threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); ctr[1] = t_; }
 
   if (p.prologue == BK_PRO_Q8)
-    prologue_q8(p, B, xs, d8s, s8s);
+    prologue_q8<false>(p, B, xs, d8s, s8s);
   else if (p.prologue == BK_PRO_BF16)
     prologue_bf16<false>(p, B, xs, d8s, s8s, red, wpre);
   else

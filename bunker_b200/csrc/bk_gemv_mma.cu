@@ -25,57 +25,45 @@ namespace {
 constexpr int kTileRows = 16;
 constexpr int kMaxTilesPerRound = 4;  // a round = tiles_per_round tiles x 4 sub-block pairs = up to 16 warps
 
-__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+// A: unsigned bytes (nibbles, or nibbles left in the high half = 16*q), B: signed Q8_1 quants
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-struct RowHdr {
-  float d, dmin, fm0, fm1;
-  int sc0, sc1;
-};
-
-__device__ __forceinline__ RowHdr decode_hdr(const uint8_t* sb, int p) {
-  const uint4 h = *reinterpret_cast<const uint4*>(sb);
-  RowHdr r;
-  r.d = bk_f16_to_f32((uint16_t)(h.x & 0xffffu));
-  r.dmin = bk_f16_to_f32((uint16_t)(h.x >> 16));
-  uint32_t sc2, mn2;
-  bk_q4k_scale_min_pair(h.y, h.z, h.w, p, sc2, mn2);
-  r.sc0 = (int)(sc2 & 0xffu);
-  r.sc1 = (int)(sc2 >> 8);
-  r.fm0 = (float)(int)(mn2 & 0xffu);
-  r.fm1 = (float)(int)(mn2 >> 8);
-  return r;
+// Decoded header of one (row, superblock) for the warp's sub-block pair: {d, dmin, sc0, sc1 (int bits)} and {m0, m1}.
+// unit value for one (row, column): i0 exact sum of sub-block 2p, i1x16 = 16 * exact sum of sub-block 2p+1 (the high
+// nibbles stay in place); sc.y already carries the matching 1/16, so fma(d8_1/16, f32(16*sc1*i1), .) rounds the same
+// real number as fma(d8_1, f32(sc1*i1), .).  16*sc1*i1 < 2^26 is a multiple of 16, hence exact in f32.
+__device__ __forceinline__ float unit_value(const float4 h, const float2 m, int i0, int i1x16, const float4 sc) {
+  float accd = __fmul_rn(sc.x, (float)(__float_as_int(h.z) * i0));
+  accd = fmaf(sc.y, (float)(__float_as_int(h.w) * i1x16), accd);
+  float accm = __fmul_rn(sc.z, m.x);
+  accm = fmaf(sc.w, m.y, accm);
+  const float t = __fmul_rn(h.y, accm);
+  return fmaf(h.x, accd, -t);
 }
 
-// unit value for one (row, column): i0/i1 exact sub-block sums, d8/s8 of the column's two Q8_1 blocks
-__device__ __forceinline__ float unit_value(const RowHdr& h, int i0, int i1, float2 d8, float2 s8) {
-  float accd = __fmul_rn(d8.x, (float)(h.sc0 * i0));
-  accd = fmaf(d8.y, (float)(h.sc1 * i1), accd);
-  float accm = __fmul_rn(s8.x, h.fm0);
-  accm = fmaf(s8.y, h.fm1, accm);
-  const float t = __fmul_rn(h.dmin, accm);
-  return fmaf(h.d, accd, -t);
-}
+constexpr int kChunk = 4;                       // superblocks whose headers a warp decodes at a time
+constexpr int kTabBytes = kChunk * 16 * 24;     // per warp: float4 + float2 per (superblock of the chunk, row)
 
-// Shared memory: xs [B][K/4 + 4] words | d8s [B][K/32+2] | s8s [B][K/32+2] | red[72] | bars[n_slots] | part[2][4 tiles][4 p][16][8] f32 |
-// tile slots [n_slots][16 rows][rowb+16].
+// Shared memory: xs [B][K/4 + 8] words | sc4 [K/64][8] float4 | red[72] | bars[n_slots] | part[2][tiles][4 p][16][8] f32 |
+// header tables [warps][kTabBytes] | tile slots [n_slots][16 rows][rowb+16].
 __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kernel(const GemvParams p, const int B) {
   bk_pdl_trigger();
   bk_stamp(p.trace, 0);
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int K = p.K, nsb = K / 256;
   uint32_t* xs = reinterpret_cast<uint32_t*>(smem_raw);
-  float* d8s = reinterpret_cast<float*>(xs + (size_t)B * p.x_row_words);
-  float* s8s = d8s + (size_t)B * p.x_scale_ld;
-  float* red = s8s + (size_t)B * p.x_scale_ld;
+  float* sc4f = reinterpret_cast<float*>(xs + (size_t)B * p.x_row_words);
+  float* red = sc4f + (size_t)(K / 64) * 32;
   uint64_t* bars = reinterpret_cast<uint64_t*>(red + 72);   // red: 8 warp sums per batch row + one rstd per row
   const int tpr = blockDim.x >> 7;   // tiles per round (4 or 2): four warps per tile
   const int nwarps = blockDim.x >> 5;
   float* part = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(bars + p.n_slots) + 15) & ~(uintptr_t)15);
-  uint8_t* slots = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(part + 2 * tpr * 4 * 128) + 127) & ~(uintptr_t)127);
+  uint8_t* tabs = reinterpret_cast<uint8_t*>(part + 2 * tpr * 4 * 128);
+  uint8_t* slots = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tabs + (size_t)nwarps * kTabBytes) + 127) & ~(uintptr_t)127);
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, tid = threadIdx.x;
   // tiles are dealt out evenly: the first tiles_extra CTAs own one tile more than the others
@@ -86,20 +74,21 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
   const int n_rows_cta = min(p.total_vrows, c0 + n_tiles * kTileRows) - c0;
   const uint32_t rowb = (uint32_t)nsb * 144, rstride = rowb + 16;
   const uint32_t slot_bytes = kTileRows * rstride;
-  const int n_slots = p.n_slots;      // >= tiles of the CTA (pool) or a multiple of 4 (ring)
+  const int n_slots = p.n_slots;      // >= tiles of the CTA (pool) or a multiple of tiles-per-round (ring)
   const uint32_t bar_base = smem_u32(bars), slot_base = smem_u32(slots);
   const bool swiglu = p.segs[0].epi == BK_EPI_SWIGLU;
 
-  // one bulk copy per row (padded stride); requested by lane 0 of the warp with p == 0 of the tile's round position
+  // one bulk copy per row (padded stride), issued by the first 16 lanes of the calling warp
   auto request_tile = [&](int t, int slot) {
     const int nr = min(kTileRows, n_rows_cta - t * kTileRows);
-    mbar_expect_tx(bar_base + 8 * slot, nr * rowb);
-    for (int r = 0; r < kTileRows; r++) {
+    if (lane == 0) mbar_expect_tx(bar_base + 8 * slot, nr * rowb);
+    __syncwarp();
+    if (lane < kTileRows) {
       // SwiGLU: slot rows 0..7 are the gate rows of the tile's 8 outputs, rows 8..15 their up rows
-      const int vv = swiglu ? 2 * (r & 7) + (r >> 3) : r;
+      const int vv = swiglu ? 2 * (lane & 7) + (lane >> 3) : lane;
       if (vv < nr) {
         const VRow vr = decode_vrow(p, c0 + t * kTileRows + vv);
-        bulk_g2s(slot_base + slot * slot_bytes + r * rstride, vr.row, rowb, bar_base + 8 * slot);
+        bulk_g2s(slot_base + slot * slot_bytes + lane * rstride, vr.row, rowb, bar_base + 8 * slot);
       }
     }
   };
@@ -110,16 +99,14 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncthreads();
-  if (lane == 0) {
-    for (int t = warp; t < n_tiles && t < n_slots; t += nwarps) request_tile(t, t);
-  }
+  for (int t = warp; t < n_tiles && t < n_slots; t += nwarps) request_tile(t, t);
   bk_stamp(p.trace, 1);
   bk_pdl_wait();
   bk_stamp(p.trace, 2);
 
-  if (p.prologue == BK_PRO_Q8) prologue_q8(p, B, xs, d8s, s8s);
-  else if (p.prologue == BK_PRO_BF16) prologue_bf16_batched<false>(p, B, xs, d8s, s8s, red);
-  else prologue_bf16_batched<true>(p, B, xs, d8s, s8s, red);
+  if (p.prologue == BK_PRO_Q8) prologue_q8<true>(p, B, xs, sc4f, nullptr);
+  else if (p.prologue == BK_PRO_BF16) prologue_bf16_batched<false>(p, B, xs, sc4f, nullptr, red);
+  else prologue_bf16_batched<true>(p, B, xs, sc4f, nullptr, red);
   __syncthreads();
   bk_stamp(p.trace, 3);
 
@@ -129,12 +116,10 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
   const int col0 = 2 * j, col1 = 2 * j + 1;   // C columns of this lane
   // columns beyond the batch read the last real column; their results are never stored
   const int cR = min(R, B - 1), ca = min(col0, B - 1), cb = min(col1, B - 1);
-  const uint32_t* xbase = xs + (size_t)cR * p.x_row_words + tp * 16 + j;
-  const int ld8 = p.x_scale_ld;
-  const float* d8a = d8s + ca * ld8 + 2 * tp;
-  const float* s8a = s8s + ca * ld8 + 2 * tp;
-  const float* d8b = d8s + cb * ld8 + 2 * tp;
-  const float* s8b = s8s + cb * ld8 + 2 * tp;
+  const uint2* xbase = reinterpret_cast<const uint2*>(xs + (size_t)cR * p.x_row_words + tp * 16) + j;
+  const float4* sc4 = reinterpret_cast<const float4*>(sc4f) + tp * 8;
+  float4* tabA = reinterpret_cast<float4*>(tabs + (size_t)warp * kTabBytes);
+  float2* tabB = reinterpret_cast<float2*>(tabA + kChunk * 16);
   const int n_rounds = (n_tiles + tpr - 1) / tpr;
 
   for (int rd = 0; rd < n_rounds; rd++) {
@@ -145,65 +130,75 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
       const uint32_t parity = (uint32_t)((t / n_slots) & 1);
       mbar_wait_bounded(bar_base + 8 * slot, parity, p.status);
       if (rd == 0) bk_stamp(p.trace, 4);
-      const uint8_t* rowA = slots + (size_t)slot * slot_bytes + R * rstride;
+      const uint8_t* tile = slots + (size_t)slot * slot_bytes;
+      const uint8_t* rowA = tile + R * rstride + 16 + tp * 32 + 4 * j;
       const uint8_t* rowB = rowA + 8 * rstride;
-      const uint32_t qoff = 16 + tp * 32 + 4 * j;
-      // classes in the order 0,4,2,6,1,5,3,7 so the tree closes with three live partial sums per value
-      float stk0[4], stk1[4];
+      // class c = s mod 8 collects the unit values of s = c, c+8, ... in ascending order
+      float P[8][4];
 #pragma unroll
-      for (int ci = 0; ci < 8; ci++) {
-        const int c = ((ci & 1) << 2) | (ci & 2) | ((ci >> 2) & 1);
-        float P[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        for (int s = c; s < nsb; s += 8) {
-          const uint8_t* sa = rowA + s * 144;
-          const uint8_t* sb = rowB + s * 144;
-          const uint32_t qa0 = *reinterpret_cast<const uint32_t*>(sa + qoff);
-          const uint32_t qa2 = *reinterpret_cast<const uint32_t*>(sa + qoff + 16);
-          const uint32_t qb0 = *reinterpret_cast<const uint32_t*>(sb + qoff);
-          const uint32_t qb2 = *reinterpret_cast<const uint32_t*>(sb + qoff + 16);
-          const uint32_t* xr = xbase + s * 64;
-          const uint32_t x00 = xr[0], x01 = xr[4], x10 = xr[8], x11 = xr[12];
-          int ilo[4] = {0, 0, 0, 0}, ihi[4] = {0, 0, 0, 0};
-          mma_s8(ilo, qa0 & 0x0f0f0f0fu, qb0 & 0x0f0f0f0fu, qa2 & 0x0f0f0f0fu, qb2 & 0x0f0f0f0fu, x00, x01);
-          mma_s8(ihi, (qa0 >> 4) & 0x0f0f0f0fu, (qb0 >> 4) & 0x0f0f0f0fu, (qa2 >> 4) & 0x0f0f0f0fu, (qb2 >> 4) & 0x0f0f0f0fu,
-                 x10, x11);
-          const RowHdr ha = decode_hdr(sa, tp), hb = decode_hdr(sb, tp);
-          const float2 da = *reinterpret_cast<const float2*>(d8a + 8 * s);
-          const float2 sa8 = *reinterpret_cast<const float2*>(s8a + 8 * s);
-          const float2 db = *reinterpret_cast<const float2*>(d8b + 8 * s);
-          const float2 sb8 = *reinterpret_cast<const float2*>(s8b + 8 * s);
-          P[0] = __fadd_rn(P[0], unit_value(ha, ilo[0], ihi[0], da, sa8));
-          P[1] = __fadd_rn(P[1], unit_value(ha, ilo[1], ihi[1], db, sb8));
-          P[2] = __fadd_rn(P[2], unit_value(hb, ilo[2], ihi[2], da, sa8));
-          P[3] = __fadd_rn(P[3], unit_value(hb, ilo[3], ihi[3], db, sb8));
-        }
-        // tree: ci 0,1 -> a = P0+P4; ci 2,3 -> b = P2+P6, ab = a+b; ci 4,5 -> a'; ci 6,7 -> b', T = ab + (a'+b')
+      for (int c = 0; c < 8; c++) {
 #pragma unroll
-        for (int v = 0; v < 4; v++) {
-          if ((ci & 1) == 0) {
-            stk1[v] = P[v];
-          } else {
-            const float pair = __fadd_rn(stk1[v], P[v]);
-            if (ci == 1 || ci == 5) {
-              stk0[v] = pair;
-            } else {
-              const float quad = __fadd_rn(stk0[v], pair);
-              if (ci == 3) T[v] = quad;
-              else T[v] = __fadd_rn(T[v], quad);
+        for (int v = 0; v < 4; v++) P[c][v] = 0.0f;
+      }
+      for (int s0 = 0; s0 < nsb; s0 += 8) {
+#pragma unroll
+        for (int h = 0; h < 8 / kChunk; h++) {
+          const int sbase = s0 + kChunk * h;
+          if (sbase < nsb) {
+            __syncwarp();   // the previous chunk's table has been read by every lane
+#pragma unroll
+            for (int k = 0; k < kChunk * 16 / 32; k++) {
+              const int e = lane + 32 * k, row = e & 15, s = sbase + (e >> 4);
+              if (s < nsb) {
+                const uint4 hw = *reinterpret_cast<const uint4*>(tile + row * rstride + s * 144);
+                uint32_t sc2, mn2;
+                bk_q4k_scale_min_pair(hw.y, hw.z, hw.w, tp, sc2, mn2);
+                tabA[e] = make_float4(bk_f16_to_f32((uint16_t)(hw.x & 0xffffu)), bk_f16_to_f32((uint16_t)(hw.x >> 16)),
+                                      __int_as_float((int)(sc2 & 0xffu)), __int_as_float((int)(sc2 >> 8)));
+                tabB[e] = make_float2((float)(int)(mn2 & 0xffu), (float)(int)(mn2 >> 8));
+              }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int sl = 0; sl < kChunk; sl++) {
+              const int s = sbase + sl;
+              if (s < nsb) {
+                const uint32_t qa0 = *reinterpret_cast<const uint32_t*>(rowA + s * 144);
+                const uint32_t qa2 = *reinterpret_cast<const uint32_t*>(rowA + s * 144 + 16);
+                const uint32_t qb0 = *reinterpret_cast<const uint32_t*>(rowB + s * 144);
+                const uint32_t qb2 = *reinterpret_cast<const uint32_t*>(rowB + s * 144 + 16);
+                const uint2 xlo = xbase[s * 32], xhi = xbase[s * 32 + 4];
+                int ilo[4] = {0, 0, 0, 0}, ihi[4] = {0, 0, 0, 0};
+                mma_u8s8(ilo, qa0 & 0x0f0f0f0fu, qb0 & 0x0f0f0f0fu, qa2 & 0x0f0f0f0fu, qb2 & 0x0f0f0f0fu, xlo.x, xlo.y);
+                mma_u8s8(ihi, qa0 & 0xf0f0f0f0u, qb0 & 0xf0f0f0f0u, qa2 & 0xf0f0f0f0u, qb2 & 0xf0f0f0f0u, xhi.x, xhi.y);
+                const float4 ha = tabA[sl * 16 + R], hb = tabA[sl * 16 + R + 8];
+                const float2 ma = tabB[sl * 16 + R], mb = tabB[sl * 16 + R + 8];
+                const float4 sa = sc4[s * 32 + ca], sb = sc4[s * 32 + cb];
+                float* Pc = P[kChunk * h + sl];
+                Pc[0] = __fadd_rn(Pc[0], unit_value(ha, ma, ilo[0], ihi[0], sa));
+                Pc[1] = __fadd_rn(Pc[1], unit_value(ha, ma, ilo[1], ihi[1], sb));
+                Pc[2] = __fadd_rn(Pc[2], unit_value(hb, mb, ilo[2], ihi[2], sa));
+                Pc[3] = __fadd_rn(Pc[3], unit_value(hb, mb, ilo[3], ihi[3], sb));
+              }
             }
           }
         }
       }
+      // T_p = ((P0+P4)+(P2+P6)) + ((P1+P5)+(P3+P7))
+#pragma unroll
+      for (int v = 0; v < 4; v++)
+        T[v] = __fadd_rn(__fadd_rn(__fadd_rn(P[0][v], P[4][v]), __fadd_rn(P[2][v], P[6][v])),
+                         __fadd_rn(__fadd_rn(P[1][v], P[5][v]), __fadd_rn(P[3][v], P[7][v])));
     }
     __syncwarp();
-    // ring refill: once the four p-warps of a tile are done with a slot the round barrier below releases it
     float* pw = part + (size_t)(rd & 1) * (tpr * 4 * 128) + (size_t)(tq * 4 + tp) * 128;
     pw[R * 8 + col0] = T[0];
     pw[R * 8 + col1] = T[1];
     pw[(R + 8) * 8 + col0] = T[2];
     pw[(R + 8) * 8 + col1] = T[3];
     __syncthreads();   // all partial totals of the round are in shared memory; its weight slots are free
-    if (lane == 0 && tp == 0) {
+    // ring refill: the round barrier above released the slot
+    if (tp == 0) {
       const int t2 = t + n_slots;
       if (t < n_tiles && t2 < n_tiles) request_tile(t2, t % n_slots);
     }
@@ -236,8 +231,8 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
 }
 
 size_t mma_fixed_smem(int K, int B, int n_slots, int tpr) {
-  return (size_t)B * (K / 4 + 4) * 4 + (size_t)B * (K / 32 + 2) * 8 + 288 + (size_t)n_slots * 8 + 16 +
-         (size_t)2 * tpr * 4 * 128 * 4 + 128;
+  return (size_t)B * (K / 4 + 8) * 4 + (size_t)(K / 64) * 8 * 16 + 288 + (size_t)n_slots * 8 + 16 +
+         (size_t)2 * tpr * 4 * 128 * 4 + (size_t)tpr * 4 * kTabBytes + 128;
 }
 
 }  // namespace
@@ -279,8 +274,8 @@ int32_t bk_gemv_mma_launch(void* params, int K, int B, int vrows, bool has_swigl
   p.depth = 0;
   p.group_rows = kTileRows;
   p.x_unit_words = 16;
-  p.x_row_words = K / 4 + 4;
-  p.x_scale_ld = K / 32 + 2;   // two floats of padding: the four column pairs of a quad land in different banks
+  p.x_row_words = K / 4 + 8;   // 8 words of padding: the 64-bit loads of a half-warp (4 columns x 4 j) tile the 32 banks
+  p.x_scale_ld = 0;            // scales live in the float4 layout of the tensor-core path
   const size_t smem = mma_fixed_smem(K, B, n_slots, tpr) + (size_t)n_slots * tile_bytes;
   static size_t configured = 0;
   if (smem > configured) {

@@ -47,31 +47,58 @@ struct GemvParams {
   SegDev segs[4];
 };
 
+// ---- staged activation layouts ---------------------------------------------------
+// Plain (dp4a kernel): quants of block blk at xs[b*x_row_words + (blk>>1)*x_unit_words + (blk&1)*8 + w], w = 0..7;
+// scales d8s[b*x_scale_ld + blk], s8s likewise.
+// MMA (TC = true): the eight words of a block are stored in the order 0,4,1,5,2,6,3,7 so that the two words a lane
+// feeds to one mma (w = j and j+4) are one 64-bit load; the scales of unit u = blk>>1 and column b form one float4
+// {d8 of block 2u, d8 of block 2u+1 divided by 16, s8 of 2u, s8 of 2u+1} at sc4[u*8 + b] (s8s is unused).
+// The division by 16 pairs with high nibbles left in place (16*q) in the integer dot: the product is unchanged.
+template <bool TC>
+__device__ __forceinline__ uint32_t* x_block_ptr(const GemvParams& p, uint32_t* xs, int b, int blk) {
+  return xs + (size_t)b * p.x_row_words + (blk >> 1) * p.x_unit_words + (blk & 1) * 8;
+}
+template <bool TC>
+__device__ __forceinline__ int x_word_pos(int w) { return TC ? ((w & 3) * 2 + (w >> 2)) : w; }
+template <bool TC>
+__device__ __forceinline__ void store_block_scales(const GemvParams& p, float* d8s, float* s8s, int b, int blk, float d8,
+                                                   float s8) {
+  if (TC) {
+    float* e = d8s + ((size_t)((blk >> 1) * 8 + b) * 4 + (blk & 1));
+    e[0] = (blk & 1) ? __fmul_rn(d8, 0.0625f) : d8;
+    e[2] = s8;
+  } else {
+    d8s[b * p.x_scale_ld + blk] = d8;
+    s8s[b * p.x_scale_ld + blk] = s8;
+  }
+}
+
 // ---- prologues ---------------------------------------------------------------
 
 // Q8_1 blocks [B][nblk][36] -> shared layout
+template <bool TC>
 __device__ void prologue_q8(const GemvParams& p, const int B, uint32_t* xs, float* d8s, float* s8s) {
   const int nblk = p.K / 32;
   const uint32_t* src = reinterpret_cast<const uint32_t*>(p.x);
   for (int i = threadIdx.x; i < B * nblk; i += blockDim.x) {
     int b = i / nblk, blk = i - b * nblk;
     const uint32_t* s = src + (size_t)i * 9;
-    uint32_t* dst = xs + (size_t)b * p.x_row_words + (blk >> 1) * p.x_unit_words + (blk & 1) * 8;
+    uint32_t* dst = x_block_ptr<TC>(p, xs, b, blk);
     int qsum = 0;
 #pragma unroll
     for (int k = 0; k < 8; k++) {
       uint32_t w = s[k];
-      dst[k] = w;
+      dst[x_word_pos<TC>(k)] = w;
       qsum = bk_dp4a_ss(w, 0x01010101u, qsum);
     }
     float d8 = bk_q8half_to_f32((uint16_t)(s[8] & 0xffffu));
-    d8s[b * p.x_scale_ld + blk] = d8;
-    s8s[b * p.x_scale_ld + blk] = __fmul_rn(d8, (float)qsum);
+    store_block_scales<TC>(p, d8s, s8s, b, blk, d8, __fmul_rn(d8, (float)qsum));
   }
 }
 
 // quantise 8 consecutive values held by this thread; the 4 threads of an aligned
 // lane group hold one 32-element block (packQ8_1, bench/bench.ts:53-72, in f32)
+template <bool TC>
 __device__ __forceinline__ void quant_chunk(const GemvParams& p, const float (&y)[8], int q, int b, int nblk, uint32_t* xs,
                                             float* d8s, float* s8s) {
   float amax = 0.0f;
@@ -97,13 +124,12 @@ __device__ __forceinline__ void quant_chunk(const GemvParams& p, const float (&y
   uint32_t w1 = (uint32_t)(qs[4] & 0xff) | ((uint32_t)(qs[5] & 0xff) << 8) | ((uint32_t)(qs[6] & 0xff) << 16) |
                 ((uint32_t)(qs[7] & 0xff) << 24);
   int blk = q >> 2;
-  uint32_t* dst = xs + (size_t)b * p.x_row_words + (blk >> 1) * p.x_unit_words + (blk & 1) * 8 + (q & 3) * 2;
-  dst[0] = w0;
-  dst[1] = w1;
+  uint32_t* dst = x_block_ptr<TC>(p, xs, b, blk);
+  dst[x_word_pos<TC>((q & 3) * 2)] = w0;
+  dst[x_word_pos<TC>((q & 3) * 2 + 1)] = w1;
   if ((q & 3) == 0) {
     float d8 = bk_q8half_to_f32(bk_f32_to_f16_trunc(d));
-    d8s[b * p.x_scale_ld + blk] = d8;
-    s8s[b * p.x_scale_ld + blk] = __fmul_rn(d8, (float)qsum);
+    store_block_scales<TC>(p, d8s, s8s, b, blk, d8, __fmul_rn(d8, (float)qsum));
   }
 }
 
@@ -186,7 +212,7 @@ __device__ void prologue_bf16(const GemvParams& p, const int B, uint32_t* xs, fl
           y[e + 1] = __uint_as_float(pk & 0xffff0000u);
         }
       }
-      quant_chunk(p, y, q, b, nblk, xs, d8s, s8s);
+      quant_chunk<false>(p, y, q, b, nblk, xs, d8s, s8s);
     }
     (void)one_pass;
   }
@@ -248,7 +274,7 @@ __device__ void prologue_bf16_batched(const GemvParams& p, const int B, uint32_t
         y[e + 1] = __uint_as_float(pk & 0xffff0000u);
       }
     }
-    quant_chunk(p, y, q, b, nblk, xs, d8s, s8s);
+    quant_chunk<true>(p, y, q, b, nblk, xs, d8s, s8s);
   }
 }
 
