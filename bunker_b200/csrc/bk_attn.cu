@@ -35,6 +35,7 @@ struct AttnParams {
   const int32_t* pos;
   uint16_t* out;
   uint8_t* out_q8;
+  int out_q8_staged;
   float* scratch;
   const uint16_t* gate;
   int B, Hq, Hkv, rot_half, max_len, split_len, max_splits, fused;
@@ -155,7 +156,8 @@ __device__ void combine_head_warp(const AttnParams& p, int b, int h, int ns, flo
       y[2 * e] = __uint_as_float(o[e] << 16);
       y[2 * e + 1] = __uint_as_float(o[e] & 0xffff0000u);
     }
-    bk_q8_1_store<8>(p.out_q8 + ((((size_t)b * p.Hq + h) * kHD + lane * 8) >> 5) * 36, y, (lane & 3) * 8);
+    if (p.out_q8_staged) bk_staged_store<8>(p.out_q8, p.Hq * kHD, p.B, b, (h * kHD + lane * 8) >> 5, y, (lane & 3) * 8);
+    else bk_q8_1_store<8>(p.out_q8 + ((((size_t)b * p.Hq + h) * kHD + lane * 8) >> 5) * 36, y, (lane & 3) * 8);
   }
 }
 
@@ -477,6 +479,9 @@ int32_t bkAttnDecode(const bkAttnArgs* args) {
   p.pos = bk_ptr<int32_t>(a.pos);
   p.out = bk_ptr<uint16_t>(a.out);
   p.out_q8 = bk_ptr<uint8_t>(a.out_q8);
+  p.out_q8_staged = a.out_q8_layout == BK_Q8_STAGED;
+  BK_ARG(a.out_q8_layout == BK_Q8_BLOCKS || (a.out_q8_layout == BK_Q8_STAGED && a.B <= 8),
+         "bkAttnDecode: out_q8_layout %d (a staged image needs B <= 8)", a.out_q8_layout);
   p.scratch = bk_ptr<float>(a.scratch);
   p.gate = bk_ptr<uint16_t>(a.gate);
   p.B = a.B;

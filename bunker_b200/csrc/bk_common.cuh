@@ -187,6 +187,57 @@ BK_DEVINL void bk_q8_1_store(uint8_t* blk, const float (&y)[PER], int idx_in_blo
   }
 }
 
+// ---- staged activation image of the tensor-core GEMV (batch 3..8) ---------------------
+// The exact bytes that kernel keeps in shared memory, so that its prologue is one bulk copy:
+//   words  [B][K/4 + 8]   Q8_1 quants, the eight words of a block in the order 0,4,1,5,2,6,3,7
+//   float4 [K/64][8]      per 64-value unit u and column b: {d8 of block 2u, d8 of block 2u+1 / 16,
+//                          s8 of 2u, s8 of 2u+1}, d8 = the block scale after its f16 round trip, s8 = d8 * sum(q)
+__host__ __device__ __forceinline__ size_t bk_staged_row_words(int K) { return (size_t)K / 4 + 8; }
+__host__ __device__ __forceinline__ size_t bk_staged_bytes(int K, int B) { return (size_t)B * bk_staged_row_words(K) * 4 + (size_t)(K / 64) * 8 * 16; }
+
+// Same contract as bk_q8_1_store, writing block blk of column b into a staged image.
+template <int PER>
+BK_DEVINL void bk_staged_store(uint8_t* img, int K, int B, int b, int blk, const float (&y)[PER], int idx_in_block) {
+  constexpr int GROUP = 32 / PER;
+  float amax = 0.0f;
+#pragma unroll
+  for (int e = 0; e < PER; e++) amax = fmaxf(amax, fabsf(y[e]));
+#pragma unroll
+  for (int off = GROUP / 2; off >= 1; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  const float d = __fdiv_rn(amax, 127.0f);
+  const float id = (d == 0.0f) ? 1.0f : __fdiv_rn(1.0f, d);
+  int sum = 0;
+  int qs[PER];
+#pragma unroll
+  for (int e = 0; e < PER; e++) {
+    int v = __float2int_rd(fmaf(y[e], id, 0.5f));
+    qs[e] = max(-128, min(127, v));
+    sum += qs[e];  // of the stored quants, as a reader of the blocks would recompute it
+  }
+#pragma unroll
+  for (int off = GROUP / 2; off >= 1; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+  uint32_t* xw = reinterpret_cast<uint32_t*>(img) + (size_t)b * bk_staged_row_words(K) + (blk >> 1) * 16 + (blk & 1) * 8;
+  if (PER == 1) {
+    // byte idx of the block lives in word idx/4, stored at position (w&3)*2 + (w>>2)
+    const int w = idx_in_block >> 2;
+    reinterpret_cast<uint8_t*>(xw + ((w & 3) * 2 + (w >> 2)))[idx_in_block & 3] = (uint8_t)(int8_t)qs[0];
+  } else {
+    static_assert(PER == 1 || PER % 4 == 0, "values per lane");
+#pragma unroll
+    for (int e = 0; e < PER / 4 * 4; e += 4) {
+      const int w = (idx_in_block + e) >> 2;
+      xw[(w & 3) * 2 + (w >> 2)] = (uint32_t)(qs[e] & 0xff) | ((uint32_t)(qs[e + 1] & 0xff) << 8) |
+                                   ((uint32_t)(qs[e + 2] & 0xff) << 16) | ((uint32_t)(qs[e + 3] & 0xff) << 24);
+    }
+  }
+  if (idx_in_block == 0) {
+    const float d8 = bk_q8half_to_f32(bk_f32_to_f16_trunc(d));
+    float* e4 = reinterpret_cast<float*>(img + (size_t)B * bk_staged_row_words(K) * 4) + ((size_t)((blk >> 1) * 8 + b) * 4 + (blk & 1));
+    e4[0] = (blk & 1) ? __fmul_rn(d8, 0.0625f) : d8;
+    e4[2] = __fmul_rn(d8, (float)sum);
+  }
+}
+
 // ---- Q4_K superblock header -------------------------------------------------
 // bytes [4,16) of a superblock as three words w0,w1,w2; sub-block j in 0..7
 BK_DEVINL void bk_q4k_scale_min(uint32_t w0, uint32_t w1, uint32_t w2, int j, int& sc, int& mn) {

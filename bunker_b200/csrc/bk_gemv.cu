@@ -453,14 +453,16 @@ __global__ void quant_q8_1_kernel(const void* x, int K, int B, uint8_t* out) {
 // ---- host entry points ---------------------------------------------------------
 
 int32_t bk_gemv_mma_launch(void* params, int K, int B, int vrows, bool has_swiglu);  // bk_gemv_mma.cu
-bool bk_gemv_mma_fits(int K, int B);
 
 int32_t bk_gemv_launch(const bkGemvArgs& a) {
   BkContext& c = bk_ctx();
   BK_ARG(a.K > 0 && a.K % 256 == 0, "bkGemvQ4K: K=%d is not a positive multiple of 256", a.K);
   BK_ARG(a.B >= 1 && a.B <= 8, "bkGemvQ4K: B=%d outside 1..8", a.B);
   BK_ARG(a.n_segs >= 1 && a.n_segs <= 4, "bkGemvQ4K: n_segs=%d outside 1..4", a.n_segs);
-  BK_ARG(a.prologue >= BK_PRO_Q8 && a.prologue <= BK_PRO_RMSNORM, "bkGemvQ4K: unknown prologue %d", a.prologue);
+  BK_ARG(a.prologue >= BK_PRO_Q8 && a.prologue <= BK_PRO_STAGED, "bkGemvQ4K: unknown prologue %d", a.prologue);
+  if (a.prologue == BK_PRO_STAGED)
+    BK_ARG(a.B >= 3 && bk_gemv_mma_fits(a.K, a.B),
+           "bkGemvQ4K: a staged activation needs batch 3..8 and a K that fits the tensor-core path (K=%d B=%d)", a.K, a.B);
   BK_ARG(a.x != 0 && (a.x & 15) == 0, "bkGemvQ4K: x must be a non-null 16-byte aligned device pointer");
   if (a.prologue == BK_PRO_RMSNORM)
     BK_ARG(a.norm_w != 0 && (a.norm_w & 15) == 0, "bkGemvQ4K: norm_w must be non-null and 16-byte aligned");

@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
   uint64_t* bars = reinterpret_cast<uint64_t*>(red + 72);   // red: 8 warp sums per batch row + one rstd per row
   const int tpr = blockDim.x >> 7;   // tiles per round (4 or 2): four warps per tile
   const int nwarps = blockDim.x >> 5;
-  float* part = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(bars + p.n_slots) + 15) & ~(uintptr_t)15);
+  float* part = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(bars + p.n_slots + 1) + 15) & ~(uintptr_t)15);
   uint8_t* tabs = reinterpret_cast<uint8_t*>(part + 2 * tpr * 4 * 128);
   uint8_t* slots = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tabs + (size_t)nwarps * kTabBytes) + 127) & ~(uintptr_t)127);
 
@@ -93,8 +93,9 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
     }
   };
   // ---- before the dependency wait: weights only ----
+  const uint32_t xbar = bar_base + 8 * n_slots;   // arrival of a staged activation image
   if (lane == 0) {
-    for (int s = warp; s < n_slots; s += nwarps) mbar_init(bar_base + 8 * s, 1);
+    for (int s = warp; s < n_slots + 1; s += nwarps) mbar_init(bar_base + 8 * s, 1);
   }
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -104,7 +105,15 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
   bk_pdl_wait();
   bk_stamp(p.trace, 2);
 
-  if (p.prologue == BK_PRO_Q8) prologue_q8<true>(p, B, xs, sc4f, nullptr);
+  if (p.prologue == BK_PRO_STAGED) {
+    // the producer wrote exactly the bytes of xs | sc4: one bulk copy, nothing to compute
+    if (tid == 0) {
+      const uint32_t bytes = (uint32_t)bk_staged_bytes(K, B);
+      mbar_expect_tx(xbar, bytes);
+      bulk_g2s(smem_u32(xs), p.x, bytes, xbar);
+    }
+    mbar_wait_bounded(xbar, 0, p.status);
+  } else if (p.prologue == BK_PRO_Q8) prologue_q8<true>(p, B, xs, sc4f, nullptr);
   else if (p.prologue == BK_PRO_BF16) prologue_bf16_batched<false>(p, B, xs, sc4f, nullptr, red);
   else prologue_bf16_batched<true>(p, B, xs, sc4f, nullptr, red);
   __syncthreads();
@@ -231,7 +240,7 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
 }
 
 size_t mma_fixed_smem(int K, int B, int n_slots, int tpr) {
-  return (size_t)B * (K / 4 + 8) * 4 + (size_t)(K / 64) * 8 * 16 + 288 + (size_t)n_slots * 8 + 16 +
+  return (size_t)B * (K / 4 + 8) * 4 + (size_t)(K / 64) * 8 * 16 + 288 + (size_t)(n_slots + 1) * 8 + 16 +
          (size_t)2 * tpr * 4 * 128 * 4 + (size_t)tpr * 4 * kTabBytes + 128;
 }
 

@@ -65,6 +65,7 @@ template <typename T>
 static inline T* bk_ptr(uint64_t p) { return reinterpret_cast<T*>(static_cast<uintptr_t>(p)); }
 
 // internal launchers shared between translation units
+bool bk_gemv_mma_fits(int K, int B);   // whether the batch-3..8 tensor-core GEMV can hold this K (else column pairs)
 int32_t bk_gemv_launch(const bkGemvArgs& a);
 int32_t bk_argmax_launch(uint64_t logits, int32_t V, int32_t B, uint64_t idx, uint64_t val, uint64_t scratch,
                          uint64_t pos, uint64_t hist, int32_t hist_ld, int32_t hist_rows);

@@ -18,6 +18,7 @@
 #include <unordered_map>
 #include <vector>
 
+#include "bk_common.cuh"
 #include "bk_internal.h"
 
 namespace {
@@ -140,8 +141,9 @@ int32_t enqueue_step(Model& m, int parity) {
   auto set_input = [&](bkGemvArgs& g, uint64_t x, int K, uint64_t norm_w) -> int32_t {
     g.K = K; g.B = B; g.eps = c.eps;
     if (q8_handoff) {
-      PROF(PC_QUANT, bkRmsNormQuantQ8_1(x, norm_w, K, B, c.eps, m.xq));
-      g.prologue = BK_PRO_Q8; g.x = m.xq;
+      const bool staged = bk_gemv_mma_fits(K, B);   // else the GEMV runs as column pairs reading plain blocks
+      PROF(PC_QUANT, bkRmsNormQuantQ8_1(x, norm_w, K, B, c.eps, m.xq, staged ? BK_Q8_STAGED : BK_Q8_BLOCKS));
+      g.prologue = staged ? BK_PRO_STAGED : BK_PRO_Q8; g.x = m.xq;
     } else {
       g.prologue = norm_w ? BK_PRO_RMSNORM : BK_PRO_BF16; g.x = x; g.norm_w = norm_w;
     }
@@ -166,12 +168,14 @@ int32_t enqueue_step(Model& m, int parity) {
       ga.conv_w = L.conv_w; ga.conv_state_in = L.conv_state[parity]; ga.conv_state_new = L.conv_state[parity ^ 1];
       ga.A_log = L.A_log; ga.dt_bias = L.dt_bias; ga.norm_w = L.gnorm;
       ga.S_in = L.S; ga.S_new = L.S;  // in place: each thread rewrites exactly the rows it read
-      ga.out = m.attn_out; ga.out_q8 = q8_handoff ? m.attn_q8 : 0; ga.B = B; ga.Hk = m.Hk; ga.Hv = m.Hv; ga.apply_conv = 1;
+      const bool zd_staged = q8_handoff && bk_gemv_mma_fits(m.ZD, B);
+      ga.out = m.attn_out; ga.out_q8 = q8_handoff ? m.attn_q8 : 0; ga.out_q8_layout = zd_staged ? BK_Q8_STAGED : BK_Q8_BLOCKS;
+      ga.B = B; ga.Hk = m.Hk; ga.Hv = m.Hv; ga.apply_conv = 1;
       ga.state_is_settled = 1;  // this layer's state was last written one whole step ago
       PROF(PC_GDN, bkGdnStep(&ga));
       memset(&g, 0, sizeof(g));
       g.K = m.ZD; g.B = B; g.n_segs = 1;
-      g.prologue = q8_handoff ? BK_PRO_Q8 : BK_PRO_BF16; g.x = q8_handoff ? m.attn_q8 : m.attn_out;
+      g.prologue = zd_staged ? BK_PRO_STAGED : q8_handoff ? BK_PRO_Q8 : BK_PRO_BF16; g.x = q8_handoff ? m.attn_q8 : m.attn_out;
       if (m.tp == 1) {
         g.segs[0] = bkGemvSeg{L.out_proj, 0, m.h1, m.x[cur], H, BK_EPI_ADD_BF16, H, 0};
         PROF(PC_GEMV_OUT, bk_gemv_launch(g));
@@ -192,7 +196,9 @@ int32_t enqueue_step(Model& m, int parity) {
       memset(&aa, 0, sizeof(aa));
       aa.qg = m.qg; aa.k = m.kbuf; aa.v = m.vbuf; aa.q_norm_w = L.q_norm; aa.k_norm_w = L.k_norm;
       aa.cos_t = m.cos_t; aa.sin_t = m.sin_t; aa.k_cache = L.kc; aa.v_cache = L.vc; aa.pos = m.pos;
-      aa.out = m.attn_out; aa.out_q8 = q8_handoff ? m.attn_q8 : 0; aa.scratch = m.attn_scratch;
+      const bool o_staged = q8_handoff && bk_gemv_mma_fits(m.Hq * c.head_dim, B);
+      aa.out = m.attn_out; aa.out_q8 = q8_handoff ? m.attn_q8 : 0; aa.out_q8_layout = o_staged ? BK_Q8_STAGED : BK_Q8_BLOCKS;
+      aa.scratch = m.attn_scratch;
       aa.B = B; aa.Hq = m.Hq; aa.Hkv = m.Hkv; aa.HD = c.head_dim; aa.rot_half = c.rot_dim / 2; aa.max_len = c.max_len;
       aa.split_len = m.split_len; aa.max_pos = c.max_len - 1; aa.scale = 1.0f / sqrtf((float)c.head_dim);
       aa.fused_norm_rope = 1;
@@ -200,7 +206,7 @@ int32_t enqueue_step(Model& m, int parity) {
       PROF(PC_ATTN, bkAttnDecode(&aa));
       memset(&g, 0, sizeof(g));
       g.K = m.Hq * c.head_dim; g.B = B; g.n_segs = 1;
-      g.prologue = q8_handoff ? BK_PRO_Q8 : BK_PRO_BF16; g.x = q8_handoff ? m.attn_q8 : m.attn_out;
+      g.prologue = o_staged ? BK_PRO_STAGED : q8_handoff ? BK_PRO_Q8 : BK_PRO_BF16; g.x = q8_handoff ? m.attn_q8 : m.attn_out;
       if (m.tp == 1) {
         g.segs[0] = bkGemvSeg{L.o, 0, m.h1, m.x[cur], H, BK_EPI_ADD_BF16, H, 0};
         PROF(PC_GEMV_OUT, bk_gemv_launch(g));
@@ -417,8 +423,13 @@ int32_t bkModelFinalize(uint64_t model) {
   TRY(dev_alloc(m, (size_t)B * m.Hv * 4, &m.a));
   TRY(dev_alloc(m, (size_t)B * m.Hv * 4, &m.b));
   TRY(dev_alloc(m, (size_t)B * (m.ZD > attn_w ? m.ZD : attn_w) * 2, &m.attn_out));
-  TRY(dev_alloc(m, (size_t)B * (m.ZD > attn_w ? m.ZD : attn_w) / 32 * 36, &m.attn_q8));
-  TRY(dev_alloc(m, (size_t)B * (m.inter > H ? m.inter : H) / 32 * 36, &m.xq));
+  {  // quantised handoff buffers: room for either layout
+    const int ka = m.ZD > attn_w ? m.ZD : attn_w, kx = m.inter > H ? m.inter : H;
+    const size_t ba = (size_t)B * ka / 32 * 36, bx = (size_t)B * kx / 32 * 36;
+    const size_t sa = B <= 8 ? bk_staged_bytes(ka, B) : 0, sx = B <= 8 ? bk_staged_bytes(kx, B) : 0;
+    TRY(dev_alloc(m, ba > sa ? ba : sa, &m.attn_q8));
+    TRY(dev_alloc(m, bx > sx ? bx : sx, &m.xq));
+  }
   TRY(dev_alloc(m, (size_t)B * m.QG * 2, &m.qg));
   TRY(dev_alloc(m, (size_t)B * m.KVD * 2, &m.kbuf));
   TRY(dev_alloc(m, (size_t)B * m.KVD * 2, &m.vbuf));

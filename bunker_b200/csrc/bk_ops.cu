@@ -93,7 +93,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t* x, const u
 // At batch >= 3 the projection kernels read their activation as ready Q8_1 blocks instead of each of the
 // 148 CTAs normalising and quantising all batch rows again.  NORM: one CTA per batch row (the canonical
 // 256-thread sum of squares).  Plain: 256 chunks of 8 values per CTA.  Output blocks [B][K/32][36].
-template <bool NORM>
+// STAGED: the output is the staged image of the tensor-core GEMV instead of 36-byte blocks.
+template <bool NORM, bool STAGED>
 __global__ void __launch_bounds__(256) quant_rows_kernel(const uint16_t* x, const uint16_t* w, int K, float eps,
                                                          uint8_t* out) {
   bk_pdl_trigger();
@@ -139,7 +140,8 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const uint16_t* x, cons
 #pragma unroll
       for (int e = 0; e < 8; e++)
         y[e] = bk_bf16_to_f32(bk_f32_to_bf16(__fmul_rn(__fmul_rn(v[e], rstd), __fadd_rn(1.0f, wv[e]))));
-      bk_q8_1_store<8>(orow + (size_t)(q >> 2) * 36, y, (q & 3) * 8);
+      if (STAGED) bk_staged_store<8>(out, K, gridDim.y, b, q >> 2, y, (q & 3) * 8);
+      else bk_q8_1_store<8>(orow + (size_t)(q >> 2) * 36, y, (q & 3) * 8);
     }
   } else {
     bk_pdl_wait();
@@ -147,7 +149,8 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const uint16_t* x, cons
     if (q < nchunk) {
       float y[8];
       load8_bf16(row + (size_t)q * 8, y);
-      bk_q8_1_store<8>(orow + (size_t)(q >> 2) * 36, y, (q & 3) * 8);
+      if (STAGED) bk_staged_store<8>(out, K, gridDim.y, b, q >> 2, y, (q & 3) * 8);
+      else bk_q8_1_store<8>(orow + (size_t)(q >> 2) * 36, y, (q & 3) * 8);
     }
   }
 }
@@ -206,6 +209,7 @@ struct GdnParams {
   float* o_raw;
   uint16_t* conv_out;
   uint8_t* out_q8;
+  int out_q8_staged;
   int B, Hk, Hv, apply_conv;
   int early;  // state / conv state / weights are not outputs of the immediately preceding launch
   unsigned long long* trace;
@@ -356,7 +360,8 @@ __global__ void __launch_bounds__(576) gdn_step_kernel(const GdnParams p) {
     p.out[((size_t)b * p.Hv + hv) * D + t] = ob;
     if (p.out_q8) {  // warp w of the first four holds block w of this head
       const float y[1] = {bk_bf16_to_f32(ob)};
-      bk_q8_1_store<1>(p.out_q8 + (((size_t)b * p.Hv + hv) * 4 + warp) * 36, y, lane);
+      if (p.out_q8_staged) bk_staged_store<1>(p.out_q8, p.Hv * D, p.B, b, hv * 4 + warp, y, lane);
+      else bk_q8_1_store<1>(p.out_q8 + (((size_t)b * p.Hv + hv) * 4 + warp) * 36, y, lane);
     }
   }
   bk_stamp(p.trace, 5);
@@ -510,20 +515,28 @@ int32_t bkRmsNorm(uint64_t x, uint64_t w, int32_t H, int32_t B, float eps, uint6
   return BK_OK;
 }
 
-int32_t bkRmsNormQuantQ8_1(uint64_t x, uint64_t w, int32_t K, int32_t B, float eps, uint64_t out_blocks) {
+int32_t bkRmsNormQuantQ8_1(uint64_t x, uint64_t w, int32_t K, int32_t B, float eps, uint64_t out, int32_t layout) {
   BK_REQUIRE_INIT();
   BK_ARG(K > 0 && K % 256 == 0 && B > 0, "bkRmsNormQuantQ8_1: bad shape K=%d B=%d (K a multiple of 256)", K, B);
-  BK_ARG(x && out_blocks && ((x | w) & 15) == 0 && (out_blocks & 3) == 0, "bkRmsNormQuantQ8_1: null or misaligned pointer");
+  BK_ARG(x && out && ((x | w) & 15) == 0 && (out & 3) == 0, "bkRmsNormQuantQ8_1: null or misaligned pointer");
+  BK_ARG(layout == BK_Q8_BLOCKS || layout == BK_Q8_STAGED, "bkRmsNormQuantQ8_1: unknown layout %d", layout);
+  if (layout == BK_Q8_STAGED) BK_ARG(B <= 8 && (out & 15) == 0, "bkRmsNormQuantQ8_1: a staged image holds at most 8 rows and is 16-byte aligned");
+  const dim3 grid = w ? dim3(1, B) : dim3((K / 8 + 255) / 256, B);
+  auto* px = bk_ptr<uint16_t>(x);
+  auto* pw = bk_ptr<uint16_t>(w);
+  auto* po = bk_ptr<uint8_t>(out);
   if (w) {
-    BK_CUDA(bk_launch_pdl(quant_rows_kernel<true>, dim3(1, B), dim3(256), 0, bk_ptr<uint16_t>(x), bk_ptr<uint16_t>(w), K,
-                          eps, bk_ptr<uint8_t>(out_blocks)));
+    if (layout == BK_Q8_STAGED) BK_CUDA(bk_launch_pdl(quant_rows_kernel<true, true>, grid, dim3(256), 0, px, pw, K, eps, po));
+    else BK_CUDA(bk_launch_pdl(quant_rows_kernel<true, false>, grid, dim3(256), 0, px, pw, K, eps, po));
   } else {
-    BK_CUDA(bk_launch_pdl(quant_rows_kernel<false>, dim3((K / 8 + 255) / 256, B), dim3(256), 0, bk_ptr<uint16_t>(x),
-                          bk_ptr<uint16_t>(w), K, eps, bk_ptr<uint8_t>(out_blocks)));
+    if (layout == BK_Q8_STAGED) BK_CUDA(bk_launch_pdl(quant_rows_kernel<false, true>, grid, dim3(256), 0, px, pw, K, eps, po));
+    else BK_CUDA(bk_launch_pdl(quant_rows_kernel<false, false>, grid, dim3(256), 0, px, pw, K, eps, po));
   }
   BK_CHECK_LAUNCH();
   return BK_OK;
 }
+
+uint64_t bkStagedBytes(int32_t K, int32_t B) { return (K > 0 && B > 0) ? (uint64_t)bk_staged_bytes(K, B) : 0; }
 
 int32_t bkSwiglu(uint64_t g_f32, uint64_t u_f32, int32_t n, uint64_t out_bf16) {
   BK_REQUIRE_INIT();
@@ -578,6 +591,9 @@ int32_t bkGdnStep(const bkGdnArgs* args) {
   p.o_raw = bk_ptr<float>(a.o_raw);
   p.conv_out = bk_ptr<uint16_t>(a.conv_out);
   p.out_q8 = bk_ptr<uint8_t>(a.out_q8);
+  p.out_q8_staged = a.out_q8_layout == BK_Q8_STAGED;
+  BK_ARG(a.out_q8_layout == BK_Q8_BLOCKS || (a.out_q8_layout == BK_Q8_STAGED && a.B <= 8 && (a.Hv * 128) % 256 == 0),
+         "bkGdnStep: out_q8_layout %d (a staged image needs B <= 8 and Hv*128 a multiple of 256)", a.out_q8_layout);
   p.B = a.B;
   p.Hk = a.Hk;
   p.Hv = a.Hv;

@@ -57,9 +57,27 @@ def rmsnorm(x: int, w: int, H: int, B: int, y: int, eps: float = 1e-6) -> None:
     _check(cu().bkRmsNorm(x, w, H, B, eps, y))
 
 
-def rmsnorm_quant_q8_1(x: int, w: int, K: int, B: int, out: int, eps: float = 1e-6) -> None:
-    """RMSNorm (w != 0) and Q8_1 quantisation of bf16 rows in one launch; w = 0 quantises the rows as they are."""
-    _check(cu().bkRmsNormQuantQ8_1(x, w, K, B, eps, out))
+def rmsnorm_quant_q8_1(x: int, w: int, K: int, B: int, out: int, eps: float = 1e-6, layout: int = R.BK_Q8_BLOCKS) -> None:
+    """RMSNorm (w != 0) and Q8_1 quantisation of bf16 rows in one launch; w = 0 quantises the rows as they are.
+    layout BK_Q8_STAGED writes the staged image of the batch-3..8 GEMV (staged_bytes(K, B) bytes)."""
+    _check(cu().bkRmsNormQuantQ8_1(x, w, K, B, eps, out, layout))
+
+
+def staged_bytes(K: int, B: int) -> int:
+    return int(R.load_library().bkStagedBytes(K, B))
+
+
+def staged_to_blocks(img: np.ndarray, K: int, B: int):
+    """Unpack a staged image (uint8) into (quants int8 [B][K], d8 f32 [B][K/32] with the 1/16 of odd blocks undone,
+    s8 f32 [B][K/32]) -- the three things the GEMV reads from Q8_1 blocks."""
+    rw = K // 4 + 8
+    words = img[:B * rw * 4].view(np.uint32).reshape(B, rw)[:, :K // 4].reshape(B, K // 32, 8)
+    pos = np.array([(w & 3) * 2 + (w >> 2) for w in range(8)])
+    q = np.ascontiguousarray(words[:, :, pos]).view(np.int8).reshape(B, K)
+    sc = img[B * rw * 4:B * rw * 4 + (K // 64) * 8 * 16].view(np.float32).reshape(K // 64, 8, 4)[:, :B]
+    d8 = np.stack([sc[:, :, 0], sc[:, :, 1] * np.float32(16.0)], axis=-1)    # [u][b][2]
+    s8 = np.stack([sc[:, :, 2], sc[:, :, 3]], axis=-1)
+    return q, d8.transpose(1, 0, 2).reshape(B, K // 32), s8.transpose(1, 0, 2).reshape(B, K // 32)
 
 
 def swiglu(g: int, u: int, n: int, out: int) -> None:

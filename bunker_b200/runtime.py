@@ -27,7 +27,8 @@ BK_ERR_TIMEOUT = 10003
 BK_ERR_UNSUPPORTED = 10004
 BK_ERR_COMM = 10005
 
-BK_PRO_Q8, BK_PRO_BF16, BK_PRO_RMSNORM = 0, 1, 2
+BK_PRO_Q8, BK_PRO_BF16, BK_PRO_RMSNORM, BK_PRO_STAGED = 0, 1, 2, 3
+BK_Q8_BLOCKS, BK_Q8_STAGED = 0, 1
 BK_EPI_F32, BK_EPI_BF16, BK_EPI_ADD_BF16, BK_EPI_SWIGLU = 0, 1, 2, 3
 
 BK_OP_EMBED, BK_OP_RMSNORM, BK_OP_GEMV, BK_OP_SWIGLU, BK_OP_CONV1D, BK_OP_ARGMAX, BK_OP_QUANT_Q8_1 = range(1, 8)
@@ -53,7 +54,7 @@ class bkGemvArgs(C.Structure):
 class bkGdnArgs(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in ("qkv", "z", "a", "b", "conv_w", "conv_state_in", "conv_state_new", "A_log",
                                            "dt_bias", "norm_w", "S_in", "S_new", "out", "o_raw", "conv_out")] + \
-               [(n, C.c_int32) for n in ("B", "Hk", "Hv", "apply_conv", "state_is_settled", "reserved")] + \
+               [(n, C.c_int32) for n in ("B", "Hk", "Hv", "apply_conv", "state_is_settled", "out_q8_layout")] + \
                [("out_q8", C.c_uint64)]
 
 
@@ -62,7 +63,7 @@ class bkAttnArgs(C.Structure):
                                            "v_cache", "pos", "out", "scratch")] + \
                [(n, C.c_int32) for n in ("B", "Hq", "Hkv", "HD", "rot_half", "max_len", "split_len", "max_pos")] + \
                [("scale", C.c_float), ("fused_norm_rope", C.c_int32), ("gate", C.c_uint64),
-                ("cache_is_settled", C.c_int32), ("reserved", C.c_int32), ("out_q8", C.c_uint64)]
+                ("cache_is_settled", C.c_int32), ("out_q8_layout", C.c_int32), ("out_q8", C.c_uint64)]
 
 
 class bkModelConfig(C.Structure):
@@ -109,7 +110,8 @@ SIGNATURES = {
     "bkQuantQ8_1Bf16": (_I32, [_U64, _I32, _I32, _U64]),
     "bkEmbedQ4K": (_I32, [_U64, _I32, _U64, _I32, _U64]),
     "bkRmsNorm": (_I32, [_U64, _U64, _I32, _I32, _F32, _U64]),
-    "bkRmsNormQuantQ8_1": (_I32, [_U64, _U64, _I32, _I32, _F32, _U64]),
+    "bkRmsNormQuantQ8_1": (_I32, [_U64, _U64, _I32, _I32, _F32, _U64, _I32]),
+    "bkStagedBytes": (_U64, [_I32, _I32]),
     "bkSwiglu": (_I32, [_U64, _U64, _I32, _U64]),
     "bkConv1dStep": (_I32, [_U64, _U64, _U64, _I32, _I32, _U64, _U64]),
     "bkGdnStep": (_I32, [C.POINTER(bkGdnArgs)]),

@@ -91,6 +91,7 @@ BK_API int32_t bkLaunchCount(uint64_t* out_count);
 /* prologues: how the activation reaches the kernel */
 #define BK_PRO_Q8 0       /* x = Q8_1 blocks [B][K/32][36] (bench/bench.ts:7 layout) */
 #define BK_PRO_BF16 1     /* x = bf16 [B][K]; quantised to Q8_1 inside the kernel */
+#define BK_PRO_STAGED 3   /* x = staged image (BK_Q8_STAGED) for this K and B; batch 3..8 only */
 #define BK_PRO_RMSNORM 2  /* x = bf16 [B][K]; RMSNorm(x, norm_w, eps) -> bf16 -> Q8_1 inside the kernel
                              (buildRMS, prototypes/decode.ts:201-216, fused) */
 /* epilogues */
@@ -98,6 +99,16 @@ BK_API int32_t bkLaunchCount(uint64_t* out_count);
 #define BK_EPI_BF16 1     /* out bf16(acc)                      (decode.ts cast) */
 #define BK_EPI_ADD_BF16 2 /* out bf16(acc + f32(residual))      (decode.ts:152-154 add) */
 #define BK_EPI_SWIGLU 3   /* out bf16((g*sigmoid(g))*u), g from W, u from W2 (decode.ts:117-119) */
+
+/* Layouts of a quantised activation handed from one op to the next.
+ * BK_Q8_BLOCKS: the reference's Q8_1 blocks [B][K/32][36] (bench/bench.ts:7), read with BK_PRO_Q8.
+ * BK_Q8_STAGED: the image the batch-3..8 GEMV keeps in shared memory (bkStagedBytes(K, B) bytes, 16-byte aligned):
+ *   words [B][K/4+8] with the eight words of each block in the order 0,4,1,5,2,6,3,7, then float4 [K/64][8] =
+ *   {d8 of block 2u, d8 of block 2u+1 / 16, s8 of 2u, s8 of 2u+1} per 64-value unit u and batch column.  The GEMV
+ *   prologue is then a single bulk copy (BK_PRO_STAGED).  No counterpart in the reference. */
+#define BK_Q8_BLOCKS 0
+#define BK_Q8_STAGED 1
+BK_API uint64_t bkStagedBytes(int32_t K, int32_t B);
 
 typedef struct bkGemvSeg {
   uint64_t W;        /* Q4_K rows [n_rows][K/256][144] */
@@ -142,9 +153,9 @@ BK_API int32_t bkEmbedQ4K(uint64_t table, int32_t H, uint64_t ids, int32_t B, ui
 /* buildRMS (prototypes/decode.ts:201-216): y = bf16((x*rstd)*(1+w)) */
 BK_API int32_t bkRmsNorm(uint64_t x, uint64_t w, int32_t H, int32_t B, float eps, uint64_t y);
 /* buildRMS followed by packQ8_1 (prototypes/decode.ts:201-216, bench/bench.ts:53-72) in one launch: bf16 rows
- * x [B][K] -> Q8_1 blocks [B][K/32][36] of bf16((x*rstd)*(1+w)); w = 0 skips the norm (plain bf16 -> Q8_1).
- * The blocks are what bkGemvQ4K reads with BK_PRO_Q8; used between ops at batch >= 3. */
-BK_API int32_t bkRmsNormQuantQ8_1(uint64_t x, uint64_t w, int32_t K, int32_t B, float eps, uint64_t out_blocks);
+ * x [B][K] -> Q8_1 of bf16((x*rstd)*(1+w)) in `layout` (BK_Q8_BLOCKS or BK_Q8_STAGED); w = 0 skips the norm
+ * (plain bf16 -> Q8_1).  Used between ops at batch >= 3. */
+BK_API int32_t bkRmsNormQuantQ8_1(uint64_t x, uint64_t w, int32_t K, int32_t B, float eps, uint64_t out, int32_t layout);
 /* emitSwiGLU (src/fusion.ts:324-330): out bf16 [n] from f32 g,u */
 BK_API int32_t bkSwiglu(uint64_t g_f32, uint64_t u_f32, int32_t n, uint64_t out_bf16);
 /* emitConv1d (src/emitters.ts:48-72): state [B][3][C] bf16 oldest first, w [C][4] bf16 */
@@ -166,9 +177,8 @@ typedef struct bkGdnArgs {
   int32_t state_is_settled;      /* 1: S_in, conv_state_in and the weights were NOT written by the launch that
                                     immediately precedes this one on the stream, so the kernel may read them while that
                                     launch is still running (programmatic dependent launch).  0: read everything after it. */
-  int32_t reserved;
-  uint64_t out_q8;               /* optional (0 to skip): the same output as Q8_1 blocks [B][Hv*4][36], the form the
-                                    output projection reads with BK_PRO_Q8 */
+  int32_t out_q8_layout;         /* BK_Q8_BLOCKS or BK_Q8_STAGED */
+  uint64_t out_q8;               /* optional (0 to skip): the same output quantised for the output projection */
 } bkGdnArgs;
 BK_API int32_t bkGdnStep(const bkGdnArgs* args);
 
@@ -201,8 +211,8 @@ typedef struct bkAttnArgs {
   uint64_t gate;     /* only for fused_norm_rope=0: bf16 [B][Hq*HD] */
   int32_t cache_is_settled; /* 1: pos[] and the cache rows below pos[b] were NOT written by the launch that immediately
                                precedes this one on the stream, so they may be read while that launch is still running */
-  int32_t reserved;
-  uint64_t out_q8;   /* optional (0 to skip): the same output as Q8_1 blocks [B][Hq*HD/32][36] */
+  int32_t out_q8_layout; /* BK_Q8_BLOCKS or BK_Q8_STAGED */
+  uint64_t out_q8;   /* optional (0 to skip): the same output quantised for the output projection */
 } bkAttnArgs;
 BK_API int32_t bkAttnDecode(const bkAttnArgs* args);
 /* split length and warps per split the library uses for n rows */

@@ -151,6 +151,14 @@ def q8_1_dequant(xq: np.ndarray) -> np.ndarray:
     return (q * d).reshape(B, nb * 32)
 
 
+def q8_1_scales(xq: np.ndarray) -> np.ndarray:
+    """uint8 [B, nb, 36] -> the block scales f32 [B, nb] as the GEMV reads them (flush-denormal half decode)."""
+    xq = _c(xq, np.uint8)
+    B, nb, _ = xq.shape
+    dh = xq[:, :, 32].astype(np.uint16) | (xq[:, :, 33].astype(np.uint16) << 8)
+    return np.array([lib().orc_q8half_to_f32(int(v)) for v in dh.ravel()], np.float32).reshape(B, nb)
+
+
 def block_dots(wrow: np.ndarray, xq: np.ndarray, K: int):
     isum = np.empty(K // 32, np.int32)
     qsum = np.empty(K // 32, np.int32)

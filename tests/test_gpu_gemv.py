@@ -91,6 +91,28 @@ def test_gemv_batches_and_tails(bk, B, K):
     assert_same_bits(dy.download(np.float32, (B, N)), O.gemv_q4k_q8(W, N, K, xq), f"gemv B={B} K={K}")
 
 
+@pytest.mark.parametrize("B,K", [(3, 2048), (8, 2048), (5, 4096), (8, 6144), (8, 5120)])
+def test_gemv_staged_activation(bk, B, K):
+    """Batch 3..8: the activation arrives as the staged image written by the norm+quantise launch; SwiGLU and
+    plain segments; same bits as the oracle's RMSNorm -> Q8_1 -> GEMV."""
+    N = 300
+    rng = np.random.default_rng(90 + B + K)
+    Wg, Wu = synth.q4k_weights(rng, N, K), synth.q4k_weights(rng, N, K)
+    x, nw = synth.normal_bf16(rng, (B, K)), synth.normal_bf16(rng, (K,), 0.02)
+    xq = O.q8_1_quantize_bf16(O.rmsnorm(x, nw))
+    dx, dnw, dWg, dWu = dev(x), dev(nw), dev(Wg), dev(Wu)
+    img = R.DeviceBuffer.zeros(ops.staged_bytes(K, B))
+    ops.rmsnorm_quant_q8_1(dx.ptr, dnw.ptr, K, B, img.ptr, layout=R.BK_Q8_STAGED)
+    act, y = R.DeviceBuffer(B * N * 2), R.DeviceBuffer(B * N * 4)
+    ops.gemv(img.ptr, K, B, [ops.gemv_seg(dWg.ptr, N, act.ptr, R.BK_EPI_SWIGLU, W2=dWu.ptr)], prologue=R.BK_PRO_STAGED)
+    ops.gemv(img.ptr, K, B, [ops.gemv_seg(dWg.ptr, N, y.ptr, R.BK_EPI_F32)], prologue=R.BK_PRO_STAGED)
+    g, u = O.gemv_q4k_q8(Wg, N, K, xq), O.gemv_q4k_q8(Wu, N, K, xq)
+    assert_same_bits(y.download(np.float32, (B, N)), g, "f32 segment from a staged activation")
+    assert_same_bits(act.download(np.uint16, (B, N)), O.swiglu(g, u), "SwiGLU segment from a staged activation")
+    with pytest.raises(R.BunkerCudaError):   # batch 1-2 has no staged path
+        ops.gemv(img.ptr, K, 2, [ops.gemv_seg(dWg.ptr, N, y.ptr, R.BK_EPI_F32)], prologue=R.BK_PRO_STAGED)
+
+
 @pytest.mark.parametrize("B", [3, 8])
 def test_gemv_widest_k_batched(bk, B):
     """K = 17408 (FFN width of the 64-layer configuration) at batch >= 3: too wide for the tensor-core path's

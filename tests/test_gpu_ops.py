@@ -45,6 +45,20 @@ def test_rmsnorm_quant_q8_1(bk, K):
     assert_same_bits(dq.download(np.uint8, (B, K // 32, 36)), O.q8_1_quantize_bf16(O.rmsnorm(x, w)), "norm + Q8_1")
     ops.rmsnorm_quant_q8_1(dx.ptr, 0, K, B, dq.ptr)
     assert_same_bits(dq.download(np.uint8, (B, K // 32, 36)), O.q8_1_quantize_bf16(x), "plain Q8_1")
+    # the staged image carries the same quants, block scales (after their f16 round trip) and d8 * sum(q)
+    img = R.DeviceBuffer.zeros(ops.staged_bytes(K, B))
+    for w_ptr, ref in ((dw.ptr, O.rmsnorm(x, w)), (0, x)):
+        ops.rmsnorm_quant_q8_1(dx.ptr, w_ptr, K, B, img.ptr, layout=R.BK_Q8_STAGED)
+        _check_staged(img.download(np.uint8, (ops.staged_bytes(K, B),)), O.q8_1_quantize_bf16(ref), K, B)
+
+
+def _check_staged(img, blocks, K, B):
+    q, d8, s8 = ops.staged_to_blocks(img, K, B)
+    assert_same_bits(q.reshape(B, K // 32, 32), blocks[:, :, :32].view(np.int8), "staged quants")
+    want_d8 = O.q8_1_scales(blocks)
+    assert_same_bits(d8, want_d8, "staged block scales")
+    want_s8 = want_d8 * blocks[:, :, :32].view(np.int8).astype(np.int32).sum(-1).astype(np.float32)
+    assert_same_bits(s8, want_s8.astype(np.float32), "staged d8 * sum(q)")
 
 
 def test_swiglu(bk):
@@ -98,6 +112,13 @@ def test_gdn_step_config1(bk, B):
     assert_same_bits(out.download(np.uint16, (B, Hv * 128)), w_out, "gated out")
     assert_same_bits(out_q8.download(np.uint8, (B, Hv * 4, 36)), O.q8_1_quantize_bf16(w_out).reshape(B, Hv * 4, 36),
                      "gated out as Q8_1 blocks")
+    img = R.DeviceBuffer.zeros(ops.staged_bytes(Hv * 128, B))
+    d2 = dev(c["S"])
+    ops.gdn_step(out_q8=img.ptr, out_q8_layout=R.BK_Q8_STAGED, qkv=d["qkv"].ptr, z=d["z"].ptr, a=d["a"].ptr, b=d["b"].ptr,
+                 conv_w=d["conv_w"].ptr, conv_state_in=d["conv_state"].ptr, conv_state_new=cs_new.ptr,
+                 A_log=d["A_log"].ptr, dt_bias=d["dt_bias"].ptr, norm_w=d["norm_w"].ptr, S_in=d2.ptr, S_new=S_new.ptr,
+                 out=out.ptr, B=B, Hk=Hk, Hv=Hv, apply_conv=1)
+    _check_staged(img.download(np.uint8, (ops.staged_bytes(Hv * 128, B),)), O.q8_1_quantize_bf16(w_out), Hv * 128, B)
     # plain recurrence (prototypes/gdn_gated.ts:67-88) on head (0, 5), double math
     import math
     hv, hk = 5, 5 // (Hv // Hk)
@@ -172,6 +193,15 @@ def _run_attn(c, cos_t, sin_t, split_len=0):
     assert_same_bits(out_q8.download(np.uint8, (B, Hq * HD // 32, 36)),
                      O.q8_1_quantize_bf16(got).reshape(B, Hq * HD // 32, 36), "attention output as Q8_1 blocks")
     out_q8.free()
+    if B <= 8:   # same call again (the cache row is rewritten with the same values) with the staged layout
+        img = R.DeviceBuffer.zeros(ops.staged_bytes(Hq * HD, B))
+        ops.attn_decode(out_q8=img.ptr, out_q8_layout=R.BK_Q8_STAGED, qg=d["qg"].ptr, k=d["k"].ptr, v=d["v"].ptr,
+                        q_norm_w=d["q_norm_w"].ptr, k_norm_w=d["k_norm_w"].ptr, cos_t=dc.ptr, sin_t=ds.ptr,
+                        k_cache=d["k_cache"].ptr, v_cache=d["v_cache"].ptr, pos=d["pos"].ptr, out=out.ptr,
+                        scratch=scratch.ptr, B=B, Hq=Hq, Hkv=Hkv, HD=HD, rot_half=32, max_len=ml, split_len=split_len,
+                        max_pos=max_pos, scale=1.0 / 16.0, fused_norm_rope=1)
+        _check_staged(img.download(np.uint8, (ops.staged_bytes(Hq * HD, B),)), O.q8_1_quantize_bf16(got), Hq * HD, B)
+        img.free()
     Kg = d["k_cache"].download(np.uint16, c["k_cache"].shape)
     Vg = d["v_cache"].download(np.uint16, c["v_cache"].shape)
     for b in d.values():
