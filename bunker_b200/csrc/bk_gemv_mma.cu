@@ -199,36 +199,36 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
         T[v] = __fadd_rn(__fadd_rn(__fadd_rn(P[0][v], P[4][v]), __fadd_rn(P[2][v], P[6][v])),
                          __fadd_rn(__fadd_rn(P[1][v], P[5][v]), __fadd_rn(P[3][v], P[7][v])));
     }
-    __syncwarp();
-    float* pw = part + (size_t)(rd & 1) * (tpr * 4 * 128) + (size_t)(tq * 4 + tp) * 128;
-    pw[R * 8 + col0] = T[0];
-    pw[R * 8 + col1] = T[1];
-    pw[(R + 8) * 8 + col0] = T[2];
-    pw[(R + 8) * 8 + col1] = T[3];
-    __syncthreads();   // all partial totals of the round are in shared memory; its weight slots are free
-    // ring refill: the round barrier above released the slot
-    if (tp == 0) {
-      const int t2 = t + n_slots;
-      if (t < n_tiles && t2 < n_tiles) request_tile(t2, t % n_slots);
-    }
-    // epilogue: thread -> (tile position, row, column)
-    {
-      const int eq = tid >> 7, er = (tid >> 3) & 15, ec = tid & 7;
-      const int et = rd * tpr + eq;
-      const float* pr = part + (size_t)(rd & 1) * (tpr * 4 * 128) + (size_t)(eq * 4) * 128 + er * 8 + ec;
-      if (et < n_tiles && ec < B) {
-        const int nr = min(kTileRows, n_rows_cta - et * kTileRows);
+    // The four p-warps of a tile position form a group with its own named barrier: groups drift apart freely,
+    // so one group's barrier, epilogue and refill overlap the other groups' dot products.
+    if (t < n_tiles) {   // uniform within the group
+      float* pw = part + (size_t)(rd & 1) * (tpr * 4 * 128) + (size_t)(tq * 4 + tp) * 128;
+      pw[R * 8 + col0] = T[0];
+      pw[R * 8 + col1] = T[1];
+      pw[(R + 8) * 8 + col0] = T[2];
+      pw[(R + 8) * 8 + col1] = T[3];
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + tq) : "memory");   // the tile's partial totals are in shared memory; its slot is free
+      if (tp == 0) {
+        const int t2 = t + n_slots;
+        if (t2 < n_tiles) request_tile(t2, t % n_slots);
+      }
+      // epilogue: the group's 128 threads -> (row, column) of the tile.  The other half of `part` is written in the
+      // next round only after every warp of the group has passed that round's barrier, i.e. finished reading here.
+      const int g = tid & 127, er = g >> 3, ec = g & 7;
+      const float* pr = part + (size_t)(rd & 1) * (tpr * 4 * 128) + (size_t)(tq * 4) * 128 + er * 8 + ec;
+      if (ec < B) {
+        const int nr = min(kTileRows, n_rows_cta - t * kTileRows);
         const float y = __fadd_rn(__fadd_rn(pr[0], pr[2 * 128]), __fadd_rn(pr[1 * 128], pr[3 * 128]));
         if (swiglu) {
           if (er < 8 && 2 * er < nr) {
             const float* pu = pr + 8 * 8;   // the up row of the same output
             const float yup = __fadd_rn(__fadd_rn(pu[0], pu[2 * 128]), __fadd_rn(pu[1 * 128], pu[3 * 128]));
-            const VRow vr = decode_vrow(p, c0 + et * kTileRows + 2 * er);
+            const VRow vr = decode_vrow(p, c0 + t * kTileRows + 2 * er);
             const SegDev& sg = p.segs[vr.si];
             store_epilogue(sg, (size_t)ec * sg.ld_out + sg.col_off + vr.n, y, yup);
           }
         } else if (er < nr) {
-          const VRow vr = decode_vrow(p, c0 + et * kTileRows + er);
+          const VRow vr = decode_vrow(p, c0 + t * kTileRows + er);
           const SegDev& sg = p.segs[vr.si];
           store_epilogue(sg, (size_t)ec * sg.ld_out + sg.col_off + vr.n, y, 0.0f);
         }

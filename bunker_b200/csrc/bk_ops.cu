@@ -215,8 +215,10 @@ struct GdnParams {
   unsigned long long* trace;
 };
 
-// Launched with 576 threads: the two extra warps only keep a second CTA of this grid off the SM (register file).
-__global__ void __launch_bounds__(576) gdn_step_kernel(const GdnParams p) {
+// Two builds of this body.  gdn_step_kernel: launched with 576 threads when the grid has at most one CTA per SM; the
+// two extra warps only keep a second CTA of this grid off the SM (register file), so no SM finishes last with two.
+// gdn_step_kernel_x2: 64 registers, two CTAs per SM, for grids larger than the SM count (batch 8: 256 CTAs, one wave).
+__device__ __forceinline__ void gdn_step_body(const GdnParams& p) {
   constexpr int D = 128;
   __shared__ float s_q[D], s_k[D], s_v[D], s_o[D];
   __shared__ float s_part[4][D];
@@ -366,6 +368,9 @@ __global__ void __launch_bounds__(576) gdn_step_kernel(const GdnParams p) {
   }
   bk_stamp(p.trace, 5);
 }
+
+__global__ void __launch_bounds__(576) gdn_step_kernel(const GdnParams p) { gdn_step_body(p); }
+__global__ void __launch_bounds__(512, 2) gdn_step_kernel_x2(const GdnParams p) { gdn_step_body(p); }
 
 // ---- q/k head RMSNorm + partial rotary, one warp per (batch, head) ----------------
 // (src/emitters.ts:123-183).  Lane l owns the HD/32 contiguous dims of the head.
@@ -600,7 +605,8 @@ int32_t bkGdnStep(const bkGdnArgs* args) {
   p.apply_conv = a.apply_conv;
   p.early = a.state_is_settled;
   p.trace = bk_trace_slot();
-  BK_CUDA(bk_launch_pdl(gdn_step_kernel, dim3(a.Hv, a.B), dim3(576), 0, p));
+  if (a.Hv * a.B > bk_ctx().sm_count) BK_CUDA(bk_launch_pdl(gdn_step_kernel_x2, dim3(a.Hv, a.B), dim3(512), 0, p));
+  else BK_CUDA(bk_launch_pdl(gdn_step_kernel, dim3(a.Hv, a.B), dim3(576), 0, p));
   BK_CHECK_LAUNCH();
   return BK_OK;
 }
