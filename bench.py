@@ -299,7 +299,7 @@ def run_ours(args):
         "e2e": {"value": K * B / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 4 * B,
                 "d2h_bytes_per_step": 8 * B, "ms_per_step": e2e_ms / K, "same_tokens_as_resident_leg": same_stream},
         "gpu_launches": int(launches),
-        "roofline": {"bound": "hbm", "kernel": f"gemv_q4k_kernel<{B},8>" if B <= 2 else "gemv_q4k_mma_kernel", "achieved": achieved,
+        "roofline": {"bound": "hbm", "kernel": f"gemv_q4k_kernel<{B},8>" if B <= 1 else "gemv_q4k_mma_kernel", "achieved": achieved,
                      "peak": hbm_peak / world, "unit": "GB/s", "frac": achieved / (hbm_peak / world),
                      "traffic": NCU_GEMV_LMHEAD_TRAFFIC if (world == 1 and B == 1) else None, "peak_source": peak_src,
                      "launch": f"lm_head shard [{Vl} x {H}] Q4_K, RMSNorm+Q8_1 prologue, batch {B}",

@@ -187,7 +187,7 @@ BK_DEVINL void bk_q8_1_store(uint8_t* blk, const float (&y)[PER], int idx_in_blo
   }
 }
 
-// ---- staged activation image of the tensor-core GEMV (batch 3..8) ---------------------
+// ---- staged activation image of the tensor-core GEMV (batch 2..8) ---------------------
 // The exact bytes that kernel keeps in shared memory, so that its prologue is one bulk copy:
 //   words  [B][K/4 + 8]   Q8_1 quants, the eight words of a block in the order 0,4,1,5,2,6,3,7
 //   float4 [K/64][8]      per 64-value unit u and column b: {d8 of block 2u, d8 of block 2u+1 / 16,

@@ -87,7 +87,7 @@ __device__ __forceinline__ WRegs decode_unit(const RowRegs& r, int p) {
 #pragma unroll
   for (int k = 0; k < 8; k++) {
     w.lo[k] = qw[k] & 0x0f0f0f0fu;
-    w.hi[k] = (qw[k] >> 4) & 0x0f0f0f0fu;
+    w.hi[k] = qw[k] & 0xf0f0f0f0u;   // high nibbles stay in place: unsigned bytes 16*q, the staged d8 of odd blocks carries 1/16
   }
   return w;
 }
@@ -110,6 +110,8 @@ __device__ __forceinline__ float unit_val(const WRegs& w, const XRegs& x) {
   i1 = bk_dp4a(w.hi[5], x.x3.y, i1);
   i1 = bk_dp4a(w.hi[6], x.x3.z, i1);
   i1 = bk_dp4a(w.hi[7], x.x3.w, i1);
+  // i1 = 16 * (sub-block sum): sc1*i1 < 2^26 is a multiple of 16, exact in f32, and x.d8.y = d8/16 (exact), so the
+  // fma rounds the same real number as fma(d8, f32(sc1*sum), accd)
   float accd = __fmul_rn(x.d8.x, (float)(w.sc0 * i0));
   accd = fmaf(x.d8.y, (float)(w.sc1 * i1), accd);
   float accm = __fmul_rn(x.s8.x, w.fm0);
@@ -461,8 +463,8 @@ int32_t bk_gemv_launch(const bkGemvArgs& a) {
   BK_ARG(a.n_segs >= 1 && a.n_segs <= 4, "bkGemvQ4K: n_segs=%d outside 1..4", a.n_segs);
   BK_ARG(a.prologue >= BK_PRO_Q8 && a.prologue <= BK_PRO_STAGED, "bkGemvQ4K: unknown prologue %d", a.prologue);
   if (a.prologue == BK_PRO_STAGED)
-    BK_ARG(a.B >= 3 && bk_gemv_mma_fits(a.K, a.B),
-           "bkGemvQ4K: a staged activation needs batch 3..8 and a K that fits the tensor-core path (K=%d B=%d)", a.K, a.B);
+    BK_ARG(a.B >= 2 && bk_gemv_mma_fits(a.K, a.B),
+           "bkGemvQ4K: a staged activation needs batch 2..8 and a K that fits the tensor-core path (K=%d B=%d)", a.K, a.B);
   BK_ARG(a.x != 0 && (a.x & 15) == 0, "bkGemvQ4K: x must be a non-null 16-byte aligned device pointer");
   if (a.prologue == BK_PRO_RMSNORM)
     BK_ARG(a.norm_w != 0 && (a.norm_w & 15) == 0, "bkGemvQ4K: norm_w must be non-null and 16-byte aligned");
@@ -530,7 +532,7 @@ int32_t bk_gemv_launch(const bkGemvArgs& a) {
   p.cta_trace = nullptr;
   if (c.cta_trace && c.cta_trace_seen++ == c.cta_trace_launch) p.cta_trace = c.cta_trace;
 
-  if (a.B >= 3) return bk_gemv_mma_launch(&p, a.K, a.B, vrows, has_swiglu);
+  if (a.B >= 2 && bk_gemv_mma_fits(a.K, a.B)) return bk_gemv_mma_launch(&p, a.K, a.B, vrows, has_swiglu);
 
   // ---- launch shape ----
   const size_t rowb = (size_t)(a.K / 256) * 144;
@@ -599,13 +601,7 @@ int32_t bk_gemv_launch(const bkGemvArgs& a) {
   }
   switch (a.B) {
     case 1: return launch_gemv<1, gemv_gmax(1)>(p, grid, threads, smem);
-    case 2: return launch_gemv<2, gemv_gmax(2)>(p, grid, threads, smem);
-    case 3: return launch_gemv<3, gemv_gmax(3)>(p, grid, threads, smem);
-    case 4: return launch_gemv<4, gemv_gmax(4)>(p, grid, threads, smem);
-    case 5: return launch_gemv<5, gemv_gmax(5)>(p, grid, threads, smem);
-    case 6: return launch_gemv<6, gemv_gmax(6)>(p, grid, threads, smem);
-    case 7: return launch_gemv<7, gemv_gmax(7)>(p, grid, threads, smem);
-    default: return launch_gemv<8, gemv_gmax(8)>(p, grid, threads, smem);
+    default: return launch_gemv<2, gemv_gmax(2)>(p, grid, threads, smem);   // batch 2 only when K is too wide for the tensor-core path
   }
 }
 

@@ -1,4 +1,4 @@
-// bk_gemv_mma.cu -- Q4_K x Q8_1 GEMV for batch 3..8 on the int8 tensor-core path (mma.sync m16n8k32).
+// bk_gemv_mma.cu -- Q4_K x Q8_1 GEMV for batch 2..8 on the int8 tensor-core path (mma.sync m16n8k32).
 //
 // At these batch sizes 16 dp4a per 64 weights per batch column no longer fit under the HBM stream; one
 // m16n8k32 computes a 32-value sub-block dot for 16 rows and all 8 batch columns, with exact int32 sums,

@@ -49,7 +49,7 @@ struct GemvParams {
 
 // ---- staged activation layouts ---------------------------------------------------
 // Plain (dp4a kernel): quants of block blk at xs[b*x_row_words + (blk>>1)*x_unit_words + (blk&1)*8 + w], w = 0..7;
-// scales d8s[b*x_scale_ld + blk], s8s likewise.
+// scales d8s[b*x_scale_ld + blk] (odd blocks divided by 16, like the MMA layout), s8s likewise (undivided).
 // MMA (TC = true): the eight words of a block are stored in the order 0,4,1,5,2,6,3,7 so that the two words a lane
 // feeds to one mma (w = j and j+4) are one 64-bit load; the scales of unit u = blk>>1 and column b form one float4
 // {d8 of block 2u, d8 of block 2u+1 divided by 16, s8 of 2u, s8 of 2u+1} at sc4[u*8 + b] (s8s is unused).
@@ -68,7 +68,7 @@ __device__ __forceinline__ void store_block_scales(const GemvParams& p, float* d
     e[0] = (blk & 1) ? __fmul_rn(d8, 0.0625f) : d8;
     e[2] = s8;
   } else {
-    d8s[b * p.x_scale_ld + blk] = d8;
+    d8s[b * p.x_scale_ld + blk] = (blk & 1) ? __fmul_rn(d8, 0.0625f) : d8;   // see unit_val() of the dp4a kernel
     s8s[b * p.x_scale_ld + blk] = s8;
   }
 }
@@ -218,7 +218,7 @@ __device__ void prologue_bf16(const GemvParams& p, const int B, uint32_t* xs, fl
   }
 }
 
-// The same prologue for several batch rows at once (batch 3..8 path).  Row b's sum of squares still uses the
+// The same prologue for several batch rows at once (batch 2..8 path).  Row b's sum of squares still uses the
 // canonical 256-thread order, but each aligned block of 256 threads takes a different row, the per-row warp sums
 // land in red[b*8 + w], and one barrier serves all rows; the quantisation then runs over the flattened
 // (row, chunk) items so that every thread has several independent items in flight.

@@ -135,8 +135,8 @@ int32_t enqueue_step(Model& m, int parity) {
   int cur = 0;
   // GDN / attention also emit their output as Q8_1 blocks.  Reading those spares the output projection its own
   // quantisation, which pays once that prologue covers several batch rows; at batch 1-2 the bf16 row is as fast.
-  const bool q8_handoff = B >= 3;
-  // Input of a projection: fused RMSNorm/quantise prologue at batch 1-2; at batch >= 3 one small launch
+  const bool q8_handoff = B >= 2;
+  // Input of a projection: fused RMSNorm/quantise prologue at batch 1; at batch >= 2 one small launch
   // normalises and quantises the rows once and every CTA of the projection just copies the blocks.
   auto set_input = [&](bkGemvArgs& g, uint64_t x, int K, uint64_t norm_w) -> int32_t {
     g.K = K; g.B = B; g.eps = c.eps;

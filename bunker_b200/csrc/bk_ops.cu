@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t* x, const u
 }
 
 // ---- (RMSNorm ->) Q8_1 rows, computed once for all consumers ------------------------
-// At batch >= 3 the projection kernels read their activation as ready Q8_1 blocks instead of each of the
+// At batch >= 2 the projection kernels read their activation as ready Q8_1 blocks instead of each of the
 // 148 CTAs normalising and quantising all batch rows again.  NORM: one CTA per batch row (the canonical
 // 256-thread sum of squares).  Plain: 256 chunks of 8 values per CTA.  Output blocks [B][K/32][36].
 // STAGED: the output is the staged image of the tensor-core GEMV instead of 36-byte blocks.

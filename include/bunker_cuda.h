@@ -91,7 +91,7 @@ BK_API int32_t bkLaunchCount(uint64_t* out_count);
 /* prologues: how the activation reaches the kernel */
 #define BK_PRO_Q8 0       /* x = Q8_1 blocks [B][K/32][36] (bench/bench.ts:7 layout) */
 #define BK_PRO_BF16 1     /* x = bf16 [B][K]; quantised to Q8_1 inside the kernel */
-#define BK_PRO_STAGED 3   /* x = staged image (BK_Q8_STAGED) for this K and B; batch 3..8 only */
+#define BK_PRO_STAGED 3   /* x = staged image (BK_Q8_STAGED) for this K and B; batch 2..8 only */
 #define BK_PRO_RMSNORM 2  /* x = bf16 [B][K]; RMSNorm(x, norm_w, eps) -> bf16 -> Q8_1 inside the kernel
                              (buildRMS, prototypes/decode.ts:201-216, fused) */
 /* epilogues */
@@ -102,7 +102,7 @@ BK_API int32_t bkLaunchCount(uint64_t* out_count);
 
 /* Layouts of a quantised activation handed from one op to the next.
  * BK_Q8_BLOCKS: the reference's Q8_1 blocks [B][K/32][36] (bench/bench.ts:7), read with BK_PRO_Q8.
- * BK_Q8_STAGED: the image the batch-3..8 GEMV keeps in shared memory (bkStagedBytes(K, B) bytes, 16-byte aligned):
+ * BK_Q8_STAGED: the image the batch-2..8 GEMV keeps in shared memory (bkStagedBytes(K, B) bytes, 16-byte aligned):
  *   words [B][K/4+8] with the eight words of each block in the order 0,4,1,5,2,6,3,7, then float4 [K/64][8] =
  *   {d8 of block 2u, d8 of block 2u+1 / 16, s8 of 2u, s8 of 2u+1} per 64-value unit u and batch column.  The GEMV
  *   prologue is then a single bulk copy (BK_PRO_STAGED).  No counterpart in the reference. */
@@ -154,7 +154,7 @@ BK_API int32_t bkEmbedQ4K(uint64_t table, int32_t H, uint64_t ids, int32_t B, ui
 BK_API int32_t bkRmsNorm(uint64_t x, uint64_t w, int32_t H, int32_t B, float eps, uint64_t y);
 /* buildRMS followed by packQ8_1 (prototypes/decode.ts:201-216, bench/bench.ts:53-72) in one launch: bf16 rows
  * x [B][K] -> Q8_1 of bf16((x*rstd)*(1+w)) in `layout` (BK_Q8_BLOCKS or BK_Q8_STAGED); w = 0 skips the norm
- * (plain bf16 -> Q8_1).  Used between ops at batch >= 3. */
+ * (plain bf16 -> Q8_1).  Used between ops at batch >= 2. */
 BK_API int32_t bkRmsNormQuantQ8_1(uint64_t x, uint64_t w, int32_t K, int32_t B, float eps, uint64_t out, int32_t layout);
 /* emitSwiGLU (src/fusion.ts:324-330): out bf16 [n] from f32 g,u */
 BK_API int32_t bkSwiglu(uint64_t g_f32, uint64_t u_f32, int32_t n, uint64_t out_bf16);
@@ -280,7 +280,7 @@ BK_API int32_t bkDecodeRun(uint64_t model, int32_t n_steps);
 /* One eagerly launched step with a CUDA-event pair around every op (the BUNKER_GPU_PROF=1 profiler of
  * src/ttir.ts:352-417).  ms_out/count_out[n_classes >= 11]: 0 embed, 1 projection GEMV (qkv|z|a|b, q|k|v),
  * 2 conv1d+GDN, 3 attention (2 kernels per call), 4 out/o_proj GEMV, 5 gate|up GEMV, 6 down GEMV, 7 lm_head GEMV, 8 argmax,
- * 9 tensor-parallel exchanges, 10 stand-alone norm+quantise launches (batch >= 3 only). */
+ * 9 tensor-parallel exchanges, 10 stand-alone norm+quantise launches (batch >= 2 only). */
 BK_API int32_t bkDecodeStepProfiled(uint64_t model, float* ms_out, int32_t* count_out, int32_t n_classes);
 /* Tokens produced by steps [first_step, first_step+n_steps): out[n_steps][B] host ints. */
 BK_API int32_t bkModelTokens(uint64_t model, int32_t first_step, int32_t n_steps, int32_t* out);

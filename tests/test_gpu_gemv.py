@@ -91,7 +91,7 @@ def test_gemv_batches_and_tails(bk, B, K):
     assert_same_bits(dy.download(np.float32, (B, N)), O.gemv_q4k_q8(W, N, K, xq), f"gemv B={B} K={K}")
 
 
-@pytest.mark.parametrize("B,K", [(3, 2048), (8, 2048), (5, 4096), (8, 6144), (8, 5120)])
+@pytest.mark.parametrize("B,K", [(2, 2048), (3, 2048), (8, 2048), (5, 4096), (8, 6144), (8, 5120)])
 def test_gemv_staged_activation(bk, B, K):
     """Batch 3..8: the activation arrives as the staged image written by the norm+quantise launch; SwiGLU and
     plain segments; same bits as the oracle's RMSNorm -> Q8_1 -> GEMV."""
@@ -109,8 +109,8 @@ def test_gemv_staged_activation(bk, B, K):
     g, u = O.gemv_q4k_q8(Wg, N, K, xq), O.gemv_q4k_q8(Wu, N, K, xq)
     assert_same_bits(y.download(np.float32, (B, N)), g, "f32 segment from a staged activation")
     assert_same_bits(act.download(np.uint16, (B, N)), O.swiglu(g, u), "SwiGLU segment from a staged activation")
-    with pytest.raises(R.BunkerCudaError):   # batch 1-2 has no staged path
-        ops.gemv(img.ptr, K, 2, [ops.gemv_seg(dWg.ptr, N, y.ptr, R.BK_EPI_F32)], prologue=R.BK_PRO_STAGED)
+    with pytest.raises(R.BunkerCudaError):   # batch 1 has no staged path
+        ops.gemv(img.ptr, K, 1, [ops.gemv_seg(dWg.ptr, N, y.ptr, R.BK_EPI_F32)], prologue=R.BK_PRO_STAGED)
 
 
 @pytest.mark.parametrize("B", [3, 8])

@@ -35,7 +35,7 @@ def test_rmsnorm(bk, H):
 
 @pytest.mark.parametrize("K", [256, 2048, 5120, 17408])
 def test_rmsnorm_quant_q8_1(bk, K):
-    """The stand-alone (RMSNorm ->) Q8_1 launch used between ops at batch >= 3, with and without the norm."""
+    """The stand-alone (RMSNorm ->) Q8_1 launch used between ops at batch >= 2, with and without the norm."""
     B = 5
     rng = np.random.default_rng(60)
     x, w = synth.normal_bf16(rng, (B, K), 2.0), synth.normal_bf16(rng, (K,), 0.02)
