@@ -17,6 +17,14 @@
 //   Consecutive exchanges must use different slots: nobody can start exchange s+2 before it finished
 //   s+1, which needs every peer's flag s+1, which a peer only raises after it has finished reading s.
 // Every wait is bounded; on timeout the kernel sets the status word and returns.
+//
+// Fused exchange (the model's row-parallel GEMVs): a second region, push[2 slots][ranks][payload], receives the
+// partial sums of ALL ranks by remote stores from the producing GEMV itself; every CTA of that GEMV then adds 1
+// to arrivals[slot][its rank] on every rank (release, system scope).  The consumer -- the prologue of the next
+// projection, or the norm+quantise launch -- waits for the full CTA count from every rank and sums from local
+// memory: one NVLink store latency per exchange, no extra launch, no remote loads.  Slots alternate; a pushing
+// launch zeroes the local arrival counters of the other slot (its consumers finished before this launch passed
+// its dependency wait, and no peer can push into that slot again before it has seen this launch's arrivals).
 #include <string.h>
 
 #include "bk_common.cuh"
@@ -25,7 +33,8 @@
 struct BkComm {
   int rank = 0, nranks = 1;
   size_t payload_bytes = 0;       // per slot
-  uint8_t* local = nullptr;       // [3 slots][payload] | flags[8] u64 | counter u64
+  uint8_t* local = nullptr;       // [3 slots][payload] | flags[8] u64 | counter u64 | pad | push [2][nranks][payload] | arrivals [2][8] u32
+  size_t push_off = 0, cnt_off = 0;   // byte offsets of the push region and its arrival counters (same on every rank)
   uint8_t* peer[8] = {nullptr};   // mapped bases, peer[rank] == local
   bool imported = false;
 };
@@ -214,6 +223,31 @@ int32_t bk_comm_argmax_merge(uint64_t comm, int slot, int B, uint64_t local_val,
   return BK_OK;
 }
 
+int32_t bk_comm_push_desc(uint64_t comm, int slot, BkPush* out) {
+  BkComm* c = as_comm(comm);
+  BK_ARG(c && c->imported && out && (slot == 0 || slot == 1), "push descriptor: bad communicator or slot");
+  memset(out, 0, sizeof(*out));
+  for (int r = 0; r < c->nranks; r++) {
+    out->dst[r] = reinterpret_cast<float*>(c->peer[r] + c->push_off + ((size_t)slot * c->nranks + c->rank) * c->payload_bytes);
+    out->cnt[r] = reinterpret_cast<unsigned int*>(c->peer[r] + c->cnt_off) + slot * kMaxRanks + c->rank;
+  }
+  out->reset = reinterpret_cast<unsigned int*>(c->local + c->cnt_off) + (1 - slot) * kMaxRanks;
+  out->reset_n = c->nranks;
+  out->n = c->nranks;
+  return BK_OK;
+}
+
+int32_t bk_comm_reduce_desc(uint64_t comm, int slot, BkReduce* out) {
+  BkComm* c = as_comm(comm);
+  BK_ARG(c && c->imported && out && (slot == 0 || slot == 1), "reduce descriptor: bad communicator or slot");
+  memset(out, 0, sizeof(*out));
+  out->src = reinterpret_cast<const float*>(c->local + c->push_off + (size_t)slot * c->nranks * c->payload_bytes);
+  out->cnt = reinterpret_cast<const unsigned int*>(c->local + c->cnt_off) + slot * kMaxRanks;
+  out->stride = c->payload_bytes / 4;
+  out->n = c->nranks;
+  return BK_OK;
+}
+
 int32_t bk_comm_info(uint64_t comm, int* rank, int* nranks) {
   BkComm* c = as_comm(comm);
   if (!c) return bk_fail(BK_ERR_ARG, "null communicator");
@@ -236,7 +270,9 @@ int32_t bkCommCreate(int32_t rank, int32_t nranks, uint64_t payload_bytes, uint6
   c->rank = rank;
   c->nranks = nranks;
   c->payload_bytes = (payload_bytes + 255) / 256 * 256;
-  size_t total = kSlots * c->payload_bytes + (kMaxRanks + 1) * sizeof(unsigned long long);
+  c->push_off = (kSlots * c->payload_bytes + (kMaxRanks + 1) * sizeof(unsigned long long) + 255) / 256 * 256;
+  c->cnt_off = c->push_off + (size_t)2 * nranks * c->payload_bytes;
+  size_t total = c->cnt_off + 2 * kMaxRanks * sizeof(unsigned int);
   void* p = nullptr;
   cudaError_t e = cudaMalloc(&p, total);
   if (e != cudaSuccess) {

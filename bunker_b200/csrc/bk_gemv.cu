@@ -236,7 +236,7 @@ __global__ void __launch_bounds__(576, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kern
     }
   }
   uint4 wpre = make_uint4(0, 0, 0, 0);  // norm weights are weights: fetched before the wait as well
-  if (p.prologue == BK_PRO_RMSNORM && (int)threadIdx.x < K / 8)
+  if ((p.prologue == BK_PRO_RMSNORM || p.prologue == BK_PRO_REDUCE_RMSNORM) && (int)threadIdx.x < K / 8)
     wpre = __ldg(reinterpret_cast<const uint4*>(p.norm_w) + threadIdx.x);
   __syncwarp();
   bk_stamp(p.trace, 1);
@@ -244,12 +244,17 @@ __global__ void __launch_bounds__(576, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kern
   bk_stamp(p.trace, 2);
   if (ctr && threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); ctr[1] = t_; }
 
+  if (p.push.n && blockIdx.x == 0 && (int)threadIdx.x < p.push.reset_n) p.push.reset[threadIdx.x] = 0;
   if (p.prologue == BK_PRO_Q8)
     prologue_q8<false>(p, B, xs, d8s, s8s);
   else if (p.prologue == BK_PRO_BF16)
     prologue_bf16<false>(p, B, xs, d8s, s8s, red, wpre);
-  else
+  else if (p.prologue == BK_PRO_RMSNORM)
     prologue_bf16<true>(p, B, xs, d8s, s8s, red, wpre);
+  else {
+    bk_reduce_wait(p.red.cnt, p.red.n, p.red.expected, p.status);
+    prologue_bf16<true, true>(p, B, xs, d8s, s8s, red, wpre);
+  }
   __syncthreads();
   bk_stamp(p.trace, 3);
   bk_stamp_max(p.trace, 1);  // (reuses slot 1) latest prologue end over all CTAs
@@ -319,9 +324,10 @@ __global__ void __launch_bounds__(576, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kern
       for (int r = 0; r < 8; r++) pa[r] = r < GMAX ? acc[r < GMAX ? r : 0][b] : 0.0f;
       const float y = warp_sum8(pa);
       const float yup = __shfl_xor_sync(0xffffffffu, y, 4);  // the odd neighbour row (the "up" row of a SwiGLU pair)
-      if (mine && !(sg.epi == BK_EPI_SWIGLU && (ri & 1))) store_epilogue(sg, (size_t)b * sg.ld_out + sg.col_off + vr.n, y, yup);
+      if (mine && !(sg.epi == BK_EPI_SWIGLU && (ri & 1))) store_epilogue(p, sg, (size_t)b * sg.ld_out + sg.col_off + vr.n, y, yup);
     }
   }
+  if (p.push.n) bk_push_signal(p.push.cnt, p.push.n);
   bk_stamp(p.trace, 5);
   bk_stamp_max(p.trace, 6);  // latest exit over all warps of all CTAs
   if (ctr) bk_stamp_max(ctr, 3);
@@ -454,26 +460,37 @@ __global__ void quant_q8_1_kernel(const void* x, int K, int B, uint8_t* out) {
 
 // ---- host entry points ---------------------------------------------------------
 
-int32_t bk_gemv_mma_launch(void* params, int K, int B, int vrows, bool has_swiglu);  // bk_gemv_mma.cu
+int32_t bk_gemv_mma_launch(void* params, int K, int B, int vrows, bool has_swiglu, int* ctas_out);  // bk_gemv_mma.cu
 
-int32_t bk_gemv_launch(const bkGemvArgs& a) {
+int32_t bk_gemv_launch(const bkGemvArgs& a) { return bk_gemv_launch_tp(a, nullptr, nullptr, nullptr); }
+
+int32_t bk_gemv_launch_tp(const bkGemvArgs& a, const BkPush* push, const BkReduce* reduce, int* ctas_out) {
   BkContext& c = bk_ctx();
   BK_ARG(a.K > 0 && a.K % 256 == 0, "bkGemvQ4K: K=%d is not a positive multiple of 256", a.K);
   BK_ARG(a.B >= 1 && a.B <= 8, "bkGemvQ4K: B=%d outside 1..8", a.B);
   BK_ARG(a.n_segs >= 1 && a.n_segs <= 4, "bkGemvQ4K: n_segs=%d outside 1..4", a.n_segs);
-  BK_ARG(a.prologue >= BK_PRO_Q8 && a.prologue <= BK_PRO_STAGED, "bkGemvQ4K: unknown prologue %d", a.prologue);
+  BK_ARG((a.prologue >= BK_PRO_Q8 && a.prologue <= BK_PRO_STAGED) || (a.prologue == BK_PRO_REDUCE_RMSNORM && reduce && reduce->n > 0),
+         "bkGemvQ4K: unknown prologue %d", a.prologue);
+  const bool tc_path = a.B >= 2 && bk_gemv_mma_fits(a.K, a.B);
+  BK_ARG(a.prologue != BK_PRO_REDUCE_RMSNORM || !tc_path, "bkGemvQ4K: the reduce prologue exists on the batch-1 kernel only");
   if (a.prologue == BK_PRO_STAGED)
     BK_ARG(a.B >= 2 && bk_gemv_mma_fits(a.K, a.B),
            "bkGemvQ4K: a staged activation needs batch 2..8 and a K that fits the tensor-core path (K=%d B=%d)", a.K, a.B);
   BK_ARG(a.x != 0 && (a.x & 15) == 0, "bkGemvQ4K: x must be a non-null 16-byte aligned device pointer");
-  if (a.prologue == BK_PRO_RMSNORM)
+  if (a.prologue == BK_PRO_RMSNORM || a.prologue == BK_PRO_REDUCE_RMSNORM)
     BK_ARG(a.norm_w != 0 && (a.norm_w & 15) == 0, "bkGemvQ4K: norm_w must be non-null and 16-byte aligned");
   if (a.B >= 3 && !bk_gemv_mma_fits(a.K, a.B)) {
     // A K this wide (FFN 17408 of the 64-layer configuration) leaves no room for a 16-row tile beside the staged
     // activation of 3..8 columns.  The columns are independent, so the launch is cut into column pairs on the
     // small-batch kernel (same arithmetic, same bits); the weights of the later pairs come mostly from L2.
+    if (ctas_out) *ctas_out = 0;
     for (int b0 = 0; b0 < a.B; b0 += 2) {
       bkGemvArgs s = a;
+      BkPush ps;
+      if (push) {
+        ps = *push;
+        for (int r = 0; r < ps.n; r++) ps.dst[r] += (size_t)b0 * a.segs[0].ld_out;
+      }
       s.B = a.B - b0 < 2 ? a.B - b0 : 2;
       s.x = a.x + (uint64_t)b0 * (a.prologue == BK_PRO_Q8 ? (uint64_t)(a.K / 32) * 36 : (uint64_t)a.K * 2);
       for (int i = 0; i < a.n_segs && i < 4; i++) {
@@ -481,8 +498,10 @@ int32_t bk_gemv_launch(const bkGemvArgs& a) {
         s.segs[i].out = a.segs[i].out + (uint64_t)b0 * a.segs[i].ld_out * esz;
         if (a.segs[i].residual) s.segs[i].residual = a.segs[i].residual + (uint64_t)b0 * a.segs[i].ld_out * 2;
       }
-      int32_t rc = bk_gemv_launch(s);
+      int ctas = 0;
+      int32_t rc = bk_gemv_launch_tp(s, push ? &ps : nullptr, reduce, &ctas);
       if (rc != BK_OK) return rc;
+      if (ctas_out) *ctas_out += ctas;
     }
     return BK_OK;
   }
@@ -491,6 +510,9 @@ int32_t bk_gemv_launch(const bkGemvArgs& a) {
   p.n_segs = a.n_segs;
   p.prologue = a.prologue;
   p.x = bk_ptr<void>(a.x);
+  memset(&p.push, 0, sizeof(p.push));
+  memset(&p.red, 0, sizeof(p.red));
+  if (reduce && a.prologue == BK_PRO_REDUCE_RMSNORM) p.red = *reduce;
   p.norm_w = bk_ptr<uint16_t>(a.norm_w);
   p.eps = a.eps;
   int vrows = 0;
@@ -504,9 +526,14 @@ int32_t bk_gemv_launch(const bkGemvArgs& a) {
     const bkGemvSeg& g = a.segs[s];
     BK_ARG(g.n_rows > 0, "bkGemvQ4K: segment %d has n_rows=%d", s, g.n_rows);
     BK_ARG(g.W != 0 && (g.W & 15) == 0, "bkGemvQ4K: segment %d W must be non-null and 16-byte aligned", s);
-    BK_ARG(g.out != 0, "bkGemvQ4K: segment %d out is null", s);
-    BK_ARG(g.epilogue >= BK_EPI_F32 && g.epilogue <= BK_EPI_SWIGLU, "bkGemvQ4K: segment %d unknown epilogue %d", s,
-           g.epilogue);
+    if (g.epilogue == BK_EPI_PUSH_F32) {
+      BK_ARG(push && push->n > 0 && a.n_segs == 1, "bkGemvQ4K: segment %d: the push epilogue needs an exchange and a single segment", s);
+      p.push = *push;
+    } else {
+      BK_ARG(g.out != 0, "bkGemvQ4K: segment %d out is null", s);
+      BK_ARG(g.epilogue >= BK_EPI_F32 && g.epilogue <= BK_EPI_SWIGLU, "bkGemvQ4K: segment %d unknown epilogue %d", s,
+             g.epilogue);
+    }
     BK_ARG(g.ld_out >= g.col_off + g.n_rows, "bkGemvQ4K: segment %d ld_out=%d < col_off+n_rows", s, g.ld_out);
     if (g.epilogue == BK_EPI_SWIGLU) {
       BK_ARG(g.W2 != 0 && (g.W2 & 15) == 0, "bkGemvQ4K: segment %d needs a 16-byte aligned W2 for SwiGLU", s);
@@ -532,7 +559,7 @@ int32_t bk_gemv_launch(const bkGemvArgs& a) {
   p.cta_trace = nullptr;
   if (c.cta_trace && c.cta_trace_seen++ == c.cta_trace_launch) p.cta_trace = c.cta_trace;
 
-  if (a.B >= 2 && bk_gemv_mma_fits(a.K, a.B)) return bk_gemv_mma_launch(&p, a.K, a.B, vrows, has_swiglu);
+  if (tc_path) return bk_gemv_mma_launch(&p, a.K, a.B, vrows, has_swiglu, ctas_out);
 
   // ---- launch shape ----
   const size_t rowb = (size_t)(a.K / 256) * 144;
@@ -599,6 +626,7 @@ int32_t bk_gemv_launch(const bkGemvArgs& a) {
       threads = 18 * 32;                                        // > half of the registers: one class-B CTA per SM
     }
   }
+  if (ctas_out) *ctas_out = grid;
   switch (a.B) {
     case 1: return launch_gemv<1, gemv_gmax(1)>(p, grid, threads, smem);
     default: return launch_gemv<2, gemv_gmax(2)>(p, grid, threads, smem);   // batch 2 only when K is too wide for the tensor-core path

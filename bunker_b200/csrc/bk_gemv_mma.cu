@@ -105,6 +105,7 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
   bk_pdl_wait();
   bk_stamp(p.trace, 2);
 
+  if (p.push.n && blockIdx.x == 0 && tid < p.push.reset_n) p.push.reset[tid] = 0;
   if (p.prologue == BK_PRO_STAGED) {
     // the producer wrote exactly the bytes of xs | sc4: one bulk copy, nothing to compute
     if (tid == 0) {
@@ -225,16 +226,17 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
             const float yup = __fadd_rn(__fadd_rn(pu[0], pu[2 * 128]), __fadd_rn(pu[1 * 128], pu[3 * 128]));
             const VRow vr = decode_vrow(p, c0 + t * kTileRows + 2 * er);
             const SegDev& sg = p.segs[vr.si];
-            store_epilogue(sg, (size_t)ec * sg.ld_out + sg.col_off + vr.n, y, yup);
+            store_epilogue(p, sg, (size_t)ec * sg.ld_out + sg.col_off + vr.n, y, yup);
           }
         } else if (er < nr) {
           const VRow vr = decode_vrow(p, c0 + t * kTileRows + er);
           const SegDev& sg = p.segs[vr.si];
-          store_epilogue(sg, (size_t)ec * sg.ld_out + sg.col_off + vr.n, y, 0.0f);
+          store_epilogue(p, sg, (size_t)ec * sg.ld_out + sg.col_off + vr.n, y, 0.0f);
         }
       }
     }
   }
+  if (p.push.n) bk_push_signal(p.push.cnt, p.push.n);
   bk_stamp(p.trace, 5);
   bk_stamp_max(p.trace, 6);
 }
@@ -254,7 +256,7 @@ bool bk_gemv_mma_fits(int K, int B) {
 }
 
 // Launch shape for the MMA path; `p` arrives with segments, prologue and trace already filled in.
-int32_t bk_gemv_mma_launch(void* params, int K, int B, int vrows, bool has_swiglu) {
+int32_t bk_gemv_mma_launch(void* params, int K, int B, int vrows, bool has_swiglu, int* ctas_out) {
   GemvParams& p = *static_cast<GemvParams*>(params);
   BkContext& c = bk_ctx();
   const size_t rowb = (size_t)(K / 256) * 144, tile_bytes = (size_t)kTileRows * (rowb + 16);
@@ -275,6 +277,7 @@ int32_t bk_gemv_mma_launch(void* params, int K, int B, int vrows, bool has_swigl
     if (rounds > 8) rounds = 8;
     n_slots = rounds * tpr;
   }
+  if (ctas_out) *ctas_out = grid;
   p.tiles_base = base;
   p.tiles_extra = extra;
   (void)has_swiglu;

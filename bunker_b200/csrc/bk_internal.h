@@ -64,9 +64,39 @@ inline void bk_count_launch() {
 template <typename T>
 static inline T* bk_ptr(uint64_t p) { return reinterpret_cast<T*>(static_cast<uintptr_t>(p)); }
 
+// ---- tensor-parallel exchange fused into the GEMV (descriptors filled by bk_comm.cu) --------------------
+// Push: a row-parallel GEMV stores its f32 partial result into the exchange region of EVERY rank (its own included)
+// and, when a CTA is done, adds 1 to that CTA's arrival counter on every rank (release, system scope).
+// Reduce: the consumer (the next projection's prologue, or the norm+quantise launch at batch >= 2) waits until every
+// rank's counter shows all CTAs of the producing launch, then sums the partials from LOCAL memory in rank order,
+// adds the residual, rounds to bf16 once.  Two slots alternate; a push launch zeroes the other slot's local counters.
+#define BK_EPI_PUSH_F32 4        /* internal epilogue: f32 partial pushed to all ranks */
+#define BK_PRO_REDUCE_RMSNORM 4  /* internal prologue: reduce + residual -> bf16 -> RMSNorm -> Q8_1 */
+struct BkPush {
+  float* dst[8];
+  unsigned int* cnt[8];
+  unsigned int* reset;   // local counters to zero (the other slot's), reset_n of them
+  int n;                 // ranks; 0 = no push
+  int reset_n;
+};
+struct BkReduce {
+  const float* src;            // local region [n][stride] f32
+  const unsigned int* cnt;     // local arrival counters [n]
+  const uint16_t* res;         // residual bf16, same indexing as the partials
+  uint16_t* out;               // sum + residual as bf16 (materialised for later residual adds)
+  unsigned long long stride;   // floats between ranks' partials
+  unsigned int expected;       // arrivals per rank
+  int n;                       // ranks; 0 = no reduce
+};
+
 // internal launchers shared between translation units
 bool bk_gemv_mma_fits(int K, int B);   // whether the batch-3..8 tensor-core GEMV can hold this K (else column pairs)
 int32_t bk_gemv_launch(const bkGemvArgs& a);
+// same with the fused exchange: push (may be null) for BK_EPI_PUSH_F32 segments, reduce (may be null) for
+// BK_PRO_REDUCE_RMSNORM; ctas_out (may be null) receives the number of CTAs that will signal arrival
+int32_t bk_gemv_launch_tp(const bkGemvArgs& a, const BkPush* push, const BkReduce* reduce, int* ctas_out);
+int32_t bk_quant_rows_launch(uint64_t x, uint64_t w, int32_t K, int32_t B, float eps, uint64_t out, int32_t layout,
+                             const BkReduce* reduce);
 int32_t bk_argmax_launch(uint64_t logits, int32_t V, int32_t B, uint64_t idx, uint64_t val, uint64_t scratch,
                          uint64_t pos, uint64_t hist, int32_t hist_ld, int32_t hist_rows);
 
@@ -97,6 +127,8 @@ inline unsigned long long* bk_trace_slot() {
 
 // tensor-parallel exchange (bk_comm.cu)
 uint64_t bk_comm_slot_ptr(uint64_t comm, int slot);
+int32_t bk_comm_push_desc(uint64_t comm, int slot, BkPush* out);       // slot 0 or 1 of the push region
+int32_t bk_comm_reduce_desc(uint64_t comm, int slot, BkReduce* out);   // src/cnt/stride/n filled in
 int32_t bk_comm_allreduce_residual(uint64_t comm, int slot, int n, uint64_t residual, uint64_t out);
 int32_t bk_comm_argmax_merge(uint64_t comm, int slot, int B, uint64_t local_val, uint64_t local_idx, int offset, uint64_t idx,
                              uint64_t val, uint64_t pos, uint64_t hist, int hist_ld, int hist_rows);

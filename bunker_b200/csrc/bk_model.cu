@@ -138,15 +138,42 @@ int32_t enqueue_step(Model& m, int parity) {
   const bool q8_handoff = B >= 2;
   // Input of a projection: fused RMSNorm/quantise prologue at batch 1; at batch >= 2 one small launch
   // normalises and quantises the rows once and every CTA of the projection just copies the blocks.
+  // Tensor parallel: a row-parallel GEMV pushes its partial sums to every rank (BK_EPI_PUSH_F32); the sum over ranks,
+  // the residual add and the bf16 rounding happen in the prologue of whatever reads the result next (`pending`).
+  struct Pending { bool on; int slot; int ctas; uint64_t res, out; } pending = {false, 0, 0, 0, 0};
+  BkReduce red_desc;
+  bool use_red = false;   // the GEMV being set up carries the reduce prologue (batch 1)
   auto set_input = [&](bkGemvArgs& g, uint64_t x, int K, uint64_t norm_w) -> int32_t {
     g.K = K; g.B = B; g.eps = c.eps;
+    use_red = false;
+    const bool reduce = pending.on && norm_w && x == pending.out;
+    if (reduce) {
+      TRY(bk_comm_reduce_desc(m.comm, pending.slot, &red_desc));
+      red_desc.res = bk_ptr<uint16_t>(pending.res);
+      red_desc.out = bk_ptr<uint16_t>(pending.out);
+      red_desc.expected = (unsigned int)pending.ctas;
+      pending.on = false;
+    }
     if (q8_handoff) {
       const bool staged = bk_gemv_mma_fits(K, B);   // else the GEMV runs as column pairs reading plain blocks
-      PROF(PC_QUANT, bkRmsNormQuantQ8_1(x, norm_w, K, B, c.eps, m.xq, staged ? BK_Q8_STAGED : BK_Q8_BLOCKS));
+      PROF(PC_QUANT, bk_quant_rows_launch(x, norm_w, K, B, c.eps, m.xq, staged ? BK_Q8_STAGED : BK_Q8_BLOCKS,
+                                          reduce ? &red_desc : nullptr));
       g.prologue = staged ? BK_PRO_STAGED : BK_PRO_Q8; g.x = m.xq;
     } else {
-      g.prologue = norm_w ? BK_PRO_RMSNORM : BK_PRO_BF16; g.x = x; g.norm_w = norm_w;
+      g.prologue = reduce ? BK_PRO_REDUCE_RMSNORM : norm_w ? BK_PRO_RMSNORM : BK_PRO_BF16; g.x = x; g.norm_w = norm_w;
+      use_red = reduce;
     }
+    return BK_OK;
+  };
+  auto launch = [&](const bkGemvArgs& g) -> int32_t { return bk_gemv_launch_tp(g, nullptr, use_red ? &red_desc : nullptr, nullptr); };
+  // row-parallel GEMV of a tensor-parallel model: push the partials, remember who adds the residual
+  auto launch_push = [&](bkGemvArgs& g, uint64_t W, int slot, uint64_t res, uint64_t out) -> int32_t {
+    BkPush ps;
+    TRY(bk_comm_push_desc(m.comm, slot, &ps));
+    g.segs[0] = bkGemvSeg{W, 0, 0, 0, H, BK_EPI_PUSH_F32, H, 0};
+    int ctas = 0;
+    TRY(bk_gemv_launch_tp(g, &ps, use_red ? &red_desc : nullptr, &ctas));
+    pending = Pending{true, slot, ctas, res, out};
     return BK_OK;
   };
   PROF(PC_EMBED, bkEmbedQ4K(m.embed, H, m.ids, B, m.x[0]));
@@ -161,7 +188,7 @@ int32_t enqueue_step(Model& m, int parity) {
       g.segs[1] = bkGemvSeg{L.z, 0, m.z, 0, m.ZD, BK_EPI_BF16, m.ZD, 0};
       g.segs[2] = bkGemvSeg{L.a, 0, m.a, 0, m.Hv, BK_EPI_F32, m.Hv, 0};
       g.segs[3] = bkGemvSeg{L.b, 0, m.b, 0, m.Hv, BK_EPI_F32, m.Hv, 0};
-      PROF(PC_GEMV_PROJ, bk_gemv_launch(g));
+      PROF(PC_GEMV_PROJ, launch(g));
       bkGdnArgs ga;
       memset(&ga, 0, sizeof(ga));
       ga.qkv = m.qkv; ga.z = m.z; ga.a = m.a; ga.b = m.b;
@@ -178,11 +205,9 @@ int32_t enqueue_step(Model& m, int parity) {
       g.prologue = zd_staged ? BK_PRO_STAGED : q8_handoff ? BK_PRO_Q8 : BK_PRO_BF16; g.x = q8_handoff ? m.attn_q8 : m.attn_out;
       if (m.tp == 1) {
         g.segs[0] = bkGemvSeg{L.out_proj, 0, m.h1, m.x[cur], H, BK_EPI_ADD_BF16, H, 0};
-        PROF(PC_GEMV_OUT, bk_gemv_launch(g));
+        PROF(PC_GEMV_OUT, launch(g));
       } else {
-        g.segs[0] = bkGemvSeg{L.out_proj, 0, bk_comm_slot_ptr(m.comm, 0), 0, H, BK_EPI_F32, H, 0};
-        PROF(PC_GEMV_OUT, bk_gemv_launch(g));
-        PROF(PC_EXCHANGE, bk_comm_allreduce_residual(m.comm, 0, B * H, m.x[cur], m.h1));
+        PROF(PC_GEMV_OUT, launch_push(g, L.out_proj, 0, m.x[cur], m.h1));
       }
     } else {
       memset(&g, 0, sizeof(g));
@@ -191,7 +216,7 @@ int32_t enqueue_step(Model& m, int parity) {
       g.segs[0] = bkGemvSeg{L.q, 0, m.qg, 0, m.QG, BK_EPI_BF16, m.QG, 0};
       g.segs[1] = bkGemvSeg{L.k, 0, m.kbuf, 0, m.KVD, BK_EPI_BF16, m.KVD, 0};
       g.segs[2] = bkGemvSeg{L.v, 0, m.vbuf, 0, m.KVD, BK_EPI_BF16, m.KVD, 0};
-      PROF(PC_GEMV_PROJ, bk_gemv_launch(g));
+      PROF(PC_GEMV_PROJ, launch(g));
       bkAttnArgs aa;
       memset(&aa, 0, sizeof(aa));
       aa.qg = m.qg; aa.k = m.kbuf; aa.v = m.vbuf; aa.q_norm_w = L.q_norm; aa.k_norm_w = L.k_norm;
@@ -209,28 +234,24 @@ int32_t enqueue_step(Model& m, int parity) {
       g.prologue = o_staged ? BK_PRO_STAGED : q8_handoff ? BK_PRO_Q8 : BK_PRO_BF16; g.x = q8_handoff ? m.attn_q8 : m.attn_out;
       if (m.tp == 1) {
         g.segs[0] = bkGemvSeg{L.o, 0, m.h1, m.x[cur], H, BK_EPI_ADD_BF16, H, 0};
-        PROF(PC_GEMV_OUT, bk_gemv_launch(g));
+        PROF(PC_GEMV_OUT, launch(g));
       } else {
-        g.segs[0] = bkGemvSeg{L.o, 0, bk_comm_slot_ptr(m.comm, 0), 0, H, BK_EPI_F32, H, 0};
-        PROF(PC_GEMV_OUT, bk_gemv_launch(g));
-        PROF(PC_EXCHANGE, bk_comm_allreduce_residual(m.comm, 0, B * H, m.x[cur], m.h1));
+        PROF(PC_GEMV_OUT, launch_push(g, L.o, 0, m.x[cur], m.h1));
       }
     }
     memset(&g, 0, sizeof(g));
     TRY(set_input(g, m.h1, H, L.post_ln));
     g.n_segs = 1;
     g.segs[0] = bkGemvSeg{L.gate, L.up, m.act, 0, m.inter, BK_EPI_SWIGLU, m.inter, 0};
-    PROF(PC_GEMV_GATEUP, bk_gemv_launch(g));
+    PROF(PC_GEMV_GATEUP, launch(g));
     memset(&g, 0, sizeof(g));
     TRY(set_input(g, m.act, m.inter, 0));
     g.n_segs = 1;
     if (m.tp == 1) {
       g.segs[0] = bkGemvSeg{L.down, 0, m.x[cur ^ 1], m.h1, H, BK_EPI_ADD_BF16, H, 0};
-      PROF(PC_GEMV_DOWN, bk_gemv_launch(g));
+      PROF(PC_GEMV_DOWN, launch(g));
     } else {
-      g.segs[0] = bkGemvSeg{L.down, 0, bk_comm_slot_ptr(m.comm, 1), 0, H, BK_EPI_F32, H, 0};
-      PROF(PC_GEMV_DOWN, bk_gemv_launch(g));
-      PROF(PC_EXCHANGE, bk_comm_allreduce_residual(m.comm, 1, B * H, m.h1, m.x[cur ^ 1]));
+      PROF(PC_GEMV_DOWN, launch_push(g, L.down, 1, m.h1, m.x[cur ^ 1]));
     }
     cur ^= 1;
   }
@@ -240,7 +261,7 @@ int32_t enqueue_step(Model& m, int parity) {
   g.n_segs = 1;
   g.segs[0] = bkGemvSeg{m.embed + (uint64_t)m.vocab_offset * (H / 256) * 144, 0, m.logits, 0, m.vocab_local, BK_EPI_F32,
                         m.vocab_local, 0};
-  PROF(PC_GEMV_LMHEAD, bk_gemv_launch(g));
+  PROF(PC_GEMV_LMHEAD, launch(g));
   if (m.tp == 1) {
     PROF(PC_ARGMAX, bk_argmax_launch(m.logits, m.vocab_local, B, m.ids, m.val, m.argmax_scratch, m.pos, m.hist, B, c.max_len));
   } else {

@@ -94,9 +94,10 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t* x, const u
 // 148 CTAs normalising and quantising all batch rows again.  NORM: one CTA per batch row (the canonical
 // 256-thread sum of squares).  Plain: 256 chunks of 8 values per CTA.  Output blocks [B][K/32][36].
 // STAGED: the output is the staged image of the tensor-core GEMV instead of 36-byte blocks.
+// rd.n > 0 (NORM only): row b is not read from x but formed from the tensor-parallel partial sums + residual.
 template <bool NORM, bool STAGED>
 __global__ void __launch_bounds__(256) quant_rows_kernel(const uint16_t* x, const uint16_t* w, int K, float eps,
-                                                         uint8_t* out) {
+                                                         uint8_t* out, const BkReduce rd, int* status) {
   bk_pdl_trigger();
   __shared__ float red[8];
   const int b = blockIdx.y, nchunk = K / 8, tid = threadIdx.x;
@@ -107,16 +108,21 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const uint16_t* x, cons
     const bool have0 = tid < nchunk;
     if (have0) load8_bf16(w + (size_t)tid * 8, wv0);
     bk_pdl_wait();
+    if (rd.n) bk_reduce_wait(rd.cnt, rd.n, rd.expected, status);
+    auto load_in = [&](int q, float (&y)[8]) {
+      if (rd.n) bk_reduce_load8(rd.src, rd.stride, rd.n, rd.res, rd.out, (size_t)b * K + (size_t)q * 8, true, y);
+      else load8_bf16(row + (size_t)q * 8, y);
+    };
     float y0[8];
     float acc = 0.0f;
     if (have0) {
-      load8_bf16(row + (size_t)tid * 8, y0);
+      load_in(tid, y0);
 #pragma unroll
       for (int e = 0; e < 8; e++) acc = fmaf(y0[e], y0[e], acc);
     }
     for (int q = tid + 256; q < nchunk; q += 256) {
       float v[8];
-      load8_bf16(row + (size_t)q * 8, v);
+      load_in(q, v);
 #pragma unroll
       for (int e = 0; e < 8; e++) acc = fmaf(v[e], v[e], acc);
     }
@@ -133,7 +139,7 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const uint16_t* x, cons
 #pragma unroll
         for (int e = 0; e < 8; e++) { v[e] = y0[e]; wv[e] = wv0[e]; }
       } else {
-        load8_bf16(row + (size_t)q * 8, v);
+        load_in(q, v);
         load8_bf16(w + (size_t)q * 8, wv);
       }
       float y[8];
@@ -520,25 +526,39 @@ int32_t bkRmsNorm(uint64_t x, uint64_t w, int32_t H, int32_t B, float eps, uint6
   return BK_OK;
 }
 
-int32_t bkRmsNormQuantQ8_1(uint64_t x, uint64_t w, int32_t K, int32_t B, float eps, uint64_t out, int32_t layout) {
-  BK_REQUIRE_INIT();
+}  // extern "C"
+
+int32_t bk_quant_rows_launch(uint64_t x, uint64_t w, int32_t K, int32_t B, float eps, uint64_t out, int32_t layout,
+                             const BkReduce* reduce) {
   BK_ARG(K > 0 && K % 256 == 0 && B > 0, "bkRmsNormQuantQ8_1: bad shape K=%d B=%d (K a multiple of 256)", K, B);
-  BK_ARG(x && out && ((x | w) & 15) == 0 && (out & 3) == 0, "bkRmsNormQuantQ8_1: null or misaligned pointer");
+  BK_ARG((x || reduce) && out && ((x | w) & 15) == 0 && (out & 3) == 0, "bkRmsNormQuantQ8_1: null or misaligned pointer");
   BK_ARG(layout == BK_Q8_BLOCKS || layout == BK_Q8_STAGED, "bkRmsNormQuantQ8_1: unknown layout %d", layout);
+  BK_ARG(!reduce || w, "bkRmsNormQuantQ8_1: the reduce input exists with the norm only");
   if (layout == BK_Q8_STAGED) BK_ARG(B <= 8 && (out & 15) == 0, "bkRmsNormQuantQ8_1: a staged image holds at most 8 rows and is 16-byte aligned");
   const dim3 grid = w ? dim3(1, B) : dim3((K / 8 + 255) / 256, B);
   auto* px = bk_ptr<uint16_t>(x);
   auto* pw = bk_ptr<uint16_t>(w);
   auto* po = bk_ptr<uint8_t>(out);
+  BkReduce red;
+  memset(&red, 0, sizeof(red));
+  if (reduce) red = *reduce;
+  int* st = bk_ctx().d_status;
   if (w) {
-    if (layout == BK_Q8_STAGED) BK_CUDA(bk_launch_pdl(quant_rows_kernel<true, true>, grid, dim3(256), 0, px, pw, K, eps, po));
-    else BK_CUDA(bk_launch_pdl(quant_rows_kernel<true, false>, grid, dim3(256), 0, px, pw, K, eps, po));
+    if (layout == BK_Q8_STAGED) BK_CUDA(bk_launch_pdl(quant_rows_kernel<true, true>, grid, dim3(256), 0, px, pw, K, eps, po, red, st));
+    else BK_CUDA(bk_launch_pdl(quant_rows_kernel<true, false>, grid, dim3(256), 0, px, pw, K, eps, po, red, st));
   } else {
-    if (layout == BK_Q8_STAGED) BK_CUDA(bk_launch_pdl(quant_rows_kernel<false, true>, grid, dim3(256), 0, px, pw, K, eps, po));
-    else BK_CUDA(bk_launch_pdl(quant_rows_kernel<false, false>, grid, dim3(256), 0, px, pw, K, eps, po));
+    if (layout == BK_Q8_STAGED) BK_CUDA(bk_launch_pdl(quant_rows_kernel<false, true>, grid, dim3(256), 0, px, pw, K, eps, po, red, st));
+    else BK_CUDA(bk_launch_pdl(quant_rows_kernel<false, false>, grid, dim3(256), 0, px, pw, K, eps, po, red, st));
   }
   BK_CHECK_LAUNCH();
   return BK_OK;
+}
+
+extern "C" {
+int32_t bkRmsNormQuantQ8_1(uint64_t x, uint64_t w, int32_t K, int32_t B, float eps, uint64_t out, int32_t layout) {
+  BK_REQUIRE_INIT();
+  BK_ARG(x != 0, "bkRmsNormQuantQ8_1: x is null");
+  return bk_quant_rows_launch(x, w, K, B, eps, out, layout, nullptr);
 }
 
 uint64_t bkStagedBytes(int32_t K, int32_t B) { return (K > 0 && B > 0) ? (uint64_t)bk_staged_bytes(K, B) : 0; }
