@@ -18,13 +18,14 @@
 //   s+1, which needs every peer's flag s+1, which a peer only raises after it has finished reading s.
 // Every wait is bounded; on timeout the kernel sets the status word and returns.
 //
-// Fused exchange (the model's row-parallel GEMVs): a second region, push[2 slots][ranks][payload], receives the
-// partial sums of ALL ranks by remote stores from the producing GEMV itself; every CTA of that GEMV then adds 1
-// to arrivals[slot][its rank] on every rank (release, system scope).  The consumer -- the prologue of the next
-// projection, or the norm+quantise launch -- waits for the full CTA count from every rank and sums from local
-// memory: one NVLink store latency per exchange, no extra launch, no remote loads.  Slots alternate; a pushing
-// launch zeroes the local arrival counters of the other slot (its consumers finished before this launch passed
-// its dependency wait, and no peer can push into that slot again before it has seen this launch's arrivals).
+// Fused exchange (the model's row-parallel GEMVs): a second region, push[2 slots][ranks][payload as {value, tag}
+// words], receives the partial sums of ALL ranks by remote 8-byte stores from the producing GEMV itself.  The
+// consumer -- the prologue of the next projection, or the norm+quantise launch -- polls the words it needs in
+// local memory until their tag is the current one and sums them: one NVLink store latency per exchange, no extra
+// launch, no fence, no remote load.  The tag is epoch*256 + (index of the exchange in the step) + 1; the epoch
+// word is advanced by the last kernel of every step (argmax_merge_kernel), identically on all ranks.  Slots
+// alternate: nobody can push exchange e+2 before it has consumed e+1, which needs every rank's e+1 words, which
+// a rank only sends after it has consumed e.
 #include <string.h>
 
 #include "bk_common.cuh"
@@ -33,8 +34,8 @@
 struct BkComm {
   int rank = 0, nranks = 1;
   size_t payload_bytes = 0;       // per slot
-  uint8_t* local = nullptr;       // [3 slots][payload] | flags[8] u64 | counter u64 | pad | push [2][nranks][payload] | arrivals [2][8] u32
-  size_t push_off = 0, cnt_off = 0;   // byte offsets of the push region and its arrival counters (same on every rank)
+  uint8_t* local = nullptr;       // [3 slots][payload] | flags[8] u64 | counter u64 | pad | push [2][nranks][2*payload] | epoch u32
+  size_t push_off = 0, epoch_off = 0; // byte offsets of the push region and the step counter (same on every rank)
   uint8_t* peer[8] = {nullptr};   // mapped bases, peer[rank] == local
   bool imported = false;
 };
@@ -134,7 +135,8 @@ __global__ void __launch_bounds__(1024) allreduce_residual_kernel(const CommDev 
 // merge per-rank (value, index) pairs: payload of rank r = B pairs {f32 val, i32 idx (already global)}.
 // Strict '>' in rank order keeps the lowest index on ties because rank order is vocabulary order.
 __global__ void __launch_bounds__(32) argmax_merge_kernel(const CommDev c, int slot_id, int B, int32_t* idx, float* val, int32_t* pos,
-                                                          int32_t* hist, int hist_ld, int hist_rows, int* status) {
+                                                          int32_t* hist, int hist_ld, int hist_rows, int* status,
+                                                          unsigned int* epoch) {
   bk_pdl_trigger();
   bk_pdl_wait();
   unsigned long long* counter = flags_of(c.peer[c.rank], c.payload_bytes) + kMaxRanks;
@@ -164,7 +166,10 @@ __global__ void __launch_bounds__(32) argmax_merge_kernel(const CommDev c, int s
     }
   }
   __syncthreads();
-  if (threadIdx.x == 0) *counter = seq;
+  if (threadIdx.x == 0) {
+    *counter = seq;
+    if (epoch) *epoch = *epoch + 1;   // last kernel of a decode step: the tags of the next step's fused exchanges change
+  }
 }
 
 // local (val, idx) of this rank -> {val, idx + offset} pairs in the exchange slot of the next sequence number
@@ -218,7 +223,8 @@ int32_t bk_comm_argmax_merge(uint64_t comm, int slot, int B, uint64_t local_val,
                         bk_ptr<int32_t>(local_idx), offset));
   BK_CHECK_LAUNCH();
   BK_CUDA(bk_launch_pdl(argmax_merge_kernel, dim3(1), dim3(32), 0, dev_view(*c), slot, B, bk_ptr<int32_t>(idx), bk_ptr<float>(val),
-                        bk_ptr<int32_t>(pos), bk_ptr<int32_t>(hist), hist_ld, hist_rows, bk_ctx().d_status));
+                        bk_ptr<int32_t>(pos), bk_ptr<int32_t>(hist), hist_ld, hist_rows, bk_ctx().d_status,
+                        reinterpret_cast<unsigned int*>(c->local + c->epoch_off)));
   BK_CHECK_LAUNCH();
   return BK_OK;
 }
@@ -227,23 +233,26 @@ int32_t bk_comm_push_desc(uint64_t comm, int slot, BkPush* out) {
   BkComm* c = as_comm(comm);
   BK_ARG(c && c->imported && out && (slot == 0 || slot == 1), "push descriptor: bad communicator or slot");
   memset(out, 0, sizeof(*out));
-  for (int r = 0; r < c->nranks; r++) {
-    out->dst[r] = reinterpret_cast<float*>(c->peer[r] + c->push_off + ((size_t)slot * c->nranks + c->rank) * c->payload_bytes);
-    out->cnt[r] = reinterpret_cast<unsigned int*>(c->peer[r] + c->cnt_off) + slot * kMaxRanks + c->rank;
-  }
-  out->reset = reinterpret_cast<unsigned int*>(c->local + c->cnt_off) + (1 - slot) * kMaxRanks;
-  out->reset_n = c->nranks;
+  for (int r = 0; r < c->nranks; r++)
+    out->dst[r] = reinterpret_cast<uint2*>(c->peer[r] + c->push_off + ((size_t)slot * c->nranks + c->rank) * 2 * c->payload_bytes);
+  out->epoch = reinterpret_cast<const unsigned int*>(c->local + c->epoch_off);
   out->n = c->nranks;
   return BK_OK;
+}
+
+uint64_t bk_comm_epoch_ptr(uint64_t comm) {
+  BkComm* c = as_comm(comm);
+  return c ? (uint64_t)(uintptr_t)(c->local + c->epoch_off) : 0;
 }
 
 int32_t bk_comm_reduce_desc(uint64_t comm, int slot, BkReduce* out) {
   BkComm* c = as_comm(comm);
   BK_ARG(c && c->imported && out && (slot == 0 || slot == 1), "reduce descriptor: bad communicator or slot");
   memset(out, 0, sizeof(*out));
-  out->src = reinterpret_cast<const float*>(c->local + c->push_off + (size_t)slot * c->nranks * c->payload_bytes);
-  out->cnt = reinterpret_cast<const unsigned int*>(c->local + c->cnt_off) + slot * kMaxRanks;
-  out->stride = c->payload_bytes / 4;
+  out->src = reinterpret_cast<const uint2*>(c->local + c->push_off + (size_t)slot * c->nranks * 2 * c->payload_bytes);
+  out->epoch = reinterpret_cast<const unsigned int*>(c->local + c->epoch_off);
+  out->stride = c->payload_bytes / 4;   // one 8-byte word per f32 of the payload
+  out->ready = reinterpret_cast<unsigned int*>(c->local + c->epoch_off + 64) + slot;
   out->n = c->nranks;
   return BK_OK;
 }
@@ -271,8 +280,8 @@ int32_t bkCommCreate(int32_t rank, int32_t nranks, uint64_t payload_bytes, uint6
   c->nranks = nranks;
   c->payload_bytes = (payload_bytes + 255) / 256 * 256;
   c->push_off = (kSlots * c->payload_bytes + (kMaxRanks + 1) * sizeof(unsigned long long) + 255) / 256 * 256;
-  c->cnt_off = c->push_off + (size_t)2 * nranks * c->payload_bytes;
-  size_t total = c->cnt_off + 2 * kMaxRanks * sizeof(unsigned int);
+  c->epoch_off = c->push_off + (size_t)2 * nranks * 2 * c->payload_bytes;
+  size_t total = c->epoch_off + 256;
   void* p = nullptr;
   cudaError_t e = cudaMalloc(&p, total);
   if (e != cudaSuccess) {

@@ -188,54 +188,63 @@ BK_DEVINL void bk_q8_1_store(uint8_t* blk, const float (&y)[PER], int idx_in_blo
 }
 
 // ---- fused tensor-parallel exchange (descriptors: BkPush / BkReduce in bk_internal.h) ------------------
-// bounded wait for `expected` arrivals from each of n ranks; ends with a CTA barrier.  Sets *status on timeout.
-BK_DEVINL void bk_reduce_wait(const unsigned int* cnt, int n, unsigned int expected, int* status) {
-  if ((int)threadIdx.x < n) {
-    const unsigned int* c = cnt + threadIdx.x;
-    unsigned int v;
-    int it = 0;
-    // an earlier wait already gave up: the step is lost, do not wait again
-    if (status && *reinterpret_cast<volatile int*>(status) != 0) it = 1 << 20;
-    for (;;) {
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(c) : "memory");
-      if (v >= expected) break;
-      if (++it > (1 << 20)) {
-        if (status) atomicExch(status, 10003 /* BK_ERR_TIMEOUT */);
-        break;
+BK_DEVINL unsigned int bk_exchange_tag(const unsigned int* epoch, unsigned int tag_add) {
+  return *reinterpret_cast<const volatile unsigned int*>(epoch) * 256u + tag_add;
+}
+BK_DEVINL void bk_push_store(uint2* dst, float y, unsigned int tag) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(y)), "r"(tag) : "memory");
+}
+BK_DEVINL uint4 bk_ld_volatile_v4(const uint2* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+// four 16-byte loads = 8 {value, tag} words (each half carries its own tag); polls until all tags show.
+// Bounded: on timeout *status is set and whatever is there is used.
+BK_DEVINL void bk_pull8(const uint2* s, unsigned int tag, int* status, uint4 (&w)[4]) {
+  for (int it = 0;; it++) {
+#pragma unroll
+    for (int k = 0; k < 4; k++) w[k] = bk_ld_volatile_v4(s + 2 * k);
+    bool ok = true;
+#pragma unroll
+    for (int k = 0; k < 4; k++) ok = ok && w[k].y == tag && w[k].w == tag;
+    if (ok) break;
+    if (it > (1 << 20) || (status && (it & 255) == 255 && *reinterpret_cast<volatile int*>(status) != 0)) {
+      if (status) atomicExch(status, 10003 /* BK_ERR_TIMEOUT */);
+      break;
+    }
+  }
+}
+// 8 consecutive values at element offset o (a multiple of 8): ((p0 + p1) + ...) + residual, rounded to bf16 (returned
+// as f32); the ranks' words are polled in rank order.
+BK_DEVINL void bk_reduce_load8(const uint2* src, unsigned long long stride, int n, unsigned int tag, const uint16_t* res,
+                               uint16_t* out, size_t o, bool write_out, int* status, float (&y)[8]) {
+  float a[8];
+  for (int r = 0; r < n; r++) {
+    uint4 w[4];
+    bk_pull8(src + r * stride + o, tag, status, w);
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      if (r == 0) {
+        a[2 * k] = __uint_as_float(w[k].x);
+        a[2 * k + 1] = __uint_as_float(w[k].z);
+      } else {
+        a[2 * k] = __fadd_rn(a[2 * k], __uint_as_float(w[k].x));
+        a[2 * k + 1] = __fadd_rn(a[2 * k + 1], __uint_as_float(w[k].z));
       }
     }
   }
-  __syncthreads();
-}
-// 8 consecutive values at element offset o: ((p0 + p1) + ...) + residual, rounded to bf16 (returned as f32)
-BK_DEVINL void bk_reduce_load8(const float* src, unsigned long long stride, int n, const uint16_t* res, uint16_t* out,
-                               size_t o, bool write_out, float (&y)[8]) {
-  float4 a = __ldcg(reinterpret_cast<const float4*>(src + o)), c = __ldcg(reinterpret_cast<const float4*>(src + o) + 1);
-  for (int r = 1; r < n; r++) {
-    const float4 v = __ldcg(reinterpret_cast<const float4*>(src + r * stride + o));
-    const float4 w = __ldcg(reinterpret_cast<const float4*>(src + r * stride + o) + 1);
-    a.x = __fadd_rn(a.x, v.x); a.y = __fadd_rn(a.y, v.y); a.z = __fadd_rn(a.z, v.z); a.w = __fadd_rn(a.w, v.w);
-    c.x = __fadd_rn(c.x, w.x); c.y = __fadd_rn(c.y, w.y); c.z = __fadd_rn(c.z, w.z); c.w = __fadd_rn(c.w, w.w);
-  }
   const uint4 rv = *reinterpret_cast<const uint4*>(res + o);
   uint4 ov;
-  ov.x = bk_f32x2_to_bf16x2(__fadd_rn(a.x, __uint_as_float(rv.x << 16)), __fadd_rn(a.y, __uint_as_float(rv.x & 0xffff0000u)));
-  ov.y = bk_f32x2_to_bf16x2(__fadd_rn(a.z, __uint_as_float(rv.y << 16)), __fadd_rn(a.w, __uint_as_float(rv.y & 0xffff0000u)));
-  ov.z = bk_f32x2_to_bf16x2(__fadd_rn(c.x, __uint_as_float(rv.z << 16)), __fadd_rn(c.y, __uint_as_float(rv.z & 0xffff0000u)));
-  ov.w = bk_f32x2_to_bf16x2(__fadd_rn(c.z, __uint_as_float(rv.w << 16)), __fadd_rn(c.w, __uint_as_float(rv.w & 0xffff0000u)));
+  ov.x = bk_f32x2_to_bf16x2(__fadd_rn(a[0], __uint_as_float(rv.x << 16)), __fadd_rn(a[1], __uint_as_float(rv.x & 0xffff0000u)));
+  ov.y = bk_f32x2_to_bf16x2(__fadd_rn(a[2], __uint_as_float(rv.y << 16)), __fadd_rn(a[3], __uint_as_float(rv.y & 0xffff0000u)));
+  ov.z = bk_f32x2_to_bf16x2(__fadd_rn(a[4], __uint_as_float(rv.z << 16)), __fadd_rn(a[5], __uint_as_float(rv.z & 0xffff0000u)));
+  ov.w = bk_f32x2_to_bf16x2(__fadd_rn(a[6], __uint_as_float(rv.w << 16)), __fadd_rn(a[7], __uint_as_float(rv.w & 0xffff0000u)));
   if (write_out) *reinterpret_cast<uint4*>(out + o) = ov;
   y[0] = __uint_as_float(ov.x << 16); y[1] = __uint_as_float(ov.x & 0xffff0000u);
   y[2] = __uint_as_float(ov.y << 16); y[3] = __uint_as_float(ov.y & 0xffff0000u);
   y[4] = __uint_as_float(ov.z << 16); y[5] = __uint_as_float(ov.z & 0xffff0000u);
   y[6] = __uint_as_float(ov.w << 16); y[7] = __uint_as_float(ov.w & 0xffff0000u);
-}
-// end of a pushing CTA: everything the CTA stored becomes visible before the arrival is counted on each rank
-BK_DEVINL void bk_push_signal(unsigned int* const* cnt, int n) {
-  __syncthreads();
-  if ((int)threadIdx.x < n) {
-    __threadfence_system();
-    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt[threadIdx.x]) : "memory");
-  }
 }
 
 // ---- staged activation image of the tensor-core GEMV (batch 2..8) ---------------------

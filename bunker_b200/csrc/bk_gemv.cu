@@ -190,7 +190,9 @@ __device__ __forceinline__ int slot_row(bool swiglu, int r, int nr) { return swi
 // G rows in shared memory and an mbarrier.  depth == 0 ("pool"): every group has its own slot and all
 // copies are issued before the dependency wait.  depth > 0 ("ring"): a warp owns `depth` slots and
 // refills a slot with its next group as soon as the slot is consumed.
-template <int B, int GMAX>
+// TP: the build with the tensor-parallel reduce prologue and push epilogue (kept out of the single-GPU build, whose
+// register allocation they would disturb).
+template <int B, int GMAX, bool TP>
 __global__ void __launch_bounds__(576, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kernel(const GemvParams p) {
   bk_pdl_trigger();
   bk_stamp(p.trace, 0);
@@ -240,20 +242,48 @@ __global__ void __launch_bounds__(576, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kern
     wpre = __ldg(reinterpret_cast<const uint4*>(p.norm_w) + threadIdx.x);
   __syncwarp();
   bk_stamp(p.trace, 1);
-  bk_pdl_wait();
+  // A reducing launch depends on its predecessor (the pushing GEMV) only through the tagged exchange words, which it
+  // polls; it does not wait for that grid to complete, because completion includes the acknowledgement of the
+  // predecessor's remote stores -- an NVLink round trip.  Everything older is complete: the predecessor passed its own
+  // dependency wait before it pushed anything.  Nothing is written here before every tag of the row has been seen,
+  // i.e. before every CTA of the predecessor has finished reading its inputs.
+  if (!(TP && p.prologue == BK_PRO_REDUCE_RMSNORM)) bk_pdl_wait();
   bk_stamp(p.trace, 2);
   if (ctr && threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); ctr[1] = t_; }
 
-  if (p.push.n && blockIdx.x == 0 && (int)threadIdx.x < p.push.reset_n) p.push.reset[threadIdx.x] = 0;
   if (p.prologue == BK_PRO_Q8)
     prologue_q8<false>(p, B, xs, d8s, s8s);
   else if (p.prologue == BK_PRO_BF16)
     prologue_bf16<false>(p, B, xs, d8s, s8s, red, wpre);
   else if (p.prologue == BK_PRO_RMSNORM)
     prologue_bf16<true>(p, B, xs, d8s, s8s, red, wpre);
-  else {
-    bk_reduce_wait(p.red.cnt, p.red.n, p.red.expected, p.status);
-    prologue_bf16<true, true>(p, B, xs, d8s, s8s, red, wpre);
+  else if constexpr (TP) {
+    // Tensor-parallel input.  CTA 0 gathers the ranks' partial sums (tagged words, polled), adds the residual and
+    // writes the bf16 row; it then publishes the exchange tag in a local word.  The other CTAs wait for that word
+    // and read the 4 KB row from L2 -- 148 CTAs polling the tagged words themselves would flood L2.
+    const unsigned int tag = bk_exchange_tag(p.red.epoch, p.red.tag_add);
+    if (blockIdx.x == 0) {
+      prologue_bf16<true, 1>(p, B, xs, d8s, s8s, red, wpre);
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence();
+        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.red.ready), "r"(tag) : "memory");
+      }
+    } else {
+      if (threadIdx.x == 0) {
+        unsigned int v;
+        for (int it = 0;; it++) {
+          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.red.ready) : "memory");
+          if (v == tag) break;
+          if (it > (1 << 22)) {
+            if (p.status) atomicExch(p.status, BK_ERR_TIMEOUT);
+            break;
+          }
+        }
+      }
+      __syncthreads();
+      prologue_bf16<true, 2>(p, B, xs, d8s, s8s, red, wpre);
+    }
   }
   __syncthreads();
   bk_stamp(p.trace, 3);
@@ -324,10 +354,9 @@ __global__ void __launch_bounds__(576, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kern
       for (int r = 0; r < 8; r++) pa[r] = r < GMAX ? acc[r < GMAX ? r : 0][b] : 0.0f;
       const float y = warp_sum8(pa);
       const float yup = __shfl_xor_sync(0xffffffffu, y, 4);  // the odd neighbour row (the "up" row of a SwiGLU pair)
-      if (mine && !(sg.epi == BK_EPI_SWIGLU && (ri & 1))) store_epilogue(p, sg, (size_t)b * sg.ld_out + sg.col_off + vr.n, y, yup);
+      if (mine && !(sg.epi == BK_EPI_SWIGLU && (ri & 1))) store_epilogue<TP>(p, sg, (size_t)b * sg.ld_out + sg.col_off + vr.n, y, yup);
     }
   }
-  if (p.push.n) bk_push_signal(p.push.cnt, p.push.n);
   bk_stamp(p.trace, 5);
   bk_stamp_max(p.trace, 6);  // latest exit over all warps of all CTAs
   if (ctr) bk_stamp_max(ctr, 3);
@@ -339,14 +368,14 @@ size_t gemv_fixed_smem(int K, int B, int n_slots) {
   return (size_t)B * nunits * kUnitWords * 4 + (size_t)B * nblk * 8 + 8 * 4 + (size_t)n_slots * 8 + 128;
 }
 
-template <int B, int GMAX>
+template <int B, int GMAX, bool TP>
 int32_t launch_gemv(const GemvParams& p, int grid, int threads, size_t smem) {
   static size_t configured = 0;
   if (smem > configured) {
-    BK_CUDA((cudaFuncSetAttribute(gemv_q4k_kernel<B, GMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)));
+    BK_CUDA((cudaFuncSetAttribute(gemv_q4k_kernel<B, GMAX, TP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)));
     configured = smem;
   }
-  BK_CUDA((bk_launch_pdl(gemv_q4k_kernel<B, GMAX>, dim3(grid), dim3(threads), smem, p)));
+  BK_CUDA((bk_launch_pdl(gemv_q4k_kernel<B, GMAX, TP>, dim3(grid), dim3(threads), smem, p)));
   BK_CHECK_LAUNCH();
   return BK_OK;
 }
@@ -627,10 +656,10 @@ int32_t bk_gemv_launch_tp(const bkGemvArgs& a, const BkPush* push, const BkReduc
     }
   }
   if (ctas_out) *ctas_out = grid;
-  switch (a.B) {
-    case 1: return launch_gemv<1, gemv_gmax(1)>(p, grid, threads, smem);
-    default: return launch_gemv<2, gemv_gmax(2)>(p, grid, threads, smem);   // batch 2 only when K is too wide for the tensor-core path
-  }
+  const bool tp = p.push.n > 0 || p.red.n > 0;
+  if (a.B == 1) return tp ? launch_gemv<1, gemv_gmax(1), true>(p, grid, threads, smem) : launch_gemv<1, gemv_gmax(1), false>(p, grid, threads, smem);
+  // batch 2 only when K is too wide for the tensor-core path
+  return tp ? launch_gemv<2, gemv_gmax(2), true>(p, grid, threads, smem) : launch_gemv<2, gemv_gmax(2), false>(p, grid, threads, smem);
 }
 
 extern "C" {

@@ -105,7 +105,6 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
   bk_pdl_wait();
   bk_stamp(p.trace, 2);
 
-  if (p.push.n && blockIdx.x == 0 && tid < p.push.reset_n) p.push.reset[tid] = 0;
   if (p.prologue == BK_PRO_STAGED) {
     // the producer wrote exactly the bytes of xs | sc4: one bulk copy, nothing to compute
     if (tid == 0) {
@@ -236,7 +235,6 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
       }
     }
   }
-  if (p.push.n) bk_push_signal(p.push.cnt, p.push.n);
   bk_stamp(p.trace, 5);
   bk_stamp_max(p.trace, 6);
 }

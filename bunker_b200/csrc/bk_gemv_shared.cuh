@@ -147,19 +147,28 @@ __device__ __forceinline__ void load_chunk_bf16(const uint16_t* row, int q, floa
   y[7] = __uint_as_float(v.w & 0xffff0000u);
 }
 
-// chunk q (8 values) of batch row b: from the bf16 row, or (REDUCE) from the ranks' partial sums + residual
-template <bool REDUCE>
+// chunk q (8 values) of batch row b.  SRC 0: from the bf16 row.  SRC 1: from the ranks' partial sums + residual
+// (tensor-parallel reduce; also writes the bf16 result to p.red.out).  SRC 2: from p.red.out as written by CTA 0 of
+// this same launch (L2 loads: the L1 of this SM knows nothing of another CTA's stores).
+template <int SRC>
 __device__ __forceinline__ void load_chunk_in(const GemvParams& p, const uint16_t* row, int b, int q, float (&y)[8]) {
-  if (REDUCE) bk_reduce_load8(p.red.src, p.red.stride, p.red.n, p.red.res, p.red.out, (size_t)b * p.K + (size_t)q * 8, blockIdx.x == 0, y);
+  if (SRC == 2) {
+    const uint4 v = __ldcg(reinterpret_cast<const uint4*>(p.red.out + (size_t)b * p.K) + q);
+    y[0] = __uint_as_float(v.x << 16); y[1] = __uint_as_float(v.x & 0xffff0000u);
+    y[2] = __uint_as_float(v.y << 16); y[3] = __uint_as_float(v.y & 0xffff0000u);
+    y[4] = __uint_as_float(v.z << 16); y[5] = __uint_as_float(v.z & 0xffff0000u);
+    y[6] = __uint_as_float(v.w << 16); y[7] = __uint_as_float(v.w & 0xffff0000u);
+  } else if (SRC == 1) bk_reduce_load8(p.red.src, p.red.stride, p.red.n, bk_exchange_tag(p.red.epoch, p.red.tag_add), p.red.res, p.red.out,
+                              (size_t)b * p.K + (size_t)q * 8, true, p.status, y);
   else load_chunk_bf16(row, q, y);
 }
 
 // bf16 rows -> (optional RMSNorm -> bf16) -> Q8_1 in shared memory.
-// REDUCE: the row is not read from p.x but formed from the tensor-parallel partial sums (see BkReduce).
+// SRC: where the row comes from (see load_chunk_in).
 // Sum of squares in the 256-thread block order: chunk q (8 elements) belongs to
 // thread q mod 256, fmaf chain inside; warp butterflies; the 8 warp sums in order.
 // wpre: the norm weights of chunk threadIdx.x, loaded by the caller before the dependency wait.
-template <bool NORM, bool REDUCE = false>
+template <bool NORM, int SRC = 0>
 __device__ void prologue_bf16(const GemvParams& p, const int B, uint32_t* xs, float* d8s, float* s8s, float* red, const uint4 wpre) {
   const int K = p.K, nblk = K / 32, nchunk = K / 8;
   const uint16_t* x = reinterpret_cast<const uint16_t*>(p.x);
@@ -170,7 +179,7 @@ __device__ void prologue_bf16(const GemvParams& p, const int B, uint32_t* xs, fl
     float rstd = 1.0f;
     float y0[8];
     const bool have0 = (int)threadIdx.x < nchunk;
-    if (have0) load_chunk_in<REDUCE>(p, row, b, threadIdx.x, y0);
+    if (have0) load_chunk_in<SRC>(p, row, b, threadIdx.x, y0);
     if (NORM) {
       float acc = 0.0f;
       if (threadIdx.x < kThreads) {  // the fixed 256-thread order, whatever the CTA size
@@ -180,7 +189,7 @@ __device__ void prologue_bf16(const GemvParams& p, const int B, uint32_t* xs, fl
         }
         for (int q = threadIdx.x + kThreads; q < nchunk; q += kThreads) {
           float y[8];
-          load_chunk_in<REDUCE>(p, row, b, q, y);
+          load_chunk_in<SRC>(p, row, b, q, y);
 #pragma unroll
           for (int e = 0; e < 8; e++) acc = fmaf(y[e], y[e], acc);
         }
@@ -201,7 +210,7 @@ __device__ void prologue_bf16(const GemvParams& p, const int B, uint32_t* xs, fl
 #pragma unroll
         for (int e = 0; e < 8; e++) y[e] = y0[e];
       } else {
-        load_chunk_in<REDUCE>(p, row, b, q, y);
+        load_chunk_in<SRC>(p, row, b, q, y);
       }
       if (NORM) {
         float wv[8];
@@ -346,9 +355,11 @@ BK_DEVINL void mbar_wait_bounded(uint32_t bar, uint32_t parity, int* status) {
   if (status) atomicExch(status, BK_ERR_TIMEOUT);
 }
 
+template <bool TP = true>
 __device__ __forceinline__ void store_epilogue(const GemvParams& p, const SegDev& sg, size_t o, float y, float yup) {
-  if (sg.epi == BK_EPI_PUSH_F32) {
-    for (int r = 0; r < p.push.n; r++) p.push.dst[r][o] = y;   // remote stores over NVLink, fire and forget
+  if (TP && sg.epi == BK_EPI_PUSH_F32) {
+    const unsigned int tag = bk_exchange_tag(p.push.epoch, p.push.tag_add);
+    for (int r = 0; r < p.push.n; r++) bk_push_store(p.push.dst[r] + o, y, tag);   // remote stores over NVLink, fire and forget
   } else if (sg.epi == BK_EPI_SWIGLU) {
     float sig = bk_sigmoidf(y);
     reinterpret_cast<uint16_t*>(sg.out)[o] = bk_f32_to_bf16(__fmul_rn(__fmul_rn(y, sig), yup));

@@ -66,27 +66,31 @@ static inline T* bk_ptr(uint64_t p) { return reinterpret_cast<T*>(static_cast<ui
 
 // ---- tensor-parallel exchange fused into the GEMV (descriptors filled by bk_comm.cu) --------------------
 // Push: a row-parallel GEMV stores its f32 partial result into the exchange region of EVERY rank (its own included)
-// and, when a CTA is done, adds 1 to that CTA's arrival counter on every rank (release, system scope).
-// Reduce: the consumer (the next projection's prologue, or the norm+quantise launch at batch >= 2) waits until every
-// rank's counter shows all CTAs of the producing launch, then sums the partials from LOCAL memory in rank order,
-// adds the residual, rounds to bf16 once.  Two slots alternate; a push launch zeroes the other slot's local counters.
+// as 8-byte words {value, tag}: an aligned 8-byte store arrives whole, so a reader that sees the tag has the value --
+// no fence, flag or counter, one NVLink store latency.  (Forwarding from the reducer instead of pushing from the GEMV
+// epilogue was measured slower: the words leave later, and the reducer's successor still waits for the acknowledgement
+// of the remote stores before the grid counts as complete.)  tag = epoch*256 + index of the exchange in the step + 1;
+// the epoch is a device word every rank advances once per step, so a tag never repeats in a slot.
+// Reduce: the consumer (the next projection's prologue, or the norm+quantise launch at batch >= 2) polls -- bounded --
+// the words it needs in LOCAL memory, sums the partials in rank order, adds the residual, rounds to bf16 once.
+// Two slots alternate so that a rank running ahead cannot overwrite words a slower rank has not read yet.
 #define BK_EPI_PUSH_F32 4        /* internal epilogue: f32 partial pushed to all ranks */
 #define BK_PRO_REDUCE_RMSNORM 4  /* internal prologue: reduce + residual -> bf16 -> RMSNorm -> Q8_1 */
 struct BkPush {
-  float* dst[8];
-  unsigned int* cnt[8];
-  unsigned int* reset;   // local counters to zero (the other slot's), reset_n of them
-  int n;                 // ranks; 0 = no push
-  int reset_n;
+  uint2* dst[8];               // [r]: rank r's region for this rank's {value, tag} words
+  const unsigned int* epoch;   // local step counter
+  unsigned int tag_add;        // index of the exchange in the step + 1
+  int n;                       // ranks; 0 = no push
 };
 struct BkReduce {
-  const float* src;            // local region [n][stride] f32
-  const unsigned int* cnt;     // local arrival counters [n]
+  const uint2* src;            // local region [n][stride] {value, tag} words
+  const unsigned int* epoch;
   const uint16_t* res;         // residual bf16, same indexing as the partials
   uint16_t* out;               // sum + residual as bf16 (materialised for later residual adds)
-  unsigned long long stride;   // floats between ranks' partials
-  unsigned int expected;       // arrivals per rank
+  unsigned long long stride;   // words between ranks' partials
+  unsigned int tag_add;
   int n;                       // ranks; 0 = no reduce
+  unsigned int* ready;         // local word: CTA 0 of a reducing GEMV stores the tag here once `out` is complete
 };
 
 // internal launchers shared between translation units
@@ -127,8 +131,9 @@ inline unsigned long long* bk_trace_slot() {
 
 // tensor-parallel exchange (bk_comm.cu)
 uint64_t bk_comm_slot_ptr(uint64_t comm, int slot);
-int32_t bk_comm_push_desc(uint64_t comm, int slot, BkPush* out);       // slot 0 or 1 of the push region
-int32_t bk_comm_reduce_desc(uint64_t comm, int slot, BkReduce* out);   // src/cnt/stride/n filled in
+int32_t bk_comm_push_desc(uint64_t comm, int slot, BkPush* out);       // slot 0 or 1 of the push region; tag_add left 0
+int32_t bk_comm_reduce_desc(uint64_t comm, int slot, BkReduce* out);   // src/epoch/stride/n filled in
+uint64_t bk_comm_epoch_ptr(uint64_t comm);                             // device word to advance once per step
 int32_t bk_comm_allreduce_residual(uint64_t comm, int slot, int n, uint64_t residual, uint64_t out);
 int32_t bk_comm_argmax_merge(uint64_t comm, int slot, int B, uint64_t local_val, uint64_t local_idx, int offset, uint64_t idx,
                              uint64_t val, uint64_t pos, uint64_t hist, int hist_ld, int hist_rows);

@@ -140,7 +140,8 @@ int32_t enqueue_step(Model& m, int parity) {
   // normalises and quantises the rows once and every CTA of the projection just copies the blocks.
   // Tensor parallel: a row-parallel GEMV pushes its partial sums to every rank (BK_EPI_PUSH_F32); the sum over ranks,
   // the residual add and the bf16 rounding happen in the prologue of whatever reads the result next (`pending`).
-  struct Pending { bool on; int slot; int ctas; uint64_t res, out; } pending = {false, 0, 0, 0, 0};
+  struct Pending { bool on; int slot; unsigned int tag_add; uint64_t res, out; } pending = {false, 0, 0, 0, 0};
+  unsigned int n_exchanges = 0;   // fused exchanges enqueued so far in this step
   BkReduce red_desc;
   bool use_red = false;   // the GEMV being set up carries the reduce prologue (batch 1)
   auto set_input = [&](bkGemvArgs& g, uint64_t x, int K, uint64_t norm_w) -> int32_t {
@@ -151,7 +152,7 @@ int32_t enqueue_step(Model& m, int parity) {
       TRY(bk_comm_reduce_desc(m.comm, pending.slot, &red_desc));
       red_desc.res = bk_ptr<uint16_t>(pending.res);
       red_desc.out = bk_ptr<uint16_t>(pending.out);
-      red_desc.expected = (unsigned int)pending.ctas;
+      red_desc.tag_add = pending.tag_add;
       pending.on = false;
     }
     if (q8_handoff) {
@@ -170,10 +171,11 @@ int32_t enqueue_step(Model& m, int parity) {
   auto launch_push = [&](bkGemvArgs& g, uint64_t W, int slot, uint64_t res, uint64_t out) -> int32_t {
     BkPush ps;
     TRY(bk_comm_push_desc(m.comm, slot, &ps));
+    ps.tag_add = ++n_exchanges;
+    BK_ARG(n_exchanges < 256, "decode step: more than 255 tensor-parallel exchanges");
     g.segs[0] = bkGemvSeg{W, 0, 0, 0, H, BK_EPI_PUSH_F32, H, 0};
-    int ctas = 0;
-    TRY(bk_gemv_launch_tp(g, &ps, use_red ? &red_desc : nullptr, &ctas));
-    pending = Pending{true, slot, ctas, res, out};
+    TRY(bk_gemv_launch_tp(g, &ps, use_red ? &red_desc : nullptr, nullptr));
+    pending = Pending{true, slot, ps.tag_add, res, out};
     return BK_OK;
   };
   PROF(PC_EMBED, bkEmbedQ4K(m.embed, H, m.ids, B, m.x[0]));

@@ -107,10 +107,10 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const uint16_t* x, cons
     float wv0[8];
     const bool have0 = tid < nchunk;
     if (have0) load8_bf16(w + (size_t)tid * 8, wv0);
-    bk_pdl_wait();
-    if (rd.n) bk_reduce_wait(rd.cnt, rd.n, rd.expected, status);
+    if (!rd.n) bk_pdl_wait();   // a reducing launch synchronises through the tagged words instead (see gemv_q4k_kernel)
+    const unsigned int tag = rd.n ? bk_exchange_tag(rd.epoch, rd.tag_add) : 0u;
     auto load_in = [&](int q, float (&y)[8]) {
-      if (rd.n) bk_reduce_load8(rd.src, rd.stride, rd.n, rd.res, rd.out, (size_t)b * K + (size_t)q * 8, true, y);
+      if (rd.n) bk_reduce_load8(rd.src, rd.stride, rd.n, tag, rd.res, rd.out, (size_t)b * K + (size_t)q * 8, true, status, y);
       else load8_bf16(row + (size_t)q * 8, y);
     };
     float y0[8];
