@@ -199,38 +199,42 @@ BK_DEVINL uint4 bk_ld_volatile_v4(const uint2* p) {
   asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;
 }
-// four 16-byte loads = 8 {value, tag} words (each half carries its own tag); polls until all tags show.
-// Bounded: on timeout *status is set and whatever is there is used.
-BK_DEVINL void bk_pull8(const uint2* s, unsigned int tag, int* status, uint4 (&w)[4]) {
-  for (int it = 0;; it++) {
-#pragma unroll
-    for (int k = 0; k < 4; k++) w[k] = bk_ld_volatile_v4(s + 2 * k);
-    bool ok = true;
-#pragma unroll
-    for (int k = 0; k < 4; k++) ok = ok && w[k].y == tag && w[k].w == tag;
-    if (ok) break;
-    if (it > (1 << 20) || (status && (it & 255) == 255 && *reinterpret_cast<volatile int*>(status) != 0)) {
-      if (status) atomicExch(status, 10003 /* BK_ERR_TIMEOUT */);
-      break;
-    }
-  }
-}
 // 8 consecutive values at element offset o (a multiple of 8): ((p0 + p1) + ...) + residual, rounded to bf16 (returned
-// as f32); the ranks' words are polled in rank order.
+// as f32).  Two ranks are polled per pass so that their loads are in flight together; sums stay in rank order.
 BK_DEVINL void bk_reduce_load8(const uint2* src, unsigned long long stride, int n, unsigned int tag, const uint16_t* res,
                                uint16_t* out, size_t o, bool write_out, int* status, float (&y)[8]) {
   float a[8];
-  for (int r = 0; r < n; r++) {
-    uint4 w[4];
-    bk_pull8(src + r * stride + o, tag, status, w);
+  for (int r = 0; r < n; r += 2) {
+    const bool two = r + 1 < n;
+    const uint2* s0 = src + r * stride + o;
+    const uint2* s1 = s0 + (two ? stride : 0);
+    uint4 w0[4], w1[4];
+    for (int it = 0;; it++) {
+#pragma unroll
+      for (int k = 0; k < 4; k++) w0[k] = bk_ld_volatile_v4(s0 + 2 * k);
+#pragma unroll
+      for (int k = 0; k < 4; k++) w1[k] = bk_ld_volatile_v4(s1 + 2 * k);
+      bool ok = true;
+#pragma unroll
+      for (int k = 0; k < 4; k++) ok = ok && w0[k].y == tag && w0[k].w == tag && w1[k].y == tag && w1[k].w == tag;
+      if (ok) break;
+      if (it > (1 << 20) || (status && (it & 255) == 255 && *reinterpret_cast<volatile int*>(status) != 0)) {
+        if (status) atomicExch(status, 10003 /* BK_ERR_TIMEOUT */);
+        break;
+      }
+    }
 #pragma unroll
     for (int k = 0; k < 4; k++) {
       if (r == 0) {
-        a[2 * k] = __uint_as_float(w[k].x);
-        a[2 * k + 1] = __uint_as_float(w[k].z);
+        a[2 * k] = __uint_as_float(w0[k].x);
+        a[2 * k + 1] = __uint_as_float(w0[k].z);
       } else {
-        a[2 * k] = __fadd_rn(a[2 * k], __uint_as_float(w[k].x));
-        a[2 * k + 1] = __fadd_rn(a[2 * k + 1], __uint_as_float(w[k].z));
+        a[2 * k] = __fadd_rn(a[2 * k], __uint_as_float(w0[k].x));
+        a[2 * k + 1] = __fadd_rn(a[2 * k + 1], __uint_as_float(w0[k].z));
+      }
+      if (two) {
+        a[2 * k] = __fadd_rn(a[2 * k], __uint_as_float(w1[k].x));
+        a[2 * k + 1] = __fadd_rn(a[2 * k + 1], __uint_as_float(w1[k].z));
       }
     }
   }
