@@ -491,6 +491,8 @@ __global__ void quant_q8_1_kernel(const void* x, int K, int B, uint8_t* out) {
 
 int32_t bk_gemv_mma_launch(void* params, int K, int B, int vrows, bool has_swiglu, int* ctas_out);  // bk_gemv_mma.cu
 
+static int g_tune_warps = 0, g_tune_rows = 0, g_tune_depth = 0;
+
 int32_t bk_gemv_launch(const bkGemvArgs& a) { return bk_gemv_launch_tp(a, nullptr, nullptr, nullptr); }
 
 int32_t bk_gemv_launch_tp(const bkGemvArgs& a, const BkPush* push, const BkReduce* reduce, int* ctas_out) {
@@ -620,20 +622,33 @@ int32_t bk_gemv_launch_tp(const bkGemvArgs& a, const BkPush* push, const BkReduc
   int depth = 0, n_slots = n_groups;
   const size_t half = limit / 2;
   if (gemv_fixed_smem(a.K, a.B, n_groups) + (size_t)n_groups * G * rowb > half + 8 * 1024) {
+    // Ring: the CTA's rows do not fit at once.  Measured on K = 2048 ... 17408: 16 warps with as many rows per group as
+    // fit beat fewer warps with wider groups (more independent copy/compute chains); single-row groups take 18 warps.
+    const int min_g = has_swiglu ? 2 : 1, step_g = has_swiglu ? 2 : 1;
+    nw = 16;
+    G = (rpc + nw - 1) / nw;
+    if (has_swiglu) G = (G + 1) & ~1;
+    if (G > gmax) G = gmax;
+    if (G < min_g) G = min_g;
+    while (G > min_g && gemv_fixed_smem(a.K, a.B, nw * 8) + (size_t)nw * G * rowb > limit) G -= step_g;
+    if (G == 1 && gemv_fixed_smem(a.K, a.B, 18 * 8) + (size_t)18 * rowb <= limit) nw = 18;
+    while (nw > 8 && gemv_fixed_smem(a.K, a.B, nw * 8) + (size_t)nw * G * rowb > limit) nw -= 2;
     size_t per_level = (size_t)nw * G * rowb;
-    while (nw > 8 && gemv_fixed_smem(a.K, a.B, nw * 8) + per_level > limit) {
-      nw = 8;
-      per_level = (size_t)nw * G * rowb;
-    }
-    while (G > (has_swiglu ? 2 : 1) && gemv_fixed_smem(a.K, a.B, nw * 8) + per_level > limit) {
-      G = has_swiglu ? ((G / 2 + 1) & ~1) : (G + 1) / 2;
-      if (has_swiglu && G < 2) G = 2;
-      per_level = (size_t)nw * G * rowb;
-    }
-    const size_t fixed = gemv_fixed_smem(a.K, a.B, nw * 8);
+    size_t fixed = gemv_fixed_smem(a.K, a.B, nw * 8);
     BK_ARG(fixed + per_level <= limit, "bkGemvQ4K: K=%d B=%d does not fit in shared memory", a.K, a.B);
     n_groups = (rpc + G - 1) / G;
     depth = (int)((limit - fixed) / per_level);
+    if (g_tune_warps > 0 && g_tune_rows > 0) {   // bkTuneGemvRing: measurement aid
+      nw = g_tune_warps;
+      G = g_tune_rows;
+      if (has_swiglu) G = (G + 1) & ~1;
+      per_level = (size_t)nw * G * rowb;
+      fixed = gemv_fixed_smem(a.K, a.B, nw * 8);
+      BK_ARG(fixed + per_level <= limit, "bkTuneGemvRing: %d warps x %d rows of K=%d do not fit in shared memory", nw, G, a.K);
+      n_groups = (rpc + G - 1) / G;
+      depth = (int)((limit - fixed) / per_level);
+      if (g_tune_depth > 0 && depth > g_tune_depth) depth = g_tune_depth;
+    }
     const int max_depth = (n_groups + nw - 1) / nw;
     if (depth > max_depth) depth = max_depth;
     if (depth > 8) depth = 8;
@@ -663,6 +678,14 @@ int32_t bk_gemv_launch_tp(const bkGemvArgs& a, const BkPush* push, const BkReduc
 }
 
 extern "C" {
+
+int32_t bkTuneGemvRing(int32_t warps, int32_t rows_per_group, int32_t max_depth) {
+  BK_ARG(warps == 0 || (warps >= 8 && warps <= 18 && rows_per_group >= 1 && rows_per_group <= 8), "bkTuneGemvRing: bad shape");
+  g_tune_warps = warps;
+  g_tune_rows = rows_per_group;
+  g_tune_depth = max_depth;
+  return BK_OK;
+}
 
 int32_t bkGemvQ4K(const bkGemvArgs* args) {
   BK_REQUIRE_INIT();

@@ -62,11 +62,11 @@ class ModelConfig:
         return ModelConfig(**d)
 
 
-# BASELINE configs[3]: hidden 2048, 24 layers [GDN,GDN,GDN,attn]x6, 16/32 GDN heads, 16/2 attention heads,
+# the 24-layer benchmark configuration: hidden 2048, 24 layers [GDN,GDN,GDN,attn]x6, 16/32 GDN heads, 16/2 attention heads,
 # FFN 6144, vocabulary 151936, tied embedding
 CONFIG_HYBRID_24L = ModelConfig(hidden=2048, n_layers=24, vocab=151936, gdn_k_heads=16, gdn_v_heads=32,
                                 attn_q_heads=16, attn_kv_heads=2, intermediate=6144, name="hybrid-24L-2048")
-# BASELINE configs[4]: hidden 5120, 64 layers, 16/48 GDN heads, 24/4 attention heads, FFN 17408
+# the scaled 64-layer configuration: hidden 5120, 64 layers, 16/48 GDN heads, 24/4 attention heads, FFN 17408
 CONFIG_HYBRID_64L = ModelConfig(hidden=5120, n_layers=64, vocab=151936, gdn_k_heads=16, gdn_v_heads=48,
                                 attn_q_heads=24, attn_kv_heads=4, intermediate=17408, max_len=4096,
                                 name="hybrid-64L-5120")
@@ -151,7 +151,7 @@ def split_counts(total: int, n: int) -> list[int]:
 
 
 def local_dims(cfg: ModelConfig, rank: int, n: int) -> dict:
-    """Shard shapes of one tensor-parallel rank (SURVEY 8e: heads per rank, KV heads split or replicated,
+    """Shard shapes of one tensor-parallel rank (heads per rank, KV heads split or replicated,
     row-parallel K slices in whole superblocks)."""
     assert cfg.gdn_k_heads % n == 0 and cfg.gdn_v_heads % n == 0 and cfg.attn_q_heads % n == 0
     hkv = cfg.attn_kv_heads

@@ -112,6 +112,7 @@ SIGNATURES = {
     "bkRmsNorm": (_I32, [_U64, _U64, _I32, _I32, _F32, _U64]),
     "bkRmsNormQuantQ8_1": (_I32, [_U64, _U64, _I32, _I32, _F32, _U64, _I32]),
     "bkStagedBytes": (_U64, [_I32, _I32]),
+    "bkTuneGemvRing": (_I32, [_I32, _I32, _I32]),
     "bkSwiglu": (_I32, [_U64, _U64, _I32, _U64]),
     "bkConv1dStep": (_I32, [_U64, _U64, _U64, _I32, _I32, _U64, _U64]),
     "bkGdnStep": (_I32, [C.POINTER(bkGdnArgs)]),

@@ -134,6 +134,10 @@ typedef struct bkGemvArgs {
 } bkGemvArgs;
 
 BK_API int32_t bkGemvQ4K(const bkGemvArgs* args);
+/* Measurement aid, no counterpart in the reference: force the batch-1 kernel's weight ring (warps per CTA, rows per
+ * warp group, maximum ring depth) for launches whose rows do not fit in shared memory at once; warps = 0 restores the
+ * library's own choice. */
+BK_API int32_t bkTuneGemvRing(int32_t warps, int32_t rows_per_group, int32_t max_depth);
 /* config-0 convenience: y f32 [B][N] = W[N][K] (Q4_K) x xq (Q8_1 blocks) */
 BK_API int32_t bkGemvQ4KSimple(uint64_t W, int32_t N, int32_t K, uint64_t xq, int32_t B, uint64_t y);
 
