@@ -480,8 +480,7 @@ int32_t bkAttnDecode(const bkAttnArgs* args) {
   p.out = bk_ptr<uint16_t>(a.out);
   p.out_q8 = bk_ptr<uint8_t>(a.out_q8);
   p.out_q8_staged = a.out_q8_layout == BK_Q8_STAGED;
-  BK_ARG(a.out_q8_layout == BK_Q8_BLOCKS || (a.out_q8_layout == BK_Q8_STAGED && a.B <= 8),
-         "bkAttnDecode: out_q8_layout %d (a staged image needs B <= 8)", a.out_q8_layout);
+  BK_ARG(a.out_q8_layout == BK_Q8_BLOCKS || a.out_q8_layout == BK_Q8_STAGED, "bkAttnDecode: out_q8_layout %d", a.out_q8_layout);
   p.scratch = bk_ptr<float>(a.scratch);
   p.gate = bk_ptr<uint16_t>(a.gate);
   p.B = a.B;

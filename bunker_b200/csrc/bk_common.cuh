@@ -257,11 +257,24 @@ BK_DEVINL void bk_reduce_load8(const uint2* src, unsigned long long stride, int 
 //   float4 [K/64][8]      per 64-value unit u and column b: {d8 of block 2u, d8 of block 2u+1 / 16,
 //                          s8 of 2u, s8 of 2u+1}, d8 = the block scale after its f16 round trip, s8 = d8 * sum(q)
 __host__ __device__ __forceinline__ size_t bk_staged_row_words(int K) { return (size_t)K / 4 + 8; }
+// More than 8 batch rows: one image per group of 8 rows (the last group may be smaller), each at a stride of the
+// 8-row image size; the GEMV then runs once per group.
+__host__ __device__ __forceinline__ size_t bk_staged_group_stride(int K) { return (size_t)8 * bk_staged_row_words(K) * 4 + (size_t)(K / 64) * 8 * 16; }
+__host__ __device__ __forceinline__ size_t bk_staged_total_bytes(int K, int B);
 __host__ __device__ __forceinline__ size_t bk_staged_bytes(int K, int B) { return (size_t)B * bk_staged_row_words(K) * 4 + (size_t)(K / 64) * 8 * 16; }
 
-// Same contract as bk_q8_1_store, writing block blk of column b into a staged image.
+__host__ __device__ __forceinline__ size_t bk_staged_total_bytes(int K, int B) {
+  return B <= 8 ? bk_staged_bytes(K, B) : (size_t)((B + 7) / 8) * bk_staged_group_stride(K);
+}
+
+// Same contract as bk_q8_1_store, writing block blk of column b into a staged image (grouped when B > 8).
 template <int PER>
 BK_DEVINL void bk_staged_store(uint8_t* img, int K, int B, int b, int blk, const float (&y)[PER], int idx_in_block) {
+  if (B > 8) {
+    img += (size_t)(b >> 3) * bk_staged_group_stride(K);
+    B = min(8, B - (b & ~7));
+    b &= 7;
+  }
   constexpr int GROUP = 32 / PER;
   float amax = 0.0f;
 #pragma unroll

@@ -194,6 +194,7 @@ __device__ __forceinline__ int slot_row(bool swiglu, int r, int nr) { return swi
 // register allocation they would disturb).
 template <int B, int GMAX, bool TP>
 __global__ void __launch_bounds__(576, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kernel(const GemvParams p) {
+  static_assert(B <= 2, "batch >= 3 runs on the tensor-core kernel (bk_gemv_mma.cu) or as column pairs of this one");
   bk_pdl_trigger();
   bk_stamp(p.trace, 0);
   unsigned long long* ctr = p.cta_trace ? p.cta_trace + 4 * blockIdx.x : nullptr;
@@ -309,27 +310,16 @@ __global__ void __launch_bounds__(576, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kern
       for (int b = 0; b < B; b++) acc[r][b] = 0.0f;
     for (int u = lane; u < nunits; u += 32) {
       const int pp = u & 3;
-      if constexpr (B <= 2) {
-        // few columns: the activation of this unit stays in registers across the G rows
-        XRegs xr[B];
+      // one or two columns: the activation of this unit stays in registers across the G rows
+      XRegs xr[B];
 #pragma unroll
-        for (int b = 0; b < B; b++) xr[b] = load_x(xs, d8s, s8s, b, u, nunits, nblk);
+      for (int b = 0; b < B; b++) xr[b] = load_x(xs, d8s, s8s, b, u, nunits, nblk);
 #pragma unroll
-        for (int r = 0; r < GMAX; r++) {
-          if (r < nr) {
-            const WRegs w = decode_unit(load_unit_smem(wbase + slot_row(swiglu, r, nr) * rowb, u), pp);
+      for (int r = 0; r < GMAX; r++) {
+        if (r < nr) {
+          const WRegs w = decode_unit(load_unit_smem(wbase + slot_row(swiglu, r, nr) * rowb, u), pp);
 #pragma unroll
-            for (int b = 0; b < B; b++) acc[r][b] = __fadd_rn(acc[r][b], unit_val(w, xr[b]));
-          }
-        }
-      } else {
-#pragma unroll
-        for (int r = 0; r < GMAX; r++) {
-          if (r < nr) {
-            const WRegs w = decode_unit(load_unit_smem(wbase + slot_row(swiglu, r, nr) * rowb, u), pp);
-#pragma unroll
-            for (int b = 0; b < B; b++) acc[r][b] = __fadd_rn(acc[r][b], unit_val(w, load_x(xs, d8s, s8s, b, u, nunits, nblk)));
-          }
+          for (int b = 0; b < B; b++) acc[r][b] = __fadd_rn(acc[r][b], unit_val(w, xr[b]));
         }
       }
     }
@@ -381,7 +371,7 @@ int32_t launch_gemv(const GemvParams& p, int grid, int threads, size_t smem) {
 }
 
 // widest row group the register budget of batch B allows
-constexpr int gemv_gmax(int B) { return B <= 2 ? 8 : 4; }
+constexpr int gemv_gmax(int) { return 8; }
 
 // ---- dequant / block-dot check kernels ---------------------------------------
 
@@ -493,12 +483,49 @@ int32_t bk_gemv_mma_launch(void* params, int K, int B, int vrows, bool has_swigl
 
 static int g_tune_warps = 0, g_tune_rows = 0, g_tune_depth = 0;
 
+// K view of the launch being set up by the split-K driver below (null otherwise)
+struct KView {
+  unsigned int row_stride, row_off;
+  int xq_ld, xq_off;
+  const float* carry_in;
+  float* carry_out;
+};
+static const KView* g_view = nullptr;
+
 int32_t bk_gemv_launch(const bkGemvArgs& a) { return bk_gemv_launch_tp(a, nullptr, nullptr, nullptr); }
 
 int32_t bk_gemv_launch_tp(const bkGemvArgs& a, const BkPush* push, const BkReduce* reduce, int* ctas_out) {
   BkContext& c = bk_ctx();
   BK_ARG(a.K > 0 && a.K % 256 == 0, "bkGemvQ4K: K=%d is not a positive multiple of 256", a.K);
-  BK_ARG(a.B >= 1 && a.B <= 8, "bkGemvQ4K: B=%d outside 1..8", a.B);
+  BK_ARG(a.B >= 1 && a.B <= 64, "bkGemvQ4K: B=%d outside 1..64", a.B);
+  if (a.B > 8) {
+    // More than 8 columns: groups of 8 on the tensor-core kernel, one launch per group (the weights of the later
+    // groups come from L2 when they fit there).  A dense tile kernel for batch >= 16 does not exist in this library.
+    BK_ARG(a.prologue != BK_PRO_REDUCE_RMSNORM, "bkGemvQ4K: the reduce prologue is a batch-1 path");
+    if (ctas_out) *ctas_out = 0;
+    for (int b0 = 0; b0 < a.B; b0 += 8) {
+      bkGemvArgs s = a;
+      s.B = a.B - b0 < 8 ? a.B - b0 : 8;
+      if (a.prologue == BK_PRO_STAGED) s.x = a.x + (uint64_t)(b0 / 8) * bk_staged_group_stride(a.K);
+      else s.x = a.x + (uint64_t)b0 * (a.prologue == BK_PRO_Q8 ? (uint64_t)(a.K / 32) * 36 : (uint64_t)a.K * 2);
+      if (s.B == 1 && a.prologue == BK_PRO_STAGED) return bk_fail(BK_ERR_ARG, "bkGemvQ4K: a staged activation cannot end in a group of one column (B=%d)", a.B);
+      BkPush ps;
+      if (push) {
+        ps = *push;
+        for (int r = 0; r < ps.n; r++) ps.dst[r] += (size_t)b0 * a.segs[0].ld_out;
+      }
+      for (int i = 0; i < a.n_segs && i < 4; i++) {
+        const uint64_t esz = a.segs[i].epilogue == BK_EPI_F32 ? 4 : 2;
+        if (a.segs[i].out) s.segs[i].out = a.segs[i].out + (uint64_t)b0 * a.segs[i].ld_out * esz;
+        if (a.segs[i].residual) s.segs[i].residual = a.segs[i].residual + (uint64_t)b0 * a.segs[i].ld_out * 2;
+      }
+      int ctas = 0;
+      const int32_t rc = bk_gemv_launch_tp(s, push ? &ps : nullptr, nullptr, &ctas);
+      if (rc != BK_OK) return rc;
+      if (ctas_out) *ctas_out += ctas;
+    }
+    return BK_OK;
+  }
   BK_ARG(a.n_segs >= 1 && a.n_segs <= 4, "bkGemvQ4K: n_segs=%d outside 1..4", a.n_segs);
   BK_ARG((a.prologue >= BK_PRO_Q8 && a.prologue <= BK_PRO_STAGED) || (a.prologue == BK_PRO_REDUCE_RMSNORM && reduce && reduce->n > 0),
          "bkGemvQ4K: unknown prologue %d", a.prologue);
@@ -510,7 +537,46 @@ int32_t bk_gemv_launch_tp(const bkGemvArgs& a, const BkPush* push, const BkReduc
   BK_ARG(a.x != 0 && (a.x & 15) == 0, "bkGemvQ4K: x must be a non-null 16-byte aligned device pointer");
   if (a.prologue == BK_PRO_RMSNORM || a.prologue == BK_PRO_REDUCE_RMSNORM)
     BK_ARG(a.norm_w != 0 && (a.norm_w & 15) == 0, "bkGemvQ4K: norm_w must be non-null and 16-byte aligned");
-  if (a.B >= 3 && !bk_gemv_mma_fits(a.K, a.B)) {
+  if (a.B >= 2 && !g_view && a.prologue == BK_PRO_Q8 && !bk_gemv_mma_fits(a.K, a.B)) {
+    // Rows too wide for the tensor-core path's shared memory (FFN 17408 of the 64-layer configuration): the launch is
+    // cut along K into parts of whole 8-superblock groups.  The canonical order adds a row's unit values per class
+    // (superblock mod 8) in ascending order, so a part starts from the class accumulators its predecessor left in a
+    // scratch buffer and only the last part closes the tree and runs the epilogue: same bits as one launch.
+    int psb = 0;
+    for (int cand = 32; cand >= 8; cand -= 8)
+      if (bk_gemv_mma_fits(cand * 256, a.B)) { psb = cand; break; }
+    if (psb) {
+      const int nsb = a.K / 256, nparts = (nsb + psb - 1) / psb;
+      int per = ((nsb + nparts - 1) / nparts + 7) & ~7;   // even parts, whole groups of 8
+      int vr = 0;
+      for (int i = 0; i < a.n_segs && i < 4; i++) vr += a.segs[i].epilogue == BK_EPI_SWIGLU ? 2 * a.segs[i].n_rows : a.segs[i].n_rows;
+      const size_t need = (size_t)((vr + 15) / 16) * 16384;
+      if (c.gemv_carry_bytes < need) {
+        if (c.capturing) return bk_fail(BK_ERR_STATE, "bkGemvQ4K: the split-K scratch must be sized by an eager launch before a capture");
+        if (c.gemv_carry) cudaFree(c.gemv_carry);
+        c.gemv_carry = nullptr;
+        c.gemv_carry_bytes = 0;
+        void* q = nullptr;
+        BK_CUDA(cudaMalloc(&q, need));
+        c.gemv_carry = static_cast<float*>(q);
+        c.gemv_carry_bytes = need;
+      }
+      for (int s0 = 0, i = 0; s0 < nsb; s0 += per, i++) {
+        const int s1 = s0 + per < nsb ? s0 + per : nsb;
+        const bool last = s1 == nsb;
+        bkGemvArgs s = a;
+        s.K = (s1 - s0) * 256;
+        const KView v = {(unsigned int)(nsb * 144), (unsigned int)(s0 * 144), a.K / 32, s0 * 8, i ? c.gemv_carry : nullptr,
+                         last ? nullptr : c.gemv_carry};
+        g_view = &v;
+        const int32_t rc = bk_gemv_launch_tp(s, push, nullptr, last ? ctas_out : nullptr);
+        g_view = nullptr;
+        if (rc != BK_OK) return rc;
+      }
+      return BK_OK;
+    }
+  }
+  if (a.B >= 3 && !g_view && !bk_gemv_mma_fits(a.K, a.B)) {
     // A K this wide (FFN 17408 of the 64-layer configuration) leaves no room for a 16-row tile beside the staged
     // activation of 3..8 columns.  The columns are independent, so the launch is cut into column pairs on the
     // small-batch kernel (same arithmetic, same bits); the weights of the later pairs come mostly from L2.
@@ -541,6 +607,12 @@ int32_t bk_gemv_launch_tp(const bkGemvArgs& a, const BkPush* push, const BkReduc
   p.n_segs = a.n_segs;
   p.prologue = a.prologue;
   p.x = bk_ptr<void>(a.x);
+  p.row_stride = g_view ? g_view->row_stride : 0;
+  p.row_off = g_view ? g_view->row_off : 0;
+  p.xq_ld = g_view ? g_view->xq_ld : 0;
+  p.xq_off = g_view ? g_view->xq_off : 0;
+  p.carry_in = g_view ? g_view->carry_in : nullptr;
+  p.carry_out = g_view ? g_view->carry_out : nullptr;
   memset(&p.push, 0, sizeof(p.push));
   memset(&p.red, 0, sizeof(p.red));
   if (reduce && a.prologue == BK_PRO_REDUCE_RMSNORM) p.red = *reduce;

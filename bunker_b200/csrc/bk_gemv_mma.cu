@@ -144,10 +144,13 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
       const uint8_t* rowB = rowA + 8 * rstride;
       // class c = s mod 8 collects the unit values of s = c, c+8, ... in ascending order
       float P[8][4];
+      // class accumulators of (global tile, pair): 8 x float4 per lane, carried between the K parts of a split launch
+      const size_t carry_idx = ((size_t)(tile0 + t) * 4 + tp) * 8 * 32 + lane;
 #pragma unroll
       for (int c = 0; c < 8; c++) {
-#pragma unroll
-        for (int v = 0; v < 4; v++) P[c][v] = 0.0f;
+        float4 v4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (p.carry_in) v4 = __ldcg(reinterpret_cast<const float4*>(p.carry_in) + carry_idx + c * 32);
+        P[c][0] = v4.x; P[c][1] = v4.y; P[c][2] = v4.z; P[c][3] = v4.w;
       }
       for (int s0 = 0; s0 < nsb; s0 += 8) {
 #pragma unroll
@@ -193,6 +196,11 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
           }
         }
       }
+      if (p.carry_out) {
+#pragma unroll
+        for (int c = 0; c < 8; c++)
+          reinterpret_cast<float4*>(p.carry_out)[carry_idx + c * 32] = make_float4(P[c][0], P[c][1], P[c][2], P[c][3]);
+      }
       // T_p = ((P0+P4)+(P2+P6)) + ((P1+P5)+(P3+P7))
 #pragma unroll
       for (int v = 0; v < 4; v++)
@@ -216,7 +224,7 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
       // next round only after every warp of the group has passed that round's barrier, i.e. finished reading here.
       const int g = tid & 127, er = g >> 3, ec = g & 7;
       const float* pr = part + (size_t)(rd & 1) * (tpr * 4 * 128) + (size_t)(tq * 4) * 128 + er * 8 + ec;
-      if (ec < B) {
+      if (ec < B && !p.carry_out) {
         const int nr = min(kTileRows, n_rows_cta - t * kTileRows);
         const float y = __fadd_rn(__fadd_rn(pr[0], pr[2 * 128]), __fadd_rn(pr[1 * 128], pr[3 * 128]));
         if (swiglu) {

@@ -45,6 +45,12 @@ struct GemvParams {
   unsigned long long* trace;  // timeline record of this launch, or null
   unsigned long long* cta_trace;  // per-CTA timeline of this launch, or null
   SegDev segs[4];
+  // K view of a split launch (batch >= 2, rows too wide for shared memory): K above is the part's width
+  unsigned int row_stride;   // bytes between weight rows in memory; 0 = the part is the whole row
+  unsigned int row_off;      // byte offset of the part inside each row
+  int xq_ld, xq_off;         // BK_PRO_Q8 input: blocks between batch rows (0 = K/32) and first block of the part
+  const float* carry_in;     // class accumulators of the parts before this one, or null
+  float* carry_out;          // where to leave them for the next part (then no epilogue runs), or null
   BkPush push;     // n = 0 unless a segment has the BK_EPI_PUSH_F32 epilogue
   BkReduce red;    // n = 0 unless the prologue is BK_PRO_REDUCE_RMSNORM
 };
@@ -84,7 +90,7 @@ __device__ void prologue_q8(const GemvParams& p, const int B, uint32_t* xs, floa
   const uint32_t* src = reinterpret_cast<const uint32_t*>(p.x);
   for (int i = threadIdx.x; i < B * nblk; i += blockDim.x) {
     int b = i / nblk, blk = i - b * nblk;
-    const uint32_t* s = src + (size_t)i * 9;
+    const uint32_t* s = src + ((size_t)b * (p.xq_ld ? p.xq_ld : nblk) + p.xq_off + blk) * 9;
     uint32_t* dst = x_block_ptr<TC>(p, xs, b, blk);
     int qsum = 0;
 #pragma unroll
@@ -313,15 +319,15 @@ __device__ __forceinline__ VRow decode_vrow(const GemvParams& p, int v) {
     if (s < p.n_segs && v >= p.segs[s].vrow_begin) si = s;
   const SegDev& sg = p.segs[si];
   const int t = v - sg.vrow_begin;
-  const size_t rowb = (size_t)(p.K / 256) * 144;
+  const size_t rowb = p.row_stride ? (size_t)p.row_stride : (size_t)(p.K / 256) * 144;
   VRow r;
   r.si = si;
   if (sg.epi == BK_EPI_SWIGLU) {
     r.n = t >> 1;
-    r.row = ((t & 1) ? sg.W2 : sg.W) + rowb * (size_t)r.n;
+    r.row = ((t & 1) ? sg.W2 : sg.W) + rowb * (size_t)r.n + p.row_off;
   } else {
     r.n = t;
-    r.row = sg.W + rowb * (size_t)t;
+    r.row = sg.W + rowb * (size_t)t + p.row_off;
   }
   return r;
 }

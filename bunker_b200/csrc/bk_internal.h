@@ -24,6 +24,8 @@ struct BkContext {
   int cta_trace_launch = -1;          // index (among GEMV launches since bkTraceCtas) of the launch to record
   int cta_trace_seen = 0;
   int* d_status = nullptr;           // device word set by kernels whose bounded waits gave up
+  float* gemv_carry = nullptr;       // class accumulators handed from one K part of a split GEMV to the next
+  size_t gemv_carry_bytes = 0;
   char err[512] = {0};
 };
 

@@ -136,6 +136,9 @@ int32_t enqueue_step(Model& m, int parity) {
   // GDN / attention also emit their output as Q8_1 blocks.  Reading those spares the output projection its own
   // quantisation, which pays once that prologue covers several batch rows; at batch 1-2 the bf16 row is as fast.
   const bool q8_handoff = B >= 2;
+  // the staged layout serves groups of 2..8 columns on the tensor-core kernel; a last group of one column (B = 9, 17, ...)
+  // or a K too wide for that kernel reads plain blocks instead
+  auto staged_ok = [&](int K) { return bk_gemv_mma_fits(K, B < 8 ? B : 8) && !(B > 8 && B % 8 == 1); };
   // Input of a projection: fused RMSNorm/quantise prologue at batch 1; at batch >= 2 one small launch
   // normalises and quantises the rows once and every CTA of the projection just copies the blocks.
   // Tensor parallel: a row-parallel GEMV pushes its partial sums to every rank (BK_EPI_PUSH_F32); the sum over ranks,
@@ -156,7 +159,7 @@ int32_t enqueue_step(Model& m, int parity) {
       pending.on = false;
     }
     if (q8_handoff) {
-      const bool staged = bk_gemv_mma_fits(K, B);   // else the GEMV runs as column pairs reading plain blocks
+      const bool staged = staged_ok(K);   // else the GEMV is cut along K (or runs as column pairs) reading plain blocks
       PROF(PC_QUANT, bk_quant_rows_launch(x, norm_w, K, B, c.eps, m.xq, staged ? BK_Q8_STAGED : BK_Q8_BLOCKS,
                                           reduce ? &red_desc : nullptr));
       g.prologue = staged ? BK_PRO_STAGED : BK_PRO_Q8; g.x = m.xq;
@@ -197,7 +200,7 @@ int32_t enqueue_step(Model& m, int parity) {
       ga.conv_w = L.conv_w; ga.conv_state_in = L.conv_state[parity]; ga.conv_state_new = L.conv_state[parity ^ 1];
       ga.A_log = L.A_log; ga.dt_bias = L.dt_bias; ga.norm_w = L.gnorm;
       ga.S_in = L.S; ga.S_new = L.S;  // in place: each thread rewrites exactly the rows it read
-      const bool zd_staged = q8_handoff && bk_gemv_mma_fits(m.ZD, B);
+      const bool zd_staged = q8_handoff && staged_ok(m.ZD);
       ga.out = m.attn_out; ga.out_q8 = q8_handoff ? m.attn_q8 : 0; ga.out_q8_layout = zd_staged ? BK_Q8_STAGED : BK_Q8_BLOCKS;
       ga.B = B; ga.Hk = m.Hk; ga.Hv = m.Hv; ga.apply_conv = 1;
       ga.state_is_settled = 1;  // this layer's state was last written one whole step ago
@@ -223,7 +226,7 @@ int32_t enqueue_step(Model& m, int parity) {
       memset(&aa, 0, sizeof(aa));
       aa.qg = m.qg; aa.k = m.kbuf; aa.v = m.vbuf; aa.q_norm_w = L.q_norm; aa.k_norm_w = L.k_norm;
       aa.cos_t = m.cos_t; aa.sin_t = m.sin_t; aa.k_cache = L.kc; aa.v_cache = L.vc; aa.pos = m.pos;
-      const bool o_staged = q8_handoff && bk_gemv_mma_fits(m.Hq * c.head_dim, B);
+      const bool o_staged = q8_handoff && staged_ok(m.Hq * c.head_dim);
       aa.out = m.attn_out; aa.out_q8 = q8_handoff ? m.attn_q8 : 0; aa.out_q8_layout = o_staged ? BK_Q8_STAGED : BK_Q8_BLOCKS;
       aa.scratch = m.attn_scratch;
       aa.B = B; aa.Hq = m.Hq; aa.Hkv = m.Hkv; aa.HD = c.head_dim; aa.rot_half = c.rot_dim / 2; aa.max_len = c.max_len;
@@ -333,7 +336,7 @@ int32_t bkModelCreate(const bkModelConfig* cfg, uint64_t* out_model) {
              c.attn_q_heads / c.attn_kv_heads <= 8, "bkModelCreate: bad attention head counts");
   BK_ARG(c.head_dim == 256, "bkModelCreate: head_dim=%d unsupported (256)", c.head_dim);
   BK_ARG(c.rot_dim > 0 && c.rot_dim % 2 == 0 && c.rot_dim <= c.head_dim, "bkModelCreate: rot_dim=%d", c.rot_dim);
-  BK_ARG(c.batch >= 1 && c.batch <= 8, "bkModelCreate: batch=%d outside 1..8", c.batch);
+  BK_ARG(c.batch >= 1 && c.batch <= 64, "bkModelCreate: batch=%d outside 1..64", c.batch);
   BK_ARG(c.max_len >= 1, "bkModelCreate: max_len=%d", c.max_len);
   BK_ARG(c.vocab > 0, "bkModelCreate: vocab=%d", c.vocab);
   BK_ARG(c.tp_size >= 1 && c.tp_size <= 8 && c.tp_rank >= 0 && c.tp_rank < c.tp_size, "bkModelCreate: tp rank %d of %d", c.tp_rank, c.tp_size);
@@ -449,7 +452,7 @@ int32_t bkModelFinalize(uint64_t model) {
   {  // quantised handoff buffers: room for either layout
     const int ka = m.ZD > attn_w ? m.ZD : attn_w, kx = m.inter > H ? m.inter : H;
     const size_t ba = (size_t)B * ka / 32 * 36, bx = (size_t)B * kx / 32 * 36;
-    const size_t sa = B <= 8 ? bk_staged_bytes(ka, B) : 0, sx = B <= 8 ? bk_staged_bytes(kx, B) : 0;
+    const size_t sa = bk_staged_total_bytes(ka, B), sx = bk_staged_total_bytes(kx, B);
     TRY(dev_alloc(m, ba > sa ? ba : sa, &m.attn_q8));
     TRY(dev_alloc(m, bx > sx ? bx : sx, &m.xq));
   }

@@ -534,7 +534,7 @@ int32_t bk_quant_rows_launch(uint64_t x, uint64_t w, int32_t K, int32_t B, float
   BK_ARG((x || reduce) && out && ((x | w) & 15) == 0 && (out & 3) == 0, "bkRmsNormQuantQ8_1: null or misaligned pointer");
   BK_ARG(layout == BK_Q8_BLOCKS || layout == BK_Q8_STAGED, "bkRmsNormQuantQ8_1: unknown layout %d", layout);
   BK_ARG(!reduce || w, "bkRmsNormQuantQ8_1: the reduce input exists with the norm only");
-  if (layout == BK_Q8_STAGED) BK_ARG(B <= 8 && (out & 15) == 0, "bkRmsNormQuantQ8_1: a staged image holds at most 8 rows and is 16-byte aligned");
+  if (layout == BK_Q8_STAGED) BK_ARG((out & 15) == 0, "bkRmsNormQuantQ8_1: a staged image is 16-byte aligned");
   const dim3 grid = w ? dim3(1, B) : dim3((K / 8 + 255) / 256, B);
   auto* px = bk_ptr<uint16_t>(x);
   auto* pw = bk_ptr<uint16_t>(w);
@@ -561,7 +561,7 @@ int32_t bkRmsNormQuantQ8_1(uint64_t x, uint64_t w, int32_t K, int32_t B, float e
   return bk_quant_rows_launch(x, w, K, B, eps, out, layout, nullptr);
 }
 
-uint64_t bkStagedBytes(int32_t K, int32_t B) { return (K > 0 && B > 0) ? (uint64_t)bk_staged_bytes(K, B) : 0; }
+uint64_t bkStagedBytes(int32_t K, int32_t B) { return (K > 0 && B > 0) ? (uint64_t)bk_staged_total_bytes(K, B) : 0; }
 
 int32_t bkSwiglu(uint64_t g_f32, uint64_t u_f32, int32_t n, uint64_t out_bf16) {
   BK_REQUIRE_INIT();
@@ -617,8 +617,8 @@ int32_t bkGdnStep(const bkGdnArgs* args) {
   p.conv_out = bk_ptr<uint16_t>(a.conv_out);
   p.out_q8 = bk_ptr<uint8_t>(a.out_q8);
   p.out_q8_staged = a.out_q8_layout == BK_Q8_STAGED;
-  BK_ARG(a.out_q8_layout == BK_Q8_BLOCKS || (a.out_q8_layout == BK_Q8_STAGED && a.B <= 8 && (a.Hv * 128) % 256 == 0),
-         "bkGdnStep: out_q8_layout %d (a staged image needs B <= 8 and Hv*128 a multiple of 256)", a.out_q8_layout);
+  BK_ARG(a.out_q8_layout == BK_Q8_BLOCKS || (a.out_q8_layout == BK_Q8_STAGED && (a.Hv * 128) % 256 == 0),
+         "bkGdnStep: out_q8_layout %d (a staged image needs Hv*128 a multiple of 256)", a.out_q8_layout);
   p.B = a.B;
   p.Hk = a.Hk;
   p.Hv = a.Hv;

@@ -113,6 +113,32 @@ def test_gemv_staged_activation(bk, B, K):
         ops.gemv(img.ptr, K, 1, [ops.gemv_seg(dWg.ptr, N, y.ptr, R.BK_EPI_F32)], prologue=R.BK_PRO_STAGED)
 
 
+@pytest.mark.parametrize("B", [9, 16, 20, 32])
+def test_gemv_more_than_eight_columns(bk, B):
+    """Batch 9..32 runs as groups of 8 columns (a last group of one column takes the batch-1 kernel): Q8_1 blocks in,
+    bf16 rows in with the fused norm, and -- unless a group of one is left over -- the grouped staged image."""
+    K, N = 2048, 150
+    rng = np.random.default_rng(200 + B)
+    W = synth.q4k_weights(rng, N, K)
+    x, nw = synth.normal_bf16(rng, (B, K)), synth.normal_bf16(rng, (K,), 0.02)
+    res = synth.normal_bf16(rng, (B, N))
+    xq = O.q8_1_quantize_bf16(O.rmsnorm(x, nw))
+    want = O.gemv_q4k_q8(W, N, K, xq)
+    dW, dx, dnw, dxq, dres = dev(W), dev(x), dev(nw), dev(xq), dev(res)
+    y = R.DeviceBuffer(B * N * 4)
+    ops.gemv_simple(dW.ptr, N, K, dxq.ptr, B, y.ptr)
+    assert_same_bits(y.download(np.float32, (B, N)), want, "Q8_1 blocks in")
+    o = R.DeviceBuffer(B * N * 2)
+    ops.gemv(dx.ptr, K, B, [ops.gemv_seg(dW.ptr, N, o.ptr, R.BK_EPI_ADD_BF16, residual=dres.ptr)], prologue=R.BK_PRO_RMSNORM,
+             norm_w=dnw.ptr)
+    assert_same_bits(o.download(np.uint16, (B, N)), O.epilogue_add(want, res), "bf16 rows in, fused norm, residual out")
+    if B % 8 != 1:
+        img = R.DeviceBuffer.zeros(ops.staged_bytes(K, B))
+        ops.rmsnorm_quant_q8_1(dx.ptr, dnw.ptr, K, B, img.ptr, layout=R.BK_Q8_STAGED)
+        ops.gemv(img.ptr, K, B, [ops.gemv_seg(dW.ptr, N, y.ptr, R.BK_EPI_F32)], prologue=R.BK_PRO_STAGED)
+        assert_same_bits(y.download(np.float32, (B, N)), want, "grouped staged image in")
+
+
 @pytest.mark.parametrize("B", [3, 8])
 def test_gemv_widest_k_batched(bk, B):
     """K = 17408 (FFN width of the 64-layer configuration) at batch >= 3: too wide for the tensor-core path's
@@ -181,7 +207,7 @@ def test_gemv_rejects_bad_arguments(bk):
         ops.gemv_simple(16, 4, 100, 16, 1, 16)  # K not a multiple of 256
     assert e.value.code == R.BK_ERR_ARG
     with pytest.raises(R.BunkerCudaError):
-        ops.gemv_simple(16, 4, 256, 16, 9, 16)  # batch beyond 8
+        ops.gemv_simple(16, 4, 256, 16, 65, 16)  # batch beyond 64
 
 
 def test_gemv_linearity_full_size(bk):

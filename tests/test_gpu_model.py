@@ -94,6 +94,25 @@ def test_full_size_model_first_steps_match_oracle(bk):
     gm.destroy()
 
 
+@pytest.mark.parametrize("B", [9, 12, 32])
+def test_tiny_model_more_than_eight_sequences(bk, B):
+    """Batch above 8 (column groups of 8 in every projection): 6 prompt tokens + 10 greedy steps, tokens identical to
+    the oracle and logits bit-identical at the end."""
+    cfg = M.CONFIG_TINY.with_(max_len=32)
+    w = M.synth_weights(cfg, seed=20 + B)
+    gm = M.DecodeModel(cfg, w, batch=B)
+    info = gm.info()
+    om = OracleModel(cfg, w, batch=B, split_len=info["split_len"], attn_warps=info["attn_warps"])
+    prompt = np.random.default_rng(6).integers(0, cfg.vocab, (6, B)).astype(np.int32)
+    ids_g = ids_o = None
+    for t in range(16):
+        ids_o, _ = om.step(prompt[t] if t < 6 else ids_o)
+        ids_g, _ = gm.step(prompt[t] if t < 6 else ids_g)
+        assert np.array_equal(ids_g, ids_o), f"step {t}"
+    assert_same_bits(gm.logits(), om.logits, "logits")
+    gm.destroy()
+
+
 def test_scaled_model_shapes_first_steps_match_oracle(bk):
     """configs[4] shapes (hidden 5120, 16/48 GDN heads, 24/4 attention heads of 256, FFN 17408 = 68 superblocks) on a
     4-layer stack with a reduced vocabulary: exercises K = 5120, 6144 and 17408 and group size 6 in attention."""
