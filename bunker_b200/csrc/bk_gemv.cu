@@ -193,7 +193,7 @@ __device__ __forceinline__ int slot_row(bool swiglu, int r, int nr) { return swi
 // TP: the build with the tensor-parallel reduce prologue and push epilogue (kept out of the single-GPU build, whose
 // register allocation they would disturb).
 template <int B, int GMAX, bool TP>
-__global__ void __launch_bounds__(576, ((B * GMAX <= 16) ? 2 : 1)) gemv_q4k_kernel(const GemvParams p) {
+__global__ void __maxnreg__(64) gemv_q4k_kernel(const GemvParams p) {
   static_assert(B <= 2, "batch >= 3 runs on the tensor-core kernel (bk_gemv_mma.cu) or as column pairs of this one");
   bk_pdl_trigger();
   bk_stamp(p.trace, 0);
