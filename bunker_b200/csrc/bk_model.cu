@@ -63,6 +63,12 @@ struct Model {
   cudaGraphExec_t graph[2] = {nullptr, nullptr};
   unsigned long long graph_kernels = 0;
   long long steps = 0;  // steps taken since the last reset (host mirror of pos)
+  // buffers of the multi-token prompt path (bkModelPrefill), sized for `cols` = tokens x sequences columns
+  struct Prefill {
+    int cols = 0;
+    uint64_t x[2] = {0, 0}, h1 = 0, qkv = 0, z = 0, a = 0, b = 0, attn_out = 0, qg = 0, kbuf = 0, vbuf = 0, act = 0, xq = 0;
+    uint64_t ids = 0, pos = 0;   // int32 [cols]: token ids, position of every column
+  } pf;
 };
 
 int32_t dev_alloc(Model& m, size_t bytes, uint64_t* out, bool zero = true) {
@@ -273,6 +279,154 @@ int32_t enqueue_step(Model& m, int parity) {
     PROF(PC_ARGMAX, bk_argmax_launch(m.logits, m.vocab_local, B, m.lidx, m.lval, m.argmax_scratch, 0, 0, 0, 0));
     PROF(PC_EXCHANGE, bk_comm_argmax_merge(m.comm, 2, B, m.lval, m.lidx, m.vocab_offset, m.ids, m.val, m.pos, m.hist, B, c.max_len));
   }
+  return BK_OK;
+}
+
+// pos_cols[t*B + b] = pos[b] + t
+__global__ void prefill_positions_kernel(const int32_t* pos, int32_t* pos_cols, int T, int B) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < T * B) pos_cols[i] = pos[i % B] + i / B;
+}
+__global__ void advance_positions_kernel(int32_t* pos, int B, int delta) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < B) pos[b] += delta;
+}
+
+int32_t alloc_prefill(Model& m, int cols) {
+  if (m.pf.cols >= cols) return BK_OK;
+  const bkModelConfig& c = m.cfg;
+  const int H = c.hidden, attn_w = m.Hq * c.head_dim;
+  const size_t C = (size_t)cols;
+  Model::Prefill& f = m.pf;
+  TRY(dev_alloc(m, C * H * 2, &f.x[0]));
+  TRY(dev_alloc(m, C * H * 2, &f.x[1]));
+  TRY(dev_alloc(m, C * H * 2, &f.h1));
+  TRY(dev_alloc(m, C * m.Cw * 2, &f.qkv));
+  TRY(dev_alloc(m, C * m.ZD * 2, &f.z));
+  TRY(dev_alloc(m, C * m.Hv * 4, &f.a));
+  TRY(dev_alloc(m, C * m.Hv * 4, &f.b));
+  TRY(dev_alloc(m, C * (m.ZD > attn_w ? m.ZD : attn_w) * 2, &f.attn_out));
+  TRY(dev_alloc(m, C * m.QG * 2, &f.qg));
+  TRY(dev_alloc(m, C * m.KVD * 2, &f.kbuf));
+  TRY(dev_alloc(m, C * m.KVD * 2, &f.vbuf));
+  TRY(dev_alloc(m, C * m.inter * 2, &f.act));
+  int kmax = m.inter > H ? m.inter : H;
+  if (m.ZD > kmax) kmax = m.ZD;
+  if (attn_w > kmax) kmax = attn_w;
+  const size_t blocks = C * kmax / 32 * 36, staged = bk_staged_total_bytes(kmax, cols);
+  TRY(dev_alloc(m, blocks > staged ? blocks : staged, &f.xq));
+  TRY(dev_alloc(m, C * 4, &f.ids));
+  TRY(dev_alloc(m, C * 4, &f.pos));
+  f.cols = cols;
+  return BK_OK;
+}
+
+// T prompt tokens of every sequence in one pass: the projections see T*B columns (weights streamed once per 8
+// columns instead of once per token); the recurrent parts -- conv1d + GDN state, KV append + attention -- run token
+// after token with the decode kernels.  Every column goes through the arithmetic of the decode step, so the state
+// and the logits of the last token are bit-identical to T decode steps.  Single GPU only.
+int32_t enqueue_prefill(Model& m, int T) {
+  const bkModelConfig& c = m.cfg;
+  const int B = m.B, H = c.hidden, C = T * B;
+  Model::Prefill& f = m.pf;
+  auto staged_ok = [&](int K, int cols) { return cols >= 2 && bk_gemv_mma_fits(K, cols < 8 ? cols : 8) && !(cols > 8 && cols % 8 == 1); };
+  // quantise `cols` rows once (optionally RMSNorm first) and point the GEMV at the result
+  auto set_input = [&](bkGemvArgs& g, uint64_t x, int K, uint64_t norm_w, int cols) -> int32_t {
+    g.K = K; g.B = cols; g.eps = c.eps;
+    if (cols == 1) {
+      g.prologue = norm_w ? BK_PRO_RMSNORM : BK_PRO_BF16; g.x = x; g.norm_w = norm_w;
+      return BK_OK;
+    }
+    const bool staged = staged_ok(K, cols);
+    TRY(bk_quant_rows_launch(x, norm_w, K, cols, c.eps, f.xq, staged ? BK_Q8_STAGED : BK_Q8_BLOCKS, nullptr));
+    g.prologue = staged ? BK_PRO_STAGED : BK_PRO_Q8; g.x = f.xq;
+    return BK_OK;
+  };
+  prefill_positions_kernel<<<(C + 127) / 128, 128, 0, bk_ctx().stream>>>(bk_ptr<int32_t>(m.pos), bk_ptr<int32_t>(f.pos), T, B);
+  BK_CHECK_LAUNCH();
+  int cur = 0;
+  TRY(bkEmbedQ4K(m.embed, H, f.ids, C, f.x[0]));
+  for (int li = 0; li < c.n_layers; li++) {
+    LayerW& L = m.layers[li];
+    bkGemvArgs g;
+    memset(&g, 0, sizeof(g));
+    TRY(set_input(g, f.x[cur], H, L.in_ln, C));
+    if (!L.full) {
+      g.n_segs = 4;
+      g.segs[0] = bkGemvSeg{L.qkv, 0, f.qkv, 0, m.Cw, BK_EPI_BF16, m.Cw, 0};
+      g.segs[1] = bkGemvSeg{L.z, 0, f.z, 0, m.ZD, BK_EPI_BF16, m.ZD, 0};
+      g.segs[2] = bkGemvSeg{L.a, 0, f.a, 0, m.Hv, BK_EPI_F32, m.Hv, 0};
+      g.segs[3] = bkGemvSeg{L.b, 0, f.b, 0, m.Hv, BK_EPI_F32, m.Hv, 0};
+      TRY(bk_gemv_launch(g));
+      for (int t = 0; t < T; t++) {
+        const uint64_t r = (uint64_t)t * B;   // first column of this token
+        const int parity = (int)((m.steps + t) & 1);
+        bkGdnArgs ga;
+        memset(&ga, 0, sizeof(ga));
+        ga.qkv = f.qkv + r * m.Cw * 2; ga.z = f.z + r * m.ZD * 2; ga.a = f.a + r * m.Hv * 4; ga.b = f.b + r * m.Hv * 4;
+        ga.conv_w = L.conv_w; ga.conv_state_in = L.conv_state[parity]; ga.conv_state_new = L.conv_state[parity ^ 1];
+        ga.A_log = L.A_log; ga.dt_bias = L.dt_bias; ga.norm_w = L.gnorm;
+        ga.S_in = L.S; ga.S_new = L.S;
+        ga.out = f.attn_out + r * m.ZD * 2; ga.B = B; ga.Hk = m.Hk; ga.Hv = m.Hv; ga.apply_conv = 1;
+        ga.state_is_settled = 0;   // the launch just before this one wrote the state it reads
+        TRY(bkGdnStep(&ga));
+      }
+      memset(&g, 0, sizeof(g));
+      TRY(set_input(g, f.attn_out, m.ZD, 0, C));
+      g.n_segs = 1;
+      g.segs[0] = bkGemvSeg{L.out_proj, 0, f.h1, f.x[cur], H, BK_EPI_ADD_BF16, H, 0};
+      TRY(bk_gemv_launch(g));
+    } else {
+      g.n_segs = 3;
+      g.segs[0] = bkGemvSeg{L.q, 0, f.qg, 0, m.QG, BK_EPI_BF16, m.QG, 0};
+      g.segs[1] = bkGemvSeg{L.k, 0, f.kbuf, 0, m.KVD, BK_EPI_BF16, m.KVD, 0};
+      g.segs[2] = bkGemvSeg{L.v, 0, f.vbuf, 0, m.KVD, BK_EPI_BF16, m.KVD, 0};
+      TRY(bk_gemv_launch(g));
+      const int attn_w = m.Hq * c.head_dim;
+      for (int t = 0; t < T; t++) {
+        const uint64_t r = (uint64_t)t * B;
+        bkAttnArgs aa;
+        memset(&aa, 0, sizeof(aa));
+        aa.qg = f.qg + r * m.QG * 2; aa.k = f.kbuf + r * m.KVD * 2; aa.v = f.vbuf + r * m.KVD * 2;
+        aa.q_norm_w = L.q_norm; aa.k_norm_w = L.k_norm;
+        aa.cos_t = m.cos_t; aa.sin_t = m.sin_t; aa.k_cache = L.kc; aa.v_cache = L.vc; aa.pos = f.pos + r * 4;
+        aa.out = f.attn_out + r * attn_w * 2; aa.scratch = m.attn_scratch;
+        aa.B = B; aa.Hq = m.Hq; aa.Hkv = m.Hkv; aa.HD = c.head_dim; aa.rot_half = c.rot_dim / 2; aa.max_len = c.max_len;
+        aa.split_len = m.split_len; aa.max_pos = c.max_len - 1; aa.scale = 1.0f / sqrtf((float)c.head_dim);
+        aa.fused_norm_rope = 1;
+        aa.cache_is_settled = 0;   // the previous token's launch appended the row this one reads
+        TRY(bkAttnDecode(&aa));
+      }
+      memset(&g, 0, sizeof(g));
+      TRY(set_input(g, f.attn_out, attn_w, 0, C));
+      g.n_segs = 1;
+      g.segs[0] = bkGemvSeg{L.o, 0, f.h1, f.x[cur], H, BK_EPI_ADD_BF16, H, 0};
+      TRY(bk_gemv_launch(g));
+    }
+    memset(&g, 0, sizeof(g));
+    TRY(set_input(g, f.h1, H, L.post_ln, C));
+    g.n_segs = 1;
+    g.segs[0] = bkGemvSeg{L.gate, L.up, f.act, 0, m.inter, BK_EPI_SWIGLU, m.inter, 0};
+    TRY(bk_gemv_launch(g));
+    memset(&g, 0, sizeof(g));
+    TRY(set_input(g, f.act, m.inter, 0, C));
+    g.n_segs = 1;
+    g.segs[0] = bkGemvSeg{L.down, 0, f.x[cur ^ 1], f.h1, H, BK_EPI_ADD_BF16, H, 0};
+    TRY(bk_gemv_launch(g));
+    cur ^= 1;
+  }
+  // logits and argmax of the last token only
+  bkGemvArgs g;
+  memset(&g, 0, sizeof(g));
+  TRY(set_input(g, f.x[cur] + (uint64_t)(C - B) * H * 2, H, m.final_norm, B));
+  g.n_segs = 1;
+  g.segs[0] = bkGemvSeg{m.embed, 0, m.logits, 0, m.vocab_local, BK_EPI_F32, m.vocab_local, 0};
+  TRY(bk_gemv_launch(g));
+  if (T > 1) {
+    advance_positions_kernel<<<(B + 127) / 128, 128, 0, bk_ctx().stream>>>(bk_ptr<int32_t>(m.pos), B, T - 1);
+    BK_CHECK_LAUNCH();
+  }
+  TRY(bk_argmax_launch(m.logits, m.vocab_local, B, m.ids, m.val, m.argmax_scratch, m.pos, m.hist, B, c.max_len));
   return BK_OK;
 }
 
@@ -577,6 +731,33 @@ int32_t bkDecodeStepProfiled(uint64_t model, float* ms_out, int32_t* count_out, 
   if (rc) return rc;
   if (e != cudaSuccess) return bk_fail((int32_t)e, "bkDecodeStepProfiled: %s", cudaGetErrorString(e));
   m.steps++;
+  return BK_OK;
+}
+
+int32_t bkModelPrefill(uint64_t model, const int32_t* tokens, int32_t T, int32_t* out_ids, float* out_vals) {
+  BK_REQUIRE_INIT();
+  BK_ARG(model && tokens && T >= 1, "bkModelPrefill: bad arguments");
+  Model& m = *as_model(model);
+  BK_ARG(m.finalized, "bkModelPrefill: model is not finalized");
+  BK_ARG(m.tp == 1, "bkModelPrefill: single-GPU models only");
+  const int B = m.B, C = T * B;
+  BK_ARG(C <= 64, "bkModelPrefill: %d tokens x %d sequences exceed 64 columns; feed the prompt in chunks", T, B);
+  BK_ARG(m.steps + T <= m.cfg.max_len, "bkModelPrefill: position %lld + %d tokens exceeds max_len=%d", m.steps, T, m.cfg.max_len);
+  for (int i = 0; i < C; i++)
+    BK_ARG(tokens[i] >= 0 && tokens[i] < m.cfg.vocab, "bkModelPrefill: token %d outside the vocabulary", tokens[i]);
+  cudaStream_t st = bk_ctx().stream;
+  TRY(alloc_prefill(m, C));
+  BK_CUDA(cudaMemcpyAsync(bk_ptr<void>(m.pf.ids), tokens, (size_t)C * 4, cudaMemcpyHostToDevice, st));
+  BK_CUDA(cudaStreamSynchronize(st));   // the caller may reuse `tokens` as soon as this returns
+  TRY(enqueue_prefill(m, T));
+  m.steps += T;
+  if (out_ids || out_vals) {
+    BK_CUDA(cudaMemcpyAsync(m.pin_ids + B, bk_ptr<void>(m.ids), (size_t)B * 4, cudaMemcpyDeviceToHost, st));
+    if (out_vals) BK_CUDA(cudaMemcpyAsync(m.pin_ids + 2 * B, bk_ptr<void>(m.val), (size_t)B * 4, cudaMemcpyDeviceToHost, st));
+    BK_CUDA(cudaStreamSynchronize(st));
+    if (out_ids) memcpy(out_ids, m.pin_ids + B, (size_t)B * 4);
+    if (out_vals) memcpy(out_vals, m.pin_ids + 2 * B, (size_t)B * 4);
+  }
   return BK_OK;
 }
 

@@ -300,6 +300,21 @@ class DecodeModel:
     def run(self, n_steps: int) -> None:
         R._check(R.cu().bkDecodeRun(self.handle, n_steps))
 
+    def prefill(self, tokens: np.ndarray, read: bool = True, chunk: int | None = None):
+        """Prompt tokens [T, batch] in passes of up to 64 // batch tokens (the projections see all their columns at once;
+        same state and results as T calls of step()).  Returns (ids, vals) after the last token when read is set."""
+        tokens = np.ascontiguousarray(tokens, np.int32).reshape(-1, self.batch)
+        per = max(1, 64 // self.batch) if chunk is None else chunk
+        out = None
+        for t0 in range(0, tokens.shape[0], per):
+            part = np.ascontiguousarray(tokens[t0:t0 + per])
+            last = t0 + per >= tokens.shape[0]
+            R._check(R.cu().bkModelPrefill(self.handle, part.ctypes.data_as(C.POINTER(C.c_int32)), part.shape[0],
+                                           self._out if (read and last) else None, self._val if (read and last) else None))
+            if read and last:
+                out = (np.array(self._out[:], np.int32), np.array(self._val[:], np.float32))
+        return out
+
     PROFILE_CLASSES = ("embed", "gemv_proj", "gdn", "attn", "gemv_out", "gemv_gateup", "gemv_down", "gemv_lmhead",
                        "argmax", "exchange", "quant")
 

@@ -140,6 +140,7 @@ _MODEL_SIGS = {
     "bkModelReset": (C.c_int32, [C.c_uint64]),
     "bkDecodeStep": (C.c_int32, [C.c_uint64, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
     "bkDecodeRun": (C.c_int32, [C.c_uint64, C.c_int32]),
+    "bkModelPrefill": (C.c_int32, [C.c_uint64, C.POINTER(C.c_int32), C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
     "bkDecodeStepProfiled": (C.c_int32, [C.c_uint64, C.POINTER(C.c_float), C.POINTER(C.c_int32), C.c_int32]),
     "bkModelTokens": (C.c_int32, [C.c_uint64, C.c_int32, C.c_int32, C.POINTER(C.c_int32)]),
     "bkModelInfo": (C.c_int32, [C.c_uint64, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32),

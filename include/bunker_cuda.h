@@ -279,6 +279,12 @@ BK_API int32_t bkModelReset(uint64_t model);
  * feed back the previous step's argmax on the device.  out_ids / out_vals: B host values each, or NULL to
  * skip the read-back (and its synchronisation). */
 BK_API int32_t bkDecodeStep(uint64_t model, const int32_t* tokens, int32_t* out_ids, float* out_vals);
+/* T prompt tokens of every sequence in one call (tokens host int32 [T][B], T*B <= 64; longer prompts in chunks):
+ * the projections run once over T*B columns, the recurrent parts (conv1d + GDN state, KV append + attention) token
+ * after token.  State and results are bit-identical to T calls of bkDecodeStep; out_ids/out_vals (optional) are the
+ * argmax after the last token.  Replaces the token-by-token prompt loop of prototypes/decode.ts:952-1061.
+ * Single-GPU models only. */
+BK_API int32_t bkModelPrefill(uint64_t model, const int32_t* tokens, int32_t T, int32_t* out_ids, float* out_vals);
 /* n_steps greedy steps with device-side token feedback and no host traffic. */
 BK_API int32_t bkDecodeRun(uint64_t model, int32_t n_steps);
 /* One eagerly launched step with a CUDA-event pair around every op (the BUNKER_GPU_PROF=1 profiler of

@@ -113,6 +113,30 @@ def test_tiny_model_more_than_eight_sequences(bk, B):
     gm.destroy()
 
 
+@pytest.mark.parametrize("B,T,chunk", [(1, 13, None), (1, 20, 9), (2, 11, None), (3, 7, 3), (8, 5, None)])
+def test_prefill_equals_token_by_token(bk, B, T, chunk):
+    """bkModelPrefill: T prompt tokens in multi-token passes leave the model in the state T single steps leave it in:
+    same argmax after the prompt, then 6 greedy steps with identical tokens and bit-identical logits."""
+    cfg = M.CONFIG_TINY.with_(max_len=64)
+    w = M.synth_weights(cfg, seed=40 + B)
+    gm = M.DecodeModel(cfg, w, batch=B)
+    info = gm.info()
+    om = OracleModel(cfg, w, batch=B, split_len=info["split_len"], attn_warps=info["attn_warps"])
+    prompt = np.random.default_rng(T).integers(0, cfg.vocab, (T, B)).astype(np.int32)
+    for t in range(T):
+        ids_o, val_o = om.step(prompt[t])
+    ids_g, val_g = gm.prefill(prompt, chunk=chunk)
+    assert np.array_equal(ids_g, ids_o)
+    assert_same_bits(val_g, val_o, "max logit after the prompt")
+    assert_same_bits(gm.logits(), om.logits, "logits after the prompt")
+    for t in range(6):
+        ids_o, _ = om.step(ids_o)
+        ids_g, _ = gm.step(ids_g)
+        assert np.array_equal(ids_g, ids_o), f"step {t} after the prompt"
+    assert_same_bits(gm.logits(), om.logits, "logits after 6 more steps")
+    gm.destroy()
+
+
 def test_scaled_model_shapes_first_steps_match_oracle(bk):
     """configs[4] shapes (hidden 5120, 16/48 GDN heads, 24/4 attention heads of 256, FFN 17408 = 68 superblocks) on a
     4-layer stack with a reduced vocabulary: exercises K = 5120, 6144 and 17408 and group size 6 in attention."""
