@@ -63,6 +63,7 @@ struct Model {
   cudaGraphExec_t graph[2] = {nullptr, nullptr};
   unsigned long long graph_kernels = 0;
   long long steps = 0;  // steps taken since the last reset (host mirror of pos)
+  int conv_cur = 0;     // which of the two conv-state buffers is current (flips with every decode step / prompt pass)
   // buffers of the multi-token prompt path (bkModelPrefill), sized for `cols` = tokens x sequences columns
   struct Prefill {
     int cols = 0;
@@ -358,17 +359,16 @@ int32_t enqueue_prefill(Model& m, int T) {
       g.segs[2] = bkGemvSeg{L.a, 0, f.a, 0, m.Hv, BK_EPI_F32, m.Hv, 0};
       g.segs[3] = bkGemvSeg{L.b, 0, f.b, 0, m.Hv, BK_EPI_F32, m.Hv, 0};
       TRY(bk_gemv_launch(g));
-      for (int t = 0; t < T; t++) {
-        const uint64_t r = (uint64_t)t * B;   // first column of this token
-        const int parity = (int)((m.steps + t) & 1);
+      {   // all T tokens in one launch: the state is read and written once, the taps once
+        const int parity = m.conv_cur;
         bkGdnArgs ga;
         memset(&ga, 0, sizeof(ga));
-        ga.qkv = f.qkv + r * m.Cw * 2; ga.z = f.z + r * m.ZD * 2; ga.a = f.a + r * m.Hv * 4; ga.b = f.b + r * m.Hv * 4;
+        ga.qkv = f.qkv; ga.z = f.z; ga.a = f.a; ga.b = f.b;
         ga.conv_w = L.conv_w; ga.conv_state_in = L.conv_state[parity]; ga.conv_state_new = L.conv_state[parity ^ 1];
         ga.A_log = L.A_log; ga.dt_bias = L.dt_bias; ga.norm_w = L.gnorm;
         ga.S_in = L.S; ga.S_new = L.S;
-        ga.out = f.attn_out + r * m.ZD * 2; ga.B = B; ga.Hk = m.Hk; ga.Hv = m.Hv; ga.apply_conv = 1;
-        ga.state_is_settled = 0;   // the launch just before this one wrote the state it reads
+        ga.out = f.attn_out; ga.B = B; ga.Hk = m.Hk; ga.Hv = m.Hv; ga.apply_conv = 1; ga.n_tokens = T;
+        ga.state_is_settled = 1;   // written by the previous pass, many launches ago
         TRY(bkGdnStep(&ga));
       }
       memset(&g, 0, sizeof(g));
@@ -469,6 +469,7 @@ int32_t reset_state(Model& m) {
   BK_CUDA(cudaMemsetAsync(bk_ptr<void>(m.ids), 0, (size_t)m.B * 4, st));
   BK_CUDA(cudaMemsetAsync(bk_ptr<void>(m.hist), 0, (size_t)c.max_len * m.B * 4, st));
   m.steps = 0;
+  m.conv_cur = 0;
   return BK_OK;
 }
 
@@ -671,9 +672,10 @@ int32_t bkModelInfo(uint64_t model, int32_t* split_len, int32_t* attn_warps, int
 static int32_t launch_step(Model& m) {
   BkContext& c = bk_ctx();
   BK_ARG(m.steps < m.cfg.max_len, "bkDecodeStep: position %lld reached max_len=%d", m.steps, m.cfg.max_len);
-  BK_CUDA(cudaGraphLaunch(m.graph[m.steps & 1], c.stream));
+  BK_CUDA(cudaGraphLaunch(m.graph[m.conv_cur], c.stream));
   c.launches += m.graph_kernels;
   m.steps++;
+  m.conv_cur ^= 1;
   return BK_OK;
 }
 
@@ -711,7 +713,7 @@ int32_t bkDecodeStepProfiled(uint64_t model, float* ms_out, int32_t* count_out, 
   g_prof.on = true;
   g_prof.ev.clear();
   g_prof.cls.clear();
-  int32_t rc = enqueue_step(m, (int)(m.steps & 1));
+  int32_t rc = enqueue_step(m, m.conv_cur);
   g_prof.on = false;
   cudaError_t e = cudaStreamSynchronize(bk_ctx().stream);
   for (int i = 0; i < n_classes; i++) {
@@ -731,6 +733,7 @@ int32_t bkDecodeStepProfiled(uint64_t model, float* ms_out, int32_t* count_out, 
   if (rc) return rc;
   if (e != cudaSuccess) return bk_fail((int32_t)e, "bkDecodeStepProfiled: %s", cudaGetErrorString(e));
   m.steps++;
+  m.conv_cur ^= 1;
   return BK_OK;
 }
 
@@ -751,6 +754,7 @@ int32_t bkModelPrefill(uint64_t model, const int32_t* tokens, int32_t T, int32_t
   BK_CUDA(cudaStreamSynchronize(st));   // the caller may reuse `tokens` as soon as this returns
   TRY(enqueue_prefill(m, T));
   m.steps += T;
+  m.conv_cur ^= 1;
   if (out_ids || out_vals) {
     BK_CUDA(cudaMemcpyAsync(m.pin_ids + B, bk_ptr<void>(m.ids), (size_t)B * 4, cudaMemcpyDeviceToHost, st));
     if (out_vals) BK_CUDA(cudaMemcpyAsync(m.pin_ids + 2 * B, bk_ptr<void>(m.val), (size_t)B * 4, cudaMemcpyDeviceToHost, st));

@@ -217,6 +217,7 @@ struct GdnParams {
   uint8_t* out_q8;
   int out_q8_staged;
   int B, Hk, Hv, apply_conv;
+  int T;      // tokens per sequence handled by this launch, in order (1 in the decode step)
   int early;  // state / conv state / weights are not outputs of the immediately preceding launch
   unsigned long long* trace;
 };
@@ -224,6 +225,8 @@ struct GdnParams {
 // Two builds of this body.  gdn_step_kernel: launched with 576 threads when the grid has at most one CTA per SM; the
 // two extra warps only keep a second CTA of this grid off the SM (register file), so no SM finishes last with two.
 // gdn_step_kernel_x2: 64 registers, two CTAs per SM, for grids larger than the SM count (batch 8: 256 CTAs, one wave).
+// MULTI = false compiles the single-token body of the decode step (no loop, no carried taps).
+template <bool MULTI>
 __device__ __forceinline__ void gdn_step_body(const GdnParams& p) {
   constexpr int D = 128;
   __shared__ float s_q[D], s_k[D], s_v[D], s_o[D];
@@ -275,108 +278,124 @@ __device__ __forceinline__ void gdn_step_body(const GdnParams& p) {
   bk_stamp(p.trace, 2);
   if (!p.early) load_static();
 
-  float zv = 0.0f;
-  if (t < D) zv = bk_bf16_to_f32(p.z[((size_t)b * p.Hv + hv) * D + t]);
-  if (t < 3 * D) {
-    uint16_t hx = p.qkv[(size_t)b * C + ch];
-    float val;
-    if (p.apply_conv) {
-      float w0 = __uint_as_float(cw.x << 16), w1 = __uint_as_float(cw.x & 0xffff0000u);
-      float w2 = __uint_as_float(cw.y << 16), w3 = __uint_as_float(cw.y & 0xffff0000u);
-      float raw = __fadd_rn(__fadd_rn(__fmul_rn(w0, bk_bf16_to_f32(h0)), __fmul_rn(w1, bk_bf16_to_f32(h1))),
-                            __fadd_rn(__fmul_rn(w2, bk_bf16_to_f32(h2)), __fmul_rn(w3, bk_bf16_to_f32(hx))));
-      uint16_t ob = bk_f32_to_bf16(__fmul_rn(raw, bk_sigmoidf(raw)));
-      val = bk_bf16_to_f32(ob);
-      // q/k channels are shared by `ratio` value heads: the first of them writes
-      if (which == 2 || hv % ratio == 0) {
-        uint16_t* d = p.cs_new + (size_t)b * 3 * C;
-        d[ch] = h1;
-        d[C + ch] = h2;
-        d[2 * C + ch] = hx;
-        if (p.conv_out) p.conv_out[(size_t)b * C + ch] = ob;
+  // Tokens tk = 0..T-1 of this sequence in order (T = 1 in the decode step): rows tk*B + b of the per-token inputs and
+  // outputs.  The state and the three conv taps stay in registers between tokens; both are written back after the last.
+  const int T = MULTI ? p.T : 1;
+  for (int tk = 0; tk < T; tk++) {
+    const size_t row = (size_t)tk * p.B + b;
+    const bool last = !MULTI || tk == T - 1;
+    float zv = 0.0f;
+    if (t < D) zv = bk_bf16_to_f32(p.z[(row * p.Hv + hv) * D + t]);
+    if (t < 3 * D) {
+      uint16_t hx = p.qkv[row * C + ch];
+      float val;
+      if (p.apply_conv) {
+        float w0 = __uint_as_float(cw.x << 16), w1 = __uint_as_float(cw.x & 0xffff0000u);
+        float w2 = __uint_as_float(cw.y << 16), w3 = __uint_as_float(cw.y & 0xffff0000u);
+        float raw = __fadd_rn(__fadd_rn(__fmul_rn(w0, bk_bf16_to_f32(h0)), __fmul_rn(w1, bk_bf16_to_f32(h1))),
+                              __fadd_rn(__fmul_rn(w2, bk_bf16_to_f32(h2)), __fmul_rn(w3, bk_bf16_to_f32(hx))));
+        uint16_t ob = bk_f32_to_bf16(__fmul_rn(raw, bk_sigmoidf(raw)));
+        val = bk_bf16_to_f32(ob);
+        // q/k channels are shared by `ratio` value heads: the first of them writes
+        if (which == 2 || hv % ratio == 0) {
+          if (last) {
+            uint16_t* d = p.cs_new + (size_t)b * 3 * C;
+            d[ch] = h1;
+            d[C + ch] = h2;
+            d[2 * C + ch] = hx;
+          }
+          if (p.conv_out) p.conv_out[row * C + ch] = ob;
+        }
+        if (MULTI) {
+          h0 = h1;
+          h1 = h2;
+          h2 = hx;
+        }
+      } else {
+        val = bk_bf16_to_f32(hx);
       }
-    } else {
-      val = bk_bf16_to_f32(hx);
+      if (which == 0) s_q[ci] = val;
+      else if (which == 1) s_k[ci] = val;
+      else s_v[ci] = val;
+    } else if (t == 3 * D) {
+      // gates on an otherwise idle warp, overlapping the conv above
+      float sp = bk_softplusf(__fadd_rn(p.a[row * p.Hv + hv], dtb));
+      s_scal[2] = bk_expf(-__fmul_rn(bk_expf(alog), sp));
+      s_scal[3] = bk_sigmoidf(p.b[row * p.Hv + hv]);
     }
-    if (which == 0) s_q[ci] = val;
-    else if (which == 1) s_k[ci] = val;
-    else s_v[ci] = val;
-  } else if (t == 3 * D) {
-    // gates on an otherwise idle warp, overlapping the conv above
-    float sp = bk_softplusf(__fadd_rn(p.a[(size_t)b * p.Hv + hv], dtb));
-    s_scal[2] = bk_expf(-__fmul_rn(bk_expf(alog), sp));
-    s_scal[3] = bk_sigmoidf(p.b[(size_t)b * p.Hv + hv]);
-  }
-  __syncthreads();
-  if (warp < 2) {
-    const float* src = warp == 0 ? s_q : s_k;
-    float acc = 0.0f;
+    __syncthreads();
+    if (warp < 2) {
+      const float* src = warp == 0 ? s_q : s_k;
+      float acc = 0.0f;
 #pragma unroll
-    for (int e = 0; e < 4; e++) acc = fmaf(src[lane * 4 + e], src[lane * 4 + e], acc);
-    acc = bk_warp_sum(acc);
-    float rr = bk_rcp_sqrt(__fadd_rn(acc, 1e-6f));
-    if (lane == 0) s_scal[warp] = (warp == 0) ? __fmul_rn(rr, 0.088388347648318441f) : rr;
-  }
-  __syncthreads();
-  if (t < D) s_q[t] = __fmul_rn(s_q[t], s_scal[0]);
-  else if (t < 2 * D) s_k[t - D] = __fmul_rn(s_k[t - D], s_scal[1]);
-  __syncthreads();
+      for (int e = 0; e < 4; e++) acc = fmaf(src[lane * 4 + e], src[lane * 4 + e], acc);
+      acc = bk_warp_sum(acc);
+      float rr = bk_rcp_sqrt(__fadd_rn(acc, 1e-6f));
+      if (lane == 0) s_scal[warp] = (warp == 0) ? __fmul_rn(rr, 0.088388347648318441f) : rr;
+    }
+    __syncthreads();
+    if (t < D) s_q[t] = __fmul_rn(s_q[t], s_scal[0]);
+    else if (t < 2 * D) s_k[t - D] = __fmul_rn(s_k[t - D], s_scal[1]);
+    __syncthreads();
 
-  const float decay = s_scal[2], beta = s_scal[3];
-  float acc = 0.0f;
-  if (active) {
+    const float decay = s_scal[2], beta = s_scal[3];
+    float acc = 0.0f;
+    if (active) {
 #pragma unroll
-    for (int i = 0; i < 32; i++) {
-      sd[i] = __fmul_rn(sd[i], decay);
-      acc = fmaf(s_k[32 * r + i], sd[i], acc);
+      for (int i = 0; i < 32; i++) {
+        sd[i] = __fmul_rn(sd[i], decay);
+        acc = fmaf(s_k[32 * r + i], sd[i], acc);
+      }
+      s_part[r][j] = acc;
     }
-    s_part[r][j] = acc;
-  }
-  __syncthreads();
-  float kS = __fadd_rn(__fadd_rn(__fadd_rn(s_part[0][j], s_part[1][j]), s_part[2][j]), s_part[3][j]);
-  float delta = __fmul_rn(__fsub_rn(s_v[j], kS), beta);
-  __syncthreads();
-  acc = 0.0f;
-  if (active) {
+    __syncthreads();
+    float kS = __fadd_rn(__fadd_rn(__fadd_rn(s_part[0][j], s_part[1][j]), s_part[2][j]), s_part[3][j]);
+    float delta = __fmul_rn(__fsub_rn(s_v[j], kS), beta);
+    __syncthreads();
+    acc = 0.0f;
+    if (active) {
 #pragma unroll
-    for (int i = 0; i < 32; i++) {
-      float sn = fmaf(s_k[32 * r + i], delta, sd[i]);
-      Sn[(size_t)i * D] = sn;
-      acc = fmaf(s_q[32 * r + i], sn, acc);
+      for (int i = 0; i < 32; i++) {
+        sd[i] = fmaf(s_k[32 * r + i], delta, sd[i]);
+        if (last) Sn[(size_t)i * D] = sd[i];
+        acc = fmaf(s_q[32 * r + i], sd[i], acc);
+      }
+      s_part[r][j] = acc;
     }
-    s_part[r][j] = acc;
-  }
-  __syncthreads();
-  if (t < D) {
-    float o = __fadd_rn(__fadd_rn(__fadd_rn(s_part[0][t], s_part[1][t]), s_part[2][t]), s_part[3][t]);
-    s_o[t] = o;
-    if (p.o_raw) p.o_raw[((size_t)b * p.Hv + hv) * D + t] = o;
-  }
-  __syncthreads();
-  if (warp == 0) {
-    float a2 = 0.0f;
+    __syncthreads();
+    if (t < D) {
+      float o = __fadd_rn(__fadd_rn(__fadd_rn(s_part[0][t], s_part[1][t]), s_part[2][t]), s_part[3][t]);
+      s_o[t] = o;
+      if (p.o_raw) p.o_raw[(row * p.Hv + hv) * D + t] = o;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      float a2 = 0.0f;
 #pragma unroll
-    for (int e = 0; e < 4; e++) a2 = fmaf(s_o[lane * 4 + e], s_o[lane * 4 + e], a2);
-    a2 = bk_warp_sum(a2);
-    if (lane == 0) s_scal[0] = bk_rcp_sqrt(__fadd_rn(__fdiv_rn(a2, (float)D), 1e-6f));
-  }
-  __syncthreads();
-  if (t < D) {
-    float zs = __fmul_rn(zv, bk_sigmoidf(zv));
-    float ow = __fmul_rn(__fmul_rn(s_o[t], s_scal[0]), nw);
-    const uint16_t ob = bk_f32_to_bf16(__fmul_rn(ow, zs));
-    p.out[((size_t)b * p.Hv + hv) * D + t] = ob;
-    if (p.out_q8) {  // warp w of the first four holds block w of this head
-      const float y[1] = {bk_bf16_to_f32(ob)};
-      if (p.out_q8_staged) bk_staged_store<1>(p.out_q8, p.Hv * D, p.B, b, hv * 4 + warp, y, lane);
-      else bk_q8_1_store<1>(p.out_q8 + (((size_t)b * p.Hv + hv) * 4 + warp) * 36, y, lane);
+      for (int e = 0; e < 4; e++) a2 = fmaf(s_o[lane * 4 + e], s_o[lane * 4 + e], a2);
+      a2 = bk_warp_sum(a2);
+      if (lane == 0) s_scal[0] = bk_rcp_sqrt(__fadd_rn(__fdiv_rn(a2, (float)D), 1e-6f));
     }
+    __syncthreads();
+    if (t < D) {
+      float zs = __fmul_rn(zv, bk_sigmoidf(zv));
+      float ow = __fmul_rn(__fmul_rn(s_o[t], s_scal[0]), nw);
+      const uint16_t ob = bk_f32_to_bf16(__fmul_rn(ow, zs));
+      p.out[(row * p.Hv + hv) * D + t] = ob;
+      if (p.out_q8) {  // warp w of the first four holds block w of this head
+        const float y[1] = {bk_bf16_to_f32(ob)};
+        if (p.out_q8_staged) bk_staged_store<1>(p.out_q8, p.Hv * D, p.B * T, (int)row, hv * 4 + warp, y, lane);
+        else bk_q8_1_store<1>(p.out_q8 + ((row * p.Hv + hv) * 4 + warp) * 36, y, lane);
+      }
+    }
+    if (!last) __syncthreads();   // s_scal[0] and s_o are rewritten by the next token
   }
   bk_stamp(p.trace, 5);
 }
 
-__global__ void __launch_bounds__(576) gdn_step_kernel(const GdnParams p) { gdn_step_body(p); }
-__global__ void __launch_bounds__(512, 2) gdn_step_kernel_x2(const GdnParams p) { gdn_step_body(p); }
+__global__ void __launch_bounds__(576) gdn_step_kernel(const GdnParams p) { gdn_step_body<false>(p); }
+__global__ void __launch_bounds__(512, 2) gdn_step_kernel_x2(const GdnParams p) { gdn_step_body<false>(p); }
+__global__ void __launch_bounds__(576) gdn_step_kernel_multi(const GdnParams p) { gdn_step_body<true>(p); }
 
 // ---- q/k head RMSNorm + partial rotary, one warp per (batch, head) ----------------
 // (src/emitters.ts:123-183).  Lane l owns the HD/32 contiguous dims of the head.
@@ -624,8 +643,11 @@ int32_t bkGdnStep(const bkGdnArgs* args) {
   p.Hv = a.Hv;
   p.apply_conv = a.apply_conv;
   p.early = a.state_is_settled;
+  p.T = a.n_tokens > 1 ? a.n_tokens : 1;
+  BK_ARG(a.n_tokens >= 0 && (p.out_q8_staged == 0 || (size_t)a.B * p.T <= 64), "bkGdnStep: n_tokens=%d", a.n_tokens);
   p.trace = bk_trace_slot();
-  if (a.Hv * a.B > bk_ctx().sm_count) BK_CUDA(bk_launch_pdl(gdn_step_kernel_x2, dim3(a.Hv, a.B), dim3(512), 0, p));
+  if (p.T > 1) BK_CUDA(bk_launch_pdl(gdn_step_kernel_multi, dim3(a.Hv, a.B), dim3(576), 0, p));
+  else if (a.Hv * a.B > bk_ctx().sm_count) BK_CUDA(bk_launch_pdl(gdn_step_kernel_x2, dim3(a.Hv, a.B), dim3(512), 0, p));
   else BK_CUDA(bk_launch_pdl(gdn_step_kernel, dim3(a.Hv, a.B), dim3(576), 0, p));
   BK_CHECK_LAUNCH();
   return BK_OK;

@@ -55,7 +55,7 @@ class bkGdnArgs(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in ("qkv", "z", "a", "b", "conv_w", "conv_state_in", "conv_state_new", "A_log",
                                            "dt_bias", "norm_w", "S_in", "S_new", "out", "o_raw", "conv_out")] + \
                [(n, C.c_int32) for n in ("B", "Hk", "Hv", "apply_conv", "state_is_settled", "out_q8_layout")] + \
-               [("out_q8", C.c_uint64)]
+               [("out_q8", C.c_uint64), ("n_tokens", C.c_int32), ("reserved", C.c_int32)]
 
 
 class bkAttnArgs(C.Structure):

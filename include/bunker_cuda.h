@@ -183,6 +183,10 @@ typedef struct bkGdnArgs {
                                     launch is still running (programmatic dependent launch).  0: read everything after it. */
   int32_t out_q8_layout;         /* BK_Q8_BLOCKS or BK_Q8_STAGED */
   uint64_t out_q8;               /* optional (0 to skip): the same output quantised for the output projection */
+  int32_t n_tokens;              /* 0 or 1: one token per sequence (the decode step).  T > 1: T consecutive tokens of every
+                                    sequence in one launch; token t of sequence b is row t*B + b of qkv, z, a, b and of
+                                    every output ([T*B][...]); the state stays in registers between tokens. */
+  int32_t reserved;
 } bkGdnArgs;
 BK_API int32_t bkGdnStep(const bkGdnArgs* args);
 

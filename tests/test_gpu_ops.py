@@ -132,6 +132,38 @@ def test_gdn_step_config1(bk, B):
     assert rel_err(w_S[0, hv], Sp) < 1e-3 and rel_err(w_o[0, hv], op) < 1e-3
 
 
+def test_gdn_step_several_tokens_in_one_launch(bk):
+    """n_tokens = 3: three consecutive tokens of two sequences in one launch (state and conv taps stay in registers)
+    equal three single-token launches: outputs of every token, final state, final conv state; staged output too."""
+    B, T = 2, 3
+    cases = [synth.gdn_case(B, config_id=50 + t) for t in range(T)]
+    c0 = cases[0]
+    Hk, Hv = c0["Hk"], c0["Hv"]
+    Cw = 2 * Hk * 128 + Hv * 128
+    S, cs = c0["S"], c0["conv_state"]
+    want_out = []
+    for t in range(T):
+        c = dict(cases[t], S=S, conv_state=cs, conv_w=c0["conv_w"], A_log=c0["A_log"], dt_bias=c0["dt_bias"], norm_w=c0["norm_w"])
+        _, cs, S, _, out = _gdn_oracle(c)
+        want_out.append(out)
+    stack = lambda k: np.ascontiguousarray(np.concatenate([cases[t][k] for t in range(T)], axis=0))
+    d = {k: dev(stack(k)) for k in ("qkv", "z", "a", "b")}
+    d0 = {k: dev(c0[k]) for k in ("conv_w", "conv_state", "A_log", "dt_bias", "norm_w", "S")}
+    cs_new, out = R.DeviceBuffer(B * 3 * Cw * 2), R.DeviceBuffer(T * B * Hv * 128 * 2)
+    img = R.DeviceBuffer.zeros(ops.staged_bytes(Hv * 128, T * B))
+    ops.gdn_step(qkv=d["qkv"].ptr, z=d["z"].ptr, a=d["a"].ptr, b=d["b"].ptr, conv_w=d0["conv_w"].ptr,
+                 conv_state_in=d0["conv_state"].ptr, conv_state_new=cs_new.ptr, A_log=d0["A_log"].ptr,
+                 dt_bias=d0["dt_bias"].ptr, norm_w=d0["norm_w"].ptr, S_in=d0["S"].ptr, S_new=d0["S"].ptr, out=out.ptr,
+                 out_q8=img.ptr, out_q8_layout=R.BK_Q8_STAGED, B=B, Hk=Hk, Hv=Hv, apply_conv=1, n_tokens=T)
+    got = out.download(np.uint16, (T, B, Hv * 128))
+    for t in range(T):
+        assert_same_bits(got[t], want_out[t], f"gated out of token {t}")
+    assert_same_bits(d0["S"].download(np.float32, (B, Hv, 128, 128)), S, "state after the last token")
+    assert_same_bits(cs_new.download(np.uint16, (B, 3, Cw)), cs, "conv state after the last token")
+    _check_staged(img.download(np.uint8, (ops.staged_bytes(Hv * 128, T * B),)),
+                  O.q8_1_quantize_bf16(np.concatenate(want_out, axis=0)), Hv * 128, T * B)
+
+
 def test_gdn_step_without_conv(bk):
     c = synth.gdn_case(2, Hk=2, Hv=4, config_id=21)
     Hk, Hv, B = 2, 4, 2

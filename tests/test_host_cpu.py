@@ -49,7 +49,7 @@ def test_calls_fail_loudly_without_a_gpu_or_init():
 def test_struct_layouts_match_the_header():
     import ctypes as C
     assert C.sizeof(R.bkGemvSeg) == 48 and C.sizeof(R.bkGemvArgs) == 40 + 4 * 48
-    assert C.sizeof(R.bkGdnArgs) == 15 * 8 + 24 + 8 and R.bkGdnArgs.out_q8.offset == 144
+    assert C.sizeof(R.bkGdnArgs) == 15 * 8 + 24 + 8 + 8 and R.bkGdnArgs.out_q8.offset == 144 and R.bkGdnArgs.n_tokens.offset == 152
     assert C.sizeof(R.bkAttnArgs) == 12 * 8 + 8 * 4 + 4 + 4 + 8 + 8 + 8 and R.bkAttnArgs.out_q8.offset == 152
     assert C.sizeof(R.bkModelConfig) == 15 * 4 + 4 + 8
 
