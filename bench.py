@@ -297,7 +297,9 @@ def run_ours(args):
                    "attn_split_len": info["split_len"], "kernels_per_step": info["kernels_per_step"]},
         "clocks": sampler.summary(),
         "e2e": {"value": K * B / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 4 * B,
-                "d2h_bytes_per_step": 8 * B, "ms_per_step": e2e_ms / K, "same_tokens_as_resident_leg": same_stream},
+                "d2h_bytes_per_step": 8 * B, "ms_per_step": e2e_ms / K, "same_tokens_as_resident_leg": same_stream,
+                "transfer": ("mapped pinned host memory: the embed kernel reads the token, the argmax kernel writes id and logit"
+                             if world == 1 else "cudaMemcpyAsync from/to pinned host memory")},
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "kernel": f"gemv_q4k_kernel<{B},8>" if B <= 1 else "gemv_q4k_mma_kernel", "achieved": achieved,
                      "peak": hbm_peak / world, "unit": "GB/s", "frac": achieved / (hbm_peak / world),

@@ -104,7 +104,7 @@ int32_t bk_gemv_launch_tp(const bkGemvArgs& a, const BkPush* push, const BkReduc
 int32_t bk_quant_rows_launch(uint64_t x, uint64_t w, int32_t K, int32_t B, float eps, uint64_t out, int32_t layout,
                              const BkReduce* reduce);
 int32_t bk_argmax_launch(uint64_t logits, int32_t V, int32_t B, uint64_t idx, uint64_t val, uint64_t scratch,
-                         uint64_t pos, uint64_t hist, int32_t hist_ld, int32_t hist_rows);
+                         uint64_t pos, uint64_t hist, int32_t hist_ld, int32_t hist_rows, uint64_t host_out = 0);
 
 // Launch with programmatic dependent launch: the kernel may start while its predecessor on the
 // stream is still running; it must execute bk_pdl_wait() (bk_common.cuh) before it touches anything

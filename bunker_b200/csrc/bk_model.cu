@@ -59,8 +59,13 @@ struct Model {
   std::vector<uint64_t> owned;
   uint64_t x[2] = {0, 0}, h1 = 0, qkv = 0, z = 0, a = 0, b = 0, attn_out = 0, attn_q8 = 0, xq = 0, qg = 0, kbuf = 0, vbuf = 0, act = 0;
   uint64_t logits = 0, ids = 0, val = 0, pos = 0, hist = 0, argmax_scratch = 0, attn_scratch = 0, cos_t = 0, sin_t = 0;
-  int32_t* pin_ids = nullptr;  // pinned staging: B ids in, B ids out, B vals
-  cudaGraphExec_t graph[2] = {nullptr, nullptr};
+  int32_t* pin_ids = nullptr;  // pinned, mapped into the device: 2 x B ids in (one slot per graph parity), B ids out,
+                               // B vals (float bits)
+  cudaEvent_t pin_read[2] = {nullptr, nullptr};   // recorded after the step that reads ids slot p
+  bool pin_busy[2] = {false, false};
+  uint64_t pin_dev = 0;        // device address of pin_ids
+  cudaGraphExec_t graph[2] = {nullptr, nullptr};       // token fed back on the device (embed reads m.ids)
+  cudaGraphExec_t graph_host[2] = {nullptr, nullptr};  // token from the host (embed reads the mapped pinned ids)
   unsigned long long graph_kernels = 0;
   long long steps = 0;  // steps taken since the last reset (host mirror of pos)
   int conv_cur = 0;     // which of the two conv-state buffers is current (flips with every decode step / prompt pass)
@@ -136,7 +141,7 @@ struct ProfScope {
   } while (0)
 
 // enqueue one decode step on the library stream; parity selects the conv-state buffer pair
-int32_t enqueue_step(Model& m, int parity) {
+int32_t enqueue_step(Model& m, int parity, bool host_tokens = false) {
   const bkModelConfig& c = m.cfg;
   const int B = m.B, H = c.hidden;
   int cur = 0;
@@ -188,7 +193,11 @@ int32_t enqueue_step(Model& m, int parity) {
     pending = Pending{true, slot, ps.tag_add, res, out};
     return BK_OK;
   };
-  PROF(PC_EMBED, bkEmbedQ4K(m.embed, H, m.ids, B, m.x[0]));
+  // single GPU: the step talks to the host through mapped pinned memory -- the embed kernel can read the host's
+  // tokens there and the argmax kernel always leaves (id, logit) there -- so a step with host I/O is one graph launch
+  // and one synchronisation, no copy-engine operations
+  const bool mapped_io = m.tp == 1 && m.pin_dev != 0;
+  PROF(PC_EMBED, bkEmbedQ4K(m.embed, H, (host_tokens && mapped_io) ? m.pin_dev + (uint64_t)parity * B * 4 : m.ids, B, m.x[0]));
   for (int li = 0; li < c.n_layers; li++) {
     LayerW& L = m.layers[li];
     bkGemvArgs g;
@@ -275,7 +284,8 @@ int32_t enqueue_step(Model& m, int parity) {
                         m.vocab_local, 0};
   PROF(PC_GEMV_LMHEAD, launch(g));
   if (m.tp == 1) {
-    PROF(PC_ARGMAX, bk_argmax_launch(m.logits, m.vocab_local, B, m.ids, m.val, m.argmax_scratch, m.pos, m.hist, B, c.max_len));
+    PROF(PC_ARGMAX, bk_argmax_launch(m.logits, m.vocab_local, B, m.ids, m.val, m.argmax_scratch, m.pos, m.hist, B, c.max_len,
+                                     mapped_io ? m.pin_dev + (uint64_t)2 * B * 4 : 0));
   } else {
     PROF(PC_ARGMAX, bk_argmax_launch(m.logits, m.vocab_local, B, m.lidx, m.lval, m.argmax_scratch, 0, 0, 0, 0));
     PROF(PC_EXCHANGE, bk_comm_argmax_merge(m.comm, 2, B, m.lval, m.lidx, m.vocab_offset, m.ids, m.val, m.pos, m.hist, B, c.max_len));
@@ -426,17 +436,18 @@ int32_t enqueue_prefill(Model& m, int T) {
     advance_positions_kernel<<<(B + 127) / 128, 128, 0, bk_ctx().stream>>>(bk_ptr<int32_t>(m.pos), B, T - 1);
     BK_CHECK_LAUNCH();
   }
-  TRY(bk_argmax_launch(m.logits, m.vocab_local, B, m.ids, m.val, m.argmax_scratch, m.pos, m.hist, B, c.max_len));
+  TRY(bk_argmax_launch(m.logits, m.vocab_local, B, m.ids, m.val, m.argmax_scratch, m.pos, m.hist, B, c.max_len,
+                       m.pin_dev ? m.pin_dev + (uint64_t)2 * B * 4 : 0));
   return BK_OK;
 }
 
-int32_t capture(Model& m, int parity) {
+int32_t capture(Model& m, int parity, bool host_tokens = false) {
   BkContext& c = bk_ctx();
   cudaGraph_t g = nullptr;
   BK_CUDA(cudaStreamBeginCapture(c.stream, cudaStreamCaptureModeThreadLocal));
   c.capturing = true;
   c.captured = 0;
-  int32_t rc = enqueue_step(m, parity);
+  int32_t rc = enqueue_step(m, parity, host_tokens);
   c.capturing = false;
   cudaError_t e = cudaStreamEndCapture(c.stream, &g);
   if (rc) {
@@ -445,7 +456,7 @@ int32_t capture(Model& m, int parity) {
   }
   if (e != cudaSuccess) return bk_fail((int32_t)e, "bkModelFinalize: graph capture -> %s", cudaGetErrorString(e));
   m.graph_kernels = c.captured;
-  e = cudaGraphInstantiate(&m.graph[parity], g, 0);
+  e = cudaGraphInstantiate(host_tokens ? &m.graph_host[parity] : &m.graph[parity], g, 0);
   cudaGraphDestroy(g);
   if (e != cudaSuccess) return bk_fail((int32_t)e, "bkModelFinalize: graph instantiate -> %s", cudaGetErrorString(e));
   return BK_OK;
@@ -637,7 +648,14 @@ int32_t bkModelFinalize(uint64_t model) {
     BK_CUDA(cudaMemcpyAsync(bk_ptr<void>(m.sin_t), st.data(), st.size() * 4, cudaMemcpyHostToDevice, bk_ctx().stream));
     BK_CUDA(cudaStreamSynchronize(bk_ctx().stream));
   }
-  BK_CUDA(cudaHostAlloc((void**)&m.pin_ids, (size_t)B * 4 * 3, cudaHostAllocDefault));
+  BK_CUDA(cudaHostAlloc((void**)&m.pin_ids, (size_t)B * 4 * 4, cudaHostAllocMapped));
+  memset(m.pin_ids, 0, (size_t)B * 4 * 4);
+  for (int i = 0; i < 2; i++) BK_CUDA(cudaEventCreateWithFlags(&m.pin_read[i], cudaEventDisableTiming));
+  {
+    void* dp = nullptr;
+    BK_CUDA(cudaHostGetDevicePointer(&dp, m.pin_ids, 0));
+    m.pin_dev = (uint64_t)(uintptr_t)dp;
+  }
   // one eager step sets the kernels' shared-memory attributes and validates every pointer, then the
   // state is cleared and the two parity graphs are captured
   TRY(enqueue_step(m, 0));
@@ -645,6 +663,10 @@ int32_t bkModelFinalize(uint64_t model) {
   TRY(reset_state(m));
   TRY(capture(m, 0));
   TRY(capture(m, 1));
+  if (m.tp == 1) {
+    TRY(capture(m, 0, true));
+    TRY(capture(m, 1, true));
+  }
   BK_CUDA(cudaStreamSynchronize(bk_ctx().stream));
   m.finalized = true;
   return BK_OK;
@@ -669,10 +691,10 @@ int32_t bkModelInfo(uint64_t model, int32_t* split_len, int32_t* attn_warps, int
   return BK_OK;
 }
 
-static int32_t launch_step(Model& m) {
+static int32_t launch_step(Model& m, bool host_tokens = false) {
   BkContext& c = bk_ctx();
   BK_ARG(m.steps < m.cfg.max_len, "bkDecodeStep: position %lld reached max_len=%d", m.steps, m.cfg.max_len);
-  BK_CUDA(cudaGraphLaunch(m.graph[m.conv_cur], c.stream));
+  BK_CUDA(cudaGraphLaunch((host_tokens && m.graph_host[m.conv_cur]) ? m.graph_host[m.conv_cur] : m.graph[m.conv_cur], c.stream));
   c.launches += m.graph_kernels;
   m.steps++;
   m.conv_cur ^= 1;
@@ -686,20 +708,37 @@ int32_t bkDecodeStep(uint64_t model, const int32_t* tokens, int32_t* out_ids, fl
   BK_ARG(m.finalized, "bkDecodeStep: model is not finalized");
   cudaStream_t st = bk_ctx().stream;
   const int B = m.B;
+  const bool mapped_io = m.tp == 1 && m.graph_host[0] != nullptr;
+  int32_t* const out_slot = m.pin_ids + 2 * B;   // ids out, then vals
   if (tokens) {
+    const int p = m.conv_cur;                     // the graph about to run reads ids slot p
+    int32_t* in_slot = m.pin_ids + (mapped_io ? p * B : 0);
+    if (mapped_io && m.pin_busy[p]) {              // the step before last may still be reading this slot
+      BK_CUDA(cudaEventSynchronize(m.pin_read[p]));
+      m.pin_busy[p] = false;
+    }
     for (int b = 0; b < B; b++) {
       BK_ARG(tokens[b] >= 0 && tokens[b] < m.cfg.vocab, "bkDecodeStep: token %d outside the vocabulary", tokens[b]);
-      m.pin_ids[b] = tokens[b];
+      in_slot[b] = tokens[b];
     }
-    BK_CUDA(cudaMemcpyAsync(bk_ptr<void>(m.ids), m.pin_ids, (size_t)B * 4, cudaMemcpyHostToDevice, st));
+    if (!mapped_io) BK_CUDA(cudaMemcpyAsync(bk_ptr<void>(m.ids), in_slot, (size_t)B * 4, cudaMemcpyHostToDevice, st));
+    TRY(launch_step(m, true));
+    if (mapped_io) {
+      BK_CUDA(cudaEventRecord(m.pin_read[p], st));
+      m.pin_busy[p] = true;
+    }
+  } else {
+    TRY(launch_step(m, false));
   }
-  TRY(launch_step(m));
   if (out_ids || out_vals) {
-    BK_CUDA(cudaMemcpyAsync(m.pin_ids + B, bk_ptr<void>(m.ids), (size_t)B * 4, cudaMemcpyDeviceToHost, st));
-    if (out_vals) BK_CUDA(cudaMemcpyAsync(m.pin_ids + 2 * B, bk_ptr<void>(m.val), (size_t)B * 4, cudaMemcpyDeviceToHost, st));
+    if (!mapped_io) {
+      BK_CUDA(cudaMemcpyAsync(out_slot, bk_ptr<void>(m.ids), (size_t)B * 4, cudaMemcpyDeviceToHost, st));
+      if (out_vals) BK_CUDA(cudaMemcpyAsync(out_slot + B, bk_ptr<void>(m.val), (size_t)B * 4, cudaMemcpyDeviceToHost, st));
+    }
     BK_CUDA(cudaStreamSynchronize(st));
-    if (out_ids) memcpy(out_ids, m.pin_ids + B, (size_t)B * 4);
-    if (out_vals) memcpy(out_vals, m.pin_ids + 2 * B, (size_t)B * 4);
+    m.pin_busy[0] = m.pin_busy[1] = false;
+    if (out_ids) memcpy(out_ids, out_slot, (size_t)B * 4);
+    if (out_vals) memcpy(out_vals, out_slot + B, (size_t)B * 4);
   }
   return BK_OK;
 }
@@ -756,11 +795,10 @@ int32_t bkModelPrefill(uint64_t model, const int32_t* tokens, int32_t T, int32_t
   m.steps += T;
   m.conv_cur ^= 1;
   if (out_ids || out_vals) {
-    BK_CUDA(cudaMemcpyAsync(m.pin_ids + B, bk_ptr<void>(m.ids), (size_t)B * 4, cudaMemcpyDeviceToHost, st));
-    if (out_vals) BK_CUDA(cudaMemcpyAsync(m.pin_ids + 2 * B, bk_ptr<void>(m.val), (size_t)B * 4, cudaMemcpyDeviceToHost, st));
+    // the argmax kernel left (id, logit) in the mapped pinned buffer
     BK_CUDA(cudaStreamSynchronize(st));
-    if (out_ids) memcpy(out_ids, m.pin_ids + B, (size_t)B * 4);
-    if (out_vals) memcpy(out_vals, m.pin_ids + 2 * B, (size_t)B * 4);
+    if (out_ids) memcpy(out_ids, m.pin_ids + 2 * B, (size_t)B * 4);
+    if (out_vals) memcpy(out_vals, m.pin_ids + 3 * B, (size_t)B * 4);
   }
   return BK_OK;
 }
@@ -804,8 +842,11 @@ int32_t bkModelDestroy(uint64_t model) {
   if (!model) return BK_OK;
   Model* m = as_model(model);
   cudaStreamSynchronize(bk_ctx().stream);
-  for (int i = 0; i < 2; i++)
+  for (int i = 0; i < 2; i++) {
     if (m->graph[i]) cudaGraphExecDestroy(m->graph[i]);
+    if (m->graph_host[i]) cudaGraphExecDestroy(m->graph_host[i]);
+    if (m->pin_read[i]) cudaEventDestroy(m->pin_read[i]);
+  }
   for (uint64_t p : m->owned) cudaFree(bk_ptr<void>(p));
   if (m->pin_ids) cudaFreeHost(m->pin_ids);
   delete m;

@@ -464,7 +464,8 @@ constexpr int kArgmaxBlocks = 64;
 // pos[b], which is how the model-level decode step feeds the next token without a host round trip.
 __global__ void __launch_bounds__(256) argmax_kernel(const float* logits, int V, int32_t* idx, float* val,
                                                      float* part_v, int32_t* part_i, unsigned int* counter,
-                                                     int32_t* pos, int32_t* hist, int hist_ld, int hist_rows) {
+                                                     int32_t* pos, int32_t* hist, int hist_ld, int hist_rows,
+                                                     int32_t* host_out) {
   __shared__ float sv[8];
   __shared__ int si[8];
   __shared__ bool last;
@@ -512,6 +513,10 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float* logits, int V,
     if (i == 0x7fffffff) i = 0;
     idx[b] = i;
     val[b] = v;
+    if (host_out) {   // pinned host memory mapped into the device: the result reaches the host without a copy engine
+      host_out[b] = i;
+      host_out[gridDim.y + b] = __float_as_int(v);
+    }
     counter[b] = 0;
     if (pos) {
       int pcur = pos[b];
@@ -690,7 +695,7 @@ int32_t bkArgmax(uint64_t logits, int32_t V, int32_t B, uint64_t idx, uint64_t v
 }  // extern "C"
 
 int32_t bk_argmax_launch(uint64_t logits, int32_t V, int32_t B, uint64_t idx, uint64_t val, uint64_t scratch,
-                         uint64_t pos, uint64_t hist, int32_t hist_ld, int32_t hist_rows) {
+                         uint64_t pos, uint64_t hist, int32_t hist_ld, int32_t hist_rows, uint64_t host_out) {
   BK_REQUIRE_INIT();
   BK_ARG(V > 0 && B > 0 && logits && idx && val && scratch, "bkArgmax: bad arguments");
   // scratch: [B][64] f32, [B][64] i32, [B] counters (zero before first use; the kernel re-zeroes them)
@@ -701,7 +706,7 @@ int32_t bk_argmax_launch(uint64_t logits, int32_t V, int32_t B, uint64_t idx, ui
   if (blocks > kArgmaxBlocks) blocks = kArgmaxBlocks;
   BK_CUDA(bk_launch_pdl(argmax_kernel, dim3(blocks, B), dim3(256), 0, bk_ptr<float>(logits), V, bk_ptr<int32_t>(idx),
                         bk_ptr<float>(val), pv, pi, cnt, bk_ptr<int32_t>(pos), bk_ptr<int32_t>(hist), hist_ld,
-                        hist_rows));
+                        hist_rows, bk_ptr<int32_t>(host_out)));
   BK_CHECK_LAUNCH();
   return BK_OK;
 }
@@ -744,7 +749,7 @@ extern "C" int32_t bkArgmaxStatic(uint64_t logits, int32_t V, int32_t B, uint64_
   int blocks = (V + 2047) / 2048;
   if (blocks > kArgmaxBlocks) blocks = kArgmaxBlocks;
   BK_CUDA(bk_launch_pdl(argmax_kernel, dim3(blocks, B), dim3(256), 0, bk_ptr<float>(logits), V, bk_ptr<int32_t>(idx),
-                        bk_ptr<float>(val), pv, pi, cnt, (int32_t*)nullptr, (int32_t*)nullptr, 0, 0));
+                        bk_ptr<float>(val), pv, pi, cnt, (int32_t*)nullptr, (int32_t*)nullptr, 0, 0, (int32_t*)nullptr));
   BK_CHECK_LAUNCH();
   return BK_OK;
 }
