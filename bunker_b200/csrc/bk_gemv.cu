@@ -1,4 +1,5 @@
-// bk_gemv.cu -- Q4_K x Q8_1 dequant-GEMV for batch 1..8 (HBM-bound path).
+// bk_gemv.cu -- Q4_K x Q8_1 dequant-GEMV: the batch-1 kernel (also batch 2 when K is too wide for the tensor-core
+// kernel of bk_gemv_mma.cu) and the host-side launch logic of both kernels.
 //
 // Replaces the bf16 tt.dot GEMMs of bunker's decode loop (buildMM / buildGateSwiglu,
 // prototypes/decode.ts:101-186; emitGemm, src/fusion.ts:276-293) with integer block
@@ -17,11 +18,13 @@
 // and the xor-butterfly over the 32 lanes.  The order is fixed so a host can
 // reproduce the result bit for bit.
 //
-// Weight staging.  One CTA per SM.  Each warp owns a ring of shared-memory stages; lane 0 fills a
-// stage with two bulk async copies (cp.async.bulk, completion on an mbarrier), one per row of the task.
-// The copies of a warp's first tasks are issued before the programmatic-dependency wait, so the weight
-// stream of this launch is in flight while the previous kernel drains and while the activation
-// prologue runs; the dot products then read weights from shared memory.
+// Weight staging.  One CTA per SM owning a contiguous range of rows, handled in groups of G rows per warp.
+// Every group has a slot in shared memory (all groups at once when the CTA's rows fit, else a per-warp ring)
+// that lane 0 fills with one bulk async copy per contiguous run of rows (cp.async.bulk, completion on an
+// mbarrier).  The first copies are issued before the programmatic-dependency wait, so the weight stream of
+// this launch is in flight while the previous kernel drains and while the activation prologue runs; the
+// dot products then read weights from shared memory.  High nibbles stay in place (16*q as unsigned bytes);
+// the staged scale of odd blocks carries the 1/16.
 //
 // The activation lives in shared memory for the whole CTA: int8 quants padded to
 // 80 bytes per 64 (conflict-free 128-bit reads at lane stride), plus per-block
