@@ -179,7 +179,6 @@ __device__ void prologue_bf16(const GemvParams& p, const int B, uint32_t* xs, fl
   const int K = p.K, nblk = K / 32, nchunk = K / 8;
   const uint16_t* x = reinterpret_cast<const uint16_t*>(p.x);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const bool one_pass = nchunk <= kThreads;   // every chunk has its own thread among the first 256: keep it in registers
   for (int b = 0; b < B; b++) {
     const uint16_t* row = x + (size_t)b * K;
     float rstd = 1.0f;
@@ -239,7 +238,6 @@ __device__ void prologue_bf16(const GemvParams& p, const int B, uint32_t* xs, fl
       }
       quant_chunk<false>(p, y, q, b, nblk, xs, d8s, s8s);
     }
-    (void)one_pass;
   }
 }
 

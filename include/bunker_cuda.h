@@ -327,6 +327,9 @@ BK_API int32_t bkLaunch(int32_t op, const uint64_t* slots, int32_t nslots);
 #define BK_OP_CONV1D 5
 #define BK_OP_ARGMAX 6
 #define BK_OP_QUANT_Q8_1 7
+#define BK_OP_HEADNORM_ROPE 8 /* qnorm+rope / knorm+ropek */
+#define BK_OP_GDN 9           /* conv1d_decode + gdn_delta_rule + gated norm */
+#define BK_OP_ATTN 10         /* qnorm/knorm/rope + KV append + fa2_attn + gate */
 
 #ifdef __cplusplus
 }

@@ -313,3 +313,51 @@ def test_culaunch_surface(bk):
     assert R.cuLaunch(k, [1, 1, 1], [128, 1, 1], [dx, dw]) == R.BK_ERR_ARG  # wrong slot count -> rc, no raise
     for p in (dx, dw, dy):
         R.cuFree(p)
+
+
+def test_culaunch_fused_ops(bk):
+    """gdn_delta_rule, fa2_attn and headnorm_rope through cuLaunch slot lists give the results of the struct calls."""
+    # GDN
+    B = 2
+    c = synth.gdn_case(B, Hk=2, Hv=4, config_id=61)
+    Hk, Hv = 2, 4
+    Cw = 2 * Hk * 128 + Hv * 128
+    d = {k: dev(v) for k, v in c.items() if isinstance(v, np.ndarray)}
+    cs_new, out = R.DeviceBuffer(B * 3 * Cw * 2), R.DeviceBuffer(B * Hv * 128 * 2)
+    k = R.loadOp("gdn_delta_rule")
+    rc = R.cuLaunch(k, [1, 1, 1], [1, 1, 1], [d["qkv"].ptr, d["z"].ptr, d["a"].ptr, d["b"].ptr, d["conv_w"].ptr,
+                                              d["conv_state"].ptr, cs_new.ptr, d["A_log"].ptr, d["dt_bias"].ptr,
+                                              d["norm_w"].ptr, d["S"].ptr, d["S"].ptr, out.ptr, B, Hk, Hv, 1, 0])
+    assert rc == 0, R.last_error()
+    _, w_cs, w_S, _, w_out = _gdn_oracle(c)
+    assert_same_bits(out.download(np.uint16, (B, Hv * 128)), w_out, "gdn via cuLaunch")
+    assert_same_bits(d["S"].download(np.float32, (B, Hv, 128, 128)), w_S, "state via cuLaunch")
+    assert_same_bits(cs_new.download(np.uint16, (B, 3, Cw)), w_cs, "conv state via cuLaunch")
+    # attention
+    B, L = 2, 100
+    cos_t, sin_t = ops.rope_tables(128)
+    ca = synth.attn_case(B, L, max_len=128, config_id=62)
+    Hq, Hkv, HD, ml = ca["Hq"], ca["Hkv"], ca["HD"], ca["max_len"]
+    split_len, W = ops.attn_plan(L, B, Hkv)
+    da = {kk: dev(v) for kk, v in ca.items() if isinstance(v, np.ndarray)}
+    dc, ds = dev(cos_t), dev(sin_t)
+    scratch = R.DeviceBuffer.zeros(ops.attn_scratch_bytes(B, Hq, HD, ml, split_len))
+    o = R.DeviceBuffer(B * Hq * HD * 2)
+    k = R.loadOp("fa2_attn")
+    rc = R.cuLaunch(k, [1, 1, 1], [1, 1, 1], [da["qg"].ptr, da["k"].ptr, da["v"].ptr, da["q_norm_w"].ptr, da["k_norm_w"].ptr,
+                                              dc.ptr, ds.ptr, da["k_cache"].ptr, da["v_cache"].ptr, da["pos"].ptr, o.ptr,
+                                              scratch.ptr, B, Hq, Hkv, HD, 32, ml, split_len, int(ca["pos"].max()),
+                                              1.0 / 16.0, 0])
+    assert rc == 0, R.last_error()
+    _, _, _, want = _attn_oracle(ca, cos_t, sin_t, split_len, W)
+    assert_same_bits(o.download(np.uint16, (B, Hq * HD)), want, "attention via cuLaunch")
+    assert R.cuLaunch(k, [1, 1, 1], [1, 1, 1], [1, 2, 3]) == R.BK_ERR_ARG
+    # head norm + rope
+    rng = np.random.default_rng(63)
+    nh = 4
+    x, w = synth.normal_bf16(rng, (B, nh * HD)), synth.normal_bf16(rng, (HD,), 0.02)
+    pos = np.array([3, 77], np.int32)
+    dx, dw, dp, y = dev(x), dev(w), dev(pos), R.DeviceBuffer(B * nh * HD * 2)
+    rc = R.cuLaunch(R.loadOp("headnorm_rope"), [1, 1, 1], [1, 1, 1], [dx.ptr, HD, dw.ptr, dc.ptr, ds.ptr, 32, dp.ptr, B, nh, HD, y.ptr])
+    assert rc == 0, R.last_error()
+    assert_same_bits(y.download(np.uint16, (B, nh * HD)), O.headnorm_rope(x, HD, w, cos_t, sin_t, pos, nh, HD), "headnorm_rope via cuLaunch")
