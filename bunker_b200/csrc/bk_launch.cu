@@ -52,6 +52,9 @@ extern "C" int32_t bkLaunch(int32_t op, const uint64_t* s, int32_t n) {
     case BK_OP_QUANT_Q8_1:  // x_f32, out, K, B
       BK_ARG(n == 4, "bkLaunch(quant_q8_1): expected 4 slots, got %d", n);
       return bkQuantQ8_1(s[0], (int32_t)s[2], (int32_t)s[3], s[1]);
+    case BK_OP_QUANT_Q8_1_BF16:  // x_bf16, out, K, B
+      BK_ARG(n == 4, "bkLaunch(quant_q8_1_bf16): expected 4 slots, got %d", n);
+      return bkQuantQ8_1Bf16(s[0], (int32_t)s[2], (int32_t)s[3], s[1]);
     case BK_OP_HEADNORM_ROPE:  // x, in_stride, w, cos_t, sin_t, rot_half, pos, B, nheads, HD, out
       BK_ARG(n == 11, "bkLaunch(headnorm_rope): expected 11 slots, got %d", n);
       return bkHeadNormRope(s[0], (int32_t)s[1], s[2], s[3], s[4], (int32_t)s[5], s[6], (int32_t)s[7], (int32_t)s[8],

@@ -32,7 +32,7 @@ BK_Q8_BLOCKS, BK_Q8_STAGED = 0, 1
 BK_EPI_F32, BK_EPI_BF16, BK_EPI_ADD_BF16, BK_EPI_SWIGLU = 0, 1, 2, 3
 
 BK_OP_EMBED, BK_OP_RMSNORM, BK_OP_GEMV, BK_OP_SWIGLU, BK_OP_CONV1D, BK_OP_ARGMAX, BK_OP_QUANT_Q8_1 = range(1, 8)
-BK_OP_HEADNORM_ROPE, BK_OP_GDN, BK_OP_ATTN = 8, 9, 10
+BK_OP_HEADNORM_ROPE, BK_OP_GDN, BK_OP_ATTN, BK_OP_QUANT_Q8_1_BF16 = 8, 9, 10, 11
 
 
 class BunkerCudaError(RuntimeError):
@@ -266,7 +266,8 @@ class LoadedKernel:
 _OPS = {"embed": BK_OP_EMBED, "rmsnorm": BK_OP_RMSNORM, "gemm": BK_OP_GEMV, "swiglu": BK_OP_SWIGLU,
         "conv1d_decode": BK_OP_CONV1D, "argmax": BK_OP_ARGMAX, "quant_q8_1": BK_OP_QUANT_Q8_1,
         # fused ops: q/k head norm + rope; conv1d + gdn_delta_rule + gated norm; norms + rope + KV append + fa2_attn
-        "headnorm_rope": BK_OP_HEADNORM_ROPE, "gdn_delta_rule": BK_OP_GDN, "fa2_attn": BK_OP_ATTN}
+        "headnorm_rope": BK_OP_HEADNORM_ROPE, "gdn_delta_rule": BK_OP_GDN, "fa2_attn": BK_OP_ATTN,
+        "quant_q8_1_bf16": BK_OP_QUANT_Q8_1_BF16}
 
 
 def loadOp(name: str) -> LoadedKernel:

@@ -330,6 +330,7 @@ BK_API int32_t bkLaunch(int32_t op, const uint64_t* slots, int32_t nslots);
 #define BK_OP_HEADNORM_ROPE 8 /* qnorm+rope / knorm+ropek */
 #define BK_OP_GDN 9           /* conv1d_decode + gdn_delta_rule + gated norm */
 #define BK_OP_ATTN 10         /* qnorm/knorm/rope + KV append + fa2_attn + gate */
+#define BK_OP_QUANT_Q8_1_BF16 11 /* quant_q8_1 on bf16 rows (the activation format between ops) */
 
 #ifdef __cplusplus
 }

@@ -137,6 +137,31 @@ def test_prefill_equals_token_by_token(bk, B, T, chunk):
     gm.destroy()
 
 
+@pytest.mark.parametrize("B", [1, 2])
+def test_per_op_runner_equals_step_graph(bk, B):
+    """A host that schedules every op itself through cuLaunch (bunker's runner shape) gets the bits of the library's
+    fused step graph and of the oracle: 4 prompt tokens + 6 greedy steps, tokens and final logits."""
+    from bunker_b200.runner import OpRunner
+    cfg = M.CONFIG_TINY.with_(max_len=32)
+    w = M.synth_weights(cfg, seed=60 + B)
+    gm = M.DecodeModel(cfg, w, batch=B)
+    rn = OpRunner(cfg, w, batch=B)
+    info = gm.info()
+    assert rn.split_len == info["split_len"]
+    om = OracleModel(cfg, w, batch=B, split_len=info["split_len"], attn_warps=info["attn_warps"])
+    prompt = np.random.default_rng(7).integers(0, cfg.vocab, (4, B)).astype(np.int32)
+    ids_g = ids_r = ids_o = None
+    for t in range(10):
+        ids_o, val_o = om.step(prompt[t] if t < 4 else ids_o)
+        ids_g, val_g = gm.step(prompt[t] if t < 4 else ids_g)
+        ids_r, val_r = rn.step(prompt[t] if t < 4 else ids_r)
+        assert np.array_equal(ids_r, ids_o) and np.array_equal(ids_g, ids_o), f"step {t}"
+        assert_same_bits(val_r, val_o, f"max logit at step {t}")
+    assert_same_bits(rn.logits_host(), om.logits, "per-op logits vs oracle")
+    assert_same_bits(rn.logits_host(), gm.logits(), "per-op logits vs step graph")
+    gm.destroy()
+
+
 def test_scaled_model_shapes_first_steps_match_oracle(bk):
     """configs[4] shapes (hidden 5120, 16/48 GDN heads, 24/4 attention heads of 256, FFN 17408 = 68 superblocks) on a
     4-layer stack with a reduced vocabulary: exercises K = 5120, 6144 and 17408 and group size 6 in attention."""
