@@ -33,7 +33,7 @@ sys.path.insert(0, ROOT)
 PROMPT_LEN = 32
 # dram__bytes_read.sum + dram__bytes_write.sum of one lm_head GEMV launch at batch 1 (ncu capture summarised in
 # profiles/gemv_q4k_lmhead_b1.md)
-NCU_GEMV_LMHEAD_TRAFFIC = 179980544
+NCU_GEMV_LMHEAD_TRAFFIC = 180382976
 METRIC = "q4k_hybrid_decode_tok_s"
 
 
