@@ -87,3 +87,34 @@ def test_oracle_model_tp_emulation_close_to_single_rank():
         a.step(prompt[t]); b.step(prompt[t])
     rel = np.abs(a.logits - b.logits).max() / np.abs(a.logits).max()
     assert rel < 2e-2        # different Q8_1 block boundaries never arise (slices are whole superblocks); only sum order differs
+
+
+def test_staged_image_layout_round_trip():
+    """The staged activation layout as documented in the header, built here in numpy from oracle Q8_1 blocks, unpacks to
+    the same quants, block scales and d8*sum(q) (host-side helper ops.staged_to_blocks)."""
+    from bunker_b200 import ops
+    from oracle import oracle as O
+    B, K = 3, 512
+    rng = np.random.default_rng(5)
+    x = rng.normal(0, 1, (B, K)).astype(np.float32)
+    blocks = O.q8_1_quantize(x)                                   # [B, K/32, 36]
+    q = blocks[:, :, :32].view(np.int8)
+    d8 = O.q8_1_scales(blocks)
+    s8 = d8 * q.astype(np.int32).sum(-1).astype(np.float32)
+    rw = K // 4 + 8
+    words = np.zeros((B, rw), np.uint32)
+    qw = np.ascontiguousarray(q).view(np.uint32).reshape(B, K // 32, 8)
+    for w in range(8):
+        pos = (w & 3) * 2 + (w >> 2)
+        words[:, :K // 4].reshape(B, K // 32, 8)[:, :, pos] = qw[:, :, w]
+    sc = np.zeros((K // 64, 8, 4), np.float32)
+    for b in range(B):
+        sc[:, b, 0] = d8[b, 0::2]
+        sc[:, b, 1] = d8[b, 1::2] * np.float32(0.0625)
+        sc[:, b, 2] = s8[b, 0::2]
+        sc[:, b, 3] = s8[b, 1::2]
+    img = np.concatenate([words.view(np.uint8).ravel(), sc.view(np.uint8).ravel()])
+    q2, d2, s2 = ops.staged_to_blocks(img, K, B)
+    assert np.array_equal(q2.reshape(B, K // 32, 32), q)
+    assert np.array_equal(d2.view(np.uint32), d8.view(np.uint32))
+    assert np.array_equal(s2.view(np.uint32), s8.astype(np.float32).view(np.uint32))
