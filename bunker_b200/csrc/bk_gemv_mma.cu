@@ -50,6 +50,8 @@ constexpr int kTabBytes = kChunk * 16 * 24;     // per warp: float4 + float2 per
 
 // Shared memory: xs [B][K/4 + 8] words | sc4 [K/64][8] float4 | red[72] | bars[n_slots] | part[2][tiles][4 p][16][8] f32 |
 // header tables [warps][kTabBytes] | tile slots [n_slots][16 rows][rowb+16].
+// ALIGNED: K is a multiple of 2048 (whole groups of 8 superblocks), so the per-superblock range checks fold away.
+template <bool ALIGNED>
 __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kernel(const GemvParams p, const int B) {
   bk_pdl_trigger();
   bk_stamp(p.trace, 0);
@@ -156,12 +158,12 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
 #pragma unroll
         for (int h = 0; h < 8 / kChunk; h++) {
           const int sbase = s0 + kChunk * h;
-          if (sbase < nsb) {
+          if (ALIGNED || sbase < nsb) {
             __syncwarp();   // the previous chunk's table has been read by every lane
 #pragma unroll
             for (int k = 0; k < kChunk * 16 / 32; k++) {
               const int e = lane + 32 * k, row = e & 15, s = sbase + (e >> 4);
-              if (s < nsb) {
+              if (ALIGNED || s < nsb) {
                 const uint4 hw = *reinterpret_cast<const uint4*>(tile + row * rstride + s * 144);
                 uint32_t sc2, mn2;
                 bk_q4k_scale_min_pair(hw.y, hw.z, hw.w, tp, sc2, mn2);
@@ -174,7 +176,7 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
 #pragma unroll
             for (int sl = 0; sl < kChunk; sl++) {
               const int s = sbase + sl;
-              if (s < nsb) {
+              if (ALIGNED || s < nsb) {
                 const uint32_t qa0 = *reinterpret_cast<const uint32_t*>(rowA + s * 144);
                 const uint32_t qa2 = *reinterpret_cast<const uint32_t*>(rowA + s * 144 + 16);
                 const uint32_t qb0 = *reinterpret_cast<const uint32_t*>(rowB + s * 144);
@@ -295,12 +297,14 @@ int32_t bk_gemv_mma_launch(void* params, int K, int B, int vrows, bool has_swigl
   p.x_row_words = K / 4 + 8;   // 8 words of padding: the 64-bit loads of a half-warp (4 columns x 4 j) tile the 32 banks
   p.x_scale_ld = 0;            // scales live in the float4 layout of the tensor-core path
   const size_t smem = mma_fixed_smem(K, B, n_slots, tpr) + (size_t)n_slots * tile_bytes;
-  static size_t configured = 0;
-  if (smem > configured) {
-    BK_CUDA(cudaFuncSetAttribute(gemv_q4k_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = smem;
+  static size_t configured[2] = {0, 0};
+  const bool aligned = (K / 256) % 8 == 0;
+  auto kernel = aligned ? gemv_q4k_mma_kernel<true> : gemv_q4k_mma_kernel<false>;
+  if (smem > configured[aligned]) {
+    BK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured[aligned] = smem;
   }
-  BK_CUDA(bk_launch_pdl(gemv_q4k_mma_kernel, dim3(grid), dim3(tpr * 128), smem, p, B));
+  BK_CUDA(bk_launch_pdl(kernel, dim3(grid), dim3(tpr * 128), smem, p, B));
   BK_CHECK_LAUNCH();
   return BK_OK;
 }
