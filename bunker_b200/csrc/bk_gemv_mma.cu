@@ -51,7 +51,8 @@ constexpr int kTabBytes = kChunk * 16 * 24;     // per warp: float4 + float2 per
 // Shared memory: xs [B][K/4 + 8] words | sc4 [K/64][8] float4 | red[72] | bars[n_slots] | part[2][tiles][4 p][16][8] f32 |
 // header tables [warps][kTabBytes] | tile slots [n_slots][16 rows][rowb+16].
 // ALIGNED: K is a multiple of 2048 (whole groups of 8 superblocks), so the per-superblock range checks fold away.
-template <bool ALIGNED>
+// CARRY: a part of a launch cut along K (class accumulators come from / go to a scratch buffer).
+template <bool ALIGNED, bool CARRY>
 __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kernel(const GemvParams p, const int B) {
   bk_pdl_trigger();
   bk_stamp(p.trace, 0);
@@ -151,7 +152,7 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
 #pragma unroll
       for (int c = 0; c < 8; c++) {
         float4 v4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        if (p.carry_in) v4 = __ldcg(reinterpret_cast<const float4*>(p.carry_in) + carry_idx + c * 32);
+        if (CARRY && p.carry_in) v4 = __ldcg(reinterpret_cast<const float4*>(p.carry_in) + carry_idx + c * 32);
         P[c][0] = v4.x; P[c][1] = v4.y; P[c][2] = v4.z; P[c][3] = v4.w;
       }
       for (int s0 = 0; s0 < nsb; s0 += 8) {
@@ -198,7 +199,7 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
           }
         }
       }
-      if (p.carry_out) {
+      if (CARRY && p.carry_out) {
 #pragma unroll
         for (int c = 0; c < 8; c++)
           reinterpret_cast<float4*>(p.carry_out)[carry_idx + c * 32] = make_float4(P[c][0], P[c][1], P[c][2], P[c][3]);
@@ -226,7 +227,7 @@ __global__ void __launch_bounds__(kMaxTilesPerRound * 128, 1) gemv_q4k_mma_kerne
       // next round only after every warp of the group has passed that round's barrier, i.e. finished reading here.
       const int g = tid & 127, er = g >> 3, ec = g & 7;
       const float* pr = part + (size_t)(rd & 1) * (tpr * 4 * 128) + (size_t)(tq * 4) * 128 + er * 8 + ec;
-      if (ec < B && !p.carry_out) {
+      if (ec < B && !(CARRY && p.carry_out)) {
         const int nr = min(kTileRows, n_rows_cta - t * kTileRows);
         const float y = __fadd_rn(__fadd_rn(pr[0], pr[2 * 128]), __fadd_rn(pr[1 * 128], pr[3 * 128]));
         if (swiglu) {
@@ -297,12 +298,15 @@ int32_t bk_gemv_mma_launch(void* params, int K, int B, int vrows, bool has_swigl
   p.x_row_words = K / 4 + 8;   // 8 words of padding: the 64-bit loads of a half-warp (4 columns x 4 j) tile the 32 banks
   p.x_scale_ld = 0;            // scales live in the float4 layout of the tensor-core path
   const size_t smem = mma_fixed_smem(K, B, n_slots, tpr) + (size_t)n_slots * tile_bytes;
-  static size_t configured[2] = {0, 0};
+  static size_t configured[4] = {0, 0, 0, 0};
   const bool aligned = (K / 256) % 8 == 0;
-  auto kernel = aligned ? gemv_q4k_mma_kernel<true> : gemv_q4k_mma_kernel<false>;
-  if (smem > configured[aligned]) {
+  const bool carry = p.carry_in != nullptr || p.carry_out != nullptr;
+  auto kernel = carry ? (aligned ? gemv_q4k_mma_kernel<true, true> : gemv_q4k_mma_kernel<false, true>)
+                      : (aligned ? gemv_q4k_mma_kernel<true, false> : gemv_q4k_mma_kernel<false, false>);
+  const int ki = (carry ? 2 : 0) + (aligned ? 1 : 0);
+  if (smem > configured[ki]) {
     BK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured[aligned] = smem;
+    configured[ki] = smem;
   }
   BK_CUDA(bk_launch_pdl(kernel, dim3(grid), dim3(tpr * 128), smem, p, B));
   BK_CHECK_LAUNCH();
