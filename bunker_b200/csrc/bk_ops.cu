@@ -585,6 +585,24 @@ int32_t bkRmsNormQuantQ8_1(uint64_t x, uint64_t w, int32_t K, int32_t B, float e
   return bk_quant_rows_launch(x, w, K, B, eps, out, layout, nullptr);
 }
 
+int32_t bkReduceRmsNormQuantQ8_1(uint64_t words, int32_t n_ranks, uint64_t stride_words, uint64_t epoch, uint32_t tag_add,
+                                 uint64_t residual, uint64_t sum_out, uint64_t w, int32_t K, int32_t B, float eps, uint64_t out,
+                                 int32_t layout) {
+  BK_REQUIRE_INIT();
+  BK_ARG(words && epoch && residual && sum_out && w && n_ranks >= 1 && n_ranks <= 8 && (words & 15) == 0 && stride_words % 2 == 0,
+         "bkReduceRmsNormQuantQ8_1: bad arguments");
+  BkReduce rd;
+  memset(&rd, 0, sizeof(rd));
+  rd.src = bk_ptr<uint2>(words);
+  rd.epoch = bk_ptr<unsigned int>(epoch);
+  rd.res = bk_ptr<uint16_t>(residual);
+  rd.out = bk_ptr<uint16_t>(sum_out);
+  rd.stride = stride_words;
+  rd.tag_add = tag_add;
+  rd.n = n_ranks;
+  return bk_quant_rows_launch(sum_out, w, K, B, eps, out, layout, &rd);
+}
+
 uint64_t bkStagedBytes(int32_t K, int32_t B) { return (K > 0 && B > 0) ? (uint64_t)bk_staged_total_bytes(K, B) : 0; }
 
 int32_t bkSwiglu(uint64_t g_f32, uint64_t u_f32, int32_t n, uint64_t out_bf16) {

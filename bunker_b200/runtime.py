@@ -113,6 +113,7 @@ SIGNATURES = {
     "bkRmsNorm": (_I32, [_U64, _U64, _I32, _I32, _F32, _U64]),
     "bkRmsNormQuantQ8_1": (_I32, [_U64, _U64, _I32, _I32, _F32, _U64, _I32]),
     "bkStagedBytes": (_U64, [_I32, _I32]),
+    "bkReduceRmsNormQuantQ8_1": (_I32, [_U64, _I32, _U64, _U64, C.c_uint32, _U64, _U64, _U64, _I32, _I32, _F32, _U64, _I32]),
     "bkTuneGemvRing": (_I32, [_I32, _I32, _I32]),
     "bkSwiglu": (_I32, [_U64, _U64, _I32, _U64]),
     "bkConv1dStep": (_I32, [_U64, _U64, _U64, _I32, _I32, _U64, _U64]),

@@ -160,6 +160,13 @@ BK_API int32_t bkRmsNorm(uint64_t x, uint64_t w, int32_t H, int32_t B, float eps
  * x [B][K] -> Q8_1 of bf16((x*rstd)*(1+w)) in `layout` (BK_Q8_BLOCKS or BK_Q8_STAGED); w = 0 skips the norm
  * (plain bf16 -> Q8_1).  Used between ops at batch >= 2. */
 BK_API int32_t bkRmsNormQuantQ8_1(uint64_t x, uint64_t w, int32_t K, int32_t B, float eps, uint64_t out, int32_t layout);
+/* The consumer side of the tensor-parallel exchange as a stand-alone call (no counterpart in the reference; the model
+ * enqueues it internally at batch >= 2): `words` holds, for each of n_ranks ranks at a stride of stride_words, B*K 8-byte
+ * words {f32 partial sum, tag}; the launch polls (bounded) until every word carries the tag *epoch * 256 + tag_add, adds the
+ * partials in rank order, adds the bf16 residual, rounds to bf16 (written to sum_out), then RMSNorm(w) and Q8_1 as above. */
+BK_API int32_t bkReduceRmsNormQuantQ8_1(uint64_t words, int32_t n_ranks, uint64_t stride_words, uint64_t epoch, uint32_t tag_add,
+                                        uint64_t residual, uint64_t sum_out, uint64_t w, int32_t K, int32_t B, float eps,
+                                        uint64_t out, int32_t layout);
 /* emitSwiGLU (src/fusion.ts:324-330): out bf16 [n] from f32 g,u */
 BK_API int32_t bkSwiglu(uint64_t g_f32, uint64_t u_f32, int32_t n, uint64_t out_bf16);
 /* emitConv1d (src/emitters.ts:48-72): state [B][3][C] bf16 oldest first, w [C][4] bf16 */

@@ -361,3 +361,26 @@ def test_culaunch_fused_ops(bk):
     rc = R.cuLaunch(R.loadOp("headnorm_rope"), [1, 1, 1], [1, 1, 1], [dx.ptr, HD, dw.ptr, dc.ptr, ds.ptr, 32, dp.ptr, B, nh, HD, y.ptr])
     assert rc == 0, R.last_error()
     assert_same_bits(y.download(np.uint16, (B, nh * HD)), O.headnorm_rope(x, HD, w, cos_t, sin_t, pos, nh, HD), "headnorm_rope via cuLaunch")
+
+
+@pytest.mark.parametrize("n_ranks", [1, 2, 3, 4, 8])
+def test_exchange_reduce_all_rank_counts_on_one_gpu(bk, n_ranks):
+    """The consumer of the tensor-parallel exchange with the ranks' tagged words laid out by the host: sum in rank order +
+    residual -> bf16 -> RMSNorm -> Q8_1, for every rank count (pairs of ranks per polling pass, odd tail included)."""
+    B, K = 3, 2048
+    rng = np.random.default_rng(300 + n_ranks)
+    parts = rng.normal(0, 1, (n_ranks, B, K)).astype(np.float32)
+    res, w = synth.normal_bf16(rng, (B, K)), synth.normal_bf16(rng, (K,), 0.02)
+    epoch, tag_add = 7, 5
+    tag = epoch * 256 + tag_add
+    stride = B * K + 64          # words between ranks (padded)
+    words = np.zeros((n_ranks, stride, 2), np.uint32)
+    words[:, :B * K, 0] = parts.reshape(n_ranks, -1).view(np.uint32)
+    words[:, :B * K, 1] = tag
+    dw_, de, dres, dnw = dev(words), dev(np.array([epoch], np.uint32)), dev(res), dev(w)
+    dsum, dq = R.DeviceBuffer.zeros(B * K * 2), R.DeviceBuffer(B * K // 32 * 36)
+    R._check(R.cu().bkReduceRmsNormQuantQ8_1(dw_.ptr, n_ranks, stride, de.ptr, tag_add, dres.ptr, dsum.ptr, dnw.ptr, K, B, 1e-6,
+                                             dq.ptr, R.BK_Q8_BLOCKS))
+    want_sum = O.epilogue_add(O.sum_ranks(parts), res)
+    assert_same_bits(dsum.download(np.uint16, (B, K)), want_sum, "sum of the ranks + residual")
+    assert_same_bits(dq.download(np.uint8, (B, K // 32, 36)), O.q8_1_quantize_bf16(O.rmsnorm(want_sum, w)), "norm + Q8_1")
