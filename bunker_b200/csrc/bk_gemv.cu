@@ -738,11 +738,23 @@ int32_t bk_gemv_launch_tp(const bkGemvArgs& a, const BkPush* push, const BkReduc
   p.depth = depth;
   size_t smem = gemv_fixed_smem(a.K, a.B, n_slots) + (size_t)n_slots * G * rowb;
   int threads = nw * 32;
-  if (a.B <= 2) {  // the occupancy classes assume the 64-register build of the small-batch kernel
+  {
     if (class_a) {
       if (smem < limit / 2 + 2048) smem = limit / 2 + 2048;   // > half: one class-A CTA per SM
     } else if (smem <= limit / 2 - 4096) {
-      threads = 18 * 32;                                        // > half of the registers: one class-B CTA per SM
+      // > half of the register file: one class-B CTA per SM.  18 warps at the 64 registers the kernel is built with;
+      // should a compiler allocate fewer, as many warps more as that takes.
+      static int regs = 0;
+      if (!regs) {
+        cudaFuncAttributes fa;
+        BK_CUDA(cudaFuncGetAttributes(&fa, gemv_q4k_kernel<1, gemv_gmax(1), false>));
+        regs = fa.numRegs > 0 ? fa.numRegs : 64;
+      }
+      const int per_warp = (regs * 32 + 255) / 256 * 256;
+      int wb = 32768 / per_warp + 1;
+      if (wb < 18) wb = 18;
+      if (wb > 32) wb = 32;
+      threads = wb * 32;
     }
   }
   if (ctas_out) *ctas_out = grid;
