@@ -344,6 +344,32 @@ BK_DEVINL void bk_q4k_scale_min_pair(uint32_t w0, uint32_t w1, uint32_t w2, int 
   mn2 = p >= 2 ? mn_hi : mn_lo;
 }
 
+// One 64-weight unit u (sub-blocks 2p, 2p+1 of superblock u>>2, p = u&3) of a Q4_K row dequantised to bf16:
+// dl = d*sc, ml = dmin*m, w = dl*q - ml, each product and the difference rounded once (emitEmbed, src/emitters.ts:31-45,
+// on the tied Q4_K table).
+BK_DEVINL void bk_q4k_unit_to_bf16(const uint8_t* row, int u, uint16_t* o) {
+  const uint8_t* sb = row + (size_t)(u >> 2) * 144;
+  const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(sb));
+  const uint4* q = reinterpret_cast<const uint4*>(sb + 16 + (u & 3) * 32);
+  const uint4 qa = __ldg(q), qb = __ldg(q + 1);
+  const int p = u & 3;
+  const float d = bk_f16_to_f32((uint16_t)(hdr.x & 0xffffu)), dmin = bk_f16_to_f32((uint16_t)(hdr.x >> 16));
+  int sc0, mn0, sc1, mn1;
+  bk_q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * p, sc0, mn0);
+  bk_q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * p + 1, sc1, mn1);
+  const float dl0 = __fmul_rn(d, (float)sc0), ml0 = __fmul_rn(dmin, (float)mn0);
+  const float dl1 = __fmul_rn(d, (float)sc1), ml1 = __fmul_rn(dmin, (float)mn1);
+  const uint32_t qw[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+  for (int k = 0; k < 8; k++)
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      const uint32_t byte = (qw[k] >> (8 * e)) & 0xffu;
+      o[k * 4 + e] = bk_f32_to_bf16(__fsub_rn(__fmul_rn(dl0, (float)(byte & 15u)), ml0));
+      o[32 + k * 4 + e] = bk_f32_to_bf16(__fsub_rn(__fmul_rn(dl1, (float)(byte >> 4)), ml1));
+    }
+}
+
 BK_DEVINL int bk_dp4a(uint32_t a, uint32_t b, int c) {
   // a: four unsigned bytes (nibble values), b: four signed bytes
   int d;

@@ -155,11 +155,18 @@ __device__ __forceinline__ void load_chunk_bf16(const uint16_t* row, int q, floa
 
 // chunk q (8 values) of batch row b.  SRC 0: from the bf16 row.  SRC 1: from the ranks' partial sums + residual
 // (tensor-parallel reduce; also writes the bf16 result to p.red.out).  SRC 2: from p.red.out as written by CTA 0 of
-// this same launch (L2 loads: the L1 of this SM knows nothing of another CTA's stores).
+// this same launch (L2 loads: the L1 of this SM knows nothing of another CTA's stores).  SRC 3: from the bf16 row as
+// written by other CTAs earlier in this same launch (persistent step kernel), again past L1.
 template <int SRC>
 __device__ __forceinline__ void load_chunk_in(const GemvParams& p, const uint16_t* row, int b, int q, float (&y)[8]) {
   if (SRC == 2) {
     const uint4 v = __ldcg(reinterpret_cast<const uint4*>(p.red.out + (size_t)b * p.K) + q);
+    y[0] = __uint_as_float(v.x << 16); y[1] = __uint_as_float(v.x & 0xffff0000u);
+    y[2] = __uint_as_float(v.y << 16); y[3] = __uint_as_float(v.y & 0xffff0000u);
+    y[4] = __uint_as_float(v.z << 16); y[5] = __uint_as_float(v.z & 0xffff0000u);
+    y[6] = __uint_as_float(v.w << 16); y[7] = __uint_as_float(v.w & 0xffff0000u);
+  } else if (SRC == 3) {
+    const uint4 v = __ldcg(reinterpret_cast<const uint4*>(row) + q);
     y[0] = __uint_as_float(v.x << 16); y[1] = __uint_as_float(v.x & 0xffff0000u);
     y[2] = __uint_as_float(v.y << 16); y[3] = __uint_as_float(v.y & 0xffff0000u);
     y[4] = __uint_as_float(v.z << 16); y[5] = __uint_as_float(v.z & 0xffff0000u);
@@ -359,7 +366,8 @@ BK_DEVINL void mbar_wait_bounded(uint32_t bar, uint32_t parity, int* status) {
   if (status) atomicExch(status, BK_ERR_TIMEOUT);
 }
 
-template <bool TP = true>
+// CG: the residual was written by another CTA earlier in the same launch (persistent step kernel): read it past L1.
+template <bool TP = true, bool CG = false>
 __device__ __forceinline__ void store_epilogue(const GemvParams& p, const SegDev& sg, size_t o, float y, float yup) {
   if (TP && sg.epi == BK_EPI_PUSH_F32) {
     const unsigned int tag = bk_exchange_tag(p.push.epoch, p.push.tag_add);
@@ -372,7 +380,7 @@ __device__ __forceinline__ void store_epilogue(const GemvParams& p, const SegDev
   } else if (sg.epi == BK_EPI_BF16) {
     reinterpret_cast<uint16_t*>(sg.out)[o] = bk_f32_to_bf16(y);
   } else {  // BK_EPI_ADD_BF16
-    reinterpret_cast<uint16_t*>(sg.out)[o] = bk_f32_to_bf16(__fadd_rn(y, bk_bf16_to_f32(sg.res[o])));
+    reinterpret_cast<uint16_t*>(sg.out)[o] = bk_f32_to_bf16(__fadd_rn(y, bk_bf16_to_f32(CG ? __ldcg(sg.res + o) : sg.res[o])));
   }
 }
 

@@ -4,7 +4,7 @@
 #include <stdint.h>
 #include <stdio.h>
 
-#include "../../include/bunker_cuda.h"
+#include "../../include/bunker_cuda_diag.h"
 
 struct BkContext {
   bool ready = false;
@@ -23,6 +23,8 @@ struct BkContext {
   unsigned long long* cta_trace = nullptr;  // per-CTA timeline of one chosen GEMV launch (bkTraceCtas)
   int cta_trace_launch = -1;          // index (among GEMV launches since bkTraceCtas) of the launch to record
   int cta_trace_seen = 0;
+  unsigned long long* step_trace = nullptr;  // per-phase timeline of the persistent step kernel (bkStepTraceEnable)
+  int step_trace_phases = 0;          // phases the buffer can hold (4 slots each)
   int* d_status = nullptr;           // device word set by kernels whose bounded waits gave up
   float* gemv_carry = nullptr;       // class accumulators handed from one K part of a split GEMV to the next
   size_t gemv_carry_bytes = 0;
@@ -140,3 +142,23 @@ int32_t bk_comm_allreduce_residual(uint64_t comm, int slot, int n, uint64_t resi
 int32_t bk_comm_argmax_merge(uint64_t comm, int slot, int B, uint64_t local_val, uint64_t local_idx, int offset, uint64_t idx,
                              uint64_t val, uint64_t pos, uint64_t hist, int hist_ld, int hist_rows);
 int32_t bk_comm_info(uint64_t comm, int* rank, int* nranks);
+
+// ---- persistent decode step (bk_persist.cu) ----------------------------------------------------------------
+// A plan is the list of phases of one batch-1 decode step on one GPU: GEMV phases (bkGemvArgs, prologues
+// BK_PRO_RMSNORM / BK_PRO_BF16) and conv1d + gated-DeltaNet phases (bkGdnArgs).  bk_plan_launch runs phases
+// [first, first+count) in ONE cooperative launch with device-side barriers between them.
+#define BK_PF_EMBED 1    /* GEMV phase: the activation is the embedded row of token ids_in[0] (also stored to x0) */
+#define BK_PF_ARGMAX 2   /* GEMV phase with one f32 segment: the launch ends with the argmax tail over its rows */
+struct BkStepIO {
+  uint64_t embed, ids_in, x0;                            // BK_PF_EMBED
+  uint64_t ids_out, val_out, pos, hist, host_out;        // BK_PF_ARGMAX tail (as bk_argmax_launch)
+  int32_t H, hist_ld, hist_rows, vocab_offset;
+};
+int32_t bk_plan_create(uint64_t* out, int hidden);
+bool bk_plan_gemv_fits(uint64_t plan, int K);
+int32_t bk_plan_add_gemv(uint64_t plan, const bkGemvArgs& a, int flags);
+int32_t bk_plan_add_gdn(uint64_t plan, const bkGdnArgs& a);   // odd conv-state parity swaps conv_state_in / _new
+int32_t bk_plan_count(uint64_t plan);
+int32_t bk_plan_finish(uint64_t plan);
+int32_t bk_plan_launch(uint64_t plan, int first, int count, int parity, const BkStepIO& io);
+void bk_plan_destroy(uint64_t plan);

@@ -67,6 +67,12 @@ struct Model {
   cudaGraphExec_t graph[2] = {nullptr, nullptr};       // token fed back on the device (embed reads m.ids)
   cudaGraphExec_t graph_host[2] = {nullptr, nullptr};  // token from the host (embed reads the mapped pinned ids)
   unsigned long long graph_kernels = 0;
+  // persistent step (batch 1, one GPU): the phases of the plan run as a few cooperative launches, with the attention
+  // kernel between them
+  int step_mode = 0;    // 0 = library's choice, 1 = one launch per op, 2 = persistent step kernel
+  uint64_t plan = 0;
+  struct StepItem { int kind; int first, count; int layer; };   // kind 0: phases [first, first+count) of the plan; 1: attention of `layer`
+  std::vector<StepItem> items;
   long long steps = 0;  // steps taken since the last reset (host mirror of pos)
   int conv_cur = 0;     // which of the two conv-state buffers is current (flips with every decode step / prompt pass)
   // buffers of the multi-token prompt path (bkModelPrefill), sized for `cols` = tokens x sequences columns
@@ -140,8 +146,130 @@ struct ProfScope {
     TRY(expr);             \
   } while (0)
 
+
+// arguments of the attention launch of layer L for the decode step (one token per sequence)
+bkAttnArgs step_attn_args(Model& m, LayerW& L, bool q8_handoff, bool o_staged) {
+  const bkModelConfig& c = m.cfg;
+  bkAttnArgs aa;
+  memset(&aa, 0, sizeof(aa));
+  aa.qg = m.qg; aa.k = m.kbuf; aa.v = m.vbuf; aa.q_norm_w = L.q_norm; aa.k_norm_w = L.k_norm;
+  aa.cos_t = m.cos_t; aa.sin_t = m.sin_t; aa.k_cache = L.kc; aa.v_cache = L.vc; aa.pos = m.pos;
+  aa.out = m.attn_out; aa.out_q8 = q8_handoff ? m.attn_q8 : 0; aa.out_q8_layout = o_staged ? BK_Q8_STAGED : BK_Q8_BLOCKS;
+  aa.scratch = m.attn_scratch;
+  aa.B = m.B; aa.Hq = m.Hq; aa.Hkv = m.Hkv; aa.HD = c.head_dim; aa.rot_half = c.rot_dim / 2; aa.max_len = c.max_len;
+  aa.split_len = m.split_len; aa.max_pos = c.max_len - 1; aa.scale = 1.0f / sqrtf((float)c.head_dim);
+  aa.fused_norm_rope = 1;
+  aa.cache_is_settled = 1;  // pos and the older cache rows were written a whole step ago
+  return aa;
+}
+
+// The batch-1 single-GPU step as a plan for the persistent kernel (bk_persist.cu): the same ops in the same order as
+// enqueue_step, every GEMV and GDN launch becoming a phase; the attention kernel stays a launch of its own and cuts
+// the plan into segments.  Leaves m.plan = 0 when a shape does not fit the persistent kernel.
+int32_t build_plan(Model& m) {
+  const bkModelConfig& c = m.cfg;
+  const int H = c.hidden, attn_w = m.Hq * c.head_dim;
+  if (H > 8192) return BK_OK;
+  TRY(bk_plan_create(&m.plan, H));
+  if (!bk_plan_gemv_fits(m.plan, H) || !bk_plan_gemv_fits(m.plan, m.ZD) || !bk_plan_gemv_fits(m.plan, attn_w) ||
+      !bk_plan_gemv_fits(m.plan, m.inter)) {
+    bk_plan_destroy(m.plan);
+    m.plan = 0;
+    return BK_OK;
+  }
+  int cur = 0, seg_first = 0;
+  auto close_segment = [&]() {
+    const int n = bk_plan_count(m.plan) - seg_first;
+    if (n > 0) m.items.push_back(Model::StepItem{0, seg_first, n, -1});
+    seg_first = bk_plan_count(m.plan);
+  };
+  auto gemv = [&](uint64_t x, int K, uint64_t norm_w) {
+    bkGemvArgs g;
+    memset(&g, 0, sizeof(g));
+    g.K = K; g.B = 1; g.eps = c.eps; g.x = x; g.norm_w = norm_w;
+    g.prologue = norm_w ? BK_PRO_RMSNORM : BK_PRO_BF16;
+    return g;
+  };
+  for (int li = 0; li < c.n_layers; li++) {
+    LayerW& L = m.layers[li];
+    const int first_flags = li == 0 ? BK_PF_EMBED : 0;
+    bkGemvArgs g = gemv(m.x[cur], H, L.in_ln);
+    if (!L.full) {
+      g.n_segs = 4;
+      g.segs[0] = bkGemvSeg{L.qkv, 0, m.qkv, 0, m.Cw, BK_EPI_BF16, m.Cw, 0};
+      g.segs[1] = bkGemvSeg{L.z, 0, m.z, 0, m.ZD, BK_EPI_BF16, m.ZD, 0};
+      g.segs[2] = bkGemvSeg{L.a, 0, m.a, 0, m.Hv, BK_EPI_F32, m.Hv, 0};
+      g.segs[3] = bkGemvSeg{L.b, 0, m.b, 0, m.Hv, BK_EPI_F32, m.Hv, 0};
+      TRY(bk_plan_add_gemv(m.plan, g, first_flags));
+      bkGdnArgs ga;
+      memset(&ga, 0, sizeof(ga));
+      ga.qkv = m.qkv; ga.z = m.z; ga.a = m.a; ga.b = m.b;
+      ga.conv_w = L.conv_w; ga.conv_state_in = L.conv_state[0]; ga.conv_state_new = L.conv_state[1];
+      ga.A_log = L.A_log; ga.dt_bias = L.dt_bias; ga.norm_w = L.gnorm;
+      ga.S_in = L.S; ga.S_new = L.S;
+      ga.out = m.attn_out; ga.B = 1; ga.Hk = m.Hk; ga.Hv = m.Hv; ga.apply_conv = 1; ga.state_is_settled = 1;
+      TRY(bk_plan_add_gdn(m.plan, ga));
+      g = gemv(m.attn_out, m.ZD, 0);
+      g.n_segs = 1;
+      g.segs[0] = bkGemvSeg{L.out_proj, 0, m.h1, m.x[cur], H, BK_EPI_ADD_BF16, H, 0};
+      TRY(bk_plan_add_gemv(m.plan, g, 0));
+    } else {
+      g.n_segs = 3;
+      g.segs[0] = bkGemvSeg{L.q, 0, m.qg, 0, m.QG, BK_EPI_BF16, m.QG, 0};
+      g.segs[1] = bkGemvSeg{L.k, 0, m.kbuf, 0, m.KVD, BK_EPI_BF16, m.KVD, 0};
+      g.segs[2] = bkGemvSeg{L.v, 0, m.vbuf, 0, m.KVD, BK_EPI_BF16, m.KVD, 0};
+      TRY(bk_plan_add_gemv(m.plan, g, first_flags));
+      close_segment();
+      m.items.push_back(Model::StepItem{1, 0, 0, li});
+      g = gemv(m.attn_out, attn_w, 0);
+      g.n_segs = 1;
+      g.segs[0] = bkGemvSeg{L.o, 0, m.h1, m.x[cur], H, BK_EPI_ADD_BF16, H, 0};
+      TRY(bk_plan_add_gemv(m.plan, g, 0));
+    }
+    g = gemv(m.h1, H, L.post_ln);
+    g.n_segs = 1;
+    g.segs[0] = bkGemvSeg{L.gate, L.up, m.act, 0, m.inter, BK_EPI_SWIGLU, m.inter, 0};
+    TRY(bk_plan_add_gemv(m.plan, g, 0));
+    g = gemv(m.act, m.inter, 0);
+    g.n_segs = 1;
+    g.segs[0] = bkGemvSeg{L.down, 0, m.x[cur ^ 1], m.h1, H, BK_EPI_ADD_BF16, H, 0};
+    TRY(bk_plan_add_gemv(m.plan, g, 0));
+    cur ^= 1;
+  }
+  bkGemvArgs g = gemv(m.x[cur], H, m.final_norm);
+  g.n_segs = 1;
+  g.segs[0] = bkGemvSeg{m.embed, 0, m.logits, 0, m.vocab_local, BK_EPI_F32, m.vocab_local, 0};
+  TRY(bk_plan_add_gemv(m.plan, g, BK_PF_ARGMAX));
+  close_segment();
+  TRY(bk_plan_finish(m.plan));
+  return BK_OK;
+}
+
+int32_t enqueue_step_persist(Model& m, int parity, bool host_tokens) {
+  const bkModelConfig& c = m.cfg;
+  const bool mapped_io = m.pin_dev != 0;
+  BkStepIO io;
+  memset(&io, 0, sizeof(io));
+  io.embed = m.embed;
+  io.ids_in = (host_tokens && mapped_io) ? m.pin_dev + (uint64_t)parity * 4 : m.ids;
+  io.x0 = m.x[0];
+  io.ids_out = m.ids; io.val_out = m.val; io.pos = m.pos; io.hist = m.hist;
+  io.host_out = mapped_io ? m.pin_dev + (uint64_t)2 * 4 : 0;
+  io.H = c.hidden; io.hist_ld = 1; io.hist_rows = c.max_len; io.vocab_offset = 0;
+  for (const Model::StepItem& it : m.items) {
+    if (it.kind == 0) {
+      TRY(bk_plan_launch(m.plan, it.first, it.count, parity, io));
+    } else {
+      bkAttnArgs aa = step_attn_args(m, m.layers[it.layer], false, false);
+      TRY(bkAttnDecode(&aa));
+    }
+  }
+  return BK_OK;
+}
+
 // enqueue one decode step on the library stream; parity selects the conv-state buffer pair
 int32_t enqueue_step(Model& m, int parity, bool host_tokens = false) {
+  if (m.plan && !g_prof.on) return enqueue_step_persist(m, parity, host_tokens);
   const bkModelConfig& c = m.cfg;
   const int B = m.B, H = c.hidden;
   int cur = 0;
@@ -238,17 +366,8 @@ int32_t enqueue_step(Model& m, int parity, bool host_tokens = false) {
       g.segs[1] = bkGemvSeg{L.k, 0, m.kbuf, 0, m.KVD, BK_EPI_BF16, m.KVD, 0};
       g.segs[2] = bkGemvSeg{L.v, 0, m.vbuf, 0, m.KVD, BK_EPI_BF16, m.KVD, 0};
       PROF(PC_GEMV_PROJ, launch(g));
-      bkAttnArgs aa;
-      memset(&aa, 0, sizeof(aa));
-      aa.qg = m.qg; aa.k = m.kbuf; aa.v = m.vbuf; aa.q_norm_w = L.q_norm; aa.k_norm_w = L.k_norm;
-      aa.cos_t = m.cos_t; aa.sin_t = m.sin_t; aa.k_cache = L.kc; aa.v_cache = L.vc; aa.pos = m.pos;
       const bool o_staged = q8_handoff && staged_ok(m.Hq * c.head_dim);
-      aa.out = m.attn_out; aa.out_q8 = q8_handoff ? m.attn_q8 : 0; aa.out_q8_layout = o_staged ? BK_Q8_STAGED : BK_Q8_BLOCKS;
-      aa.scratch = m.attn_scratch;
-      aa.B = B; aa.Hq = m.Hq; aa.Hkv = m.Hkv; aa.HD = c.head_dim; aa.rot_half = c.rot_dim / 2; aa.max_len = c.max_len;
-      aa.split_len = m.split_len; aa.max_pos = c.max_len - 1; aa.scale = 1.0f / sqrtf((float)c.head_dim);
-      aa.fused_norm_rope = 1;
-      aa.cache_is_settled = 1;  // pos and the older cache rows were written a whole step ago
+      bkAttnArgs aa = step_attn_args(m, L, q8_handoff, o_staged);
       PROF(PC_ATTN, bkAttnDecode(&aa));
       memset(&g, 0, sizeof(g));
       g.K = m.Hq * c.head_dim; g.B = B; g.n_segs = 1;
@@ -541,6 +660,15 @@ int32_t bkModelSetComm(uint64_t model, uint64_t comm) {
   return BK_OK;
 }
 
+int32_t bkModelSetStepMode(uint64_t model, int32_t mode) {
+  BK_REQUIRE_INIT();
+  BK_ARG(model && mode >= 0 && mode <= 2, "bkModelSetStepMode: bad arguments");
+  Model* m = as_model(model);
+  BK_ARG(!m->finalized, "bkModelSetStepMode: model is already finalized");
+  m->step_mode = mode;
+  return BK_OK;
+}
+
 int32_t bkModelFinalize(uint64_t model) {
   BK_REQUIRE_INIT();
   BK_ARG(model, "bkModelFinalize: null model");
@@ -656,6 +784,9 @@ int32_t bkModelFinalize(uint64_t model) {
     BK_CUDA(cudaHostGetDevicePointer(&dp, m.pin_ids, 0));
     m.pin_dev = (uint64_t)(uintptr_t)dp;
   }
+  BK_ARG(m.step_mode != 2 || (B == 1 && m.tp == 1), "bkModelFinalize: the persistent step needs batch 1 on one GPU");
+  if (m.step_mode != 1 && B == 1 && m.tp == 1) TRY(build_plan(m));
+  BK_ARG(m.step_mode != 2 || m.plan, "bkModelFinalize: this model's shapes do not fit the persistent step kernel");
   // one eager step sets the kernels' shared-memory attributes and validates every pointer, then the
   // state is cleared and the two parity graphs are captured
   TRY(enqueue_step(m, 0));
@@ -776,6 +907,18 @@ int32_t bkDecodeStepProfiled(uint64_t model, float* ms_out, int32_t* count_out, 
   return BK_OK;
 }
 
+int32_t bkDecodeStepEager(uint64_t model) {
+  BK_REQUIRE_INIT();
+  BK_ARG(model, "bkDecodeStepEager: null model");
+  Model& m = *as_model(model);
+  BK_ARG(m.finalized, "bkDecodeStepEager: model is not finalized");
+  BK_ARG(m.steps < m.cfg.max_len, "bkDecodeStepEager: position reached max_len");
+  TRY(enqueue_step(m, m.conv_cur));
+  m.steps++;
+  m.conv_cur ^= 1;
+  return BK_OK;
+}
+
 int32_t bkModelPrefill(uint64_t model, const int32_t* tokens, int32_t T, int32_t* out_ids, float* out_vals) {
   BK_REQUIRE_INIT();
   BK_ARG(model && tokens && T >= 1, "bkModelPrefill: bad arguments");
@@ -848,6 +991,7 @@ int32_t bkModelDestroy(uint64_t model) {
     if (m->pin_read[i]) cudaEventDestroy(m->pin_read[i]);
   }
   for (uint64_t p : m->owned) cudaFree(bk_ptr<void>(p));
+  if (m->plan) bk_plan_destroy(m->plan);
   if (m->pin_ids) cudaFreeHost(m->pin_ids);
   delete m;
   return BK_OK;

@@ -202,8 +202,18 @@ int32_t bkTraceCtas(uint64_t dev_buf, int32_t gemv_launch_index) {
   return BK_OK;
 }
 
+int32_t bkStepTraceEnable(uint64_t dev_buf, int32_t max_phases) {
+  BK_REQUIRE_INIT();
+  BK_ARG(dev_buf && max_phases > 0, "bkStepTraceEnable: bad arguments");
+  g_ctx.step_trace = bk_ptr<unsigned long long>(dev_buf);
+  g_ctx.step_trace_phases = max_phases;
+  return BK_OK;
+}
+
 int32_t bkTraceDisable(void) {
   BK_REQUIRE_INIT();
+  g_ctx.step_trace = nullptr;
+  g_ctx.step_trace_phases = 0;
   g_ctx.trace = nullptr;
   g_ctx.trace_cap = 0;
   g_ctx.cta_trace = nullptr;

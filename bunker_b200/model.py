@@ -220,9 +220,10 @@ class DecodeModel:
     """Weights on the device + the library's step graph.  `weights` maps tensor names to numpy arrays."""
 
     def __init__(self, cfg: ModelConfig, weights: dict[str, np.ndarray], batch: int = 1, device: int = 0,
-                 tp_rank: int = 0, tp_size: int = 1):
+                 tp_rank: int = 0, tp_size: int = 1, step_mode: int = 0):
         """`weights` holds the FULL tensors; with tp_size > 1 this rank's shard is cut here and the ranks rendezvous
-        through bunker_b200.dist (torch.distributed must already be initialised)."""
+        through bunker_b200.dist (torch.distributed must already be initialised).  step_mode: 0 the library's choice,
+        1 one launch per op, 2 the persistent step kernel (bkModelSetStepMode)."""
         self.cfg, self.batch, self.tp_rank, self.tp_size = cfg, batch, tp_rank, tp_size
         lib = R.cu(device)
         specs = tensor_specs(cfg)
@@ -262,6 +263,8 @@ class DecodeModel:
             R._check(lib.bkModelSetComm(self.handle, self.comm))
             assert R.cuSync() == 0
             dist.barrier()       # finalize runs one step that exchanges with the peers: enter it together
+        if step_mode:
+            R._check(lib.bkModelSetStepMode(self.handle, step_mode))
         R._check(lib.bkModelFinalize(self.handle))
         if tp_size > 1:
             dist.barrier()
@@ -296,6 +299,10 @@ class DecodeModel:
             return np.array(self._out[:], np.int32), np.array(self._val[:], np.float32)
         R._check(R.cu().bkDecodeStep(self.handle, tp, None, None))
         return None
+
+    def step_eager(self) -> None:
+        """One step enqueued without the CUDA graph, token fed back on the device (diagnostic timelines apply to it)."""
+        R._check(R.cu().bkDecodeStepEager(self.handle))
 
     def run(self, n_steps: int) -> None:
         R._check(R.cu().bkDecodeRun(self.handle, n_steps))

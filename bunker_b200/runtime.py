@@ -103,6 +103,7 @@ SIGNATURES = {
     "bkTraceEnable": (_I32, [_U64, _I32]),
     "bkTraceCtas": (_I32, [_U64, _I32]),
     "bkTraceDisable": (_I32, []),
+    "bkStepTraceEnable": (_I32, [_U64, _I32]),
     "bkGemvQ4K": (_I32, [C.POINTER(bkGemvArgs)]),
     "bkGemvQ4KSimple": (_I32, [_U64, _I32, _I32, _U64, _I32, _U64]),
     "bkDequantQ4K": (_I32, [_U64, _I32, _I32, _U64]),
@@ -138,7 +139,9 @@ _MODEL_SIGS = {
     "bkModelCreate": (C.c_int32, [C.POINTER(bkModelConfig), C.POINTER(C.c_uint64)]),
     "bkModelSetTensor": (C.c_int32, [C.c_uint64, C.c_char_p, C.c_uint64, C.c_uint64]),
     "bkModelSetComm": (C.c_int32, [C.c_uint64, C.c_uint64]),
+    "bkModelSetStepMode": (C.c_int32, [C.c_uint64, C.c_int32]),
     "bkModelFinalize": (C.c_int32, [C.c_uint64]),
+    "bkDecodeStepEager": (C.c_int32, [C.c_uint64]),
     "bkModelReset": (C.c_int32, [C.c_uint64]),
     "bkDecodeStep": (C.c_int32, [C.c_uint64, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
     "bkDecodeRun": (C.c_int32, [C.c_uint64, C.c_int32]),

@@ -72,16 +72,6 @@ BK_API int32_t bkEventRecord(uint64_t event);
 BK_API int32_t bkEventSync(uint64_t event);
 BK_API int32_t bkEventElapsedMs(uint64_t start, uint64_t stop, float* out_ms);
 BK_API int32_t bkEventDestroy(uint64_t event);
-/* Device-side timeline.  While enabled, every kernel launched (or captured into a graph) gets the next
- * 64-byte record of dev_buf and thread 0 of its CTA 0 stamps %globaltimer (ns) into slots:
- * 0 entry, 1 own weight copies issued, 2 dependency wait returned, 3 prologue done, 4 first weights landed, 5 exit.
- * A graph replays the records it was captured with.  Off by default. */
-BK_API int32_t bkTraceEnable(uint64_t dev_buf, int32_t max_launches);
-/* Per-CTA timeline of ONE GEMV launch: the gemv_launch_index-th bkGemvQ4K-class launch issued (or captured) after
- * this call records, for every CTA c, dev_buf[4c..4c+3] = {entry, dependency wait returned, first weights landed in
- * warp 0, latest warp exit} in %globaltimer ns.  dev_buf must hold 4 x 8 bytes per SM. */
-BK_API int32_t bkTraceCtas(uint64_t dev_buf, int32_t gemv_launch_index);
-BK_API int32_t bkTraceDisable(void);
 /* Number of kernels this library has launched since bkInit (graph replays count their kernels). */
 BK_API int32_t bkLaunchCount(uint64_t* out_count);
 
@@ -134,10 +124,6 @@ typedef struct bkGemvArgs {
 } bkGemvArgs;
 
 BK_API int32_t bkGemvQ4K(const bkGemvArgs* args);
-/* Measurement aid, no counterpart in the reference: force the batch-1 kernel's weight ring (warps per CTA, rows per
- * warp group, maximum ring depth) for launches whose rows do not fit in shared memory at once; warps = 0 restores the
- * library's own choice. */
-BK_API int32_t bkTuneGemvRing(int32_t warps, int32_t rows_per_group, int32_t max_depth);
 /* config-0 convenience: y f32 [B][N] = W[N][K] (Q4_K) x xq (Q8_1 blocks) */
 BK_API int32_t bkGemvQ4KSimple(uint64_t W, int32_t N, int32_t K, uint64_t xq, int32_t B, uint64_t y);
 
@@ -281,6 +267,11 @@ BK_API int32_t bkModelSetTensor(uint64_t model, const char* name, uint64_t dev_p
  * embedding table is registered whole (replicated).  Shard shapes are derived from the config by the rule in
  * bunker_b200/model.py `shard_weights`. */
 BK_API int32_t bkModelSetComm(uint64_t model, uint64_t comm);
+/* How the decode step is issued (before bkModelFinalize).  0: the library's choice; 1: one launch per op, the shape of
+ * the reference's loop (src/runner.ts:146-149), chained with programmatic dependent launch; 2: the persistent step
+ * kernel -- a few cooperative launches per token that run the ops as phases with device-side barriers (batch 1 on
+ * one GPU only; bkModelFinalize fails if the model's shapes do not fit it).  All modes give the same bits. */
+BK_API int32_t bkModelSetStepMode(uint64_t model, int32_t mode);
 /* Checks the tensor set, allocates state and activations, captures the step graphs.  With tp_size > 1 every rank
  * must call it at about the same time: it runs one step, which exchanges with the peers. */
 BK_API int32_t bkModelFinalize(uint64_t model);

@@ -196,3 +196,30 @@ def test_scaled_model_shapes_batch8_tensor_core_path(bk):
         assert np.array_equal(ids_g, ids_o), f"step {t}"
     assert_same_bits(gm.logits(), om.logits, "logits")
     gm.destroy()
+
+
+@pytest.mark.parametrize("interval,n_layers", [(4, 4), (1, 2), (2, 3), (4, 3)])
+def test_persistent_step_equals_per_op_step_and_oracle(bk, interval, n_layers):
+    """Batch 1 on one GPU runs as a persistent kernel (phases + device-side barriers) by default.  The same model
+    stepped with one launch per op must give the same tokens and bit-identical logits, and both match the oracle --
+    also when every layer is an attention layer (interval 1) or the model ends on GDN layers."""
+    cfg = M.CONFIG_TINY.with_(full_attn_interval=interval, n_layers=n_layers, max_len=96)
+    w = M.synth_weights(cfg, seed=40 + interval)
+    prompt = np.random.default_rng(interval).integers(0, cfg.vocab, (5, 1)).astype(np.int32)
+    outs = {}
+    for mode in (1, 2):
+        gm = M.DecodeModel(cfg, w, batch=1, step_mode=mode)
+        info = gm.info()
+        toks = M.runGraphDecode(gm, prompt, 40)
+        # device-side feedback through the same graphs
+        gm.run(20)
+        assert R.cuSync() == 0
+        outs[mode] = (toks, gm.tokens(0, 5 + 39 + 20), gm.logits(), info)
+        gm.destroy()
+    assert outs[2][3]["kernels_per_step"] < outs[1][3]["kernels_per_step"]
+    assert np.array_equal(outs[1][0], outs[2][0])
+    assert np.array_equal(outs[1][1], outs[2][1])
+    assert_same_bits(outs[1][2], outs[2][2], "logits, per-op step vs persistent step")
+    om = OracleModel(cfg, w, batch=1, split_len=outs[2][3]["split_len"], attn_warps=outs[2][3]["attn_warps"])
+    want = om.generate(prompt, 40)
+    assert np.array_equal(outs[2][0], want)

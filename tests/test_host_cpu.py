@@ -13,7 +13,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def header_symbols():
-    text = open(os.path.join(ROOT, "include", "bunker_cuda.h")).read()
+    inc = os.path.join(ROOT, "include")
+    text = "".join(open(os.path.join(inc, f)).read() for f in sorted(os.listdir(inc)) if f.endswith(".h"))
     return sorted(set(re.findall(r"BK_API\s+[\w\s\*]+?\b(bk[A-Z]\w*)\s*\(", text)))
 
 
@@ -22,7 +23,7 @@ def test_library_exports_every_declared_symbol():
     names = header_symbols()
     assert len(names) >= 50
     for n in names:
-        assert hasattr(lib, n), f"{n} is declared in include/bunker_cuda.h but not exported"
+        assert hasattr(lib, n), f"{n} is declared in include/*.h but not exported"
     missing = [n for n in names if n not in R.SIGNATURES]
     assert not missing, f"declared but not bound in runtime.SIGNATURES: {missing}"
     extra = [n for n in R.SIGNATURES if n not in names]
