@@ -31,8 +31,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 PROMPT_LEN = 32
-# dram__bytes_read.sum + dram__bytes_write.sum of one lm_head GEMV launch at batch 1 (ncu capture summarised in
-# profiles/gemv_q4k_lmhead_b1.md)
+# dram__bytes_read.sum + dram__bytes_write.sum of one lm_head GEMV launch at batch 1, from an ncu capture of that
+# launch (two launches of gemv_q4k_kernel, --clock-control none)
 NCU_GEMV_LMHEAD_TRAFFIC = 180382976
 METRIC = "q4k_hybrid_decode_tok_s"
 
@@ -109,7 +109,10 @@ def make_config(steps: int, warmup: int):
 def cpu_tokens_per_s(cfg, weights, batch: int, steps: int, warmup: int, budget_s: float = 150.0):
     """Oracle decode on the host cores.  Runs the full model when K steps fit the budget, else a 1/6 sample
     (4 of 24 layers in the same 3:1 layer mix and 1/6 of the lm_head rows) with the rate scaled by 1/6."""
+    from oracle import oracle as O
     from oracle.model_oracle import OracleModel
+    # a launcher (torch.distributed.run) exports OMP_NUM_THREADS=1 to its workers: ask for every host core explicitly
+    threads = O.set_threads(os.cpu_count() or 1)
     om = OracleModel(cfg, weights, batch=batch, split_len=64)
     tok = np.zeros((batch,), np.int32)
     t0 = time.perf_counter()
@@ -135,7 +138,7 @@ def cpu_tokens_per_s(cfg, weights, batch: int, steps: int, warmup: int, budget_s
         if om.pos >= om.cfg.max_len - 1:
             om.reset()
     dt = time.perf_counter() - t0
-    return steps * batch / dt * scale, dt / steps * 1e3, sample
+    return steps * batch / dt * scale, dt / steps * 1e3, sample, threads
 
 
 def run_reference(args):
@@ -146,8 +149,7 @@ def run_reference(args):
     from bunker_b200 import model as M
     cfg = make_config(args.steps, args.warmup)
     weights = M.synth_weights(cfg)
-    val, ms, sample = cpu_tokens_per_s(cfg, weights, args.batch, args.steps, args.warmup)
-    cores = os.cpu_count() or 1
+    val, ms, sample, cores = cpu_tokens_per_s(cfg, weights, args.batch, args.steps, args.warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -281,8 +283,8 @@ def run_ours(args):
         dist.shutdown()
         return
     if world == 1:
-        cpu_val, cpu_ms, cpu_sample = cpu_tokens_per_s(cfg, weights, B, steps=6, warmup=1, budget_s=30.0)
-        cpu = {"value": cpu_val, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port",
+        cpu_val, cpu_ms, cpu_sample, cpu_threads = cpu_tokens_per_s(cfg, weights, B, steps=6, warmup=1, budget_s=30.0)
+        cpu = {"value": cpu_val, "unit": "tok/s", "cores": cpu_threads, "kind": "port",
                "sample": cpu_sample + "; 6 timed steps", "ms_per_step": cpu_ms}
     else:
         cpu = None   # reported at N=1 only

@@ -10,7 +10,7 @@
 //
 // Per split: scores for all rows (each K row is read once for the G query heads of
 // the group), exact max, p = exp(s-m), then o = sum p*V with each V row read once.
-// A second kernel merges the splits and applies the sigmoid output gate.
+// The CTA that finishes a (batch, KV head) last merges its splits and applies the sigmoid output gate.
 // Orders are fixed (see the CPU checker): lane l owns dims [8l,8l+8); row jj of a
 // split belongs to warp jj mod 8; warps and splits are added in ascending order.
 #include "bk_common.cuh"
@@ -202,6 +202,7 @@ __global__ void __launch_bounds__(kW * 32) attn_split_kernel(const AttnParams p)
       dst[e] = ok ? *reinterpret_cast<const uint4*>(base + (size_t)(j0 + jj) * kHD + lane * 8) : make_uint4(0, 0, 0, 0);
     }
   };
+  bool early = false;   // the first chunks were requested before the dependency wait and are still the right ones
   if (p.settled) {
     pos = p.pos[b];
     ns = min(pos + 1, j0 + p.split_len) - j0;   // <= 0: nothing to do for this split
@@ -209,12 +210,19 @@ __global__ void __launch_bounds__(kW * 32) attn_split_kernel(const AttnParams p)
       load_chunk(Kb, 0, kc, true);
       load_chunk(Vb, 0, vc, true);
     }
+    early = true;
   }
   bk_pdl_wait();
   bk_stamp(p.trace, 2);
-  if (!p.settled) {
-    pos = p.pos[b];
-    ns = min(pos + 1, j0 + p.split_len) - j0;
+  {
+    // The position is taken (again) after the wait: the kernel that advances it may be only a few launches back and
+    // still have been running when the early part above read it.  A changed value discards the early loads.
+    const int pos_now = __ldcg(p.pos + b);
+    if (!early || pos_now != pos) {
+      early = false;
+      pos = pos_now;
+      ns = min(pos + 1, j0 + p.split_len) - j0;
+    }
   }
   if (ns <= 0) return;
   const int nsplits = (pos + p.split_len) / p.split_len;
@@ -240,7 +248,7 @@ __global__ void __launch_bounds__(kW * 32) attn_split_kernel(const AttnParams p)
   }
   __syncthreads();  // the appended K/V row is visible to this CTA from here on
   bk_stamp(p.trace, 3);
-  if (!p.settled) {
+  if (!early) {
     load_chunk(Kb, 0, kc, false);
     load_chunk(Vb, 0, vc, false);
   } else {

@@ -253,6 +253,7 @@ int32_t bk_comm_reduce_desc(uint64_t comm, int slot, BkReduce* out) {
   out->epoch = reinterpret_cast<const unsigned int*>(c->local + c->epoch_off);
   out->stride = c->payload_bytes / 4;   // one 8-byte word per f32 of the payload
   out->ready = reinterpret_cast<unsigned int*>(c->local + c->epoch_off + 64) + slot;
+  out->spin_limit = bk_ctx().spin_limit;
   out->n = c->nranks;
   return BK_OK;
 }
@@ -288,7 +289,10 @@ int32_t bkCommCreate(int32_t rank, int32_t nranks, uint64_t payload_bytes, uint6
     delete c;
     return bk_fail((int32_t)e, "bkCommCreate: cudaMalloc -> %s", cudaGetErrorString(e));
   }
-  cudaMemset(p, 0, total);
+  // tags, flags and the epoch start at zero; the zeroing is ordered on the library stream and awaited, so no peer's
+  // store and no later launch can overtake it
+  cudaMemsetAsync(p, 0, total, bk_ctx().stream);
+  cudaStreamSynchronize(bk_ctx().stream);
   c->local = static_cast<uint8_t*>(p);
   c->peer[rank] = c->local;
   c->imported = (nranks == 1);

@@ -201,8 +201,10 @@ BK_DEVINL uint4 bk_ld_volatile_v4(const uint2* p) {
 }
 // 8 consecutive values at element offset o (a multiple of 8): ((p0 + p1) + ...) + residual, rounded to bf16 (returned
 // as f32).  Two ranks are polled per pass so that their loads are in flight together; sums stay in rank order.
+// limit: polls before the wait gives up (0 = the default of 2^20).
 BK_DEVINL void bk_reduce_load8(const uint2* src, unsigned long long stride, int n, unsigned int tag, const uint16_t* res,
-                               uint16_t* out, size_t o, bool write_out, int* status, float (&y)[8]) {
+                               uint16_t* out, size_t o, bool write_out, int* status, float (&y)[8], int limit = 0) {
+  const int max_it = limit > 0 ? limit : (1 << 20);
   float a[8];
   for (int r = 0; r < n; r += 2) {
     const bool two = r + 1 < n;
@@ -218,7 +220,7 @@ BK_DEVINL void bk_reduce_load8(const uint2* src, unsigned long long stride, int 
 #pragma unroll
       for (int k = 0; k < 4; k++) ok = ok && w0[k].y == tag && w0[k].w == tag && w1[k].y == tag && w1[k].w == tag;
       if (ok) break;
-      if (it > (1 << 20) || (status && (it & 255) == 255 && *reinterpret_cast<volatile int*>(status) != 0)) {
+      if (it > max_it || (status && (it & 255) == 255 && *reinterpret_cast<volatile int*>(status) != 0)) {
         if (status) atomicExch(status, 10003 /* BK_ERR_TIMEOUT */);
         break;
       }

@@ -2,8 +2,7 @@
 //
 // At these batch sizes 16 dp4a per 64 weights per batch column no longer fit under the HBM stream; one
 // m16n8k32 computes a 32-value sub-block dot for 16 rows and all 8 batch columns, with exact int32 sums,
-// so the integer stage stays bit-identical to the scalar one.  (north star: "integer dp4a-style block dots";
-// the tcgen05 tile path starts at batch 16, where a CTA-wide tile pays for its TMEM round trip.)
+// so the integer stage stays bit-identical to the scalar one.
 //
 // Work split.  A tile = 16 virtual rows; a warp task = (tile, p) with p = 0..3 the sub-block pair
 // (sub-blocks 2p, 2p+1 of every superblock).  The low nibbles of a 32-byte quant group are sub-block 2p and

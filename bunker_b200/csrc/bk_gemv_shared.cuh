@@ -172,7 +172,7 @@ __device__ __forceinline__ void load_chunk_in(const GemvParams& p, const uint16_
     y[4] = __uint_as_float(v.z << 16); y[5] = __uint_as_float(v.z & 0xffff0000u);
     y[6] = __uint_as_float(v.w << 16); y[7] = __uint_as_float(v.w & 0xffff0000u);
   } else if (SRC == 1) bk_reduce_load8(p.red.src, p.red.stride, p.red.n, bk_exchange_tag(p.red.epoch, p.red.tag_add), p.red.res, p.red.out,
-                              (size_t)b * p.K + (size_t)q * 8, true, p.status, y);
+                              (size_t)b * p.K + (size_t)q * 8, true, p.status, y, p.red.spin_limit);
   else load_chunk_bf16(row, q, y);
 }
 

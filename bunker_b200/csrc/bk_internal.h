@@ -25,6 +25,8 @@ struct BkContext {
   int cta_trace_seen = 0;
   unsigned long long* step_trace = nullptr;  // per-phase timeline of the persistent step kernel (bkStepTraceEnable)
   int step_trace_phases = 0;          // phases the buffer can hold (4 slots each)
+  int spin_limit = 0;                 // polls a bounded device-side wait may take (bkSetSpinLimit; 0 = built-in limits)
+  int step_barrier_mode = 0;          // grid barrier of the persistent step kernel: 0 one word per CTA, 1 one counter
   int* d_status = nullptr;           // device word set by kernels whose bounded waits gave up
   float* gemv_carry = nullptr;       // class accumulators handed from one K part of a split GEMV to the next
   size_t gemv_carry_bytes = 0;
@@ -95,6 +97,7 @@ struct BkReduce {
   unsigned int tag_add;
   int n;                       // ranks; 0 = no reduce
   unsigned int* ready;         // local word: CTA 0 of a reducing GEMV stores the tag here once `out` is complete
+  int spin_limit;              // polls before the bounded wait gives up (0 = default)
 };
 
 // internal launchers shared between translation units

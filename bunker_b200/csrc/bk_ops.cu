@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const uint16_t* x, cons
     if (!rd.n) bk_pdl_wait();   // a reducing launch synchronises through the tagged words instead (see gemv_q4k_kernel)
     const unsigned int tag = rd.n ? bk_exchange_tag(rd.epoch, rd.tag_add) : 0u;
     auto load_in = [&](int q, float (&y)[8]) {
-      if (rd.n) bk_reduce_load8(rd.src, rd.stride, rd.n, tag, rd.res, rd.out, (size_t)b * K + (size_t)q * 8, true, status, y);
+      if (rd.n) bk_reduce_load8(rd.src, rd.stride, rd.n, tag, rd.res, rd.out, (size_t)b * K + (size_t)q * 8, true, status, y, rd.spin_limit);
       else load8_bf16(row + (size_t)q * 8, y);
     };
     float y0[8];
@@ -353,6 +353,7 @@ int32_t bk_quant_rows_launch(uint64_t x, uint64_t w, int32_t K, int32_t B, float
   BkReduce red;
   memset(&red, 0, sizeof(red));
   if (reduce) red = *reduce;
+  red.spin_limit = bk_ctx().spin_limit;
   int* st = bk_ctx().d_status;
   if (w) {
     if (layout == BK_Q8_STAGED) BK_CUDA(bk_launch_pdl(quant_rows_kernel<true, true>, grid, dim3(256), 0, px, pw, K, eps, po, red, st));
@@ -544,7 +545,9 @@ extern "C" int32_t bkArgmaxStatic(uint64_t logits, int32_t V, int32_t B, uint64_
     BK_CUDA(cudaGetDevice(&cur));
     if (cur != dev) BK_CUDA(cudaSetDevice(dev));
     void* p = nullptr;
-    BK_CUDA(cudaGetSymbolAddress(&p, g_argmax_static_scratch));
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_argmax_static_scratch);
+    if (cur != dev && cur >= 0) cudaSetDevice(cur);   // the caller's current device is left as it was
+    if (e != cudaSuccess) return bk_fail((int32_t)e, "bkArgmaxStatic: cudaGetSymbolAddress -> %s", cudaGetErrorString(e));
     dev_addr[dev] = static_cast<unsigned char*>(p);
   }
   float* pv = reinterpret_cast<float*>(dev_addr[dev]);

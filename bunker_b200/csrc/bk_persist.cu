@@ -29,6 +29,8 @@ constexpr int kPT = kPW * 32;
 constexpr int kRingBars = 8;       // row groups a warp may have requested and not yet consumed
 constexpr int kMaxK = 8192;        // widest activation row the staging area holds
 constexpr int kBarrierPolls = 1 << 21;
+constexpr int kDescSlots = 8;      // phase descriptors kept in shared memory: the current phase and the next six valid,
+                                   // the seventh being copied
 
 enum { PH_GEMV = 1, PH_GDN = 2 };
 
@@ -61,6 +63,10 @@ struct PersistParams {
   int first, count;
   unsigned int* flags;
   unsigned int* epoch;
+  unsigned int* counter;        // barrier_mode 1: monotonic arrival counter and the value it had when the launch began
+  unsigned int* counter_base;
+  int barrier_mode;
+  int barrier_polls;            // polls before a barrier gives up
   int* status;
   unsigned long long* trace;   // 4 slots per phase of the plan, or null
   uint32_t ring_bytes;         // per warp
@@ -75,7 +81,7 @@ struct SmemLayout {
 __host__ __device__ inline SmemLayout smem_layout(uint32_t scratch_bytes, uint32_t ring_bytes) {
   SmemLayout L;
   size_t o = 0;
-  L.desc = o; o += 2 * ((sizeof(Phase) + 127) & ~(size_t)127);
+  L.desc = o; o += kDescSlots * ((sizeof(Phase) + 127) & ~(size_t)127);
   L.xs = o; o += (size_t)kMaxK / 64 * kUnitWords * 4;
   L.d8s = o; o += (size_t)kMaxK / 32 * 4;
   L.s8s = o; o += (size_t)kMaxK / 32 * 4;
@@ -94,12 +100,24 @@ struct Ring {
   int pp, pg, end;                 // producer cursor: phase (absolute index), group of this CTA; end of the launch
   int G, ngroups, nrows, c0;       // geometry of phase pp for this CTA
   uint32_t rowb;
+  bool ready;                      // the cursor stands on a group that can be requested
 };
 
-// position the producer on the first phase >= R.pp in which this warp has a row group
-__device__ __forceinline__ void ring_seek(Ring& R, const Phase* phases, int warp) {
-  while (R.pp < R.end) {
-    const Phase& ph = phases[R.pp];
+// descriptor of phase pp (absolute index) in the shared-memory window
+struct DescWin {
+  const uint8_t* base;
+  size_t stride;
+  __device__ __forceinline__ const Phase& at(int pp) const {
+    return *reinterpret_cast<const Phase*>(base + (size_t)(pp & (kDescSlots - 1)) * stride);
+  }
+};
+
+// position the producer on the first phase >= R.pp in which this warp has a row group (never beyond `limit`, the
+// last phase whose descriptor is in the window)
+__device__ __forceinline__ void ring_seek(Ring& R, const DescWin& win, int limit, int warp) {
+  R.ready = false;
+  while (R.pp < R.end && R.pp <= limit) {
+    const Phase& ph = win.at(R.pp);
     if (ph.type == PH_GEMV) {
       const int rpc = ph.g.rows_per_cta;
       const int c0 = blockIdx.x * rpc;
@@ -114,6 +132,7 @@ __device__ __forceinline__ void ring_seek(Ring& R, const Phase* phases, int warp
           R.c0 = c0;
           R.rowb = (uint32_t)(ph.g.K / 256) * 144;
           R.pg = warp;
+          R.ready = true;
           return;
         }
       }
@@ -123,8 +142,9 @@ __device__ __forceinline__ void ring_seek(Ring& R, const Phase* phases, int warp
 }
 
 // request as many of this warp's next groups as the ring and its mbarriers have room for
-__device__ __forceinline__ void ring_fill(Ring& R, const Phase* phases, uint32_t* ent, int warp, int lane) {
-  while (R.pp < R.end && R.issued - R.consumed < (uint32_t)kRingBars) {
+__device__ __forceinline__ void ring_fill(Ring& R, const DescWin& win, int limit, uint32_t* ent, int warp, int lane) {
+  if (!R.ready) ring_seek(R, win, limit, warp);
+  while (R.ready && R.issued - R.consumed < (uint32_t)kRingBars) {
     const int nr = min(R.G, R.nrows - R.pg * R.G);
     const uint32_t bytes = (uint32_t)nr * R.rowb;
     if (R.used == 0) R.head = 0;
@@ -138,7 +158,7 @@ __device__ __forceinline__ void ring_fill(Ring& R, const Phase* phases, uint32_t
     if (lane == 0) {
       ent[2 * e] = off;
       ent[2 * e + 1] = pad + bytes;
-      request_group(phases[R.pp].g, R.c0 + R.pg * R.G, nr, R.rowb, R.base + off, R.bar0 + 8 * e);
+      request_group(win.at(R.pp).g, R.c0 + R.pg * R.G, nr, R.rowb, R.base + off, R.bar0 + 8 * e);
     }
     R.head = off + bytes;
     R.used += pad + bytes;
@@ -146,7 +166,7 @@ __device__ __forceinline__ void ring_fill(Ring& R, const Phase* phases, uint32_t
     R.pg += kPW;
     if (R.pg >= R.ngroups) {
       R.pp++;
-      ring_seek(R, phases, warp);
+      ring_seek(R, win, limit, warp);
     }
   }
   __syncwarp();
@@ -172,34 +192,47 @@ BK_DEVINL unsigned long long global_timer() {
   return t;
 }
 
-// All CTAs of the launch meet.  Returns false when the barrier gave up (status word set): the caller must leave.
-__device__ __forceinline__ bool grid_barrier(unsigned int* flags, unsigned int gen, int* status, int* s_abort,
-                                             unsigned long long* trec) {
+// All CTAs of the launch meet.  Warp kPW-1 publishes this CTA's arrival and polls; the other warps use the wait to
+// request the weight groups their rings have room for.  Returns false when the barrier gave up (status word set):
+// the caller must leave.
+// mode 0: one word per CTA (flags[c] = generation), the poller reads all of them.
+// mode 1: one counter, an atomic add per CTA, the poller reads that word (target = base + (k+1) * CTAs).
+__device__ __forceinline__ bool grid_barrier(const PersistParams& P, unsigned int gen, unsigned int target, int* s_abort,
+                                             unsigned long long* trec, Ring& R, const DescWin& win, int limit, uint32_t* ent) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   __syncthreads();   // every warp of this CTA has finished the phase (and its global stores precede the release below)
-  if (threadIdx.x == 0) {
-    if (trec) atomicMax(trec + 3, global_timer());   // latest CTA to finish the phase
-    __threadfence();
-    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flags + blockIdx.x), "r"(gen) : "memory");
+  if (warp == kPW - 1) {
+    if (lane == 0) {
+      if (trec) atomicMax(trec + 3, global_timer());   // latest CTA to finish the phase
+      __threadfence();
+      if (P.barrier_mode == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(P.flags + blockIdx.x), "r"(gen) : "memory");
+      else atomicAdd(P.counter, 1u);
+    }
+    __syncwarp();
   }
-  if (threadIdx.x < 32) {
-    const int lane = threadIdx.x;
+  ring_fill(R, win, limit, ent, warp, lane);
+  if (warp == kPW - 1) {
     bool ok = false;
-    for (int it = 0; it < kBarrierPolls; it++) {
+    for (int it = 0; it < P.barrier_polls; it++) {
       unsigned int behind = 0;   // all loads of a poll are in flight together
-      for (int i = lane; i < (int)gridDim.x; i += 32) behind |= (ld_relaxed_gpu(flags + i) - gen) >> 31;
+      if (P.barrier_mode == 0) {
+        for (int i = lane; i < (int)gridDim.x; i += 32) behind |= (ld_relaxed_gpu(P.flags + i) - gen) >> 31;
+      } else {
+        if (lane == 0) behind = (ld_relaxed_gpu(P.counter) - target) >> 31;
+      }
       if (__all_sync(0xffffffffu, behind == 0)) {
         ok = true;
         break;
       }
       // another CTA gave up: stop waiting for it (checked only long after any healthy barrier has completed)
       if (it >= 1024 && (it & 1023) == 0) {   // warp-uniform condition: the vote below is taken by all lanes
-        const int st = *reinterpret_cast<volatile int*>(status);
+        const int st = *reinterpret_cast<volatile int*>(P.status);
         if (__any_sync(0xffffffffu, st != 0)) break;
       }
     }
     __threadfence();   // acquire: what the other CTAs wrote before their release is visible to this CTA from here
     if (lane == 0) {
-      if (!ok) atomicExch(status, BK_ERR_TIMEOUT);
+      if (!ok) atomicExch(P.status, BK_ERR_TIMEOUT);
       *s_abort = ok ? 0 : 1;
     }
   }
@@ -223,13 +256,24 @@ __global__ void __launch_bounds__(kPT, 1) decode_persist_kernel(const PersistPar
   float* s8s = reinterpret_cast<float*>(smem + L.s8s);
   float* red = reinterpret_cast<float*>(smem + L.red);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars);
-  int* misc = reinterpret_cast<int*>(smem + L.misc);   // [0] abort flag, [1] last-CTA flag, [8..24) argmax values, [24..40) indices
+  int* misc = reinterpret_cast<int*>(smem + L.misc);   // [0] abort flag, [8..24) argmax values, [24..40) indices
   uint8_t* scratch = smem + L.scratch;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint32_t* ent = reinterpret_cast<uint32_t*>(smem + L.ent) + warp * kRingBars * 2;
   const unsigned int ep = *reinterpret_cast<const volatile unsigned int*>(P.epoch);
+  const unsigned int cbase = *reinterpret_cast<const volatile unsigned int*>(P.counter_base);
   unsigned long long* const trace = (P.trace && blockIdx.x == 0 && tid == 0) ? P.trace : nullptr;
+  const DescWin win = {smem + L.desc, desc_stride};
+  const int last_phase = P.first + P.count - 1;
+
+  // descriptors of the first phases of the launch
+  auto copy_desc = [&](int pp) {
+    const uint4* src = reinterpret_cast<const uint4*>(P.phases + pp);
+    uint4* dst = reinterpret_cast<uint4*>(smem + L.desc + (size_t)(pp & (kDescSlots - 1)) * desc_stride);
+    for (int i = tid; i < (int)(sizeof(Phase) / 16); i += kPT) dst[i] = src[i];
+  };
+  for (int pp = P.first; pp <= last_phase && pp < P.first + kDescSlots - 1; pp++) copy_desc(pp);
 
   // ---- weight ring of this warp ----
   Ring R;
@@ -242,21 +286,11 @@ __global__ void __launch_bounds__(kPT, 1) decode_persist_kernel(const PersistPar
   R.pg = 0;
   R.G = R.ngroups = R.nrows = R.c0 = 0;
   R.rowb = 0;
+  R.ready = false;
   if (lane == 0) {
     for (int e = 0; e < kRingBars; e++) mbar_init(R.bar0 + 8 * e, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
-  __syncwarp();
-  ring_seek(R, P.phases, warp);
-  ring_fill(R, P.phases, ent, warp, lane);
-  const uint8_t* ring_mem = smem + L.ring + (size_t)warp * P.ring_bytes;
-
-  // descriptor of the first phase
-  {
-    const uint4* src = reinterpret_cast<const uint4*>(P.phases + P.first);
-    uint4* dst = reinterpret_cast<uint4*>(smem + L.desc);
-    for (int i = tid; i < (int)(sizeof(Phase) / 16); i += kPT) dst[i] = src[i];
   }
   uint4 wpre = make_uint4(0, 0, 0, 0);
   {
@@ -265,21 +299,21 @@ __global__ void __launch_bounds__(kPT, 1) decode_persist_kernel(const PersistPar
       wpre = __ldg(reinterpret_cast<const uint4*>(f.g.norm_w) + tid);
   }
   __syncthreads();
+  ring_fill(R, win, P.first + kDescSlots - 2, ent, warp, lane);
+  const uint8_t* ring_mem = smem + L.ring + (size_t)warp * P.ring_bytes;
 
   float best_v = -INFINITY;
   int best_i = 0x7fffffff;
   bool has_argmax = false;
 
   for (int k = 0; k < P.count; k++) {
-    Phase& ph = *reinterpret_cast<Phase*>(smem + L.desc + (size_t)(k & 1) * desc_stride);
-    unsigned long long* trec = P.trace ? P.trace + (size_t)(P.first + k) * 4 : nullptr;
+    const int cur = P.first + k;
+    const int limit = cur + kDescSlots - 2;   // last phase whose descriptor is valid in the window during this phase
+    Phase& ph = *reinterpret_cast<Phase*>(smem + L.desc + (size_t)(cur & (kDescSlots - 1)) * desc_stride);
+    unsigned long long* trec = P.trace ? P.trace + (size_t)cur * 4 : nullptr;
     if (trace) trec[0] = global_timer();
-    // descriptor of the next phase into the other slot (read after the next barrier)
-    if (k + 1 < P.count) {
-      const uint4* src = reinterpret_cast<const uint4*>(P.phases + P.first + k + 1);
-      uint4* dst = reinterpret_cast<uint4*>(smem + L.desc + (size_t)((k + 1) & 1) * desc_stride);
-      for (int i = tid; i < (int)(sizeof(Phase) / 16); i += kPT) dst[i] = src[i];
-    }
+    // one more descriptor into the slot the previous phase has left (valid after the next barrier)
+    if (cur + kDescSlots - 1 <= last_phase) copy_desc(cur + kDescSlots - 1);
 
     if (ph.type == PH_GEMV) {
       const GemvParams& p = ph.g;
@@ -340,7 +374,8 @@ __global__ void __launch_bounds__(kPT, 1) decode_persist_kernel(const PersistPar
         __syncwarp();   // every lane has consumed the group
         R.used -= fp;
         R.consumed++;
-        ring_fill(R, P.phases, ent, warp, lane);
+        // more groups of this phase to come: keep the ring full; after the last one the refill waits for the barrier
+        if (g + kPW < n_groups || cur == last_phase) ring_fill(R, win, limit, ent, warp, lane);
         const int v = c0 + g * G + ri;
         const bool mine = (lane & 3) == 0 && ri < nr;
         VRow vr = {nullptr, 0, 0};
@@ -363,14 +398,15 @@ __global__ void __launch_bounds__(kPT, 1) decode_persist_kernel(const PersistPar
       if (trace) trec[1] = global_timer();
     }
     if (trace) trec[2] = global_timer();
-    if (trec && tid == 0 && k + 1 == P.count) atomicMax(trec + 3, global_timer());
+    if (trec && tid == 0 && cur == last_phase) atomicMax(trec + 3, global_timer());
 
-    if (k + 1 < P.count) {
-      const Phase& nx = P.phases[P.first + k + 1];
+    if (cur < last_phase) {
+      const Phase& nx = win.at(cur + 1);
       if (nx.type == PH_GEMV && nx.g.prologue == BK_PRO_RMSNORM && tid < nx.g.K / 8)
         wpre = __ldg(reinterpret_cast<const uint4*>(nx.g.norm_w) + tid);
       const unsigned int gen = ep * 4096u + (unsigned int)k + 1u;
-      if (!grid_barrier(P.flags, gen, P.status, misc, trec)) {
+      const unsigned int target = cbase + (unsigned int)(k + 1) * gridDim.x;
+      if (!grid_barrier(P, gen, target, misc, trec, R, win, limit + 1, ent)) {
         // leave: wait (bounded) for the copies this warp still has in flight, then return
         while (R.consumed != R.issued) {
           wait_group(R.bar0 + 8 * (R.consumed % kRingBars), (R.consumed / kRingBars) & 1u, P.status);
@@ -424,9 +460,12 @@ __global__ void __launch_bounds__(kPT, 1) decode_persist_kernel(const PersistPar
       }
     }
   }
-  // the next launch must see a new generation base; every CTA has read `ep` (it passed this launch's barriers, or
-  // the launch has none)
-  if (blockIdx.x == 0 && tid == 0) *P.epoch = ep + 1;
+  // The next launch needs a new generation / counter base.  Every CTA has read the old ones: it has passed this
+  // launch's barriers, or the launch has none.
+  if (blockIdx.x == 0 && tid == 0) {
+    *P.epoch = ep + 1;
+    *P.counter_base = cbase + (unsigned int)(P.count - 1) * gridDim.x;
+  }
 }
 
 struct Plan {
@@ -625,6 +664,10 @@ int32_t bk_plan_launch(uint64_t plan, int first, int count, int parity, const Bk
   P.count = count;
   P.flags = pl->d_flags;
   P.epoch = pl->d_flags + pl->grid;
+  P.counter = pl->d_flags + pl->grid + 2;
+  P.counter_base = pl->d_flags + pl->grid + 3;
+  P.barrier_mode = c.step_barrier_mode;
+  P.barrier_polls = c.spin_limit > 0 ? c.spin_limit : kBarrierPolls;
   P.status = c.d_status;
   P.trace = (c.step_trace && c.step_trace_phases >= (int)pl->ph[0].size()) ? c.step_trace : nullptr;
   P.ring_bytes = pl->ring_bytes;

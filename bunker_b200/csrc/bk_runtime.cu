@@ -40,7 +40,8 @@ int32_t bkInit(int32_t device) {
   g_ctx.smem_optin = prop.sharedMemPerBlockOptin;
   BK_CUDA(cudaStreamCreateWithFlags(&g_ctx.stream, cudaStreamNonBlocking));
   BK_CUDA(cudaMalloc((void**)&g_ctx.d_status, sizeof(int)));
-  BK_CUDA(cudaMemset(g_ctx.d_status, 0, sizeof(int)));
+  BK_CUDA(cudaMemsetAsync(g_ctx.d_status, 0, sizeof(int), g_ctx.stream));   // ordered on the library stream, then awaited
+  BK_CUDA(cudaStreamSynchronize(g_ctx.stream));
   g_ctx.launches = 0;
   g_ctx.ready = true;
   return BK_OK;
@@ -145,7 +146,8 @@ int32_t bkSync(void) {
   int st = 0;
   BK_CUDA(cudaMemcpy(&st, g_ctx.d_status, sizeof(int), cudaMemcpyDeviceToHost));
   if (st != 0) {
-    cudaMemset(g_ctx.d_status, 0, sizeof(int));
+    cudaMemsetAsync(g_ctx.d_status, 0, sizeof(int), g_ctx.stream);
+    cudaStreamSynchronize(g_ctx.stream);
     return bk_fail(st, "bkSync: a kernel reported status %d (a bounded device-side wait gave up)", st);
   }
   return BK_OK;
@@ -207,6 +209,20 @@ int32_t bkStepTraceEnable(uint64_t dev_buf, int32_t max_phases) {
   BK_ARG(dev_buf && max_phases > 0, "bkStepTraceEnable: bad arguments");
   g_ctx.step_trace = bk_ptr<unsigned long long>(dev_buf);
   g_ctx.step_trace_phases = max_phases;
+  return BK_OK;
+}
+
+int32_t bkSetSpinLimit(int32_t polls) {
+  BK_REQUIRE_INIT();
+  BK_ARG(polls >= 0, "bkSetSpinLimit: polls=%d", polls);
+  g_ctx.spin_limit = polls;
+  return BK_OK;
+}
+
+int32_t bkStepBarrierMode(int32_t mode) {
+  BK_REQUIRE_INIT();
+  BK_ARG(mode == 0 || mode == 1, "bkStepBarrierMode: mode %d", mode);
+  g_ctx.step_barrier_mode = mode;
   return BK_OK;
 }
 

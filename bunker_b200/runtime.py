@@ -104,6 +104,8 @@ SIGNATURES = {
     "bkTraceCtas": (_I32, [_U64, _I32]),
     "bkTraceDisable": (_I32, []),
     "bkStepTraceEnable": (_I32, [_U64, _I32]),
+    "bkStepBarrierMode": (_I32, [_I32]),
+    "bkSetSpinLimit": (_I32, [_I32]),
     "bkGemvQ4K": (_I32, [C.POINTER(bkGemvArgs)]),
     "bkGemvQ4KSimple": (_I32, [_U64, _I32, _I32, _U64, _I32, _U64]),
     "bkDequantQ4K": (_I32, [_U64, _I32, _I32, _U64]),

@@ -316,7 +316,7 @@ BK_API int32_t bkCommAllReduceResidual(uint64_t comm, int32_t slot, uint64_t par
                                        uint64_t out_bf16);
 
 /* cuLaunch-shaped entry (src/ttir.ts:321-348): op id + 8-byte argument slots.
- * Slot lists per op are documented in INTEGRATION.md. */
+ * Slot lists per op: the comment beside every case of bkLaunch in bunker_b200/csrc/bk_launch.cu. */
 BK_API int32_t bkLaunch(int32_t op, const uint64_t* slots, int32_t nslots);
 #define BK_OP_EMBED 1
 #define BK_OP_RMSNORM 2

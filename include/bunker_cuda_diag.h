@@ -31,6 +31,14 @@ BK_API int32_t bkTuneGemvRing(int32_t warps, int32_t rows_per_group, int32_t max
  * 2 CTA 0 finished its rows, 3 the latest CTA finished (atomic max; clear the buffer between steps).  Takes effect
  * for launches issued eagerly after the call (bkDecodeStepEager); captured graphs keep what they were captured with. */
 BK_API int32_t bkStepTraceEnable(uint64_t dev_buf, int32_t max_phases);
+/* Polls a bounded device-side wait may take before it gives up and sets the status word that bkSync reports as
+ * BK_ERR_TIMEOUT (0 restores the built-in limits).  Applies to the tensor-parallel exchange consumer
+ * (bkReduceRmsNormQuantQ8_1 and the model's reducing launches) and the persistent step kernel's grid barrier, for
+ * launches issued after the call.  Lets a test make a wait run out in microseconds without hanging anything. */
+BK_API int32_t bkSetSpinLimit(int32_t polls);
+/* Grid barrier of the persistent step kernel, for models finalized after the call: 0 = one arrival word per CTA
+ * (the default), 1 = one atomic counter. */
+BK_API int32_t bkStepBarrierMode(int32_t mode);
 /* One decode step enqueued without the CUDA graph (device-side token feedback), so that timelines enabled after
  * bkModelFinalize apply to it. */
 BK_API int32_t bkDecodeStepEager(uint64_t model);

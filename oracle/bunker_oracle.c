@@ -31,8 +31,23 @@
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 #define ORC_API __attribute__((visibility("default")))
+
+/* Threads of the OpenMP loops below.  A launcher may have exported OMP_NUM_THREADS=1 for its worker processes; a
+ * caller that times this library as a CPU baseline sets the count it wants and reads back the one in effect. */
+ORC_API int orc_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}
 
 /* ------------------------------------------------------------------------ */
 /* Number formats                                                           */

@@ -49,6 +49,14 @@ def lib() -> C.CDLL:
     return _lib
 
 
+def set_threads(n: int = 0) -> int:
+    """Set the OpenMP thread count of the oracle's loops (n <= 0: leave it) and return the count in effect."""
+    fn = lib().orc_set_threads
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_int]
+    return int(fn(int(n)))
+
+
 def _p(a: np.ndarray):
     assert a.flags["C_CONTIGUOUS"], "oracle arrays must be C-contiguous"
     return a.ctypes.data_as(C.c_void_p)
