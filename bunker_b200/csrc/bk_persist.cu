@@ -68,7 +68,7 @@ struct PersistParams {
   int barrier_mode;
   int barrier_polls;            // polls before a barrier gives up
   int* status;
-  unsigned long long* trace;   // 4 slots per phase of the plan, or null
+  unsigned long long* trace;   // 8 slots per phase of the plan, or null
   uint32_t ring_bytes;         // per warp
   uint32_t scratch_bytes;
   StepIO io;
@@ -210,7 +210,6 @@ __device__ __forceinline__ bool grid_barrier(const PersistParams& P, unsigned in
     }
     __syncwarp();
   }
-  ring_fill(R, win, limit, ent, warp, lane);
   if (warp == kPW - 1) {
     bool ok = false;
     for (int it = 0; it < P.barrier_polls; it++) {
@@ -310,7 +309,7 @@ __global__ void __launch_bounds__(kPT, 1) decode_persist_kernel(const PersistPar
     const int cur = P.first + k;
     const int limit = cur + kDescSlots - 2;   // last phase whose descriptor is valid in the window during this phase
     Phase& ph = *reinterpret_cast<Phase*>(smem + L.desc + (size_t)(cur & (kDescSlots - 1)) * desc_stride);
-    unsigned long long* trec = P.trace ? P.trace + (size_t)cur * 4 : nullptr;
+    unsigned long long* trec = P.trace ? P.trace + (size_t)cur * 8 : nullptr;
     if (trace) trec[0] = global_timer();
     // one more descriptor into the slot the previous phase has left (valid after the next barrier)
     if (cur + kDescSlots - 1 <= last_phase) copy_desc(cur + kDescSlots - 1);
@@ -339,6 +338,10 @@ __global__ void __launch_bounds__(kPT, 1) decode_persist_kernel(const PersistPar
       }
       __syncthreads();
       if (trace) trec[1] = global_timer();
+      // The activation is staged: from here to the end of the phase this CTA needs nothing from global memory, so this
+      // is where the weights of the coming phases are requested (not during the barrier or the activation loads,
+      // whose latency the burst would stretch).
+      ring_fill(R, win, limit, ent, warp, lane);
 
       const int K = p.K, nunits = K / 64, nblk = K / 32;
       const int c0 = blockIdx.x * p.rows_per_cta;
@@ -356,6 +359,7 @@ __global__ void __launch_bounds__(kPT, 1) decode_persist_kernel(const PersistPar
         const uint32_t parity = (R.consumed / kRingBars) & 1u;
         const uint32_t off = ent[2 * e], fp = ent[2 * e + 1];
         wait_group(R.bar0 + 8 * e, parity, P.status);
+        if (trace && g == warp) trec[4] = global_timer();
         const uint8_t* wbase = ring_mem + off;
         float acc[8];
 #pragma unroll
@@ -372,25 +376,29 @@ __global__ void __launch_bounds__(kPT, 1) decode_persist_kernel(const PersistPar
           }
         }
         __syncwarp();   // every lane has consumed the group
+        if (trace && g == warp) trec[5] = global_timer();
         R.used -= fp;
         R.consumed++;
-        // more groups of this phase to come: keep the ring full; after the last one the refill waits for the barrier
-        if (g + kPW < n_groups || cur == last_phase) ring_fill(R, win, limit, ent, warp, lane);
+        // more groups of this phase to come: keep the ring full; after the last one the refill waits for the next phase
+        if (g + kPW < n_groups) ring_fill(R, win, limit, ent, warp, lane);
         const int v = c0 + g * G + ri;
         const bool mine = (lane & 3) == 0 && ri < nr;
         VRow vr = {nullptr, 0, 0};
         if (mine) vr = decode_vrow(p, v);
         const SegDev& sg = p.segs[vr.si];
+        if (trace && g == warp) trec[6] = global_timer();
         const float y = warp_sum8(acc);
         const float yup = __shfl_xor_sync(0xffffffffu, y, 4);   // the odd neighbour row (the "up" row of a SwiGLU pair)
         if (mine && !(sg.epi == BK_EPI_SWIGLU && (ri & 1))) {
           store_epilogue<false, true>(p, sg, (size_t)sg.col_off + vr.n, y, yup);
           if (argmax) argmax_merge_p(best_v, best_i, y, P.io.vocab_offset + vr.n);
         }
+        if (trace && g == warp) trec[7] = global_timer();
       }
     } else if (ph.type == PH_GDN) {
       const GdnParams& d = ph.d;
       GdnSmem& gsm = *reinterpret_cast<GdnSmem*>(scratch);
+      ring_fill(R, win, limit, ent, warp, lane);
       for (int i = blockIdx.x; i < d.Hv * d.B; i += gridDim.x) {
         gdn_step_body<false, true>(d, gsm, i % d.Hv, i / d.Hv);
         __syncthreads();

@@ -267,10 +267,10 @@ BK_API int32_t bkModelSetTensor(uint64_t model, const char* name, uint64_t dev_p
  * embedding table is registered whole (replicated).  Shard shapes are derived from the config by the rule in
  * bunker_b200/model.py `shard_weights`. */
 BK_API int32_t bkModelSetComm(uint64_t model, uint64_t comm);
-/* How the decode step is issued (before bkModelFinalize).  0: the library's choice; 1: one launch per op, the shape of
- * the reference's loop (src/runner.ts:146-149), chained with programmatic dependent launch; 2: the persistent step
- * kernel -- a few cooperative launches per token that run the ops as phases with device-side barriers (batch 1 on
- * one GPU only; bkModelFinalize fails if the model's shapes do not fit it).  All modes give the same bits. */
+/* How the decode step is issued (before bkModelFinalize).  0: the library's choice (currently 1); 1: one launch per
+ * op, the shape of the reference's loop (src/runner.ts:146-149), chained with programmatic dependent launch; 2: the
+ * persistent step kernel -- a few cooperative launches per token that run the ops as phases with device-side barriers
+ * (batch 1 on one GPU only; bkModelFinalize fails if the model's shapes do not fit it).  All modes give the same bits. */
 BK_API int32_t bkModelSetStepMode(uint64_t model, int32_t mode);
 /* Checks the tensor set, allocates state and activations, captures the step graphs.  With tp_size > 1 every rank
  * must call it at about the same time: it runs one step, which exchanges with the peers. */

@@ -27,8 +27,9 @@ BK_API int32_t bkTraceDisable(void);
  * library's own choice. */
 BK_API int32_t bkTuneGemvRing(int32_t warps, int32_t rows_per_group, int32_t max_depth);
 /* Per-phase timeline of the persistent step kernel.  While enabled, every launch of that kernel stamps %globaltimer
- * (ns) into dev_buf[4*phase + k] for each phase it runs: 0 phase entered (CTA 0), 1 activation staged (CTA 0),
- * 2 CTA 0 finished its rows, 3 the latest CTA finished (atomic max; clear the buffer between steps).  Takes effect
+ * (ns) into dev_buf[8*phase + k] for each phase it runs: 0 phase entered (CTA 0), 1 activation staged (CTA 0),
+ * 2 CTA 0 finished its rows, 3 the latest CTA finished (atomic max; clear the buffer between steps), and for warp 0's
+ * first row group of a GEMV phase 4 weights landed, 5 dot products done, 6 ring refilled, 7 epilogue stored.  Takes effect
  * for launches issued eagerly after the call (bkDecodeStepEager); captured graphs keep what they were captured with. */
 BK_API int32_t bkStepTraceEnable(uint64_t dev_buf, int32_t max_phases);
 /* Polls a bounded device-side wait may take before it gives up and sets the status word that bkSync reports as

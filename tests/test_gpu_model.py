@@ -200,7 +200,7 @@ def test_scaled_model_shapes_batch8_tensor_core_path(bk):
 
 @pytest.mark.parametrize("interval,n_layers", [(4, 4), (1, 2), (2, 3), (4, 3)])
 def test_persistent_step_equals_per_op_step_and_oracle(bk, interval, n_layers):
-    """Batch 1 on one GPU runs as a persistent kernel (phases + device-side barriers) by default.  The same model
+    """Batch 1 on one GPU can run as a persistent kernel (phases + device-side barriers, step mode 2).  The same model
     stepped with one launch per op must give the same tokens and bit-identical logits, and both match the oracle --
     also when every layer is an attention layer (interval 1) or the model ends on GDN layers."""
     cfg = M.CONFIG_TINY.with_(full_attn_interval=interval, n_layers=n_layers, max_len=96)
