@@ -26,7 +26,7 @@ struct BkContext {
   unsigned long long* step_trace = nullptr;  // per-phase timeline of the persistent step kernel (bkStepTraceEnable)
   int step_trace_phases = 0;          // phases the buffer can hold (4 slots each)
   int spin_limit = 0;                 // polls a bounded device-side wait may take (bkSetSpinLimit; 0 = built-in limits)
-  int step_barrier_mode = 0;          // grid barrier of the persistent step kernel: 0 one word per CTA, 1 one counter
+  int step_barrier_mode = 1;          // grid barrier of the persistent step kernel: 0 one word per CTA, 1 one counter (faster, measured)
   int* d_status = nullptr;           // device word set by kernels whose bounded waits gave up
   float* gemv_carry = nullptr;       // class accumulators handed from one K part of a split GEMV to the next
   size_t gemv_carry_bytes = 0;
@@ -164,4 +164,5 @@ int32_t bk_plan_add_gdn(uint64_t plan, const bkGdnArgs& a);   // odd conv-state 
 int32_t bk_plan_count(uint64_t plan);
 int32_t bk_plan_finish(uint64_t plan);
 int32_t bk_plan_launch(uint64_t plan, int first, int count, int parity, const BkStepIO& io);
+int32_t bk_plan_reset(uint64_t plan);
 void bk_plan_destroy(uint64_t plan);

@@ -598,6 +598,7 @@ int32_t reset_state(Model& m) {
   BK_CUDA(cudaMemsetAsync(bk_ptr<void>(m.pos), 0, (size_t)m.B * 4, st));
   BK_CUDA(cudaMemsetAsync(bk_ptr<void>(m.ids), 0, (size_t)m.B * 4, st));
   BK_CUDA(cudaMemsetAsync(bk_ptr<void>(m.hist), 0, (size_t)c.max_len * m.B * 4, st));
+  if (m.plan) TRY(bk_plan_reset(m.plan));
   m.steps = 0;
   m.conv_cur = 0;
   return BK_OK;

@@ -186,6 +186,12 @@ BK_DEVINL bool wait_group(uint32_t bar, uint32_t parity, int* status) {
   atomicExch(status, BK_ERR_TIMEOUT);
   return false;
 }
+// On the way out after a failed barrier: the copies this warp has requested must have landed before the CTA may
+// exit (they write its shared memory), whatever the status word says.  Bounded all the same.
+BK_DEVINL void drain_group(uint32_t bar, uint32_t parity) {
+  for (int it = 0; it < (1 << 22); it++)
+    if (mbar_try_wait(bar, parity)) return;
+}
 BK_DEVINL unsigned long long global_timer() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -304,6 +310,7 @@ __global__ void __launch_bounds__(kPT, 1) decode_persist_kernel(const PersistPar
   float best_v = -INFINITY;
   int best_i = 0x7fffffff;
   bool has_argmax = false;
+  bool dead = false;   // a wait for weights gave up: no further row groups are consumed by this warp
 
   for (int k = 0; k < P.count; k++) {
     const int cur = P.first + k;
@@ -353,12 +360,17 @@ __global__ void __launch_bounds__(kPT, 1) decode_persist_kernel(const PersistPar
       const bool swiglu = p.segs[0].epi == BK_EPI_SWIGLU;
       const bool argmax = (ph.flags & BK_PF_ARGMAX) != 0;
       has_argmax = has_argmax || argmax;
-      for (int g = warp; g < n_groups; g += kPW) {
+      for (int g = warp; g < n_groups && !dead; g += kPW) {
         const int nr = min(G, n_rows_cta - g * G);
         const uint32_t e = R.consumed % kRingBars;
         const uint32_t parity = (R.consumed / kRingBars) & 1u;
         const uint32_t off = ent[2 * e], fp = ent[2 * e + 1];
-        wait_group(R.bar0 + 8 * e, parity, P.status);
+        if (!wait_group(R.bar0 + 8 * e, parity, P.status)) {
+          // the weights did not arrive (or another wait already failed): this warp stops consuming; the next barrier
+          // sees the status word and winds the launch down
+          dead = true;
+          break;
+        }
         if (trace && g == warp) trec[4] = global_timer();
         const uint8_t* wbase = ring_mem + off;
         float acc[8];
@@ -417,12 +429,17 @@ __global__ void __launch_bounds__(kPT, 1) decode_persist_kernel(const PersistPar
       if (!grid_barrier(P, gen, target, misc, trec, R, win, limit + 1, ent)) {
         // leave: wait (bounded) for the copies this warp still has in flight, then return
         while (R.consumed != R.issued) {
-          wait_group(R.bar0 + 8 * (R.consumed % kRingBars), (R.consumed / kRingBars) & 1u, P.status);
+          drain_group(R.bar0 + 8 * (R.consumed % kRingBars), (R.consumed / kRingBars) & 1u);
           R.consumed++;
         }
         return;
       }
     }
+  }
+
+  while (dead && R.consumed != R.issued) {
+    drain_group(R.bar0 + 8 * (R.consumed % kRingBars), (R.consumed / kRingBars) & 1u);
+    R.consumed++;
   }
 
   // ---- argmax over the lm_head rows of this launch: per CTA, then the CTA that arrives last merges ----
@@ -707,6 +724,15 @@ int32_t bk_plan_launch(uint64_t plan, int first, int count, int parity, const Bk
   cfg.numAttrs = 1;
   BK_CUDA(cudaLaunchKernelEx(&cfg, decode_persist_kernel, P));
   BK_CHECK_LAUNCH();
+  return BK_OK;
+}
+
+// Barrier words, generation bases and the argmax counter back to zero (after a launch that gave up they are in an
+// unknown state).  Enqueued on the library stream.
+int32_t bk_plan_reset(uint64_t plan) {
+  Plan* pl = as_plan(plan);
+  BK_ARG(pl && pl->finished, "step plan: not finished");
+  BK_CUDA(cudaMemsetAsync(pl->d_flags, 0, ((size_t)pl->grid + 8) * 4, bk_ctx().stream));
   return BK_OK;
 }
 

@@ -64,6 +64,48 @@ def max_over_ranks(x: float) -> float:
     return float(t.item())
 
 
+class PeerLost(RuntimeError):
+    """A tensor-parallel peer has left (or stopped answering) between two steps."""
+
+
+class StepGate:
+    """Host-side liveness check between decode steps, over the process group's key-value store.
+
+    A tensor-parallel step exchanges partial sums with every peer on the device; a rank that is gone would leave the
+    others waiting on the device until their bounded waits give up.  The gate moves that discovery to the host and
+    before the launch: every rank posts `gate/<step>/<rank>` and then looks for the same key of its peers; a rank
+    that leaves on purpose posts `left/<rank>` first.  A missing key after `timeout_s`, or a `left` key, raises
+    PeerLost -- an error code path, never a hang and never a GPU fault.  A rank leaves only between steps, with none
+    of its kernels in flight."""
+
+    def __init__(self, store=None, rank: int | None = None, world: int | None = None, poll_s: float = 0.005):
+        import torch.distributed as dist
+        if store is None:
+            from torch.distributed.distributed_c10d import _get_default_store
+            store = _get_default_store()
+        self.store = store
+        self.rank = dist.get_rank() if rank is None else rank
+        self.world = dist.get_world_size() if world is None else world
+        self.poll_s = poll_s
+
+    def leave(self) -> None:
+        self.store.set(f"left/{self.rank}", b"1")
+
+    def arrive(self, step: int, timeout_s: float = 5.0) -> None:
+        import time
+        self.store.set(f"gate/{step}/{self.rank}", b"1")
+        deadline = time.monotonic() + timeout_s
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            while not self.store.check([f"gate/{step}/{r}"]):
+                if self.store.check([f"left/{r}"]):
+                    raise PeerLost(f"rank {r} left before step {step}")
+                if time.monotonic() > deadline:
+                    raise PeerLost(f"rank {r} did not reach step {step} within {timeout_s} s")
+                time.sleep(self.poll_s)
+
+
 def shutdown() -> None:
     import torch.distributed as dist
     if dist.is_initialized():

@@ -275,7 +275,8 @@ BK_API int32_t bkModelSetStepMode(uint64_t model, int32_t mode);
 /* Checks the tensor set, allocates state and activations, captures the step graphs.  With tp_size > 1 every rank
  * must call it at about the same time: it runs one step, which exchanges with the peers. */
 BK_API int32_t bkModelFinalize(uint64_t model);
-/* Zero the recurrent state, conv state, KV cache and position. */
+/* Zero the recurrent state, conv state, KV cache and position.  Also the way back after bkSync reported
+ * BK_ERR_TIMEOUT for a decode step (a step that gave up leaves the state half-written). */
 BK_API int32_t bkModelReset(uint64_t model);
 /* One decode step (runGraphDecode's loop body, src/runner.ts:133-160).  tokens: B host ints, or NULL to
  * feed back the previous step's argmax on the device.  out_ids / out_vals: B host values each, or NULL to

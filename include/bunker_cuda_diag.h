@@ -38,7 +38,7 @@ BK_API int32_t bkStepTraceEnable(uint64_t dev_buf, int32_t max_phases);
  * launches issued after the call.  Lets a test make a wait run out in microseconds without hanging anything. */
 BK_API int32_t bkSetSpinLimit(int32_t polls);
 /* Grid barrier of the persistent step kernel, for models finalized after the call: 0 = one arrival word per CTA
- * (the default), 1 = one atomic counter. */
+ * , 1 = one atomic counter (the default: 1.8 us against 3-5 us per barrier on 148 CTAs). */
 BK_API int32_t bkStepBarrierMode(int32_t mode);
 /* One decode step enqueued without the CUDA graph (device-side token feedback), so that timelines enabled after
  * bkModelFinalize apply to it. */

@@ -75,12 +75,14 @@ def test_model_rejects_missing_tensor(bk):
     assert lib.bkModelDestroy(h.value) == 0
 
 
-def test_full_size_model_first_steps_match_oracle(bk):
+@pytest.mark.parametrize("mode", [1, 2])
+def test_full_size_model_first_steps_match_oracle(bk, mode):
     """configs[3] at full size (24 layers, hidden 2048, vocabulary 151936): 3 prompt tokens + 3 greedy steps
-    against the oracle (about 1.1 GB of Q4_K weights per token on the CPU), logits bit-exact."""
+    against the oracle (about 1.1 GB of Q4_K weights per token on the CPU), logits bit-exact; once with one launch
+    per op, once with the persistent step kernel."""
     cfg = M.CONFIG_HYBRID_24L.with_(max_len=64)
     w = M.synth_weights(cfg)
-    gm = M.DecodeModel(cfg, w, batch=1)
+    gm = M.DecodeModel(cfg, w, batch=1, step_mode=mode)
     info = gm.info()
     om = OracleModel(cfg, w, batch=1, split_len=info["split_len"], attn_warps=info["attn_warps"])
     prompt = np.random.default_rng(3).integers(0, cfg.vocab, (3, 1)).astype(np.int32)
@@ -91,6 +93,66 @@ def test_full_size_model_first_steps_match_oracle(bk):
         assert np.array_equal(ids_g, ids_o), f"step {t}"
         assert_same_bits(gm.logits(), om.logits, f"logits at step {t}")
     assert np.isfinite(om.logits).all()
+    gm.destroy()
+
+
+def test_full_size_model_256_greedy_steps_match_oracle(bk):
+    """The whole configs[3] workload at batch 1: 32-token random prompt, then 256 greedy steps, on the full 24-layer
+    model.  Every token must equal the oracle's (the CPU takes about 0.15 s per token), the max logit bit for bit,
+    and the full logits at the first generated step and at the end."""
+    from oracle import oracle as O
+    import os
+    O.set_threads(os.cpu_count() or 1)
+    P, G = 32, 256
+    cfg = M.CONFIG_HYBRID_24L.with_(max_len=P + G + 32)
+    w = M.synth_weights(cfg)
+    gm = M.DecodeModel(cfg, w, batch=1)
+    info = gm.info()
+    om = OracleModel(cfg, w, batch=1, split_len=info["split_len"], attn_warps=info["attn_warps"])
+    prompt = np.random.default_rng(0xB0B0 + 3000).integers(0, cfg.vocab, (P, 1)).astype(np.int32)
+    ids_g = ids_o = None
+    min_gap = np.inf
+    for t in range(P + G - 1):
+        ids_o, val_o = om.step(prompt[t] if t < P else ids_o)
+        ids_g, val_g = gm.step(prompt[t] if t < P else ids_g)
+        assert np.array_equal(ids_g, ids_o), f"step {t}: gpu {ids_g} oracle {ids_o}"
+        assert_same_bits(val_g, val_o, f"step {t} max logit")
+        if t in (P - 1, P + G - 2):
+            assert_same_bits(gm.logits(), om.logits, f"logits at step {t}")
+        top2 = np.partition(om.logits[0], -2)[-2:]
+        min_gap = min(min_gap, float(top2[1] - top2[0]))
+    print(f"smallest top-1/top-2 logit gap over {P + G - 1} steps: {min_gap:.3e}")
+    gm.destroy()
+
+
+def test_persistent_step_barrier_gives_up_cleanly(bk):
+    """The grid barrier of the persistent step kernel with a poll limit of 1: some CTA's first look at the arrival
+    counter comes too early, its barrier gives up, sets the status word and the launch winds down by itself (every
+    other wait ends as soon as it sees the status).  bkSync must report BK_ERR_TIMEOUT and clear it; afterwards, with
+    the limit restored and the state reset, the same model must decode exactly like a fresh one."""
+    cfg = M.CONFIG_TINY.with_(max_len=64)
+    w = M.synth_weights(cfg, seed=9)
+    prompt = np.random.default_rng(2).integers(0, cfg.vocab, (4, 1)).astype(np.int32)
+    lib = R.cu()
+    gm = M.DecodeModel(cfg, w, batch=1, step_mode=2)
+    want = M.runGraphDecode(gm, prompt, 12)
+    gm.reset()
+    assert R.cuSync() == 0
+    R._check(lib.bkSetSpinLimit(1))
+    try:
+        seen = 0
+        for _ in range(20):                      # eager launches pick the limit up; a few steps make the race certain
+            gm.step_eager()
+            rc = R.cuSync()
+            assert rc in (0, R.BK_ERR_TIMEOUT)
+            seen += rc == R.BK_ERR_TIMEOUT
+        assert seen > 0, "no barrier ran out with a poll limit of 1"
+    finally:
+        R._check(lib.bkSetSpinLimit(0))
+    assert R.cuSync() == 0
+    gm.reset()
+    got = M.runGraphDecode(gm, prompt, 12)
+    assert np.array_equal(got, want)
     gm.destroy()
 
 

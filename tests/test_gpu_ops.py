@@ -271,14 +271,14 @@ def test_attn_decode_ragged_positions_and_plain(bk):
     assert rel_err(synth.bf16_to_f32(got[b, h * HD:(h + 1) * HD]), plain) < 5e-3  # bf16 output rounding
 
 
-def test_attn_decode_long_context(bk):
-    """configs[2] longest cache (32768 rows), batch 1, default plan; bit-exact against the oracle."""
-    L = 32768
+@pytest.mark.parametrize("B,L", [(1, 32768), (8, 4096), (8, 32768)])
+def test_attn_decode_long_context(bk, B, L):
+    """configs[2] long caches (4096 and 32768 rows) at batch 1 and 8, default plan; bit-exact against the oracle."""
     cos_t, sin_t = ops.rope_tables(L)
-    c = synth.attn_case(1, L)
+    c = synth.attn_case(B, L)
     got, Kg, Vg, split_len, W = _run_attn(c, cos_t, sin_t)
     q, Kc, Vc, want = _attn_oracle(c, cos_t, sin_t, split_len, W)
-    assert_same_bits(got, want, f"attention L={L} split_len={split_len}")
+    assert_same_bits(got, want, f"attention B={B} L={L} split_len={split_len}")
 
 
 def test_argmax(bk):
@@ -384,3 +384,38 @@ def test_exchange_reduce_all_rank_counts_on_one_gpu(bk, n_ranks):
     want_sum = O.epilogue_add(O.sum_ranks(parts), res)
     assert_same_bits(dsum.download(np.uint16, (B, K)), want_sum, "sum of the ranks + residual")
     assert_same_bits(dq.download(np.uint8, (B, K // 32, 36)), O.q8_1_quantize_bf16(O.rmsnorm(want_sum, w)), "norm + Q8_1")
+
+
+def test_exchange_wait_runs_out_and_reports_timeout(bk):
+    """A bounded device-side wait that can never be satisfied: the consumer of the tensor-parallel exchange is given
+    words whose tag never matches and a poll limit of a few hundred.  The launch must return by itself, bkSync must
+    report BK_ERR_TIMEOUT once (and clear the status), and the same call with matching tags must then pass."""
+    B, K, n_ranks = 1, 2048, 2
+    rng = np.random.default_rng(77)
+    parts = rng.normal(0, 1, (n_ranks, B, K)).astype(np.float32)
+    res, w = synth.normal_bf16(rng, (B, K)), synth.normal_bf16(rng, (K,), 0.02)
+    epoch, tag_add = 3, 9
+    stride = B * K
+    words = np.zeros((n_ranks, stride, 2), np.uint32)
+    words[:, :, 0] = parts.reshape(n_ranks, -1).view(np.uint32)
+    words[:, :, 1] = epoch * 256 + tag_add + 1          # a tag this exchange never waits for
+    dw_, de, dres, dnw = dev(words), dev(np.array([epoch], np.uint32)), dev(res), dev(w)
+    dsum, dq = R.DeviceBuffer.zeros(B * K * 2), R.DeviceBuffer(B * K // 32 * 36)
+    lib = R.cu()
+    assert R.cuSync() == 0
+    R._check(lib.bkSetSpinLimit(200))
+    try:
+        R._check(lib.bkReduceRmsNormQuantQ8_1(dw_.ptr, n_ranks, stride, de.ptr, tag_add, dres.ptr, dsum.ptr, dnw.ptr, K, B,
+                                              1e-6, dq.ptr, R.BK_Q8_BLOCKS))
+        assert R.cuSync() == R.BK_ERR_TIMEOUT
+        assert "bounded device-side wait" in R.last_error()
+        assert R.cuSync() == 0                           # reported once, then cleared
+    finally:
+        R._check(lib.bkSetSpinLimit(0))
+    words[:, :, 1] = epoch * 256 + tag_add
+    R.cuHtoD(dw_.ptr, words)
+    R._check(lib.bkReduceRmsNormQuantQ8_1(dw_.ptr, n_ranks, stride, de.ptr, tag_add, dres.ptr, dsum.ptr, dnw.ptr, K, B, 1e-6,
+                                          dq.ptr, R.BK_Q8_BLOCKS))
+    assert R.cuSync() == 0
+    want_sum = O.epilogue_add(O.sum_ranks(parts), res)
+    assert_same_bits(dsum.download(np.uint16, (B, K)), want_sum, "sum of the ranks + residual after a timed-out call")

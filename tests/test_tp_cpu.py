@@ -84,6 +84,54 @@ def test_two_gloo_ranks_shard_and_sum():
     assert all(r[1] == "ok" for r in res), res
 
 
+def _gate_worker(rank: int, world: int, port: int, q, mode: str):
+    try:
+        os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                          MASTER_PORT=str(port))
+        sys.path.insert(0, ROOT)
+        from bunker_b200 import dist
+        dist.init("gloo")
+        gate = dist.StepGate()
+        steps_done = 0
+        try:
+            for step in range(8):
+                if rank == 1 and step == 3:
+                    if mode == "leaves":
+                        gate.leave()          # between steps, nothing of this rank in flight
+                    break                      # "dies": simply never shows up again
+                gate.arrive(step, timeout_s=1.5)
+                steps_done += 1                # the device step would be launched here
+            q.put((rank, "done", steps_done))
+        except dist.PeerLost as e:
+            q.put((rank, "peer lost", steps_done, str(e)))
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        q.put((rank, traceback.format_exc() or repr(e)))
+
+
+@pytest.mark.parametrize("mode", ["leaves", "dies"])
+def test_rank_gone_between_steps_is_an_error_not_a_hang(mode):
+    """Two gloo ranks step through the host-side gate that precedes every tensor-parallel launch.  Rank 1 goes away
+    after three steps -- once announcing it, once silently.  Rank 0 must get PeerLost at the gate of step 3 (at once
+    when the leave was announced, after the gate's timeout otherwise) having launched exactly three steps."""
+    import multiprocessing as mp
+    import time
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gate_worker, args=(r, 2, port, q, mode)) for r in range(2)]
+    t0 = time.monotonic()
+    for p in procs:
+        p.start()
+    res = {r[0]: r for r in (q.get(timeout=120) for _ in procs)}
+    for p in procs:
+        p.join(timeout=30)
+    assert res[1][1] == "done" and res[1][2] == 3, res
+    assert res[0][1] == "peer lost" and res[0][2] == 3, res
+    assert ("left before step 3" in res[0][3]) if mode == "leaves" else ("did not reach step 3" in res[0][3]), res
+    assert time.monotonic() - t0 < 100
+
+
 def test_split_rule_uneven():
     sys.path.insert(0, ROOT)
     from bunker_b200 import model as M
