@@ -14,14 +14,18 @@ def _ngpus() -> int:
     return torch.cuda.device_count()
 
 
-@pytest.mark.parametrize("n,batch", [(2, 1), (2, 2), (4, 1), (4, 3), (8, 1), (8, 2)])
-def test_tensor_parallel_matches_oracle(n, batch):
-    """batch 1: the reduce runs in the next projection's prologue; batch >= 2: in the norm+quantise launch."""
+@pytest.mark.parametrize("n,batch,ffn_per_rank", [(2, 1, 0), (2, 2, 0), (2, 3, 17408), (2, 8, 17408), (4, 1, 0), (4, 3, 0),
+                                                  (4, 5, 17408), (8, 1, 0), (8, 2, 0)])
+def test_tensor_parallel_matches_oracle(n, batch, ffn_per_rank):
+    """batch 1: the reduce runs in the next projection's prologue; batch >= 2: in the norm+quantise launch.  An FFN of
+    17408 columns per rank is too wide for one tensor-core launch: the row-parallel down projection then pushes its
+    partial sums from the split-K / column-pair path."""
     if _ngpus() < n:
         pytest.skip(f"needs {n} GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
-           "--master-port", str(29500 + n), os.path.join(ROOT, "tests", "tp_worker.py"), "24", str(batch)]
+           "--master-port", str(29500 + n), os.path.join(ROOT, "tests", "tp_worker.py"), "12" if ffn_per_rank else "24", str(batch),
+           str(ffn_per_rank)]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert f"TP{n} OK" in out.stdout

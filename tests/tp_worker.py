@@ -1,5 +1,5 @@
 """One tensor-parallel rank of the GPU parity test.  Launched by tests/test_gpu_tp.py (or by hand) as
-    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P tests/tp_worker.py [steps]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P tests/tp_worker.py [steps] [batch] [ffn width per rank]
 Every rank decodes with the library and compares its tokens and its shard of the logits, bit for bit, with the
 CPU oracle emulating the same N ranks."""
 import os
@@ -18,13 +18,16 @@ from bunker_b200 import runtime as R  # noqa: E402
 def main():
     steps = int(sys.argv[1]) if len(sys.argv) > 1 else 40
     B = int(sys.argv[2]) if len(sys.argv) > 2 else 2
+    inter_per_rank = int(sys.argv[3]) if len(sys.argv) > 3 else 0   # > 0: FFN width per rank (a K too wide for one
+                                                                    # tensor-core launch takes the split-K / column-pair path)
     rank, world = dist.init("nccl")
     local = int(os.environ.get("LOCAL_RANK", rank))
     R.cu(local)
     from oracle.model_oracle import OracleModel
     cfg = M.CONFIG_TINY.with_(gdn_k_heads=max(2, world), gdn_v_heads=2 * max(2, world), attn_q_heads=max(4, world),
                               attn_kv_heads=2 if world <= 2 else 1, max_len=64 + steps,
-                              intermediate=256 * max(4, world) + 256, vocab=4099)
+                              intermediate=(inter_per_rank * world) if inter_per_rank else 256 * max(4, world) + 256,
+                              vocab=4099)
     w = M.synth_weights(cfg)
     gm = M.DecodeModel(cfg, w, batch=B, device=local, tp_rank=rank, tp_size=world)
     info = gm.info()
