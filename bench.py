@@ -10,8 +10,11 @@ inputs (1.1 GB of weights) exceed L2, so no flush is needed between timed steps.
 `value`  : tokens/s over K graph-replayed steps with the token fed back on the device (inputs resident).
 `e2e`    : tokens/s over K calls of the per-token API with HOST buffers: token ids copied host->device,
            (id, logit) copied device->host and synchronised every step (the reference's loop, src/runner.ts:133-160).
-`roofline`: the dominant kernel (gemv_q4k_kernel) timed with CUDA-event pairs around each launch of
-           one eagerly launched step; algorithmic bytes = Q4_K weight bytes + activations of those launches.
+`roofline`: the dominant kernel (gemv_q4k_kernel) over all its launches inside the step: weight bytes / (step time x
+           the GEMV share of a per-op CUDA-event profile); `lm_head_alone` = the same kernel on its largest launch, timed
+           back to back between two events.
+`ops`    : stand-alone roofline lines of the GEMV (4096x4096 over rotating weight copies), the GDN step (batch 1, 8) and
+           decode attention (cache 1024 / 4096 / 32768 rows, batch 1, 8): median / min / max of 5 timed regions each.
 `cpu_baseline` / `--impl reference`: the CPU oracle (C restatement of the reference's op math, OpenMP) on the
            host cores.  The reference is TypeScript for bun with Triton-generated GPU kernels; neither bun
            nor its shim exist here, so kind = "port".
@@ -205,6 +208,22 @@ def run_ours(args):
     launches = R.launch_count() - l0
     value = K * B / (ms * 1e-3)
     tokens_resident = gm.tokens(PROMPT_LEN + W, K)
+    # the same region four more times from the same starting state (reset, prompt, warm-up): spread of the measurement
+    region_ms = [ms / K]
+    for _ in range(4):
+        gm.reset()
+        for t in range(PROMPT_LEN):
+            gm.step(prompt[t], read=False)
+        gm.run(W)
+        assert R.cuSync() == 0, R.last_error()
+        dist.barrier()
+        r0, r1 = R.Event(), R.Event()
+        r0.record()
+        gm.run(K)
+        r1.record()
+        r1.synchronize()
+        dist.barrier()
+        region_ms.append(dist.max_over_ranks(r0.elapsed_ms(r1)) / K)
 
     # ---- per-op profile of one eager step (event pair around every launch; launch-bound, shares only) ----
     prof = gm.step_profiled()
@@ -289,9 +308,28 @@ def run_ours(args):
     else:
         cpu = None   # reported at N=1 only
 
+    # GEMV over ALL its launches inside the step: the per-op event profile gives the GEMV classes' share of an eagerly
+    # launched step, the graph-replayed step time scales it; bytes = every Q4_K weight byte of this rank's shard
+    gemv_cls = ("gemv_proj", "gemv_out", "gemv_gateup", "gemv_down", "gemv_lmhead")
+    eager_ms = sum(v[0] for v in prof.values())
+    gemv_share = sum(prof[k][0] for k in gemv_cls) / eager_ms if eager_ms > 0 else 0.0
+    gemv_calls = sum(prof[k][1] for k in gemv_cls)
+    step_us = ms / K * 1e3
+    gemv_in_step_us = gemv_share * step_us
+    wbytes_rank = wbytes / world
+    in_step_gbs = wbytes_rank / (gemv_in_step_us * 1e-6) / 1e9 if gemv_in_step_us > 0 else 0.0
+    peak1 = hbm_peak / world
+    ops_lines = None
+    if world == 1 and not args.no_ops:
+        from bunker_b200 import opbench
+        ops_lines = opbench.run_all(peak1)
+
     line = {
         "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
-        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "ms_per_step": ms / K,
+        "ms_per_step_regions": {"median": float(np.median(region_ms)), "min": float(min(region_ms)),
+                                "max": float(max(region_ms)), "n": len(region_ms),
+                                "note": "the timed K-step region repeated from the same state; value uses the first"}, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8xint4->int32, f32 accumulate", "data": "synthetic",
         "config": {"workload": f"configs[3] hybrid 24-layer Q4_K decode (hidden 2048, vocab 151936), batch {B}, "
                                f"{PROMPT_LEN}-token random prompt then greedy", "batch": B, "parallelism": f"tp{world}",
@@ -303,11 +341,23 @@ def run_ours(args):
                 "transfer": ("mapped pinned host memory: the embed kernel reads the token, the argmax kernel writes id and logit"
                              if world == 1 else "cudaMemcpyAsync from/to pinned host memory")},
         "gpu_launches": int(launches),
-        "roofline": {"bound": "hbm", "kernel": f"gemv_q4k_kernel<{B},8>" if B <= 1 else "gemv_q4k_mma_kernel", "achieved": achieved,
-                     "peak": hbm_peak / world, "unit": "GB/s", "frac": achieved / (hbm_peak / world),
-                     "traffic": NCU_GEMV_LMHEAD_TRAFFIC if (world == 1 and B == 1) else None, "peak_source": peak_src,
-                     "launch": f"lm_head shard [{Vl} x {H}] Q4_K, RMSNorm+Q8_1 prologue, batch {B}",
-                     "avg_launch_us": gemv_us, "algorithmic_bytes_per_launch": gemv_bytes, "launches_timed": reps},
+        "roofline": {"bound": "hbm", "kernel": f"gemv_q4k_kernel<{B},8>" if B <= 1 else "gemv_q4k_mma_kernel",
+                     "achieved": in_step_gbs, "peak": peak1, "unit": "GB/s", "frac": in_step_gbs / peak1,
+                     "traffic": (int(wbytes_rank / max(gemv_calls, 1) * NCU_GEMV_LMHEAD_TRAFFIC / 175646208)
+                                 if (world == 1 and B == 1) else None),
+                     "peak_source": peak_src,
+                     "scope": (f"all {gemv_calls} GEMV launches of one decode step: weight bytes / (graph-replayed step time x the "
+                               "GEMV classes' share of the per-op CUDA-event profile); traffic = the lm_head capture's "
+                               "DRAM bytes scaled by weight bytes"),
+                     "avg_launch_us": gemv_in_step_us / max(gemv_calls, 1),
+                     "algorithmic_bytes_per_launch": wbytes_rank / max(gemv_calls, 1), "launches_timed": gemv_calls,
+                     "gemv_share_of_step": gemv_share,
+                     "lm_head_alone": {"achieved": achieved, "frac": achieved / peak1,
+                                       "traffic": NCU_GEMV_LMHEAD_TRAFFIC if (world == 1 and B == 1) else None,
+                                       "launch": f"lm_head shard [{Vl} x {H}] Q4_K, RMSNorm+Q8_1 prologue, batch {B}, "
+                                                 f"{reps} back-to-back launches between two events",
+                                       "avg_launch_us": gemv_us, "algorithmic_bytes_per_launch": gemv_bytes}},
+        "ops": ops_lines,
         "model_roofline": {"weight_bytes_per_step": wbytes, "achieved_gbs": wbytes / (ms / K * 1e-3) / 1e9,
                            "frac_of_hbm": wbytes / (ms / K * 1e-3) / 1e9 / hbm_peak,
                            "roofline_tok_s": hbm_peak * 1e9 / wbytes * B},
@@ -328,6 +378,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--no-batch8", action="store_true", help="skip the extra batch-8 leg of the default run")
+    ap.add_argument("--no-ops", action="store_true", help="skip the stand-alone per-kernel roofline lines (key `ops`)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
     if args.warmup < 3:
