@@ -248,6 +248,12 @@ class DecodeModel:
         for name, _, _ in specs:
             a = np.ascontiguousarray(weights[name])
             R.cuHtoD(self.slab.ptr + offs[name], a)
+        self._create(lib, {name: (self.slab.ptr + offs[name], weights[name].nbytes) for name, _, _ in specs}, step_mode)
+
+
+    def _create(self, lib, tensor_ptrs: dict, step_mode: int) -> None:
+        """bkModelCreate + one bkModelSetTensor per weight (device pointer, bytes) + bkModelFinalize."""
+        cfg, batch, tp_rank, tp_size = self.cfg, self.batch, self.tp_rank, self.tp_size
         c = bkModelConfig(hidden=cfg.hidden, n_layers=cfg.n_layers, full_attn_interval=cfg.full_attn_interval,
                           vocab=cfg.vocab, gdn_k_heads=cfg.gdn_k_heads, gdn_v_heads=cfg.gdn_v_heads,
                           attn_q_heads=cfg.attn_q_heads, attn_kv_heads=cfg.attn_kv_heads, head_dim=cfg.head_dim,
@@ -256,8 +262,8 @@ class DecodeModel:
         h = C.c_uint64(0)
         R._check(lib.bkModelCreate(C.byref(c), C.byref(h)))
         self.handle = h.value
-        for name, _, _ in specs:
-            R._check(lib.bkModelSetTensor(self.handle, name.encode(), self.slab.ptr + offs[name], weights[name].nbytes))
+        for name, (ptr, nbytes) in tensor_ptrs.items():
+            R._check(lib.bkModelSetTensor(self.handle, name.encode(), ptr, nbytes))
         if tp_size > 1:
             from . import dist
             R._check(lib.bkModelSetComm(self.handle, self.comm))
@@ -271,6 +277,19 @@ class DecodeModel:
         self._ids = (C.c_int32 * batch)()
         self._out = (C.c_int32 * batch)()
         self._val = (C.c_float * batch)()
+
+    @classmethod
+    def from_device(cls, cfg: ModelConfig, tensor_ptrs: dict, slab, batch: int = 1, device: int = 0,
+                    step_mode: int = 0) -> "DecodeModel":
+        """A single-GPU model over weights that already sit in device memory (the loader's path): tensor_ptrs maps
+        every name of tensor_specs(cfg) to (device pointer, bytes); `slab` is the DeviceBuffer that owns them."""
+        self = object.__new__(cls)
+        self.cfg, self.batch, self.tp_rank, self.tp_size, self.comm = cfg, batch, 0, 1, 0
+        lib = R.cu(device)
+        self.slab = slab
+        self.offsets = {n: p - slab.ptr for n, (p, _) in tensor_ptrs.items()}
+        self._create(lib, tensor_ptrs, step_mode)
+        return self
 
     def info(self) -> dict:
         sl, w, k, st = C.c_int32(), C.c_int32(), C.c_int32(), C.c_int64()

@@ -45,6 +45,11 @@ def block_dots(W: int, N: int, K: int, xq: int, isum: int, qsum: int) -> None:
     _check(cu().bkBlockDotsQ4K(W, N, K, xq, isum, qsum))
 
 
+def quantize_q4k(x: int, n_rows: int, K: int, out: int, bf16: bool = False) -> None:
+    """Weight rows f32 / bf16 [n_rows][K] -> Q4_K rows (the loader's quantiser)."""
+    _check(cu().bkQuantizeQ4K(x, R.BK_DTYPE_BF16 if bf16 else R.BK_DTYPE_F32, n_rows, K, out))
+
+
 def quant_q8_1(x: int, K: int, B: int, out: int, bf16: bool = False) -> None:
     _check((cu().bkQuantQ8_1Bf16 if bf16 else cu().bkQuantQ8_1)(x, K, B, out))
 

@@ -30,6 +30,7 @@ BK_ERR_COMM = 10005
 BK_PRO_Q8, BK_PRO_BF16, BK_PRO_RMSNORM, BK_PRO_STAGED = 0, 1, 2, 3
 BK_Q8_BLOCKS, BK_Q8_STAGED = 0, 1
 BK_EPI_F32, BK_EPI_BF16, BK_EPI_ADD_BF16, BK_EPI_SWIGLU = 0, 1, 2, 3
+BK_DTYPE_F32, BK_DTYPE_BF16 = 0, 1
 
 BK_OP_EMBED, BK_OP_RMSNORM, BK_OP_GEMV, BK_OP_SWIGLU, BK_OP_CONV1D, BK_OP_ARGMAX, BK_OP_QUANT_Q8_1 = range(1, 8)
 BK_OP_HEADNORM_ROPE, BK_OP_GDN, BK_OP_ATTN, BK_OP_QUANT_Q8_1_BF16 = 8, 9, 10, 11
@@ -110,6 +111,7 @@ SIGNATURES = {
     "bkGemvQ4KSimple": (_I32, [_U64, _I32, _I32, _U64, _I32, _U64]),
     "bkDequantQ4K": (_I32, [_U64, _I32, _I32, _U64]),
     "bkBlockDotsQ4K": (_I32, [_U64, _I32, _I32, _U64, _U64, _U64]),
+    "bkQuantizeQ4K": (_I32, [_U64, _I32, C.c_int64, _I32, _U64]),
     "bkQuantQ8_1": (_I32, [_U64, _I32, _I32, _U64]),
     "bkQuantQ8_1Bf16": (_I32, [_U64, _I32, _I32, _U64]),
     "bkEmbedQ4K": (_I32, [_U64, _I32, _U64, _I32, _U64]),

@@ -132,6 +132,15 @@ BK_API int32_t bkDequantQ4K(uint64_t W, int32_t N, int32_t K, uint64_t out_f32);
 /* integer stage alone (bench/bench.ts:24-33 s1/s2): int32 [N][K/32] each, for one Q8_1 row */
 BK_API int32_t bkBlockDotsQ4K(uint64_t W, int32_t N, int32_t K, uint64_t xq, uint64_t isum, uint64_t qsum);
 
+/* Weight loader's quantiser (no counterpart in the reference, which uploads its safetensors weights as bf16 --
+ * loadWeights, prototypes/decode.ts:64-76 -- and keeps them bf16): rows of f32 or bf16 [n_rows][K] -> Q4_K rows
+ * [n_rows][K/256][144].  Per 32-weight sub-block lo = min(min x, 0), scale = (max x - lo)/15, min = -lo; per superblock
+ * d = f16(max scale/63), dmin = f16(max min/63); 6-bit sc = round(scale/d), m = round(min/dmin);
+ * q = clamp(round((x + dmin*m)/(d*sc)), 0, 15). */
+#define BK_DTYPE_F32 0
+#define BK_DTYPE_BF16 1
+BK_API int32_t bkQuantizeQ4K(uint64_t x, int32_t dtype, int64_t n_rows, int32_t K, uint64_t out_q4k);
+
 /* packQ8_1 (bench/bench.ts:53-72) on the device: f32 or bf16 [B][K] -> blocks [B][K/32][36] */
 BK_API int32_t bkQuantQ8_1(uint64_t x_f32, int32_t K, int32_t B, uint64_t out_blocks);
 BK_API int32_t bkQuantQ8_1Bf16(uint64_t x_bf16, int32_t K, int32_t B, uint64_t out_blocks);

@@ -267,6 +267,95 @@ ORC_API void orc_q4k_dequant_row(const uint8_t* row, int K, float* out) {
   }
 }
 
+
+/* ------------------------------------------------------------------------ */
+/* f32 -> Q4_K quantiser (the weight side of the loader)                      */
+/* ------------------------------------------------------------------------ */
+/* The reference loads bf16 safetensors weights and never quantises them (prototypes/decode.ts:64-76); the Q4_K model
+ * of this build needs a quantiser, restated here from the published description of the format, not from any
+ * implementation: per 32-weight sub-block  lo = min(min x, 0), scale = (max x - lo)/15, mn = -lo;  per 256-weight
+ * superblock  d = f16(max scale / 63), dmin = f16(max mn / 63) (round to nearest even), sc = round(scale/d),
+ * m = round(mn/dmin) (6 bits each, half up);  q = clamp(round((x + dmin*m) / (d*sc)), 0, 15).  Every operation is a
+ * single rounded f32 operation in the order written, so the CUDA quantiser gives the same bytes. */
+static uint16_t f32_to_f16_rne(float v) {
+  uint32_t x = f2u(v);
+  uint32_t sign = (x >> 16) & 0x8000u;
+  uint32_t e = (x >> 23) & 0xffu, m = x & 0x7fffffu;
+  if (e == 0xffu) return (uint16_t)(sign | 0x7c00u | (m ? 0x200u : 0u));
+  int ne = (int)e - 127 + 15;
+  if (ne >= 31) return (uint16_t)(sign | 0x7c00u);
+  if (ne <= 0) {
+    if (ne < -10) return (uint16_t)sign;
+    m |= 0x800000u;
+    int shift = 14 - ne;                       /* 14..24 */
+    uint32_t h = m >> shift;
+    uint32_t rem = m & ((1u << shift) - 1u), half = 1u << (shift - 1);
+    if (rem > half || (rem == half && (h & 1u))) h++;
+    return (uint16_t)(sign | h);
+  }
+  uint32_t h = ((uint32_t)ne << 10) | (m >> 13);
+  uint32_t rem = m & 0x1fffu;
+  if (rem > 0x1000u || (rem == 0x1000u && (h & 1u))) h++;   /* a carry into the exponent is the right result */
+  return (uint16_t)(sign | h);
+}
+
+ORC_API uint16_t orc_f32_to_f16_rne(float v) { return f32_to_f16_rne(v); }
+
+ORC_API void orc_q4k_quantize_row(const float* x, int K, uint8_t* out) {
+  int nsb = K / 256;
+  for (int s = 0; s < nsb; s++) {
+    const float* xs = x + (size_t)s * 256;
+    uint8_t* sb = out + (size_t)s * 144;
+    float scale[8], mn[8], max_scale = 0.0f, max_min = 0.0f;
+    for (int j = 0; j < 8; j++) {
+      float lo = xs[j * 32], hi = xs[j * 32];
+      for (int i = 1; i < 32; i++) {
+        float v = xs[j * 32 + i];
+        if (v < lo) lo = v;
+        if (v > hi) hi = v;
+      }
+      if (lo > 0.0f) lo = 0.0f;
+      scale[j] = (hi - lo) / 15.0f;
+      if (!(scale[j] > 0.0f)) scale[j] = 0.0f;
+      mn[j] = -lo;
+      if (scale[j] > max_scale) max_scale = scale[j];
+      if (mn[j] > max_min) max_min = mn[j];
+    }
+    uint16_t dh = f32_to_f16_rne(max_scale / 63.0f), mh = f32_to_f16_rne(max_min / 63.0f);
+    float d = orc_f16_to_f32(dh), dm = orc_f16_to_f32(mh);
+    float inv_d = d > 0.0f ? 1.0f / d : 0.0f, inv_dm = dm > 0.0f ? 1.0f / dm : 0.0f;
+    uint8_t sc6[8], m6[8];
+    for (int j = 0; j < 8; j++) {
+      int a = (int)floorf(scale[j] * inv_d + 0.5f), b = (int)floorf(mn[j] * inv_dm + 0.5f);
+      sc6[j] = (uint8_t)(a > 63 ? 63 : a);
+      m6[j] = (uint8_t)(b > 63 ? 63 : b);
+    }
+    sb[0] = (uint8_t)(dh & 0xff); sb[1] = (uint8_t)(dh >> 8);
+    sb[2] = (uint8_t)(mh & 0xff); sb[3] = (uint8_t)(mh >> 8);
+    for (int j = 0; j < 4; j++) {
+      sb[4 + j] = (uint8_t)(sc6[j] | ((sc6[j + 4] >> 4) << 6));
+      sb[8 + j] = (uint8_t)(m6[j] | ((m6[j + 4] >> 4) << 6));
+      sb[12 + j] = (uint8_t)((sc6[j + 4] & 0x0f) | ((m6[j + 4] & 0x0f) << 4));
+    }
+    for (int p = 0; p < 4; p++) {
+      float dl0 = d * (float)sc6[2 * p], ml0 = dm * (float)m6[2 * p];
+      float dl1 = d * (float)sc6[2 * p + 1], ml1 = dm * (float)m6[2 * p + 1];
+      for (int i = 0; i < 32; i++) {
+        int q0 = 0, q1 = 0;
+        if (dl0 > 0.0f) {
+          q0 = (int)floorf((xs[p * 64 + i] + ml0) / dl0 + 0.5f);
+          q0 = q0 < 0 ? 0 : (q0 > 15 ? 15 : q0);
+        }
+        if (dl1 > 0.0f) {
+          q1 = (int)floorf((xs[p * 64 + 32 + i] + ml1) / dl1 + 0.5f);
+          q1 = q1 < 0 ? 0 : (q1 > 15 ? 15 : q1);
+        }
+        sb[16 + p * 32 + i] = (uint8_t)(q0 | (q1 << 4));
+      }
+    }
+  }
+}
+
 /* Embedding gather from the tied Q4_K table: X = bf16(dequant(E[id,:]))
  * (reference gathers a bf16 row, src/emitters.ts:31-45). */
 ORC_API void orc_embed_q4k(const uint8_t* table, int H, const int32_t* ids, int B, uint16_t* x) {

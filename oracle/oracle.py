@@ -119,6 +119,17 @@ def q4k_dequant(W: np.ndarray, N: int, K: int) -> np.ndarray:
     return out
 
 
+def q4k_quantize(x: np.ndarray) -> np.ndarray:
+    """f32 [N, K] -> Q4_K rows uint8 [N, K/256*144] (the loader's quantiser; see orc_q4k_quantize_row)."""
+    x = _c(x, np.float32)
+    N, K = x.shape
+    assert K % 256 == 0
+    out = np.empty((N, q4k_row_bytes(K)), np.uint8)
+    for n in range(N):
+        lib().orc_q4k_quantize_row(_p(x[n]), K, _p(out[n]))
+    return out
+
+
 def embed_q4k(table: np.ndarray, H: int, ids) -> np.ndarray:
     ids = _c(ids, np.int32)
     x = np.empty((len(ids), H), np.uint16)
