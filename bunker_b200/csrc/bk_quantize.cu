@@ -3,7 +3,7 @@
 // bunker uploads its safetensors weights as they are, bf16 (loadWeights, prototypes/decode.ts:64-76); the Q4_K model
 // served here needs them quantised once at load time.  One warp per 256-weight superblock, lane l holding weights
 // [8l, 8l+8) (a quarter of sub-block l/4).  The arithmetic is the CPU checker's, operation for operation:
-//   sub-block:  lo = min(min x, 0), scale = (max x - lo) / 15, mn = -lo
+//   sub-block:  lo = min(min x, 0), scale = (max x - lo) / 15, mn = 0 - lo
 //   superblock: d = f16_rn(max scale / 63), dmin = f16_rn(max mn / 63), sc = floor(scale * (1/d) + 0.5) (<= 63),
 //               m = floor(mn * (1/dmin) + 0.5) (<= 63)
 //   weight:     q = clamp(floor((x + dmin*m) / (d*sc) + 0.5), 0, 15)
@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(256) quantize_q4k_kernel(const void* x, size_t
   if (lo > 0.0f) lo = 0.0f;
   float scale = __fdiv_rn(__fsub_rn(hi, lo), 15.0f);
   if (!(scale > 0.0f)) scale = 0.0f;
-  const float mn = -lo;
+  const float mn = __fsub_rn(0.0f, lo);   // 0 - lo, not -lo: a zero minimum stays +0 (its sign would reach the f16 dmin)
   float max_scale = scale, max_min = mn;
 #pragma unroll
   for (int off = 4; off <= 16; off <<= 1) {

@@ -317,7 +317,7 @@ ORC_API void orc_q4k_quantize_row(const float* x, int K, uint8_t* out) {
       if (lo > 0.0f) lo = 0.0f;
       scale[j] = (hi - lo) / 15.0f;
       if (!(scale[j] > 0.0f)) scale[j] = 0.0f;
-      mn[j] = -lo;
+      mn[j] = 0.0f - lo;
       if (scale[j] > max_scale) max_scale = scale[j];
       if (mn[j] > max_min) max_min = mn[j];
     }
