@@ -21,6 +21,7 @@ namespace {
 constexpr int kW = 8;        // warps per split CTA
 constexpr int kHD = 256;     // head dim (8 per lane)
 constexpr int kMaxSplits = 1024;
+constexpr int kCh = 4;       // rows of one warp per register chunk (two chunks are live: the one in use and the next)
 
 struct AttnParams {
   const uint16_t* qg;
@@ -172,8 +173,10 @@ __device__ void combine_head_warp(const AttnParams& p, int b, int h, int ns, flo
 // the kernel running just before this one, so (p.settled) the first 8 K rows and 8 V rows of every warp are
 // requested before the dependency wait; longer splits stream further chunks of 8 rows per warp with the next
 // chunk in flight while the current one is reduced.  The CTA that finishes a (batch, KV head) last merges the splits.
+// Two CTAs per SM (at most 128 registers): with one CTA of 8 warps an SM cannot hide the latency of the per-row
+// shuffle reductions and the stream stalls.
 template <int G>
-__global__ void __launch_bounds__(kW * 32) attn_split_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kW * 32, 2) attn_split_kernel(const AttnParams p) {
   bk_pdl_trigger();
   bk_stamp(p.trace, 0);
   extern __shared__ __align__(16) uint8_t smem[];
@@ -191,13 +194,13 @@ __global__ void __launch_bounds__(kW * 32) attn_split_kernel(const AttnParams p)
   uint16_t* Vb = p.v_cache + ((size_t)b * p.Hkv + kvh) * (size_t)p.max_len * kHD;
   const int j0 = split * p.split_len;
 
-  // rows of this warp: jj = warp + 8*i; chunk c holds i in [8c, 8c+8)
-  uint4 kc[8], vc[8];
+  // rows of this warp: jj = warp + 8*i; chunk c holds i in [kCh*c, kCh*c + kCh)
+  uint4 kc[kCh], vc[kCh];
   int pos = 0, ns = 0;
-  auto load_chunk = [&](const uint16_t* base, int c, uint4 (&dst)[8], bool skip_pos) {
+  auto load_chunk = [&](const uint16_t* base, int c, uint4 (&dst)[kCh], bool skip_pos) {
 #pragma unroll
-    for (int e = 0; e < 8; e++) {
-      const int jj = warp + 8 * (8 * c + e);
+    for (int e = 0; e < kCh; e++) {
+      const int jj = warp + 8 * (kCh * c + e);
       const bool ok = jj < ns && !(skip_pos && j0 + jj == pos);
       dst[e] = ok ? *reinterpret_cast<const uint4*>(base + (size_t)(j0 + jj) * kHD + lane * 8) : make_uint4(0, 0, 0, 0);
     }
@@ -254,17 +257,17 @@ __global__ void __launch_bounds__(kW * 32) attn_split_kernel(const AttnParams p)
   } else {
     // the row appended above was left out of the early loads
     const int jp = pos - j0;
-    if (jp >= 0 && jp < ns && (jp & 7) == warp && (jp >> 3) < 8) {
+    if (jp >= 0 && jp < ns && (jp & 7) == warp && (jp >> 3) < kCh) {
       const int e = jp >> 3;
 #pragma unroll
-      for (int i = 0; i < 8; i++)
+      for (int i = 0; i < kCh; i++)
         if (i == e) {
           kc[i] = *reinterpret_cast<const uint4*>(Kb + (size_t)pos * kHD + lane * 8);
           vc[i] = *reinterpret_cast<const uint4*>(Vb + (size_t)pos * kHD + lane * 8);
         }
     }
   }
-  const int nchunks = (ns + 63) / 64;
+  const int nchunks = (ns + 8 * kCh - 1) / (8 * kCh);
 
   // ---- phase 1: scores ----
   {
@@ -273,11 +276,11 @@ __global__ void __launch_bounds__(kW * 32) attn_split_kernel(const AttnParams p)
     for (int g = 0; g < G; g++) bf16x8_to_f32(*reinterpret_cast<const uint4*>(q_st + g * kHD + lane * 8), qf[g]);
     const int hsel = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
     for (int c = 0; c < nchunks; c++) {
-      uint4 kn[8];
+      uint4 kn[kCh];
       if (c + 1 < nchunks) load_chunk(Kb, c + 1, kn, false);
 #pragma unroll
-      for (int e = 0; e < 8; e++) {
-        const int jj = warp + 8 * (8 * c + e);
+      for (int e = 0; e < kCh; e++) {
+        const int jj = warp + 8 * (kCh * c + e);
         if (jj < ns) {   // warp-uniform
           float kf[8], pa[8];
           bf16x8_to_f32(kc[e], kf);
@@ -296,7 +299,7 @@ __global__ void __launch_bounds__(kW * 32) attn_split_kernel(const AttnParams p)
       }
       if (c + 1 < nchunks) {
 #pragma unroll
-        for (int e = 0; e < 8; e++) kc[e] = kn[e];
+        for (int e = 0; e < kCh; e++) kc[e] = kn[e];
       }
     }
   }
@@ -337,11 +340,11 @@ __global__ void __launch_bounds__(kW * 32) attn_split_kernel(const AttnParams p)
       for (int e = 0; e < 8; e++) acc[g][e] = 0.0f;
     }
     for (int c = 0; c < nchunks; c++) {
-      uint4 vn[8];
+      uint4 vn[kCh];
       if (c + 1 < nchunks) load_chunk(Vb, c + 1, vn, false);
 #pragma unroll
-      for (int e = 0; e < 8; e++) {
-        const int jj = warp + 8 * (8 * c + e);
+      for (int e = 0; e < kCh; e++) {
+        const int jj = warp + 8 * (kCh * c + e);
         if (jj < ns) {
           float vf[8];
           bf16x8_to_f32(vc[e], vf);
@@ -358,7 +361,7 @@ __global__ void __launch_bounds__(kW * 32) attn_split_kernel(const AttnParams p)
       }
       if (c + 1 < nchunks) {
 #pragma unroll
-        for (int e = 0; e < 8; e++) vc[e] = vn[e];
+        for (int e = 0; e < kCh; e++) vc[e] = vn[e];
       }
     }
 #pragma unroll

@@ -337,35 +337,6 @@ __device__ __forceinline__ VRow decode_vrow(const GemvParams& p, int v) {
   return r;
 }
 
-// ---- mbarrier + bulk async copy (global -> this CTA's shared memory, no multicast) ----
-BK_DEVINL uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-BK_DEVINL void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-BK_DEVINL void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-BK_DEVINL void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
-BK_DEVINL bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// bounded: a copy that never lands sets the status word instead of hanging the GPU
-BK_DEVINL void mbar_wait_bounded(uint32_t bar, uint32_t parity, int* status) {
-  for (int it = 0; it < (1 << 22); it++)
-    if (mbar_try_wait(bar, parity)) return;
-  if (status) atomicExch(status, BK_ERR_TIMEOUT);
-}
-
 // CG: the residual was written by another CTA earlier in the same launch (persistent step kernel): read it past L1.
 template <bool TP = true, bool CG = false>
 __device__ __forceinline__ void store_epilogue(const GemvParams& p, const SegDev& sg, size_t o, float y, float yup) {

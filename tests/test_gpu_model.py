@@ -285,3 +285,24 @@ def test_persistent_step_equals_per_op_step_and_oracle(bk, interval, n_layers):
     om = OracleModel(cfg, w, batch=1, split_len=outs[2][3]["split_len"], attn_warps=outs[2][3]["attn_warps"])
     want = om.generate(prompt, 40)
     assert np.array_equal(outs[2][0], want)
+
+
+def test_graph_front_end_decodes_like_the_step_graph(bk):
+    """A runner.ts-style caller: build the declarative graph, take the static partition, resolve weights and
+    double-buffered state through callbacks, rotate the state after every token.  Tokens must equal DecodeModel's and
+    the oracle's."""
+    from bunker_b200 import graph as G
+    cfg = M.CONFIG_TINY.with_(max_len=64)
+    w = M.synth_weights(cfg, seed=12)
+    prompt = np.random.default_rng(4).integers(0, cfg.vocab, (5, 1)).astype(np.int32)
+    g = G.buildModelGraph(cfg)
+    comp = G.compileStep(g, G.choosePartition(g))
+    store = G.StateStore(g, cfg, w)
+    runner = G.GraphRunner(comp, cfg, store.resolve)
+    got = G.runGraphDecode(runner, prompt, 20, store.onToken)
+    gm = M.DecodeModel(cfg, w, batch=1)
+    want = M.runGraphDecode(gm, prompt, 20)
+    assert np.array_equal(got, want)
+    om = OracleModel(cfg, w, batch=1, split_len=runner.split_len, attn_warps=runner.attn_warps)
+    assert np.array_equal(got, om.generate(prompt, 20))
+    gm.destroy()

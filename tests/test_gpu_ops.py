@@ -209,10 +209,9 @@ def _attn_oracle(c, cos_t, sin_t, split_len, W):
 def _run_attn(c, cos_t, sin_t, split_len=0):
     B, Hq, Hkv, HD, ml = c["B"], c["Hq"], c["Hkv"], c["HD"], c["max_len"]
     max_pos = int(c["pos"].max())
+    plan_len, W = ops.attn_plan(max_pos + 1, B, Hkv)   # W: row classes (warps per split) of the library's kernel
     if split_len == 0:
-        split_len, W = ops.attn_plan(max_pos + 1, B, Hkv)
-    else:
-        W = 8
+        split_len = plan_len
     d = {k: dev(v) for k, v in c.items() if isinstance(v, np.ndarray)}
     dc, ds = dev(cos_t), dev(sin_t)
     scratch = R.DeviceBuffer.zeros(ops.attn_scratch_bytes(B, Hq, HD, ml, split_len))

@@ -119,3 +119,28 @@ def test_staged_image_layout_round_trip():
     assert np.array_equal(q2.reshape(B, K // 32, 32), q)
     assert np.array_equal(d2.view(np.uint32), d8.view(np.uint32))
     assert np.array_equal(s2.view(np.uint32), s8.astype(np.float32).view(np.uint32))
+
+
+def test_graph_front_end_partitions_onto_fused_kernels():
+    """The declarative step graph (src/model.ts shape) falls into exactly the launches of the per-op step: embed, five
+    per layer, lm_head, argmax; a graph with a node outside the fused groups is refused by node."""
+    from bunker_b200 import graph as G
+    cfg = M.CONFIG_HYBRID_24L
+    g = G.buildModelGraph(cfg)
+    assert len(g.nodes) == 1 + 18 * 17 + 6 * 19 + 3        # embed + GDN layers + attention layers + final norm, lm_head, argmax
+    part = G.choosePartition(g)
+    assert len(part) == 1 + 24 * 5 + 2
+    comp = G.compileStep(g, part)
+    kinds = [k.kind for k in comp.schedule]
+    assert kinds[:6] == ["embed", "norm_gemv", "gdn", "gemv_add", "norm_gemv_swiglu", "gemv_add"]
+    assert kinds[16:21] == ["norm_gemv", "attn", "gemv_add", "norm_gemv_swiglu", "gemv_add"]
+    assert kinds[-2:] == ["norm_gemv", "argmax"]
+    assert [len(k.group) for k in comp.schedule[1:6]] == [5, 2, 3, 4, 3]
+    ext = set(g.externals())
+    assert {"token_id", "pos", "embed.weight", "lm_head.weight", "model.layers.0.conv_state_in", "model.layers.3.kv_k_in",
+            "rope_cos"} <= ext
+    bad = G.Graph()
+    x = bad.input("x", G.TensorType((1, 64), "f32"))
+    bad.node("swiglu", [("g", x), ("u", x)], [("out", G.TensorType((1, 64), "bf16"))])
+    with pytest.raises(ValueError, match="swiglu"):
+        G.choosePartition(bad)
