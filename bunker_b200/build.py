@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libbunker_cuda.so")
-SOURCES = ["bk_runtime.cu", "bk_gemv.cu", "bk_gemv_mma.cu", "bk_ops.cu", "bk_attn.cu", "bk_launch.cu", "bk_model.cu", "bk_comm.cu", "bk_persist.cu", "bk_quantize.cu"]
+SOURCES = ["bk_runtime.cu", "bk_gemv.cu", "bk_gemv_mma.cu", "bk_ops.cu", "bk_attn.cu", "bk_launch.cu", "bk_model.cu", "bk_comm.cu", "bk_persist.cu", "bk_quantize.cu", "bk_gemv_umma.cu"]
 HEADERS = ["bk_common.cuh", "bk_internal.h", "bk_gemv_shared.cuh", "bk_gemv_dp4a.cuh", "bk_gdn.cuh",
            os.path.join("..", "..", "include", "bunker_cuda.h"), os.path.join("..", "..", "include", "bunker_cuda_diag.h")]
 

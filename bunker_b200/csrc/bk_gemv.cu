@@ -332,6 +332,8 @@ __global__ void quant_q8_1_kernel(const void* x, int K, int B, uint8_t* out) {
 // ---- host entry points ---------------------------------------------------------
 
 int32_t bk_gemv_mma_launch(void* params, int K, int B, int vrows, bool has_swiglu, int* ctas_out);  // bk_gemv_mma.cu
+int32_t bk_gemv_umma_launch(void* params, int B);                                                   // bk_gemv_umma.cu
+static bool g_umma_group = false;   // the launch being set up is one group of <= 32 columns of the dense tile path
 
 static int g_tune_warps = 0, g_tune_rows = 0, g_tune_depth = 0;
 
@@ -350,17 +352,23 @@ int32_t bk_gemv_launch_tp(const bkGemvArgs& a, const BkPush* push, const BkReduc
   BkContext& c = bk_ctx();
   BK_ARG(a.K > 0 && a.K % 256 == 0, "bkGemvQ4K: K=%d is not a positive multiple of 256", a.K);
   BK_ARG(a.B >= 1 && a.B <= 64, "bkGemvQ4K: B=%d outside 1..64", a.B);
-  if (a.B > 8) {
-    // More than 8 columns: groups of 8 on the tensor-core kernel, one launch per group (the weights of the later
-    // groups come from L2 when they fit there).  A dense tile kernel for batch >= 16 does not exist in this library.
+  // From 16 columns on, ready-made Q8_1 blocks go to the dense tile kernel (tcgen05 int8 MMA, bk_gemv_umma.cu): the
+  // weights are streamed once per 32 columns.  Its f32 order differs from the batch <= 8 kernels' (see there);
+  // order = BK_GEMV_ORDER_LANES keeps the columns on those kernels.
+  const bool tile_path = !g_umma_group && a.B >= 16 && a.prologue == BK_PRO_Q8 && a.order != BK_GEMV_ORDER_LANES && !push &&
+                         !reduce && !g_view;
+  if (a.B > 8 && !g_umma_group) {
+    // More than 8 columns without the tile path: groups of 8 on the mma.sync kernel, one launch per group (the weights
+    // of the later groups come from L2 when they fit there).
     BK_ARG(a.prologue != BK_PRO_REDUCE_RMSNORM, "bkGemvQ4K: the reduce prologue is a batch-1 path");
     if (ctas_out) *ctas_out = 0;
-    for (int b0 = 0; b0 < a.B; b0 += 8) {
+    const int gsz = tile_path ? 32 : 8;
+    for (int b0 = 0; b0 < a.B; b0 += gsz) {
       bkGemvArgs s = a;
-      s.B = a.B - b0 < 8 ? a.B - b0 : 8;
+      s.B = a.B - b0 < gsz ? a.B - b0 : gsz;
       if (a.prologue == BK_PRO_STAGED) s.x = a.x + (uint64_t)(b0 / 8) * bk_staged_group_stride(a.K);
       else s.x = a.x + (uint64_t)b0 * (a.prologue == BK_PRO_Q8 ? (uint64_t)(a.K / 32) * 36 : (uint64_t)a.K * 2);
-      if (s.B == 1 && a.prologue == BK_PRO_STAGED) return bk_fail(BK_ERR_ARG, "bkGemvQ4K: a staged activation cannot end in a group of one column (B=%d)", a.B);
+      if (s.B == 1 && a.prologue == BK_PRO_STAGED && !tile_path) return bk_fail(BK_ERR_ARG, "bkGemvQ4K: a staged activation cannot end in a group of one column (B=%d)", a.B);
       BkPush ps;
       if (push) {
         ps = *push;
@@ -372,7 +380,9 @@ int32_t bk_gemv_launch_tp(const bkGemvArgs& a, const BkPush* push, const BkReduc
         if (a.segs[i].residual) s.segs[i].residual = a.segs[i].residual + (uint64_t)b0 * a.segs[i].ld_out * 2;
       }
       int ctas = 0;
+      g_umma_group = tile_path;
       const int32_t rc = bk_gemv_launch_tp(s, push ? &ps : nullptr, nullptr, &ctas);
+      g_umma_group = false;
       if (rc != BK_OK) return rc;
       if (ctas_out) *ctas_out += ctas;
     }
@@ -381,7 +391,7 @@ int32_t bk_gemv_launch_tp(const bkGemvArgs& a, const BkPush* push, const BkReduc
   BK_ARG(a.n_segs >= 1 && a.n_segs <= 4, "bkGemvQ4K: n_segs=%d outside 1..4", a.n_segs);
   BK_ARG((a.prologue >= BK_PRO_Q8 && a.prologue <= BK_PRO_STAGED) || (a.prologue == BK_PRO_REDUCE_RMSNORM && reduce && reduce->n > 0),
          "bkGemvQ4K: unknown prologue %d", a.prologue);
-  const bool tc_path = a.B >= 2 && bk_gemv_mma_fits(a.K, a.B);
+  const bool tc_path = !g_umma_group && a.B >= 2 && bk_gemv_mma_fits(a.K, a.B);
   BK_ARG(a.prologue != BK_PRO_REDUCE_RMSNORM || !tc_path, "bkGemvQ4K: the reduce prologue exists on the batch-1 kernel only");
   if (a.prologue == BK_PRO_STAGED)
     BK_ARG(a.B >= 2 && bk_gemv_mma_fits(a.K, a.B),
@@ -389,7 +399,7 @@ int32_t bk_gemv_launch_tp(const bkGemvArgs& a, const BkPush* push, const BkReduc
   BK_ARG(a.x != 0 && (a.x & 15) == 0, "bkGemvQ4K: x must be a non-null 16-byte aligned device pointer");
   if (a.prologue == BK_PRO_RMSNORM || a.prologue == BK_PRO_REDUCE_RMSNORM)
     BK_ARG(a.norm_w != 0 && (a.norm_w & 15) == 0, "bkGemvQ4K: norm_w must be non-null and 16-byte aligned");
-  if (a.B >= 2 && !g_view && a.prologue == BK_PRO_Q8 && !bk_gemv_mma_fits(a.K, a.B)) {
+  if (!g_umma_group && a.B >= 2 && !g_view && a.prologue == BK_PRO_Q8 && !bk_gemv_mma_fits(a.K, a.B)) {
     // Rows too wide for the tensor-core path's shared memory (FFN 17408 of the 64-layer configuration): the launch is
     // cut along K into parts of whole 8-superblock groups.  The canonical order adds a row's unit values per class
     // (superblock mod 8) in ascending order, so a part starts from the class accumulators its predecessor left in a
@@ -428,7 +438,7 @@ int32_t bk_gemv_launch_tp(const bkGemvArgs& a, const BkPush* push, const BkReduc
       return BK_OK;
     }
   }
-  if (a.B >= 3 && !g_view && !bk_gemv_mma_fits(a.K, a.B)) {
+  if (!g_umma_group && a.B >= 3 && !g_view && !bk_gemv_mma_fits(a.K, a.B)) {
     // A K this wide (FFN 17408 of the 64-layer configuration) leaves no room for a 16-row tile beside the staged
     // activation of 3..8 columns.  The columns are independent, so the launch is cut into column pairs on the
     // small-batch kernel (same arithmetic, same bits); the weights of the later pairs come mostly from L2.
@@ -514,6 +524,10 @@ int32_t bk_gemv_launch_tp(const bkGemvArgs& a, const BkPush* push, const BkReduc
   p.cta_trace = nullptr;
   if (c.cta_trace && c.cta_trace_seen++ == c.cta_trace_launch) p.cta_trace = c.cta_trace;
 
+  if (g_umma_group) {
+    if (ctas_out) *ctas_out = 0;
+    return bk_gemv_umma_launch(&p, a.B);
+  }
   if (tc_path) return bk_gemv_mma_launch(&p, a.K, a.B, vrows, has_swiglu, ctas_out);
 
   // ---- launch shape ----

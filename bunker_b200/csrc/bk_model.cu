@@ -278,7 +278,10 @@ int32_t enqueue_step(Model& m, int parity, bool host_tokens = false) {
   const bool q8_handoff = B >= 2;
   // the staged layout serves groups of 2..8 columns on the tensor-core kernel; a last group of one column (B = 9, 17, ...)
   // or a K too wide for that kernel reads plain blocks instead
-  auto staged_ok = [&](int K) { return bk_gemv_mma_fits(K, B < 8 ? B : 8) && !(B > 8 && B % 8 == 1); };
+  // from 16 sequences on (one GPU) every projection runs on the dense tile kernel, which reads plain blocks
+  const bool tile_path = B >= 16 && m.tp == 1;
+  const int gemv_order = tile_path ? BK_GEMV_ORDER_AUTO : BK_GEMV_ORDER_LANES;
+  auto staged_ok = [&](int K) { return !tile_path && bk_gemv_mma_fits(K, B < 8 ? B : 8) && !(B > 8 && B % 8 == 1); };
   // Input of a projection: fused RMSNorm/quantise prologue at batch 1; at batch >= 2 one small launch
   // normalises and quantises the rows once and every CTA of the projection just copies the blocks.
   // Tensor parallel: a row-parallel GEMV pushes its partial sums to every rank (BK_EPI_PUSH_F32); the sum over ranks,
@@ -288,7 +291,7 @@ int32_t enqueue_step(Model& m, int parity, bool host_tokens = false) {
   BkReduce red_desc;
   bool use_red = false;   // the GEMV being set up carries the reduce prologue (batch 1)
   auto set_input = [&](bkGemvArgs& g, uint64_t x, int K, uint64_t norm_w) -> int32_t {
-    g.K = K; g.B = B; g.eps = c.eps;
+    g.K = K; g.B = B; g.eps = c.eps; g.order = gemv_order;
     use_red = false;
     const bool reduce = pending.on && norm_w && x == pending.out;
     if (reduce) {
@@ -350,7 +353,7 @@ int32_t enqueue_step(Model& m, int parity, bool host_tokens = false) {
       ga.state_is_settled = 1;  // this layer's state was last written one whole step ago
       PROF(PC_GDN, bkGdnStep(&ga));
       memset(&g, 0, sizeof(g));
-      g.K = m.ZD; g.B = B; g.n_segs = 1;
+      g.K = m.ZD; g.B = B; g.n_segs = 1; g.order = gemv_order;
       g.prologue = zd_staged ? BK_PRO_STAGED : q8_handoff ? BK_PRO_Q8 : BK_PRO_BF16; g.x = q8_handoff ? m.attn_q8 : m.attn_out;
       if (m.tp == 1) {
         g.segs[0] = bkGemvSeg{L.out_proj, 0, m.h1, m.x[cur], H, BK_EPI_ADD_BF16, H, 0};
@@ -370,7 +373,7 @@ int32_t enqueue_step(Model& m, int parity, bool host_tokens = false) {
       bkAttnArgs aa = step_attn_args(m, L, q8_handoff, o_staged);
       PROF(PC_ATTN, bkAttnDecode(&aa));
       memset(&g, 0, sizeof(g));
-      g.K = m.Hq * c.head_dim; g.B = B; g.n_segs = 1;
+      g.K = m.Hq * c.head_dim; g.B = B; g.n_segs = 1; g.order = gemv_order;
       g.prologue = o_staged ? BK_PRO_STAGED : q8_handoff ? BK_PRO_Q8 : BK_PRO_BF16; g.x = q8_handoff ? m.attn_q8 : m.attn_out;
       if (m.tp == 1) {
         g.segs[0] = bkGemvSeg{L.o, 0, m.h1, m.x[cur], H, BK_EPI_ADD_BF16, H, 0};
@@ -463,6 +466,7 @@ int32_t enqueue_prefill(Model& m, int T) {
   // quantise `cols` rows once (optionally RMSNorm first) and point the GEMV at the result
   auto set_input = [&](bkGemvArgs& g, uint64_t x, int K, uint64_t norm_w, int cols) -> int32_t {
     g.K = K; g.B = cols; g.eps = c.eps;
+    g.order = BK_GEMV_ORDER_LANES;   // every column must get the bits of a single decode step
     if (cols == 1) {
       g.prologue = norm_w ? BK_PRO_RMSNORM : BK_PRO_BF16; g.x = x; g.norm_w = norm_w;
       return BK_OK;

@@ -31,6 +31,7 @@ BK_PRO_Q8, BK_PRO_BF16, BK_PRO_RMSNORM, BK_PRO_STAGED = 0, 1, 2, 3
 BK_Q8_BLOCKS, BK_Q8_STAGED = 0, 1
 BK_EPI_F32, BK_EPI_BF16, BK_EPI_ADD_BF16, BK_EPI_SWIGLU = 0, 1, 2, 3
 BK_DTYPE_F32, BK_DTYPE_BF16 = 0, 1
+BK_GEMV_ORDER_AUTO, BK_GEMV_ORDER_LANES = 0, 1
 
 BK_OP_EMBED, BK_OP_RMSNORM, BK_OP_GEMV, BK_OP_SWIGLU, BK_OP_CONV1D, BK_OP_ARGMAX, BK_OP_QUANT_Q8_1 = range(1, 8)
 BK_OP_HEADNORM_ROPE, BK_OP_GDN, BK_OP_ATTN, BK_OP_QUANT_Q8_1_BF16 = 8, 9, 10, 11
@@ -49,7 +50,7 @@ class bkGemvSeg(C.Structure):
 
 class bkGemvArgs(C.Structure):
     _fields_ = [("K", C.c_int32), ("B", C.c_int32), ("n_segs", C.c_int32), ("prologue", C.c_int32),
-                ("x", C.c_uint64), ("norm_w", C.c_uint64), ("eps", C.c_float), ("reserved", C.c_int32),
+                ("x", C.c_uint64), ("norm_w", C.c_uint64), ("eps", C.c_float), ("order", C.c_int32),
                 ("segs", bkGemvSeg * 4)]
 
 

@@ -100,6 +100,14 @@ BK_API int32_t bkLaunchCount(uint64_t* out_count);
 #define BK_Q8_STAGED 1
 BK_API uint64_t bkStagedBytes(int32_t K, int32_t B);
 
+/* f32 accumulation order of a row's result (the integer block dots are exact either way).  LANES: the order of the
+ * batch <= 8 kernels (64-weight units over 32 lanes, butterfly).  AUTO: LANES up to 15 columns; from 16 columns on,
+ * with BK_PRO_Q8 input, the dense tile kernel (tcgen05 int8 MMA, accumulators in tensor memory) and its order: one
+ * chain per (row, column), sub-blocks then superblocks ascending.  Both are within a few ulp of each other and of the
+ * reference's f32 accumulation (prototypes/decode.ts:141-145). */
+#define BK_GEMV_ORDER_AUTO 0
+#define BK_GEMV_ORDER_LANES 1
+
 typedef struct bkGemvSeg {
   uint64_t W;        /* Q4_K rows [n_rows][K/256][144] */
   uint64_t W2;       /* BK_EPI_SWIGLU: the up_proj rows, else 0 */
@@ -113,13 +121,13 @@ typedef struct bkGemvSeg {
 
 typedef struct bkGemvArgs {
   int32_t K;         /* multiple of 256 */
-  int32_t B;         /* 1..8 */
+  int32_t B;         /* 1..64 */
   int32_t n_segs;    /* 1..4 row segments that share the activation (qkv|z|a|b, gate|up, ...) */
   int32_t prologue;
   uint64_t x;
   uint64_t norm_w;   /* bf16 [K], BK_PRO_RMSNORM only */
   float eps;
-  int32_t reserved;
+  int32_t order;     /* BK_GEMV_ORDER_AUTO or BK_GEMV_ORDER_LANES */
   bkGemvSeg segs[4];
 } bkGemvArgs;
 

@@ -501,6 +501,50 @@ ORC_API void orc_gemv_q4k_q8(const uint8_t* W, int N, int K, const uint8_t* xq, 
     for (int b = 0; b < B; b++) y[(size_t)b * N + n] = gemv_row_canonical(W + rowb * n, xq + xb * b, K);
 }
 
+
+/* The order of the dense tile path (batch >= 16, tensor-core integer dots): per (row, column) one chain.  Inside a
+ * superblock the eight sub-blocks in ascending order, accd = fma(d8_j, f32(sc_j*isum_j), accd) and
+ * accm = fma(s8_j, f32(m_j), accm) from zero; then val = fma(d, accd, -(dmin*accm)) and y = y + val over the
+ * superblocks in ascending order.  Integer sums are exact either way; only this f32 order differs from the
+ * lane / butterfly order above (by a few ulp). */
+static float gemv_row_tile(const uint8_t* wrow, const uint8_t* xq, int K) {
+  float y = 0.0f;
+  int nsb = K / 256;
+  for (int s = 0; s < nsb; s++) {
+    const uint8_t* sb = wrow + (size_t)s * 144;
+    float d = orc_f16_to_f32(rd16(sb)), dmin = orc_f16_to_f32(rd16(sb + 2));
+    uint8_t sc[8], mn[8];
+    orc_q4k_scales(sb, sc, mn);
+    float accd = 0.0f, accm = 0.0f;
+    for (int j = 0; j < 8; j++) {
+      const uint8_t* qs = sb + 16 + (j >> 1) * 32;
+      const uint8_t* xb = xq + (size_t)(s * 8 + j) * 36;
+      const int8_t* x8 = (const int8_t*)xb;
+      int32_t isum = 0, qsum = 0;
+      for (int i = 0; i < 32; i++) {
+        int q4 = (j & 1) ? (qs[i] >> 4) : (qs[i] & 15);
+        isum += q4 * x8[i];
+        qsum += x8[i];
+      }
+      float d8 = orc_q8half_to_f32(rd16(xb + 32));
+      float s8 = d8 * (float)qsum;
+      accd = fmaf(d8, (float)((int32_t)sc[j] * isum), accd);
+      accm = fmaf(s8, (float)mn[j], accm);
+    }
+    float t = dmin * accm;
+    float val = fmaf(d, accd, -t);
+    y = y + val;
+  }
+  return y;
+}
+
+ORC_API void orc_gemv_q4k_q8_tile(const uint8_t* W, int N, int K, const uint8_t* xq, int B, float* y) {
+  size_t rowb = (size_t)(K / 256) * 144, xb = (size_t)(K / 32) * 36;
+#pragma omp parallel for schedule(static)
+  for (int n = 0; n < N; n++)
+    for (int b = 0; b < B; b++) y[(size_t)b * N + n] = gemv_row_tile(W + rowb * n, xq + xb * b, K);
+}
+
 /* Plain restatement: dequantise both sides and accumulate in double, the way
  * the reference's host loops run on JS numbers (bench/bench.ts:18-35). */
 ORC_API void orc_gemv_q4k_q8_plain(const uint8_t* W, int N, int K, const uint8_t* xq, int B, double* y) {

@@ -12,8 +12,12 @@ from . import oracle as O
 
 
 class OracleModel:
-    def __init__(self, cfg, weights: dict, batch: int, split_len: int, attn_warps: int = 8, tp: int = 1):
+    def __init__(self, cfg, weights: dict, batch: int, split_len: int, attn_warps: int = 8, tp: int = 1,
+                 gemv_order: str | None = None):
+        """gemv_order: "lanes" (the batch <= 8 kernels: units over lanes, butterfly) or "tile" (the dense tile path);
+        None picks what the library picks for this batch (tile from 16 sequences on, on one GPU)."""
         self.cfg, self.w, self.B, self.split_len, self.W, self.tp = cfg, weights, batch, split_len, attn_warps, tp
+        self.gemv_order = gemv_order or ("tile" if (batch >= 16 and tp == 1) else "lanes")
         self.cos_t, self.sin_t = O.rope_tables(cfg.max_len, cfg.rot_dim, cfg.rope_theta)
         self.reset()
 
@@ -33,7 +37,7 @@ class OracleModel:
                 self.S[li] = np.zeros((B, c.gdn_v_heads, 128, 128), np.float32)
 
     def _gemv(self, name: str, N: int, K: int, xq: np.ndarray) -> np.ndarray:
-        return O.gemv_q4k_q8(self.w[name], N, K, xq)
+        return (O.gemv_q4k_q8_tile if self.gemv_order == "tile" else O.gemv_q4k_q8)(self.w[name], N, K, xq)
 
     def _gemv_rowpar(self, name: str, N: int, K: int, x_bf16: np.ndarray) -> np.ndarray:
         """f32 [B, N]; with tp > 1 the K dimension is cut into tp slices of whole superblocks."""
@@ -47,7 +51,8 @@ class OracleModel:
             n = base + (1 if r < extra else 0)
             Wr = np.ascontiguousarray(W[:, s0:s0 + n]).reshape(N, n * 144)
             xr = np.ascontiguousarray(x_bf16[:, s0 * 256:(s0 + n) * 256])
-            parts.append(O.gemv_q4k_q8(Wr, N, n * 256, O.q8_1_quantize_bf16(xr)))
+            parts.append((O.gemv_q4k_q8_tile if self.gemv_order == "tile" else O.gemv_q4k_q8)(
+                Wr, N, n * 256, O.q8_1_quantize_bf16(xr)))
             s0 += n
         return O.sum_ranks(np.stack(parts))
 

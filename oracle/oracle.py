@@ -196,6 +196,16 @@ def gemv_q4k_q8(W: np.ndarray, N: int, K: int, xq: np.ndarray) -> np.ndarray:
     return y
 
 
+def gemv_q4k_q8_tile(W: np.ndarray, N: int, K: int, xq: np.ndarray) -> np.ndarray:
+    """f32 [B, N] in the order of the dense tile path (batch >= 16): one chain per (row, column), sub-blocks then
+    superblocks ascending."""
+    xq = _c(xq, np.uint8).reshape(-1, K // 32, 36)
+    B = xq.shape[0]
+    y = np.empty((B, N), np.float32)
+    lib().orc_gemv_q4k_q8_tile(_p(_c(W, np.uint8)), N, K, _p(xq), B, _p(y))
+    return y
+
+
 def gemv_q4k_q8_plain(W: np.ndarray, N: int, K: int, xq: np.ndarray) -> np.ndarray:
     xq = _c(xq, np.uint8).reshape(-1, K // 32, 36)
     B = xq.shape[0]

@@ -126,8 +126,10 @@ def test_gemv_more_than_eight_columns(bk, B):
     want = O.gemv_q4k_q8(W, N, K, xq)
     dW, dx, dnw, dxq, dres = dev(W), dev(x), dev(nw), dev(xq), dev(res)
     y = R.DeviceBuffer(B * N * 4)
-    ops.gemv_simple(dW.ptr, N, K, dxq.ptr, B, y.ptr)
-    assert_same_bits(y.download(np.float32, (B, N)), want, "Q8_1 blocks in")
+    ops.gemv_simple(dW.ptr, N, K, dxq.ptr, B, y.ptr)    # from 16 columns on: the dense tile kernel and its order
+    assert_same_bits(y.download(np.float32, (B, N)), O.gemv_q4k_q8_tile(W, N, K, xq) if B >= 16 else want, "Q8_1 blocks in")
+    ops.gemv(dxq.ptr, K, B, [ops.gemv_seg(dW.ptr, N, y.ptr, R.BK_EPI_F32)], order=R.BK_GEMV_ORDER_LANES)
+    assert_same_bits(y.download(np.float32, (B, N)), want, "Q8_1 blocks in, lane order forced")
     o = R.DeviceBuffer(B * N * 2)
     ops.gemv(dx.ptr, K, B, [ops.gemv_seg(dW.ptr, N, o.ptr, R.BK_EPI_ADD_BF16, residual=dres.ptr)], prologue=R.BK_PRO_RMSNORM,
              norm_w=dnw.ptr)
@@ -228,3 +230,42 @@ def test_gemv_linearity_full_size(bk):
     rows = np.random.default_rng(0).choice(N, 64, replace=False)
     want = O.gemv_q4k_q8(W[rows], 64, K, xq)
     assert_same_bits(y1[rows].reshape(1, -1), want, "sampled rows")
+
+
+@pytest.mark.parametrize("B,K,N", [(16, 256, 128), (16, 2048, 131), (17, 2048, 300), (31, 4096, 260), (32, 2048, 1000),
+                                   (33, 2048, 150), (64, 6144, 200), (32, 17408, 140)])
+def test_gemv_dense_tile_path(bk, B, K, N):
+    """16 or more columns of Q8_1 blocks: tcgen05 int8 MMA (one per 32-weight sub-block) with TMEM accumulators.  The
+    integer block dots are exact; the f32 chain per (row, column) is the tile order of the oracle, so results are
+    bit-identical to it -- for plain f32 output, for several segments with different epilogues in one launch, and
+    for the SwiGLU pair."""
+    rng = np.random.default_rng(500 + B + K)
+    W = synth.q4k_weights(rng, N, K)
+    W2 = synth.q4k_weights(rng, N, K)
+    x = rng.normal(0, 1, (B, K)).astype(np.float32)
+    res = synth.normal_bf16(rng, (B, N))
+    xq = O.q8_1_quantize(x)
+    want, want2 = O.gemv_q4k_q8_tile(W, N, K, xq), O.gemv_q4k_q8_tile(W2, N, K, xq)
+    assert rel_err(want, O.gemv_q4k_q8_plain(W, N, K, xq)) < 1e-3
+    dW, dW2, dxq, dres = dev(W), dev(W2), dev(xq), dev(res)
+    y = R.DeviceBuffer(B * N * 4)
+    ops.gemv_simple(dW.ptr, N, K, dxq.ptr, B, y.ptr)
+    assert_same_bits(y.download(np.float32, (B, N)), want, "f32 out")
+    # three segments in one launch: bf16 cast | residual add | f32, written side by side into rows of 3N
+    wide_bf, wide_f = R.DeviceBuffer.zeros(B * 2 * N * 2), R.DeviceBuffer.zeros(B * N * 4)
+    segs = [ops.gemv_seg(dW.ptr, N, wide_bf.ptr, R.BK_EPI_BF16, ld_out=2 * N, col_off=0),
+            ops.gemv_seg(dW2.ptr, N, wide_bf.ptr, R.BK_EPI_ADD_BF16, ld_out=2 * N, col_off=N, residual=0),
+            ops.gemv_seg(dW2.ptr, N, wide_f.ptr, R.BK_EPI_F32)]
+    # the residual of segment 1 is indexed like its output: a [B][2N] buffer whose right half holds `res`
+    res_wide = np.zeros((B, 2 * N), np.uint16)
+    res_wide[:, N:] = res
+    dres_w = dev(res_wide)
+    segs[1].residual = dres_w.ptr
+    ops.gemv(dxq.ptr, K, B, segs)
+    got = wide_bf.download(np.uint16, (B, 2 * N))
+    assert_same_bits(got[:, :N], O.epilogue_cast(want), "bf16 segment")
+    assert_same_bits(got[:, N:], O.epilogue_add(want2, res), "residual segment")
+    assert_same_bits(wide_f.download(np.float32, (B, N)), want2, "f32 segment")
+    act = R.DeviceBuffer(B * N * 2)
+    ops.gemv(dxq.ptr, K, B, [ops.gemv_seg(dW.ptr, N, act.ptr, R.BK_EPI_SWIGLU, W2=dW2.ptr)])
+    assert_same_bits(act.download(np.uint16, (B, N)), O.swiglu(want, want2), "SwiGLU pair")
