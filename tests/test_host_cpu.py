@@ -144,3 +144,16 @@ def test_graph_front_end_partitions_onto_fused_kernels():
     bad.node("swiglu", [("g", x), ("u", x)], [("out", G.TensorType((1, 64), "bf16"))])
     with pytest.raises(ValueError, match="swiglu"):
         G.choosePartition(bad)
+
+
+def test_typescript_binding_lists_every_export():
+    """bunker_b200/ts/bunker_cuda.ts is the bun:ffi side of the boundary (it cannot run here: no bun).  Its symbol
+    table must name exactly the exports the headers declare, with pointer-sized handles as u64, never `ptr`."""
+    ts = open(os.path.join(ROOT, "bunker_b200", "ts", "bunker_cuda.ts")).read()
+    table = ts[ts.index("const SYMBOLS = {"):ts.index("} as const;")]
+    bound = dict(re.findall(r"^\s+(bk\w+): \{ args: \[([^\]]*)\]", table, flags=re.M))
+    assert sorted(bound) == header_symbols()
+    assert bound["bkAlloc"] == '"u64", "ptr"' and bound["bkFree"] == '"u64"' and bound["bkModelFinalize"] == '"u64"'
+    for name in ("cuAlloc", "cuHtoD", "cuDtoH", "cuFree", "cuSync", "cuHtoDAsync", "cuDtoHAsync", "cuLaunch", "loadOp",
+                 "LoadedKernel", "profGpuReport", "runGraphDecode"):
+        assert re.search(rf"export (function|interface|class) {name}\b", ts), name
