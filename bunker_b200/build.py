@@ -13,7 +13,9 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libbunker_cuda.so")
-SOURCES = ["bk_runtime.cu", "bk_gemv.cu", "bk_gemv_mma.cu", "bk_ops.cu", "bk_attn.cu", "bk_launch.cu", "bk_model.cu", "bk_comm.cu", "bk_persist.cu", "bk_quantize.cu", "bk_gemv_umma.cu"]
+TOK_LIB = os.path.join(HERE, "libbunker_tok.so")
+TOK_SRC = os.path.join(CSRC, "bk_tokenizer.cpp")
+SOURCES = ["bk_runtime.cu", "bk_gemv.cu", "bk_gemv_mma.cu", "bk_ops.cu", "bk_attn.cu", "bk_launch.cu", "bk_model.cu", "bk_comm.cu", "bk_persist.cu", "bk_quantize.cu", "bk_gemv_umma.cu", "bk_sample.cu"]
 HEADERS = ["bk_common.cuh", "bk_internal.h", "bk_gemv_shared.cuh", "bk_gemv_dp4a.cuh", "bk_gdn.cuh",
            os.path.join("..", "..", "include", "bunker_cuda.h"), os.path.join("..", "..", "include", "bunker_cuda_diag.h")]
 
@@ -42,7 +44,17 @@ def needs_build() -> bool:
     return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
 
 
+def build_tokenizer(force: bool = False) -> str:
+    """libbunker_tok.so: plain C++ (g++), no CUDA."""
+    if not force and os.path.exists(TOK_LIB) and os.path.getmtime(TOK_LIB) >= os.path.getmtime(TOK_SRC):
+        return TOK_LIB
+    cxx = os.environ.get("CXX_FOR_BUNKER", "g++")
+    subprocess.check_call([cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-pthread", "-Wall", "-o", TOK_LIB, TOK_SRC])
+    return TOK_LIB
+
+
 def build_library(force: bool = False, verbose: bool = False) -> str:
+    build_tokenizer(force)
     if not force and not needs_build():
         return LIB
     objs = []

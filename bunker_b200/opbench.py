@@ -170,11 +170,28 @@ def run_all(peak_gbs: float, reps: int = 5) -> dict:
 
 
 if __name__ == "__main__":
+    import argparse
     import os
+    ap = argparse.ArgumentParser(description="stand-alone roofline timings of the GEMV, GDN-step and decode-attention kernels")
+    ap.add_argument("--op", default="all", choices=["all", "gemv", "gdn", "attn"])
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--rows", type=int, default=32768, help="attention: cache rows")
+    ap.add_argument("--reps", type=int, default=5, help="timed regions")
+    ap.add_argument("--n", type=int, default=0, help="launches per region (0: the default of the op)")
+    a = ap.parse_args()
     peak = 6650.0
     p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
     if os.path.exists(p):
         peak = float(json.load(open(p))["hbm_gbs"])
     R.cu(0)
-    for k, v in run_all(peak).items():
+    kw = {"reps": a.reps, **({"n": a.n} if a.n else {})}
+    if a.op == "all":
+        res = run_all(peak, reps=a.reps)
+    elif a.op == "gemv":
+        res = {f"gemv_4096x4096_b{a.batch}": bench_gemv_q4k(peak, B=a.batch, **kw)}
+    elif a.op == "gdn":
+        res = {f"gdn_step_b{a.batch}": bench_gdn(peak, a.batch, **kw)}
+    else:
+        res = {f"attn_L{a.rows}_b{a.batch}": bench_attn(peak, a.batch, a.rows, **kw)}
+    for k, v in res.items():
         print(k, json.dumps(v))

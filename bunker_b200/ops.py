@@ -148,3 +148,9 @@ def argmax_static(logits: int, V: int, B: int, idx: int, val: int) -> None:
     """bkArgmax for callers that cannot allocate: the scratch is built into the library (B <= 64).
     Calls share that scratch, so do not let two of them overlap on the GPU."""
     _check(cu().bkArgmaxStatic(logits, V, B, idx, val))
+
+
+def sample(logits: int, V: int, B: int, idx: int, val: int = 0, temperature: float = 1.0, top_k: int = 40, top_p: float = 1.0,
+           seed: int = 0, step_dev: int = 0, step_add: int = 0) -> None:
+    """Temperature / top-k / top-p sampling over f32 logits [B][V] (deterministic; see bkSample)."""
+    _check(cu().bkSample(logits, V, B, temperature, top_k, top_p, seed, step_dev, step_add, idx, val))

@@ -132,6 +132,7 @@ SIGNATURES = {
     "bkArgmax": (_I32, [_U64, _I32, _I32, _U64, _U64, _U64]),
     "bkArgmaxScratchBytes": (_U64, [_I32]),
     "bkArgmaxStatic": (_I32, [_U64, _I32, _I32, _U64, _U64]),
+    "bkSample": (_I32, [_U64, _I32, _I32, _F32, _I32, _F32, _U64, _U64, C.c_uint32, _U64, _U64]),
     "bkLaunch": (_I32, [_I32, _PU64, _I32]),
     "bkCommCreate": (_I32, [_I32, _I32, _U64, _PU64]),
     "bkCommExportHandle": (_I32, [_U64, C.POINTER(C.c_uint8)]),

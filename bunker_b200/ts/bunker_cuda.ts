@@ -67,6 +67,7 @@ const SYMBOLS = {
   bkArgmax: { args: ["u64", "i32", "i32", "u64", "u64", "u64"], returns: "i32" },
   bkArgmaxScratchBytes: { args: ["i32"], returns: "u64" },
   bkArgmaxStatic: { args: ["u64", "i32", "i32", "u64", "u64"], returns: "i32" },
+  bkSample: { args: ["u64", "i32", "i32", "f32", "i32", "f32", "u64", "u64", "u32", "u64", "u64"], returns: "i32" },
   bkModelCreate: { args: ["ptr", "ptr"], returns: "i32" },
   bkModelSetTensor: { args: ["u64", "ptr", "u64", "u64"], returns: "i32" },
   bkModelSetComm: { args: ["u64", "u64"], returns: "i32" },

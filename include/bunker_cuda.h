@@ -249,6 +249,16 @@ BK_API uint64_t bkArgmaxScratchBytes(int32_t B);
  * calls share the array: calls that overlap on the GPU race. */
 BK_API int32_t bkArgmaxStatic(uint64_t logits, int32_t V, int32_t B, uint64_t idx, uint64_t val);
 
+/* Sampling beside the greedy tail (no counterpart in the reference, which only takes the argmax,
+ * prototypes/decode.ts:749-791).  logits f32 [B][V].  Per sequence: the top_k (1..64) largest logits, ties to the lower
+ * index, in descending order; p_i = exp((l_i - l_0)/temperature) summed in that order; the shortest prefix reaching
+ * top_p * total; u in [0,1) from splitmix64(splitmix64(seed ^ (step << 20)) + sequence) >> 40; the first candidate whose
+ * running sum exceeds u * (prefix total).  step = (step_dev ? step_dev[b] : 0) + step_add (step_dev: device int32 [B],
+ * e.g. the model's position buffer, or 0).  temperature 0 or top_k 1 is the argmax.  idx int32 [B]; val f32 [B] (the
+ * chosen logit; 0 to skip).  Deterministic: the same inputs give the same tokens, on any GPU and on the CPU checker. */
+BK_API int32_t bkSample(uint64_t logits, int32_t V, int32_t B, float temperature, int32_t top_k, float top_p, uint64_t seed,
+                        uint64_t step_dev, uint32_t step_add, uint64_t idx, uint64_t val);
+
 /* ---- whole decode step: replaces buildModelGraph + compileStep + runGraphDecode
  *      (src/model.ts:46-204, src/runner.ts:94-162) --------------------------------
  * One call per token; the CUDA graph lives inside the library because replaying a graph

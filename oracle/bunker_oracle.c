@@ -939,6 +939,65 @@ ORC_API void orc_attn_decode_plain(const uint16_t* q, const uint16_t* Kc, const 
   free(s);
 }
 
+
+/* ------------------------------------------------------------------------ */
+/* Sampling (temperature / top-k / top-p)                                     */
+/* ------------------------------------------------------------------------ */
+/* The reference decodes greedily only (prototypes/decode.ts:749-791).  Sampling as the library defines it: the top_k
+ * largest logits (ties to the lower index) in descending order; p_i = exp((l_i - l_0)/T) summed in that order; the
+ * shortest prefix reaching top_p * total; u from splitmix64 of (seed, step, sequence); first i whose running sum
+ * exceeds u * prefix total. */
+static uint64_t splitmix64(uint64_t x) {
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+
+ORC_API void orc_sample(const float* logits, int V, int B, float temperature, int top_k, float top_p, uint64_t seed,
+                        const int32_t* step, uint32_t step_add, int32_t* idx, float* val) {
+  for (int b = 0; b < B; b++) {
+    const float* l = logits + (size_t)b * V;
+    float cv[64];
+    int ci[64];
+    float pv = INFINITY;
+    int pi = -1, k = 0;
+    for (int r = 0; r < top_k && r < 64; r++) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int i = 0; i < V; i++) {
+        float v = l[i];
+        if (v != v) continue;
+        if (!(v < pv || (v == pv && i > pi))) continue;
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+      }
+      if (bi == 0x7fffffff) break;
+      cv[r] = bv; ci[r] = bi; pv = bv; pi = bi; k = r + 1;
+    }
+    if (k == 0) { idx[b] = 0; if (val) val[b] = -INFINITY; continue; }
+    int pick = 0;
+    if (temperature > 0.0f && k > 1) {
+      float pr[64];
+      float inv_t = 1.0f / temperature, total = 0.0f;
+      for (int i = 0; i < k; i++) { pr[i] = orc_expf((cv[i] - cv[0]) * inv_t); total = total + pr[i]; }
+      float need = top_p * total, run = 0.0f;
+      int n = k;
+      for (int i = 0; i < k; i++) { run = run + pr[i]; if (run >= need) { n = i + 1; break; } }
+      float prefix = 0.0f;
+      for (int i = 0; i < n; i++) prefix = prefix + pr[i];
+      uint32_t st = (step ? (uint32_t)step[b] : 0u) + step_add;
+      uint64_t h = splitmix64(splitmix64(seed ^ ((uint64_t)st << 20)) + (uint64_t)b);
+      float u = (float)(uint32_t)(h >> 40) * 5.9604644775390625e-8f;
+      float target = u * prefix;
+      pick = n - 1;
+      run = 0.0f;
+      for (int i = 0; i < n; i++) { run = run + pr[i]; if (run > target) { pick = i; break; } }
+    }
+    idx[b] = ci[pick];
+    if (val) val[b] = cv[pick];
+  }
+}
+
 /* ------------------------------------------------------------------------ */
 /* Argmax                                                                   */
 /* ------------------------------------------------------------------------ */

@@ -346,6 +346,17 @@ def attn_decode_plain(q, Kc, Vc, n: int, HD: int, scale: float) -> np.ndarray:
     return out
 
 
+def sample(logits: np.ndarray, temperature: float, top_k: int, top_p: float, seed: int, step=None, step_add: int = 0):
+    """-> (idx int32 [B], val f32 [B]); step: int32 [B] per-sequence counters or None."""
+    logits = _c(logits, np.float32)
+    B, V = logits.reshape(-1, logits.shape[-1]).shape
+    idx, val = np.empty(B, np.int32), np.empty(B, np.float32)
+    st = None if step is None else _c(step, np.int32)
+    lib().orc_sample(_p(logits), V, B, C.c_float(temperature), top_k, C.c_float(top_p), C.c_uint64(seed),
+                     None if st is None else _p(st), C.c_uint32(step_add), _p(idx), _p(val))
+    return idx, val
+
+
 def argmax(logits: np.ndarray):
     logits = _c(logits, np.float32)
     B, V = logits.reshape(-1, logits.shape[-1]).shape

@@ -418,3 +418,32 @@ def test_exchange_wait_runs_out_and_reports_timeout(bk):
     assert R.cuSync() == 0
     want_sum = O.epilogue_add(O.sum_ranks(parts), res)
     assert_same_bits(dsum.download(np.uint16, (B, K)), want_sum, "sum of the ranks + residual after a timed-out call")
+
+
+def test_sampling_matches_oracle(bk):
+    """Temperature / top-k / top-p sampling: the same token as the CPU checker for every (seed, step, sequence) tried,
+    the argmax at temperature 0 and at top_k 1, ties resolved to the lower index, and a plausible spread of tokens."""
+    B, V = 4, 151936
+    rng = np.random.default_rng(70)
+    logits = rng.normal(0, 2, (B, V)).astype(np.float32)
+    logits[0, 7] = logits[0, 100000] = 9.5          # a tie among the candidates
+    logits[1, :] = -3.0                             # all equal: candidates are indices 0..k-1
+    logits[2, 5] = np.nan                           # NaN is never a candidate
+    dl, idx, val = dev(logits), R.DeviceBuffer(B * 4), R.DeviceBuffer(B * 4)
+    steps = np.array([0, 5, 9, 1000], np.int32)
+    dsteps = dev(steps)
+    seen = set()
+    for seed in range(6):
+        for (T, k, p) in ((1.0, 40, 1.0), (0.7, 64, 0.9), (1.5, 8, 0.5), (0.0, 40, 1.0), (1.0, 1, 1.0)):
+            ops.sample(dl.ptr, V, B, idx.ptr, val.ptr, temperature=T, top_k=k, top_p=p, seed=seed, step_dev=dsteps.ptr, step_add=seed * 3)
+            gi, gv = idx.download(np.int32, (B,)), val.download(np.float32, (B,))
+            wi, wv = O.sample(logits, T, k, p, seed, steps, seed * 3)
+            assert np.array_equal(gi, wi), (seed, T, k, p, gi, wi)
+            assert_same_bits(gv, wv, "sampled logit")
+            if T == 0.0 or k == 1:
+                assert gi[0] == 7 and gi[1] == 0 and gi[3] == int(np.argmax(logits[3]))
+            else:
+                seen.add(int(gi[3]))
+    assert len(seen) > 3
+    with pytest.raises(R.BunkerCudaError):
+        ops.sample(dl.ptr, V, B, idx.ptr, top_k=65)
