@@ -117,12 +117,12 @@ def test_encode_matches_python_bpe_and_round_trips(tok, text):
 
 def test_multithreaded_encode_keeps_text_order(tok):
     t, vocab, merges, added = tok
-    text = CORPUS * 40                       # large enough to be cut into chunks
+    text = CORPUS * 400                      # large enough to be cut into chunks on any core count
     one = t.encode(text)
     many = t.encode(text, threads=True)
-    assert len(one) > 5000 and len(text.encode()) > 40000
+    assert len(one) > 50000
     assert t.decode(many) == text            # chunk boundaries may tokenize a space differently, the text is the same
-    assert abs(len(many) - len(one)) < 64
+    assert abs(len(many) - len(one)) < 512
     # the out_max contract of the reference: never more ids written than the caller's buffer holds
     lib = T.load_library()
     small = (C.c_uint32 * 8)()
