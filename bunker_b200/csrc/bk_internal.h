@@ -102,6 +102,7 @@ struct BkReduce {
 
 // internal launchers shared between translation units
 bool bk_gemv_mma_fits(int K, int B);   // whether the batch-3..8 tensor-core GEMV can hold this K (else column pairs)
+int bk_gemv_tile_min_rows();           // launch rows from which BK_GEMV_ORDER_AUTO takes the dense tile path
 int32_t bk_gemv_launch(const bkGemvArgs& a);
 // same with the fused exchange: push (may be null) for BK_EPI_PUSH_F32 segments, reduce (may be null) for
 // BK_PRO_REDUCE_RMSNORM; ctas_out (may be null) receives the number of CTAs that will signal arrival

@@ -278,10 +278,13 @@ int32_t enqueue_step(Model& m, int parity, bool host_tokens = false) {
   const bool q8_handoff = B >= 2;
   // the staged layout serves groups of 2..8 columns on the tensor-core kernel; a last group of one column (B = 9, 17, ...)
   // or a K too wide for that kernel reads plain blocks instead
-  // from 16 sequences on (one GPU) every projection runs on the dense tile kernel, which reads plain blocks
+  // from 16 sequences on (one GPU) the projections of many rows run on the dense tile kernel, which reads plain blocks
+  // (the library's rule for BK_GEMV_ORDER_AUTO: launch rows >= bk_gemv_tile_min_rows())
   const bool tile_path = B >= 16 && m.tp == 1;
   const int gemv_order = tile_path ? BK_GEMV_ORDER_AUTO : BK_GEMV_ORDER_LANES;
-  auto staged_ok = [&](int K) { return !tile_path && bk_gemv_mma_fits(K, B < 8 ? B : 8) && !(B > 8 && B % 8 == 1); };
+  auto staged_ok = [&](int K, int rows) {
+    return !(tile_path && rows >= bk_gemv_tile_min_rows()) && bk_gemv_mma_fits(K, B < 8 ? B : 8) && !(B > 8 && B % 8 == 1);
+  };
   // Input of a projection: fused RMSNorm/quantise prologue at batch 1; at batch >= 2 one small launch
   // normalises and quantises the rows once and every CTA of the projection just copies the blocks.
   // Tensor parallel: a row-parallel GEMV pushes its partial sums to every rank (BK_EPI_PUSH_F32); the sum over ranks,
@@ -290,7 +293,7 @@ int32_t enqueue_step(Model& m, int parity, bool host_tokens = false) {
   unsigned int n_exchanges = 0;   // fused exchanges enqueued so far in this step
   BkReduce red_desc;
   bool use_red = false;   // the GEMV being set up carries the reduce prologue (batch 1)
-  auto set_input = [&](bkGemvArgs& g, uint64_t x, int K, uint64_t norm_w) -> int32_t {
+  auto set_input = [&](bkGemvArgs& g, uint64_t x, int K, uint64_t norm_w, int rows) -> int32_t {
     g.K = K; g.B = B; g.eps = c.eps; g.order = gemv_order;
     use_red = false;
     const bool reduce = pending.on && norm_w && x == pending.out;
@@ -302,7 +305,7 @@ int32_t enqueue_step(Model& m, int parity, bool host_tokens = false) {
       pending.on = false;
     }
     if (q8_handoff) {
-      const bool staged = staged_ok(K);   // else the GEMV is cut along K (or runs as column pairs) reading plain blocks
+      const bool staged = staged_ok(K, rows);   // else the GEMV is cut along K (or runs as column pairs) reading plain blocks
       PROF(PC_QUANT, bk_quant_rows_launch(x, norm_w, K, B, c.eps, m.xq, staged ? BK_Q8_STAGED : BK_Q8_BLOCKS,
                                           reduce ? &red_desc : nullptr));
       g.prologue = staged ? BK_PRO_STAGED : BK_PRO_Q8; g.x = m.xq;
@@ -334,7 +337,7 @@ int32_t enqueue_step(Model& m, int parity, bool host_tokens = false) {
     bkGemvArgs g;
     if (!L.full) {
       memset(&g, 0, sizeof(g));
-      TRY(set_input(g, m.x[cur], H, L.in_ln));
+      TRY(set_input(g, m.x[cur], H, L.in_ln, m.Cw + m.ZD + 2 * m.Hv));
       g.n_segs = 4;
       g.segs[0] = bkGemvSeg{L.qkv, 0, m.qkv, 0, m.Cw, BK_EPI_BF16, m.Cw, 0};
       g.segs[1] = bkGemvSeg{L.z, 0, m.z, 0, m.ZD, BK_EPI_BF16, m.ZD, 0};
@@ -347,7 +350,7 @@ int32_t enqueue_step(Model& m, int parity, bool host_tokens = false) {
       ga.conv_w = L.conv_w; ga.conv_state_in = L.conv_state[parity]; ga.conv_state_new = L.conv_state[parity ^ 1];
       ga.A_log = L.A_log; ga.dt_bias = L.dt_bias; ga.norm_w = L.gnorm;
       ga.S_in = L.S; ga.S_new = L.S;  // in place: each thread rewrites exactly the rows it read
-      const bool zd_staged = q8_handoff && staged_ok(m.ZD);
+      const bool zd_staged = q8_handoff && staged_ok(m.ZD, H);
       ga.out = m.attn_out; ga.out_q8 = q8_handoff ? m.attn_q8 : 0; ga.out_q8_layout = zd_staged ? BK_Q8_STAGED : BK_Q8_BLOCKS;
       ga.B = B; ga.Hk = m.Hk; ga.Hv = m.Hv; ga.apply_conv = 1;
       ga.state_is_settled = 1;  // this layer's state was last written one whole step ago
@@ -363,13 +366,13 @@ int32_t enqueue_step(Model& m, int parity, bool host_tokens = false) {
       }
     } else {
       memset(&g, 0, sizeof(g));
-      TRY(set_input(g, m.x[cur], H, L.in_ln));
+      TRY(set_input(g, m.x[cur], H, L.in_ln, m.QG + 2 * m.KVD));
       g.n_segs = 3;
       g.segs[0] = bkGemvSeg{L.q, 0, m.qg, 0, m.QG, BK_EPI_BF16, m.QG, 0};
       g.segs[1] = bkGemvSeg{L.k, 0, m.kbuf, 0, m.KVD, BK_EPI_BF16, m.KVD, 0};
       g.segs[2] = bkGemvSeg{L.v, 0, m.vbuf, 0, m.KVD, BK_EPI_BF16, m.KVD, 0};
       PROF(PC_GEMV_PROJ, launch(g));
-      const bool o_staged = q8_handoff && staged_ok(m.Hq * c.head_dim);
+      const bool o_staged = q8_handoff && staged_ok(m.Hq * c.head_dim, H);
       bkAttnArgs aa = step_attn_args(m, L, q8_handoff, o_staged);
       PROF(PC_ATTN, bkAttnDecode(&aa));
       memset(&g, 0, sizeof(g));
@@ -383,12 +386,12 @@ int32_t enqueue_step(Model& m, int parity, bool host_tokens = false) {
       }
     }
     memset(&g, 0, sizeof(g));
-    TRY(set_input(g, m.h1, H, L.post_ln));
+    TRY(set_input(g, m.h1, H, L.post_ln, 2 * m.inter));
     g.n_segs = 1;
     g.segs[0] = bkGemvSeg{L.gate, L.up, m.act, 0, m.inter, BK_EPI_SWIGLU, m.inter, 0};
     PROF(PC_GEMV_GATEUP, launch(g));
     memset(&g, 0, sizeof(g));
-    TRY(set_input(g, m.act, m.inter, 0));
+    TRY(set_input(g, m.act, m.inter, 0, H));
     g.n_segs = 1;
     if (m.tp == 1) {
       g.segs[0] = bkGemvSeg{L.down, 0, m.x[cur ^ 1], m.h1, H, BK_EPI_ADD_BF16, H, 0};
@@ -400,7 +403,7 @@ int32_t enqueue_step(Model& m, int parity, bool host_tokens = false) {
   }
   bkGemvArgs g;
   memset(&g, 0, sizeof(g));
-  TRY(set_input(g, m.x[cur], H, m.final_norm));
+  TRY(set_input(g, m.x[cur], H, m.final_norm, m.vocab_local));
   g.n_segs = 1;
   g.segs[0] = bkGemvSeg{m.embed + (uint64_t)m.vocab_offset * (H / 256) * 144, 0, m.logits, 0, m.vocab_local, BK_EPI_F32,
                         m.vocab_local, 0};

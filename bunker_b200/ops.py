@@ -25,8 +25,9 @@ def gemv_seg(W: int, n_rows: int, out: int, epilogue: int = BK_EPI_F32, *, ld_ou
 def gemv(x: int, K: int, B: int, segs: Sequence[R.bkGemvSeg], prologue: int = BK_PRO_Q8, norm_w: int = 0,
          eps: float = 1e-6, order: int = 0) -> None:
     """Q4_K x Q8_1 GEMV with fused prologue/epilogues (buildMM / buildGateSwiglu, prototypes/decode.ts:101-186).
-    order: BK_GEMV_ORDER_AUTO (0; the dense tcgen05 tile kernel from 16 columns of Q8_1 blocks on) or
-    BK_GEMV_ORDER_LANES (1; always the batch <= 8 kernels' accumulation order)."""
+    order: BK_GEMV_ORDER_AUTO (0; the dense tcgen05 tile kernel from 16 columns of Q8_1 blocks and 4096 launch rows on),
+    BK_GEMV_ORDER_LANES (1; always the batch <= 8 kernels' accumulation order) or BK_GEMV_ORDER_TILE (2; the tile kernel
+    from 16 columns on whatever the row count)."""
     a = R.bkGemvArgs()
     a.K, a.B, a.n_segs, a.prologue, a.order = K, B, len(segs), prologue, order
     a.x, a.norm_w, a.eps = x, norm_w, eps

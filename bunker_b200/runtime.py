@@ -31,7 +31,7 @@ BK_PRO_Q8, BK_PRO_BF16, BK_PRO_RMSNORM, BK_PRO_STAGED = 0, 1, 2, 3
 BK_Q8_BLOCKS, BK_Q8_STAGED = 0, 1
 BK_EPI_F32, BK_EPI_BF16, BK_EPI_ADD_BF16, BK_EPI_SWIGLU = 0, 1, 2, 3
 BK_DTYPE_F32, BK_DTYPE_BF16 = 0, 1
-BK_GEMV_ORDER_AUTO, BK_GEMV_ORDER_LANES = 0, 1
+BK_GEMV_ORDER_AUTO, BK_GEMV_ORDER_LANES, BK_GEMV_ORDER_TILE = 0, 1, 2
 
 BK_OP_EMBED, BK_OP_RMSNORM, BK_OP_GEMV, BK_OP_SWIGLU, BK_OP_CONV1D, BK_OP_ARGMAX, BK_OP_QUANT_Q8_1 = range(1, 8)
 BK_OP_HEADNORM_ROPE, BK_OP_GDN, BK_OP_ATTN, BK_OP_QUANT_Q8_1_BF16 = 8, 9, 10, 11
@@ -121,6 +121,7 @@ SIGNATURES = {
     "bkStagedBytes": (_U64, [_I32, _I32]),
     "bkReduceRmsNormQuantQ8_1": (_I32, [_U64, _I32, _U64, _U64, C.c_uint32, _U64, _U64, _U64, _I32, _I32, _F32, _U64, _I32]),
     "bkTuneGemvRing": (_I32, [_I32, _I32, _I32]),
+    "bkTuneTileMinRows": (_I32, [_I32]),
     "bkSwiglu": (_I32, [_U64, _U64, _I32, _U64]),
     "bkConv1dStep": (_I32, [_U64, _U64, _U64, _I32, _I32, _U64, _U64]),
     "bkGdnStep": (_I32, [C.POINTER(bkGdnArgs)]),

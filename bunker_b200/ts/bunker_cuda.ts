@@ -16,7 +16,7 @@ import { dlopen, ptr as ffiPtr, CString } from "bun:ffi";
 export const BK_OK = 0, BK_ERR_ARG = 10001, BK_ERR_STATE = 10002, BK_ERR_TIMEOUT = 10003, BK_ERR_UNSUPPORTED = 10004, BK_ERR_COMM = 10005;
 export const BK_PRO_Q8 = 0, BK_PRO_BF16 = 1, BK_PRO_RMSNORM = 2, BK_PRO_STAGED = 3;
 export const BK_EPI_F32 = 0, BK_EPI_BF16 = 1, BK_EPI_ADD_BF16 = 2, BK_EPI_SWIGLU = 3;
-export const BK_Q8_BLOCKS = 0, BK_Q8_STAGED = 1, BK_DTYPE_F32 = 0, BK_DTYPE_BF16 = 1, BK_GEMV_ORDER_AUTO = 0, BK_GEMV_ORDER_LANES = 1;
+export const BK_Q8_BLOCKS = 0, BK_Q8_STAGED = 1, BK_DTYPE_F32 = 0, BK_DTYPE_BF16 = 1, BK_GEMV_ORDER_AUTO = 0, BK_GEMV_ORDER_LANES = 1, BK_GEMV_ORDER_TILE = 2;
 export const OPS: Record<string, number> = {
   embed: 1, rmsnorm: 2, gemm: 3, swiglu: 4, conv1d_decode: 5, argmax: 6, quant_q8_1: 7, headnorm_rope: 8,
   gdn_delta_rule: 9, fa2_attn: 10, quant_q8_1_bf16: 11,
@@ -92,6 +92,7 @@ const SYMBOLS = {
   bkTraceCtas: { args: ["u64", "i32"], returns: "i32" },
   bkTraceDisable: { args: [], returns: "i32" },
   bkTuneGemvRing: { args: ["i32", "i32", "i32"], returns: "i32" },
+  bkTuneTileMinRows: { args: ["i32"], returns: "i32" },
   bkStepTraceEnable: { args: ["u64", "i32"], returns: "i32" },
   bkSetSpinLimit: { args: ["i32"], returns: "i32" },
   bkStepBarrierMode: { args: ["i32"], returns: "i32" },

@@ -101,12 +101,14 @@ BK_API int32_t bkLaunchCount(uint64_t* out_count);
 BK_API uint64_t bkStagedBytes(int32_t K, int32_t B);
 
 /* f32 accumulation order of a row's result (the integer block dots are exact either way).  LANES: the order of the
- * batch <= 8 kernels (64-weight units over 32 lanes, butterfly).  AUTO: LANES up to 15 columns; from 16 columns on,
- * with BK_PRO_Q8 input, the dense tile kernel (tcgen05 int8 MMA, accumulators in tensor memory) and its order: one
- * chain per (row, column), sub-blocks then superblocks ascending.  Both are within a few ulp of each other and of the
- * reference's f32 accumulation (prototypes/decode.ts:141-145). */
+ * batch <= 8 kernels (64-weight units over 32 lanes, butterfly).  TILE: from 16 columns on, with BK_PRO_Q8 input, the
+ * dense tile kernel (tcgen05 int8 MMA, accumulators in tensor memory) and its order: one chain per (row, column),
+ * sub-blocks then superblocks ascending; below 16 columns TILE means LANES.  AUTO: TILE when the launch has at least
+ * 4096 rows (all segments together), else LANES -- a rule of the shapes alone, so a host can mirror it.  Both orders are
+ * within a few ulp of each other and of the reference's f32 accumulation (prototypes/decode.ts:141-145). */
 #define BK_GEMV_ORDER_AUTO 0
 #define BK_GEMV_ORDER_LANES 1
+#define BK_GEMV_ORDER_TILE 2
 
 typedef struct bkGemvSeg {
   uint64_t W;        /* Q4_K rows [n_rows][K/256][144] */
@@ -127,7 +129,7 @@ typedef struct bkGemvArgs {
   uint64_t x;
   uint64_t norm_w;   /* bf16 [K], BK_PRO_RMSNORM only */
   float eps;
-  int32_t order;     /* BK_GEMV_ORDER_AUTO or BK_GEMV_ORDER_LANES */
+  int32_t order;     /* BK_GEMV_ORDER_AUTO, _LANES or _TILE */
   bkGemvSeg segs[4];
 } bkGemvArgs;
 

@@ -13,11 +13,13 @@ from . import oracle as O
 
 class OracleModel:
     def __init__(self, cfg, weights: dict, batch: int, split_len: int, attn_warps: int = 8, tp: int = 1,
-                 gemv_order: str | None = None):
-        """gemv_order: "lanes" (the batch <= 8 kernels: units over lanes, butterfly) or "tile" (the dense tile path);
-        None picks what the library picks for this batch (tile from 16 sequences on, on one GPU)."""
+                 gemv_order: str | None = None, tile_min_rows: int = 4096):
+        """gemv_order: "lanes" (the batch <= 8 kernels: units over lanes, butterfly) or "tile" (the dense tile path
+        for every launch of at least tile_min_rows rows, all its segments together -- the library's rule for
+        BK_GEMV_ORDER_AUTO); None picks what the library picks for this batch (tile from 16 sequences on, on one GPU)."""
         self.cfg, self.w, self.B, self.split_len, self.W, self.tp = cfg, weights, batch, split_len, attn_warps, tp
         self.gemv_order = gemv_order or ("tile" if (batch >= 16 and tp == 1) else "lanes")
+        self.tile_min_rows = tile_min_rows
         self.cos_t, self.sin_t = O.rope_tables(cfg.max_len, cfg.rot_dim, cfg.rope_theta)
         self.reset()
 
@@ -36,13 +38,15 @@ class OracleModel:
                 self.conv[li] = np.zeros((B, 3, c.conv_width), np.uint16)
                 self.S[li] = np.zeros((B, c.gdn_v_heads, 128, 128), np.float32)
 
-    def _gemv(self, name: str, N: int, K: int, xq: np.ndarray) -> np.ndarray:
-        return (O.gemv_q4k_q8_tile if self.gemv_order == "tile" else O.gemv_q4k_q8)(self.w[name], N, K, xq)
+    def _gemv(self, name: str, N: int, K: int, xq: np.ndarray, launch_rows: int) -> np.ndarray:
+        """launch_rows: rows of the whole launch this projection is a segment of (it decides the f32 order)."""
+        tile = self.gemv_order == "tile" and launch_rows >= self.tile_min_rows
+        return (O.gemv_q4k_q8_tile if tile else O.gemv_q4k_q8)(self.w[name], N, K, xq)
 
     def _gemv_rowpar(self, name: str, N: int, K: int, x_bf16: np.ndarray) -> np.ndarray:
         """f32 [B, N]; with tp > 1 the K dimension is cut into tp slices of whole superblocks."""
         if self.tp == 1:
-            return self._gemv(name, N, K, O.q8_1_quantize_bf16(x_bf16))
+            return self._gemv(name, N, K, O.q8_1_quantize_bf16(x_bf16), N)
         W = np.ascontiguousarray(self.w[name]).reshape(N, K // 256, 144)
         nsb = K // 256
         base, extra = divmod(nsb, self.tp)
@@ -51,8 +55,7 @@ class OracleModel:
             n = base + (1 if r < extra else 0)
             Wr = np.ascontiguousarray(W[:, s0:s0 + n]).reshape(N, n * 144)
             xr = np.ascontiguousarray(x_bf16[:, s0 * 256:(s0 + n) * 256])
-            parts.append((O.gemv_q4k_q8_tile if self.gemv_order == "tile" else O.gemv_q4k_q8)(
-                Wr, N, n * 256, O.q8_1_quantize_bf16(xr)))
+            parts.append(O.gemv_q4k_q8(Wr, N, n * 256, O.q8_1_quantize_bf16(xr)))   # tensor parallel: lanes order
             s0 += n
         return O.sum_ranks(np.stack(parts))
 
@@ -67,10 +70,11 @@ class OracleModel:
             xq = O.q8_1_quantize_bf16(O.rmsnorm(x, w[f"{p}.input_layernorm.weight"], c.eps))
             if not c.is_full(li):
                 q = f"{p}.linear_attn"
-                qkv = O.epilogue_cast(self._gemv(f"{q}.in_proj_qkv.weight", c.conv_width, H, xq))
-                z = O.epilogue_cast(self._gemv(f"{q}.in_proj_z.weight", c.z_dim, H, xq))
-                a = self._gemv(f"{q}.in_proj_a.weight", c.gdn_v_heads, H, xq)
-                b = self._gemv(f"{q}.in_proj_b.weight", c.gdn_v_heads, H, xq)
+                rows = c.conv_width + c.z_dim + 2 * c.gdn_v_heads   # one launch, four segments
+                qkv = O.epilogue_cast(self._gemv(f"{q}.in_proj_qkv.weight", c.conv_width, H, xq, rows))
+                z = O.epilogue_cast(self._gemv(f"{q}.in_proj_z.weight", c.z_dim, H, xq, rows))
+                a = self._gemv(f"{q}.in_proj_a.weight", c.gdn_v_heads, H, xq, rows)
+                b = self._gemv(f"{q}.in_proj_b.weight", c.gdn_v_heads, H, xq, rows)
                 conv_out, self.conv[li] = O.conv1d_step(qkv, self.conv[li], w[f"{q}.conv1d.weight"])
                 self.S[li], o_raw = O.gdn_step(conv_out, a, b, w[f"{q}.A_log"], w[f"{q}.dt_bias"], self.S[li],
                                                c.gdn_k_heads, c.gdn_v_heads)
@@ -78,9 +82,10 @@ class OracleModel:
                 y = self._gemv_rowpar(f"{q}.out_proj.weight", H, c.z_dim, attn)
             else:
                 q = f"{p}.self_attn"
-                qg = O.epilogue_cast(self._gemv(f"{q}.q_proj.weight", c.qgate_dim, H, xq))
-                k = O.epilogue_cast(self._gemv(f"{q}.k_proj.weight", c.kv_dim, H, xq))
-                v = O.epilogue_cast(self._gemv(f"{q}.v_proj.weight", c.kv_dim, H, xq))
+                rows = c.qgate_dim + 2 * c.kv_dim
+                qg = O.epilogue_cast(self._gemv(f"{q}.q_proj.weight", c.qgate_dim, H, xq, rows))
+                k = O.epilogue_cast(self._gemv(f"{q}.k_proj.weight", c.kv_dim, H, xq, rows))
+                v = O.epilogue_cast(self._gemv(f"{q}.v_proj.weight", c.kv_dim, H, xq, rows))
                 HD = c.head_dim
                 qn = O.headnorm_rope(qg, 2 * HD, w[f"{q}.q_norm.weight"], self.cos_t, self.sin_t, pos, c.attn_q_heads, HD)
                 kn = O.headnorm_rope(k, HD, w[f"{q}.k_norm.weight"], self.cos_t, self.sin_t, pos, c.attn_kv_heads, HD)
@@ -92,13 +97,13 @@ class OracleModel:
                 y = self._gemv_rowpar(f"{q}.o_proj.weight", H, c.attn_q_heads * HD, attn)
             h1 = O.epilogue_add(y, x)
             xq2 = O.q8_1_quantize_bf16(O.rmsnorm(h1, w[f"{p}.post_attention_layernorm.weight"], c.eps))
-            g = self._gemv(f"{p}.mlp.gate_proj.weight", c.intermediate, H, xq2)
-            u = self._gemv(f"{p}.mlp.up_proj.weight", c.intermediate, H, xq2)
+            g = self._gemv(f"{p}.mlp.gate_proj.weight", c.intermediate, H, xq2, 2 * c.intermediate)
+            u = self._gemv(f"{p}.mlp.up_proj.weight", c.intermediate, H, xq2, 2 * c.intermediate)
             act = O.swiglu(g, u)
             y2 = self._gemv_rowpar(f"{p}.mlp.down_proj.weight", H, c.intermediate, act)
             x = O.epilogue_add(y2, h1)
         xqf = O.q8_1_quantize_bf16(O.rmsnorm(x, w["final.norm.weight"], c.eps))
-        self.logits = self._gemv("embed.weight", c.vocab, H, xqf)
+        self.logits = self._gemv("embed.weight", c.vocab, H, xqf, c.vocab)
         idx, val = O.argmax(self.logits)
         self.pos += 1
         return idx, val

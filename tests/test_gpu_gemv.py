@@ -126,10 +126,13 @@ def test_gemv_more_than_eight_columns(bk, B):
     want = O.gemv_q4k_q8(W, N, K, xq)
     dW, dx, dnw, dxq, dres = dev(W), dev(x), dev(nw), dev(xq), dev(res)
     y = R.DeviceBuffer(B * N * 4)
-    ops.gemv_simple(dW.ptr, N, K, dxq.ptr, B, y.ptr)    # from 16 columns on: the dense tile kernel and its order
-    assert_same_bits(y.download(np.float32, (B, N)), O.gemv_q4k_q8_tile(W, N, K, xq) if B >= 16 else want, "Q8_1 blocks in")
+    ops.gemv_simple(dW.ptr, N, K, dxq.ptr, B, y.ptr)    # few rows: the automatic choice stays on these kernels
+    assert_same_bits(y.download(np.float32, (B, N)), want, "Q8_1 blocks in")
     ops.gemv(dxq.ptr, K, B, [ops.gemv_seg(dW.ptr, N, y.ptr, R.BK_EPI_F32)], order=R.BK_GEMV_ORDER_LANES)
     assert_same_bits(y.download(np.float32, (B, N)), want, "Q8_1 blocks in, lane order forced")
+    ops.gemv(dxq.ptr, K, B, [ops.gemv_seg(dW.ptr, N, y.ptr, R.BK_EPI_F32)], order=R.BK_GEMV_ORDER_TILE)
+    assert_same_bits(y.download(np.float32, (B, N)), O.gemv_q4k_q8_tile(W, N, K, xq) if B >= 16 else want,
+                     "Q8_1 blocks in, tile order asked for (the tile kernel from 16 columns on)")
     o = R.DeviceBuffer(B * N * 2)
     ops.gemv(dx.ptr, K, B, [ops.gemv_seg(dW.ptr, N, o.ptr, R.BK_EPI_ADD_BF16, residual=dres.ptr)], prologue=R.BK_PRO_RMSNORM,
              norm_w=dnw.ptr)
@@ -249,7 +252,8 @@ def test_gemv_dense_tile_path(bk, B, K, N):
     assert rel_err(want, O.gemv_q4k_q8_plain(W, N, K, xq)) < 1e-3
     dW, dW2, dxq, dres = dev(W), dev(W2), dev(xq), dev(res)
     y = R.DeviceBuffer(B * N * 4)
-    ops.gemv_simple(dW.ptr, N, K, dxq.ptr, B, y.ptr)
+    T = R.BK_GEMV_ORDER_TILE
+    ops.gemv(dxq.ptr, K, B, [ops.gemv_seg(dW.ptr, N, y.ptr, R.BK_EPI_F32)], order=T)
     assert_same_bits(y.download(np.float32, (B, N)), want, "f32 out")
     # three segments in one launch: bf16 cast | residual add | f32, written side by side into rows of 3N
     wide_bf, wide_f = R.DeviceBuffer.zeros(B * 2 * N * 2), R.DeviceBuffer.zeros(B * N * 4)
@@ -261,11 +265,32 @@ def test_gemv_dense_tile_path(bk, B, K, N):
     res_wide[:, N:] = res
     dres_w = dev(res_wide)
     segs[1].residual = dres_w.ptr
-    ops.gemv(dxq.ptr, K, B, segs)
+    ops.gemv(dxq.ptr, K, B, segs, order=T)
     got = wide_bf.download(np.uint16, (B, 2 * N))
     assert_same_bits(got[:, :N], O.epilogue_cast(want), "bf16 segment")
     assert_same_bits(got[:, N:], O.epilogue_add(want2, res), "residual segment")
     assert_same_bits(wide_f.download(np.float32, (B, N)), want2, "f32 segment")
     act = R.DeviceBuffer(B * N * 2)
-    ops.gemv(dxq.ptr, K, B, [ops.gemv_seg(dW.ptr, N, act.ptr, R.BK_EPI_SWIGLU, W2=dW2.ptr)])
+    ops.gemv(dxq.ptr, K, B, [ops.gemv_seg(dW.ptr, N, act.ptr, R.BK_EPI_SWIGLU, W2=dW2.ptr)], order=T)
     assert_same_bits(act.download(np.uint16, (B, N)), O.swiglu(want, want2), "SwiGLU pair")
+
+
+def test_gemv_automatic_order_follows_the_row_count(bk):
+    """BK_GEMV_ORDER_AUTO at 32 columns: a launch of at least 4096 rows (a SwiGLU pair counts twice) takes the tile
+    kernel and its order, a smaller one the batch <= 8 kernels and theirs."""
+    B, K = 32, 512
+    rng = np.random.default_rng(77)
+    xq = O.q8_1_quantize(rng.normal(0, 1, (B, K)).astype(np.float32))
+    dxq = dev(xq)
+    for N, tile in ((4096, True), (4095, False)):
+        W = synth.q4k_weights(rng, N, K)
+        dW, y = dev(W), R.DeviceBuffer(B * N * 4)
+        ops.gemv_simple(dW.ptr, N, K, dxq.ptr, B, y.ptr)
+        want = (O.gemv_q4k_q8_tile if tile else O.gemv_q4k_q8)(W, N, K, xq)
+        assert_same_bits(y.download(np.float32, (B, N)), want, f"{N} rows")
+    N = 2048   # pair: 4096 launch rows
+    Wg, Wu = synth.q4k_weights(rng, N, K), synth.q4k_weights(rng, N, K)
+    dWg, dWu, act = dev(Wg), dev(Wu), R.DeviceBuffer(B * N * 2)
+    ops.gemv(dxq.ptr, K, B, [ops.gemv_seg(dWg.ptr, N, act.ptr, R.BK_EPI_SWIGLU, W2=dWu.ptr)])
+    assert_same_bits(act.download(np.uint16, (B, N)),
+                     O.swiglu(O.gemv_q4k_q8_tile(Wg, N, K, xq), O.gemv_q4k_q8_tile(Wu, N, K, xq)), "SwiGLU pair of 2 x 2048 rows")

@@ -175,6 +175,30 @@ def test_tiny_model_more_than_eight_sequences(bk, B):
     gm.destroy()
 
 
+@pytest.mark.parametrize("B", [16, 32, 40])
+def test_tiny_model_every_projection_on_the_tile_kernel(bk, B):
+    """From 16 sequences on the projections of many rows run on the dense tile kernel.  The small model's launches are
+    all below the row threshold except the output projection, so the threshold is lowered to 1 for this model (and
+    the oracle told the same): every GEMV of the step then takes the tcgen05 path, with each fused epilogue."""
+    cfg = M.CONFIG_TINY.with_(max_len=32)
+    w = M.synth_weights(cfg, seed=40 + B)
+    assert R.cu().bkTuneTileMinRows(1) == 0
+    try:
+        gm = M.DecodeModel(cfg, w, batch=B)
+        info = gm.info()
+        om = OracleModel(cfg, w, batch=B, split_len=info["split_len"], attn_warps=info["attn_warps"], tile_min_rows=1)
+        prompt = np.random.default_rng(8).integers(0, cfg.vocab, (4, B)).astype(np.int32)
+        ids_g = ids_o = None
+        for t in range(10):
+            ids_o, _ = om.step(prompt[t] if t < 4 else ids_o)
+            ids_g, _ = gm.step(prompt[t] if t < 4 else ids_g)
+            assert np.array_equal(ids_g, ids_o), f"step {t}"
+        assert_same_bits(gm.logits(), om.logits, "logits")
+        gm.destroy()
+    finally:
+        R.cu().bkTuneTileMinRows(0)
+
+
 @pytest.mark.parametrize("B,T,chunk", [(1, 13, None), (1, 20, 9), (2, 11, None), (3, 7, 3), (8, 5, None)])
 def test_prefill_equals_token_by_token(bk, B, T, chunk):
     """bkModelPrefill: T prompt tokens in multi-token passes leave the model in the state T single steps leave it in:
