@@ -6,20 +6,23 @@
 // (src/kernel.ts:396-456: 4-bit blocks expanded to int8 tiles, int32 accumulators, scales applied afterwards,
 // experiments/q4k_q81_final.ts:217); this is that scheme on the 144-byte Q4_K layout.
 //
-// One CTA of 256 threads per 128-row tile; threads t and t+128 <-> tile row t <-> TMEM lane t, each owning half of the
-// row's sub-blocks (expansion) and half of the columns (f32 part).  Per 256-weight superblock column:
-//   1. every thread copies its 64 quant bytes of the row into shared memory (cp.async, three superblocks in flight) and
-//      reads the 16-byte superblock header straight into registers, one superblock ahead;
-//   2. it expands the quant bytes into four 32-byte rows of unsigned int8 (one per sub-block) and stores them in the
-//      K-major "core matrix" layout the MMA reads (8 rows x 16 bytes contiguous, no swizzle);
-//   3. the Q8_1 activation blocks of the superblock are staged the same way (signed int8, N = columns);
-//   4. one thread issues eight MMAs (M = 128, N = 16 or 32, K = 32: exactly one sub-block each) into eight separate
-//      TMEM accumulators -- the integer dot of every (row, column, sub-block), exact -- and commits to an mbarrier;
-//   5. while the tensor core works on superblock s, all threads run the f32 part of superblock s-1: tcgen05.ld brings a
-//      thread its row's int32 sums, and  accd = fma(d8, f32(sc*isum), accd), accm = fma(s8, f32(m), accm)  over the
-//      sub-blocks in ascending order, then  y += fma(d, accd, -(dmin*accm)).
-// That f32 order ("tile order": one chain per (row, column)) is fixed and mirrored by the CPU checker; it differs from
-// the batch <= 8 kernels' lane / butterfly order by a few ulp.
+// One CTA of 640 threads per SM walks over its 128-row tiles, as two groups of warps that meet only at mbarriers:
+//   * four EXPANDER warps (thread <-> tile row).  Warp 0 of them keeps a ring of three stages filled with bulk copies:
+//     a stage holds two superblock columns (288 bytes) of each of the 128 rows; the ring runs ahead across tile
+//     boundaries and starts before the dependency wait.  Per 256-weight superblock column every expander thread
+//     unpacks its row's 128 quant bytes into eight 32-byte rows of unsigned int8 (one per sub-block), stored in the
+//     K-major "core matrix" layout the MMA reads (8 rows x 16 bytes contiguous, no swizzle), decodes the eight 6-bit
+//     scales and mins into a table, and stages a share of the Q8_1 activation blocks the same way (signed int8,
+//     N = columns) with their {d8, s8} pairs.  When all 128 have arrived, one thread issues eight MMAs (M = 128,
+//     N = 16 or 32, K = 32: exactly one sub-block each) into eight separate TMEM accumulators -- the integer dot of
+//     every (row, column, sub-block), exact -- and commits to an mbarrier;
+//   * sixteen SCALER warps (four per TMEM lane quarter, each a quarter of the columns) run the f32 part of a
+//     superblock as soon as its MMAs have completed: tcgen05.ld brings a thread its row's int32 sums, and
+//     accd = fma(d8, f32(sc*isum), accd), accm = fma(s8, f32(m), accm)  over the sub-blocks in ascending order, then
+//     yc += fma(d, accd, -(dmin*accm));  every four superblocks  y += yc.  They release the buffers (shared-memory
+//     tiles, tables, accumulators; two of each) back to the expanders through another mbarrier.
+// That f32 order ("tile order": per (row, column) one chain per chunk of four superblocks, chunks added in order) is
+// fixed and mirrored by the CPU checker; it differs from the batch <= 8 kernels' lane / butterfly order by a few ulp.
 //
 // Single CTA per tile, no cluster, no multicast, no tensor maps.  Every wait is bounded; TMEM is released on every
 // path out of the kernel.
@@ -28,8 +31,12 @@
 namespace {
 
 constexpr int kTileM = 128;
-constexpr int kUT = 256;            // threads: warps w and w+4 share TMEM lane quarter w (rows 32w..32w+31) and split the columns
-constexpr int kRawStages = 3;       // superblock columns of raw Q4_K rows in flight
+constexpr int kScalerWarps = 16;    // warp w reads TMEM lanes 32*(w mod 4)..+31 and the columns of quarter w / 4
+constexpr int kExpanderWarps = 4;   // thread <-> tile row
+constexpr int kUT = (kScalerWarps + kExpanderWarps) * 32;
+constexpr int kStages = 3;          // ring stages, two superblock columns each
+constexpr int kRowPitch = 2 * 144 + 16;   // bytes between rows of a stage: 76 words, so 16-byte reads of 8 rows hit 8 bank groups
+constexpr int kStageBytes = kTileM * kRowPitch;
 constexpr int kTmemCols = 512;
 
 struct UmmaParams {
@@ -45,10 +52,6 @@ BK_DEVINL uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sb
          ((uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46);
 }
 
-BK_DEVINL void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-
 // {a.x*b.x + c.x, a.y*b.y + c.y}: two IEEE fused multiply-adds in one instruction
 BK_DEVINL float2 fma2(float2 a, float2 b, float2 c) {
   unsigned long long ra, rb, rc, rd;
@@ -61,29 +64,67 @@ BK_DEVINL float2 fma2(float2 a, float2 b, float2 c) {
   return d;
 }
 
-// NC: accumulator columns per thread (Npad / 2): 8 or 16
+// f32 of the integer sc*isum, |sc*isum| < 2^22: the product lands in the mantissa of 1.5 * 2^23, which is then
+// subtracted -- both steps exact, so the value equals the integer-to-float conversion
+BK_DEVINL float scaled_sum_f32(int sc, int isum) { return __fsub_rn(__int_as_float(sc * isum + 0x4B400000), 12582912.0f); }
+
+// NC accumulator columns of this thread's TMEM lane, starting at column taddr; the load is complete after tmem_wait
+template <int NC>
+BK_DEVINL void tmem_ld(uint32_t taddr, uint32_t (&r)[NC]) {
+  if constexpr (NC == 8) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+  } else {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(taddr)
+                 : "memory");
+  }
+}
+// the registers are operands so that no use of them can be scheduled before the wait
+template <int NC>
+BK_DEVINL void tmem_wait(uint32_t (&r)[NC]) {
+  if constexpr (NC == 8) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7])::"memory");
+  } else {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3])::"memory");
+  }
+}
+
+BK_DEVINL void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+
+// NC: accumulator columns per scaler thread (MMA N / 4): 4 or 8
 template <int NC>
 __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams P) {
   bk_pdl_trigger();
   const GemvParams& p = P.g;
   extern __shared__ __align__(1024) uint8_t smem[];
-  constexpr int Npad = 2 * NC;
-  uint8_t* raw = smem;                                              // [kRawStages][128][144]
-  uint8_t* As = raw + (size_t)kRawStages * kTileM * 144;            // [2][8][4096]
-  As = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(As) + 1023) & ~(uintptr_t)1023);
-  uint8_t* Bs = As + 2 * 8 * 4096;                                  // [2][8][Npad*32]
-  float2* scs = reinterpret_cast<float2*>(Bs + 2 * 8 * 32 * 32);    // [2][8][32] {d8, s8}
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(scs + 2 * 8 * 32);   // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 2);
+  constexpr int Npad = 4 * NC;
+  uint8_t* raw = smem;                                             // [kStages][128 rows][kRowPitch]
+  uint8_t* As = raw + (size_t)kStages * kStageBytes;               // [2][8][4096]
+  uint8_t* Bs = As + 2 * 8 * 4096;                                 // [2][8][Npad*32]
+  float2* scs = reinterpret_cast<float2*>(Bs + 2 * 8 * 32 * 32);   // [2][8][32] {d8, s8} of (sub-block, column)
+  int2* scm = reinterpret_cast<int2*>(scs + 2 * 8 * 32);           // [2][8][128] {sc, bits of f32(m)} of (sub-block, row)
+  float2* dd = reinterpret_cast<float2*>(scm + 2 * 8 * kTileM);    // [2][128] {d, dmin} of a row's superblock
+  uint64_t* full = reinterpret_cast<uint64_t*>(dd + 2 * kTileM);   // [kStages] weights of a stage have landed
+  uint64_t* ab_full = full + kStages;                              // [2] tiles and tables of a step written (128 arrivals)
+  uint64_t* mma_done = ab_full + 2;                                // [2] the step's MMAs have completed
+  uint64_t* buf_free = mma_done + 2;                               // [2] the scalers are done with a buffer (16 arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(buf_free + 2);
 
-  const int t = threadIdx.x, warp = t >> 5;
-  const int row_t = t & (kTileM - 1);       // tile row (= TMEM lane) of this thread
-  const int half = t >> 7;                  // 0: sub-blocks 0..3 and columns [0, NC); 1: sub-blocks 4..7 and columns [NC, 2NC)
-  const int K = p.K, nsb = K / 256, nblk = K / 32;
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+  const int K = p.K, nsb = K / 256, nblk = K / 32, npairs = (nsb + 1) / 2;
 
   if (t == 0) {
-    mbar_init(smem_u32(mbar), 1);
-    mbar_init(smem_u32(mbar + 1), 1);
+    for (int i = 0; i < kStages; i++) mbar_init(smem_u32(full + i), 1);
+    for (int i = 0; i < 2; i++) {
+      mbar_init(smem_u32(ab_full + i), kExpanderWarps * 32);
+      mbar_init(smem_u32(mma_done + i), 1);
+      mbar_init(smem_u32(buf_free + i), kScalerWarps);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
@@ -95,185 +136,208 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams 
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
-  // M = 128, N = Npad, int32 accumulators, A unsigned 8-bit, B signed 8-bit, both K-major
-  const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(Npad >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
 
   const int n_tiles = (p.total_vrows + kTileM - 1) / kTileM;
-  uint32_t uses[2] = {0u, 0u};   // completed commits per accumulator buffer (mbarrier phase)
-  const uint32_t* xq = reinterpret_cast<const uint32_t*>(p.x);
-  bool waited = false;           // the dependency wait has been executed (weights are requested before it)
+  const int n_my = (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;   // tiles of this CTA
+  const int G = n_my * nsb;       // superblock steps of this CTA, tile after tile
+  const int Q = n_my * npairs;    // ring fills: pairs of superblock columns, never across a tile boundary
 
-  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-    const int vrow = tile * kTileM + row_t;
-    const bool have_row = vrow < p.total_vrows;
-    VRow vr = {nullptr, 0, 0};
-    if (have_row) vr = decode_vrow(p, vrow);
-    const uint8_t* wrow = vr.row;
-
-    float y[NC];
+  if (warp < kScalerWarps) {
+    // ================= scalers: f32 part of step g from accumulator buffer g&1 =================
+    const int row_t = t & (kTileM - 1);   // tile row (= TMEM lane) of this thread
+    const int qd = t >> 7;                // which quarter of the columns
+    bk_pdl_wait();
+    float y[NC], yc[NC];
 #pragma unroll
-    for (int c = 0; c < NC; c++) y[c] = 0.0f;
-
-    // this thread's share of its row's superblock s: the four 16-byte quant chunks of two 32-byte groups
-    // (half 0: groups 0,1 = sub-blocks 0..3; half 1: groups 2,3 = sub-blocks 4..7)
-    auto request_raw = [&](int s) {
-      if (s < nsb && have_row) {
-        const uint32_t dst = smem_u32(raw + ((size_t)(s % kRawStages) * kTileM + row_t) * 144) + 16 + half * 64;
-        const uint8_t* src = wrow + (size_t)s * 144 + 16 + half * 64;
-#pragma unroll
-        for (int k = 0; k < 4; k++) cp_async16(dst + 16 * k, src + 16 * k);
-      }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-    // activation block (j, b) of superblock s for this thread: item i = j*Npad + b, Npad*8 <= 256 items
-    uint32_t xw[9];
-    const int xi_j = t / Npad, xi_b = t - (t / Npad) * Npad;
-    auto load_x = [&](int s) {
-      const bool ok = s < nsb && t < Npad * 8 && xi_b < P.B;
-#pragma unroll
-      for (int k = 0; k < 9; k++) xw[k] = ok ? __ldcg(xq + ((size_t)xi_b * nblk + (size_t)s * 8 + xi_j) * 9 + k) : 0u;
-    };
-    auto store_x = [&](int s) {
-      if (t < Npad * 8) {
-        uint8_t* tile_j = Bs + (size_t)(s & 1) * 8 * (Npad * 32) + (size_t)xi_j * (Npad * 32) + (xi_b >> 3) * 128 + (xi_b & 7) * 16;
-        *reinterpret_cast<uint4*>(tile_j) = make_uint4(xw[0], xw[1], xw[2], xw[3]);
-        *reinterpret_cast<uint4*>(tile_j + Npad * 16) = make_uint4(xw[4], xw[5], xw[6], xw[7]);
-        int qsum = 0;
-#pragma unroll
-        for (int k = 0; k < 8; k++) qsum = bk_dp4a_ss(xw[k], 0x01010101u, qsum);
-        const float d8 = bk_q8half_to_f32((uint16_t)(xw[8] & 0xffffu));
-        scs[(size_t)(s & 1) * 8 * 32 + xi_j * 32 + xi_b] = make_float2(d8, __fmul_rn(d8, (float)qsum));
-      }
-    };
-    // superblock header (d, dmin, scales, mins) of this thread's row, read straight from global memory one superblock
-    // ahead: next (in flight), current (being multiplied), previous (being scaled)
-    uint4 h_next = make_uint4(0, 0, 0, 0), h_cur = make_uint4(0, 0, 0, 0), h_prev = make_uint4(0, 0, 0, 0);
-    auto load_hdr = [&](int s) { h_next = (s < nsb && have_row) ? __ldg(reinterpret_cast<const uint4*>(wrow + (size_t)s * 144)) : make_uint4(0, 0, 0, 0); };
-
-    auto epilogue = [&](int s) {   // f32 part of superblock s from accumulator buffer s&1, this thread's NC columns
-      const int buf = s & 1;
-      mbar_wait_bounded(smem_u32(mbar + buf), (uses[buf] & 1u), p.status);
-      uses[buf]++;
+    for (int c = 0; c < NC; c++) y[c] = yc[c] = 0.0f;
+    int s = 0, tl = 0;
+    for (int g = 0; g < G; g++) {
+      const int buf = g & 1;
+      const uint32_t par = (uint32_t)((g >> 1) & 1);
+      mbar_wait_bounded(smem_u32(ab_full + buf), par, p.status);    // the tables of this step are visible
+      mbar_wait_bounded(smem_u32(mma_done + buf), par, p.status);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const float d = bk_f16_to_f32((uint16_t)(h_prev.x & 0xffffu)), dmin = bk_f16_to_f32((uint16_t)(h_prev.x >> 16));
-      const float2* sb_ = scs + (size_t)buf * 8 * 32 + half * NC;
+      const float2 dm = dd[buf * kTileM + row_t];
+      const float4* sb4 = reinterpret_cast<const float4*>(scs + (size_t)buf * 8 * 32 + qd * NC);
+      const int2* sm_ = scm + (size_t)buf * 8 * kTileM + row_t;
+      const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(buf * 256 + qd * NC);
       float2 acc[NC];   // {accd, accm}
 #pragma unroll
       for (int c = 0; c < NC; c++) acc[c] = make_float2(0.0f, 0.0f);
+      uint32_t r[NC], rn[NC];
+      tmem_ld<NC>(taddr, r);
+      tmem_wait<NC>(r);
 #pragma unroll
       for (int j = 0; j < 8; j++) {
-        int sc, mn;
-        bk_q4k_scale_min(h_prev.y, h_prev.z, h_prev.w, j, sc, mn);
-        const float fsc = (float)sc, fm = (float)mn;
-        uint32_t r[NC];
-        const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(buf * 256 + j * Npad + half * NC);
-        if constexpr (NC == 16) {
-          asm volatile(
-              "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-              : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-                "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-              : "r"(taddr)
-              : "memory");
-        } else {
-          asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                       : "r"(taddr)
-                       : "memory");
+        if (j < 7) tmem_ld<NC>(taddr + (uint32_t)((j + 1) * Npad), rn);   // in flight during this sub-block's arithmetic
+        const int2 s2 = sm_[j * kTileM];
+        const float fm = __int_as_float(s2.y);
+#pragma unroll
+        for (int c = 0; c < NC; c += 2) {
+          const float4 f = sb4[j * 16 + (c >> 1)];   // {d8, s8} of columns c, c+1
+          acc[c] = fma2(make_float2(f.x, f.y), make_float2(scaled_sum_f32(s2.x, (int)r[c]), fm), acc[c]);
+          acc[c + 1] = fma2(make_float2(f.z, f.w), make_float2(scaled_sum_f32(s2.x, (int)r[c + 1]), fm), acc[c + 1]);
         }
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (j < 7) {
+          tmem_wait<NC>(rn);
+#pragma unroll
+          for (int c = 0; c < NC; c++) r[c] = rn[c];
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(buf_free + buf));   // tables and accumulators of this buffer may be overwritten
+#pragma unroll
+      for (int c = 0; c < NC; c++) yc[c] = __fadd_rn(yc[c], fmaf(dm.x, acc[c].x, -__fmul_rn(dm.y, acc[c].y)));
+      const bool last = s == nsb - 1;
+      if ((s & 3) == 3 || last) {   // a chunk of four superblocks ends
 #pragma unroll
         for (int c = 0; c < NC; c++) {
-          // accd = fma(d8, f32(sc*isum), accd) and accm = fma(s8, f32(m), accm) as one packed instruction; sc*isum < 2^22
-          // is exact as the f32 product of the two integers
-          acc[c] = fma2(sb_[j * 32 + c], make_float2(__fmul_rn(fsc, (float)(int)r[c]), fm), acc[c]);
+          y[c] = __fadd_rn(y[c], yc[c]);
+          yc[c] = 0.0f;
         }
       }
+      if (last) {   // fused epilogue of the tile; uniform over the warp
+        const int vrow = ((int)blockIdx.x + tl * (int)gridDim.x) * kTileM + row_t;
+        const bool have_row = vrow < p.total_vrows;
+        VRow vr = {nullptr, 0, 0};
+        if (have_row) vr = decode_vrow(p, vrow);
+        const SegDev& sg = p.segs[vr.si];
+        const bool swiglu = have_row && sg.epi == BK_EPI_SWIGLU;
 #pragma unroll
-      for (int c = 0; c < NC; c++) y[c] = __fadd_rn(y[c], fmaf(d, acc[c].x, -__fmul_rn(dmin, acc[c].y)));
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        for (int c = 0; c < NC; c++) {
+          const int b = qd * NC + c;
+          const float yup = __shfl_xor_sync(0xffffffffu, y[c], 1);   // the odd neighbour row: the "up" row of a SwiGLU pair
+          if (b < P.B && have_row && !(swiglu && (row_t & 1)))
+            store_epilogue<false>(p, sg, (size_t)b * sg.ld_out + sg.col_off + vr.n, y[c], yup);
+          y[c] = 0.0f;
+        }
+        s = 0;
+        tl++;
+      } else {
+        s++;
+      }
+    }
+  } else {
+    // ================= expanders: ring, unpacking, activation staging, MMA issue =================
+    const int te = t - kScalerWarps * 32;   // tile row of this thread
+    const bool lead = warp == kScalerWarps; // the warp that fills the ring and issues the MMAs
+    const uint32_t* xq = reinterpret_cast<const uint32_t*>(p.x);
+    // M = 128, N = Npad, int32 accumulators, A unsigned 8-bit, B signed 8-bit, both K-major
+    const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(Npad >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+    // fill ring stage q mod kStages with pair q (weights depend on no earlier kernel)
+    auto issue_pair = [&](int q) {
+      if (q >= Q) return;
+      const int tl = q / npairs, pp = q - tl * npairs;
+      const int tile = (int)blockIdx.x + tl * (int)gridDim.x;
+      const uint32_t bytes = (uint32_t)((nsb - 2 * pp) >= 2 ? 288 : 144);
+      const int rows_here = min(kTileM, p.total_vrows - tile * kTileM);
+      const uint32_t bar = smem_u32(full + q % kStages);
+      if (lane == 0) mbar_expect_tx(bar, (uint32_t)rows_here * bytes);
+      __syncwarp();
+      const uint32_t dst0 = smem_u32(raw + (size_t)(q % kStages) * kStageBytes);
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        const int r = lane + 32 * k;
+        if (r < rows_here) bulk_g2s(dst0 + r * kRowPitch, decode_vrow(p, tile * kTileM + r).row + (size_t)pp * 288, bytes, bar);
+      }
+    };
+    // activation blocks of a superblock: Npad*8 items (column b, sub-block j), item i = b*8 + j so that neighbouring
+    // threads read neighbouring 36-byte blocks; thread te takes items te and te + 128
+    constexpr int kXI = Npad * 8 / 128;   // 1 or 2
+    uint32_t xw[kXI][9];
+    auto load_x = [&](int s) {
+#pragma unroll
+      for (int i = 0; i < kXI; i++) {
+        const int it = te + 128 * i, b = it >> 3, j = it & 7;
+#pragma unroll
+        for (int k = 0; k < 9; k++) xw[i][k] = b < P.B ? __ldcg(xq + ((size_t)b * nblk + (size_t)s * 8 + j) * 9 + k) : 0u;
+      }
+    };
+    auto store_x = [&](int buf) {
+#pragma unroll
+      for (int i = 0; i < kXI; i++) {
+        const int it = te + 128 * i, b = it >> 3, j = it & 7;
+        uint8_t* tile_j = Bs + (size_t)buf * 8 * (Npad * 32) + (size_t)j * (Npad * 32) + (b >> 3) * 128 + (b & 7) * 16;
+        *reinterpret_cast<uint4*>(tile_j) = make_uint4(xw[i][0], xw[i][1], xw[i][2], xw[i][3]);
+        *reinterpret_cast<uint4*>(tile_j + Npad * 16) = make_uint4(xw[i][4], xw[i][5], xw[i][6], xw[i][7]);
+        int qsum = 0;
+#pragma unroll
+        for (int k = 0; k < 8; k++) qsum = bk_dp4a_ss(xw[i][k], 0x01010101u, qsum);
+        const float d8 = bk_q8half_to_f32((uint16_t)(xw[i][8] & 0xffffu));
+        scs[(size_t)buf * 8 * 32 + j * 32 + b] = make_float2(d8, __fmul_rn(d8, (float)qsum));
+      }
     };
 
-    // ---- pipeline over the superblock columns of this tile ----
-    for (int s = 0; s < kRawStages; s++) request_raw(s);   // weights depend on nothing: requested before the wait
-    load_hdr(0);
-    if (!waited) {
-      bk_pdl_wait();
-      waited = true;
-    }
+    if (lead)
+      for (int q = 0; q < kStages; q++) issue_pair(q);
+    bk_pdl_wait();
     load_x(0);
-    store_x(0);
-    for (int s = 0; s < nsb; s++) {
-      h_prev = h_cur;
-      h_cur = h_next;
-      load_hdr(s + 1);
-      load_x(s + 1);   // in flight during the expansion below
-      // (1) this thread's 64 quant bytes of superblock s have landed (it copied them itself)
-      asm volatile("cp.async.wait_group %0;" ::"n"(kRawStages - 1) : "memory");
-      const uint8_t* rw = raw + ((size_t)(s % kRawStages) * kTileM + row_t) * 144 + 16 + half * 64;
-      uint4 q[4];
+    int s = 0, tl = 0;
+    for (int g = 0; g < G; g++) {
+      const int buf = g & 1;
+      const uint32_t par = (uint32_t)((g >> 1) & 1);
+      const int q = tl * npairs + (s >> 1);
+      const int stage = q % kStages;
+      if ((s & 1) == 0) mbar_wait_bounded(smem_u32(full + stage), (uint32_t)((q / kStages) & 1), p.status);
+      if (g >= 2) mbar_wait_bounded(smem_u32(buf_free + buf), par ^ 1u, p.status);   // the scalers have finished step g-2
+      // (1) activations of this step (loaded during the previous one), then request the next step's
+      store_x(buf);
+      const int s_next = s + 1 == nsb ? 0 : s + 1;
+      if (g + 1 < G) load_x(s_next);
+      // (2) header -> scale table; 4-bit quants -> unsigned int8 rows, sub-block 2p from the low nibbles of group p,
+      //     2p+1 from the high nibbles
+      const uint8_t* rw = raw + (size_t)stage * kStageBytes + (size_t)te * kRowPitch + (s & 1) * 144;
+      const uint4 hdr = *reinterpret_cast<const uint4*>(rw);
+      dd[buf * kTileM + te] = make_float2(bk_f16_to_f32((uint16_t)(hdr.x & 0xffffu)), bk_f16_to_f32((uint16_t)(hdr.x >> 16)));
+      int2* sm_w = scm + (size_t)buf * 8 * kTileM + te;
+      uint8_t* Ab = As + (size_t)buf * 8 * 4096 + (te >> 3) * 128 + (te & 7) * 16;
 #pragma unroll
-      for (int k = 0; k < 4; k++) q[k] = have_row ? *reinterpret_cast<const uint4*>(rw + 16 * k) : make_uint4(0, 0, 0, 0);
-      request_raw(s + kRawStages);   // refills the stage just read
-      // (2) 4-bit quants -> unsigned int8 rows of this thread's four sub-block tiles
-      uint8_t* Ab = As + (size_t)(s & 1) * 8 * 4096 + (row_t >> 3) * 128 + (row_t & 7) * 16;
-#pragma unroll
-      for (int g = 0; g < 2; g++) {
-        const int grp = half * 2 + g;
-        const uint4 a = q[2 * g], b = q[2 * g + 1];
-        const uint4 lo0 = make_uint4(a.x & 0x0f0f0f0fu, a.y & 0x0f0f0f0fu, a.z & 0x0f0f0f0fu, a.w & 0x0f0f0f0fu);
-        const uint4 lo1 = make_uint4(b.x & 0x0f0f0f0fu, b.y & 0x0f0f0f0fu, b.z & 0x0f0f0f0fu, b.w & 0x0f0f0f0fu);
-        const uint4 hi0 = make_uint4((a.x >> 4) & 0x0f0f0f0fu, (a.y >> 4) & 0x0f0f0f0fu, (a.z >> 4) & 0x0f0f0f0fu, (a.w >> 4) & 0x0f0f0f0fu);
-        const uint4 hi1 = make_uint4((b.x >> 4) & 0x0f0f0f0fu, (b.y >> 4) & 0x0f0f0f0fu, (b.z >> 4) & 0x0f0f0f0fu, (b.w >> 4) & 0x0f0f0f0fu);
-        *reinterpret_cast<uint4*>(Ab + (2 * grp) * 4096) = lo0;
-        *reinterpret_cast<uint4*>(Ab + (2 * grp) * 4096 + 2048) = lo1;
-        *reinterpret_cast<uint4*>(Ab + (2 * grp + 1) * 4096) = hi0;
-        *reinterpret_cast<uint4*>(Ab + (2 * grp + 1) * 4096 + 2048) = hi1;
+      for (int pq = 0; pq < 4; pq++) {
+        uint32_t sc2, mn2;
+        bk_q4k_scale_min_pair(hdr.y, hdr.z, hdr.w, pq, sc2, mn2);
+        sm_w[(2 * pq) * kTileM] = make_int2((int)(sc2 & 0xffu), __float_as_int((float)(mn2 & 0xffu)));
+        sm_w[(2 * pq + 1) * kTileM] = make_int2((int)(sc2 >> 8), __float_as_int((float)(mn2 >> 8)));
+        const uint4 qa = *reinterpret_cast<const uint4*>(rw + 16 + pq * 32), qb = *reinterpret_cast<const uint4*>(rw + 32 + pq * 32);
+        uint8_t* A0 = Ab + (size_t)(2 * pq) * 4096;
+        *reinterpret_cast<uint4*>(A0) = make_uint4(qa.x & 0x0f0f0f0fu, qa.y & 0x0f0f0f0fu, qa.z & 0x0f0f0f0fu, qa.w & 0x0f0f0f0fu);
+        *reinterpret_cast<uint4*>(A0 + 2048) = make_uint4(qb.x & 0x0f0f0f0fu, qb.y & 0x0f0f0f0fu, qb.z & 0x0f0f0f0fu, qb.w & 0x0f0f0f0fu);
+        *reinterpret_cast<uint4*>(A0 + 4096) =
+            make_uint4((qa.x >> 4) & 0x0f0f0f0fu, (qa.y >> 4) & 0x0f0f0f0fu, (qa.z >> 4) & 0x0f0f0f0fu, (qa.w >> 4) & 0x0f0f0f0fu);
+        *reinterpret_cast<uint4*>(A0 + 4096 + 2048) =
+            make_uint4((qb.x >> 4) & 0x0f0f0f0fu, (qb.y >> 4) & 0x0f0f0f0fu, (qb.z >> 4) & 0x0f0f0f0fu, (qb.w >> 4) & 0x0f0f0f0fu);
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads shared memory through the async proxy
-      __syncthreads();
-      // (3) eight MMAs, one per sub-block, into accumulator buffer s&1
-      if (t == 0) {
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a0 = smem_u32(As + (size_t)(s & 1) * 8 * 4096);
-        const uint32_t b0 = smem_u32(Bs + (size_t)(s & 1) * 8 * (Npad * 32));
+      mbar_arrive(smem_u32(ab_full + buf));
+      if (lead) {
+        mbar_wait_bounded(smem_u32(ab_full + buf), par, p.status);   // all 128 rows and the activations are in place
+        // (3) eight MMAs, one per sub-block, into accumulator buffer g&1
+        if (lane == 0) {
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a0 = smem_u32(As + (size_t)buf * 8 * 4096);
+          const uint32_t b0 = smem_u32(Bs + (size_t)buf * 8 * (Npad * 32));
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-          const uint64_t ad = umma_desc(a0 + j * 4096, 2048, 128);
-          const uint64_t bd = umma_desc(b0 + j * (Npad * 32), (uint32_t)Npad * 16, 128);
-          const uint32_t dcol = tmem + (uint32_t)((s & 1) * 256 + j * Npad);
-          asm volatile(
-              "{\n\t.reg .pred pz;\n\tsetp.ne.b32 pz, %4, 0;\n\t"
-              "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, pz;\n\t}"
-              ::"r"(dcol), "l"(ad), "l"(bd), "r"(idesc), "r"(0u), "r"(0u)
-              : "memory");
+          for (int j = 0; j < 8; j++) {
+            const uint64_t ad = umma_desc(a0 + j * 4096, 2048, 128);
+            const uint64_t bd = umma_desc(b0 + j * (Npad * 32), (uint32_t)Npad * 16, 128);
+            const uint32_t dcol = tmem + (uint32_t)(buf * 256 + j * Npad);
+            asm volatile(
+                "{\n\t.reg .pred pz;\n\tsetp.ne.b32 pz, %4, 0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, pz;\n\t}"
+                ::"r"(dcol), "l"(ad), "l"(bd), "r"(idesc), "r"(0u), "r"(0u)
+                : "memory");
+          }
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(mma_done + buf))
+                       : "memory");
         }
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(mbar + (s & 1)))
-                     : "memory");
+        __syncwarp();
+        // the ring stage is free once every row has been unpacked from both of its superblock columns
+        if ((s & 1) || s == nsb - 1) issue_pair(q + kStages);
       }
-      // (4) f32 part of the previous superblock while the tensor core works on this one
-      if (s > 0) epilogue(s - 1);
-      // (5) activations of the next superblock into the buffers the previous one has released -- once every thread
-      //     has finished reading that one's block scales
-      __syncthreads();
-      store_x(s + 1);
+      s = s_next;
+      if (s == 0) tl++;
     }
-    h_prev = h_cur;
-    epilogue(nsb - 1);
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-
-    // ---- fused epilogues: this thread's columns [half*NC, half*NC + NC) of its row ----
-    const SegDev& sg = p.segs[vr.si];
-    const bool swiglu = have_row && sg.epi == BK_EPI_SWIGLU;
-#pragma unroll
-    for (int c = 0; c < NC; c++) {
-      const int b = half * NC + c;
-      const float yup = __shfl_xor_sync(0xffffffffu, y[c], 1);   // the odd neighbour row: the "up" row of a SwiGLU pair
-      if (b < P.B && have_row && !(swiglu && (row_t & 1)))
-        store_epilogue<false>(p, sg, (size_t)b * sg.ld_out + sg.col_off + vr.n, y[c], yup);
-    }
-    __syncthreads();   // shared buffers and accumulators are reused by the next tile
   }
-  if (!waited) bk_pdl_wait();
 
   // ---- release tensor memory (every thread gets here, whatever happened above) ----
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -285,7 +349,7 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams 
 }
 
 size_t umma_smem_bytes() {
-  return (size_t)kRawStages * kTileM * 144 + 1024 + 2 * 8 * 4096 + 2 * 8 * 32 * 32 + 2 * 8 * 32 * 8 + 64;
+  return (size_t)kStages * kStageBytes + 2 * 8 * 4096 + 2 * 8 * 32 * 32 + 2 * 8 * 32 * 8 + 2 * 8 * kTileM * 8 + 2 * kTileM * 8 + 128;
 }
 
 }  // namespace
@@ -301,14 +365,14 @@ int32_t bk_gemv_umma_launch(void* params, int B) {
   static bool configured = false;
   const size_t smem = umma_smem_bytes();
   if (!configured) {
+    BK_CUDA(cudaFuncSetAttribute(gemv_q4k_umma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     BK_CUDA(cudaFuncSetAttribute(gemv_q4k_umma_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    BK_CUDA(cudaFuncSetAttribute(gemv_q4k_umma_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
   const int tiles = (P.g.total_vrows + kTileM - 1) / kTileM;
   const int grid = tiles < c.sm_count ? tiles : c.sm_count;
-  if (P.Npad == 16) BK_CUDA(bk_launch_pdl(gemv_q4k_umma_kernel<8>, dim3(grid), dim3(kUT), smem, P));
-  else BK_CUDA(bk_launch_pdl(gemv_q4k_umma_kernel<16>, dim3(grid), dim3(kUT), smem, P));
+  if (P.Npad == 16) BK_CUDA(bk_launch_pdl(gemv_q4k_umma_kernel<4>, dim3(grid), dim3(kUT), smem, P));
+  else BK_CUDA(bk_launch_pdl(gemv_q4k_umma_kernel<8>, dim3(grid), dim3(kUT), smem, P));
   BK_CHECK_LAUNCH();
   return BK_OK;
 }

@@ -502,13 +502,15 @@ ORC_API void orc_gemv_q4k_q8(const uint8_t* W, int N, int K, const uint8_t* xq, 
 }
 
 
-/* The order of the dense tile path (batch >= 16, tensor-core integer dots): per (row, column) one chain.  Inside a
- * superblock the eight sub-blocks in ascending order, accd = fma(d8_j, f32(sc_j*isum_j), accd) and
- * accm = fma(s8_j, f32(m_j), accm) from zero; then val = fma(d, accd, -(dmin*accm)) and y = y + val over the
- * superblocks in ascending order.  Integer sums are exact either way; only this f32 order differs from the
- * lane / butterfly order above (by a few ulp). */
+/* The order of the dense tile path (batch >= 16, tensor-core integer dots): per (row, column) one chain per chunk
+ * of four superblocks.  Inside a superblock the eight sub-blocks in ascending order,
+ * accd = fma(d8_j, f32(sc_j*isum_j), accd) and accm = fma(s8_j, f32(m_j), accm) from zero; then
+ * val = fma(d, accd, -(dmin*accm)); yc = yc + val over the (up to four) superblocks of a chunk in ascending order from
+ * zero; y = y + yc over the chunks in ascending order from zero.  (The chunks are what lets a launch of few rows be
+ * cut along K over several thread blocks without changing a bit.)  Integer sums are exact either way; only this f32
+ * order differs from the lane / butterfly order above (by a few ulp). */
 static float gemv_row_tile(const uint8_t* wrow, const uint8_t* xq, int K) {
-  float y = 0.0f;
+  float y = 0.0f, yc = 0.0f;
   int nsb = K / 256;
   for (int s = 0; s < nsb; s++) {
     const uint8_t* sb = wrow + (size_t)s * 144;
@@ -533,7 +535,11 @@ static float gemv_row_tile(const uint8_t* wrow, const uint8_t* xq, int K) {
     }
     float t = dmin * accm;
     float val = fmaf(d, accd, -t);
-    y = y + val;
+    yc = yc + val;
+    if ((s & 3) == 3 || s == nsb - 1) {
+      y = y + yc;
+      yc = 0.0f;
+    }
   }
   return y;
 }
