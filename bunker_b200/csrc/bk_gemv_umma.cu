@@ -7,15 +7,20 @@
 // experiments/q4k_q81_final.ts:217); this is that scheme on the 144-byte Q4_K layout.
 //
 // One CTA of 640 threads per SM walks over its 128-row tiles, as two groups of warps that meet only at mbarriers:
-//   * four EXPANDER warps (thread <-> tile row).  Warp 0 of them keeps a ring of three stages filled with bulk copies:
-//     a stage holds two superblock columns (288 bytes) of each of the 128 rows; the ring runs ahead across tile
-//     boundaries and starts before the dependency wait.  Per 256-weight superblock column every expander thread
+//   * one PRODUCER warp keeps a ring of three stages filled with bulk copies: a stage holds two superblock columns
+//     (288 bytes) of each of the 128 rows; the ring runs ahead across tile boundaries and starts before the
+//     dependency wait.  (A bulk copy of a few hundred bytes costs its issuer about 75 cycles, 128 of them per stage:
+//     that is why this warp does nothing else.)
+//   * four EXPANDER warps (thread <-> tile row).  Per 256-weight superblock column every expander thread
 //     unpacks its row's 128 quant bytes into eight 32-byte rows of unsigned int8 (one per sub-block), stored in the
-//     K-major "core matrix" layout the MMA reads (8 rows x 16 bytes contiguous, no swizzle), decodes the eight 6-bit
-//     scales and mins into a table, and stages a share of the Q8_1 activation blocks the same way (signed int8,
-//     N = columns) with their {d8, s8} pairs.  When all 128 have arrived, one thread issues eight MMAs (M = 128,
-//     N = 16 or 32, K = 32: exactly one sub-block each) into eight separate TMEM accumulators -- the integer dot of
-//     every (row, column, sub-block), exact -- and commits to an mbarrier;
+//     K-major "core matrix" layout the MMA reads (8 rows x 16 bytes contiguous, no swizzle), and decodes the eight
+//     6-bit scales and mins into a table;
+//   * two STAGER warps put the superblock's Q8_1 activation blocks into the same layout (signed int8, N = columns)
+//     with their d8 and s8 scales, reading one superblock ahead;
+//   * one MMA warp: when all 128 expander threads have arrived, one thread issues eight MMAs (M = 128, N = 16 or 32,
+//     K = 32: exactly one sub-block each) into eight separate TMEM accumulators -- the integer dot of every (row,
+//     column, sub-block), exact -- and commits to an mbarrier (issue and commit keep that thread busy for about a
+//     thousand cycles per superblock, which is why it is not an expander);
 //   * sixteen SCALER warps (four per TMEM lane quarter, each a quarter of the columns) run the f32 part of a
 //     superblock as soon as its MMAs have completed: tcgen05.ld brings a thread its row's int32 sums, and
 //     accd = fma(d8, f32(sc*isum), accd), accm = fma(s8, f32(m), accm)  over the sub-blocks in ascending order, then
@@ -31,9 +36,13 @@
 namespace {
 
 constexpr int kTileM = 128;
-constexpr int kScalerWarps = 16;    // warp w reads TMEM lanes 32*(w mod 4)..+31 and the columns of quarter w / 4
-constexpr int kExpanderWarps = 4;   // thread <-> tile row
-constexpr int kUT = (kScalerWarps + kExpanderWarps) * 32;
+constexpr int kExpanderWarps = 4;   // warps 0..3 (the oldest warps, which the scheduler prefers): thread <-> tile row
+constexpr int kScalerWarps = 16;    // warps 4..19: warp w reads TMEM lanes 32*(w mod 4)..+31, columns of quarter (w - 4) / 4
+constexpr int kProducerWarp = kExpanderWarps + kScalerWarps;   // warp 20 keeps the weight ring filled
+constexpr int kMmaWarp = kProducerWarp + 1;                    // warp 21 issues the MMAs
+constexpr int kStagerWarp0 = kMmaWarp + 1;                     // warps 22, 23 stage the activation blocks
+constexpr int kStagerWarps = 2;
+constexpr int kUT = (kStagerWarp0 + kStagerWarps) * 32;
 constexpr int kStages = 3;          // ring stages, two superblock columns each
 constexpr int kRowPitch = 2 * 144 + 16;   // bytes between rows of a stage: 76 words, so 16-byte reads of 8 rows hit 8 bank groups
 constexpr int kStageBytes = kTileM * kRowPitch;
@@ -106,11 +115,12 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams 
   uint8_t* raw = smem;                                             // [kStages][128 rows][kRowPitch]
   uint8_t* As = raw + (size_t)kStages * kStageBytes;               // [2][8][4096]
   uint8_t* Bs = As + 2 * 8 * 4096;                                 // [2][8][Npad*32]
-  float2* scs = reinterpret_cast<float2*>(Bs + 2 * 8 * 32 * 32);   // [2][8][32] {d8, s8} of (sub-block, column)
-  int2* scm = reinterpret_cast<int2*>(scs + 2 * 8 * 32);           // [2][8][128] {sc, bits of f32(m)} of (sub-block, row)
+  float* scs = reinterpret_cast<float*>(Bs + 2 * 8 * 32 * 32);     // [2][8][d8 of 32 columns | s8 of 32 columns]
+  int2* scm = reinterpret_cast<int2*>(scs + 2 * 8 * 64);           // [2][8][128] {sc, bits of f32(m)} of (sub-block, row)
   float2* dd = reinterpret_cast<float2*>(scm + 2 * 8 * kTileM);    // [2][128] {d, dmin} of a row's superblock
   uint64_t* full = reinterpret_cast<uint64_t*>(dd + 2 * kTileM);   // [kStages] weights of a stage have landed
-  uint64_t* ab_full = full + kStages;                              // [2] tiles and tables of a step written (128 arrivals)
+  uint64_t* empty = full + kStages;                                // [kStages] every row of a stage has been unpacked (4 arrivals)
+  uint64_t* ab_full = empty + kStages;                             // [2] tiles and tables of a step written (192 arrivals)
   uint64_t* mma_done = ab_full + 2;                                // [2] the step's MMAs have completed
   uint64_t* buf_free = mma_done + 2;                               // [2] the scalers are done with a buffer (16 arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(buf_free + 2);
@@ -119,9 +129,12 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams 
   const int K = p.K, nsb = K / 256, nblk = K / 32, npairs = (nsb + 1) / 2;
 
   if (t == 0) {
-    for (int i = 0; i < kStages; i++) mbar_init(smem_u32(full + i), 1);
+    for (int i = 0; i < kStages; i++) {
+      mbar_init(smem_u32(full + i), 1);
+      mbar_init(smem_u32(empty + i), kExpanderWarps);
+    }
     for (int i = 0; i < 2; i++) {
-      mbar_init(smem_u32(ab_full + i), kExpanderWarps * 32);
+      mbar_init(smem_u32(ab_full + i), (kExpanderWarps + kStagerWarps) * 32);
       mbar_init(smem_u32(mma_done + i), 1);
       mbar_init(smem_u32(buf_free + i), kScalerWarps);
     }
@@ -142,10 +155,99 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams 
   const int G = n_my * nsb;       // superblock steps of this CTA, tile after tile
   const int Q = n_my * npairs;    // ring fills: pairs of superblock columns, never across a tile boundary
 
-  if (warp < kScalerWarps) {
+  if (warp >= kStagerWarp0) {
+    // ================= stagers: Q8_1 activation blocks of step g -> B tiles and scales of buffer g&1 =================
+    const int te = t - kStagerWarp0 * 32;
+    const uint32_t* xq = reinterpret_cast<const uint32_t*>(p.x);
+    // activation blocks of a superblock: Npad*8 items (column b, sub-block j), item i = b*8 + j so that neighbouring
+    // threads read neighbouring 36-byte blocks; stager thread te takes items te, te + 64, ...
+    constexpr int kXI = Npad * 8 / 64;   // 2 or 4
+    uint32_t xw[kXI][9];
+    auto load_x = [&](int s) {
+#pragma unroll
+      for (int i = 0; i < kXI; i++) {
+        const int it = te + 64 * i, b = it >> 3, j = it & 7;
+#pragma unroll
+        for (int k = 0; k < 9; k++) xw[i][k] = b < P.B ? __ldcg(xq + ((size_t)b * nblk + (size_t)s * 8 + j) * 9 + k) : 0u;
+      }
+    };
+    auto store_x = [&](int buf) {
+#pragma unroll
+      for (int i = 0; i < kXI; i++) {
+        const int it = te + 64 * i, b = it >> 3, j = it & 7;
+        uint8_t* tile_j = Bs + (size_t)buf * 8 * (Npad * 32) + (size_t)j * (Npad * 32) + (b >> 3) * 128 + (b & 7) * 16;
+        *reinterpret_cast<uint4*>(tile_j) = make_uint4(xw[i][0], xw[i][1], xw[i][2], xw[i][3]);
+        *reinterpret_cast<uint4*>(tile_j + Npad * 16) = make_uint4(xw[i][4], xw[i][5], xw[i][6], xw[i][7]);
+        int qsum = 0;
+#pragma unroll
+        for (int k = 0; k < 8; k++) qsum = bk_dp4a_ss(xw[i][k], 0x01010101u, qsum);
+        const float d8 = bk_q8half_to_f32((uint16_t)(xw[i][8] & 0xffffu));
+        scs[(size_t)buf * 8 * 64 + j * 64 + b] = d8;
+        scs[(size_t)buf * 8 * 64 + j * 64 + 32 + b] = __fmul_rn(d8, (float)qsum);
+      }
+    };
+
+    bk_pdl_wait();
+    load_x(0);
+    int s = 0;
+    for (int g = 0; g < G; g++) {
+      const int buf = g & 1;
+      if (g >= 2) mbar_wait_bounded(smem_u32(buf_free + buf), (uint32_t)(((g >> 1) & 1) ^ 1), p.status);   // the scalers have finished step g-2
+      store_x(buf);
+      s = s + 1 == nsb ? 0 : s + 1;
+      if (g + 1 < G) load_x(s);   // in flight until the next step
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(smem_u32(ab_full + buf));
+    }
+  } else if (warp == kMmaWarp) {
+    // ================= MMA issue: eight MMAs, one per sub-block, into accumulator buffer g&1 =================
+    // M = 128, N = Npad, int32 accumulators, A unsigned 8-bit, B signed 8-bit, both K-major
+    const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(Npad >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+    for (int g = 0; g < G; g++) {
+      const int buf = g & 1;
+      mbar_wait_bounded(smem_u32(ab_full + buf), (uint32_t)((g >> 1) & 1), p.status);   // all 128 rows and the activations are in place
+      if (lane == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a0 = smem_u32(As + (size_t)buf * 8 * 4096);
+        const uint32_t b0 = smem_u32(Bs + (size_t)buf * 8 * (Npad * 32));
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          const uint64_t ad = umma_desc(a0 + j * 4096, 2048, 128);
+          const uint64_t bd = umma_desc(b0 + j * (Npad * 32), (uint32_t)Npad * 16, 128);
+          const uint32_t dcol = tmem + (uint32_t)(buf * 256 + j * Npad);
+          asm volatile(
+              "{\n\t.reg .pred pz;\n\tsetp.ne.b32 pz, %4, 0;\n\t"
+              "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, pz;\n\t}"
+              ::"r"(dcol), "l"(ad), "l"(bd), "r"(idesc), "r"(0u), "r"(0u)
+              : "memory");
+        }
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(mma_done + buf))
+                     : "memory");
+      }
+      __syncwarp();
+    }
+  } else if (warp == kProducerWarp) {
+    // ================= producer: fill ring stage q mod kStages with pair q (weights depend on no earlier kernel) ==========
+    for (int q = 0; q < Q; q++) {
+      if (q >= kStages) mbar_wait_bounded(smem_u32(empty + q % kStages), (uint32_t)((q / kStages - 1) & 1), p.status);
+      const int tl = q / npairs, pp = q - tl * npairs;
+      const int tile = (int)blockIdx.x + tl * (int)gridDim.x;
+      const uint32_t bytes = (uint32_t)((nsb - 2 * pp) >= 2 ? 288 : 144);
+      const int rows_here = min(kTileM, p.total_vrows - tile * kTileM);
+      const uint32_t bar = smem_u32(full + q % kStages);
+      if (lane == 0) mbar_expect_tx(bar, (uint32_t)rows_here * bytes);
+      __syncwarp();
+      const uint32_t dst0 = smem_u32(raw + (size_t)(q % kStages) * kStageBytes);
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        const int r = lane + 32 * k;
+        if (r < rows_here) bulk_g2s(dst0 + r * kRowPitch, decode_vrow(p, tile * kTileM + r).row + (size_t)pp * 288, bytes, bar);
+      }
+    }
+  } else if (warp >= kExpanderWarps) {
     // ================= scalers: f32 part of step g from accumulator buffer g&1 =================
     const int row_t = t & (kTileM - 1);   // tile row (= TMEM lane) of this thread
-    const int qd = t >> 7;                // which quarter of the columns
+    const int qd = (t >> 7) - 1;          // which quarter of the columns
     bk_pdl_wait();
     float y[NC], yc[NC];
 #pragma unroll
@@ -158,12 +260,12 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams 
       mbar_wait_bounded(smem_u32(mma_done + buf), par, p.status);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float2 dm = dd[buf * kTileM + row_t];
-      const float4* sb4 = reinterpret_cast<const float4*>(scs + (size_t)buf * 8 * 32 + qd * NC);
+      const float4* sb4 = reinterpret_cast<const float4*>(scs + (size_t)buf * 8 * 64 + qd * NC);   // d8 of this thread's columns; s8 8 float4 further
       const int2* sm_ = scm + (size_t)buf * 8 * kTileM + row_t;
       const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(buf * 256 + qd * NC);
-      float2 acc[NC];   // {accd, accm}
+      float2 accd[NC / 2], accm[NC / 2];   // columns (2i, 2i+1) side by side: one packed FMA serves both
 #pragma unroll
-      for (int c = 0; c < NC; c++) acc[c] = make_float2(0.0f, 0.0f);
+      for (int c = 0; c < NC / 2; c++) accd[c] = accm[c] = make_float2(0.0f, 0.0f);
       uint32_t r[NC], rn[NC];
       tmem_ld<NC>(taddr, r);
       tmem_wait<NC>(r);
@@ -172,11 +274,16 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams 
         if (j < 7) tmem_ld<NC>(taddr + (uint32_t)((j + 1) * Npad), rn);   // in flight during this sub-block's arithmetic
         const int2 s2 = sm_[j * kTileM];
         const float fm = __int_as_float(s2.y);
+        const float2 fm2 = make_float2(fm, fm);
 #pragma unroll
-        for (int c = 0; c < NC; c += 2) {
-          const float4 f = sb4[j * 16 + (c >> 1)];   // {d8, s8} of columns c, c+1
-          acc[c] = fma2(make_float2(f.x, f.y), make_float2(scaled_sum_f32(s2.x, (int)r[c]), fm), acc[c]);
-          acc[c + 1] = fma2(make_float2(f.z, f.w), make_float2(scaled_sum_f32(s2.x, (int)r[c + 1]), fm), acc[c + 1]);
+        for (int c = 0; c < NC; c += 4) {
+          const float4 d4 = sb4[j * 16 + (c >> 2)], s4 = sb4[j * 16 + 8 + (c >> 2)];   // d8, s8 of columns c..c+3
+          accd[c / 2] = fma2(make_float2(d4.x, d4.y),
+                             make_float2(scaled_sum_f32(s2.x, (int)r[c]), scaled_sum_f32(s2.x, (int)r[c + 1])), accd[c / 2]);
+          accd[c / 2 + 1] = fma2(make_float2(d4.z, d4.w),
+                                 make_float2(scaled_sum_f32(s2.x, (int)r[c + 2]), scaled_sum_f32(s2.x, (int)r[c + 3])), accd[c / 2 + 1]);
+          accm[c / 2] = fma2(make_float2(s4.x, s4.y), fm2, accm[c / 2]);
+          accm[c / 2 + 1] = fma2(make_float2(s4.z, s4.w), fm2, accm[c / 2 + 1]);
         }
         if (j < 7) {
           tmem_wait<NC>(rn);
@@ -188,7 +295,10 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams 
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(buf_free + buf));   // tables and accumulators of this buffer may be overwritten
 #pragma unroll
-      for (int c = 0; c < NC; c++) yc[c] = __fadd_rn(yc[c], fmaf(dm.x, acc[c].x, -__fmul_rn(dm.y, acc[c].y)));
+      for (int c = 0; c < NC; c += 2) {
+        yc[c] = __fadd_rn(yc[c], fmaf(dm.x, accd[c / 2].x, -__fmul_rn(dm.y, accm[c / 2].x)));
+        yc[c + 1] = __fadd_rn(yc[c + 1], fmaf(dm.x, accd[c / 2].y, -__fmul_rn(dm.y, accm[c / 2].y)));
+      }
       const bool last = s == nsb - 1;
       if ((s & 3) == 3 || last) {   // a chunk of four superblocks ends
 #pragma unroll
@@ -219,60 +329,9 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams 
       }
     }
   } else {
-    // ================= expanders: ring, unpacking, activation staging, MMA issue =================
-    const int te = t - kScalerWarps * 32;   // tile row of this thread
-    const bool lead = warp == kScalerWarps; // the warp that fills the ring and issues the MMAs
-    const uint32_t* xq = reinterpret_cast<const uint32_t*>(p.x);
-    // M = 128, N = Npad, int32 accumulators, A unsigned 8-bit, B signed 8-bit, both K-major
-    const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(Npad >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
-    // fill ring stage q mod kStages with pair q (weights depend on no earlier kernel)
-    auto issue_pair = [&](int q) {
-      if (q >= Q) return;
-      const int tl = q / npairs, pp = q - tl * npairs;
-      const int tile = (int)blockIdx.x + tl * (int)gridDim.x;
-      const uint32_t bytes = (uint32_t)((nsb - 2 * pp) >= 2 ? 288 : 144);
-      const int rows_here = min(kTileM, p.total_vrows - tile * kTileM);
-      const uint32_t bar = smem_u32(full + q % kStages);
-      if (lane == 0) mbar_expect_tx(bar, (uint32_t)rows_here * bytes);
-      __syncwarp();
-      const uint32_t dst0 = smem_u32(raw + (size_t)(q % kStages) * kStageBytes);
-#pragma unroll
-      for (int k = 0; k < 4; k++) {
-        const int r = lane + 32 * k;
-        if (r < rows_here) bulk_g2s(dst0 + r * kRowPitch, decode_vrow(p, tile * kTileM + r).row + (size_t)pp * 288, bytes, bar);
-      }
-    };
-    // activation blocks of a superblock: Npad*8 items (column b, sub-block j), item i = b*8 + j so that neighbouring
-    // threads read neighbouring 36-byte blocks; thread te takes items te and te + 128
-    constexpr int kXI = Npad * 8 / 128;   // 1 or 2
-    uint32_t xw[kXI][9];
-    auto load_x = [&](int s) {
-#pragma unroll
-      for (int i = 0; i < kXI; i++) {
-        const int it = te + 128 * i, b = it >> 3, j = it & 7;
-#pragma unroll
-        for (int k = 0; k < 9; k++) xw[i][k] = b < P.B ? __ldcg(xq + ((size_t)b * nblk + (size_t)s * 8 + j) * 9 + k) : 0u;
-      }
-    };
-    auto store_x = [&](int buf) {
-#pragma unroll
-      for (int i = 0; i < kXI; i++) {
-        const int it = te + 128 * i, b = it >> 3, j = it & 7;
-        uint8_t* tile_j = Bs + (size_t)buf * 8 * (Npad * 32) + (size_t)j * (Npad * 32) + (b >> 3) * 128 + (b & 7) * 16;
-        *reinterpret_cast<uint4*>(tile_j) = make_uint4(xw[i][0], xw[i][1], xw[i][2], xw[i][3]);
-        *reinterpret_cast<uint4*>(tile_j + Npad * 16) = make_uint4(xw[i][4], xw[i][5], xw[i][6], xw[i][7]);
-        int qsum = 0;
-#pragma unroll
-        for (int k = 0; k < 8; k++) qsum = bk_dp4a_ss(xw[i][k], 0x01010101u, qsum);
-        const float d8 = bk_q8half_to_f32((uint16_t)(xw[i][8] & 0xffffu));
-        scs[(size_t)buf * 8 * 32 + j * 32 + b] = make_float2(d8, __fmul_rn(d8, (float)qsum));
-      }
-    };
-
-    if (lead)
-      for (int q = 0; q < kStages; q++) issue_pair(q);
+    // ================= expanders: unpacking, scale tables =================
+    const int te = t;                 // tile row of this thread
     bk_pdl_wait();
-    load_x(0);
     int s = 0, tl = 0;
     for (int g = 0; g < G; g++) {
       const int buf = g & 1;
@@ -281,24 +340,28 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams 
       const int stage = q % kStages;
       if ((s & 1) == 0) mbar_wait_bounded(smem_u32(full + stage), (uint32_t)((q / kStages) & 1), p.status);
       if (g >= 2) mbar_wait_bounded(smem_u32(buf_free + buf), par ^ 1u, p.status);   // the scalers have finished step g-2
-      // (1) activations of this step (loaded during the previous one), then request the next step's
-      store_x(buf);
       const int s_next = s + 1 == nsb ? 0 : s + 1;
-      if (g + 1 < G) load_x(s_next);
-      // (2) header -> scale table; 4-bit quants -> unsigned int8 rows, sub-block 2p from the low nibbles of group p,
+      // header -> scale table; 4-bit quants -> unsigned int8 rows, sub-block 2p from the low nibbles of group p,
       //     2p+1 from the high nibbles
       const uint8_t* rw = raw + (size_t)stage * kStageBytes + (size_t)te * kRowPitch + (s & 1) * 144;
       const uint4 hdr = *reinterpret_cast<const uint4*>(rw);
       dd[buf * kTileM + te] = make_float2(bk_f16_to_f32((uint16_t)(hdr.x & 0xffffu)), bk_f16_to_f32((uint16_t)(hdr.x >> 16)));
       int2* sm_w = scm + (size_t)buf * 8 * kTileM + te;
       uint8_t* Ab = As + (size_t)buf * 8 * 4096 + (te >> 3) * 128 + (te & 7) * 16;
+      uint4 qv[8];
+#pragma unroll
+      for (int k = 0; k < 8; k++) qv[k] = *reinterpret_cast<const uint4*>(rw + 16 + 16 * k);
+      if ((s & 1) || s == nsb - 1) {   // this warp's rows of the stage are in registers: hand the stage back
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(empty + stage));
+      }
 #pragma unroll
       for (int pq = 0; pq < 4; pq++) {
         uint32_t sc2, mn2;
         bk_q4k_scale_min_pair(hdr.y, hdr.z, hdr.w, pq, sc2, mn2);
         sm_w[(2 * pq) * kTileM] = make_int2((int)(sc2 & 0xffu), __float_as_int((float)(mn2 & 0xffu)));
         sm_w[(2 * pq + 1) * kTileM] = make_int2((int)(sc2 >> 8), __float_as_int((float)(mn2 >> 8)));
-        const uint4 qa = *reinterpret_cast<const uint4*>(rw + 16 + pq * 32), qb = *reinterpret_cast<const uint4*>(rw + 32 + pq * 32);
+        const uint4 qa = qv[2 * pq], qb = qv[2 * pq + 1];
         uint8_t* A0 = Ab + (size_t)(2 * pq) * 4096;
         *reinterpret_cast<uint4*>(A0) = make_uint4(qa.x & 0x0f0f0f0fu, qa.y & 0x0f0f0f0fu, qa.z & 0x0f0f0f0fu, qa.w & 0x0f0f0f0fu);
         *reinterpret_cast<uint4*>(A0 + 2048) = make_uint4(qb.x & 0x0f0f0f0fu, qb.y & 0x0f0f0f0fu, qb.z & 0x0f0f0f0fu, qb.w & 0x0f0f0f0fu);
@@ -309,31 +372,6 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams 
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads shared memory through the async proxy
       mbar_arrive(smem_u32(ab_full + buf));
-      if (lead) {
-        mbar_wait_bounded(smem_u32(ab_full + buf), par, p.status);   // all 128 rows and the activations are in place
-        // (3) eight MMAs, one per sub-block, into accumulator buffer g&1
-        if (lane == 0) {
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a0 = smem_u32(As + (size_t)buf * 8 * 4096);
-          const uint32_t b0 = smem_u32(Bs + (size_t)buf * 8 * (Npad * 32));
-#pragma unroll
-          for (int j = 0; j < 8; j++) {
-            const uint64_t ad = umma_desc(a0 + j * 4096, 2048, 128);
-            const uint64_t bd = umma_desc(b0 + j * (Npad * 32), (uint32_t)Npad * 16, 128);
-            const uint32_t dcol = tmem + (uint32_t)(buf * 256 + j * Npad);
-            asm volatile(
-                "{\n\t.reg .pred pz;\n\tsetp.ne.b32 pz, %4, 0;\n\t"
-                "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, pz;\n\t}"
-                ::"r"(dcol), "l"(ad), "l"(bd), "r"(idesc), "r"(0u), "r"(0u)
-                : "memory");
-          }
-          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(mma_done + buf))
-                       : "memory");
-        }
-        __syncwarp();
-        // the ring stage is free once every row has been unpacked from both of its superblock columns
-        if ((s & 1) || s == nsb - 1) issue_pair(q + kStages);
-      }
       s = s_next;
       if (s == 0) tl++;
     }
@@ -349,7 +387,7 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams 
 }
 
 size_t umma_smem_bytes() {
-  return (size_t)kStages * kStageBytes + 2 * 8 * 4096 + 2 * 8 * 32 * 32 + 2 * 8 * 32 * 8 + 2 * 8 * kTileM * 8 + 2 * kTileM * 8 + 128;
+  return (size_t)kStages * kStageBytes + 2 * 8 * 4096 + 2 * 8 * 32 * 32 + 2 * 8 * 64 * 4 + 2 * 8 * kTileM * 8 + 2 * kTileM * 8 + 160;
 }
 
 }  // namespace
