@@ -334,7 +334,9 @@ __global__ void quant_q8_1_kernel(const void* x, int K, int B, uint8_t* out) {
 int32_t bk_gemv_mma_launch(void* params, int K, int B, int vrows, bool has_swiglu, int* ctas_out);  // bk_gemv_mma.cu
 int32_t bk_gemv_umma_launch(void* params, int B);                                                   // bk_gemv_umma.cu
 static bool g_umma_group = false;   // the launch being set up is one group of <= 32 columns of the dense tile path
-static int g_tile_min_rows = 4096;  // BK_GEMV_ORDER_AUTO takes the tile path from this many launch rows on (bkTuneTileMinRows)
+// BK_GEMV_ORDER_AUTO takes the tile path from g_tile_min_rows launch rows on, and from g_tile_min_rows_cut rows on when K is
+// at least 2048 (such a launch has few 128-row tiles and is cut along K over several thread blocks); bkTuneTileMinRows
+static int g_tile_min_rows = 4096, g_tile_min_rows_cut = 1024;
 
 static int g_tune_warps = 0, g_tune_rows = 0, g_tune_depth = 0;
 
@@ -356,12 +358,13 @@ int32_t bk_gemv_launch_tp(const bkGemvArgs& a, const BkPush* push, const BkReduc
   // From 16 columns on, ready-made Q8_1 blocks go to the dense tile kernel (tcgen05 int8 MMA, bk_gemv_umma.cu): the
   // weights are streamed once per 32 columns.  Its f32 order differs from the batch <= 8 kernels' (see there);
   // order = BK_GEMV_ORDER_LANES keeps the columns on those kernels.
-  // A launch of few rows has too few 128-row tiles to fill the machine and its weights stay in L2 between groups of
-  // 8 columns anyway, so AUTO sends it to the batch <= 8 kernels; the rule depends on the shapes only.
+  // A launch of very few rows (or few rows and a short K) has too few 128-row tiles to fill the machine and its
+  // weights stay in L2 between groups of 8 columns anyway, so AUTO sends it to the batch <= 8 kernels; the rule
+  // depends on the shapes only.
   int launch_rows = 0;
   for (int i = 0; i < a.n_segs && i < 4; i++) launch_rows += a.segs[i].n_rows * (a.segs[i].epilogue == BK_EPI_SWIGLU ? 2 : 1);
   const bool tile_path = !g_umma_group && a.B >= 16 && a.prologue == BK_PRO_Q8 && !push && !reduce && !g_view &&
-                         (a.order == BK_GEMV_ORDER_TILE || (a.order == BK_GEMV_ORDER_AUTO && launch_rows >= g_tile_min_rows));
+                         (a.order == BK_GEMV_ORDER_TILE || (a.order == BK_GEMV_ORDER_AUTO && bk_gemv_auto_tile(launch_rows, a.K)));
   if (a.B > 8 && !g_umma_group) {
     // More than 8 columns without the tile path: groups of 8 on the mma.sync kernel, one launch per group (the weights
     // of the later groups come from L2 when they fit there).
@@ -632,7 +635,7 @@ int32_t bk_gemv_launch_tp(const bkGemvArgs& a, const BkPush* push, const BkReduc
   return tp ? launch_gemv<2, gemv_gmax(2), true>(p, grid, threads, smem) : launch_gemv<2, gemv_gmax(2), false>(p, grid, threads, smem);
 }
 
-int bk_gemv_tile_min_rows() { return g_tile_min_rows; }
+bool bk_gemv_auto_tile(int rows, int K) { return rows >= g_tile_min_rows || (rows >= g_tile_min_rows_cut && K >= 2048); }
 
 extern "C" {
 
@@ -647,6 +650,7 @@ int32_t bkTuneGemvRing(int32_t warps, int32_t rows_per_group, int32_t max_depth)
 int32_t bkTuneTileMinRows(int32_t rows) {
   BK_ARG(rows >= 0, "bkTuneTileMinRows: rows=%d", rows);
   g_tile_min_rows = rows == 0 ? 4096 : rows;
+  g_tile_min_rows_cut = rows == 0 ? 1024 : rows;
   return BK_OK;
 }
 

@@ -29,29 +29,56 @@
 // That f32 order ("tile order": per (row, column) one chain per chunk of four superblocks, chunks added in order) is
 // fixed and mirrored by the CPU checker; it differs from the batch <= 8 kernels' lane / butterfly order by a few ulp.
 //
-// Single CTA per tile, no cluster, no multicast, no tensor maps.  Every wait is bounded; TMEM is released on every
+// A launch of few tiles (fewer than half the SMs) is cut along K: thread block (tile, part) runs a contiguous range of
+// whole chunks and leaves each chunk's partial sums in a scratch buffer; the block that arrives last at the tile's
+// counter adds the chunks in ascending order -- the same chain as an uncut launch -- and runs the epilogue.
+//
+// Weight feed: when every segment's row count is a multiple of 32 (all shapes of the model) a stage is filled with one
+// tiled TMA load per 32-row box and superblock column (cp.async.bulk.tensor.2d through a tensor map of the weight
+// matrix; 8 instructions per stage instead of 128 row copies -- the row copies cap the feed at about 7 GB/s per SM
+// and cost 5 us before the first stage has landed).  A SwiGLU launch then keeps its 64 gate rows in tile rows 0..63
+// and the 64 up rows in 64..127 (boxes are contiguous rows of one matrix), and the epilogue passes the up values to
+// the gate rows' threads through shared memory.  Other shapes keep the per-row copies.
+//
+// No cluster, no multicast.  Every wait is bounded; TMEM is released on every
 // path out of the kernel.
+#include <cuda.h>   // CUtensorMap and the types of its encoder; the encoder itself is looked up at run time
+
 #include "bk_gemv_shared.cuh"
 
 namespace {
 
 constexpr int kTileM = 128;
-constexpr int kExpanderWarps = 4;   // warps 0..3 (the oldest warps, which the scheduler prefers): thread <-> tile row
-constexpr int kScalerWarps = 16;    // warps 4..19: warp w reads TMEM lanes 32*(w mod 4)..+31, columns of quarter (w - 4) / 4
-constexpr int kProducerWarp = kExpanderWarps + kScalerWarps;   // warp 20 keeps the weight ring filled
-constexpr int kMmaWarp = kProducerWarp + 1;                    // warp 21 issues the MMAs
-constexpr int kStagerWarp0 = kMmaWarp + 1;                     // warps 22, 23 stage the activation blocks
+// The supporting roles come first: their work per step is short but the scalers wait for it
+constexpr int kExpanderWarps = 4;   // warps 0..3: thread <-> tile row
+constexpr int kStagerWarp0 = 4;     // warps 4, 5 stage the activation blocks
 constexpr int kStagerWarps = 2;
-constexpr int kUT = (kStagerWarp0 + kStagerWarps) * 32;
+constexpr int kProducerWarp = 6;    // keeps the weight ring filled
+constexpr int kMmaWarp = 7;         // issues the MMAs
+constexpr int kScalerWarp0 = 8;     // warps 8..23: warp w reads TMEM lanes 32*(w mod 4)..+31, columns of quarter (w - 8) / 4
+constexpr int kScalerWarps = 16;
+constexpr int kUT = (kScalerWarp0 + kScalerWarps) * 32;
 constexpr int kStages = 3;          // ring stages, two superblock columns each
 constexpr int kRowPitch = 2 * 144 + 16;   // bytes between rows of a stage: 76 words, so 16-byte reads of 8 rows hit 8 bank groups
 constexpr int kStageBytes = kTileM * kRowPitch;
+constexpr int kPlaneBytes = kTileM * 144;   // tensor-map feed: a stage is two planes [128 rows][144 bytes], one per superblock column
 constexpr int kTmemCols = 512;
+
+// dynamic shared memory without the SwiGLU exchange buffer, which follows it: ring, A tiles (2 x 8 x 4 KB), B tiles,
+// column scales, row scale table, row {d, dmin}, barriers and flags
+__host__ __device__ constexpr size_t umma_smem_core_bytes() {
+  return (size_t)kStages * kStageBytes + 2 * 8 * 4096 + 2 * 8 * 32 * 32 + 2 * 8 * 64 * 4 + 2 * 8 * kTileM * 8 + 2 * kTileM * 8 + 160;
+}
 
 struct UmmaParams {
   GemvParams g;   // K, segments, total_vrows, x = Q8_1 blocks [B][K/32][36], status
   int B;          // activation columns of this launch, 1..32
   int Npad;       // MMA N: 16 or 32
+  int use_maps;   // weights are fed by tiled TMA loads through maps[] (segment i -> maps[i]; the up matrix of a SwiGLU launch -> maps[4])
+  int ksplit;     // > 1: every tile is cut along K over ksplit thread blocks (launches of few tiles)
+  float* scratch; // ksplit > 1: per-chunk partial sums [tile][chunk][32 columns][128 rows]
+  int* counters;  // ksplit > 1: arrivals per tile; the last block to arrive adds the chunks in order and resets the count
+  CUtensorMap maps[5];   // use_maps: uint8 [n_rows][row bytes], box 32 rows x 144 bytes
 };
 
 BK_DEVINL uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
@@ -107,7 +134,7 @@ BK_DEVINL void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared:
 
 // NC: accumulator columns per scaler thread (MMA N / 4): 4 or 8
 template <int NC>
-__global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams P) {
+__global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_constant__ UmmaParams P) {
   bk_pdl_trigger();
   const GemvParams& p = P.g;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -124,9 +151,12 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams 
   uint64_t* mma_done = ab_full + 2;                                // [2] the step's MMAs have completed
   uint64_t* buf_free = mma_done + 2;                               // [2] the scalers are done with a buffer (16 arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(buf_free + 2);
+  int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);   // K cut: this block arrived last at its tile's counter
+  float* xchg = reinterpret_cast<float*>(smem + umma_smem_core_bytes());   // [32 columns][64]: up values of a SwiGLU tile (tensor-map feed)
+  const bool swiglu_halves = P.use_maps && p.segs[0].epi == BK_EPI_SWIGLU;   // tile rows 0..63 gate, 64..127 up
 
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
-  const int K = p.K, nsb = K / 256, nblk = K / 32, npairs = (nsb + 1) / 2;
+  const int K = p.K, nsb = K / 256, nblk = K / 32;
 
   if (t == 0) {
     for (int i = 0; i < kStages; i++) {
@@ -151,11 +181,24 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams 
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
   const int n_tiles = (p.total_vrows + kTileM - 1) / kTileM;
-  const int n_my = (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;   // tiles of this CTA
-  const int G = n_my * nsb;       // superblock steps of this CTA, tile after tile
+  const int n_chunks = (nsb + 3) / 4;
+  // this CTA's tiles tile0, tile0 + tile_step, ... (n_my of them) and, of each, superblocks [s_begin, s_begin + n_s)
+  int tile0 = (int)blockIdx.x, tile_step = (int)gridDim.x, s_begin = 0, n_s = nsb;
+  int n_my = (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  if (P.ksplit > 1) {
+    const int part = (int)blockIdx.x % P.ksplit;
+    const int c0 = part * n_chunks / P.ksplit, c1 = (part + 1) * n_chunks / P.ksplit;   // whole chunks, at least one
+    tile0 = (int)blockIdx.x / P.ksplit;
+    tile_step = 0;
+    n_my = 1;
+    s_begin = 4 * c0;
+    n_s = min(nsb, 4 * c1) - s_begin;
+  }
+  const int npairs = (n_s + 1) / 2;
+  const int G = n_my * n_s;       // superblock steps of this CTA, tile after tile
   const int Q = n_my * npairs;    // ring fills: pairs of superblock columns, never across a tile boundary
 
-  if (warp >= kStagerWarp0) {
+  if (warp >= kStagerWarp0 && warp < kStagerWarp0 + kStagerWarps) {
     // ================= stagers: Q8_1 activation blocks of step g -> B tiles and scales of buffer g&1 =================
     const int te = t - kStagerWarp0 * 32;
     const uint32_t* xq = reinterpret_cast<const uint32_t*>(p.x);
@@ -188,14 +231,14 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams 
     };
 
     bk_pdl_wait();
-    load_x(0);
+    load_x(s_begin);
     int s = 0;
     for (int g = 0; g < G; g++) {
       const int buf = g & 1;
       if (g >= 2) mbar_wait_bounded(smem_u32(buf_free + buf), (uint32_t)(((g >> 1) & 1) ^ 1), p.status);   // the scalers have finished step g-2
       store_x(buf);
-      s = s + 1 == nsb ? 0 : s + 1;
-      if (g + 1 < G) load_x(s);   // in flight until the next step
+      s = s + 1 == n_s ? 0 : s + 1;
+      if (g + 1 < G) load_x(s_begin + s);   // in flight until the next step
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(smem_u32(ab_full + buf));
     }
@@ -231,23 +274,53 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams 
     for (int q = 0; q < Q; q++) {
       if (q >= kStages) mbar_wait_bounded(smem_u32(empty + q % kStages), (uint32_t)((q / kStages - 1) & 1), p.status);
       const int tl = q / npairs, pp = q - tl * npairs;
-      const int tile = (int)blockIdx.x + tl * (int)gridDim.x;
-      const uint32_t bytes = (uint32_t)((nsb - 2 * pp) >= 2 ? 288 : 144);
+      const int tile = tile0 + tl * tile_step;
+      const uint32_t bytes = (uint32_t)((n_s - 2 * pp) >= 2 ? 288 : 144);
       const int rows_here = min(kTileM, p.total_vrows - tile * kTileM);
       const uint32_t bar = smem_u32(full + q % kStages);
+      const uint32_t dst0 = smem_u32(raw + (size_t)(q % kStages) * kStageBytes);
+      if (P.use_maps) {
+        // lane l < 8: 32-row box l & 3 of the tile, superblock column l >> 2 of the pair
+        const int k = lane & 3, sbi = lane >> 2;
+        bool valid = lane < 8 && (uint32_t)sbi * 144 < bytes;
+        int mi = 0, row0 = 0;
+        if (swiglu_halves) {   // boxes 0, 1: gate rows tile*64 + 32k; boxes 2, 3: the same rows of the up matrix
+          row0 = tile * 64 + 32 * (k & 1);
+          mi = k < 2 ? 0 : 4;
+          valid = valid && row0 < p.segs[0].n_rows;
+        } else {
+          const int v0 = tile * kTileM + 32 * k;
+          valid = valid && v0 < p.total_vrows;
+#pragma unroll
+          for (int i = 1; i < 4; i++)
+            if (i < p.n_segs && v0 >= p.segs[i].vrow_begin) mi = i;
+          row0 = v0 - p.segs[mi].vrow_begin;
+        }
+        const unsigned n_valid = __popc(__ballot_sync(0xffffffffu, valid));
+        if (lane == 0) mbar_expect_tx(bar, n_valid * 32u * 144u);
+        __syncwarp();
+        if (valid) {
+          const int x = (s_begin + 2 * pp + sbi) * 144;
+          asm volatile(
+              "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+              ::"r"(dst0 + (uint32_t)(sbi * kPlaneBytes + 32 * k * 144)), "l"(reinterpret_cast<uint64_t>(&P.maps[mi])), "r"(x), "r"(row0),
+              "r"(bar)
+              : "memory");
+        }
+        continue;
+      }
       if (lane == 0) mbar_expect_tx(bar, (uint32_t)rows_here * bytes);
       __syncwarp();
-      const uint32_t dst0 = smem_u32(raw + (size_t)(q % kStages) * kStageBytes);
 #pragma unroll
       for (int k = 0; k < 4; k++) {
         const int r = lane + 32 * k;
-        if (r < rows_here) bulk_g2s(dst0 + r * kRowPitch, decode_vrow(p, tile * kTileM + r).row + (size_t)pp * 288, bytes, bar);
+        if (r < rows_here) bulk_g2s(dst0 + r * kRowPitch, decode_vrow(p, tile * kTileM + r).row + (size_t)s_begin * 144 + (size_t)pp * 288, bytes, bar);
       }
     }
-  } else if (warp >= kExpanderWarps) {
+  } else if (warp >= kScalerWarp0) {
     // ================= scalers: f32 part of step g from accumulator buffer g&1 =================
     const int row_t = t & (kTileM - 1);   // tile row (= TMEM lane) of this thread
-    const int qd = (t >> 7) - 1;          // which quarter of the columns
+    const int qd = (t >> 7) - kScalerWarp0 / 4;   // which quarter of the columns
     bk_pdl_wait();
     float y[NC], yc[NC];
 #pragma unroll
@@ -299,16 +372,63 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams 
         yc[c] = __fadd_rn(yc[c], fmaf(dm.x, accd[c / 2].x, -__fmul_rn(dm.y, accm[c / 2].x)));
         yc[c + 1] = __fadd_rn(yc[c + 1], fmaf(dm.x, accd[c / 2].y, -__fmul_rn(dm.y, accm[c / 2].y)));
       }
-      const bool last = s == nsb - 1;
+      const bool last = s == n_s - 1;
+      const int tile = tile0 + tl * tile_step;
       if ((s & 3) == 3 || last) {   // a chunk of four superblocks ends
+        if (P.ksplit > 1) {         // its partial sums go to the scratch buffer; the last block of the tile adds them up
+          float* dst = P.scratch + (((size_t)tile * n_chunks + ((s_begin + s) >> 2)) * 32 + qd * NC) * kTileM + row_t;
 #pragma unroll
-        for (int c = 0; c < NC; c++) {
-          y[c] = __fadd_rn(y[c], yc[c]);
-          yc[c] = 0.0f;
+          for (int c = 0; c < NC; c++) {
+            __stcg(dst + c * kTileM, yc[c]);
+            yc[c] = 0.0f;
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < NC; c++) {
+            y[c] = __fadd_rn(y[c], yc[c]);
+            yc[c] = 0.0f;
+          }
         }
       }
-      if (last) {   // fused epilogue of the tile; uniform over the warp
-        const int vrow = ((int)blockIdx.x + tl * (int)gridDim.x) * kTileM + row_t;
+      bool merge = true;
+      if (last && P.ksplit > 1) {
+        __threadfence();                                   // this thread's partial sums before the arrival
+        asm volatile("bar.sync 1, %0;" ::"n"(kScalerWarps * 32) : "memory");
+        if (t == kScalerWarp0 * 32) {
+          const int old = atomicAdd(P.counters + tile, 1);
+          if (old == P.ksplit - 1) P.counters[tile] = 0;   // everyone has arrived: ready for the next launch
+          *last_flag = old == P.ksplit - 1;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kScalerWarps * 32) : "memory");
+        merge = *last_flag != 0;
+        if (merge) {
+          __threadfence();
+          const float* src = P.scratch + (((size_t)tile * n_chunks) * 32 + qd * NC) * kTileM + row_t;
+          for (int ch = 0; ch < n_chunks; ch++)
+#pragma unroll
+            for (int c = 0; c < NC; c++) y[c] = __fadd_rn(y[c], __ldcg(src + ((size_t)ch * 32 + c) * kTileM));
+        }
+      }
+      if (last && merge && swiglu_halves) {   // gate rows in tile rows 0..63, their up rows 64 further on (other warps)
+        if (row_t >= 64) {
+#pragma unroll
+          for (int c = 0; c < NC; c++) xchg[(qd * NC + c) * 64 + row_t - 64] = y[c];
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kScalerWarps * 32) : "memory");
+        const SegDev& sg = p.segs[0];
+        const int n = tile * 64 + row_t;
+#pragma unroll
+        for (int c = 0; c < NC; c++) {
+          const int b = qd * NC + c;
+          if (row_t < 64 && b < P.B && n < sg.n_rows)
+            store_epilogue<false>(p, sg, (size_t)b * sg.ld_out + sg.col_off + n, y[c], xchg[b * 64 + row_t]);
+          y[c] = 0.0f;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kScalerWarps * 32) : "memory");   // the values have been read: the next tile may overwrite them
+        s = 0;
+        tl++;
+      } else if (last && merge) {   // fused epilogue of the tile; uniform over the CTA
+        const int vrow = tile * kTileM + row_t;
         const bool have_row = vrow < p.total_vrows;
         VRow vr = {nullptr, 0, 0};
         if (have_row) vr = decode_vrow(p, vrow);
@@ -340,10 +460,11 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams 
       const int stage = q % kStages;
       if ((s & 1) == 0) mbar_wait_bounded(smem_u32(full + stage), (uint32_t)((q / kStages) & 1), p.status);
       if (g >= 2) mbar_wait_bounded(smem_u32(buf_free + buf), par ^ 1u, p.status);   // the scalers have finished step g-2
-      const int s_next = s + 1 == nsb ? 0 : s + 1;
+      const int s_next = s + 1 == n_s ? 0 : s + 1;
       // header -> scale table; 4-bit quants -> unsigned int8 rows, sub-block 2p from the low nibbles of group p,
       //     2p+1 from the high nibbles
-      const uint8_t* rw = raw + (size_t)stage * kStageBytes + (size_t)te * kRowPitch + (s & 1) * 144;
+      const uint8_t* rw = raw + (size_t)stage * kStageBytes +
+                          (P.use_maps ? (size_t)(s & 1) * kPlaneBytes + (size_t)te * 144 : (size_t)te * kRowPitch + (s & 1) * 144);
       const uint4 hdr = *reinterpret_cast<const uint4*>(rw);
       dd[buf * kTileM + te] = make_float2(bk_f16_to_f32((uint16_t)(hdr.x & 0xffffu)), bk_f16_to_f32((uint16_t)(hdr.x >> 16)));
       int2* sm_w = scm + (size_t)buf * 8 * kTileM + te;
@@ -351,7 +472,7 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams 
       uint4 qv[8];
 #pragma unroll
       for (int k = 0; k < 8; k++) qv[k] = *reinterpret_cast<const uint4*>(rw + 16 + 16 * k);
-      if ((s & 1) || s == nsb - 1) {   // this warp's rows of the stage are in registers: hand the stage back
+      if ((s & 1) || s == n_s - 1) {   // this warp's rows of the stage are in registers: hand the stage back
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(empty + stage));
       }
@@ -386,8 +507,35 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const UmmaParams 
   }
 }
 
-size_t umma_smem_bytes() {
-  return (size_t)kStages * kStageBytes + 2 * 8 * 4096 + 2 * 8 * 32 * 32 + 2 * 8 * 64 * 4 + 2 * 8 * kTileM * 8 + 2 * kTileM * 8 + 160;
+size_t umma_smem_bytes() { return umma_smem_core_bytes() + 32 * 64 * sizeof(float); }
+
+// cuTensorMapEncodeTiled, looked up through the runtime so that the library needs no link against the driver
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool looked = false;
+  if (!looked) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qr) == cudaSuccess && qr == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    looked = true;
+  }
+  return fn;
+}
+
+// uint8 matrix [n_rows][row_bytes], box = 32 rows x 144 bytes (one superblock column of 32 rows), no swizzle
+bool encode_weight_map(CUtensorMap* m, const uint8_t* W, int n_rows, size_t row_bytes) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn || (reinterpret_cast<uintptr_t>(W) & 15) || row_bytes % 16) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)n_rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+  const cuuint32_t box[2] = {144, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(W), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 }  // namespace
@@ -400,6 +548,23 @@ int32_t bk_gemv_umma_launch(void* params, int B) {
   BK_ARG(B >= 1 && B <= 32, "tile GEMV: %d columns per launch (1..32)", B);
   P.B = B;
   P.Npad = B <= 16 ? 16 : 32;
+  // tensor-map feed: whole rows in memory, 32-row boxes that never straddle two segments, and a SwiGLU segment alone
+  {
+    const GemvParams& g = P.g;
+    bool ok = g.row_stride == 0 && g.row_off == 0;
+    bool any_swiglu = false;
+    for (int i = 0; i < g.n_segs; i++) {
+      ok = ok && g.segs[i].n_rows % 32 == 0;
+      any_swiglu = any_swiglu || g.segs[i].epi == BK_EPI_SWIGLU;
+    }
+    ok = ok && (!any_swiglu || g.n_segs == 1);
+    const size_t row_bytes = (size_t)(g.K / 256) * 144;
+    for (int i = 0; ok && i < g.n_segs; i++) {
+      ok = encode_weight_map(&P.maps[i], g.segs[i].W, g.segs[i].n_rows, row_bytes);
+      if (ok && g.segs[i].epi == BK_EPI_SWIGLU) ok = encode_weight_map(&P.maps[4], g.segs[i].W2, g.segs[i].n_rows, row_bytes);
+    }
+    P.use_maps = ok ? 1 : 0;
+  }
   static bool configured = false;
   const size_t smem = umma_smem_bytes();
   if (!configured) {
@@ -408,7 +573,17 @@ int32_t bk_gemv_umma_launch(void* params, int B) {
     configured = true;
   }
   const int tiles = (P.g.total_vrows + kTileM - 1) / kTileM;
-  const int grid = tiles < c.sm_count ? tiles : c.sm_count;
+  int grid = tiles < c.sm_count ? tiles : c.sm_count;
+  // few tiles: cut each along K into parts of whole chunks (four superblocks), as many as there are SMs for
+  const int n_chunks = (P.g.K / 256 + 3) / 4;
+  P.ksplit = 1;
+  P.scratch = c.tile_scratch;
+  P.counters = c.tile_counters;
+  if (tiles * 2 <= c.sm_count && n_chunks >= 2 && tiles <= 256 &&
+      (size_t)tiles * n_chunks * 32 * kTileM * sizeof(float) <= c.tile_scratch_bytes) {
+    P.ksplit = c.sm_count / tiles < n_chunks ? c.sm_count / tiles : n_chunks;
+    if (P.ksplit > 1) grid = tiles * P.ksplit;
+  }
   if (P.Npad == 16) BK_CUDA(bk_launch_pdl(gemv_q4k_umma_kernel<4>, dim3(grid), dim3(kUT), smem, P));
   else BK_CUDA(bk_launch_pdl(gemv_q4k_umma_kernel<8>, dim3(grid), dim3(kUT), smem, P));
   BK_CHECK_LAUNCH();

@@ -28,6 +28,9 @@ struct BkContext {
   int spin_limit = 0;                 // polls a bounded device-side wait may take (bkSetSpinLimit; 0 = built-in limits)
   int step_barrier_mode = 1;          // grid barrier of the persistent step kernel: 0 one word per CTA, 1 one counter (faster, measured)
   int* d_status = nullptr;           // device word set by kernels whose bounded waits gave up
+  float* tile_scratch = nullptr;     // dense tile GEMV cut along K: per-chunk partial sums [tile][chunk][32 columns][128 rows]
+  int* tile_counters = nullptr;      // ... and one arrival counter per tile (self-resetting)
+  size_t tile_scratch_bytes = 0;
   float* gemv_carry = nullptr;       // class accumulators handed from one K part of a split GEMV to the next
   size_t gemv_carry_bytes = 0;
   char err[512] = {0};
@@ -102,7 +105,7 @@ struct BkReduce {
 
 // internal launchers shared between translation units
 bool bk_gemv_mma_fits(int K, int B);   // whether the batch-3..8 tensor-core GEMV can hold this K (else column pairs)
-int bk_gemv_tile_min_rows();           // launch rows from which BK_GEMV_ORDER_AUTO takes the dense tile path
+bool bk_gemv_auto_tile(int rows, int K);   // whether BK_GEMV_ORDER_AUTO sends a launch of these shapes (>= 16 columns) to the dense tile path
 int32_t bk_gemv_launch(const bkGemvArgs& a);
 // same with the fused exchange: push (may be null) for BK_EPI_PUSH_F32 segments, reduce (may be null) for
 // BK_PRO_REDUCE_RMSNORM; ctas_out (may be null) receives the number of CTAs that will signal arrival

@@ -279,11 +279,11 @@ int32_t enqueue_step(Model& m, int parity, bool host_tokens = false) {
   // the staged layout serves groups of 2..8 columns on the tensor-core kernel; a last group of one column (B = 9, 17, ...)
   // or a K too wide for that kernel reads plain blocks instead
   // from 16 sequences on (one GPU) the projections of many rows run on the dense tile kernel, which reads plain blocks
-  // (the library's rule for BK_GEMV_ORDER_AUTO: launch rows >= bk_gemv_tile_min_rows())
+  // (the library's rule for BK_GEMV_ORDER_AUTO, bk_gemv_auto_tile)
   const bool tile_path = B >= 16 && m.tp == 1;
   const int gemv_order = tile_path ? BK_GEMV_ORDER_AUTO : BK_GEMV_ORDER_LANES;
   auto staged_ok = [&](int K, int rows) {
-    return !(tile_path && rows >= bk_gemv_tile_min_rows()) && bk_gemv_mma_fits(K, B < 8 ? B : 8) && !(B > 8 && B % 8 == 1);
+    return !(tile_path && bk_gemv_auto_tile(rows, K)) && bk_gemv_mma_fits(K, B < 8 ? B : 8) && !(B > 8 && B % 8 == 1);
   };
   // Input of a projection: fused RMSNorm/quantise prologue at batch 1; at batch >= 2 one small launch
   // normalises and quantises the rows once and every CTA of the projection just copies the blocks.

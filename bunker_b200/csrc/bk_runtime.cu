@@ -41,6 +41,10 @@ int32_t bkInit(int32_t device) {
   BK_CUDA(cudaStreamCreateWithFlags(&g_ctx.stream, cudaStreamNonBlocking));
   BK_CUDA(cudaMalloc((void**)&g_ctx.d_status, sizeof(int)));
   BK_CUDA(cudaMemsetAsync(g_ctx.d_status, 0, sizeof(int), g_ctx.stream));   // ordered on the library stream, then awaited
+  g_ctx.tile_scratch_bytes = (size_t)24 << 20;
+  BK_CUDA(cudaMalloc((void**)&g_ctx.tile_scratch, g_ctx.tile_scratch_bytes));
+  BK_CUDA(cudaMalloc((void**)&g_ctx.tile_counters, 256 * sizeof(int)));
+  BK_CUDA(cudaMemsetAsync(g_ctx.tile_counters, 0, 256 * sizeof(int), g_ctx.stream));
   BK_CUDA(cudaStreamSynchronize(g_ctx.stream));
   g_ctx.launches = 0;
   g_ctx.ready = true;
@@ -51,6 +55,12 @@ int32_t bkShutdown(void) {
   if (!g_ctx.ready) return BK_OK;
   cudaStreamSynchronize(g_ctx.stream);
   cudaStreamDestroy(g_ctx.stream);
+  cudaFree(g_ctx.d_status);
+  cudaFree(g_ctx.tile_scratch);
+  cudaFree(g_ctx.tile_counters);
+  g_ctx.d_status = nullptr;
+  g_ctx.tile_scratch = nullptr;
+  g_ctx.tile_counters = nullptr;
   g_ctx.stream = nullptr;
   g_ctx.ready = false;
   return BK_OK;

@@ -103,8 +103,9 @@ BK_API uint64_t bkStagedBytes(int32_t K, int32_t B);
 /* f32 accumulation order of a row's result (the integer block dots are exact either way).  LANES: the order of the
  * batch <= 8 kernels (64-weight units over 32 lanes, butterfly).  TILE: from 16 columns on, with BK_PRO_Q8 input, the
  * dense tile kernel (tcgen05 int8 MMA, accumulators in tensor memory) and its order: one chain per (row, column),
- * sub-blocks then superblocks ascending; below 16 columns TILE means LANES.  AUTO: TILE when the launch has at least
- * 4096 rows (all segments together), else LANES -- a rule of the shapes alone, so a host can mirror it.  Both orders are
+ * sub-blocks ascending, superblocks ascending within a chunk of four, chunks ascending; below 16 columns TILE means
+ * LANES.  AUTO: TILE when the launch has at least 4096 rows (all segments together, a SwiGLU pair counting twice), or
+ * at least 1024 rows and K >= 2048; else LANES -- a rule of the shapes alone, so a host can mirror it.  Both orders are
  * within a few ulp of each other and of the reference's f32 accumulation (prototypes/decode.ts:141-145). */
 #define BK_GEMV_ORDER_AUTO 0
 #define BK_GEMV_ORDER_LANES 1

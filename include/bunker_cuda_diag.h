@@ -26,7 +26,7 @@ BK_API int32_t bkTraceDisable(void);
  * warp group, maximum ring depth) for launches whose rows do not fit in shared memory at once; warps = 0 restores the
  * library's own choice. */
 BK_API int32_t bkTuneGemvRing(int32_t warps, int32_t rows_per_group, int32_t max_depth);
-/* Row count from which BK_GEMV_ORDER_AUTO takes the dense tile path (default 4096; 0 restores it).  Lets a small test
+/* Row count from which BK_GEMV_ORDER_AUTO takes the dense tile path (default 4096, or 1024 when K >= 2048; 0 restores both).  Lets a small test
  * model run every GEMV of its step on the tile kernel.  Captured graphs keep the choice they were captured with. */
 BK_API int32_t bkTuneTileMinRows(int32_t rows);
 /* Per-phase timeline of the persistent step kernel.  While enabled, every launch of that kernel stamps %globaltimer

@@ -13,10 +13,11 @@ from . import oracle as O
 
 class OracleModel:
     def __init__(self, cfg, weights: dict, batch: int, split_len: int, attn_warps: int = 8, tp: int = 1,
-                 gemv_order: str | None = None, tile_min_rows: int = 4096):
+                 gemv_order: str | None = None, tile_min_rows: int | None = None):
         """gemv_order: "lanes" (the batch <= 8 kernels: units over lanes, butterfly) or "tile" (the dense tile path
-        for every launch of at least tile_min_rows rows, all its segments together -- the library's rule for
-        BK_GEMV_ORDER_AUTO); None picks what the library picks for this batch (tile from 16 sequences on, on one GPU)."""
+        for every launch of at least 4096 rows, all its segments together, or at least 1024 rows and K >= 2048 -- the
+        library's rule for BK_GEMV_ORDER_AUTO; tile_min_rows replaces both row thresholds, as bkTuneTileMinRows does);
+        None picks what the library picks for this batch (tile from 16 sequences on, on one GPU)."""
         self.cfg, self.w, self.B, self.split_len, self.W, self.tp = cfg, weights, batch, split_len, attn_warps, tp
         self.gemv_order = gemv_order or ("tile" if (batch >= 16 and tp == 1) else "lanes")
         self.tile_min_rows = tile_min_rows
@@ -40,7 +41,8 @@ class OracleModel:
 
     def _gemv(self, name: str, N: int, K: int, xq: np.ndarray, launch_rows: int) -> np.ndarray:
         """launch_rows: rows of the whole launch this projection is a segment of (it decides the f32 order)."""
-        tile = self.gemv_order == "tile" and launch_rows >= self.tile_min_rows
+        big, cut = (4096, 1024) if self.tile_min_rows is None else (self.tile_min_rows, self.tile_min_rows)
+        tile = self.gemv_order == "tile" and (launch_rows >= big or (launch_rows >= cut and K >= 2048))
         return (O.gemv_q4k_q8_tile if tile else O.gemv_q4k_q8)(self.w[name], N, K, xq)
 
     def _gemv_rowpar(self, name: str, N: int, K: int, x_bf16: np.ndarray) -> np.ndarray:

@@ -236,7 +236,9 @@ def test_gemv_linearity_full_size(bk):
 
 
 @pytest.mark.parametrize("B,K,N", [(16, 256, 128), (16, 2048, 131), (17, 2048, 300), (31, 4096, 260), (32, 2048, 1000),
-                                   (33, 2048, 150), (64, 6144, 200), (32, 17408, 140)])
+                                   (33, 2048, 150), (64, 6144, 200), (32, 17408, 140),
+                                   # row counts that are multiples of 32: weights fed by tiled TMA loads
+                                   (16, 1024, 96), (32, 2048, 2080), (24, 768, 4128), (40, 4096, 1056), (32, 6144, 2048)])
 def test_gemv_dense_tile_path(bk, B, K, N):
     """16 or more columns of Q8_1 blocks: tcgen05 int8 MMA (one per 32-weight sub-block) with TMEM accumulators.  The
     integer block dots are exact; the f32 chain per (row, column) is the tile order of the oracle, so results are
@@ -276,8 +278,8 @@ def test_gemv_dense_tile_path(bk, B, K, N):
 
 
 def test_gemv_automatic_order_follows_the_row_count(bk):
-    """BK_GEMV_ORDER_AUTO at 32 columns: a launch of at least 4096 rows (a SwiGLU pair counts twice) takes the tile
-    kernel and its order, a smaller one the batch <= 8 kernels and theirs."""
+    """BK_GEMV_ORDER_AUTO at 32 columns: a launch of at least 4096 rows (a SwiGLU pair counts twice), or of at least
+    1024 rows with K >= 2048, takes the tile kernel and its order, a smaller one the batch <= 8 kernels and theirs."""
     B, K = 32, 512
     rng = np.random.default_rng(77)
     xq = O.q8_1_quantize(rng.normal(0, 1, (B, K)).astype(np.float32))
@@ -288,6 +290,16 @@ def test_gemv_automatic_order_follows_the_row_count(bk):
         ops.gemv_simple(dW.ptr, N, K, dxq.ptr, B, y.ptr)
         want = (O.gemv_q4k_q8_tile if tile else O.gemv_q4k_q8)(W, N, K, xq)
         assert_same_bits(y.download(np.float32, (B, N)), want, f"{N} rows")
+    K2 = 2048   # from K = 2048 on, 1024 rows are enough (the launch is cut along K over several thread blocks)
+    xq2 = O.q8_1_quantize(rng.normal(0, 1, (B, K2)).astype(np.float32))
+    dxq2 = dev(xq2)
+    for N, tile in ((1024, True), (1023, False)):
+        W = synth.q4k_weights(rng, N, K2)
+        dW, y = dev(W), R.DeviceBuffer(B * N * 4)
+        for _ in range(3):   # the arrival counters of a cut launch reset themselves
+            ops.gemv_simple(dW.ptr, N, K2, dxq2.ptr, B, y.ptr)
+        want = (O.gemv_q4k_q8_tile if tile else O.gemv_q4k_q8)(W, N, K2, xq2)
+        assert_same_bits(y.download(np.float32, (B, N)), want, f"{N} rows, K = 2048")
     N = 2048   # pair: 4096 launch rows
     Wg, Wu = synth.q4k_weights(rng, N, K), synth.q4k_weights(rng, N, K)
     dWg, dWu, act = dev(Wg), dev(Wu), R.DeviceBuffer(B * N * 2)
