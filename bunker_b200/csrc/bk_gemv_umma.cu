@@ -63,11 +63,12 @@ constexpr int kRowPitch = 2 * 144 + 16;   // bytes between rows of a stage: 76 w
 constexpr int kStageBytes = kTileM * kRowPitch;
 constexpr int kPlaneBytes = kTileM * 144;   // tensor-map feed: a stage is two planes [128 rows][144 bytes], one per superblock column
 constexpr int kTmemCols = 512;
+constexpr int kScsLd = 72;          // floats per sub-block of the column scales: 32 d8, 32 s8, 8 of padding (bank spread)
 
 // dynamic shared memory without the SwiGLU exchange buffer, which follows it: ring, A tiles (2 x 8 x 4 KB), B tiles,
 // column scales, row scale table, row {d, dmin}, barriers and flags
 __host__ __device__ constexpr size_t umma_smem_core_bytes() {
-  return (size_t)kStages * kStageBytes + 2 * 8 * 4096 + 2 * 8 * 32 * 32 + 2 * 8 * 64 * 4 + 2 * 8 * kTileM * 8 + 2 * kTileM * 8 + 160;
+  return (size_t)kStages * kStageBytes + 2 * 8 * 4096 + 2 * 8 * 32 * 32 + 2 * 8 * kScsLd * 4 + 2 * 8 * kTileM * 8 + 2 * kTileM * 8 + 160;
 }
 
 struct UmmaParams {
@@ -142,8 +143,8 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
   uint8_t* raw = smem;                                             // [kStages][128 rows][kRowPitch]
   uint8_t* As = raw + (size_t)kStages * kStageBytes;               // [2][8][4096]
   uint8_t* Bs = As + 2 * 8 * 4096;                                 // [2][8][Npad*32]
-  float* scs = reinterpret_cast<float*>(Bs + 2 * 8 * 32 * 32);     // [2][8][d8 of 32 columns | s8 of 32 columns]
-  int2* scm = reinterpret_cast<int2*>(scs + 2 * 8 * 64);           // [2][8][128] {sc, bits of f32(m)} of (sub-block, row)
+  float* scs = reinterpret_cast<float*>(Bs + 2 * 8 * 32 * 32);     // [2][8][d8 of 32 columns | s8 of 32 columns | pad]
+  int2* scm = reinterpret_cast<int2*>(scs + 2 * 8 * kScsLd);           // [2][8][128] {sc, bits of f32(m)} of (sub-block, row)
   float2* dd = reinterpret_cast<float2*>(scm + 2 * 8 * kTileM);    // [2][128] {d, dmin} of a row's superblock
   uint64_t* full = reinterpret_cast<uint64_t*>(dd + 2 * kTileM);   // [kStages] weights of a stage have landed
   uint64_t* empty = full + kStages;                                // [kStages] every row of a stage has been unpacked (4 arrivals)
@@ -202,14 +203,15 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
     // ================= stagers: Q8_1 activation blocks of step g -> B tiles and scales of buffer g&1 =================
     const int te = t - kStagerWarp0 * 32;
     const uint32_t* xq = reinterpret_cast<const uint32_t*>(p.x);
-    // activation blocks of a superblock: Npad*8 items (column b, sub-block j), item i = b*8 + j so that neighbouring
-    // threads read neighbouring 36-byte blocks; stager thread te takes items te, te + 64, ...
+    // activation blocks of a superblock: Npad*8 items (column b, sub-block j); eight neighbouring threads take eight
+    // neighbouring columns of one sub-block, whose 16-byte rows are contiguous in the B tile (no bank conflicts);
+    // stager thread te takes items te, te + 64, ...
     constexpr int kXI = Npad * 8 / 64;   // 2 or 4
     uint32_t xw[kXI][9];
     auto load_x = [&](int s) {
 #pragma unroll
       for (int i = 0; i < kXI; i++) {
-        const int it = te + 64 * i, b = it >> 3, j = it & 7;
+        const int it = te + 64 * i, j = (it >> 3) & 7, b = (it & 7) + 8 * (it >> 6);
 #pragma unroll
         for (int k = 0; k < 9; k++) xw[i][k] = b < P.B ? __ldcg(xq + ((size_t)b * nblk + (size_t)s * 8 + j) * 9 + k) : 0u;
       }
@@ -217,7 +219,7 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
     auto store_x = [&](int buf) {
 #pragma unroll
       for (int i = 0; i < kXI; i++) {
-        const int it = te + 64 * i, b = it >> 3, j = it & 7;
+        const int it = te + 64 * i, j = (it >> 3) & 7, b = (it & 7) + 8 * (it >> 6);
         uint8_t* tile_j = Bs + (size_t)buf * 8 * (Npad * 32) + (size_t)j * (Npad * 32) + (b >> 3) * 128 + (b & 7) * 16;
         *reinterpret_cast<uint4*>(tile_j) = make_uint4(xw[i][0], xw[i][1], xw[i][2], xw[i][3]);
         *reinterpret_cast<uint4*>(tile_j + Npad * 16) = make_uint4(xw[i][4], xw[i][5], xw[i][6], xw[i][7]);
@@ -225,8 +227,8 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
 #pragma unroll
         for (int k = 0; k < 8; k++) qsum = bk_dp4a_ss(xw[i][k], 0x01010101u, qsum);
         const float d8 = bk_q8half_to_f32((uint16_t)(xw[i][8] & 0xffffu));
-        scs[(size_t)buf * 8 * 64 + j * 64 + b] = d8;
-        scs[(size_t)buf * 8 * 64 + j * 64 + 32 + b] = __fmul_rn(d8, (float)qsum);
+        scs[(size_t)buf * 8 * kScsLd + j * kScsLd + b] = d8;
+        scs[(size_t)buf * 8 * kScsLd + j * kScsLd + 32 + b] = __fmul_rn(d8, (float)qsum);
       }
     };
 
@@ -333,7 +335,7 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
       mbar_wait_bounded(smem_u32(mma_done + buf), par, p.status);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float2 dm = dd[buf * kTileM + row_t];
-      const float4* sb4 = reinterpret_cast<const float4*>(scs + (size_t)buf * 8 * 64 + qd * NC);   // d8 of this thread's columns; s8 8 float4 further
+      const float4* sb4 = reinterpret_cast<const float4*>(scs + (size_t)buf * 8 * kScsLd + qd * NC);   // d8 of this thread's columns; s8 8 float4 further
       const int2* sm_ = scm + (size_t)buf * 8 * kTileM + row_t;
       const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(buf * 256 + qd * NC);
       float2 accd[NC / 2], accm[NC / 2];   // columns (2i, 2i+1) side by side: one packed FMA serves both
@@ -350,7 +352,7 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
         const float2 fm2 = make_float2(fm, fm);
 #pragma unroll
         for (int c = 0; c < NC; c += 4) {
-          const float4 d4 = sb4[j * 16 + (c >> 2)], s4 = sb4[j * 16 + 8 + (c >> 2)];   // d8, s8 of columns c..c+3
+          const float4 d4 = sb4[j * (kScsLd / 4) + (c >> 2)], s4 = sb4[j * (kScsLd / 4) + 8 + (c >> 2)];   // d8, s8 of columns c..c+3
           accd[c / 2] = fma2(make_float2(d4.x, d4.y),
                              make_float2(scaled_sum_f32(s2.x, (int)r[c]), scaled_sum_f32(s2.x, (int)r[c + 1])), accd[c / 2]);
           accd[c / 2 + 1] = fma2(make_float2(d4.z, d4.w),
