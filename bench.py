@@ -103,10 +103,33 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
-def make_config(steps: int, warmup: int):
+def make_config(steps: int, warmup: int, config: int = 3):
+    """configs[3] (24 layers, hidden 2048, 32-token prompt) or configs[4] (64 layers, hidden 5120, FFN 17408,
+    2048-token context) -> (model config, prompt length, workload description)"""
     from bunker_b200 import model as M
+    if config == 4:
+        need = 2048 + warmup + steps + 8
+        return (M.CONFIG_HYBRID_64L.with_(max_len=(need + 63) // 64 * 64), 2048,
+                "configs[4] scaled hybrid 64-layer Q4_K decode (hidden 5120, FFN 17408, vocab 151936)")
     need = PROMPT_LEN + warmup + steps + 8
-    return M.CONFIG_HYBRID_24L.with_(max_len=(max(need, 320) + 63) // 64 * 64)
+    return (M.CONFIG_HYBRID_24L.with_(max_len=(max(need, 320) + 63) // 64 * 64), PROMPT_LEN,
+            "configs[3] hybrid 24-layer Q4_K decode (hidden 2048, vocab 151936)")
+
+
+def oracle_parity(cfg, weights, info, got, prompt, world: int):
+    """Rank 0: the first argmax ids of the run (`got`, from the model's own token history) against the CPU oracle with
+    its emulation of `world` tensor-parallel ranks and the library's attention split."""
+    from oracle import oracle as O
+    from oracle.model_oracle import OracleModel
+    O.set_threads(os.cpu_count() or 1)
+    B, n_steps = prompt.shape[1], got.shape[0]
+    om = OracleModel(cfg, weights, batch=B, split_len=info["split_len"], attn_warps=info["attn_warps"], tp=world)
+    same = True
+    t0 = time.perf_counter()
+    for t in range(n_steps):
+        ids, _ = om.step(prompt[t])
+        same = same and bool(np.array_equal(ids, got[t]))
+    return {"steps_checked": n_steps, "identical_tokens": same, "oracle_tp": world, "seconds": round(time.perf_counter() - t0, 1)}
 
 
 def cpu_tokens_per_s(cfg, weights, batch: int, steps: int, warmup: int, budget_s: float = 150.0):
@@ -116,11 +139,15 @@ def cpu_tokens_per_s(cfg, weights, batch: int, steps: int, warmup: int, budget_s
     from oracle.model_oracle import OracleModel
     # a launcher (torch.distributed.run) exports OMP_NUM_THREADS=1 to its workers: ask for every host core explicitly
     threads = O.set_threads(os.cpu_count() or 1)
-    om = OracleModel(cfg, weights, batch=batch, split_len=64)
+    full = f"model.layers.{cfg.n_layers - 1}.mlp.down_proj.weight" in weights
+    t_full = float("inf")
+    if full:
+        om = OracleModel(cfg, weights, batch=batch, split_len=64)
+        tok = np.zeros((batch,), np.int32)
+        t0 = time.perf_counter()
+        om.step(tok)
+        t_full = time.perf_counter() - t0
     tok = np.zeros((batch,), np.int32)
-    t0 = time.perf_counter()
-    om.step(tok)
-    t_full = time.perf_counter() - t0
     scale, sample = 1.0, "full model, every step one whole token"
     if t_full * (steps + warmup) > budget_s:
         from bunker_b200 import model as M
@@ -150,16 +177,15 @@ def run_reference(args):
     if rank != 0:
         return
     from bunker_b200 import model as M
-    cfg = make_config(args.steps, args.warmup)
-    weights = M.synth_weights(cfg)
+    cfg, plen, wname = make_config(args.steps, args.warmup, args.config)
+    weights = M.synth_weights(cfg.with_(n_layers=4)) if args.config == 4 else M.synth_weights(cfg)   # the sample uses 4 layers
     val, ms, sample, cores = cpu_tokens_per_s(cfg, weights, args.batch, args.steps, args.warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8xint4->int32, f32 accumulate", "data": "synthetic",
-        "config": {"workload": f"configs[3] hybrid 24-layer Q4_K decode (hidden 2048, vocab 151936), batch {args.batch}, "
-                               f"{PROMPT_LEN}-token random prompt then greedy", "batch": args.batch, "parallelism": "cpu",
-                   "inputs": "weights (1.12 GB/step) larger than L2, no flush", "max_len": cfg.max_len},
+        "config": {"workload": f"{wname}, batch {args.batch}, {plen}-token random prompt then greedy", "batch": args.batch,
+                   "parallelism": "cpu", "inputs": "weights larger than L2, no flush", "max_len": cfg.max_len},
         "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -178,19 +204,29 @@ def run_ours(args):
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (launch with torch.distributed.run), found {world}")
     local = dist.env_rank()[2] if world > 1 else 0
-    cfg = make_config(K, W)
-    weights = M.synth_weights(cfg)
+    cfg, PLEN, wname = make_config(K, W, args.config)
+    weights = M.synth_weights(cfg)        # every layer drawn on its own
     R.cu(local)
     gm = M.DecodeModel(cfg, weights, batch=B, device=local, tp_rank=rank, tp_size=world)
     info = gm.info()
-    prompt = np.random.default_rng(0xB0B0 + 3000).integers(0, cfg.vocab, (PROMPT_LEN, B)).astype(np.int32)
+    prompt = np.random.default_rng(0xB0B0 + 1000 * args.config).integers(0, cfg.vocab, (PLEN, B)).astype(np.int32)
+
+    def feed_prompt(read_last: bool = False):
+        # a long context goes through the multi-token prompt path where that exists (one GPU, up to 8 sequences);
+        # otherwise token by token through the decode step; the last token always takes the decode step
+        if PLEN > 64 and world == 1 and B <= 8:
+            gm.prefill(prompt[:-1], read=False)
+        else:
+            for t in range(PLEN - 1):
+                gm.step(prompt[t], read=False)
+        return gm.step(prompt[-1], read=read_last)
+
     wbytes = M.weight_bytes(cfg)          # whole model; every rank streams 1/world of it (plus the lm_head shard)
     hbm_peak, peak_src = load_peaks()
     hbm_peak *= world
 
     # ---- resident leg: prompt, W warm-up steps, K timed graph replays with device-side token feedback ----
-    for t in range(PROMPT_LEN):
-        gm.step(prompt[t], read=False)
+    feed_prompt()
     gm.run(W)
     assert R.cuSync() == 0, R.last_error()
     dist.barrier()
@@ -207,13 +243,12 @@ def run_ours(args):
     ms = dist.max_over_ranks(e0.elapsed_ms(e1))
     launches = R.launch_count() - l0
     value = K * B / (ms * 1e-3)
-    tokens_resident = gm.tokens(PROMPT_LEN + W, K)
+    tokens_resident = gm.tokens(PLEN + W, K)
     # the same region four more times from the same starting state (reset, prompt, warm-up): spread of the measurement
     region_ms = [ms / K]
-    for _ in range(4):
+    for _ in range(4 if args.config == 3 else 1):
         gm.reset()
-        for t in range(PROMPT_LEN):
-            gm.step(prompt[t], read=False)
+        feed_prompt()
         gm.run(W)
         assert R.cuSync() == 0, R.last_error()
         dist.barrier()
@@ -255,9 +290,8 @@ def run_ours(args):
 
     # ---- end-to-end leg: host token in, host (id, logit) out, every step ----
     gm.reset()
-    ids = None
-    for t in range(PROMPT_LEN):
-        ids, _ = gm.step(prompt[t])
+    ids, _ = feed_prompt(read_last=True)
+    first_ids = gm.tokens(0, 8) if PLEN <= 64 else None   # checked against the CPU oracle once the GPU legs are done
     for _ in range(W):
         ids, _ = gm.step(ids)
     e2, e3 = R.Event(), R.Event()
@@ -275,12 +309,12 @@ def run_ours(args):
 
     # ---- the metric's second batch size: the same resident leg at batch 8 (skipped when --batch is given) ----
     batch8 = None
-    if B == 1 and not args.no_batch8:
+    if B == 1 and not args.no_batch8 and args.config == 3:
         gm.destroy()
         B8 = 8
         gm8 = M.DecodeModel(cfg, weights, batch=B8, device=local, tp_rank=rank, tp_size=world)
-        p8 = np.random.default_rng(0xB0B0 + 3008).integers(0, cfg.vocab, (PROMPT_LEN, B8)).astype(np.int32)
-        for t in range(PROMPT_LEN):
+        p8 = np.random.default_rng(0xB0B0 + 3008).integers(0, cfg.vocab, (PLEN, B8)).astype(np.int32)
+        for t in range(PLEN):
             gm8.step(p8[t], read=False)
         gm8.run(W)
         assert R.cuSync() == 0, R.last_error()
@@ -301,6 +335,7 @@ def run_ours(args):
         gm.destroy()
         dist.shutdown()
         return
+    parity = oracle_parity(cfg, weights, info, first_ids, prompt, world) if first_ids is not None else None
     if world == 1:
         cpu_val, cpu_ms, cpu_sample, cpu_threads = cpu_tokens_per_s(cfg, weights, B, steps=6, warmup=1, budget_s=30.0)
         cpu = {"value": cpu_val, "unit": "tok/s", "cores": cpu_threads, "kind": "port",
@@ -320,7 +355,7 @@ def run_ours(args):
     in_step_gbs = wbytes_rank / (gemv_in_step_us * 1e-6) / 1e9 if gemv_in_step_us > 0 else 0.0
     peak1 = hbm_peak / world
     ops_lines = None
-    if world == 1 and not args.no_ops:
+    if world == 1 and not args.no_ops and args.config == 3:
         from bunker_b200 import opbench
         ops_lines = opbench.run_all(peak1)
 
@@ -331,9 +366,9 @@ def run_ours(args):
                                 "max": float(max(region_ms)), "n": len(region_ms),
                                 "note": "the timed K-step region repeated from the same state; value uses the first"}, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8xint4->int32, f32 accumulate", "data": "synthetic",
-        "config": {"workload": f"configs[3] hybrid 24-layer Q4_K decode (hidden 2048, vocab 151936), batch {B}, "
-                               f"{PROMPT_LEN}-token random prompt then greedy", "batch": B, "parallelism": f"tp{world}",
-                   "inputs": "weights (1.12 GB/step) larger than L2, no flush", "max_len": cfg.max_len,
+        "config": {"workload": f"{wname}, batch {B}, {PLEN}-token random prompt then greedy", "batch": B,
+                   "parallelism": f"tp{world}",
+                   "inputs": f"weights ({wbytes / 1e9:.2f} GB/step) larger than L2, no flush", "max_len": cfg.max_len,
                    "attn_split_len": info["split_len"], "kernels_per_step": info["kernels_per_step"]},
         "clocks": sampler.summary(),
         "e2e": {"value": K * B / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 4 * B,
@@ -341,7 +376,9 @@ def run_ours(args):
                 "transfer": ("mapped pinned host memory: the embed kernel reads the token, the argmax kernel writes id and logit"
                              if world == 1 else "cudaMemcpyAsync from/to pinned host memory")},
         "gpu_launches": int(launches),
-        "roofline": {"bound": "hbm", "kernel": f"gemv_q4k_kernel<{B},8>" if B <= 1 else "gemv_q4k_mma_kernel",
+        "parity_vs_oracle": parity,
+        "roofline": {"bound": "hbm", "kernel": (f"gemv_q4k_kernel<{B},8>" if B <= 1 else "gemv_q4k_mma_kernel" if B < 16 or world > 1
+                                                else "gemv_q4k_umma_kernel (tcgen05 int8, launches of 1024+ rows) + gemv_q4k_mma_kernel"),
                      "achieved": in_step_gbs, "peak": peak1, "unit": "GB/s", "frac": in_step_gbs / peak1,
                      "traffic": (int(wbytes_rank / max(gemv_calls, 1) * NCU_GEMV_LMHEAD_TRAFFIC / 175646208)
                                  if (world == 1 and B == 1) else None),
@@ -377,6 +414,8 @@ def main():
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--config", type=int, default=3, choices=[3, 4],
+                    help="3: the 24-layer model the metric is quoted on (default); 4: the scaled 64-layer model, 2048-token context")
     ap.add_argument("--no-batch8", action="store_true", help="skip the extra batch-8 leg of the default run")
     ap.add_argument("--no-ops", action="store_true", help="skip the stand-alone per-kernel roofline lines (key `ops`)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
