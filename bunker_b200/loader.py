@@ -6,7 +6,9 @@ checkpoint-name rule of safeKey (prototypes/decode_graph.ts:99-109).  bunker upl
 here every linear weight is quantised to Q4_K on the device (bkQuantizeQ4K) on its way into the weight slab, one
 tensor at a time, so the host never holds more than one tensor and the device never holds the bf16 model.
 
-Single GPU.  (A tensor-parallel load would cut each rank's rows / K slice before quantising; not built.)
+Tensor parallel: every rank reads the file and cuts its rows / K range out of each tensor BEFORE quantising
+(model.shard_plan).  K ranges are whole superblocks and the quantiser works superblock by superblock, so the shard is
+bit-identical to the same cut of the quantised full tensor.
 """
 from __future__ import annotations
 
@@ -89,13 +91,30 @@ def _to_bf16(a: np.ndarray, dtype: str) -> np.ndarray:
     return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
 
 
-def load_model(cfg: M.ModelConfig, path: str, batch: int = 1, device: int = 0, step_mode: int = 0) -> M.DecodeModel:
+def shard_source(cfg: M.ModelConfig, name: str, a: np.ndarray, rank: int, n: int) -> np.ndarray:
+    """This rank's part of an unquantised tensor `a` (shaped as tensor_specs gives it), cut as model.shard_plan says."""
+    plan = M.shard_plan(cfg, name, rank, n)
+    if plan is None:
+        return a
+    if plan[0] == "rows":
+        return np.ascontiguousarray(a[plan[1]])
+    return np.ascontiguousarray(a[:, plan[1]:plan[2]])
+
+
+def load_model(cfg: M.ModelConfig, path: str, batch: int = 1, device: int = 0, step_mode: int = 0,
+               tp_rank: int = 0, tp_size: int = 1) -> M.DecodeModel:
     """Build the decode model of `cfg` from the checkpoint at `path`.  Linear weights may be BF16, F16 or F32 and are
     quantised to Q4_K on the device; norm weights, conv taps and dt_bias become bf16, A_log and the GDN norm f32
-    (their dtypes in tensor_specs).  Raises KeyError for a missing tensor and ValueError for a wrong shape."""
+    (their dtypes in tensor_specs).  With tp_size > 1 this rank loads its shard only (torch.distributed must already
+    be initialised, as for DecodeModel).  Raises KeyError for a missing tensor and ValueError for a wrong shape."""
     R.cu(device)
     hdr, data0 = read_header(path)
-    specs = M.tensor_specs(cfg)
+    full_specs = M.tensor_specs(cfg)
+    specs = []   # (name, kind, shape of this rank's shard)
+    for name, kind, shape in full_specs:
+        probe = shard_source(cfg, name, np.empty(shape, np.bool_), tp_rank, tp_size) if tp_size > 1 else None
+        specs.append((name, kind, tuple(probe.shape) if probe is not None else shape))
+    full_shape = {name: shape for name, _, shape in full_specs}
     sizes = {}
     for name, kind, shape in specs:
         n = int(np.prod(shape))
@@ -114,12 +133,13 @@ def load_model(cfg: M.ModelConfig, path: str, batch: int = 1, device: int = 0, s
             raise KeyError(f"checkpoint {path} has no tensor for '{name}'")
         ent = hdr[key]
         np_dt, esz = _DTYPES[ent["dtype"]]
-        n = int(np.prod(shape))
-        if int(np.prod(ent["shape"])) != n:
+        if int(np.prod(ent["shape"])) != int(np.prod(full_shape[name])):
             slab.free()
-            raise ValueError(f"{key}: shape {ent['shape']} does not hold the {shape} of '{name}'")
+            raise ValueError(f"{key}: shape {ent['shape']} does not hold the {full_shape[name]} of '{name}'")
         b0, b1 = ent["data_offsets"]
         raw = np.frombuffer(mm[data0 + b0:data0 + b1], dtype=np_dt)
+        if tp_size > 1:
+            raw = shard_source(cfg, name, raw.reshape(full_shape[name]), tp_rank, tp_size).reshape(-1)
         if kind == "q4k":
             # upload as f32 or bf16 and quantise on the device, straight into the slab
             src = raw.astype(np.float32) if ent["dtype"] == "F16" else raw
@@ -138,4 +158,5 @@ def load_model(cfg: M.ModelConfig, path: str, batch: int = 1, device: int = 0, s
         stage.free()
     del mm
     ptrs = {name: (slab.ptr + offs[name], sizes[name]) for name, _, _ in specs}
-    return M.DecodeModel.from_device(cfg, ptrs, slab, batch=batch, device=device, step_mode=step_mode)
+    return M.DecodeModel.from_device(cfg, ptrs, slab, batch=batch, device=device, step_mode=step_mode, tp_rank=tp_rank,
+                                     tp_size=tp_size)

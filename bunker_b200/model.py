@@ -177,42 +177,52 @@ def _q4k_kslice(W: np.ndarray, K: int, k0: int, k1: int) -> np.ndarray:
     return np.ascontiguousarray(W3[:, k0 // 256:k1 // 256]).reshape(N, -1)
 
 
-def shard_weights(cfg: ModelConfig, weights: dict[str, np.ndarray], rank: int, n: int) -> dict[str, np.ndarray]:
-    """The tensors rank `rank` of `n` registers.  Column-parallel: qkv/z/a/b (rows of the rank's key and value heads),
-    q/k/v (rows of its query heads and their KV head), gate/up (its FFN rows).  Row-parallel: out_proj, o_proj, down
-    (all rows, the rank's K slice).  Norm weights and the embedding table are replicated."""
+def shard_plan(cfg: ModelConfig, name: str, rank: int, n: int):
+    """How rank `rank` of `n` cuts tensor `name`: ("rows", index array) for column-parallel tensors (qkv/z/a/b rows of
+    the rank's key and value heads, q/k/v rows of its query heads and their KV head, gate/up: its FFN rows),
+    ("k", k0, k1) for row-parallel ones (out_proj, o_proj, down: all rows, the rank's K range, whole superblocks), None
+    for replicated ones (norm weights, the embedding table)."""
     if n == 1:
-        return weights
+        return None
     d = local_dims(cfg, rank, n)
-    H, D, HD = cfg.hidden, 128, cfg.head_dim
+    D, HD = 128, cfg.head_dim
     keydim = cfg.gdn_k_heads * D
     hk = np.arange(rank * d["Hk"] * D, (rank + 1) * d["Hk"] * D)
     hv = np.arange(rank * d["Hv"] * D, (rank + 1) * d["Hv"] * D)
-    chan = np.concatenate([hk, keydim + hk, 2 * keydim + hv])
-    vh = np.arange(rank * d["Hv"], (rank + 1) * d["Hv"])
+    if name.endswith("in_proj_qkv.weight") or name.endswith("conv1d.weight"):
+        return ("rows", np.concatenate([hk, keydim + hk, 2 * keydim + hv]))
+    if name.endswith("in_proj_z.weight"):
+        return ("rows", hv)
+    if name.endswith(("in_proj_a.weight", "in_proj_b.weight", "A_log", "dt_bias")):
+        return ("rows", np.arange(rank * d["Hv"], (rank + 1) * d["Hv"]))
+    if name.endswith("linear_attn.out_proj.weight"):
+        return ("k", rank * d["Hv"] * D, (rank + 1) * d["Hv"] * D)
+    if name.endswith("q_proj.weight"):
+        return ("rows", np.arange(rank * d["Hq"] * 2 * HD, (rank + 1) * d["Hq"] * 2 * HD))
+    if name.endswith(("k_proj.weight", "v_proj.weight")):
+        return ("rows", np.arange(d["kv0"] * HD, (d["kv0"] + d["Hkv"]) * HD))
+    if name.endswith("o_proj.weight"):
+        return ("k", rank * d["Hq"] * HD, (rank + 1) * d["Hq"] * HD)
+    if name.endswith(("gate_proj.weight", "up_proj.weight")):
+        return ("rows", np.arange(d["inter_off"], d["inter_off"] + d["inter"]))
+    if name.endswith("down_proj.weight"):
+        return ("k", d["inter_off"], d["inter_off"] + d["inter"])
+    return None
+
+
+def shard_weights(cfg: ModelConfig, weights: dict[str, np.ndarray], rank: int, n: int) -> dict[str, np.ndarray]:
+    """The tensors rank `rank` of `n` registers, cut from the full (quantised) tensors as shard_plan says."""
+    if n == 1:
+        return weights
     out: dict[str, np.ndarray] = {}
     for name, kind, shape in tensor_specs(cfg):
-        w = weights[name]
-        if name.endswith("in_proj_qkv.weight") or name.endswith("conv1d.weight"):
-            out[name] = _q4k_rows(w, chan)
-        elif name.endswith("in_proj_z.weight"):
-            out[name] = _q4k_rows(w, hv)
-        elif name.endswith(("in_proj_a.weight", "in_proj_b.weight", "A_log", "dt_bias")):
-            out[name] = _q4k_rows(w, vh)
-        elif name.endswith("linear_attn.out_proj.weight"):
-            out[name] = _q4k_kslice(w, cfg.z_dim, rank * d["Hv"] * D, (rank + 1) * d["Hv"] * D)
-        elif name.endswith("q_proj.weight"):
-            out[name] = _q4k_rows(w, np.arange(rank * d["Hq"] * 2 * HD, (rank + 1) * d["Hq"] * 2 * HD))
-        elif name.endswith(("k_proj.weight", "v_proj.weight")):
-            out[name] = _q4k_rows(w, np.arange(d["kv0"] * HD, (d["kv0"] + d["Hkv"]) * HD))
-        elif name.endswith("o_proj.weight"):
-            out[name] = _q4k_kslice(w, cfg.attn_q_heads * HD, rank * d["Hq"] * HD, (rank + 1) * d["Hq"] * HD)
-        elif name.endswith(("gate_proj.weight", "up_proj.weight")):
-            out[name] = _q4k_rows(w, np.arange(d["inter_off"], d["inter_off"] + d["inter"]))
-        elif name.endswith("down_proj.weight"):
-            out[name] = _q4k_kslice(w, cfg.intermediate, d["inter_off"], d["inter_off"] + d["inter"])
-        else:
+        w, plan = weights[name], shard_plan(cfg, name, rank, n)
+        if plan is None:
             out[name] = w
+        elif plan[0] == "rows":
+            out[name] = _q4k_rows(w, plan[1])
+        else:
+            out[name] = _q4k_kslice(w, shape[1], plan[1], plan[2])
     return out
 
 
@@ -230,14 +240,7 @@ class DecodeModel:
         weights = shard_weights(cfg, weights, tp_rank, tp_size)
         self.comm = 0
         if tp_size > 1:
-            from . import dist
-            h = C.c_uint64(0)
-            R._check(lib.bkCommCreate(tp_rank, tp_size, batch * cfg.hidden * 4, C.byref(h)))
-            self.comm = h.value
-            mine = (C.c_uint8 * 64)()
-            R._check(lib.bkCommExportHandle(self.comm, mine))
-            allh = b"".join(dist.all_gather_bytes(bytes(mine)))
-            R._check(lib.bkCommImportPeers(self.comm, (C.c_uint8 * len(allh)).from_buffer_copy(allh)))
+            self._create_comm(lib)
         # one slab, addressed by offset (prototypes/decode.ts:64-75), 256-byte aligned tensors
         offs, total = {}, 0
         for name, _, _ in specs:
@@ -250,6 +253,17 @@ class DecodeModel:
             R.cuHtoD(self.slab.ptr + offs[name], a)
         self._create(lib, {name: (self.slab.ptr + offs[name], weights[name].nbytes) for name, _, _ in specs}, step_mode)
 
+
+    def _create_comm(self, lib) -> None:
+        """Exchange buffer of this rank, exported to and mapped from its peers (CUDA IPC handles through the process group)."""
+        from . import dist
+        h = C.c_uint64(0)
+        R._check(lib.bkCommCreate(self.tp_rank, self.tp_size, self.batch * self.cfg.hidden * 4, C.byref(h)))
+        self.comm = h.value
+        mine = (C.c_uint8 * 64)()
+        R._check(lib.bkCommExportHandle(self.comm, mine))
+        allh = b"".join(dist.all_gather_bytes(bytes(mine)))
+        R._check(lib.bkCommImportPeers(self.comm, (C.c_uint8 * len(allh)).from_buffer_copy(allh)))
 
     def _create(self, lib, tensor_ptrs: dict, step_mode: int) -> None:
         """bkModelCreate + one bkModelSetTensor per weight (device pointer, bytes) + bkModelFinalize."""
@@ -280,12 +294,14 @@ class DecodeModel:
 
     @classmethod
     def from_device(cls, cfg: ModelConfig, tensor_ptrs: dict, slab, batch: int = 1, device: int = 0,
-                    step_mode: int = 0) -> "DecodeModel":
-        """A single-GPU model over weights that already sit in device memory (the loader's path): tensor_ptrs maps
-        every name of tensor_specs(cfg) to (device pointer, bytes); `slab` is the DeviceBuffer that owns them."""
+                    step_mode: int = 0, tp_rank: int = 0, tp_size: int = 1) -> "DecodeModel":
+        """A model over weights that already sit in device memory (the loader's path): tensor_ptrs maps every name of
+        tensor_specs(cfg) to (device pointer, bytes) of this rank's shard; `slab` is the DeviceBuffer that owns them."""
         self = object.__new__(cls)
-        self.cfg, self.batch, self.tp_rank, self.tp_size, self.comm = cfg, batch, 0, 1, 0
+        self.cfg, self.batch, self.tp_rank, self.tp_size, self.comm = cfg, batch, tp_rank, tp_size, 0
         lib = R.cu(device)
+        if tp_size > 1:
+            self._create_comm(lib)
         self.slab = slab
         self.offsets = {n: p - slab.ptr for n, (p, _) in tensor_ptrs.items()}
         self._create(lib, tensor_ptrs, step_mode)

@@ -82,3 +82,28 @@ def test_checkpoint_names_and_file_round_trip(tmp_path):
     assert hdr["a"] == {"dtype": "F32", "shape": [3, 4], "data_offsets": [0, 48]} and hdr["b"]["dtype"] == "BF16"
     raw = np.fromfile(p, np.uint8)[data0:]
     assert np.array_equal(raw[:48].view(np.float32).reshape(3, 4), a) and np.array_equal(raw[48:58].view(np.uint16), b)
+
+
+def test_tensor_parallel_cut_commutes_with_quantising():
+    """A rank that loads its shard cuts rows / a K range of whole superblocks out of the unquantised tensor and then
+    quantises; the result must be the same bytes as cutting the quantised full tensor (model.shard_weights), for every
+    linear weight of a small hybrid model, 2 and 4 ranks."""
+    from bunker_b200 import model as M
+    cfg = M.CONFIG_TINY.with_(n_layers=4, gdn_k_heads=4, gdn_v_heads=8)   # head counts divisible by 4 ranks
+    rng = np.random.default_rng(11)
+    raw, full_q = {}, {}
+    for name, kind, shape in M.tensor_specs(cfg):
+        if kind == "q4k" and name != "embed.weight":
+            raw[name] = rng.normal(0, 0.05, shape).astype(np.float32)
+            full_q[name] = O.q4k_quantize(raw[name])
+        else:   # replicated or small tensors: any bytes do; quantised dict entries must exist for shard_weights
+            raw[name] = rng.normal(0, 0.05, shape).astype(np.float32)
+            full_q[name] = raw[name] if kind != "q4k" else O.q4k_quantize(raw[name])
+    for n in (2, 4):
+        for rank in range(n):
+            want = M.shard_weights(cfg, full_q, rank, n)
+            for name, kind, shape in M.tensor_specs(cfg):
+                part = L.shard_source(cfg, name, raw[name], rank, n)
+                got = O.q4k_quantize(part) if kind == "q4k" else part
+                assert got.shape == want[name].shape, (name, n, rank)
+                assert np.array_equal(got, want[name]), (name, n, rank)
