@@ -75,6 +75,26 @@ def test_gemv_canonical_vs_plain_and_linearity():
     assert np.abs(ys - yp).max() / np.abs(yp).max() < 1e-5
 
 
+def test_gemv_tile_order_is_a_chain_of_four_superblock_chunks():
+    """The dense tile path's order: per (row, column) y = ((0 + c0) + c1) + ... over chunks of four superblocks, each
+    chunk a chain from zero -- so a chunk computed on its own K slice is exactly that chunk's term (what lets a launch
+    be cut along K), and a ragged last chunk (K = 2304: 4 + 4 + 1 superblocks) is a term like any other."""
+    N, B = 40, 5
+    for K in (1024, 2048, 2304):
+        W, x = synth.gemv_case(N, K, B)
+        xq = O.q8_1_quantize(x)
+        y = O.gemv_q4k_q8_tile(W, N, K, xq)
+        yp = O.gemv_q4k_q8_plain(W, N, K, xq)
+        assert np.abs(y - yp).max() / np.abs(yp).max() < 1e-5
+        W3 = W.reshape(N, K // 256, 144)
+        acc = np.zeros((B, N), np.float32)
+        for s0 in range(0, K // 256, 4):
+            n = min(4, K // 256 - s0)
+            Wc = np.ascontiguousarray(W3[:, s0:s0 + n]).reshape(N, -1)
+            acc = acc + O.gemv_q4k_q8_tile(Wc, N, n * 256, np.ascontiguousarray(xq[:, 8 * s0:8 * (s0 + n)]))
+        assert np.array_equal(bits(acc), bits(y)), K
+
+
 def test_transcendentals_close_to_libm():
     for x in np.linspace(-80, 80, 4001).astype(np.float32):
         x = float(x)
