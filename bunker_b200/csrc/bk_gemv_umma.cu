@@ -58,17 +58,20 @@ constexpr int kMmaWarp = 7;         // issues the MMAs
 constexpr int kScalerWarp0 = 8;     // warps 8..23: warp w reads TMEM lanes 32*(w mod 4)..+31, columns of quarter (w - 8) / 4
 constexpr int kScalerWarps = 16;
 constexpr int kUT = (kScalerWarp0 + kScalerWarps) * 32;
-constexpr int kStages = 3;          // ring stages, two superblock columns each
+constexpr int kStages = 2;          // ring stages, two superblock columns each
+constexpr int kSB = 3;              // shared-memory buffers (A / B tiles, scale tables): the unpacking runs up to two steps
+                                    // ahead of the two TMEM accumulator buffers
 constexpr int kRowPitch = 2 * 144 + 16;   // bytes between rows of a stage: 76 words, so 16-byte reads of 8 rows hit 8 bank groups
 constexpr int kStageBytes = kTileM * kRowPitch;
 constexpr int kPlaneBytes = kTileM * 144;   // tensor-map feed: a stage is two planes [128 rows][144 bytes], one per superblock column
 constexpr int kTmemCols = 512;
 constexpr int kScsLd = 72;          // floats per sub-block of the column scales: 32 d8, 32 s8, 8 of padding (bank spread)
 
-// dynamic shared memory without the SwiGLU exchange buffer, which follows it: ring, A tiles (2 x 8 x 4 KB), B tiles,
+// dynamic shared memory without the SwiGLU exchange buffer, which follows it: ring, A tiles (3 x 8 x 4 KB), B tiles,
 // column scales, row scale table, row {d, dmin}, barriers and flags
 __host__ __device__ constexpr size_t umma_smem_core_bytes() {
-  return (size_t)kStages * kStageBytes + 2 * 8 * 4096 + 2 * 8 * 32 * 32 + 2 * 8 * kScsLd * 4 + 2 * 8 * kTileM * 8 + 2 * kTileM * 8 + 160;
+  return (size_t)kStages * kStageBytes + kSB * 8 * 4096 + kSB * 8 * 32 * 32 + kSB * 8 * kScsLd * 4 + kSB * 8 * kTileM * 2 +
+         kSB * kTileM * 8 + 160;
 }
 
 struct UmmaParams {
@@ -141,17 +144,18 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
   extern __shared__ __align__(1024) uint8_t smem[];
   constexpr int Npad = 4 * NC;
   uint8_t* raw = smem;                                             // [kStages][128 rows][kRowPitch]
-  uint8_t* As = raw + (size_t)kStages * kStageBytes;               // [2][8][4096]
-  uint8_t* Bs = As + 2 * 8 * 4096;                                 // [2][8][Npad*32]
-  float* scs = reinterpret_cast<float*>(Bs + 2 * 8 * 32 * 32);     // [2][8][d8 of 32 columns | s8 of 32 columns | pad]
-  int2* scm = reinterpret_cast<int2*>(scs + 2 * 8 * kScsLd);           // [2][8][128] {sc, bits of f32(m)} of (sub-block, row)
-  float2* dd = reinterpret_cast<float2*>(scm + 2 * 8 * kTileM);    // [2][128] {d, dmin} of a row's superblock
-  uint64_t* full = reinterpret_cast<uint64_t*>(dd + 2 * kTileM);   // [kStages] weights of a stage have landed
+  uint8_t* As = raw + (size_t)kStages * kStageBytes;               // [kSB][8][4096]
+  uint8_t* Bs = As + kSB * 8 * 4096;                               // [kSB][8][Npad*32]
+  float* scs = reinterpret_cast<float*>(Bs + kSB * 8 * 32 * 32);   // [kSB][8][d8 of 32 columns | s8 of 32 columns | pad]
+  uint16_t* scm = reinterpret_cast<uint16_t*>(scs + kSB * 8 * kScsLd);   // [kSB][8][128] sc | m << 8 of (sub-block, row)
+  float2* dd = reinterpret_cast<float2*>(scm + kSB * 8 * kTileM);  // [kSB][128] {d, dmin} of a row's superblock
+  uint64_t* full = reinterpret_cast<uint64_t*>(dd + kSB * kTileM); // [kStages] weights of a stage have landed
   uint64_t* empty = full + kStages;                                // [kStages] every row of a stage has been unpacked (4 arrivals)
-  uint64_t* ab_full = empty + kStages;                             // [2] tiles and tables of a step written (192 arrivals)
-  uint64_t* mma_done = ab_full + 2;                                // [2] the step's MMAs have completed
-  uint64_t* buf_free = mma_done + 2;                               // [2] the scalers are done with a buffer (16 arrivals)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(buf_free + 2);
+  uint64_t* ab_full = empty + kStages;                             // [kSB] tiles and tables of a step written (192 arrivals)
+  uint64_t* smem_free = ab_full + kSB;                             // [kSB] the scalers are done with a shared-memory buffer (16 arrivals)
+  uint64_t* mma_done = smem_free + kSB;                            // [2] the step's MMAs have completed
+  uint64_t* tmem_free = mma_done + 2;                              // [2] the scalers have read an accumulator buffer (16 arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_free + 2);
   int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);   // K cut: this block arrived last at its tile's counter
   float* xchg = reinterpret_cast<float*>(smem + umma_smem_core_bytes());   // [32 columns][64]: up values of a SwiGLU tile (tensor-map feed)
   const bool swiglu_halves = P.use_maps && p.segs[0].epi == BK_EPI_SWIGLU;   // tile rows 0..63 gate, 64..127 up
@@ -164,10 +168,13 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
       mbar_init(smem_u32(full + i), 1);
       mbar_init(smem_u32(empty + i), kExpanderWarps);
     }
-    for (int i = 0; i < 2; i++) {
+    for (int i = 0; i < kSB; i++) {
       mbar_init(smem_u32(ab_full + i), (kExpanderWarps + kStagerWarps) * 32);
+      mbar_init(smem_u32(smem_free + i), kScalerWarps);
+    }
+    for (int i = 0; i < 2; i++) {
       mbar_init(smem_u32(mma_done + i), 1);
-      mbar_init(smem_u32(buf_free + i), kScalerWarps);
+      mbar_init(smem_u32(tmem_free + i), kScalerWarps);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -235,22 +242,30 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
     bk_pdl_wait();
     load_x(s_begin);
     int s = 0;
+    int buf = 0;          // shared-memory buffer g mod kSB, and the parity of its use number g / kSB
+    uint32_t upar = 0;
     for (int g = 0; g < G; g++) {
-      const int buf = g & 1;
-      if (g >= 2) mbar_wait_bounded(smem_u32(buf_free + buf), (uint32_t)(((g >> 1) & 1) ^ 1), p.status);   // the scalers have finished step g-2
+      if (g >= kSB) mbar_wait_bounded(smem_u32(smem_free + buf), upar ^ 1u, p.status);   // the scalers have finished step g - kSB
       store_x(buf);
       s = s + 1 == n_s ? 0 : s + 1;
       if (g + 1 < G) load_x(s_begin + s);   // in flight until the next step
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(smem_u32(ab_full + buf));
+      if (++buf == kSB) {
+        buf = 0;
+        upar ^= 1u;
+      }
     }
   } else if (warp == kMmaWarp) {
     // ================= MMA issue: eight MMAs, one per sub-block, into accumulator buffer g&1 =================
     // M = 128, N = Npad, int32 accumulators, A unsigned 8-bit, B signed 8-bit, both K-major
     const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(Npad >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+    int buf = 0;
+    uint32_t upar = 0;
     for (int g = 0; g < G; g++) {
-      const int buf = g & 1;
-      mbar_wait_bounded(smem_u32(ab_full + buf), (uint32_t)((g >> 1) & 1), p.status);   // all 128 rows and the activations are in place
+      const int tb = g & 1;   // accumulator buffer
+      mbar_wait_bounded(smem_u32(ab_full + buf), upar, p.status);   // all 128 rows and the activations are in place
+      if (g >= 2) mbar_wait_bounded(smem_u32(tmem_free + tb), (uint32_t)(((g >> 1) & 1) ^ 1), p.status);   // step g-2 has been read out
       if (lane == 0) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a0 = smem_u32(As + (size_t)buf * 8 * 4096);
@@ -259,17 +274,21 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
         for (int j = 0; j < 8; j++) {
           const uint64_t ad = umma_desc(a0 + j * 4096, 2048, 128);
           const uint64_t bd = umma_desc(b0 + j * (Npad * 32), (uint32_t)Npad * 16, 128);
-          const uint32_t dcol = tmem + (uint32_t)(buf * 256 + j * Npad);
+          const uint32_t dcol = tmem + (uint32_t)(tb * 256 + j * Npad);
           asm volatile(
               "{\n\t.reg .pred pz;\n\tsetp.ne.b32 pz, %4, 0;\n\t"
               "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, pz;\n\t}"
               ::"r"(dcol), "l"(ad), "l"(bd), "r"(idesc), "r"(0u), "r"(0u)
               : "memory");
         }
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(mma_done + buf))
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(mma_done + tb))
                      : "memory");
       }
       __syncwarp();
+      if (++buf == kSB) {
+        buf = 0;
+        upar ^= 1u;
+      }
     }
   } else if (warp == kProducerWarp) {
     // ================= producer: fill ring stage q mod kStages with pair q (weights depend on no earlier kernel) ==========
@@ -328,16 +347,17 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
 #pragma unroll
     for (int c = 0; c < NC; c++) y[c] = yc[c] = 0.0f;
     int s = 0, tl = 0;
+    int buf = 0;
+    uint32_t upar = 0;
     for (int g = 0; g < G; g++) {
-      const int buf = g & 1;
-      const uint32_t par = (uint32_t)((g >> 1) & 1);
-      mbar_wait_bounded(smem_u32(ab_full + buf), par, p.status);    // the tables of this step are visible
-      mbar_wait_bounded(smem_u32(mma_done + buf), par, p.status);
+      const int tb = g & 1;   // accumulator buffer
+      mbar_wait_bounded(smem_u32(ab_full + buf), upar, p.status);    // the tables of this step are visible
+      mbar_wait_bounded(smem_u32(mma_done + tb), (uint32_t)((g >> 1) & 1), p.status);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float2 dm = dd[buf * kTileM + row_t];
       const float4* sb4 = reinterpret_cast<const float4*>(scs + (size_t)buf * 8 * kScsLd + qd * NC);   // d8 of this thread's columns; s8 8 float4 further
-      const int2* sm_ = scm + (size_t)buf * 8 * kTileM + row_t;
-      const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(buf * 256 + qd * NC);
+      const uint16_t* sm_ = scm + (size_t)buf * 8 * kTileM + row_t;
+      const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(tb * 256 + qd * NC);
       float2 accd[NC / 2], accm[NC / 2];   // columns (2i, 2i+1) side by side: one packed FMA serves both
 #pragma unroll
       for (int c = 0; c < NC / 2; c++) accd[c] = accm[c] = make_float2(0.0f, 0.0f);
@@ -347,8 +367,9 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
 #pragma unroll
       for (int j = 0; j < 8; j++) {
         if (j < 7) tmem_ld<NC>(taddr + (uint32_t)((j + 1) * Npad), rn);   // in flight during this sub-block's arithmetic
-        const int2 s2 = sm_[j * kTileM];
-        const float fm = __int_as_float(s2.y);
+        const uint32_t scmv = sm_[j * kTileM];
+        const int2 s2 = make_int2((int)(scmv & 0xffu), 0);
+        const float fm = __fsub_rn(__int_as_float((int)(scmv >> 8) + 0x4B400000), 12582912.0f);   // f32(m), exact
         const float2 fm2 = make_float2(fm, fm);
 #pragma unroll
         for (int c = 0; c < NC; c += 4) {
@@ -368,7 +389,14 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(buf_free + buf));   // tables and accumulators of this buffer may be overwritten
+      if (lane == 0) {   // tables and accumulators of this step may be overwritten
+        mbar_arrive(smem_u32(smem_free + buf));
+        mbar_arrive(smem_u32(tmem_free + tb));
+      }
+      if (++buf == kSB) {
+        buf = 0;
+        upar ^= 1u;
+      }
 #pragma unroll
       for (int c = 0; c < NC; c += 2) {
         yc[c] = __fadd_rn(yc[c], fmaf(dm.x, accd[c / 2].x, -__fmul_rn(dm.y, accm[c / 2].x)));
@@ -455,13 +483,13 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
     const int te = t;                 // tile row of this thread
     bk_pdl_wait();
     int s = 0, tl = 0;
+    int buf = 0;
+    uint32_t upar = 0;
     for (int g = 0; g < G; g++) {
-      const int buf = g & 1;
-      const uint32_t par = (uint32_t)((g >> 1) & 1);
       const int q = tl * npairs + (s >> 1);
       const int stage = q % kStages;
       if ((s & 1) == 0) mbar_wait_bounded(smem_u32(full + stage), (uint32_t)((q / kStages) & 1), p.status);
-      if (g >= 2) mbar_wait_bounded(smem_u32(buf_free + buf), par ^ 1u, p.status);   // the scalers have finished step g-2
+      if (g >= kSB) mbar_wait_bounded(smem_u32(smem_free + buf), upar ^ 1u, p.status);   // the scalers have finished step g - kSB
       const int s_next = s + 1 == n_s ? 0 : s + 1;
       // header -> scale table; 4-bit quants -> unsigned int8 rows, sub-block 2p from the low nibbles of group p,
       //     2p+1 from the high nibbles
@@ -469,7 +497,7 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
                           (P.use_maps ? (size_t)(s & 1) * kPlaneBytes + (size_t)te * 144 : (size_t)te * kRowPitch + (s & 1) * 144);
       const uint4 hdr = *reinterpret_cast<const uint4*>(rw);
       dd[buf * kTileM + te] = make_float2(bk_f16_to_f32((uint16_t)(hdr.x & 0xffffu)), bk_f16_to_f32((uint16_t)(hdr.x >> 16)));
-      int2* sm_w = scm + (size_t)buf * 8 * kTileM + te;
+      uint16_t* sm_w = scm + (size_t)buf * 8 * kTileM + te;
       uint8_t* Ab = As + (size_t)buf * 8 * 4096 + (te >> 3) * 128 + (te & 7) * 16;
       uint4 qv[8];
 #pragma unroll
@@ -482,8 +510,8 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
       for (int pq = 0; pq < 4; pq++) {
         uint32_t sc2, mn2;
         bk_q4k_scale_min_pair(hdr.y, hdr.z, hdr.w, pq, sc2, mn2);
-        sm_w[(2 * pq) * kTileM] = make_int2((int)(sc2 & 0xffu), __float_as_int((float)(mn2 & 0xffu)));
-        sm_w[(2 * pq + 1) * kTileM] = make_int2((int)(sc2 >> 8), __float_as_int((float)(mn2 >> 8)));
+        sm_w[(2 * pq) * kTileM] = (uint16_t)((sc2 & 0xffu) | ((mn2 & 0xffu) << 8));
+        sm_w[(2 * pq + 1) * kTileM] = (uint16_t)((sc2 >> 8) | (mn2 & 0xff00u));
         const uint4 qa = qv[2 * pq], qb = qv[2 * pq + 1];
         uint8_t* A0 = Ab + (size_t)(2 * pq) * 4096;
         *reinterpret_cast<uint4*>(A0) = make_uint4(qa.x & 0x0f0f0f0fu, qa.y & 0x0f0f0f0fu, qa.z & 0x0f0f0f0fu, qa.w & 0x0f0f0f0fu);
@@ -495,6 +523,10 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads shared memory through the async proxy
       mbar_arrive(smem_u32(ab_full + buf));
+      if (++buf == kSB) {
+        buf = 0;
+        upar ^= 1u;
+      }
       s = s_next;
       if (s == 0) tl++;
     }
