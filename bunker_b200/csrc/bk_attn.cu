@@ -271,9 +271,17 @@ __global__ void __launch_bounds__(kW * 32, 2) attn_split_kernel(const AttnParams
 
   // ---- phase 1: scores ----
   {
-    float qf[G][8];
+    // query heads in pairs {q_g[d], q_g+1[d]}: one packed FMA advances the dot products of two heads (each its own
+    // chain over d, as before)
+    float2 qp[(G + 1) / 2][8];
 #pragma unroll
-    for (int g = 0; g < G; g++) bf16x8_to_f32(*reinterpret_cast<const uint4*>(q_st + g * kHD + lane * 8), qf[g]);
+    for (int g = 0; g < G; g += 2) {
+      float q0[8], q1[8];
+      bf16x8_to_f32(*reinterpret_cast<const uint4*>(q_st + g * kHD + lane * 8), q0);
+      if (g + 1 < G) bf16x8_to_f32(*reinterpret_cast<const uint4*>(q_st + (g + 1) * kHD + lane * 8), q1);
+#pragma unroll
+      for (int d = 0; d < 8; d++) qp[g >> 1][d] = make_float2(q0[d], g + 1 < G ? q1[d] : 0.0f);
+    }
     const int hsel = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
     for (int c = 0; c < nchunks; c++) {
       uint4 kn[kCh];
@@ -285,13 +293,14 @@ __global__ void __launch_bounds__(kW * 32, 2) attn_split_kernel(const AttnParams
           float kf[8], pa[8];
           bf16x8_to_f32(kc[e], kf);
 #pragma unroll
-          for (int g = 0; g < 8; g++) {
-            float a1 = 0.0f;
+          for (int g = 0; g < 8; g += 2) {
+            float2 a2 = make_float2(0.0f, 0.0f);
             if (g < G) {
 #pragma unroll
-              for (int d = 0; d < 8; d++) a1 = fmaf(qf[g < G ? g : 0][d], kf[d], a1);
+              for (int d = 0; d < 8; d++) a2 = bk_fma2(qp[(g < G ? g : 0) >> 1][d], make_float2(kf[d], kf[d]), a2);
             }
-            pa[g] = a1;
+            pa[g] = a2.x;
+            pa[g + 1] = a2.y;
           }
           const float s1 = warp_sum8(pa);
           if ((lane & 3) == 0) s_s[(size_t)jj * 8 + hsel] = __fmul_rn(s1, p.scale);
@@ -332,12 +341,13 @@ __global__ void __launch_bounds__(kW * 32, 2) attn_split_kernel(const AttnParams
 
   // ---- phase 3: o = sum p * V ----
   {
-    float acc[G][8], lw[G];
+    float2 acc[G][4];   // dims (2i, 2i+1) side by side: one packed FMA per pair
+    float lw[G];
 #pragma unroll
     for (int g = 0; g < G; g++) {
       lw[g] = 0.0f;
 #pragma unroll
-      for (int e = 0; e < 8; e++) acc[g][e] = 0.0f;
+      for (int e = 0; e < 4; e++) acc[g][e] = make_float2(0.0f, 0.0f);
     }
     for (int c = 0; c < nchunks; c++) {
       uint4 vn[kCh];
@@ -354,8 +364,9 @@ __global__ void __launch_bounds__(kW * 32, 2) attn_split_kernel(const AttnParams
 #pragma unroll
           for (int g = 0; g < G; g++) {
             lw[g] = __fadd_rn(lw[g], pp[g]);
+            const float2 p2 = make_float2(pp[g], pp[g]);
 #pragma unroll
-            for (int d = 0; d < 8; d++) acc[g][d] = fmaf(pp[g], vf[d], acc[g][d]);
+            for (int d = 0; d < 4; d++) acc[g][d] = bk_fma2(p2, make_float2(vf[2 * d], vf[2 * d + 1]), acc[g][d]);
           }
         }
       }
@@ -367,8 +378,8 @@ __global__ void __launch_bounds__(kW * 32, 2) attn_split_kernel(const AttnParams
 #pragma unroll
     for (int g = 0; g < G; g++) {
       float4* d = reinterpret_cast<float4*>(o_s + ((size_t)(warp * 8 + g)) * kHD + lane * 8);
-      d[0] = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
-      d[1] = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
+      d[0] = make_float4(acc[g][0].x, acc[g][0].y, acc[g][1].x, acc[g][1].y);
+      d[1] = make_float4(acc[g][2].x, acc[g][2].y, acc[g][3].x, acc[g][3].y);
       if (lane == 0) l_s[warp * 8 + g] = lw[g];
     }
   }

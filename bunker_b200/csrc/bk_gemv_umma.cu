@@ -92,18 +92,6 @@ BK_DEVINL uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sb
          ((uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46);
 }
 
-// {a.x*b.x + c.x, a.y*b.y + c.y}: two IEEE fused multiply-adds in one instruction
-BK_DEVINL float2 fma2(float2 a, float2 b, float2 c) {
-  unsigned long long ra, rb, rc, rd;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
-  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
-  asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
-  float2 d;
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
-  return d;
-}
-
 // f32 of the integer sc*isum, |sc*isum| < 2^22: the product lands in the mantissa of 1.5 * 2^23, which is then
 // subtracted -- both steps exact, so the value equals the integer-to-float conversion
 BK_DEVINL float scaled_sum_f32(int sc, int isum) { return __fsub_rn(__int_as_float(sc * isum + 0x4B400000), 12582912.0f); }
@@ -374,12 +362,12 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
 #pragma unroll
         for (int c = 0; c < NC; c += 4) {
           const float4 d4 = sb4[j * (kScsLd / 4) + (c >> 2)], s4 = sb4[j * (kScsLd / 4) + 8 + (c >> 2)];   // d8, s8 of columns c..c+3
-          accd[c / 2] = fma2(make_float2(d4.x, d4.y),
+          accd[c / 2] = bk_fma2(make_float2(d4.x, d4.y),
                              make_float2(scaled_sum_f32(s2.x, (int)r[c]), scaled_sum_f32(s2.x, (int)r[c + 1])), accd[c / 2]);
-          accd[c / 2 + 1] = fma2(make_float2(d4.z, d4.w),
+          accd[c / 2 + 1] = bk_fma2(make_float2(d4.z, d4.w),
                                  make_float2(scaled_sum_f32(s2.x, (int)r[c + 2]), scaled_sum_f32(s2.x, (int)r[c + 3])), accd[c / 2 + 1]);
-          accm[c / 2] = fma2(make_float2(s4.x, s4.y), fm2, accm[c / 2]);
-          accm[c / 2 + 1] = fma2(make_float2(s4.z, s4.w), fm2, accm[c / 2 + 1]);
+          accm[c / 2] = bk_fma2(make_float2(s4.x, s4.y), fm2, accm[c / 2]);
+          accm[c / 2 + 1] = bk_fma2(make_float2(s4.z, s4.w), fm2, accm[c / 2 + 1]);
         }
         if (j < 7) {
           tmem_wait<NC>(rn);
