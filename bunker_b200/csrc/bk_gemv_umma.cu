@@ -122,6 +122,22 @@ BK_DEVINL void tmem_wait(uint32_t (&r)[NC]) {
   }
 }
 
+// Bounded wait whose polls may sleep: the hint lets the hardware keep the warp suspended for up to a millisecond per
+// try (it wakes as soon as the phase completes), so that waiting roles do not spend issue slots on polling -- in this
+// kernel a fifth of all executed instructions were polls.  4096 tries bound the wait to a few seconds.
+BK_DEVINL void mbar_wait_idle(uint32_t bar, uint32_t parity, int* status) {
+  for (int it = 0; it < 4096; it++) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(1000000u)
+        : "memory");
+    if (ok) return;
+  }
+  if (status) atomicExch(status, 10003 /* BK_ERR_TIMEOUT */);
+}
+
 BK_DEVINL void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
 
 // NC: accumulator columns per scaler thread (MMA N / 4): 4 or 8
@@ -233,7 +249,7 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
     int buf = 0;          // shared-memory buffer g mod kSB, and the parity of its use number g / kSB
     uint32_t upar = 0;
     for (int g = 0; g < G; g++) {
-      if (g >= kSB) mbar_wait_bounded(smem_u32(smem_free + buf), upar ^ 1u, p.status);   // the scalers have finished step g - kSB
+      if (g >= kSB) mbar_wait_idle(smem_u32(smem_free + buf), upar ^ 1u, p.status);   // the scalers have finished step g - kSB
       store_x(buf);
       s = s + 1 == n_s ? 0 : s + 1;
       if (g + 1 < G) load_x(s_begin + s);   // in flight until the next step
@@ -252,8 +268,8 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
     uint32_t upar = 0;
     for (int g = 0; g < G; g++) {
       const int tb = g & 1;   // accumulator buffer
-      mbar_wait_bounded(smem_u32(ab_full + buf), upar, p.status);   // all 128 rows and the activations are in place
-      if (g >= 2) mbar_wait_bounded(smem_u32(tmem_free + tb), (uint32_t)(((g >> 1) & 1) ^ 1), p.status);   // step g-2 has been read out
+      mbar_wait_idle(smem_u32(ab_full + buf), upar, p.status);   // all 128 rows and the activations are in place
+      if (g >= 2) mbar_wait_idle(smem_u32(tmem_free + tb), (uint32_t)(((g >> 1) & 1) ^ 1), p.status);   // step g-2 has been read out
       if (lane == 0) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a0 = smem_u32(As + (size_t)buf * 8 * 4096);
@@ -281,7 +297,7 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
   } else if (warp == kProducerWarp) {
     // ================= producer: fill ring stage q mod kStages with pair q (weights depend on no earlier kernel) ==========
     for (int q = 0; q < Q; q++) {
-      if (q >= kStages) mbar_wait_bounded(smem_u32(empty + q % kStages), (uint32_t)((q / kStages - 1) & 1), p.status);
+      if (q >= kStages) mbar_wait_idle(smem_u32(empty + q % kStages), (uint32_t)((q / kStages - 1) & 1), p.status);
       const int tl = q / npairs, pp = q - tl * npairs;
       const int tile = tile0 + tl * tile_step;
       const uint32_t bytes = (uint32_t)((n_s - 2 * pp) >= 2 ? 288 : 144);
@@ -339,8 +355,8 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
     uint32_t upar = 0;
     for (int g = 0; g < G; g++) {
       const int tb = g & 1;   // accumulator buffer
-      mbar_wait_bounded(smem_u32(ab_full + buf), upar, p.status);    // the tables of this step are visible
-      mbar_wait_bounded(smem_u32(mma_done + tb), (uint32_t)((g >> 1) & 1), p.status);
+      mbar_wait_idle(smem_u32(ab_full + buf), upar, p.status);    // the tables of this step are visible
+      mbar_wait_idle(smem_u32(mma_done + tb), (uint32_t)((g >> 1) & 1), p.status);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float2 dm = dd[buf * kTileM + row_t];
       const float4* sb4 = reinterpret_cast<const float4*>(scs + (size_t)buf * 8 * kScsLd + qd * NC);   // d8 of this thread's columns; s8 8 float4 further
@@ -476,8 +492,8 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
     for (int g = 0; g < G; g++) {
       const int q = tl * npairs + (s >> 1);
       const int stage = q % kStages;
-      if ((s & 1) == 0) mbar_wait_bounded(smem_u32(full + stage), (uint32_t)((q / kStages) & 1), p.status);
-      if (g >= kSB) mbar_wait_bounded(smem_u32(smem_free + buf), upar ^ 1u, p.status);   // the scalers have finished step g - kSB
+      if ((s & 1) == 0) mbar_wait_idle(smem_u32(full + stage), (uint32_t)((q / kStages) & 1), p.status);
+      if (g >= kSB) mbar_wait_idle(smem_u32(smem_free + buf), upar ^ 1u, p.status);   // the scalers have finished step g - kSB
       const int s_next = s + 1 == n_s ? 0 : s + 1;
       // header -> scale table; 4-bit quants -> unsigned int8 rows, sub-block 2p from the low nibbles of group p,
       //     2p+1 from the high nibbles
