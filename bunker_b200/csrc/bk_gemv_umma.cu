@@ -96,19 +96,20 @@ BK_DEVINL uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sb
 // subtracted -- both steps exact, so the value equals the integer-to-float conversion
 BK_DEVINL float scaled_sum_f32(int sc, int isum) { return __fsub_rn(__int_as_float(sc * isum + 0x4B400000), 12582912.0f); }
 
-// NC accumulator columns of this thread's TMEM lane, starting at column taddr; the load is complete after tmem_wait
+// NC accumulator columns of this thread's TMEM lane, starting at column taddr; the load is complete after tmem_wait.
+// No memory clobber on either: they touch tensor memory only, their order among themselves is kept by `volatile`, and
+// without the clobber the compiler may move shared-memory loads of later sub-blocks across them (their latency was
+// the largest stall of the scaler warps).
 template <int NC>
 BK_DEVINL void tmem_ld(uint32_t taddr, uint32_t (&r)[NC]) {
   if constexpr (NC == 8) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr)
-                 : "memory");
+                 : "r"(taddr));
   } else {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(taddr)
-                 : "memory");
+                 : "r"(taddr));
   }
 }
 // the registers are operands so that no use of them can be scheduled before the wait
@@ -116,9 +117,9 @@ template <int NC>
 BK_DEVINL void tmem_wait(uint32_t (&r)[NC]) {
   if constexpr (NC == 8) {
     asm volatile("tcgen05.wait::ld.sync.aligned;"
-                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7])::"memory");
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]));
   } else {
-    asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3])::"memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]));
   }
 }
 
