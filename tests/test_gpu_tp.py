@@ -29,3 +29,15 @@ def test_tensor_parallel_matches_oracle(n, batch, ffn_per_rank):
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert f"TP{n} OK" in out.stdout
+
+
+def test_rank_leaving_between_steps_is_reported_on_the_host():
+    """Failure detection without a GPU fault: two ranks on two GPUs step through the host-side gate; rank 1 leaves
+    between steps with nothing in flight; rank 0 gets PeerLost before its next launch and its context stays usable."""
+    if _ngpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29541", os.path.join(ROOT, "tests", "tp_leave_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
+    assert "LEAVE OK" in out.stdout, out.stdout[-3000:] + out.stderr[-3000:]
