@@ -378,8 +378,9 @@ BK_DEVINL void bk_q4k_scale_min(uint32_t w0, uint32_t w1, uint32_t w2, int j, in
 // scales and mins of the two sub-blocks 2p, 2p+1 (p = 0..3) in one go, branch-free:
 // byte 0 of the results belongs to sub-block 2p, byte 1 to 2p+1
 BK_DEVINL void bk_q4k_scale_min_pair(uint32_t w0, uint32_t w1, uint32_t w2, int p, uint32_t& sc2, uint32_t& mn2) {
-  const int sh = (p & 1) * 16;
-  const uint32_t h0 = (w0 >> sh) & 0xffffu, h1 = (w1 >> sh) & 0xffffu, h2 = (w2 >> sh) & 0xffffu;
+  // the 16-bit half (p & 1) of each word, by one byte permute (selector bytes 0,1 or 2,3; upper half zero)
+  const uint32_t sel = (p & 1) ? 0x4432u : 0x4410u;
+  const uint32_t h0 = __byte_perm(w0, 0u, sel), h1 = __byte_perm(w1, 0u, sel), h2 = __byte_perm(w2, 0u, sel);
   const uint32_t sc_lo = h0 & 0x3f3fu, mn_lo = h1 & 0x3f3fu;
   const uint32_t sc_hi = (h2 & 0x0f0fu) | ((h0 >> 2) & 0x3030u);
   const uint32_t mn_hi = ((h2 >> 4) & 0x0f0fu) | ((h1 >> 2) & 0x3030u);
