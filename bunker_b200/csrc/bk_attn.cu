@@ -41,6 +41,10 @@ struct AttnParams {
   const uint16_t* gate;
   int B, Hq, Hkv, rot_half, max_len, split_len, max_splits, fused;
   int settled;  // cache rows of earlier steps and pos[] are not outputs of the immediately preceding launch
+  int layout_B; // entries the scratch buffer is laid out for (>= B): partials of all entries, then the completion counters,
+                // which must stay where they are from launch to launch (they reset themselves)
+  int n_seq;    // > 0: prompt columns.  Entry b of the launch is token b / n_seq of sequence b mod n_seq: it reads that
+                // sequence's cache, and its own K/V row has already been appended (attn_append_kernel)
   float scale;
   unsigned long long* trace;
 };
@@ -117,7 +121,7 @@ __device__ __forceinline__ float warp_sum8(const float (&v)[8]) {
 __device__ void combine_head_warp(const AttnParams& p, int b, int h, int ns, float* w_s) {
   const int lane = threadIdx.x & 31;
   const float* sc_ml = p.scratch + ((size_t)b * p.Hq + h) * p.max_splits * 2;
-  const float* sc_o = p.scratch + (size_t)p.B * p.Hq * p.max_splits * 2 + ((size_t)b * p.Hq + h) * p.max_splits * kHD;
+  const float* sc_o = p.scratch + (size_t)p.layout_B * p.Hq * p.max_splits * 2 + ((size_t)b * p.Hq + h) * p.max_splits * kHD;
   float m = -INFINITY;
   for (int s = lane; s < ns; s += 32) {
     float ms = __ldcg(sc_ml + 2 * s);
@@ -175,6 +179,26 @@ __device__ void combine_head_warp(const AttnParams& p, int b, int h, int ns, flo
 // chunk in flight while the current one is reduced.  The CTA that finishes a (batch, KV head) last merges the splits.
 // Two CTAs per SM (at most 128 registers): with one CTA of 8 warps an SM cannot hide the latency of the per-row
 // shuffle reductions and the stream stalls.
+// Prompt columns: every column's K row (head norm + RoPE at its own position, the arithmetic of the decode step) and V
+// row go into its sequence's cache before the attention launch, since a later token of the same pass attends to them.
+// One warp per (KV head, column).
+__global__ void __launch_bounds__(32) attn_append_kernel(const AttnParams p) {
+  bk_pdl_trigger();
+  __shared__ __align__(16) uint16_t k_st[kHD];
+  const int kvh = blockIdx.x, b = blockIdx.y, lane = threadIdx.x;
+  bk_pdl_wait();
+  const int pos = __ldcg(p.pos + b);
+  const int cb = b % p.n_seq;
+  uint16_t* Kb = p.k_cache + ((size_t)cb * p.Hkv + kvh) * (size_t)p.max_len * kHD;
+  uint16_t* Vb = p.v_cache + ((size_t)cb * p.Hkv + kvh) * (size_t)p.max_len * kHD;
+  norm_rope_256(p.k + ((size_t)b * p.Hkv + kvh) * kHD, p.k_norm_w, p.cos_t + (size_t)pos * p.rot_half,
+                p.sin_t + (size_t)pos * p.rot_half, p.rot_half, k_st);
+  __syncwarp();
+  *reinterpret_cast<uint4*>(Kb + (size_t)pos * kHD + lane * 8) = *reinterpret_cast<const uint4*>(k_st + lane * 8);
+  *reinterpret_cast<uint4*>(Vb + (size_t)pos * kHD + lane * 8) =
+      *reinterpret_cast<const uint4*>(p.v + ((size_t)b * p.Hkv + kvh) * kHD + lane * 8);
+}
+
 template <int G>
 __global__ void __launch_bounds__(kW * 32, 2) attn_split_kernel(const AttnParams p) {
   bk_pdl_trigger();
@@ -190,8 +214,9 @@ __global__ void __launch_bounds__(kW * 32, 2) attn_split_kernel(const AttnParams
 
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
-  uint16_t* Kb = p.k_cache + ((size_t)b * p.Hkv + kvh) * (size_t)p.max_len * kHD;
-  uint16_t* Vb = p.v_cache + ((size_t)b * p.Hkv + kvh) * (size_t)p.max_len * kHD;
+  const int cb = p.n_seq > 0 ? b % p.n_seq : b;   // whose cache
+  uint16_t* Kb = p.k_cache + ((size_t)cb * p.Hkv + kvh) * (size_t)p.max_len * kHD;
+  uint16_t* Vb = p.v_cache + ((size_t)cb * p.Hkv + kvh) * (size_t)p.max_len * kHD;
   const int j0 = split * p.split_len;
 
   // rows of this warp: jj = warp + 8*i; chunk c holds i in [kCh*c, kCh*c + kCh)
@@ -238,7 +263,7 @@ __global__ void __launch_bounds__(kW * 32, 2) attn_split_kernel(const AttnParams
       const uint16_t* src = p.qg + ((size_t)b * p.Hq + kvh * G + warp) * 2 * kHD;
       norm_rope_256(src, p.q_norm_w, cr, sr, p.rot_half, q_st + warp * kHD);
     }
-    if (warp == kW - 1 && pos >= j0 && pos < j0 + ns) {
+    if (p.n_seq == 0 && warp == kW - 1 && pos >= j0 && pos < j0 + ns) {
       norm_rope_256(p.k + ((size_t)b * p.Hkv + kvh) * kHD, p.k_norm_w, cr, sr, p.rot_half, k_st);
       *reinterpret_cast<uint4*>(Kb + (size_t)pos * kHD + lane * 8) = *reinterpret_cast<const uint4*>(k_st + lane * 8);
       *reinterpret_cast<uint4*>(Vb + (size_t)pos * kHD + lane * 8) =
@@ -388,7 +413,7 @@ __global__ void __launch_bounds__(kW * 32, 2) attn_split_kernel(const AttnParams
 
   // ---- cross-warp sums in warp order, partial out ----
   float* sc_ml = p.scratch;
-  float* sc_o = p.scratch + (size_t)p.B * p.Hq * p.max_splits * 2;
+  float* sc_o = p.scratch + (size_t)p.layout_B * p.Hq * p.max_splits * 2;
   for (int idx = tid; idx < G * kHD; idx += kW * 32) {
     const int g = idx >> 8, d = idx & 255;
     float o = o_s[(size_t)g * kHD + d];
@@ -409,7 +434,7 @@ __global__ void __launch_bounds__(kW * 32, 2) attn_split_kernel(const AttnParams
   __threadfence();
   __syncthreads();
   bk_stamp(p.trace, 7);
-  unsigned int* cnt = reinterpret_cast<unsigned int*>(p.scratch + (size_t)p.B * p.Hq * p.max_splits * (kHD + 2)) + b * p.Hkv + kvh;
+  unsigned int* cnt = reinterpret_cast<unsigned int*>(p.scratch + (size_t)p.layout_B * p.Hq * p.max_splits * (kHD + 2)) + b * p.Hkv + kvh;
   if (tid == 0) {
     const unsigned int done = atomicAdd(cnt, 1u);
     s_last = (done == (unsigned int)(nsplits - 1));
@@ -464,7 +489,19 @@ uint64_t bkAttnScratchBytes(int32_t B, int32_t Hq, int32_t HD, int32_t max_len, 
 int32_t bkAttnDecode(const bkAttnArgs* args) {
   BK_REQUIRE_INIT();
   BK_ARG(args != nullptr, "bkAttnDecode: args is null");
-  bkAttnArgs a = *args;
+  return bk_attn_launch(*args, 0, 0);
+}
+
+}  // extern "C"
+
+// n_seq > 0: the B entries are prompt columns of n_seq sequences (entry b = token b / n_seq of sequence b mod n_seq,
+// pos[b] its position): one launch appends every column's K/V row, a second one attends -- the same arithmetic per
+// column as B / n_seq decode steps.  layout_B > 0: the scratch buffer was sized for that many entries (launches with
+// different B then share one buffer).
+int32_t bk_attn_launch(const bkAttnArgs& args, int n_seq, int layout_B) {
+  bkAttnArgs a = args;
+  BK_ARG(layout_B == 0 || layout_B >= a.B, "attention: scratch laid out for %d entries, %d given", layout_B, a.B);
+  BK_ARG(n_seq >= 0 && (n_seq == 0 || (a.B % n_seq == 0 && a.fused_norm_rope)), "attention: %d columns of %d sequences", a.B, n_seq);
   BK_ARG(a.HD == kHD, "bkAttnDecode: head_dim %d unsupported (256 only)", a.HD);
   BK_ARG(a.B > 0 && a.Hq > 0 && a.Hkv > 0 && a.Hq % a.Hkv == 0 && a.Hq / a.Hkv <= 8,
          "bkAttnDecode: bad head counts B=%d Hq=%d Hkv=%d (group size 1..8)", a.B, a.Hq, a.Hkv);
@@ -515,7 +552,13 @@ int32_t bkAttnDecode(const bkAttnArgs* args) {
   p.fused = a.fused_norm_rope;
   p.scale = a.scale;
   p.trace = bk_trace_slot();
-  p.settled = a.cache_is_settled;
+  p.settled = n_seq ? 0 : a.cache_is_settled;
+  p.n_seq = n_seq;
+  p.layout_B = layout_B ? layout_B : a.B;
+  if (n_seq) {
+    BK_CUDA(bk_launch_pdl(attn_append_kernel, dim3(a.Hkv, a.B), dim3(32), 0, p));
+    BK_CHECK_LAUNCH();
+  }
   size_t smem = attn_smem_bytes(split_len);
   dim3 grid(nsplit, a.Hkv, a.B);
   int32_t rc;
@@ -532,5 +575,3 @@ int32_t bkAttnDecode(const bkAttnArgs* args) {
   if (rc) return rc;
   return BK_OK;
 }
-
-}  // extern "C"

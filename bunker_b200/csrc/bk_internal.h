@@ -107,6 +107,8 @@ struct BkReduce {
 bool bk_gemv_mma_fits(int K, int B);   // whether the batch-3..8 tensor-core GEMV can hold this K (else column pairs)
 bool bk_gemv_auto_tile(int rows, int K);   // whether BK_GEMV_ORDER_AUTO sends a launch of these shapes (>= 16 columns) to the dense tile path
 int32_t bk_gemv_launch(const bkGemvArgs& a);
+// decode attention; n_seq > 0: the B entries are prompt columns of n_seq sequences (append launch + attention launch)
+int32_t bk_attn_launch(const bkAttnArgs& a, int n_seq, int layout_B);
 // same with the fused exchange: push (may be null) for BK_EPI_PUSH_F32 segments, reduce (may be null) for
 // BK_PRO_REDUCE_RMSNORM; ctas_out (may be null) receives the number of CTAs that will signal arrival
 int32_t bk_gemv_launch_tp(const bkGemvArgs& a, const BkPush* push, const BkReduce* reduce, int* ctas_out);

@@ -80,6 +80,7 @@ struct Model {
     int cols = 0;
     uint64_t x[2] = {0, 0}, h1 = 0, qkv = 0, z = 0, a = 0, b = 0, attn_out = 0, qg = 0, kbuf = 0, vbuf = 0, act = 0, xq = 0;
     uint64_t ids = 0, pos = 0;   // int32 [cols]: token ids, position of every column
+    uint64_t attn_scratch = 0;   // split partials and completion counters for `cols` attention entries
   } pf;
 };
 
@@ -453,6 +454,7 @@ int32_t alloc_prefill(Model& m, int cols) {
   TRY(dev_alloc(m, blocks > staged ? blocks : staged, &f.xq));
   TRY(dev_alloc(m, C * 4, &f.ids));
   TRY(dev_alloc(m, C * 4, &f.pos));
+  TRY(dev_alloc(m, bkAttnScratchBytes(cols, m.Hq, c.head_dim, c.max_len, m.split_len), &f.attn_scratch));
   f.cols = cols;
   return BK_OK;
 }
@@ -519,19 +521,19 @@ int32_t enqueue_prefill(Model& m, int T) {
       g.segs[2] = bkGemvSeg{L.v, 0, f.vbuf, 0, m.KVD, BK_EPI_BF16, m.KVD, 0};
       TRY(bk_gemv_launch(g));
       const int attn_w = m.Hq * c.head_dim;
-      for (int t = 0; t < T; t++) {
-        const uint64_t r = (uint64_t)t * B;
+      {
+        // all columns of the pass in two launches: every column's K/V row is appended first, then column (t, b)
+        // attends to rows 0..pos[b]+t of sequence b's cache -- per column the arithmetic of a decode step
         bkAttnArgs aa;
         memset(&aa, 0, sizeof(aa));
-        aa.qg = f.qg + r * m.QG * 2; aa.k = f.kbuf + r * m.KVD * 2; aa.v = f.vbuf + r * m.KVD * 2;
+        aa.qg = f.qg; aa.k = f.kbuf; aa.v = f.vbuf;
         aa.q_norm_w = L.q_norm; aa.k_norm_w = L.k_norm;
-        aa.cos_t = m.cos_t; aa.sin_t = m.sin_t; aa.k_cache = L.kc; aa.v_cache = L.vc; aa.pos = f.pos + r * 4;
-        aa.out = f.attn_out + r * attn_w * 2; aa.scratch = m.attn_scratch;
-        aa.B = B; aa.Hq = m.Hq; aa.Hkv = m.Hkv; aa.HD = c.head_dim; aa.rot_half = c.rot_dim / 2; aa.max_len = c.max_len;
+        aa.cos_t = m.cos_t; aa.sin_t = m.sin_t; aa.k_cache = L.kc; aa.v_cache = L.vc; aa.pos = f.pos;
+        aa.out = f.attn_out; aa.scratch = f.attn_scratch;
+        aa.B = C; aa.Hq = m.Hq; aa.Hkv = m.Hkv; aa.HD = c.head_dim; aa.rot_half = c.rot_dim / 2; aa.max_len = c.max_len;
         aa.split_len = m.split_len; aa.max_pos = c.max_len - 1; aa.scale = 1.0f / sqrtf((float)c.head_dim);
         aa.fused_norm_rope = 1;
-        aa.cache_is_settled = 0;   // the previous token's launch appended the row this one reads
-        TRY(bkAttnDecode(&aa));
+        TRY(bk_attn_launch(aa, B, m.pf.cols));
       }
       memset(&g, 0, sizeof(g));
       TRY(set_input(g, f.attn_out, attn_w, 0, C));
