@@ -13,6 +13,8 @@ inputs (1.1 GB of weights) exceed L2, so no flush is needed between timed steps.
 `roofline`: the dominant kernel (gemv_q4k_kernel) over all its launches inside the step: weight bytes / (step time x
            the GEMV share of a per-op CUDA-event profile); `lm_head_alone` = the same kernel on its largest launch, timed
            back to back between two events.
+`batch8`, `batch32`: the resident leg repeated at batch 8 (the metric's second batch size) and, on one GPU, at batch 32
+           (the tcgen05 tile path).
 `ops`    : stand-alone roofline lines of the GEMV (4096x4096 over rotating weight copies), the GDN step (batch 1, 8) and
            decode attention (cache 1024 / 4096 / 32768 rows, batch 1, 8): median / min / max of 5 timed regions each.
 `cpu_baseline` / `--impl reference`: the CPU oracle (C restatement of the reference's op math, OpenMP) on the
@@ -308,29 +310,36 @@ def run_ours(args):
     same_stream = bool(np.array_equal(np.stack(toks), tokens_resident))
 
     # ---- the metric's second batch size: the same resident leg at batch 8 (skipped when --batch is given) ----
-    batch8 = None
-    if B == 1 and not args.no_batch8 and args.config == 3:
+    def extra_leg(Bx: int, kernel: str):
+        """The resident leg repeated at another batch size (same model, same prompt length, K timed graph replays)."""
+        nonlocal gm
         gm.destroy()
-        B8 = 8
-        gm8 = M.DecodeModel(cfg, weights, batch=B8, device=local, tp_rank=rank, tp_size=world)
-        p8 = np.random.default_rng(0xB0B0 + 3008).integers(0, cfg.vocab, (PLEN, B8)).astype(np.int32)
+        gx = M.DecodeModel(cfg, weights, batch=Bx, device=local, tp_rank=rank, tp_size=world)
+        px = np.random.default_rng(0xB0B0 + 3000 + Bx).integers(0, cfg.vocab, (PLEN, Bx)).astype(np.int32)
         for t in range(PLEN):
-            gm8.step(p8[t], read=False)
-        gm8.run(W)
+            gx.step(px[t], read=False)
+        gx.run(W)
         assert R.cuSync() == 0, R.last_error()
         dist.barrier()
         b0, b1 = R.Event(), R.Event()
         b0.record()
-        gm8.run(K)
+        gx.run(K)
         b1.record()
         b1.synchronize()
         dist.barrier()
-        ms8 = dist.max_over_ranks(b0.elapsed_ms(b1))
-        batch8 = {"value": K * B8 / (ms8 * 1e-3), "unit": "tok/s", "batch": B8, "ms_per_step": ms8 / K,
-                  "frac_of_hbm": wbytes / (ms8 / K * 1e-3) / 1e9 / hbm_peak,
-                  "kernels_per_step": gm8.info()["kernels_per_step"],
-                  "gemv_kernel": "gemv_q4k_mma_kernel (int8 mma.sync m16n8k32)"}
-        gm = gm8
+        msx = dist.max_over_ranks(b0.elapsed_ms(b1))
+        gm = gx
+        return {"value": K * Bx / (msx * 1e-3), "unit": "tok/s", "batch": Bx, "ms_per_step": msx / K,
+                "frac_of_hbm": wbytes / (msx / K * 1e-3) / 1e9 / hbm_peak,
+                "kernels_per_step": gx.info()["kernels_per_step"], "gemv_kernel": kernel}
+
+    # ---- the metric's second batch size (batch 8), and batch 32 on one GPU (the tcgen05 tile path) ----
+    batch8 = batch32 = None
+    if B == 1 and not args.no_batch8 and args.config == 3:
+        batch8 = extra_leg(8, "gemv_q4k_mma_kernel (int8 mma.sync m16n8k32)")
+        if world == 1:
+            batch32 = extra_leg(32, "gemv_q4k_umma_kernel (tcgen05.mma kind::i8, TMEM accumulators) for launches of 1024+ rows, "
+                                    "gemv_q4k_mma_kernel for the rest")
     if rank != 0:
         gm.destroy()
         dist.shutdown()
@@ -401,6 +410,7 @@ def run_ours(args):
         "per_op_ms": {k: round(v[0], 5) for k, v in prof.items()},
         "per_op_calls": {k: v[1] for k, v in prof.items()},
         "batch8": batch8,
+        "batch32": batch32,
         "cpu_baseline": cpu,
     }
     print(json.dumps(line), flush=True)
@@ -416,7 +426,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--config", type=int, default=3, choices=[3, 4],
                     help="3: the 24-layer model the metric is quoted on (default); 4: the scaled 64-layer model, 2048-token context")
-    ap.add_argument("--no-batch8", action="store_true", help="skip the extra batch-8 leg of the default run")
+    ap.add_argument("--no-batch8", action="store_true", help="skip the extra batch-8 and batch-32 legs of the default run")
     ap.add_argument("--no-ops", action="store_true", help="skip the stand-alone per-kernel roofline lines (key `ops`)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
