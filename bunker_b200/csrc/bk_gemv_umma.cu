@@ -6,11 +6,10 @@
 // (src/kernel.ts:396-456: 4-bit blocks expanded to int8 tiles, int32 accumulators, scales applied afterwards,
 // experiments/q4k_q81_final.ts:217); this is that scheme on the 144-byte Q4_K layout.
 //
-// One CTA of 640 threads per SM walks over its 128-row tiles, as two groups of warps that meet only at mbarriers:
-//   * one PRODUCER warp keeps a ring of three stages filled with bulk copies: a stage holds two superblock columns
-//     (288 bytes) of each of the 128 rows; the ring runs ahead across tile boundaries and starts before the
-//     dependency wait.  (A bulk copy of a few hundred bytes costs its issuer about 75 cycles, 128 of them per stage:
-//     that is why this warp does nothing else.)
+// One CTA of 768 threads per SM walks over its 128-row tiles, as five groups of warps that meet only at mbarriers:
+//   * one PRODUCER warp keeps a ring of two stages filled: a stage holds two superblock columns (288 bytes) of each of
+//     the 128 rows; the ring runs ahead across tile boundaries and starts before the dependency wait (see "Weight
+//     feed" below for the two ways a stage is filled);
 //   * four EXPANDER warps (thread <-> tile row).  Per 256-weight superblock column every expander thread
 //     unpacks its row's 128 quant bytes into eight 32-byte rows of unsigned int8 (one per sub-block), stored in the
 //     K-major "core matrix" layout the MMA reads (8 rows x 16 bytes contiguous, no swizzle), and decodes the eight
@@ -24,8 +23,9 @@
 //   * sixteen SCALER warps (four per TMEM lane quarter, each a quarter of the columns) run the f32 part of a
 //     superblock as soon as its MMAs have completed: tcgen05.ld brings a thread its row's int32 sums, and
 //     accd = fma(d8, f32(sc*isum), accd), accm = fma(s8, f32(m), accm)  over the sub-blocks in ascending order, then
-//     yc += fma(d, accd, -(dmin*accm));  every four superblocks  y += yc.  They release the buffers (shared-memory
-//     tiles, tables, accumulators; two of each) back to the expanders through another mbarrier.
+//     yc += fma(d, accd, -(dmin*accm));  every four superblocks  y += yc.  They hand the buffers back through two more
+//     mbarriers: the shared-memory side (tiles and tables, three buffers, so that the unpacking runs up to two steps
+//     ahead) to the expanders and stagers, the accumulators (two buffers of 256 TMEM columns) to the MMA warp.
 // That f32 order ("tile order": per (row, column) one chain per chunk of four superblocks, chunks added in order) is
 // fixed and mirrored by the CPU checker; it differs from the batch <= 8 kernels' lane / butterfly order by a few ulp.
 //
@@ -40,8 +40,8 @@
 // and the 64 up rows in 64..127 (boxes are contiguous rows of one matrix), and the epilogue passes the up values to
 // the gate rows' threads through shared memory.  Other shapes keep the per-row copies.
 //
-// No cluster, no multicast.  Every wait is bounded; TMEM is released on every
-// path out of the kernel.
+// No cluster, no multicast.  Every wait is bounded (and may sleep between polls); TMEM is released on every path out
+// of the kernel.
 #include <cuda.h>   // CUtensorMap and the types of its encoder; the encoder itself is looked up at run time
 
 #include "bk_gemv_shared.cuh"
