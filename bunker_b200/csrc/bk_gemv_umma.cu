@@ -124,18 +124,21 @@ BK_DEVINL void tmem_wait(uint32_t (&r)[NC]) {
 }
 
 // Bounded wait whose polls may sleep: the hint lets the hardware keep the warp suspended for up to a millisecond per
-// try (it wakes as soon as the phase completes), so that waiting roles do not spend issue slots on polling -- in this
-// kernel a fifth of all executed instructions were polls.  4096 tries bound the wait to a few seconds.
-BK_DEVINL void mbar_wait_idle(uint32_t bar, uint32_t parity, int* status) {
-  for (int it = 0; it < 4096; it++) {
+// try (it wakes as soon as the phase completes), so that waiting roles do not spend issue slots on polling.  2048 tries
+// bound a wait to about two seconds; the first wait of a CTA that gives up sets the status word and a flag in shared
+// memory, after which every other wait of that CTA returns at once -- the kernel then runs to its end (results
+// undefined, status BK_ERR_TIMEOUT) instead of timing out step after step.
+BK_DEVINL void mbar_wait_idle(uint32_t bar, uint32_t parity, int* status, volatile int* dead) {
+  for (int it = 0; it < 2048; it++) {
     uint32_t ok;
     asm volatile(
         "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; selp.u32 %0, 1, 0, p; }"
         : "=r"(ok)
         : "r"(bar), "r"(parity), "r"(1000000u)
         : "memory");
-    if (ok) return;
+    if (ok || *dead) return;
   }
+  *dead = 1;
   if (status) atomicExch(status, 10003 /* BK_ERR_TIMEOUT */);
 }
 
@@ -162,6 +165,7 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
   uint64_t* tmem_free = mma_done + 2;                              // [2] the scalers have read an accumulator buffer (16 arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_free + 2);
   int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);   // K cut: this block arrived last at its tile's counter
+  volatile int* dead = last_flag + 1;                        // a bounded wait of this CTA has given up
   float* xchg = reinterpret_cast<float*>(smem + umma_smem_core_bytes());   // [32 columns][64]: up values of a SwiGLU tile (tensor-map feed)
   const bool swiglu_halves = P.use_maps && p.segs[0].epi == BK_EPI_SWIGLU;   // tile rows 0..63 gate, 64..127 up
 
@@ -169,6 +173,7 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
   const int K = p.K, nsb = K / 256, nblk = K / 32;
 
   if (t == 0) {
+    *dead = 0;
     for (int i = 0; i < kStages; i++) {
       mbar_init(smem_u32(full + i), 1);
       mbar_init(smem_u32(empty + i), kExpanderWarps);
@@ -250,7 +255,7 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
     int buf = 0;          // shared-memory buffer g mod kSB, and the parity of its use number g / kSB
     uint32_t upar = 0;
     for (int g = 0; g < G; g++) {
-      if (g >= kSB) mbar_wait_idle(smem_u32(smem_free + buf), upar ^ 1u, p.status);   // the scalers have finished step g - kSB
+      if (g >= kSB) mbar_wait_idle(smem_u32(smem_free + buf), upar ^ 1u, p.status, dead);   // the scalers have finished step g - kSB
       store_x(buf);
       s = s + 1 == n_s ? 0 : s + 1;
       if (g + 1 < G) load_x(s_begin + s);   // in flight until the next step
@@ -269,8 +274,8 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
     uint32_t upar = 0;
     for (int g = 0; g < G; g++) {
       const int tb = g & 1;   // accumulator buffer
-      mbar_wait_idle(smem_u32(ab_full + buf), upar, p.status);   // all 128 rows and the activations are in place
-      if (g >= 2) mbar_wait_idle(smem_u32(tmem_free + tb), (uint32_t)(((g >> 1) & 1) ^ 1), p.status);   // step g-2 has been read out
+      mbar_wait_idle(smem_u32(ab_full + buf), upar, p.status, dead);   // all 128 rows and the activations are in place
+      if (g >= 2) mbar_wait_idle(smem_u32(tmem_free + tb), (uint32_t)(((g >> 1) & 1) ^ 1), p.status, dead);   // step g-2 has been read out
       if (lane == 0) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a0 = smem_u32(As + (size_t)buf * 8 * 4096);
@@ -298,7 +303,7 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
   } else if (warp == kProducerWarp) {
     // ================= producer: fill ring stage q mod kStages with pair q (weights depend on no earlier kernel) ==========
     for (int q = 0; q < Q; q++) {
-      if (q >= kStages) mbar_wait_idle(smem_u32(empty + q % kStages), (uint32_t)((q / kStages - 1) & 1), p.status);
+      if (q >= kStages) mbar_wait_idle(smem_u32(empty + q % kStages), (uint32_t)((q / kStages - 1) & 1), p.status, dead);
       const int tl = q / npairs, pp = q - tl * npairs;
       const int tile = tile0 + tl * tile_step;
       const uint32_t bytes = (uint32_t)((n_s - 2 * pp) >= 2 ? 288 : 144);
@@ -356,8 +361,8 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
     uint32_t upar = 0;
     for (int g = 0; g < G; g++) {
       const int tb = g & 1;   // accumulator buffer
-      mbar_wait_idle(smem_u32(ab_full + buf), upar, p.status);    // the tables of this step are visible
-      mbar_wait_idle(smem_u32(mma_done + tb), (uint32_t)((g >> 1) & 1), p.status);
+      mbar_wait_idle(smem_u32(ab_full + buf), upar, p.status, dead);    // the tables of this step are visible
+      mbar_wait_idle(smem_u32(mma_done + tb), (uint32_t)((g >> 1) & 1), p.status, dead);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float2 dm = dd[buf * kTileM + row_t];
       const float4* sb4 = reinterpret_cast<const float4*>(scs + (size_t)buf * 8 * kScsLd + qd * NC);   // d8 of this thread's columns; s8 8 float4 further
@@ -493,8 +498,8 @@ __global__ void __launch_bounds__(kUT, 1) gemv_q4k_umma_kernel(const __grid_cons
     for (int g = 0; g < G; g++) {
       const int q = tl * npairs + (s >> 1);
       const int stage = q % kStages;
-      if ((s & 1) == 0) mbar_wait_idle(smem_u32(full + stage), (uint32_t)((q / kStages) & 1), p.status);
-      if (g >= kSB) mbar_wait_idle(smem_u32(smem_free + buf), upar ^ 1u, p.status);   // the scalers have finished step g - kSB
+      if ((s & 1) == 0) mbar_wait_idle(smem_u32(full + stage), (uint32_t)((q / kStages) & 1), p.status, dead);
+      if (g >= kSB) mbar_wait_idle(smem_u32(smem_free + buf), upar ^ 1u, p.status, dead);   // the scalers have finished step g - kSB
       const int s_next = s + 1 == n_s ? 0 : s + 1;
       // header -> scale table; 4-bit quants -> unsigned int8 rows, sub-block 2p from the low nibbles of group p,
       //     2p+1 from the high nibbles
