@@ -40,6 +40,7 @@ PROMPT_LEN = 32
 # launch (two launches of gemv_q4k_kernel, --clock-control none)
 NCU_GEMV_LMHEAD_TRAFFIC = 180382976
 METRIC = "q4k_hybrid_decode_tok_s"
+CPU_SINGLE_THREAD = None   # filled by cpu_tokens_per_s
 
 
 def load_peaks():
@@ -170,6 +171,16 @@ def cpu_tokens_per_s(cfg, weights, batch: int, steps: int, warmup: int, budget_s
         if om.pos >= om.cfg.max_len - 1:
             om.reset()
     dt = time.perf_counter() - t0
+    # the same loops on ONE thread (two steps of the same sample): the scalar port of the reference's host loops
+    global CPU_SINGLE_THREAD
+    O.set_threads(1)
+    t1 = time.perf_counter()
+    for _ in range(2):
+        om.step(tok)
+        if om.pos >= om.cfg.max_len - 1:
+            om.reset()
+    CPU_SINGLE_THREAD = {"value": 2 * batch / (time.perf_counter() - t1) * scale, "unit": "tok/s", "cores": 1, "steps": 2}
+    O.set_threads(threads)
     return steps * batch / dt * scale, dt / steps * 1e3, sample, threads
 
 
@@ -188,7 +199,8 @@ def run_reference(args):
         "dtype": "int8xint4->int32, f32 accumulate", "data": "synthetic",
         "config": {"workload": f"{wname}, batch {args.batch}, {plen}-token random prompt then greedy", "batch": args.batch,
                    "parallelism": "cpu", "inputs": "weights larger than L2, no flush", "max_len": cfg.max_len},
-        "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample,
+                         "single_thread": CPU_SINGLE_THREAD},
         "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
         "note": "reference is TypeScript for bun + Triton-generated kernels; bun is absent, so its op math runs as the C port",
@@ -348,7 +360,7 @@ def run_ours(args):
     if world == 1:
         cpu_val, cpu_ms, cpu_sample, cpu_threads = cpu_tokens_per_s(cfg, weights, B, steps=6, warmup=1, budget_s=30.0)
         cpu = {"value": cpu_val, "unit": "tok/s", "cores": cpu_threads, "kind": "port",
-               "sample": cpu_sample + "; 6 timed steps", "ms_per_step": cpu_ms}
+               "sample": cpu_sample + "; 6 timed steps", "ms_per_step": cpu_ms, "single_thread": CPU_SINGLE_THREAD}
     else:
         cpu = None   # reported at N=1 only
 
