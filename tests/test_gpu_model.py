@@ -284,6 +284,26 @@ def test_scaled_model_shapes_batch8_tensor_core_path(bk):
     gm.destroy()
 
 
+def test_scaled_model_shapes_batch32_tile_path(bk):
+    """Same head shapes at batch 32: the projections of 1024+ rows run on the tcgen05 tile kernel -- K = 5120 (five chunks
+    of four superblocks), the down projection with K = 17408 (17 chunks, cut along K over several thread blocks), the
+    SwiGLU pair of 2 x 17408 rows with gate and up rows in separate tile halves, weights fed through tensor maps."""
+    cfg = M.CONFIG_HYBRID_64L.with_(n_layers=4, vocab=8192, max_len=32)
+    w = M.synth_weights(cfg, seed=13)
+    B = 32
+    gm = M.DecodeModel(cfg, w, batch=B)
+    info = gm.info()
+    om = OracleModel(cfg, w, batch=B, split_len=info["split_len"], attn_warps=info["attn_warps"])
+    prompt = np.random.default_rng(6).integers(0, cfg.vocab, (2, B)).astype(np.int32)
+    ids_g = ids_o = None
+    for t in range(4):
+        ids_o, _ = om.step(prompt[t] if t < 2 else ids_o)
+        ids_g, _ = gm.step(prompt[t] if t < 2 else ids_g)
+        assert np.array_equal(ids_g, ids_o), f"step {t}"
+    assert_same_bits(gm.logits(), om.logits, "logits")
+    gm.destroy()
+
+
 @pytest.mark.parametrize("interval,n_layers", [(4, 4), (1, 2), (2, 3), (4, 3)])
 def test_persistent_step_equals_per_op_step_and_oracle(bk, interval, n_layers):
     """Batch 1 on one GPU can run as a persistent kernel (phases + device-side barriers, step mode 2).  The same model
