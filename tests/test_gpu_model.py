@@ -223,6 +223,31 @@ def test_prefill_equals_token_by_token(bk, B, T, chunk):
     gm.destroy()
 
 
+@pytest.mark.parametrize("B,T", [(1, 200), (3, 70)])
+def test_long_prefill_across_attention_splits(bk, B, T):
+    """Prompt passes whose columns sit on both sides of attention split boundaries (the split length is well below
+    the prompt length) and, at batch 3, interleave three sequences: the state after bkModelPrefill equals the state after
+    T single decode steps -- same argmax, bit-identical logits, and six identical greedy steps afterwards."""
+    cfg = M.CONFIG_TINY.with_(max_len=256)
+    w = M.synth_weights(cfg, seed=70 + B)
+    prompt = np.random.default_rng(T).integers(0, cfg.vocab, (T, B)).astype(np.int32)
+    ga, gb = M.DecodeModel(cfg, w, batch=B), M.DecodeModel(cfg, w, batch=B)
+    assert ga.info()["split_len"] < T
+    ia, va = ga.prefill(prompt)
+    for t in range(T):
+        ib, vb = gb.step(prompt[t])
+    assert np.array_equal(ia, ib)
+    assert_same_bits(va, vb, "max logit after the prompt")
+    assert_same_bits(ga.logits(), gb.logits(), "logits after the prompt")
+    for t in range(6):
+        ia, _ = ga.step(ia)
+        ib, _ = gb.step(ib)
+        assert np.array_equal(ia, ib), f"step {t} after the prompt"
+    assert_same_bits(ga.logits(), gb.logits(), "logits after 6 more steps")
+    ga.destroy()
+    gb.destroy()
+
+
 @pytest.mark.parametrize("B", [1, 2])
 def test_per_op_runner_equals_step_graph(bk, B):
     """A host that schedules every op itself through cuLaunch (bunker's runner shape) gets the bits of the library's
